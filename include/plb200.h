@@ -1,0 +1,184 @@
+/*
+ * plb200 — C ABI of the B200 (sm_100a) int8 conv / depthwise / fc / sparse_conv kernels.
+ *
+ * This is the boundary a `kCUDA` / `kInt8` target of Paddle-Lite binds: every prepared
+ * object corresponds to what one reference kernel instance holds after PrepareForRun(),
+ * every *_run() to one Run().  Plain pointers and sizes only; no C++ or torch types.
+ *
+ * Conventions
+ *   - every function returns 0 on success or a PLB_E_* code; nothing aborts or throws.
+ *     plb_last_error() gives the message of the last failure on the calling thread.
+ *   - pointers are DEVICE pointers unless the name ends in _h (host).
+ *   - a plb_ctx is bound to one device and one CUDA stream; all work of objects prepared
+ *     on it is enqueued on that stream.  One ctx per host thread / stream; objects are
+ *     not thread-safe.
+ *   - tensors at this boundary use the reference layouts (NCHW activations, OIHW filters,
+ *     [K,N] fc weights) unless a function says NHWC.
+ *   - *_run() calls are asynchronous; plb_ctx_sync() waits and reports kernel-side faults
+ *     (a pipeline wait that ran out) as PLB_E_DEVICE.
+ */
+#ifndef PLB200_H_
+#define PLB200_H_
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define PLB_OK 0
+#define PLB_E_INVALID 1     /* bad argument (null pointer, bad dims, scale-vector length) */
+#define PLB_E_UNSUPPORTED 2 /* valid request this build has no kernel for */
+#define PLB_E_CUDA 3        /* a CUDA runtime / driver call failed */
+#define PLB_E_DEVICE 4      /* a kernel reported a fault through the ctx status word */
+#define PLB_E_NOMEM 5       /* workspace could not be allocated */
+
+/* activation codes = relu_type of the reference GEMM (lite/kernels/x86/conv_compute.cc:257-270) */
+#define PLB_ACT_NONE 0
+#define PLB_ACT_RELU 1
+#define PLB_ACT_RELU6 2 /* bound = act_alpha (ActivationParam::Relu_clipped_coef) */
+#define PLB_ACT_LEAKY 3 /* slope = act_alpha (ActivationParam::Leaky_relu_alpha) */
+
+#define PLB_OUT_F32 0 /* alias fp32_out */
+#define PLB_OUT_I8 1  /* alias int8_out */
+
+/* kernel choice for conv; AUTO is what a caller wants, the others exist for tests */
+#define PLB_IMPL_AUTO 0
+#define PLB_IMPL_DIRECT 1 /* CUDA-core direct convolution */
+#define PLB_IMPL_TC 2     /* tcgen05 implicit GEMM */
+
+typedef struct plb_ctx plb_ctx;
+typedef struct plb_conv plb_conv;
+typedef struct plb_fc plb_fc;
+typedef struct plb_sparse plb_sparse;
+
+/* ------------------------------------------------------------------ context
+ * Replaces Context<TARGET> + the stream the reference keeps per kernel
+ * (lite/core/context.h:430-484, KernelBase::SetContext lite/core/kernel.h:133-136). */
+int plb_ctx_create(int device, void* cuda_stream, plb_ctx** out);
+void plb_ctx_destroy(plb_ctx* ctx);
+/* Wait for the ctx stream; returns PLB_E_DEVICE if any kernel flagged a fault since the
+ * last call (the flag is cleared). */
+int plb_ctx_sync(plb_ctx* ctx);
+/* Optional: hand the ctx a caller-owned scratch buffer (layout staging for the NCHW entry
+ * points).  Without it the ctx grows its own with cudaMalloc on demand.  Replaces the
+ * per-Run TargetMalloc of the im2col buffer (conv_compute.cc:306-310). */
+int plb_ctx_set_workspace(plb_ctx* ctx, void* dptr, size_t bytes);
+/* Bytes of scratch the NCHW entry points of this object need for `batch` images. */
+size_t plb_conv_workspace_bytes(const plb_conv* conv, int batch);
+const char* plb_last_error(void);
+/* Number of kernels this library has launched on the ctx since creation. */
+long plb_ctx_launch_count(const plb_ctx* ctx);
+
+/* ------------------------------------------------------------------ conv2d / depthwise_conv2d
+ * plb_conv_desc carries what operators::ConvParam holds for an int8 kernel
+ * (lite/operators/op_params.h:403-455 + WITH_INT8_CONFIG :39-44 + ActivationParam :331-362). */
+typedef struct plb_conv_desc {
+  int cin, h, w;                 /* input [N,cin,h,w]; N is given per run                */
+  int cout, kh, kw;              /* filter [cout, cin/groups, kh, kw]                     */
+  int stride_h, stride_w;        /* ConvParam::strides                                    */
+  int pad_top, pad_bottom, pad_left, pad_right; /* ConvParam::paddings (4 entries)        */
+  int dil_h, dil_w;              /* ConvParam::dilations                                  */
+  int groups;                    /* groups == cin == cout selects the depthwise kernel    */
+  int act;                       /* PLB_ACT_*                                             */
+  float act_alpha;
+  float in_scale;                /* ConvParam::input_scale                                */
+  float out_scale;               /* ConvParam::output_scale (int8 out only)               */
+  int out_dtype;                 /* PLB_OUT_F32 | PLB_OUT_I8                              */
+  int leaky_compat;              /* !=0: int8-out leaky slope is alpha/out_scale as in
+                                    conv_compute.cc:394; 0: slope is alpha               */
+  int impl;                      /* PLB_IMPL_*                                            */
+} plb_conv_desc;
+
+/* = Conv2dCompute<kInt8,*>::PrepareForRun (conv_compute.cc:216-289, :344-420): copies the
+ * filter (OIHW, host), expands weight_scale (n_wscale must be 1 or cout, else
+ * PLB_E_INVALID like the reference's LOG(FATAL) at :242-244), folds scales and bias. */
+int plb_conv_prepare(plb_ctx* ctx, const plb_conv_desc* desc, const int8_t* filter_h,
+                     const float* wscale_h, int n_wscale, const float* bias_h /* nullable */,
+                     plb_conv** out);
+/* = Conv2dCompute<kInt8,*>::Run (conv_compute.cc:292-341, :423-472).
+ * x [batch,cin,h,w] int8 NCHW; y [batch,cout,ho,wo] float or int8 NCHW. */
+int plb_conv_run(plb_conv* conv, const int8_t* x, void* y, int batch);
+/* Same arithmetic on channels-last tensors, no layout staging: x [batch,h,w,cin] int8 with
+ * cin a multiple of 32 (depthwise: 16), y [batch,ho,wo,cout]. */
+int plb_conv_run_nhwc(plb_conv* conv, const int8_t* x, void* y, int batch);
+/* Test hook: the raw int32 accumulators, NCHW [batch,cout,ho,wo] (bit-exact check). */
+int plb_conv_acc_i32(plb_conv* conv, const int8_t* x, int32_t* acc, int batch);
+/* conv (fp32 value, no activation of its own) + fp32 residual + ReLU, then optionally the
+ * calib fp32->int8 step of the next layer, in one pass.  NHWC.  Fuses what the reference
+ * graph runs as conv(fp32_out) -> elementwise_add -> relu -> calib
+ * (lite/backends/x86/math/calib.cc:25-151 for the last step).
+ *   residual [batch,ho,wo,cout] float (nullable = no add)
+ *   y_f32    [batch,ho,wo,cout] float (nullable = not stored)
+ *   y_i8     [batch,ho,wo,cout] int8  (nullable = not stored), q = calib(y, next_scale) */
+int plb_conv_run_nhwc_add_relu(plb_conv* conv, const int8_t* x, const float* residual,
+                               float* y_f32, int8_t* y_i8, float next_scale, int batch);
+int plb_conv_out_dims(const plb_conv* conv, int* ho, int* wo);
+void plb_conv_destroy(plb_conv* conv);
+
+/* ------------------------------------------------------------------ fc
+ * = FcCompute<kInt8,*> (lite/kernels/x86/fc_compute.cc:176-269) with scale and bias
+ * indexed by output feature as lite/kernels/arm/fc_compute.cc:207-260 defines it.
+ * w_h is FcParam::w, [K,N] row-major int8 on the host; n_wscale is 1 or N. */
+int plb_fc_prepare(plb_ctx* ctx, int k, int n, int act, float act_alpha, float in_scale,
+                   float out_scale, int out_dtype, const int8_t* w_h, const float* wscale_h,
+                   int n_wscale, const float* bias_h /* nullable */, plb_fc** out);
+/* x [m,k] int8, y [m,n] float or int8. */
+int plb_fc_run(plb_fc* fc, const int8_t* x, void* y, int m);
+int plb_fc_acc_i32(plb_fc* fc, const int8_t* x, int32_t* acc, int m);
+void plb_fc_destroy(plb_fc* fc);
+
+/* ------------------------------------------------------------------ sparse_conv2d (1x1)
+ * = SparseConvCompute<*> (lite/kernels/arm/sparse_conv_compute.cc:33-267) over the encoding
+ * built by sparse_conv_detect_pass (lite/core/optimizer/mir/sparse_conv_detect_pass.cc:35-301):
+ *   nonzero_weights_h  SparseConvParam::nonzero_weights (int8 or float), n_weights entries
+ *   oc_nonzeros_h      SparseConvParam::oc_nonzeros, [cout] cumulative counts
+ *   diffs_h            SparseConvParam::diffs, byte offsets scaled by hw = ho*wo
+ *   first_ic, flag_semi  the attributes of the same names
+ * is_int8 == 0 is the fp32 kernel (alias def: fp32 in, fp32 out; weights padded to
+ * multiples of 4 per channel unless flag_semi); is_int8 != 0 takes int8 input and
+ * out_dtype picks int8_fp32_out / int8_int8_out.  The batch dimension is honoured. */
+typedef struct plb_sparse_desc {
+  int cin, cout, h, w;
+  int is_int8;
+  int out_dtype;
+  int flag_semi, first_ic;
+  int act;
+  float act_alpha;
+  float in_scale, out_scale;
+  int leaky_compat;
+  int impl; /* PLB_IMPL_AUTO | PLB_IMPL_DIRECT (walk the encoding) | PLB_IMPL_TC (densified) */
+} plb_sparse_desc;
+int plb_sparse_prepare(plb_ctx* ctx, const plb_sparse_desc* desc, const void* nonzero_weights_h,
+                       int n_weights, const uint32_t* oc_nonzeros_h, const int32_t* diffs_h,
+                       int n_diffs, const float* wscale_h, int n_wscale,
+                       const float* bias_h /* nullable */, plb_sparse** out);
+/* x [batch,cin,h,w] (int8 or float), y [batch,cout,h,w] (float or int8), NCHW. */
+int plb_sparse_run(plb_sparse* sp, const void* x, void* y, int batch);
+void plb_sparse_destroy(plb_sparse* sp);
+
+/* ------------------------------------------------------------------ glue between int8 layers
+ * calib fp32 -> int8 (lite/backends/x86/math/calib.cc:25-151): q = sat(rne(max(x/scale,-127))). */
+int plb_calib_f32_to_i8(plb_ctx* ctx, const float* x, int8_t* q, size_t n, float scale);
+/* calib int8 -> fp32 (calib.cc:153-239). */
+int plb_calib_i8_to_f32(plb_ctx* ctx, const int8_t* q, float* y, size_t n, float scale);
+/* layout staging: [n,c,h,w] <-> [n,h,w,cpad] (extra channels are zero / dropped). */
+int plb_nchw_to_nhwc_i8(plb_ctx* ctx, const int8_t* x, int8_t* y, int n, int c, int h, int w,
+                        int cpad);
+int plb_nhwc_to_nchw(plb_ctx* ctx, const void* x, void* y, int n, int c, int h, int w,
+                     int elem_bytes);
+/* fp32 NCHW image -> int8 NHWC with cpad channels: calib and layout staging in one pass. */
+int plb_calib_nchw_f32_to_nhwc_i8(plb_ctx* ctx, const float* x, int8_t* y, int n, int c, int h,
+                                  int w, int cpad, float scale);
+/* max pooling on int8 NHWC, square window, symmetric padding (pool2d, max). */
+int plb_maxpool_nhwc_i8(plb_ctx* ctx, const int8_t* x, int8_t* y, int n, int c, int h, int w,
+                        int k, int stride, int pad);
+/* global average pool of fp32 NHWC [n,h*w,c] -> [n,c], then calib to int8 when q != NULL. */
+int plb_global_avgpool_nhwc_f32(plb_ctx* ctx, const float* x, float* y, int8_t* q, int n, int hw,
+                                int c, float scale);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* PLB200_H_ */

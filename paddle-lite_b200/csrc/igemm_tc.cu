@@ -1,0 +1,561 @@
+// int8 x int8 -> int32 implicit GEMM on the sm_100a tensor cores (tcgen05.mma kind::i8,
+// accumulators in tensor memory), operands staged through shared memory by TMA
+// (cp.async.bulk.tensor, tiled for flat GEMMs and filters, im2col mode for convolutions;
+// never cluster multicast), fused dequant / bias / activation / requant epilogue.
+//
+// This is the B200 replacement for the reference's im2col<int8_t> + gemm_s8u8 pair
+// (lite/backends/x86/math/avx/conv_utils.cc:1349-1398,
+//  lite/backends/x86/math/gemm_s8u8_compute.h:65-106, gemm_s8u8_kernel.cc:353-891).
+//
+// CTA = 6 warps:  warps 0-3 epilogue (one TMEM lane quadrant each),
+//                 warp 4 TMA producer (one elected lane),
+//                 warp 5 TMEM allocation + MMA issue (one elected lane).
+// Tile = 128 output pixels x BN output channels, K consumed KC bytes per pipeline stage
+// (KC = 32/64/128 = the TMA swizzle span), 32 bytes of K per tcgen05.mma.
+// Every mbarrier wait is bounded; a wait that runs out records a fault in the ctx status
+// word and the CTA drains and exits instead of hanging.
+#include "igemm_tc.cuh"
+
+#include <cstdlib>
+
+namespace plb {
+
+namespace {
+
+constexpr int kTileM = 128;
+constexpr int kMaxStages = 8;
+constexpr int kThreads = 192;
+constexpr int kCtrlBytes = 256 + 2 * 256 * 4;  // barriers + tmem slot, then scale/bias staging
+constexpr uint32_t kWaitLimit = 1u << 22;      // polls before a wait is declared lost
+
+struct IgemmArgs {
+  int im2col;
+  int m_total, cout;
+  int bn, kc, cchunks, ksteps, stages;
+  int taps, kw;
+  int ho, wo, stride_h, stride_w, pad_t, pad_l, dil_h, dil_w;
+  int tiles_n;
+  int out_mode, ldy;
+  void* y;
+  const float* scale;
+  const float* bias;
+  int act;
+  float alpha;
+  const float* residual;
+  float* y_f32;
+  int8_t* y_i8;
+  float inv_next_scale;
+  int* status;
+};
+
+// ---------------------------------------------------------------- PTX wrappers
+__device__ __forceinline__ uint32_t smem_u32(const void* p) {
+  return static_cast<uint32_t>(__cvta_generic_to_shared(p));
+}
+__device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) {
+  asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count) : "memory");
+}
+__device__ __forceinline__ void mbar_expect_tx(uint32_t bar, uint32_t bytes) {
+  asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes)
+               : "memory");
+}
+__device__ __forceinline__ uint32_t mbar_try_wait(uint32_t bar, uint32_t parity) {
+  uint32_t ok;
+  asm volatile(
+      "{\n\t"
+      ".reg .pred p;\n\t"
+      "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+      "selp.u32 %0, 1, 0, p;\n\t"
+      "}"
+      : "=r"(ok)
+      : "r"(bar), "r"(parity)
+      : "memory");
+  return ok;
+}
+// Bounded wait.  Returns false (and records `code`) when the limit is reached or another
+// role of this CTA has already given up.
+__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int* abort_flag,
+                                          int* status, int code) {
+  for (uint32_t it = 0; it < kWaitLimit; ++it) {
+    if (mbar_try_wait(bar, parity)) return true;
+    if (it > 64) {
+      __nanosleep(32);
+      if ((it & 255u) == 0 && *abort_flag) return false;
+    }
+  }
+  *abort_flag = 1;
+  if (atomicCAS(status, 0, code) == 0) status[1] = static_cast<int>(blockIdx.x);
+  return false;
+}
+__device__ __forceinline__ void tma_load_2d(uint32_t dst, const CUtensorMap* map, uint32_t bar,
+                                            int c0, int c1) {
+  asm volatile(
+      "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes"
+      " [%0], [%1, {%3, %4}], [%2];" ::"r"(dst),
+      "l"(reinterpret_cast<uint64_t>(map)), "r"(bar), "r"(c0), "r"(c1)
+      : "memory");
+}
+__device__ __forceinline__ void tma_load_im2col_4d(uint32_t dst, const CUtensorMap* map,
+                                                   uint32_t bar, int c, int w, int h, int n,
+                                                   uint16_t off_w, uint16_t off_h) {
+  asm volatile(
+      "cp.async.bulk.tensor.4d.shared::cluster.global.im2col.mbarrier::complete_tx::bytes"
+      " [%0], [%1, {%3, %4, %5, %6}], [%2], {%7, %8};" ::"r"(dst),
+      "l"(reinterpret_cast<uint64_t>(map)), "r"(bar), "r"(c), "r"(w), "r"(h), "r"(n), "h"(off_w),
+      "h"(off_h)
+      : "memory");
+}
+__device__ __forceinline__ void tc_fence_before() {
+  asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+}
+__device__ __forceinline__ void tc_fence_after() {
+  asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+}
+__device__ __forceinline__ void tc_mma_i8(uint32_t d_tmem, uint64_t adesc, uint64_t bdesc,
+                                          uint32_t idesc, uint32_t accumulate) {
+  asm volatile(
+      "{\n\t"
+      ".reg .pred p;\n\t"
+      "setp.ne.b32 p, %4, 0;\n\t"
+      "tcgen05.mma.cta_group::1.kind::i8 [%0], %1, %2, %3, p;\n\t"
+      "}" ::"r"(d_tmem),
+      "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate)
+      : "memory");
+}
+__device__ __forceinline__ void tc_commit(uint32_t bar) {
+  asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar)
+               : "memory");
+}
+__device__ __forceinline__ void tc_ld16(uint32_t taddr, uint32_t (&r)[16]) {
+  asm volatile(
+      "tcgen05.ld.sync.aligned.32x32b.x16.b32 "
+      "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15}, [%16];"
+      : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]),
+        "=r"(r[7]), "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]),
+        "=r"(r[14]), "=r"(r[15])
+      : "r"(taddr)
+      : "memory");
+}
+__device__ __forceinline__ void tc_wait_ld() {
+  asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+}
+
+// Shared-memory matrix descriptor of a K-major tile whose rows are `kc` bytes long and
+// swizzled with span `kc` (32/64/128): groups of 8 rows are 8*kc bytes apart.
+__device__ __forceinline__ uint64_t make_smem_desc(uint32_t addr, int kc) {
+  const uint32_t layout = kc == 128 ? 2u : (kc == 64 ? 4u : 6u);
+  const uint32_t lo = ((addr >> 4) & 0x3FFFu) | (1u << 16);
+  const uint32_t hi = ((static_cast<uint32_t>(8 * kc) >> 4) & 0x3FFFu) | (1u << 14) | (layout << 29);
+  return (static_cast<uint64_t>(hi) << 32) | lo;
+}
+
+// ---------------------------------------------------------------- epilogue store of 16 columns
+__device__ __forceinline__ void epilogue_store16(const IgemmArgs& a, const uint32_t (&r)[16],
+                                                 long row, int col, const float* s_scale,
+                                                 const float* s_bias, int local_col) {
+  const int ncols = a.cout - col < 16 ? a.cout - col : 16;
+  if (ncols <= 0) return;
+  if (a.out_mode == OUT_ACC) {
+    int32_t* dst = static_cast<int32_t*>(a.y) + row * a.ldy + col;
+    if (ncols == 16 && (a.ldy & 3) == 0) {
+#pragma unroll
+      for (int j = 0; j < 16; j += 4)
+        *reinterpret_cast<int4*>(dst + j) =
+            make_int4((int)r[j], (int)r[j + 1], (int)r[j + 2], (int)r[j + 3]);
+    } else {
+      for (int j = 0; j < ncols; ++j) dst[j] = (int)r[j];
+    }
+    return;
+  }
+  float v[16];
+#pragma unroll
+  for (int j = 0; j < 16; ++j)
+    v[j] = fmaf(static_cast<float>(static_cast<int>(r[j])), s_scale[local_col + j],
+                s_bias[local_col + j]);
+  if (a.out_mode == OUT_ADD_RELU) {
+    if (a.residual != nullptr) {
+      const float* res = a.residual + row * a.ldy + col;
+      if (ncols == 16 && (a.ldy & 3) == 0) {
+#pragma unroll
+        for (int j = 0; j < 16; j += 4) {
+          const float4 t = *reinterpret_cast<const float4*>(res + j);
+          v[j] += t.x; v[j + 1] += t.y; v[j + 2] += t.z; v[j + 3] += t.w;
+        }
+      } else {
+        for (int j = 0; j < ncols; ++j) v[j] += res[j];
+      }
+    }
+#pragma unroll
+    for (int j = 0; j < 16; ++j) v[j] = v[j] > 0.f ? v[j] : 0.f;
+    if (a.y_f32 != nullptr) {
+      float* dst = a.y_f32 + row * a.ldy + col;
+      if (ncols == 16 && (a.ldy & 3) == 0) {
+#pragma unroll
+        for (int j = 0; j < 16; j += 4)
+          *reinterpret_cast<float4*>(dst + j) = make_float4(v[j], v[j + 1], v[j + 2], v[j + 3]);
+      } else {
+        for (int j = 0; j < ncols; ++j) dst[j] = v[j];
+      }
+    }
+    if (a.y_i8 != nullptr) {
+      int8_t* dst = a.y_i8 + row * a.ldy + col;
+      int q[16];
+#pragma unroll
+      for (int j = 0; j < 16; ++j) q[j] = calib_i8(v[j], a.inv_next_scale);
+      if (ncols == 16 && (a.ldy & 15) == 0) {
+        *reinterpret_cast<uint4*>(dst) =
+            make_uint4(pack4(q[0], q[1], q[2], q[3]), pack4(q[4], q[5], q[6], q[7]),
+                       pack4(q[8], q[9], q[10], q[11]), pack4(q[12], q[13], q[14], q[15]));
+      } else {
+        for (int j = 0; j < ncols; ++j) dst[j] = static_cast<int8_t>(q[j]);
+      }
+    }
+    return;
+  }
+#pragma unroll
+  for (int j = 0; j < 16; ++j) v[j] = act_apply(v[j], a.act, a.alpha);
+  if (a.out_mode == OUT_F32) {
+    float* dst = static_cast<float*>(a.y) + row * a.ldy + col;
+    if (ncols == 16 && (a.ldy & 3) == 0) {
+#pragma unroll
+      for (int j = 0; j < 16; j += 4)
+        *reinterpret_cast<float4*>(dst + j) = make_float4(v[j], v[j + 1], v[j + 2], v[j + 3]);
+    } else {
+      for (int j = 0; j < ncols; ++j) dst[j] = v[j];
+    }
+  } else {  // OUT_I8
+    int8_t* dst = static_cast<int8_t*>(a.y) + row * a.ldy + col;
+    int q[16];
+#pragma unroll
+    for (int j = 0; j < 16; ++j) q[j] = requant_i8(v[j]);
+    if (ncols == 16 && (a.ldy & 15) == 0) {
+      *reinterpret_cast<uint4*>(dst) =
+          make_uint4(pack4(q[0], q[1], q[2], q[3]), pack4(q[4], q[5], q[6], q[7]),
+                     pack4(q[8], q[9], q[10], q[11]), pack4(q[12], q[13], q[14], q[15]));
+    } else if (ncols == 16 && (a.ldy & 3) == 0) {
+#pragma unroll
+      for (int j = 0; j < 16; j += 4)
+        *reinterpret_cast<uint32_t*>(dst + j) = pack4(q[j], q[j + 1], q[j + 2], q[j + 3]);
+    } else {
+      for (int j = 0; j < ncols; ++j) dst[j] = static_cast<int8_t>(q[j]);
+    }
+  }
+}
+
+// ---------------------------------------------------------------- the kernel
+__global__ void __launch_bounds__(kThreads)
+    igemm_i8_tc_kernel(const __grid_constant__ CUtensorMap tmA,
+                       const __grid_constant__ CUtensorMap tmB, const IgemmArgs a) {
+  extern __shared__ uint8_t smem_raw[];
+  const uint32_t raw_addr = smem_u32(smem_raw);
+  uint8_t* smem = smem_raw + (((raw_addr + 1023u) & ~1023u) - raw_addr);
+
+  const int stage_a = kTileM * a.kc;
+  const int stage_b = a.bn * a.kc;
+  const int stage_bytes = stage_a + stage_b;
+  uint8_t* ctrl = smem + a.stages * stage_bytes;
+  uint64_t* full_bar = reinterpret_cast<uint64_t*>(ctrl);
+  uint64_t* empty_bar = full_bar + kMaxStages;
+  uint64_t* accum_bar = empty_bar + kMaxStages;
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(accum_bar + 1);
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
+  float* s_scale = reinterpret_cast<float*>(ctrl + 256);
+  float* s_bias = s_scale + 256;
+
+  const int warp = threadIdx.x >> 5;
+  const int lane = threadIdx.x & 31;
+  const int tile_n = blockIdx.x % a.tiles_n;
+  const int tile_m = blockIdx.x / a.tiles_n;
+  const int m0 = tile_m * kTileM;
+  const int n0 = tile_n * a.bn;
+
+  // TMEM columns: power of two >= max(32, bn)
+  uint32_t tmem_cols = 32;
+  while (tmem_cols < static_cast<uint32_t>(a.bn)) tmem_cols <<= 1;
+
+  if (threadIdx.x == 4 * 32) {
+    for (int s = 0; s < a.stages; ++s) {
+      mbar_init(smem_u32(&full_bar[s]), 1);
+      mbar_init(smem_u32(&empty_bar[s]), 1);
+    }
+    mbar_init(smem_u32(accum_bar), 1);
+    *abort_flag = 0;
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    asm volatile("prefetch.tensormap [%0];" ::"l"(reinterpret_cast<uint64_t>(&tmA)) : "memory");
+    asm volatile("prefetch.tensormap [%0];" ::"l"(reinterpret_cast<uint64_t>(&tmB)) : "memory");
+  }
+  if (warp == 5) {
+    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(
+                     smem_u32(tmem_slot)),
+                 "r"(tmem_cols)
+                 : "memory");
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = *tmem_slot;
+
+  if (warp == 4) {
+    // ------------------------------------------------------------ TMA producer
+    if (lane == 0) {
+      int cn = 0, ch = 0, cw = 0;
+      if (a.im2col) {
+        const int q = m0 % a.wo;
+        const int p = (m0 / a.wo) % a.ho;
+        cn = m0 / (a.wo * a.ho);
+        cw = q * a.stride_w - a.pad_l;
+        ch = p * a.stride_h - a.pad_t;
+      }
+      for (int ks = 0; ks < a.ksteps; ++ks) {
+        const int s = ks % a.stages;
+        const uint32_t parity = ((ks / a.stages) & 1) ^ 1;
+        if (!mbar_wait(smem_u32(&empty_bar[s]), parity, abort_flag, a.status, FAULT_WAIT_EMPTY))
+          break;
+        const uint32_t bar = smem_u32(&full_bar[s]);
+        mbar_expect_tx(bar, static_cast<uint32_t>(stage_bytes));
+        const uint32_t dst_a = smem_u32(smem + s * stage_bytes);
+        const uint32_t dst_b = dst_a + stage_a;
+        const int tap = ks / a.cchunks;
+        const int c0 = (ks - tap * a.cchunks) * a.kc;
+        if (a.im2col) {
+          const int r = tap / a.kw;
+          const int sx = tap - r * a.kw;
+          tma_load_im2col_4d(dst_a, &tmA, bar, c0, cw, ch, cn,
+                             static_cast<uint16_t>(sx * a.dil_w),
+                             static_cast<uint16_t>(r * a.dil_h));
+        } else {
+          tma_load_2d(dst_a, &tmA, bar, c0, m0);
+        }
+        tma_load_2d(dst_b, &tmB, bar, tap * a.cchunks * a.kc + c0, n0);
+      }
+    }
+  } else if (warp == 5) {
+    // ------------------------------------------------------------ MMA issuer
+    if (lane == 0) {
+      // instruction descriptor: D=s32, A=B=s8, both K-major, N=bn, M=128
+      const uint32_t idesc = (2u << 4) | (1u << 7) | (1u << 10) |
+                             (static_cast<uint32_t>(a.bn >> 3) << 17) |
+                             (static_cast<uint32_t>(kTileM >> 4) << 24);
+      const int mma_per_stage = a.kc / 32;
+      bool ok = true;
+      for (int ks = 0; ks < a.ksteps && ok; ++ks) {
+        const int s = ks % a.stages;
+        const uint32_t parity = (ks / a.stages) & 1;
+        ok = mbar_wait(smem_u32(&full_bar[s]), parity, abort_flag, a.status, FAULT_WAIT_FULL);
+        if (!ok) break;
+        tc_fence_after();
+        const uint32_t addr_a = smem_u32(smem + s * stage_bytes);
+        const uint64_t adesc = make_smem_desc(addr_a, a.kc);
+        const uint64_t bdesc = make_smem_desc(addr_a + stage_a, a.kc);
+        for (int j = 0; j < mma_per_stage; ++j) {
+          // advance 32 bytes of K inside the swizzle span: +2 in the (addr >> 4) field
+          tc_mma_i8(tmem_base, adesc + 2u * j, bdesc + 2u * j, idesc, (ks | j) != 0 ? 1u : 0u);
+        }
+        tc_commit(smem_u32(&empty_bar[s]));  // frees the stage when these MMAs retire
+      }
+      tc_commit(smem_u32(accum_bar));  // accumulator complete (or drained on a fault)
+    }
+  } else {
+    // ------------------------------------------------------------ epilogue warps 0..3
+    if (a.out_mode != OUT_ACC) {
+      for (int i = threadIdx.x; i < a.bn; i += 128) {
+        const int c = n0 + i;
+        s_scale[i] = c < a.cout ? a.scale[c] : 0.f;
+        s_bias[i] = c < a.cout ? a.bias[c] : 0.f;
+      }
+    }
+    asm volatile("bar.sync 1, 128;" ::: "memory");
+    const bool ok = mbar_wait(smem_u32(accum_bar), 0, abort_flag, a.status, FAULT_WAIT_ACCUM);
+    tc_fence_after();
+    if (ok) {
+      const long row = static_cast<long>(m0) + warp * 32 + lane;
+      const uint32_t lane_addr = tmem_base + (static_cast<uint32_t>(warp * 32) << 16);
+      for (int c = 0; c < a.bn; c += 16) {
+        if (n0 + c >= a.cout) break;  // warp-uniform
+        uint32_t r[16];
+        tc_ld16(lane_addr + static_cast<uint32_t>(c), r);
+        tc_wait_ld();
+        if (row < a.m_total) epilogue_store16(a, r, row, n0 + c, s_scale, s_bias, c);
+      }
+    }
+  }
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 5) {
+    __syncwarp();
+    tc_fence_after();
+    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base),
+                 "r"(tmem_cols)
+                 : "memory");
+  }
+}
+
+// ---------------------------------------------------------------- host side
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*,
+                                  const cuuint64_t*, const cuuint64_t*, const cuuint32_t*,
+                                  const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
+                                  CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+typedef CUresult (*EncodeIm2colFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*,
+                                   const cuuint64_t*, const cuuint64_t*, const int*, const int*,
+                                   cuuint32_t, cuuint32_t, const cuuint32_t*,
+                                   CUtensorMapInterleave, CUtensorMapSwizzle,
+                                   CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+EncodeTiledFn g_encode_tiled = nullptr;
+EncodeIm2colFn g_encode_im2col = nullptr;
+
+int load_driver_entry_points() {
+  if (g_encode_tiled && g_encode_im2col) return PLB_OK;
+  void* fn = nullptr;
+  cudaDriverEntryPointQueryResult qres;
+  cudaError_t e = cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &fn, cudaEnableDefault, &qres);
+  if (e != cudaSuccess || qres != cudaDriverEntryPointSuccess || fn == nullptr)
+    return fail(PLB_E_CUDA, "cuTensorMapEncodeTiled is not available from this driver");
+  g_encode_tiled = reinterpret_cast<EncodeTiledFn>(fn);
+  fn = nullptr;
+  e = cudaGetDriverEntryPoint("cuTensorMapEncodeIm2col", &fn, cudaEnableDefault, &qres);
+  if (e != cudaSuccess || qres != cudaDriverEntryPointSuccess || fn == nullptr)
+    return fail(PLB_E_CUDA, "cuTensorMapEncodeIm2col is not available from this driver");
+  g_encode_im2col = reinterpret_cast<EncodeIm2colFn>(fn);
+  return PLB_OK;
+}
+
+CUtensorMapSwizzle swizzle_for(int kc) {
+  return kc == 128 ? CU_TENSOR_MAP_SWIZZLE_128B
+                   : (kc == 64 ? CU_TENSOR_MAP_SWIZZLE_64B : CU_TENSOR_MAP_SWIZZLE_32B);
+}
+
+int env_int(const char* name, int dflt) {
+  const char* v = std::getenv(name);
+  return v && *v ? std::atoi(v) : dflt;
+}
+
+int pick_kc(int cin_pad) { return cin_pad % 128 == 0 ? 128 : (cin_pad % 64 == 0 ? 64 : 32); }
+
+}  // namespace
+
+bool igemm_tc_supported(const IgemmProblem& p, std::string* why) {
+  auto no = [&](const char* msg) {
+    if (why) *why = msg;
+    return false;
+  };
+  if (p.cin_pad % 32 != 0) return no("row length (padded input channels) must be a multiple of 32");
+  if (p.m_total <= 0 || p.cout <= 0) return no("empty problem");
+  if ((reinterpret_cast<uintptr_t>(p.a) & 15) || (reinterpret_cast<uintptr_t>(p.b) & 15))
+    return no("operand base addresses must be 16-byte aligned");
+  if (p.im2col) {
+    if (p.stride_h < 1 || p.stride_h > 8 || p.stride_w < 1 || p.stride_w > 8)
+      return no("im2col traversal stride must be 1..8");
+    const int up_w = p.pad_r - (p.kw - 1) * p.dil_w, up_h = p.pad_b - (p.kh - 1) * p.dil_h;
+    if (p.pad_l > 128 || p.pad_t > 128 || up_w < -128 || up_w > 127 || up_h < -128 || up_h > 127)
+      return no("im2col bounding-box corner outside [-128,127]");
+    if ((p.kw - 1) * p.dil_w > 65535 || (p.kh - 1) * p.dil_h > 65535) return no("tap offset too large");
+  }
+  return true;
+}
+
+int igemm_tc_launch(plb_ctx* ctx, const IgemmProblem& p) {
+  std::string why;
+  if (!igemm_tc_supported(p, &why)) return fail(PLB_E_UNSUPPORTED, "tensor-core path: %s", why.c_str());
+  int rc = load_driver_entry_points();
+  if (rc) return rc;
+
+  IgemmArgs a;
+  memset(&a, 0, sizeof(a));
+  a.im2col = p.im2col;
+  a.m_total = p.m_total;
+  a.cout = p.cout;
+  a.kc = pick_kc(p.cin_pad);
+  a.cchunks = p.cin_pad / a.kc;
+  a.taps = p.im2col ? p.kh * p.kw : 1;
+  a.kw = p.im2col ? p.kw : 1;
+  a.ksteps = a.taps * a.cchunks;
+  const int cout16 = (p.cout + 15) / 16 * 16;
+  int bn = cout16 < 256 ? cout16 : 256;
+  // small problems: shrink the channel tile until the grid covers the SMs
+  const int tiles_m = (p.m_total + kTileM - 1) / kTileM;
+  while (bn > 32 && tiles_m * ((cout16 + bn - 1) / bn) < ctx->sm_count && (bn / 2) % 16 == 0) bn /= 2;
+  bn = env_int("PLB_TC_BN", bn);
+  if (bn > cout16) bn = cout16;
+  if (bn < 16 || bn > 256 || bn % 16) return fail(PLB_E_INVALID, "bad channel tile %d", bn);
+  a.bn = bn;
+  a.tiles_n = (p.cout + bn - 1) / bn;
+  const int stage_bytes = (kTileM + bn) * a.kc;
+  const int budget = bn > 128 ? 100 * 1024 : 72 * 1024;
+  int stages = budget / stage_bytes;
+  stages = env_int("PLB_TC_STAGES", stages);
+  if (stages > a.ksteps) stages = a.ksteps;
+  if (stages > kMaxStages) stages = kMaxStages;
+  if (stages < 1) stages = 1;
+  a.stages = stages;
+  a.ho = p.ho; a.wo = p.wo;
+  a.stride_h = p.stride_h; a.stride_w = p.stride_w;
+  a.pad_t = p.pad_t; a.pad_l = p.pad_l;
+  a.dil_h = p.dil_h; a.dil_w = p.dil_w;
+  a.out_mode = p.out_mode;
+  a.ldy = p.ldy;
+  a.y = p.y;
+  a.scale = p.epi.scale; a.bias = p.epi.bias; a.act = p.epi.act; a.alpha = p.epi.alpha;
+  a.residual = p.residual; a.y_f32 = p.y_f32; a.y_i8 = p.y_i8;
+  a.inv_next_scale = p.inv_next_scale;
+  a.status = ctx->d_status;
+
+  alignas(64) CUtensorMap tmA;
+  alignas(64) CUtensorMap tmB;
+  const CUtensorMapSwizzle sw = swizzle_for(a.kc);
+  {
+    // filter: [cout, taps*cin_pad] bytes, box = kc x bn
+    cuuint64_t dims[2] = {static_cast<cuuint64_t>(a.taps) * p.cin_pad, static_cast<cuuint64_t>(p.cout)};
+    cuuint64_t strides[1] = {static_cast<cuuint64_t>(a.taps) * p.cin_pad};
+    cuuint32_t box[2] = {static_cast<cuuint32_t>(a.kc), static_cast<cuuint32_t>(bn)};
+    cuuint32_t estr[2] = {1, 1};
+    CUresult r = g_encode_tiled(&tmB, CU_TENSOR_MAP_DATA_TYPE_UINT8, 2, const_cast<int8_t*>(p.b), dims,
+                                strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE, sw,
+                                CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    if (r != CUDA_SUCCESS) return fail(PLB_E_CUDA, "cuTensorMapEncodeTiled(filter) failed: %d", (int)r);
+  }
+  if (!p.im2col) {
+    cuuint64_t dims[2] = {static_cast<cuuint64_t>(p.cin_pad), static_cast<cuuint64_t>(p.m_total)};
+    cuuint64_t strides[1] = {static_cast<cuuint64_t>(p.cin_pad)};
+    cuuint32_t box[2] = {static_cast<cuuint32_t>(a.kc), static_cast<cuuint32_t>(kTileM)};
+    cuuint32_t estr[2] = {1, 1};
+    CUresult r = g_encode_tiled(&tmA, CU_TENSOR_MAP_DATA_TYPE_UINT8, 2, const_cast<int8_t*>(p.a), dims,
+                                strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE, sw,
+                                CU_TENSOR_MAP_L2_PROMOTION_L2_128B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    if (r != CUDA_SUCCESS) return fail(PLB_E_CUDA, "cuTensorMapEncodeTiled(activations) failed: %d", (int)r);
+  } else {
+    cuuint64_t dims[4] = {static_cast<cuuint64_t>(p.cin_pad), static_cast<cuuint64_t>(p.w),
+                          static_cast<cuuint64_t>(p.h), static_cast<cuuint64_t>(p.batch)};
+    cuuint64_t strides[3] = {static_cast<cuuint64_t>(p.cin_pad),
+                             static_cast<cuuint64_t>(p.cin_pad) * p.w,
+                             static_cast<cuuint64_t>(p.cin_pad) * p.w * p.h};
+    int lower[2] = {-p.pad_l, -p.pad_t};
+    int upper[2] = {p.pad_r - (p.kw - 1) * p.dil_w, p.pad_b - (p.kh - 1) * p.dil_h};
+    cuuint32_t estr[4] = {1, static_cast<cuuint32_t>(p.stride_w), static_cast<cuuint32_t>(p.stride_h), 1};
+    CUresult r = g_encode_im2col(&tmA, CU_TENSOR_MAP_DATA_TYPE_UINT8, 4, const_cast<int8_t*>(p.a), dims,
+                                 strides, lower, upper, static_cast<cuuint32_t>(a.kc),
+                                 static_cast<cuuint32_t>(kTileM), estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                                 sw, CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
+                                 CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    if (r != CUDA_SUCCESS) return fail(PLB_E_CUDA, "cuTensorMapEncodeIm2col failed: %d", (int)r);
+  }
+
+  const size_t smem = static_cast<size_t>(stages) * stage_bytes + kCtrlBytes + 1024;
+  if (smem > 227 * 1024) return fail(PLB_E_UNSUPPORTED, "pipeline needs %zu bytes of shared memory", smem);
+  static size_t configured_smem[64] = {0};  // per device: the attribute belongs to the context
+  const int dev_slot = ctx->device & 63;
+  if (smem > configured_smem[dev_slot]) {
+    PLB_CUDA(cudaFuncSetAttribute(igemm_i8_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                  227 * 1024));
+    configured_smem[dev_slot] = 227 * 1024;
+  }
+  const long grid = static_cast<long>(tiles_m) * a.tiles_n;
+  if (grid > 0x7fffffffL) return fail(PLB_E_UNSUPPORTED, "grid too large");
+  igemm_i8_tc_kernel<<<static_cast<unsigned>(grid), kThreads, smem, ctx->stream>>>(tmA, tmB, a);
+  PLB_CUDA(cudaGetLastError());
+  ctx->launches++;
+  return PLB_OK;
+}
+
+}  // namespace plb

@@ -1,0 +1,443 @@
+// CUDA-core kernels: direct / depthwise / sparse convolutions and the fp32<->int8 glue.
+// All of them are bandwidth-oriented: coalesced channel-contiguous (NHWC) or
+// pixel-contiguous (NCHW sparse) accesses, packed-byte arithmetic, no atomics.
+#include "kernels_simple.cuh"
+
+#include "igemm_tc.cuh"
+
+namespace plb {
+
+namespace {
+
+constexpr int kBlock = 256;
+
+struct OutDev {
+  int mode;
+  void* y;
+  int ldy;
+  const float* scale;
+  const float* bias;
+  int act;
+  float alpha;
+  const float* residual;
+  float* y_f32;
+  int8_t* y_i8;
+  float inv_next_scale;
+};
+
+OutDev to_dev(const OutSpec& o) {
+  OutDev d;
+  d.mode = o.mode; d.y = o.y; d.ldy = o.ldy;
+  d.scale = o.epi.scale; d.bias = o.epi.bias; d.act = o.epi.act; d.alpha = o.epi.alpha;
+  d.residual = o.residual; d.y_f32 = o.y_f32; d.y_i8 = o.y_i8; d.inv_next_scale = o.inv_next_scale;
+  return d;
+}
+
+// The epilogue of one output value; identical arithmetic to the tensor-core kernel.
+__device__ __forceinline__ void emit(const OutDev& o, long row, int col, int acc) {
+  const long off = row * o.ldy + col;
+  if (o.mode == OUT_ACC) {
+    static_cast<int32_t*>(o.y)[off] = acc;
+    return;
+  }
+  float v = fmaf(static_cast<float>(acc), o.scale[col], o.bias[col]);
+  if (o.mode == OUT_ADD_RELU) {
+    if (o.residual) v += o.residual[off];
+    v = v > 0.f ? v : 0.f;
+    if (o.y_f32) o.y_f32[off] = v;
+    if (o.y_i8) o.y_i8[off] = static_cast<int8_t>(calib_i8(v, o.inv_next_scale));
+    return;
+  }
+  v = act_apply(v, o.act, o.alpha);
+  if (o.mode == OUT_F32)
+    static_cast<float*>(o.y)[off] = v;
+  else
+    static_cast<int8_t*>(o.y)[off] = static_cast<int8_t>(requant_i8(v));
+}
+
+// ------------------------------------------------------------------ direct convolution
+__global__ void __launch_bounds__(kBlock)
+    conv_direct_kernel(const ConvGeom g, const int8_t* __restrict__ x, const int8_t* __restrict__ w,
+                       const OutDev o, const long total) {
+  const long idx = static_cast<long>(blockIdx.x) * kBlock + threadIdx.x;
+  if (idx >= total) return;
+  const int co = static_cast<int>(idx % g.cout);
+  const long m = idx / g.cout;
+  const int ow = static_cast<int>(m % g.wo);
+  const int oh = static_cast<int>((m / g.wo) % g.ho);
+  const long n = m / (static_cast<long>(g.wo) * g.ho);
+  const int cog = g.cout / g.groups, cig = g.cin / g.groups;
+  const int grp = co / cog;
+  const bool vec4 = (cig & 3) == 0 && (g.cin_stride & 3) == 0 && (g.cg_pad & 3) == 0;
+  int acc = 0;
+  for (int r = 0; r < g.kh; ++r) {
+    const int ih = oh * g.stride_h - g.pad_t + r * g.dil_h;
+    if (ih < 0 || ih >= g.h) continue;
+    for (int s = 0; s < g.kw; ++s) {
+      const int iw = ow * g.stride_w - g.pad_l + s * g.dil_w;
+      if (iw < 0 || iw >= g.w) continue;
+      const int8_t* xp = x + ((n * g.h + ih) * g.w + iw) * g.cin_stride + grp * cig;
+      const int8_t* wp = w + (static_cast<long>(co) * g.kh * g.kw + r * g.kw + s) * g.cg_pad;
+      if (vec4) {
+        const int* xp4 = reinterpret_cast<const int*>(xp);
+        const int* wp4 = reinterpret_cast<const int*>(wp);
+        for (int c = 0; c < cig / 4; ++c) acc = __dp4a(xp4[c], wp4[c], acc);
+      } else {
+        for (int c = 0; c < cig; ++c) acc += static_cast<int>(xp[c]) * static_cast<int>(wp[c]);
+      }
+    }
+  }
+  emit(o, m, co, acc);
+}
+
+// ------------------------------------------------------------------ depthwise convolution
+// One thread = one output pixel x 4 consecutive channels (one 32-bit load per tap).
+__global__ void __launch_bounds__(kBlock)
+    dwconv_kernel(const ConvGeom g, const int8_t* __restrict__ x, const int8_t* __restrict__ w,
+                  const OutDev o, const long total, const int cquads) {
+  const long idx = static_cast<long>(blockIdx.x) * kBlock + threadIdx.x;
+  if (idx >= total) return;
+  const int cq = static_cast<int>(idx % cquads);
+  const long m = idx / cquads;
+  const int ow = static_cast<int>(m % g.wo);
+  const int oh = static_cast<int>((m / g.wo) % g.ho);
+  const long n = m / (static_cast<long>(g.wo) * g.ho);
+  int acc[4] = {0, 0, 0, 0};
+  for (int r = 0; r < g.kh; ++r) {
+    const int ih = oh * g.stride_h - g.pad_t + r * g.dil_h;
+    if (ih < 0 || ih >= g.h) continue;
+    for (int s = 0; s < g.kw; ++s) {
+      const int iw = ow * g.stride_w - g.pad_l + s * g.dil_w;
+      if (iw < 0 || iw >= g.w) continue;
+      const uint32_t xv = *reinterpret_cast<const uint32_t*>(
+          x + ((n * g.h + ih) * g.w + iw) * g.cin_stride + cq * 4);
+      const uint32_t wv =
+          *reinterpret_cast<const uint32_t*>(w + static_cast<long>(r * g.kw + s) * g.cg_pad + cq * 4);
+#pragma unroll
+      for (int j = 0; j < 4; ++j)
+        acc[j] += static_cast<int>(static_cast<int8_t>(xv >> (8 * j))) *
+                  static_cast<int>(static_cast<int8_t>(wv >> (8 * j)));
+    }
+  }
+  const int c0 = cq * 4;
+  if (o.mode == OUT_I8 && c0 + 3 < g.cout && (o.ldy & 3) == 0) {
+    int q[4];
+#pragma unroll
+    for (int j = 0; j < 4; ++j)
+      q[j] = requant_i8(act_apply(fmaf(static_cast<float>(acc[j]), o.scale[c0 + j], o.bias[c0 + j]),
+                                  o.act, o.alpha));
+    *reinterpret_cast<uint32_t*>(static_cast<int8_t*>(o.y) + m * o.ldy + c0) =
+        pack4(q[0], q[1], q[2], q[3]);
+    return;
+  }
+#pragma unroll
+  for (int j = 0; j < 4; ++j)
+    if (c0 + j < g.cout) emit(o, m, c0 + j, acc[j]);
+}
+
+// ------------------------------------------------------------------ sparse 1x1 convolution
+// NCHW.  grid = (pixel blocks, cout, batch).  Each thread owns VEC consecutive pixels of one
+// output channel and walks that channel's non-zero weights in ascending input channel, the
+// order the reference kernels use.
+template <int VEC>
+__global__ void __launch_bounds__(kBlock)
+    sparse_i8_kernel(const SparseGeom g, const int8_t* __restrict__ x, const int* __restrict__ row_ptr,
+                     const int* __restrict__ col, const int8_t* __restrict__ val, const EpiParams e,
+                     void* __restrict__ y) {
+  const int p = (blockIdx.x * kBlock + threadIdx.x) * VEC;
+  if (p >= g.hw) return;
+  const int oc = blockIdx.y;
+  const long n = blockIdx.z;
+  const int8_t* xb = x + n * g.cin * static_cast<long>(g.hw) + p;
+  int acc[VEC];
+#pragma unroll
+  for (int j = 0; j < VEC; ++j) acc[j] = 0;
+  const int t1 = row_ptr[oc + 1];
+  for (int t = row_ptr[oc]; t < t1; ++t) {
+    const int wv = val[t];
+    const int8_t* xp = xb + static_cast<long>(col[t]) * g.hw;
+    if (VEC == 4) {
+      const uint32_t xv = *reinterpret_cast<const uint32_t*>(xp);
+#pragma unroll
+      for (int j = 0; j < 4; ++j) acc[j] += wv * static_cast<int>(static_cast<int8_t>(xv >> (8 * j)));
+    } else {
+      acc[0] += wv * static_cast<int>(xp[0]);
+    }
+  }
+  const float sc = e.scale[oc], bi = e.bias[oc];
+  const long off = (n * g.cout + oc) * static_cast<long>(g.hw) + p;
+  if (g.out_mode == OUT_I8) {
+    int q[VEC];
+#pragma unroll
+    for (int j = 0; j < VEC; ++j)
+      q[j] = requant_i8(act_apply(fmaf(static_cast<float>(acc[j]), sc, bi), e.act, e.alpha));
+    if (VEC == 4)
+      *reinterpret_cast<uint32_t*>(static_cast<int8_t*>(y) + off) = pack4(q[0], q[1], q[2], q[3]);
+    else
+      static_cast<int8_t*>(y)[off] = static_cast<int8_t>(q[0]);
+  } else {
+#pragma unroll
+    for (int j = 0; j < VEC; ++j)
+      static_cast<float*>(y)[off + j] =
+          act_apply(fmaf(static_cast<float>(acc[j]), sc, bi), e.act, e.alpha);
+  }
+}
+
+// fp32: accumulator starts at the bias, one fused multiply-add per non-zero weight.
+__global__ void __launch_bounds__(kBlock)
+    sparse_f32_kernel(const SparseGeom g, const float* __restrict__ x, const int* __restrict__ row_ptr,
+                      const int* __restrict__ col, const float* __restrict__ val,
+                      const float* __restrict__ bias, const int act, const float alpha,
+                      float* __restrict__ y) {
+  const int p = blockIdx.x * kBlock + threadIdx.x;
+  if (p >= g.hw) return;
+  const int oc = blockIdx.y;
+  const long n = blockIdx.z;
+  const float* xb = x + n * g.cin * static_cast<long>(g.hw) + p;
+  float v = bias ? bias[oc] : 0.f;
+  const int t1 = row_ptr[oc + 1];
+  for (int t = row_ptr[oc]; t < t1; ++t) v = fmaf(val[t], xb[static_cast<long>(col[t]) * g.hw], v);
+  y[(n * g.cout + oc) * static_cast<long>(g.hw) + p] = act_apply(v, act, alpha);
+}
+
+// ------------------------------------------------------------------ glue
+__global__ void calib_f32_to_i8_kernel(const float* __restrict__ x, int8_t* __restrict__ q, size_t n,
+                                       float inv) {
+  const size_t stride = static_cast<size_t>(gridDim.x) * blockDim.x;
+  for (size_t i = static_cast<size_t>(blockIdx.x) * blockDim.x + threadIdx.x; i < n; i += stride)
+    q[i] = static_cast<int8_t>(calib_i8(x[i], inv));
+}
+__global__ void calib_i8_to_f32_kernel(const int8_t* __restrict__ q, float* __restrict__ y, size_t n,
+                                       float scale) {
+  const size_t stride = static_cast<size_t>(gridDim.x) * blockDim.x;
+  for (size_t i = static_cast<size_t>(blockIdx.x) * blockDim.x + threadIdx.x; i < n; i += stride)
+    y[i] = static_cast<float>(q[i]) * scale;
+}
+
+// [n,c,hw] -> [n,hw,cpad]; a block moves a 32-channel x 64-pixel tile through shared memory.
+// T = int8_t copies, T = float quantises on the way (calib).
+template <typename T>
+__global__ void __launch_bounds__(kBlock)
+    to_nhwc_i8_kernel(const T* __restrict__ x, int8_t* __restrict__ y, int c, int hw, int cpad,
+                      float inv) {
+  __shared__ int8_t tile[32][64 + 4];
+  const long n = blockIdx.z;
+  const int c0 = blockIdx.y * 32, p0 = blockIdx.x * 64;
+  for (int i = threadIdx.x; i < 32 * 64; i += kBlock) {
+    const int cc = i >> 6, pp = i & 63;
+    int8_t v = 0;
+    if (c0 + cc < c && p0 + pp < hw) {
+      const T raw = x[(n * c + c0 + cc) * static_cast<long>(hw) + p0 + pp];
+      if (sizeof(T) == 1) v = static_cast<int8_t>(raw);
+      else v = static_cast<int8_t>(calib_i8(static_cast<float>(raw), inv));
+    }
+    tile[cc][pp] = v;
+  }
+  __syncthreads();
+  const int pp = threadIdx.x >> 2, cg = threadIdx.x & 3;  // 64 pixels x 4 groups of 8 channels
+  if (p0 + pp < hw && c0 + cg * 8 < cpad) {
+    uint32_t lo = 0, hi = 0;
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      lo |= static_cast<uint32_t>(static_cast<uint8_t>(tile[cg * 8 + j][pp])) << (8 * j);
+      hi |= static_cast<uint32_t>(static_cast<uint8_t>(tile[cg * 8 + 4 + j][pp])) << (8 * j);
+    }
+    *reinterpret_cast<uint2*>(y + (n * hw + p0 + pp) * static_cast<long>(cpad) + c0 + cg * 8) =
+        make_uint2(lo, hi);
+  }
+}
+
+// [n,hw,c] -> [n,c,hw], 32x32 element tiles.
+template <typename T>
+__global__ void nhwc_to_nchw_kernel(const T* __restrict__ x, T* __restrict__ y, int c, int hw) {
+  __shared__ T tile[32][33];
+  const long n = blockIdx.z;
+  const int c0 = blockIdx.y * 32, p0 = blockIdx.x * 32;
+  for (int k = threadIdx.y; k < 32; k += 8) {
+    const int p = p0 + k, cc = c0 + threadIdx.x;
+    if (p < hw && cc < c) tile[k][threadIdx.x] = x[(n * hw + p) * static_cast<long>(c) + cc];
+  }
+  __syncthreads();
+  for (int k = threadIdx.y; k < 32; k += 8) {
+    const int cc = c0 + k, p = p0 + threadIdx.x;
+    if (p < hw && cc < c) y[(n * c + cc) * static_cast<long>(hw) + p] = tile[threadIdx.x][k];
+  }
+}
+
+__global__ void __launch_bounds__(kBlock)
+    maxpool_nhwc_i8_kernel(const int8_t* __restrict__ x, int8_t* __restrict__ y, int c4, int h, int w,
+                           int ho, int wo, int k, int stride, int pad, long total) {
+  const long idx = static_cast<long>(blockIdx.x) * kBlock + threadIdx.x;
+  if (idx >= total) return;
+  const int cq = static_cast<int>(idx % c4);
+  const long m = idx / c4;
+  const int ow = static_cast<int>(m % wo);
+  const int oh = static_cast<int>((m / wo) % ho);
+  const long n = m / (static_cast<long>(wo) * ho);
+  uint32_t best = 0x80808080u;  // four times -128
+  for (int r = 0; r < k; ++r) {
+    const int ih = oh * stride - pad + r;
+    if (ih < 0 || ih >= h) continue;
+    for (int s = 0; s < k; ++s) {
+      const int iw = ow * stride - pad + s;
+      if (iw < 0 || iw >= w) continue;
+      const uint32_t v = reinterpret_cast<const uint32_t*>(x)[((n * h + ih) * w + iw) * c4 + cq];
+      best = __vmaxs4(best, v);
+    }
+  }
+  reinterpret_cast<uint32_t*>(y)[m * c4 + cq] = best;
+}
+
+// x [n,hw,c] -> y [n,c] = (sum over hw in ascending order) / hw; optional calib to int8.
+__global__ void global_avgpool_kernel(const float* __restrict__ x, float* __restrict__ y,
+                                      int8_t* __restrict__ q, int hw, int c, float inv, long total) {
+  const long idx = static_cast<long>(blockIdx.x) * blockDim.x + threadIdx.x;
+  if (idx >= total) return;
+  const long n = idx / c;
+  const int cc = static_cast<int>(idx % c);
+  const float* xp = x + n * hw * static_cast<long>(c) + cc;
+  float s = 0.f;
+  for (int p = 0; p < hw; ++p) s += xp[static_cast<long>(p) * c];
+  const float v = s / static_cast<float>(hw);
+  if (y) y[idx] = v;
+  if (q) q[idx] = static_cast<int8_t>(calib_i8(v, inv));
+}
+
+unsigned blocks_for(long total) { return static_cast<unsigned>((total + kBlock - 1) / kBlock); }
+
+}  // namespace
+
+int conv_direct_launch(plb_ctx* ctx, const ConvGeom& g, const int8_t* x, const int8_t* w_rsc,
+                       const OutSpec& out) {
+  const long total = static_cast<long>(g.batch) * g.ho * g.wo * g.cout;
+  if (total == 0) return PLB_OK;
+  conv_direct_kernel<<<blocks_for(total), kBlock, 0, ctx->stream>>>(g, x, w_rsc, to_dev(out), total);
+  PLB_CUDA(cudaGetLastError());
+  ctx->launches++;
+  return PLB_OK;
+}
+
+int dwconv_launch(plb_ctx* ctx, const ConvGeom& g, const int8_t* x, const int8_t* w_tc,
+                  const OutSpec& out) {
+  const int cquads = (g.cout + 3) / 4;
+  const long total = static_cast<long>(g.batch) * g.ho * g.wo * cquads;
+  if (total == 0) return PLB_OK;
+  dwconv_kernel<<<blocks_for(total), kBlock, 0, ctx->stream>>>(g, x, w_tc, to_dev(out), total, cquads);
+  PLB_CUDA(cudaGetLastError());
+  ctx->launches++;
+  return PLB_OK;
+}
+
+int sparse_csr_launch(plb_ctx* ctx, const SparseGeom& g, const void* x, const int* row_ptr,
+                      const int* col, const void* val, const float* bias_raw, const EpiParams& epi,
+                      void* y) {
+  if (g.batch == 0 || g.hw == 0) return PLB_OK;
+  if (g.cout > 65535 || g.batch > 65535) return fail(PLB_E_UNSUPPORTED, "sparse grid too large");
+  if (g.is_int8) {
+    const bool vec4 = (g.hw & 3) == 0 && (reinterpret_cast<uintptr_t>(x) & 3) == 0 &&
+                      (reinterpret_cast<uintptr_t>(y) & 3) == 0;
+    if (vec4) {
+      dim3 grid((g.hw / 4 + kBlock - 1) / kBlock, g.cout, g.batch);
+      sparse_i8_kernel<4><<<grid, kBlock, 0, ctx->stream>>>(
+          g, static_cast<const int8_t*>(x), row_ptr, col, static_cast<const int8_t*>(val), epi, y);
+    } else {
+      dim3 grid((g.hw + kBlock - 1) / kBlock, g.cout, g.batch);
+      sparse_i8_kernel<1><<<grid, kBlock, 0, ctx->stream>>>(
+          g, static_cast<const int8_t*>(x), row_ptr, col, static_cast<const int8_t*>(val), epi, y);
+    }
+  } else {
+    dim3 grid((g.hw + kBlock - 1) / kBlock, g.cout, g.batch);
+    sparse_f32_kernel<<<grid, kBlock, 0, ctx->stream>>>(
+        g, static_cast<const float*>(x), row_ptr, col, static_cast<const float*>(val), bias_raw,
+        epi.act, epi.alpha, static_cast<float*>(y));
+  }
+  PLB_CUDA(cudaGetLastError());
+  ctx->launches++;
+  return PLB_OK;
+}
+
+int calib_f32_to_i8_launch(plb_ctx* ctx, const float* x, int8_t* q, size_t n, float scale) {
+  if (n == 0) return PLB_OK;
+  const unsigned blocks = static_cast<unsigned>(std::min<size_t>((n + kBlock - 1) / kBlock, 148 * 16));
+  calib_f32_to_i8_kernel<<<blocks, kBlock, 0, ctx->stream>>>(x, q, n, 1.f / scale);
+  PLB_CUDA(cudaGetLastError());
+  ctx->launches++;
+  return PLB_OK;
+}
+
+int calib_i8_to_f32_launch(plb_ctx* ctx, const int8_t* q, float* y, size_t n, float scale) {
+  if (n == 0) return PLB_OK;
+  const unsigned blocks = static_cast<unsigned>(std::min<size_t>((n + kBlock - 1) / kBlock, 148 * 16));
+  calib_i8_to_f32_kernel<<<blocks, kBlock, 0, ctx->stream>>>(q, y, n, scale);
+  PLB_CUDA(cudaGetLastError());
+  ctx->launches++;
+  return PLB_OK;
+}
+
+int nchw_to_nhwc_i8_launch(plb_ctx* ctx, const int8_t* x, int8_t* y, int n, int c, int h, int w,
+                           int cpad) {
+  if (n == 0) return PLB_OK;
+  if (cpad % 8 || cpad < c) return fail(PLB_E_INVALID, "cpad must be a multiple of 8 and >= c");
+  const int hw = h * w;
+  dim3 grid((hw + 63) / 64, (cpad + 31) / 32, n);
+  to_nhwc_i8_kernel<int8_t><<<grid, kBlock, 0, ctx->stream>>>(x, y, c, hw, cpad, 1.f);
+  PLB_CUDA(cudaGetLastError());
+  ctx->launches++;
+  return PLB_OK;
+}
+
+int calib_nchw_f32_to_nhwc_i8_launch(plb_ctx* ctx, const float* x, int8_t* y, int n, int c, int h,
+                                     int w, int cpad, float scale) {
+  if (n == 0) return PLB_OK;
+  if (cpad % 8 || cpad < c) return fail(PLB_E_INVALID, "cpad must be a multiple of 8 and >= c");
+  const int hw = h * w;
+  dim3 grid((hw + 63) / 64, (cpad + 31) / 32, n);
+  to_nhwc_i8_kernel<float><<<grid, kBlock, 0, ctx->stream>>>(x, y, c, hw, cpad, 1.f / scale);
+  PLB_CUDA(cudaGetLastError());
+  ctx->launches++;
+  return PLB_OK;
+}
+
+int nhwc_to_nchw_launch(plb_ctx* ctx, const void* x, void* y, int n, int c, int h, int w,
+                        int elem_bytes) {
+  if (n == 0) return PLB_OK;
+  const int hw = h * w;
+  dim3 grid((hw + 31) / 32, (c + 31) / 32, n), block(32, 8);
+  if (elem_bytes == 1)
+    nhwc_to_nchw_kernel<int8_t><<<grid, block, 0, ctx->stream>>>(
+        static_cast<const int8_t*>(x), static_cast<int8_t*>(y), c, hw);
+  else if (elem_bytes == 4)
+    nhwc_to_nchw_kernel<int32_t><<<grid, block, 0, ctx->stream>>>(
+        static_cast<const int32_t*>(x), static_cast<int32_t*>(y), c, hw);
+  else
+    return fail(PLB_E_INVALID, "element size must be 1 or 4");
+  PLB_CUDA(cudaGetLastError());
+  ctx->launches++;
+  return PLB_OK;
+}
+
+int maxpool_nhwc_i8_launch(plb_ctx* ctx, const int8_t* x, int8_t* y, int n, int c, int h, int w,
+                           int k, int stride, int pad) {
+  if (c % 4) return fail(PLB_E_UNSUPPORTED, "max pool needs a channel count that is a multiple of 4");
+  const int ho = (h + 2 * pad - k) / stride + 1, wo = (w + 2 * pad - k) / stride + 1;
+  const long total = static_cast<long>(n) * ho * wo * (c / 4);
+  if (total == 0) return PLB_OK;
+  maxpool_nhwc_i8_kernel<<<blocks_for(total), kBlock, 0, ctx->stream>>>(x, y, c / 4, h, w, ho, wo, k,
+                                                                         stride, pad, total);
+  PLB_CUDA(cudaGetLastError());
+  ctx->launches++;
+  return PLB_OK;
+}
+
+int global_avgpool_nhwc_f32_launch(plb_ctx* ctx, const float* x, float* y, int8_t* q, int n, int hw,
+                                   int c, float scale) {
+  const long total = static_cast<long>(n) * c;
+  if (total == 0) return PLB_OK;
+  global_avgpool_kernel<<<blocks_for(total), kBlock, 0, ctx->stream>>>(x, y, q, hw, c, 1.f / scale,
+                                                                        total);
+  PLB_CUDA(cudaGetLastError());
+  ctx->launches++;
+  return PLB_OK;
+}
+
+}  // namespace plb

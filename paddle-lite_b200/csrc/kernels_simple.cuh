@@ -1,0 +1,61 @@
+// CUDA-core kernels of the path: direct convolution, depthwise 3x3-style convolution,
+// sparse 1x1 convolution over the decoded reference encoding, and the glue between int8
+// layers (layout staging, calib, pooling).  Launchers are declared here and defined in
+// kernels_simple.cu.
+#pragma once
+#include "common.cuh"
+
+namespace plb {
+
+struct ConvGeom {
+  int batch, cin, h, w;       // logical input
+  int cin_stride;             // bytes between pixels of the NHWC input
+  int cout, kh, kw;
+  int stride_h, stride_w, pad_t, pad_l, dil_h, dil_w;
+  int groups;
+  int ho, wo;
+  int cg_pad;                 // filter row length per tap: [cout][kh][kw][cg_pad]
+};
+
+struct OutSpec {
+  int mode;                   // OutMode of igemm_tc.cuh
+  void* y;                    // [m_total, ldy]
+  int ldy;
+  EpiParams epi;
+  const float* residual;
+  float* y_f32;
+  int8_t* y_i8;
+  float inv_next_scale;
+};
+
+// Generic grouped convolution, NHWC in / NHWC out, one thread per output value.
+int conv_direct_launch(plb_ctx* ctx, const ConvGeom& g, const int8_t* x, const int8_t* w_rsc,
+                       const OutSpec& out);
+// Depthwise convolution, NHWC, channels multiple of 4 in storage; filter [kh*kw][c_stride].
+int dwconv_launch(plb_ctx* ctx, const ConvGeom& g, const int8_t* x, const int8_t* w_tc,
+                  const OutSpec& out);
+
+// Sparse 1x1 convolution on NCHW tensors over CSR rows decoded from the reference encoding.
+struct SparseGeom {
+  int batch, cin, cout, hw;
+  int is_int8;     // input/weight type
+  int out_mode;    // OUT_F32 / OUT_I8
+};
+int sparse_csr_launch(plb_ctx* ctx, const SparseGeom& g, const void* x, const int* row_ptr,
+                      const int* col, const void* val, const float* bias_raw, const EpiParams& epi,
+                      void* y);
+
+int calib_f32_to_i8_launch(plb_ctx* ctx, const float* x, int8_t* q, size_t n, float scale);
+int calib_i8_to_f32_launch(plb_ctx* ctx, const int8_t* q, float* y, size_t n, float scale);
+int nchw_to_nhwc_i8_launch(plb_ctx* ctx, const int8_t* x, int8_t* y, int n, int c, int h, int w,
+                           int cpad);
+int nhwc_to_nchw_launch(plb_ctx* ctx, const void* x, void* y, int n, int c, int h, int w,
+                        int elem_bytes);
+int calib_nchw_f32_to_nhwc_i8_launch(plb_ctx* ctx, const float* x, int8_t* y, int n, int c, int h,
+                                     int w, int cpad, float scale);
+int maxpool_nhwc_i8_launch(plb_ctx* ctx, const int8_t* x, int8_t* y, int n, int c, int h, int w,
+                           int k, int stride, int pad);
+int global_avgpool_nhwc_f32_launch(plb_ctx* ctx, const float* x, float* y, int8_t* q, int n, int hw,
+                                   int c, float scale);
+
+}  // namespace plb
