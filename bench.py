@@ -1,0 +1,408 @@
+#!/usr/bin/env python
+"""Benchmark of the int8 conv / fc hot path: whole-network inference throughput.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--net resnet50|mobilenet_v1]
+                    [--batch-per-gpu B] [--impl ours|reference]
+
+One "step" is one forward pass of the int8 network over a batch of B images on each GPU
+(weak scaling: the batch is sharded by image, weights are replicated, no collective on the
+data path).  Prints ONE JSON line on rank 0:
+
+  value      images/s over all GPUs, inputs resident in HBM, timed with CUDA events on the
+             launching stream (max over ranks)
+  e2e        the same with host buffers: every step copies that step's fp32 images from pinned
+             host memory and reads the logits back (copies overlap the previous step's compute)
+  roofline   of the dominant kernel (the tcgen05 implicit GEMM): algorithmic bytes of all its
+             launches in a step / their measured duration, against the measured HBM peak
+  cpu_baseline  the reference's own x86 int8 path (oracle/_ref, built from the reference
+             sources) on a bounded sample of the same workload, all host threads
+
+`--impl reference` times only that CPU path and prints the same line shape.
+"""
+import argparse
+import importlib
+import json
+import os
+import statistics
+import subprocess
+import sys
+import threading
+import time
+
+import numpy as np
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+sys.path.insert(0, ROOT)
+sys.path.insert(0, os.path.join(ROOT, "paddle-lite_b200"))
+
+DEFAULT_BATCH = {"resnet50": 128, "mobilenet_v1": 32}
+
+
+def measured_peaks():
+    path = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(path):
+        with open(path) as f:
+            d = json.load(f)
+        return float(d["hbm_gbs"]), "measured"
+    return 6650.0, "fallback"
+
+
+class ClockSampler:
+    """Samples SM clocks and throttle reasons with nvidia-smi while the timed region runs."""
+    FIELDS = ("clocks.sm,clocks.max.sm,clocks_event_reasons.hw_slowdown,"
+              "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,"
+              "clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, index):
+        self.index, self.proc, self.lines = index, None, []
+
+    def start(self):
+        try:
+            self.proc = subprocess.Popen(
+                ["nvidia-smi", "-i", str(self.index), "--query-gpu=" + self.FIELDS,
+                 "--format=csv,noheader,nounits", "-lms", "100"], stdout=subprocess.PIPE, text=True)
+            self.thread = threading.Thread(target=self._read, daemon=True)
+            self.thread.start()
+        except OSError:
+            self.proc = None
+
+    def _read(self):
+        for line in self.proc.stdout:
+            self.lines.append(line.strip())
+
+    def stop(self):
+        if not self.proc:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
+        self.proc.terminate()
+        try:
+            self.proc.wait(timeout=5)
+        except subprocess.TimeoutExpired:
+            self.proc.kill()
+        sm, mx, reasons = [], [], set()
+        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+        for line in self.lines:
+            parts = [p.strip() for p in line.split(",")]
+            if len(parts) < 6:
+                continue
+            try:
+                sm.append(float(parts[0]))
+                mx.append(float(parts[1]))
+            except ValueError:
+                continue
+            for name, val in zip(names, parts[2:6]):
+                if val.lower().startswith("active"):
+                    reasons.add(name)
+        return {"sm_mhz": statistics.median(sm) if sm else None,
+                "sm_max_mhz": max(mx) if mx else None, "reasons": sorted(reasons), "samples": len(sm)}
+
+
+def layer_bytes(spec, batch):
+    """Algorithmic bytes of the conv/fc launches of one step (int8 or fp32 tensors read and
+    written once, weights once) and their multiply-accumulates."""
+    c, h, w = spec["image"]
+    hw = {"x": (h, w)}
+    total_bytes, macs, launches = 0, 0, 0
+    per_layer = []
+    for op in spec["ops"]:
+        if op["op"] in ("conv", "conv_add_relu"):
+            ih, iw = hw[op["src"]]
+            oh, ow = (ih + 2 * op["p"] - op["k"]) // op["s"] + 1, (iw + 2 * op["p"] - op["k"]) // op["s"] + 1
+            groups = op.get("groups", 1)
+            cin_stored = 32 if op["src"] == "x" else op["cin"]
+            b = batch * ih * iw * cin_stored + op["cout"] * (op["cin"] // groups) * op["k"] ** 2 + 8 * op["cout"]
+            if op["op"] == "conv":
+                b += batch * oh * ow * op["cout"] * (1 if op["out"] == "i8" else 4)
+                hw[op["dst"]] = (oh, ow)
+            else:
+                b += batch * oh * ow * op["cout"] * 4  # residual read
+                for key, size in (("dst_f32", 4), ("dst_i8", 1)):
+                    if op[key]:
+                        b += batch * oh * ow * op["cout"] * size
+                        hw[op[key]] = (oh, ow)
+            m = batch * oh * ow * op["cout"] * (op["cin"] // groups) * op["k"] ** 2
+            if groups == 1:
+                total_bytes += b
+                macs += m
+                launches += 1
+            per_layer.append((op["name"], b, m, groups))
+        elif op["op"] == "maxpool":
+            ih, iw = hw[op["src"]]
+            hw[op["dst"]] = ((ih + 2 * op["p"] - op["k"]) // op["s"] + 1, (iw + 2 * op["p"] - op["k"]) // op["s"] + 1)
+        elif op["op"] == "fc":
+            total_bytes += batch * op["k"] + op["k"] * op["n"] + batch * op["n"] * 4 + 8 * op["n"]
+            macs += batch * op["k"] * op["n"]
+            launches += 1
+    return total_bytes, macs, launches, per_layer
+
+
+# --------------------------------------------------------------------------- CPU reference arm
+def cpu_reference_pass(qnet, images, threads):
+    """One forward pass through the reference's own x86 objects (im2col + gemm_s8u8, built from
+    the reference sources into oracle/_ref), conv and fc layers; fp32 glue in numpy/torch."""
+    import torch
+    import torch.nn.functional as F
+    from oracle import oracle as O
+    spec, layers, scales = qnet["spec"], qnet["layers"], qnet["scales"]
+    t = {"x": O.calib_f32_to_i8(images, float(scales["x"]))}
+    for op in spec["ops"]:
+        kind = op["op"]
+        if kind == "conv":
+            L = layers[op["name"]]
+            out_s = float(scales[op["dst"]]) if op["out"] == "i8" else None
+            t[op["dst"]] = O.ref_conv_int8(t[op["src"]], L["wq"], L["ws"], float(scales[op["src"]]), L["bias"],
+                                           op["act"], 0.0, out_scale=out_s, stride=(op["s"],) * 2,
+                                           pads=(op["p"],) * 4, groups=op.get("groups", 1), threads=threads)
+        elif kind == "conv_add_relu":
+            L = layers[op["name"]]
+            y = O.ref_conv_int8(t[op["src"]], L["wq"], L["ws"], float(scales[op["src"]]), L["bias"], 0,
+                                threads=threads)
+            s = np.maximum(y + t[op["residual"]], np.float32(0))
+            if op["dst_f32"]:
+                t[op["dst_f32"]] = s
+            if op["dst_i8"]:
+                t[op["dst_i8"]] = O.calib_f32_to_i8(s, float(scales[op["dst_i8"]]))
+        elif kind == "maxpool":
+            x = torch.from_numpy(t[op["src"]].astype(np.float32))
+            t[op["dst"]] = F.max_pool2d(x, op["k"], op["s"], op["p"]).numpy().astype(np.int8)
+        elif kind == "avgpool_calib":
+            avg = t[op["src"]].mean(axis=(2, 3), dtype=np.float32)
+            t[op["dst"]] = O.calib_f32_to_i8(avg, float(scales[op["dst"]]))
+        elif kind == "fc":
+            L = layers[op["name"]]
+            t[op["dst"]] = O.ref_fc_int8(t[op["src"]], L["wq"], L["ws"], float(scales[op["src"]]), L["bias"])
+    return t["logits"]
+
+
+def cpu_baseline(qnet, spec, sample_images, repeats=1):
+    from oracle import oracle as O
+    threads = os.cpu_count() or 1
+    kind = "reference" if O.ref_available() else "port"
+    rng = np.random.default_rng(5)
+    images = rng.standard_normal((sample_images,) + spec["image"]).astype(np.float32)
+    if kind == "port":  # exact-integer restatement when the reference objects are absent
+        sys.path.insert(0, os.path.join(ROOT, "tests"))
+        import net_oracle
+        fn = lambda: net_oracle.forward(qnet, images)  # noqa: E731
+    else:
+        fn = lambda: cpu_reference_pass(qnet, images, threads)  # noqa: E731
+    best = None
+    for _ in range(repeats):
+        t0 = time.perf_counter()
+        fn()
+        dt = time.perf_counter() - t0
+        best = dt if best is None else min(best, dt)
+    return {"value": sample_images / best, "unit": "images/s", "cores": threads, "kind": kind,
+            "sample": "%d images, whole %s forward (all conv/fc layers through the x86 int8 path, batch "
+                      "sharded over %d host threads), best of %d" % (sample_images, spec["name"], threads, repeats),
+            "seconds": best}
+
+
+# --------------------------------------------------------------------------- main
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=20)
+    ap.add_argument("--warmup", type=int, default=3)
+    ap.add_argument("--net", default="resnet50", choices=sorted(DEFAULT_BATCH))
+    ap.add_argument("--batch-per-gpu", type=int, default=0)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--cpu-sample", type=int, default=0, help="images in the CPU baseline sample (0 = auto)")
+    ap.add_argument("--no-cpu-baseline", action="store_true")
+    args = ap.parse_args()
+    rank = int(os.environ.get("RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+    batch = args.batch_per_gpu or DEFAULT_BATCH[args.net]
+    warmup = max(args.warmup, 3)
+
+    networks = importlib.import_module("paddle-lite_b200.networks")
+    spec = networks.SPECS[args.net]()
+    workload = "%s int8 PTQ, 224x224, batch %d per GPU" % (spec["name"], batch)
+    base = {"metric": "int8 %s inference throughput" % spec["name"], "unit": "images/s",
+            "n_gpus": args.gpus, "steps": args.steps, "warmup": warmup, "higher_is_better": True,
+            "scaling": "weak", "vs_baseline": None, "dtype": "int8 x int8 -> int32 (fp32 epilogue)",
+            "data": "synthetic: seeded N(0,1) fp32 images, He-init weights quantised per channel, "
+                    "activation scales from a 16-image calibration pass",
+            "config": {"workload": workload, "global_batch": batch * args.gpus, "parallelism":
+                       "batch-sharded replicas (dp%d), no collective" % args.gpus,
+                       "l2": "per-step activations (>1 GB) exceed the 126 MB L2; no explicit flush"}}
+
+    if args.impl == "reference":
+        if rank != 0:
+            return
+        import torch
+        torch.set_num_threads(os.cpu_count() or 1)
+        qnet = networks.build_quantized(spec, seed=1234, calib_images=4, device="cpu")
+        sample = args.cpu_sample or max(os.cpu_count() or 1, 8)
+        times = []
+        for i in range(warmup + args.steps):
+            cb = cpu_baseline(qnet, spec, sample)
+            if i >= warmup:
+                times.append(cb["seconds"])
+            if sum(times) > 240:
+                break
+        ms = 1e3 * sum(times) / len(times)
+        val = sample / (ms / 1e3)
+        cb.update(value=val)
+        cb.pop("seconds", None)
+        line = dict(base, impl="reference", value=val, ms_per_step=ms, steps=len(times),
+                    cpu_baseline=cb, e2e={"value": val, "unit": "images/s", "h2d_bytes_per_step": 0,
+                                           "d2h_bytes_per_step": 0},
+                    gpu_launches=0)
+        line["config"] = dict(base["config"], workload=workload + " (CPU sample: %d images per step)" % sample)
+        print(json.dumps(line))
+        return
+
+    import torch
+    import torch.distributed as dist
+    if not torch.cuda.is_available():
+        raise SystemExit("bench.py needs a CUDA device (there is no CPU fallback); use --impl reference "
+                         "for the CPU arm")
+    torch.cuda.set_device(local_rank)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=torch.device("cuda", local_rank))
+    sys.path.insert(0, os.path.join(ROOT, "paddle-lite_b200"))
+    import build as plb_build
+    if rank == 0:
+        plb_build.build()
+    if world > 1:
+        dist.barrier()
+    plb = importlib.import_module("paddle-lite_b200")
+
+    stream = torch.cuda.Stream()
+    copy_stream = torch.cuda.Stream()
+    ctx = plb.Context(local_rank, stream=stream)
+    qnet = networks.build_quantized(spec, seed=1234, calib_images=16, device="cuda")
+    runner = networks.Runner(plb, ctx, qnet, batch)
+    rng = np.random.default_rng(1000 + rank)
+    host_images = torch.from_numpy(rng.standard_normal(runner.image_shape).astype(np.float32)).pin_memory()
+    host_logits = [torch.empty((batch, 1000), dtype=torch.float32).pin_memory() for _ in range(2)]
+    dev_images = host_images.cuda()
+
+    def barrier():
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    def max_over_ranks(ms):
+        if world == 1:
+            return ms
+        t = torch.tensor([ms], device="cuda", dtype=torch.float64)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        return float(t.item())
+
+    with torch.cuda.stream(stream):
+        n0 = ctx.launch_count()
+        runner.forward(dev_images)       # eager pass: sets kernel attributes, checks for faults
+        ctx.sync()
+        launches_per_step = ctx.launch_count() - n0
+        head_launches = 1
+        g_full = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(g_full, stream=stream):
+            runner.forward(dev_images)
+        g_body = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(g_body, stream=stream):
+            runner.forward_body()
+        # graph of the tensor-core launches alone, for the roofline of the dominant kernel
+        g_tc = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(g_tc, stream=stream):
+            for st in runner.steps:
+                if st[0] == "conv" and st[1].desc.groups == 1:
+                    st[1].run_nhwc(runner.buf[st[2]], out=runner.buf[st[3]])
+                elif st[0] == "conv_add_relu":
+                    _, conv, src, res, df, dq, next_s = st
+                    conv.run_nhwc_add_relu(runner.buf[src], runner.buf[res], next_s, want_f32=df is not None,
+                                           out_f32=runner.buf[df] if df else None,
+                                           out_i8=runner.buf[dq] if dq else None)
+                elif st[0] == "fc":
+                    st[1].run(runner.buf[st[2]], out=runner.buf[st[3]])
+
+        # ---- device-resident throughput
+        for _ in range(warmup):
+            g_full.replay()
+        barrier()
+        sampler = ClockSampler(local_rank)
+        sampler.start()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record(stream)
+        for _ in range(args.steps):
+            g_full.replay()
+        e1.record(stream)
+        barrier()
+        clocks = sampler.stop()
+        ms_total = max_over_ranks(e0.elapsed_time(e1))
+        ms_step = ms_total / args.steps
+        value = args.gpus * batch / (ms_step / 1e3)
+
+        # ---- dominant kernel alone
+        for _ in range(2):
+            g_tc.replay()
+        torch.cuda.synchronize()
+        t0, t1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        t0.record(stream)
+        for _ in range(args.steps):
+            g_tc.replay()
+        t1.record(stream)
+        torch.cuda.synchronize()
+        tc_ms_step = t0.elapsed_time(t1) / args.steps
+
+        # ---- end to end: pinned host images in, logits out, every step
+        ev_h2d = [torch.cuda.Event() for _ in range(2)]
+        ev_head = [torch.cuda.Event() for _ in range(2)]
+
+        def e2e_steps(n):
+            for i in range(n):
+                with torch.cuda.stream(copy_stream):
+                    if i > 0:
+                        copy_stream.wait_event(ev_head[(i - 1) & 1])  # the image buffer has been consumed
+                    dev_images.copy_(host_images, non_blocking=True)
+                    ev_h2d[i & 1].record(copy_stream)
+                stream.wait_event(ev_h2d[i & 1])
+                runner.forward_head(dev_images)
+                ev_head[i & 1].record(stream)
+                g_body.replay()
+                host_logits[i & 1].copy_(runner.buf["logits"], non_blocking=True)
+
+        e2e_steps(warmup)
+        barrier()
+        s0, s1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        s0.record(stream)
+        e2e_steps(args.steps)
+        s1.record(stream)
+        barrier()
+        e2e_ms_step = max_over_ranks(s0.elapsed_time(s1)) / args.steps
+        ctx.sync()
+
+    total_bytes, macs, tc_launches, _ = layer_bytes(spec, batch)
+    peak, peak_kind = measured_peaks()
+    achieved = total_bytes / (tc_ms_step / 1e3) / 1e9
+    line = dict(base, value=value, ms_per_step=ms_step, clocks=clocks,
+                e2e={"value": args.gpus * batch / (e2e_ms_step / 1e3), "unit": "images/s",
+                     "h2d_bytes_per_step": host_images.numel() * 4, "d2h_bytes_per_step": batch * 1000 * 4,
+                     "ms_per_step": e2e_ms_step},
+                gpu_launches=int(launches_per_step * args.steps),
+                roofline={"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s",
+                          "frac": achieved / peak, "traffic": None, "peak_source": peak_kind + " copy bandwidth",
+                          "kernel": "igemm_i8_tc_kernel", "launches_per_step": tc_launches,
+                          "algorithmic_bytes_per_launch": total_bytes / tc_launches,
+                          "avg_launch_us": 1e3 * tc_ms_step / tc_launches,
+                          "tensor_tops": 2.0 * macs / (tc_ms_step / 1e3) / 1e12,
+                          "share_of_step": tc_ms_step / ms_step})
+    if rank == 0:
+        if not args.no_cpu_baseline and args.gpus == 1:
+            try:
+                cpu_q = networks.build_quantized(spec, seed=1234, calib_images=4, device="cuda")
+                sample = args.cpu_sample or max(os.cpu_count() or 1, 8)
+                cb = cpu_baseline(cpu_q, spec, sample)
+                cb.pop("seconds", None)
+                line["cpu_baseline"] = cb
+            except Exception as exc:  # the baseline is a reported number, never a reason to lose the line
+                line["cpu_baseline"] = {"value": None, "unit": "images/s", "cores": os.cpu_count(),
+                                        "kind": "unavailable", "sample": "failed: %s" % exc}
+        print(json.dumps(line))
+    if world > 1:
+        dist.destroy_process_group()
+
+
+if __name__ == "__main__":
+    main()

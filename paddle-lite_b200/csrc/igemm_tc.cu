@@ -7,9 +7,12 @@
 // (lite/backends/x86/math/avx/conv_utils.cc:1349-1398,
 //  lite/backends/x86/math/gemm_s8u8_compute.h:65-106, gemm_s8u8_kernel.cc:353-891).
 //
-// CTA = 6 warps:  warps 0-3 epilogue (one TMEM lane quadrant each),
-//                 warp 4 TMA producer (one elected lane),
-//                 warp 5 TMEM allocation + MMA issue (one elected lane).
+// Persistent CTA (one per SM) of 10 warps:
+//   warps 0-7  epilogue: warp w reads TMEM lane quadrant w%4 and the 32-column chunks of
+//              parity w/4, so two warps share each quadrant;
+//   warp 8     TMA producer (one elected lane) filling a ring of operand stages;
+//   warp 9     TMEM allocation + MMA issue (one elected lane), two accumulator buffers so
+//              the epilogue of one tile overlaps the main loop of the next.
 // Tile = 128 output pixels x BN output channels, K consumed KC bytes per pipeline stage
 // (KC = 32/64/128 = the TMA swizzle span), 32 bytes of K per tcgen05.mma.
 // Every mbarrier wait is bounded; a wait that runs out records a fault in the ctx status
@@ -24,8 +27,11 @@ namespace {
 
 constexpr int kTileM = 128;
 constexpr int kMaxStages = 8;
-constexpr int kThreads = 192;
-constexpr int kCtrlBytes = 256 + 2 * 256 * 4;  // barriers + tmem slot, then scale/bias staging
+constexpr int kEpilogueWarps = 8;
+constexpr int kProducerWarp = 8;
+constexpr int kMmaWarp = 9;
+constexpr int kThreads = 320;
+constexpr int kCtrlBytes = 256 + 4 * 256 * 4;  // barriers + tmem slot, then 2 x (scale, bias) staging
 constexpr uint32_t kWaitLimit = 1u << 22;      // polls before a wait is declared lost
 
 struct IgemmArgs {
@@ -34,7 +40,7 @@ struct IgemmArgs {
   int bn, kc, cchunks, ksteps, stages;
   int taps, kw;
   int ho, wo, stride_h, stride_w, pad_t, pad_l, dil_h, dil_w;
-  int tiles_n;
+  int tiles_n, num_tiles;
   int out_mode, ldy;
   void* y;
   const float* scale;
@@ -136,6 +142,22 @@ __device__ __forceinline__ void tc_ld16(uint32_t taddr, uint32_t (&r)[16]) {
       : "r"(taddr)
       : "memory");
 }
+__device__ __forceinline__ void tc_ld32(uint32_t taddr, uint32_t (&r)[32]) {
+  asm volatile(
+      "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
+      "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
+      "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];"
+      : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]),
+        "=r"(r[7]), "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]),
+        "=r"(r[14]), "=r"(r[15]), "=r"(r[16]), "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]),
+        "=r"(r[21]), "=r"(r[22]), "=r"(r[23]), "=r"(r[24]), "=r"(r[25]), "=r"(r[26]), "=r"(r[27]),
+        "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
+      : "r"(taddr)
+      : "memory");
+}
+__device__ __forceinline__ void mbar_arrive(uint32_t bar) {
+  asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
+}
 __device__ __forceinline__ void tc_wait_ld() {
   asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
 }
@@ -149,101 +171,127 @@ __device__ __forceinline__ uint64_t make_smem_desc(uint32_t addr, int kc) {
   return (static_cast<uint64_t>(hi) << 32) | lo;
 }
 
-// ---------------------------------------------------------------- epilogue store of 16 columns
-__device__ __forceinline__ void epilogue_store16(const IgemmArgs& a, const uint32_t (&r)[16],
+// ---------------------------------------------------------------- epilogue of 32 columns
+// One thread owns one output row (pixel) and 32 consecutive output channels of it, i.e. one
+// full 32-byte sector of an int8 row or one full 128-byte line of an fp32 row.
+__device__ __forceinline__ void epilogue_store32(const IgemmArgs& a, const uint32_t (&r)[32],
                                                  long row, int col, const float* s_scale,
-                                                 const float* s_bias, int local_col) {
-  const int ncols = a.cout - col < 16 ? a.cout - col : 16;
+                                                 const float* s_bias) {
+  const int ncols = a.cout - col < 32 ? a.cout - col : 32;
   if (ncols <= 0) return;
+  const bool full = ncols == 32;
   if (a.out_mode == OUT_ACC) {
     int32_t* dst = static_cast<int32_t*>(a.y) + row * a.ldy + col;
-    if (ncols == 16 && (a.ldy & 3) == 0) {
+    if (full && (a.ldy & 3) == 0) {
 #pragma unroll
-      for (int j = 0; j < 16; j += 4)
+      for (int j = 0; j < 32; j += 4)
         *reinterpret_cast<int4*>(dst + j) =
             make_int4((int)r[j], (int)r[j + 1], (int)r[j + 2], (int)r[j + 3]);
     } else {
-      for (int j = 0; j < ncols; ++j) dst[j] = (int)r[j];
+#pragma unroll
+      for (int j = 0; j < 32; ++j)
+        if (j < ncols) dst[j] = (int)r[j];
     }
     return;
   }
-  float v[16];
+  float v[32];
 #pragma unroll
-  for (int j = 0; j < 16; ++j)
-    v[j] = fmaf(static_cast<float>(static_cast<int>(r[j])), s_scale[local_col + j],
-                s_bias[local_col + j]);
+  for (int j = 0; j < 32; j += 4) {
+    const float4 sc = *reinterpret_cast<const float4*>(s_scale + j);
+    const float4 bi = *reinterpret_cast<const float4*>(s_bias + j);
+    v[j] = fmaf(static_cast<float>(static_cast<int>(r[j])), sc.x, bi.x);
+    v[j + 1] = fmaf(static_cast<float>(static_cast<int>(r[j + 1])), sc.y, bi.y);
+    v[j + 2] = fmaf(static_cast<float>(static_cast<int>(r[j + 2])), sc.z, bi.z);
+    v[j + 3] = fmaf(static_cast<float>(static_cast<int>(r[j + 3])), sc.w, bi.w);
+  }
   if (a.out_mode == OUT_ADD_RELU) {
     if (a.residual != nullptr) {
       const float* res = a.residual + row * a.ldy + col;
-      if (ncols == 16 && (a.ldy & 3) == 0) {
+      if (full && (a.ldy & 3) == 0) {
 #pragma unroll
-        for (int j = 0; j < 16; j += 4) {
+        for (int j = 0; j < 32; j += 4) {
           const float4 t = *reinterpret_cast<const float4*>(res + j);
           v[j] += t.x; v[j + 1] += t.y; v[j + 2] += t.z; v[j + 3] += t.w;
         }
       } else {
-        for (int j = 0; j < ncols; ++j) v[j] += res[j];
+#pragma unroll
+        for (int j = 0; j < 32; ++j)
+          if (j < ncols) v[j] += res[j];
       }
     }
 #pragma unroll
-    for (int j = 0; j < 16; ++j) v[j] = v[j] > 0.f ? v[j] : 0.f;
+    for (int j = 0; j < 32; ++j) v[j] = v[j] > 0.f ? v[j] : 0.f;
     if (a.y_f32 != nullptr) {
       float* dst = a.y_f32 + row * a.ldy + col;
-      if (ncols == 16 && (a.ldy & 3) == 0) {
+      if (full && (a.ldy & 3) == 0) {
 #pragma unroll
-        for (int j = 0; j < 16; j += 4)
+        for (int j = 0; j < 32; j += 4)
           *reinterpret_cast<float4*>(dst + j) = make_float4(v[j], v[j + 1], v[j + 2], v[j + 3]);
       } else {
-        for (int j = 0; j < ncols; ++j) dst[j] = v[j];
+#pragma unroll
+        for (int j = 0; j < 32; ++j)
+          if (j < ncols) dst[j] = v[j];
       }
     }
     if (a.y_i8 != nullptr) {
       int8_t* dst = a.y_i8 + row * a.ldy + col;
-      int q[16];
+      uint32_t q[8];
 #pragma unroll
-      for (int j = 0; j < 16; ++j) q[j] = calib_i8(v[j], a.inv_next_scale);
-      if (ncols == 16 && (a.ldy & 15) == 0) {
-        *reinterpret_cast<uint4*>(dst) =
-            make_uint4(pack4(q[0], q[1], q[2], q[3]), pack4(q[4], q[5], q[6], q[7]),
-                       pack4(q[8], q[9], q[10], q[11]), pack4(q[12], q[13], q[14], q[15]));
+      for (int j = 0; j < 8; ++j)
+        q[j] = pack4(calib_i8(v[4 * j], a.inv_next_scale), calib_i8(v[4 * j + 1], a.inv_next_scale),
+                     calib_i8(v[4 * j + 2], a.inv_next_scale), calib_i8(v[4 * j + 3], a.inv_next_scale));
+      if (full && (a.ldy & 15) == 0) {
+        *reinterpret_cast<uint4*>(dst) = make_uint4(q[0], q[1], q[2], q[3]);
+        *reinterpret_cast<uint4*>(dst + 16) = make_uint4(q[4], q[5], q[6], q[7]);
       } else {
-        for (int j = 0; j < ncols; ++j) dst[j] = static_cast<int8_t>(q[j]);
+#pragma unroll
+        for (int j = 0; j < 32; ++j)
+          if (j < ncols) dst[j] = static_cast<int8_t>(q[j >> 2] >> (8 * (j & 3)));
       }
     }
     return;
   }
 #pragma unroll
-  for (int j = 0; j < 16; ++j) v[j] = act_apply(v[j], a.act, a.alpha);
+  for (int j = 0; j < 32; ++j) v[j] = act_apply(v[j], a.act, a.alpha);
   if (a.out_mode == OUT_F32) {
     float* dst = static_cast<float*>(a.y) + row * a.ldy + col;
-    if (ncols == 16 && (a.ldy & 3) == 0) {
+    if (full && (a.ldy & 3) == 0) {
 #pragma unroll
-      for (int j = 0; j < 16; j += 4)
+      for (int j = 0; j < 32; j += 4)
         *reinterpret_cast<float4*>(dst + j) = make_float4(v[j], v[j + 1], v[j + 2], v[j + 3]);
     } else {
-      for (int j = 0; j < ncols; ++j) dst[j] = v[j];
+#pragma unroll
+      for (int j = 0; j < 32; ++j)
+        if (j < ncols) dst[j] = v[j];
     }
   } else {  // OUT_I8
     int8_t* dst = static_cast<int8_t*>(a.y) + row * a.ldy + col;
-    int q[16];
+    uint32_t q[8];
 #pragma unroll
-    for (int j = 0; j < 16; ++j) q[j] = requant_i8(v[j]);
-    if (ncols == 16 && (a.ldy & 15) == 0) {
-      *reinterpret_cast<uint4*>(dst) =
-          make_uint4(pack4(q[0], q[1], q[2], q[3]), pack4(q[4], q[5], q[6], q[7]),
-                     pack4(q[8], q[9], q[10], q[11]), pack4(q[12], q[13], q[14], q[15]));
-    } else if (ncols == 16 && (a.ldy & 3) == 0) {
+    for (int j = 0; j < 8; ++j)
+      q[j] = pack4(requant_i8(v[4 * j]), requant_i8(v[4 * j + 1]), requant_i8(v[4 * j + 2]),
+                   requant_i8(v[4 * j + 3]));
+    if (full && (a.ldy & 15) == 0) {
+      *reinterpret_cast<uint4*>(dst) = make_uint4(q[0], q[1], q[2], q[3]);
+      *reinterpret_cast<uint4*>(dst + 16) = make_uint4(q[4], q[5], q[6], q[7]);
+    } else if (full && (a.ldy & 3) == 0) {
 #pragma unroll
-      for (int j = 0; j < 16; j += 4)
-        *reinterpret_cast<uint32_t*>(dst + j) = pack4(q[j], q[j + 1], q[j + 2], q[j + 3]);
+      for (int j = 0; j < 8; ++j) *reinterpret_cast<uint32_t*>(dst + 4 * j) = q[j];
     } else {
-      for (int j = 0; j < ncols; ++j) dst[j] = static_cast<int8_t>(q[j]);
+#pragma unroll
+      for (int j = 0; j < 32; ++j)
+        if (j < ncols) dst[j] = static_cast<int8_t>(q[j >> 2] >> (8 * (j & 3)));
     }
   }
 }
 
 // ---------------------------------------------------------------- the kernel
-__global__ void __launch_bounds__(kThreads)
+// Persistent: one CTA per SM walks tiles t = blockIdx.x, blockIdx.x + gridDim.x, ...;
+// consecutive tile ids share the same 128 pixels (channel tile fastest) so that CTAs running
+// side by side hit the same activation rows in L2.  The operand ring and the two TMEM
+// accumulator buffers run across tile boundaries: the producer prefetches the next tile
+// while the epilogue warps drain the previous one.
+__global__ void __launch_bounds__(kThreads, 1)
     igemm_i8_tc_kernel(const __grid_constant__ CUtensorMap tmA,
                        const __grid_constant__ CUtensorMap tmB, const IgemmArgs a) {
   extern __shared__ uint8_t smem_raw[];
@@ -256,35 +304,36 @@ __global__ void __launch_bounds__(kThreads)
   uint8_t* ctrl = smem + a.stages * stage_bytes;
   uint64_t* full_bar = reinterpret_cast<uint64_t*>(ctrl);
   uint64_t* empty_bar = full_bar + kMaxStages;
-  uint64_t* accum_bar = empty_bar + kMaxStages;
-  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(accum_bar + 1);
+  uint64_t* acc_full = empty_bar + kMaxStages;   // [2] accumulator buffer ready for the epilogue
+  uint64_t* acc_empty = acc_full + 2;            // [2] accumulator buffer drained
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(acc_empty + 2);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
-  float* s_scale = reinterpret_cast<float*>(ctrl + 256);
-  float* s_bias = s_scale + 256;
+  float* s_scale = reinterpret_cast<float*>(ctrl + 256);  // [2][256]
+  float* s_bias = s_scale + 512;                           // [2][256]
 
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
-  const int tile_n = blockIdx.x % a.tiles_n;
-  const int tile_m = blockIdx.x / a.tiles_n;
-  const int m0 = tile_m * kTileM;
-  const int n0 = tile_n * a.bn;
 
-  // TMEM columns: power of two >= max(32, bn)
-  uint32_t tmem_cols = 32;
-  while (tmem_cols < static_cast<uint32_t>(a.bn)) tmem_cols <<= 1;
+  // TMEM: two accumulator buffers of acc_cols columns each
+  uint32_t acc_cols = 32;
+  while (acc_cols < static_cast<uint32_t>(a.bn)) acc_cols <<= 1;
+  const uint32_t tmem_cols = acc_cols * 2;
 
-  if (threadIdx.x == 4 * 32) {
+  if (threadIdx.x == kProducerWarp * 32) {
     for (int s = 0; s < a.stages; ++s) {
       mbar_init(smem_u32(&full_bar[s]), 1);
       mbar_init(smem_u32(&empty_bar[s]), 1);
     }
-    mbar_init(smem_u32(accum_bar), 1);
+    for (int b = 0; b < 2; ++b) {
+      mbar_init(smem_u32(&acc_full[b]), 1);
+      mbar_init(smem_u32(&acc_empty[b]), kEpilogueWarps);
+    }
     *abort_flag = 0;
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     asm volatile("prefetch.tensormap [%0];" ::"l"(reinterpret_cast<uint64_t>(&tmA)) : "memory");
     asm volatile("prefetch.tensormap [%0];" ::"l"(reinterpret_cast<uint64_t>(&tmB)) : "memory");
   }
-  if (warp == 5) {
+  if (warp == kMmaWarp) {
     asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(
                      smem_u32(tmem_slot)),
                  "r"(tmem_cols)
@@ -296,41 +345,47 @@ __global__ void __launch_bounds__(kThreads)
   tc_fence_after();
   const uint32_t tmem_base = *tmem_slot;
 
-  if (warp == 4) {
+  if (warp == kProducerWarp) {
     // ------------------------------------------------------------ TMA producer
     if (lane == 0) {
-      int cn = 0, ch = 0, cw = 0;
-      if (a.im2col) {
-        const int q = m0 % a.wo;
-        const int p = (m0 / a.wo) % a.ho;
-        cn = m0 / (a.wo * a.ho);
-        cw = q * a.stride_w - a.pad_l;
-        ch = p * a.stride_h - a.pad_t;
-      }
-      for (int ks = 0; ks < a.ksteps; ++ks) {
-        const int s = ks % a.stages;
-        const uint32_t parity = ((ks / a.stages) & 1) ^ 1;
-        if (!mbar_wait(smem_u32(&empty_bar[s]), parity, abort_flag, a.status, FAULT_WAIT_EMPTY))
-          break;
-        const uint32_t bar = smem_u32(&full_bar[s]);
-        mbar_expect_tx(bar, static_cast<uint32_t>(stage_bytes));
-        const uint32_t dst_a = smem_u32(smem + s * stage_bytes);
-        const uint32_t dst_b = dst_a + stage_a;
-        const int tap = ks / a.cchunks;
-        const int c0 = (ks - tap * a.cchunks) * a.kc;
+      int ks_global = 0;
+      bool ok = true;
+      for (int tile = blockIdx.x; tile < a.num_tiles && ok; tile += gridDim.x) {
+        const int m0 = (tile / a.tiles_n) * kTileM;
+        const int n0 = (tile % a.tiles_n) * a.bn;
+        int cn = 0, ch = 0, cw = 0;
         if (a.im2col) {
-          const int r = tap / a.kw;
-          const int sx = tap - r * a.kw;
-          tma_load_im2col_4d(dst_a, &tmA, bar, c0, cw, ch, cn,
-                             static_cast<uint16_t>(sx * a.dil_w),
-                             static_cast<uint16_t>(r * a.dil_h));
-        } else {
-          tma_load_2d(dst_a, &tmA, bar, c0, m0);
+          const int q = m0 % a.wo;
+          const int p = (m0 / a.wo) % a.ho;
+          cn = m0 / (a.wo * a.ho);
+          cw = q * a.stride_w - a.pad_l;
+          ch = p * a.stride_h - a.pad_t;
         }
-        tma_load_2d(dst_b, &tmB, bar, tap * a.cchunks * a.kc + c0, n0);
+        for (int ks = 0; ks < a.ksteps; ++ks, ++ks_global) {
+          const int s = ks_global % a.stages;
+          const uint32_t parity = ((ks_global / a.stages) & 1) ^ 1;
+          ok = mbar_wait(smem_u32(&empty_bar[s]), parity, abort_flag, a.status, FAULT_WAIT_EMPTY);
+          if (!ok) break;
+          const uint32_t bar = smem_u32(&full_bar[s]);
+          mbar_expect_tx(bar, static_cast<uint32_t>(stage_bytes));
+          const uint32_t dst_a = smem_u32(smem + s * stage_bytes);
+          const uint32_t dst_b = dst_a + stage_a;
+          const int tap = ks / a.cchunks;
+          const int c0 = (ks - tap * a.cchunks) * a.kc;
+          if (a.im2col) {
+            const int r = tap / a.kw;
+            const int sx = tap - r * a.kw;
+            tma_load_im2col_4d(dst_a, &tmA, bar, c0, cw, ch, cn,
+                               static_cast<uint16_t>(sx * a.dil_w),
+                               static_cast<uint16_t>(r * a.dil_h));
+          } else {
+            tma_load_2d(dst_a, &tmA, bar, c0, m0);
+          }
+          tma_load_2d(dst_b, &tmB, bar, tap * a.cchunks * a.kc + c0, n0);
+        }
       }
     }
-  } else if (warp == 5) {
+  } else if (warp == kMmaWarp) {
     // ------------------------------------------------------------ MMA issuer
     if (lane == 0) {
       // instruction descriptor: D=s32, A=B=s8, both K-major, N=bn, M=128
@@ -338,51 +393,76 @@ __global__ void __launch_bounds__(kThreads)
                              (static_cast<uint32_t>(a.bn >> 3) << 17) |
                              (static_cast<uint32_t>(kTileM >> 4) << 24);
       const int mma_per_stage = a.kc / 32;
+      int ks_global = 0, it = 0;
       bool ok = true;
-      for (int ks = 0; ks < a.ksteps && ok; ++ks) {
-        const int s = ks % a.stages;
-        const uint32_t parity = (ks / a.stages) & 1;
-        ok = mbar_wait(smem_u32(&full_bar[s]), parity, abort_flag, a.status, FAULT_WAIT_FULL);
+      for (int tile = blockIdx.x; tile < a.num_tiles && ok; tile += gridDim.x, ++it) {
+        const int buf = it & 1;
+        ok = mbar_wait(smem_u32(&acc_empty[buf]), ((it >> 1) & 1) ^ 1, abort_flag, a.status,
+                       FAULT_WAIT_ACCUM);
         if (!ok) break;
         tc_fence_after();
-        const uint32_t addr_a = smem_u32(smem + s * stage_bytes);
-        const uint64_t adesc = make_smem_desc(addr_a, a.kc);
-        const uint64_t bdesc = make_smem_desc(addr_a + stage_a, a.kc);
-        for (int j = 0; j < mma_per_stage; ++j) {
-          // advance 32 bytes of K inside the swizzle span: +2 in the (addr >> 4) field
-          tc_mma_i8(tmem_base, adesc + 2u * j, bdesc + 2u * j, idesc, (ks | j) != 0 ? 1u : 0u);
+        const uint32_t d_tmem = tmem_base + buf * acc_cols;
+        for (int ks = 0; ks < a.ksteps; ++ks, ++ks_global) {
+          const int s = ks_global % a.stages;
+          const uint32_t parity = (ks_global / a.stages) & 1;
+          ok = mbar_wait(smem_u32(&full_bar[s]), parity, abort_flag, a.status, FAULT_WAIT_FULL);
+          if (!ok) break;
+          tc_fence_after();
+          const uint32_t addr_a = smem_u32(smem + s * stage_bytes);
+          const uint64_t adesc = make_smem_desc(addr_a, a.kc);
+          const uint64_t bdesc = make_smem_desc(addr_a + stage_a, a.kc);
+          for (int j = 0; j < mma_per_stage; ++j) {
+            // advance 32 bytes of K inside the swizzle span: +2 in the (addr >> 4) field
+            tc_mma_i8(d_tmem, adesc + 2u * j, bdesc + 2u * j, idesc, (ks | j) != 0 ? 1u : 0u);
+          }
+          tc_commit(smem_u32(&empty_bar[s]));  // frees the stage when these MMAs retire
         }
-        tc_commit(smem_u32(&empty_bar[s]));  // frees the stage when these MMAs retire
+        tc_commit(smem_u32(&acc_full[buf]));  // accumulator complete (or drained on a fault)
       }
-      tc_commit(smem_u32(accum_bar));  // accumulator complete (or drained on a fault)
     }
   } else {
-    // ------------------------------------------------------------ epilogue warps 0..3
-    if (a.out_mode != OUT_ACC) {
-      for (int i = threadIdx.x; i < a.bn; i += 128) {
-        const int c = n0 + i;
-        s_scale[i] = c < a.cout ? a.scale[c] : 0.f;
-        s_bias[i] = c < a.cout ? a.bias[c] : 0.f;
+    // ------------------------------------------------------------ epilogue warps 0..7
+    const int quad = warp & 3;   // TMEM lane quadrant this warp may read
+    const int half = warp >> 2;  // which 32-column chunks (even / odd) this warp takes
+    int it = 0;
+    bool ok = true;
+    for (int tile = blockIdx.x; tile < a.num_tiles && ok; tile += gridDim.x, ++it) {
+      const int buf = it & 1;
+      const int m0 = (tile / a.tiles_n) * kTileM;
+      const int n0 = (tile % a.tiles_n) * a.bn;
+      float* sc = s_scale + buf * 256;
+      float* bi = s_bias + buf * 256;
+      if (a.out_mode != OUT_ACC) {
+        for (int i = threadIdx.x; i < 256; i += kEpilogueWarps * 32) {
+          const int c = n0 + i;
+          const bool in = i < a.bn && c < a.cout;
+          sc[i] = in ? a.scale[c] : 0.f;
+          bi[i] = in ? a.bias[c] : 0.f;
+        }
       }
-    }
-    asm volatile("bar.sync 1, 128;" ::: "memory");
-    const bool ok = mbar_wait(smem_u32(accum_bar), 0, abort_flag, a.status, FAULT_WAIT_ACCUM);
-    tc_fence_after();
-    if (ok) {
-      const long row = static_cast<long>(m0) + warp * 32 + lane;
-      const uint32_t lane_addr = tmem_base + (static_cast<uint32_t>(warp * 32) << 16);
-      for (int c = 0; c < a.bn; c += 16) {
-        if (n0 + c >= a.cout) break;  // warp-uniform
-        uint32_t r[16];
-        tc_ld16(lane_addr + static_cast<uint32_t>(c), r);
-        tc_wait_ld();
-        if (row < a.m_total) epilogue_store16(a, r, row, n0 + c, s_scale, s_bias, c);
+      asm volatile("bar.sync 1, 256;" ::: "memory");
+      ok = mbar_wait(smem_u32(&acc_full[buf]), (it >> 1) & 1, abort_flag, a.status, FAULT_WAIT_ACCUM);
+      tc_fence_after();
+      if (ok) {
+        const long row = static_cast<long>(m0) + quad * 32 + lane;
+        const uint32_t lane_addr = tmem_base + buf * acc_cols + (static_cast<uint32_t>(quad * 32) << 16);
+        for (int c = half * 32; c < a.bn; c += 64) {
+          if (n0 + c >= a.cout) break;  // warp-uniform
+          uint32_t r[32];
+          tc_ld32(lane_addr + static_cast<uint32_t>(c), r);
+          tc_wait_ld();
+          if (row < a.m_total) epilogue_store32(a, r, row, n0 + c, sc + c, bi + c);
+        }
       }
+      // this warp no longer reads the buffer: let the MMA warp overwrite it
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(smem_u32(&acc_empty[buf]));
     }
   }
   tc_fence_before();
   __syncthreads();
-  if (warp == 5) {
+  if (warp == kMmaWarp) {
     __syncwarp();
     tc_fence_after();
     asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base),
@@ -482,12 +562,11 @@ int igemm_tc_launch(plb_ctx* ctx, const IgemmProblem& p) {
   a.bn = bn;
   a.tiles_n = (p.cout + bn - 1) / bn;
   const int stage_bytes = (kTileM + bn) * a.kc;
-  const int budget = bn > 128 ? 100 * 1024 : 72 * 1024;
-  int stages = budget / stage_bytes;
+  // one CTA per SM: spend (almost) all shared memory on the operand ring
+  int stages = (200 * 1024) / stage_bytes;
   stages = env_int("PLB_TC_STAGES", stages);
-  if (stages > a.ksteps) stages = a.ksteps;
   if (stages > kMaxStages) stages = kMaxStages;
-  if (stages < 1) stages = 1;
+  if (stages < 2) stages = 2;
   a.stages = stages;
   a.ho = p.ho; a.wo = p.wo;
   a.stride_h = p.stride_h; a.stride_w = p.stride_w;
@@ -550,9 +629,11 @@ int igemm_tc_launch(plb_ctx* ctx, const IgemmProblem& p) {
                                   227 * 1024));
     configured_smem[dev_slot] = 227 * 1024;
   }
-  const long grid = static_cast<long>(tiles_m) * a.tiles_n;
-  if (grid > 0x7fffffffL) return fail(PLB_E_UNSUPPORTED, "grid too large");
-  igemm_i8_tc_kernel<<<static_cast<unsigned>(grid), kThreads, smem, ctx->stream>>>(tmA, tmB, a);
+  const long tiles = static_cast<long>(tiles_m) * a.tiles_n;
+  if (tiles > 0x7fffffffL) return fail(PLB_E_UNSUPPORTED, "too many tiles");
+  a.num_tiles = static_cast<int>(tiles);
+  const unsigned grid = static_cast<unsigned>(tiles < ctx->sm_count ? tiles : ctx->sm_count);
+  igemm_i8_tc_kernel<<<grid, kThreads, smem, ctx->stream>>>(tmA, tmB, a);
   PLB_CUDA(cudaGetLastError());
   ctx->launches++;
   return PLB_OK;

@@ -380,22 +380,26 @@ int conv_run_nchw(plb_conv* c, const int8_t* x, void* y, int batch, int mode) {
 extern "C" {
 
 int plb_conv_run(plb_conv* conv, const int8_t* x, void* y, int batch) {
-  PLB_REQUIRE(conv && x && y, "null argument");
+  PLB_REQUIRE(conv != nullptr, "null argument");
   PLB_REQUIRE(batch >= 0, "negative batch");
-  if (batch == 0) return PLB_OK;
+  if (batch == 0) return PLB_OK;  // an empty batch touches no memory
+  PLB_REQUIRE(x && y, "null argument");
   return conv_run_nchw(conv, x, y, batch, conv->d.out_dtype == PLB_OUT_I8 ? OUT_I8 : OUT_F32);
 }
 
 int plb_conv_acc_i32(plb_conv* conv, const int8_t* x, int32_t* acc, int batch) {
-  PLB_REQUIRE(conv && x && acc, "null argument");
+  PLB_REQUIRE(conv != nullptr, "null argument");
   PLB_REQUIRE(batch >= 0, "negative batch");
   if (batch == 0) return PLB_OK;
+  PLB_REQUIRE(x && acc, "null argument");
   return conv_run_nchw(conv, x, acc, batch, OUT_ACC);
 }
 
 int plb_conv_run_nhwc(plb_conv* conv, const int8_t* x, void* y, int batch) {
-  PLB_REQUIRE(conv && x && y, "null argument");
+  PLB_REQUIRE(conv != nullptr, "null argument");
   PLB_REQUIRE(batch >= 0, "negative batch");
+  if (batch == 0) return PLB_OK;
+  PLB_REQUIRE(x && y, "null argument");
   PLB_REQUIRE(conv->cin_pad == conv->d.cin,
               "channels-last entry needs cin to be a multiple of %d (got %d)",
               conv->kind == 0 || conv->d.groups == 1 ? 32 : 16, conv->d.cin);
@@ -494,16 +498,18 @@ static int fc_run_mode(plb_fc* f, const int8_t* x, void* y, int m, int mode) {
 }
 
 int plb_fc_run(plb_fc* fc, const int8_t* x, void* y, int m) {
-  PLB_REQUIRE(fc && x && y, "null argument");
+  PLB_REQUIRE(fc != nullptr, "null argument");
   PLB_REQUIRE(m >= 0, "negative row count");
   if (m == 0) return PLB_OK;
+  PLB_REQUIRE(x && y, "null argument");
   return fc_run_mode(fc, x, y, m, fc->out_dtype == PLB_OUT_I8 ? OUT_I8 : OUT_F32);
 }
 
 int plb_fc_acc_i32(plb_fc* fc, const int8_t* x, int32_t* acc, int m) {
-  PLB_REQUIRE(fc && x && acc, "null argument");
+  PLB_REQUIRE(fc != nullptr, "null argument");
   PLB_REQUIRE(m >= 0, "negative row count");
   if (m == 0) return PLB_OK;
+  PLB_REQUIRE(x && acc, "null argument");
   return fc_run_mode(fc, x, acc, m, OUT_ACC);
 }
 
@@ -635,9 +641,10 @@ int plb_sparse_prepare(plb_ctx* ctx, const plb_sparse_desc* desc, const void* no
 }
 
 int plb_sparse_run(plb_sparse* sp, const void* x, void* y, int batch) {
-  PLB_REQUIRE(sp && x && y, "null argument");
+  PLB_REQUIRE(sp != nullptr, "null argument");
   PLB_REQUIRE(batch >= 0, "negative batch");
   if (batch == 0) return PLB_OK;
+  PLB_REQUIRE(x && y, "null argument");
   if (sp->dense) return plb_conv_run(sp->dense, static_cast<const int8_t*>(x), y, batch);
   PLB_CUDA(cudaSetDevice(sp->ctx->device));
   SparseGeom g;

@@ -1,0 +1,256 @@
+"""The two whole networks the path is measured on, as chains of the int8 layers of this
+library: ResNet-50 v1.5 and MobileNetV1 1.0 at 224x224, post-training quantised.
+
+Graph semantics follow what the reference's optimiser produces for a quantised model
+(lite/core/optimizer/optimizer.cc:128-294): conv + BN folded into an int8 conv with fp32 bias,
+ReLU fused into the conv, a conv whose consumers are all int8 layers writes int8 (alias
+int8_out), a conv feeding an fp32 op (elementwise_add, pool2d avg) writes fp32 (fp32_out),
+`calib` converts fp32 -> int8 in front of the next int8 layer
+(lite/core/optimizer/mir/static_kernel_pick_pass.cc:100-121, type_precision_cast_pass.cc:75-105).
+Max pooling runs on the int8 tensor: max commutes with the monotonic quantiser, so it equals
+fp32 pooling followed by calib at the same scale.
+
+There are no model files: weights are seeded He-init, activation scales come from an fp32
+calibration pass over seeded N(0,1) images (set-up work, done with torch ops; the timed path
+is only the C-ABI library).
+"""
+import numpy as np
+
+ACT_NONE, ACT_RELU = 0, 1
+
+
+# ----------------------------------------------------------------------------- specs
+def resnet50_spec():
+    """List of ops.  Tensor names: 'x' is the int8 image; every op names its inputs/outputs."""
+    ops = [dict(op="conv", name="conv1", src="x", dst="c1", cin=3, cout=64, k=7, s=2, p=3, act=ACT_RELU, out="i8"),
+           dict(op="maxpool", name="pool1", src="c1", dst="b0", k=3, s=2, p=1)]
+    cin = 64
+    prev = "b0"          # int8 block input
+    prev_f32 = None      # fp32 block input (identity shortcut)
+    for stage, (width, blocks, stride) in enumerate([(64, 3, 1), (128, 4, 2), (256, 6, 2), (512, 3, 2)], 1):
+        for b in range(blocks):
+            s = stride if b == 0 else 1
+            pre = "s%db%d" % (stage, b)
+            ops.append(dict(op="conv", name=pre + "a", src=prev, dst=pre + "a", cin=cin, cout=width, k=1, s=1,
+                            p=0, act=ACT_RELU, out="i8"))
+            ops.append(dict(op="conv", name=pre + "b", src=pre + "a", dst=pre + "b", cin=width, cout=width,
+                            k=3, s=s, p=1, act=ACT_RELU, out="i8"))
+            if b == 0:
+                ops.append(dict(op="conv", name=pre + "ds", src=prev, dst=pre + "ds", cin=cin, cout=4 * width,
+                                k=1, s=s, p=0, act=ACT_NONE, out="f32"))
+                shortcut = pre + "ds"
+            else:
+                shortcut = prev_f32
+            last = stage == 4 and b == blocks - 1
+            next_needs_f32 = (b != blocks - 1) or last
+            ops.append(dict(op="conv_add_relu", name=pre + "c", src=pre + "b", residual=shortcut,
+                            dst_f32=(pre + "f") if next_needs_f32 else None,
+                            dst_i8=None if last else pre + "q", cin=width, cout=4 * width, k=1, s=1, p=0))
+            prev, prev_f32, cin = pre + "q", pre + "f", 4 * width
+    ops.append(dict(op="avgpool_calib", name="pool5", src=prev_f32, dst="feat", c=2048))
+    ops.append(dict(op="fc", name="fc", src="feat", dst="logits", k=2048, n=1000))
+    return dict(name="resnet50_v1.5", ops=ops, image=(3, 224, 224))
+
+
+def mobilenet_v1_spec():
+    ops = [dict(op="conv", name="conv1", src="x", dst="c1", cin=3, cout=32, k=3, s=2, p=1, act=ACT_RELU, out="i8")]
+    cfg = [(32, 64, 1), (64, 128, 2), (128, 128, 1), (128, 256, 2), (256, 256, 1), (256, 512, 2)] + \
+          [(512, 512, 1)] * 5 + [(512, 1024, 2), (1024, 1024, 1)]
+    prev = "c1"
+    for i, (cin, cout, s) in enumerate(cfg, 1):
+        ops.append(dict(op="conv", name="dw%d" % i, src=prev, dst="dw%d" % i, cin=cin, cout=cin, k=3, s=s, p=1,
+                        groups=cin, act=ACT_RELU, out="i8"))
+        last = i == len(cfg)
+        ops.append(dict(op="conv", name="pw%d" % i, src="dw%d" % i, dst="pw%d" % i, cin=cin, cout=cout, k=1, s=1,
+                        p=0, act=ACT_RELU, out="f32" if last else "i8"))
+        prev = "pw%d" % i
+    ops.append(dict(op="avgpool_calib", name="pool", src=prev, dst="feat", c=1024))
+    ops.append(dict(op="fc", name="fc", src="feat", dst="logits", k=1024, n=1000))
+    return dict(name="mobilenet_v1_1.0", ops=ops, image=(3, 224, 224))
+
+
+SPECS = {"resnet50": resnet50_spec, "mobilenet_v1": mobilenet_v1_spec}
+
+
+def conv_macs_per_image(spec):
+    """Multiply-accumulates of the conv and fc layers for one image."""
+    c, h, w = spec["image"]
+    hw = {"x": (h, w)}
+    macs = 0
+    for op in spec["ops"]:
+        if op["op"] in ("conv", "conv_add_relu"):
+            ih, iw = hw[op["src"]]
+            oh, ow = (ih + 2 * op["p"] - op["k"]) // op["s"] + 1, (iw + 2 * op["p"] - op["k"]) // op["s"] + 1
+            macs += oh * ow * op["cout"] * (op["cin"] // op.get("groups", 1)) * op["k"] ** 2
+            for key in ("dst", "dst_f32", "dst_i8"):
+                if op.get(key):
+                    hw[op[key]] = (oh, ow)
+        elif op["op"] == "maxpool":
+            ih, iw = hw[op["src"]]
+            hw[op["dst"]] = ((ih + 2 * op["p"] - op["k"]) // op["s"] + 1, (iw + 2 * op["p"] - op["k"]) // op["s"] + 1)
+        elif op["op"] == "fc":
+            macs += op["k"] * op["n"]
+    return macs
+
+
+# ----------------------------------------------------------------------------- weights + calibration
+def _quant_per_channel(w):
+    red = tuple(range(1, w.ndim))
+    amax = np.maximum(np.abs(w).max(axis=red, keepdims=True), 1e-12)
+    scale = (amax / 127.0).astype(np.float32)
+    return np.clip(np.rint(w / scale), -127, 127).astype(np.int8), scale.reshape(-1).astype(np.float32)
+
+
+def build_quantized(spec, seed=1234, calib_images=16, device="cpu"):
+    """He-init weights, per-channel int8 quantisation, activation scales from an fp32 pass over
+    `calib_images` seeded N(0,1) images.  Returns a dict the runner and the test oracle share."""
+    import torch
+    import torch.nn.functional as F
+    rng = np.random.default_rng(seed)
+    params = {}
+    for op in spec["ops"]:
+        if op["op"] in ("conv", "conv_add_relu"):
+            cig = op["cin"] // op.get("groups", 1)
+            fan_in = cig * op["k"] ** 2
+            w = (rng.standard_normal((op["cout"], cig, op["k"], op["k"])) * np.sqrt(2.0 / fan_in)).astype(np.float32)
+            b = (rng.standard_normal(op["cout"]) * 0.1).astype(np.float32)
+            params[op["name"]] = dict(w=w, b=b)
+        elif op["op"] == "fc":
+            w = (rng.standard_normal((op["k"], op["n"])) * np.sqrt(2.0 / op["k"])).astype(np.float32)
+            b = (rng.standard_normal(op["n"]) * 0.1).astype(np.float32)
+            params[op["name"]] = dict(w=w, b=b)
+    # fp32 calibration pass: maxima of every tensor that will be stored as int8
+    x = torch.from_numpy(rng.standard_normal((calib_images,) + spec["image"]).astype(np.float32)).to(device)
+    t = {"x": x}
+    amax = {"x": float(x.abs().max())}
+    tt = lambda a: torch.from_numpy(a).to(device)  # noqa: E731
+    for op in spec["ops"]:
+        if op["op"] == "conv":
+            p = params[op["name"]]
+            y = F.conv2d(t[op["src"]], tt(p["w"]), tt(p["b"]), stride=op["s"], padding=op["p"],
+                         groups=op.get("groups", 1))
+            if op["act"] == ACT_RELU:
+                y = F.relu(y)
+            t[op["dst"]] = y
+            amax[op["dst"]] = float(y.abs().max())
+        elif op["op"] == "conv_add_relu":
+            p = params[op["name"]]
+            y = F.relu(F.conv2d(t[op["src"]], tt(p["w"]), tt(p["b"])) + t[op["residual"]])
+            for key in ("dst_f32", "dst_i8"):
+                if op.get(key):
+                    t[op[key]] = y
+                    amax[op[key]] = float(y.abs().max())
+        elif op["op"] == "maxpool":
+            y = F.max_pool2d(t[op["src"]], op["k"], op["s"], op["p"])
+            t[op["dst"]] = y
+            amax[op["dst"]] = amax[op["src"]]  # same scale as its input: pooling happens in int8
+        elif op["op"] == "avgpool_calib":
+            y = t[op["src"]].mean(dim=(2, 3))
+            t[op["dst"]] = y
+            amax[op["dst"]] = float(y.abs().max())
+        elif op["op"] == "fc":
+            p = params[op["name"]]
+            t[op["dst"]] = t[op["src"]] @ tt(p["w"]) + tt(p["b"])
+    scales = {k: np.float32(max(v, 1e-8) / 127.0) for k, v in amax.items()}
+    layers = {}
+    for op in spec["ops"]:
+        if op["name"] in params:
+            p = params[op["name"]]
+            if op["op"] == "fc":
+                wq_t, ws = _quant_per_channel(np.ascontiguousarray(p["w"].T))  # per output feature
+                wq = np.ascontiguousarray(wq_t.T)
+            else:
+                wq, ws = _quant_per_channel(p["w"])
+            layers[op["name"]] = dict(wq=wq, ws=ws, bias=p["b"])
+    return dict(spec=spec, layers=layers, scales=scales)
+
+
+# ----------------------------------------------------------------------------- GPU runner
+class Runner:
+    """Holds the prepared layers and all activation buffers for one batch size on one GPU and
+    enqueues a whole forward pass on the context's stream (no allocation, no host sync)."""
+
+    def __init__(self, plb, ctx, qnet, batch):
+        import torch
+        self.plb, self.ctx, self.q, self.batch = plb, ctx, qnet, batch
+        spec, scales = qnet["spec"], qnet["scales"]
+        dev = "cuda:%d" % ctx.device
+        c, h, w = spec["image"]
+        self.hw = {"x": (h, w)}
+        self.buf = {"x": torch.empty((batch, h, w, 32), dtype=torch.int8, device=dev)}
+        self.steps = []
+        self.image_shape = (batch, c, h, w)
+        for op in spec["ops"]:
+            kind = op["op"]
+            if kind in ("conv", "conv_add_relu"):
+                L = qnet["layers"][op["name"]]
+                ih, iw = self.hw[op["src"]]
+                wq = L["wq"]
+                if op["src"] == "x":  # image is stored with 32 channels, the extra ones are zero
+                    wq = np.concatenate([wq, np.zeros((wq.shape[0], 32 - wq.shape[1]) + wq.shape[2:], np.int8)], 1)
+                in_s = float(scales[op["src"]])
+                if kind == "conv":
+                    out_s = float(scales[op["dst"]]) if op["out"] == "i8" else None
+                    groups = op.get("groups", 1)
+                    conv = plb.Conv(ctx, wq, L["ws"], in_s, L["bias"], in_hw=(ih, iw), stride=(op["s"], op["s"]),
+                                    pads=(op["p"],) * 4, groups=groups, act=op["act"], out_scale=out_s)
+                    dt = torch.int8 if out_s is not None else torch.float32
+                    self.buf[op["dst"]] = torch.empty((batch, conv.ho, conv.wo, op["cout"]), dtype=dt, device=dev)
+                    self.hw[op["dst"]] = (conv.ho, conv.wo)
+                    self.steps.append(("conv", conv, op["src"], op["dst"]))
+                else:
+                    conv = plb.Conv(ctx, wq, L["ws"], in_s, L["bias"], in_hw=(ih, iw))
+                    shape = (batch, conv.ho, conv.wo, op["cout"])
+                    if op["dst_f32"]:
+                        self.buf[op["dst_f32"]] = torch.empty(shape, dtype=torch.float32, device=dev)
+                        self.hw[op["dst_f32"]] = (conv.ho, conv.wo)
+                    if op["dst_i8"]:
+                        self.buf[op["dst_i8"]] = torch.empty(shape, dtype=torch.int8, device=dev)
+                        self.hw[op["dst_i8"]] = (conv.ho, conv.wo)
+                    next_s = float(scales[op["dst_i8"]]) if op["dst_i8"] else None
+                    self.steps.append(("conv_add_relu", conv, op["src"], op["residual"], op["dst_f32"],
+                                       op["dst_i8"], next_s))
+            elif kind == "maxpool":
+                ih, iw = self.hw[op["src"]]
+                oh, ow = (ih + 2 * op["p"] - op["k"]) // op["s"] + 1, (iw + 2 * op["p"] - op["k"]) // op["s"] + 1
+                cch = self.buf[op["src"]].shape[3]
+                self.buf[op["dst"]] = torch.empty((batch, oh, ow, cch), dtype=torch.int8, device=dev)
+                self.hw[op["dst"]] = (oh, ow)
+                self.steps.append(("maxpool", op["src"], op["dst"], op["k"], op["s"], op["p"]))
+            elif kind == "avgpool_calib":
+                self.buf[op["dst"]] = torch.empty((batch, op["c"]), dtype=torch.int8, device=dev)
+                self.buf[op["dst"] + "_f32"] = torch.empty((batch, op["c"]), dtype=torch.float32, device=dev)
+                self.steps.append(("avgpool_calib", op["src"], op["dst"], float(scales[op["dst"]])))
+            elif kind == "fc":
+                L = qnet["layers"][op["name"]]
+                fc = plb.Fc(ctx, L["wq"], L["ws"], float(scales[op["src"]]), L["bias"])
+                self.buf[op["dst"]] = torch.empty((batch, op["n"]), dtype=torch.float32, device=dev)
+                self.steps.append(("fc", fc, op["src"], op["dst"]))
+        self.in_scale = float(scales["x"])
+
+    def forward(self, image_f32_nchw):
+        """image_f32_nchw: device float32 [batch,3,224,224].  Returns the fp32 logits buffer."""
+        self.forward_head(image_f32_nchw)
+        return self.forward_body()
+
+    def forward_head(self, image_f32_nchw):
+        """calib + layout staging of the fp32 image (the only reader of the input tensor)."""
+        self.ctx.calib_nchw_f32_to_nhwc_i8(image_f32_nchw, 32, self.in_scale, out=self.buf["x"])
+
+    def forward_body(self):
+        """Everything after the image has been quantised; touches only preallocated buffers."""
+        b, ctx = self.buf, self.ctx
+        for st in self.steps:
+            if st[0] == "conv":
+                st[1].run_nhwc(b[st[2]], out=b[st[3]])
+            elif st[0] == "conv_add_relu":
+                _, conv, src, res, df, dq, next_s = st
+                conv.run_nhwc_add_relu(b[src], b[res], next_s, want_f32=df is not None,
+                                       out_f32=b[df] if df else None, out_i8=b[dq] if dq else None)
+            elif st[0] == "maxpool":
+                ctx.maxpool_nhwc_i8(b[st[1]], st[3], st[4], st[5], out=b[st[2]])
+            elif st[0] == "avgpool_calib":
+                ctx.global_avgpool_nhwc_f32(b[st[1]], scale=st[3], out_f32=b[st[2] + "_f32"], out_i8=b[st[2]])
+            elif st[0] == "fc":
+                st[1].run(b[st[2]], out=b[st[3]])
+        return b["logits"]

@@ -1,0 +1,187 @@
+"""Parity of the CUDA conv2d / depthwise_conv2d kernels with the exact-integer oracle and the
+reference golden vectors, called through the C ABI (plb_conv_*)."""
+import numpy as np
+import pytest
+import torch
+
+from helpers import O, assert_f32_close, assert_i8_close, conv_case, golden, golden_names
+
+pytestmark = pytest.mark.gpu
+DATA = golden()
+
+
+def dev(a):
+    return torch.from_numpy(np.ascontiguousarray(a)).cuda()
+
+
+def run_case(plb, ctx, xq, in_s, wq, ws, bias, *, stride=(1, 1), pads=(0, 0, 0, 0), dil=(1, 1), groups=1,
+             act=0, alpha=0.0, impl=0, check_i8=True, leaky_compat=False):
+    """Runs accumulators, fp32-out and int8-out through the ABI and checks all three against the oracle."""
+    kw = dict(stride=stride, pads=pads, dil=dil, groups=groups)
+    acc_ref = O.conv_acc_i32(xq, wq, **kw)
+    y_ref = O.epilogue(acc_ref, ws, in_s, bias, act, alpha)
+    x = dev(xq)
+    conv = plb.Conv(ctx, wq, ws, in_s, bias, in_hw=xq.shape[2:], act=act, alpha=alpha, impl=impl, **kw)
+    acc = conv.acc_i32(x)
+    y = conv.run(x)
+    ctx.sync()
+    assert np.array_equal(acc.cpu().numpy(), acc_ref), "int32 accumulators differ (%d of %d)" % (
+        int((acc.cpu().numpy() != acc_ref).sum()), acc_ref.size)
+    assert np.array_equal(y.cpu().numpy(), y_ref), "fp32 outputs are not bit-identical to the oracle"
+    if check_i8:
+        out_s = float(max(np.abs(y_ref).max(), 1e-6) / 127.0)
+        q_ref = O.epilogue(acc_ref, ws, in_s, bias, act, alpha, out_scale=out_s, leaky_compat=leaky_compat)
+        conv8 = plb.Conv(ctx, wq, ws, in_s, bias, in_hw=xq.shape[2:], act=act, alpha=alpha, impl=impl,
+                         out_scale=out_s, leaky_compat=leaky_compat, **kw)
+        q = conv8.run(x)
+        ctx.sync()
+        assert np.array_equal(q.cpu().numpy(), q_ref), "int8 outputs are not bit-identical to the oracle"
+    return y_ref
+
+
+@pytest.mark.parametrize("impl", [1, 0], ids=["direct", "auto"])
+@pytest.mark.parametrize("name", golden_names(DATA, "conv"))
+def test_golden_vectors(plb, ctx, name, impl):
+    """Outputs of the reference's own x86 objects (committed fixtures): fp32 within 1e-5 of the
+    largest output, int8 within 1 LSB on at most 0.1 % of the elements."""
+    g = {k.split("/")[1]: DATA[k] for k in DATA.files if k.startswith(name + "/")}
+    n, cin, h, w, cout, k, s, p, groups, act = [int(v) for v in g["meta"]]
+    kw = dict(stride=(s, s), pads=(p, p, p, p), groups=groups, act=act, alpha=float(g["alpha"]), impl=impl)
+    x = dev(g["x"])
+    conv = plb.Conv(ctx, g["w"], g["ws"], float(g["in_s"]), g["bias"], in_hw=(h, w), **kw)
+    y = conv.run(x).cpu().numpy()
+    conv8 = plb.Conv(ctx, g["w"], g["ws"], float(g["in_s"]), g["bias"], in_hw=(h, w),
+                     out_scale=float(g["out_s"]), leaky_compat=True, **kw)
+    q = conv8.run(x).cpu().numpy()
+    ctx.sync()
+    assert_f32_close(y, g["y_f32"], rel=1e-5, floor=float(np.abs(g["y_f32"]).max()))
+    assert_i8_close(q, g["y_i8"])
+
+
+# (n, cin, h, w, cout, k, stride, pad, act, alpha)
+DENSE_CASES = [
+    (1, 64, 56, 56, 64, 3, 1, 1, 1, 0.0),      # the single-layer benchmark config
+    (2, 64, 14, 14, 256, 1, 1, 0, 1, 0.0),     # pointwise, flat GEMM path
+    (3, 128, 28, 28, 128, 3, 2, 1, 1, 0.0),    # strided 3x3
+    (2, 256, 14, 14, 512, 1, 2, 0, 0, 0.0),    # strided 1x1 (downsample)
+    (2, 3, 32, 32, 32, 7, 2, 3, 1, 0.0),       # stem: 3 input channels, 7x7
+    (1, 32, 9, 11, 48, 3, 1, 1, 2, 6.0),       # odd sizes, relu6, cout not a multiple of 32
+    (5, 96, 7, 7, 24, 1, 1, 0, 3, 0.1),        # leaky, ragged tile tails
+    (1, 512, 7, 7, 512, 3, 1, 1, 1, 0.0),      # long K
+    (1, 40, 6, 6, 20, 3, 1, 0, 0, 0.0),        # cin, cout not multiples of 16/32
+]
+
+
+@pytest.mark.parametrize("impl", [1, 0], ids=["direct", "auto"])
+@pytest.mark.parametrize("case", DENSE_CASES, ids=lambda c: "x".join(map(str, c[:8])))
+def test_dense_conv_bit_exact(plb, ctx, case, impl):
+    n, cin, h, w, cout, k, s, p, act, alpha = case
+    xq, in_s, wq, ws, bias = conv_case(hash(case) % 10000, n, cin, h, w, cout, k)
+    run_case(plb, ctx, xq, in_s, wq, ws, bias, stride=(s, s), pads=(p, p, p, p), act=act, alpha=alpha,
+             impl=impl)
+
+
+def test_asymmetric_pad_dilation(plb, ctx):
+    xq, in_s, wq, ws, bias = conv_case(77, 2, 32, 13, 10, 32, (3, 2))
+    for impl in (1, 0):
+        run_case(plb, ctx, xq, in_s, wq, ws, bias, stride=(2, 1), pads=(0, 1, 2, 0), dil=(1, 2), act=1,
+                 impl=impl)
+
+
+# (n, c, h, w, k, stride, pad, act, alpha)
+DW_CASES = [
+    (2, 32, 112, 112, 3, 1, 1, 1, 0.0),
+    (2, 64, 56, 56, 3, 2, 1, 1, 0.0),
+    (1, 512, 14, 14, 3, 1, 1, 2, 6.0),
+    (3, 24, 9, 9, 3, 2, 1, 0, 0.0),   # channels not a multiple of 16
+    (1, 1024, 7, 7, 3, 1, 1, 1, 0.0),
+    (1, 16, 10, 10, 5, 1, 2, 3, 0.2),
+]
+
+
+@pytest.mark.parametrize("case", DW_CASES, ids=lambda c: "x".join(map(str, c[:7])))
+def test_depthwise_bit_exact(plb, ctx, case):
+    n, c, h, w, k, s, p, act, alpha = case
+    xq, in_s, wq, ws, bias = conv_case(hash(case) % 10000, n, c, h, w, c, k, groups=c, w_std=0.3)
+    run_case(plb, ctx, xq, in_s, wq, ws, bias, stride=(s, s), pads=(p, p, p, p), groups=c, act=act,
+             alpha=alpha)
+
+
+def test_grouped_conv(plb, ctx):
+    xq, in_s, wq, ws, bias = conv_case(9, 2, 32, 12, 12, 48, 3, groups=4)
+    run_case(plb, ctx, xq, in_s, wq, ws, bias, pads=(1, 1, 1, 1), groups=4, act=1)
+
+
+def test_scalar_weight_scale_and_no_bias(plb, ctx):
+    xq, in_s, wq, ws, _ = conv_case(10, 1, 32, 8, 8, 32, 1)
+    run_case(plb, ctx, xq, in_s, wq, ws[:1], None, act=1)
+
+
+def test_leaky_compat_switch(plb, ctx):
+    xq, in_s, wq, ws, bias = conv_case(12, 1, 32, 8, 8, 32, 3)
+    run_case(plb, ctx, xq, in_s, wq, ws, bias, pads=(1, 1, 1, 1), act=3, alpha=0.1, leaky_compat=True)
+    run_case(plb, ctx, xq, in_s, wq, ws, bias, pads=(1, 1, 1, 1), act=3, alpha=0.1, leaky_compat=False)
+
+
+def test_batch_zero_and_rerun(plb, ctx):
+    xq, in_s, wq, ws, bias = conv_case(13, 4, 32, 8, 8, 32, 3)
+    conv = plb.Conv(ctx, wq, ws, in_s, bias, in_hw=(8, 8), pads=(1, 1, 1, 1), act=1)
+    empty = torch.empty((0, 32, 8, 8), dtype=torch.int8, device="cuda")
+    assert conv.run(empty).shape[0] == 0
+    want = O.conv_int8(xq, wq, ws, in_s, bias, O.ACT_RELU, pads=(1, 1, 1, 1))
+    for nb in (4, 1, 3):  # batch changes between runs of one prepared layer
+        y = conv.run(dev(xq[:nb])).cpu().numpy()
+        assert np.array_equal(y, want[:nb])
+    ctx.sync()
+
+
+def test_prepare_errors(plb, ctx):
+    xq, in_s, wq, ws, bias = conv_case(14, 1, 32, 8, 8, 32, 3)
+    with pytest.raises(plb.PlbError) as e:  # conv_compute.cc:242-244
+        plb.Conv(ctx, wq, ws[:5], in_s, bias, in_hw=(8, 8))
+    assert e.value.code == plb.E_INVALID
+    with pytest.raises(plb.PlbError):
+        plb.Conv(ctx, wq, ws, in_s, bias, in_hw=(1, 1))  # empty output
+    with pytest.raises(plb.PlbError):
+        plb.Conv(ctx, wq, ws, in_s, bias, in_hw=(8, 8), act=7)
+    with pytest.raises(plb.PlbError):
+        plb.Conv(ctx, wq, ws, -1.0, bias, in_hw=(8, 8))
+
+
+def test_nhwc_entry_and_fused_add_relu(plb, ctx):
+    """Channels-last entry points: same values as the NCHW path; the fused conv + add + relu +
+    calib equals the unfused oracle sequence bit for bit."""
+    xq, in_s, wq, ws, bias = conv_case(15, 2, 64, 14, 14, 128, 1)
+    acc = O.conv_acc_i32(xq, wq)
+    y_ref = O.epilogue(acc, ws, in_s, bias, O.ACT_NONE, 0.0)
+    rng = np.random.default_rng(3)
+    res = rng.standard_normal(y_ref.shape).astype(np.float32)
+    s_ref = np.maximum(y_ref + res, np.float32(0))
+    next_s = float(np.abs(s_ref).max() / 127)
+    q_ref = O.calib_f32_to_i8(s_ref, next_s)
+    x_nhwc = dev(np.ascontiguousarray(xq.transpose(0, 2, 3, 1)))
+    conv = plb.Conv(ctx, wq, ws, in_s, bias, in_hw=(14, 14))
+    y = conv.run_nhwc(x_nhwc).cpu().numpy().transpose(0, 3, 1, 2)
+    assert np.array_equal(y, y_ref)
+    yf, yq = conv.run_nhwc_add_relu(x_nhwc, dev(np.ascontiguousarray(res.transpose(0, 2, 3, 1))), next_s)
+    ctx.sync()
+    assert np.array_equal(yf.cpu().numpy().transpose(0, 3, 1, 2), s_ref)
+    assert np.array_equal(yq.cpu().numpy().transpose(0, 3, 1, 2), q_ref)
+
+
+def test_linearity_at_full_size(plb, ctx):
+    """Size-independent property at benchmark scale (batch 32 of the 64->64 3x3 layer):
+    accumulators are linear in the input, acc(x1) + acc(x2) == acc(x1 + x2) for inputs whose sum
+    stays in int8 range."""
+    rng = np.random.default_rng(21)
+    x1 = rng.integers(-60, 61, (32, 64, 56, 56), dtype=np.int8)
+    x2 = rng.integers(-60, 61, (32, 64, 56, 56), dtype=np.int8)
+    wq = rng.integers(-127, 128, (64, 64, 3, 3), dtype=np.int8)
+    conv = plb.Conv(ctx, wq, [0.01], 0.02, None, in_hw=(56, 56), pads=(1, 1, 1, 1))
+    a1 = conv.acc_i32(dev(x1))
+    a2 = conv.acc_i32(dev(x2))
+    a3 = conv.acc_i32(dev((x1 + x2).astype(np.int8)))
+    ctx.sync()
+    assert torch.equal(a1 + a2, a3)
+    # spot-check one image against the oracle
+    assert np.array_equal(a3[5:6].cpu().numpy(), O.conv_acc_i32((x1 + x2)[5:6], wq, pads=(1, 1, 1, 1)))

@@ -1,0 +1,70 @@
+"""Parity of the CUDA fc kernel (plb_fc_*) with the oracle and the reference golden vectors."""
+import numpy as np
+import pytest
+import torch
+
+from helpers import O, assert_f32_close, assert_i8_close, fc_case, golden, golden_names
+
+pytestmark = pytest.mark.gpu
+DATA = golden()
+
+
+def dev(a):
+    return torch.from_numpy(np.ascontiguousarray(a)).cuda()
+
+
+@pytest.mark.parametrize("name", golden_names(DATA, "fc"))
+def test_golden_vectors(plb, ctx, name):
+    g = {k.split("/")[1]: DATA[k] for k in DATA.files if k.startswith(name + "/")}
+    m, k, n, act = [int(v) for v in g["meta"]]
+    x = dev(g["x"])
+    y = plb.Fc(ctx, g["w"], g["ws"], float(g["in_s"]), g["bias"], act, float(g["alpha"])).run(x).cpu().numpy()
+    q = plb.Fc(ctx, g["w"], g["ws"], float(g["in_s"]), g["bias"], act, float(g["alpha"]),
+               out_scale=float(g["out_s"])).run(x).cpu().numpy()
+    ctx.sync()
+    assert_f32_close(y, g["y_f32"], rel=1e-5, floor=float(np.abs(g["y_f32"]).max()))
+    assert_i8_close(q, g["y_i8"])
+
+
+# the fc sweep of the benchmark configs plus ragged shapes
+@pytest.mark.parametrize("m,k,n", [(1, 1024, 1000), (64, 2048, 1000), (256, 4096, 4096), (7, 96, 17),
+                                   (130, 160, 40), (3, 100, 12)])
+def test_fc_bit_exact(plb, ctx, m, k, n):
+    x, wq, ws, bias = fc_case(m * 7 + n, m, k, n)
+    in_s = 0.02
+    acc_ref = O.fc_acc_i32(x, wq)
+    y_ref = O.epilogue(acc_ref, ws, in_s, bias, O.ACT_RELU6, 6.0)
+    out_s = float(max(np.abs(y_ref).max(), 1e-6) / 127)
+    q_ref = O.epilogue(acc_ref, ws, in_s, bias, O.ACT_RELU6, 6.0, out_scale=out_s)
+    xd = dev(x)
+    fc = plb.Fc(ctx, wq, ws, in_s, bias, O.ACT_RELU6, 6.0)
+    fc8 = plb.Fc(ctx, wq, ws, in_s, bias, O.ACT_RELU6, 6.0, out_scale=out_s)
+    acc = fc.acc_i32(xd).cpu().numpy()
+    y = fc.run(xd).cpu().numpy()
+    q = fc8.run(xd).cpu().numpy()
+    ctx.sync()
+    assert np.array_equal(acc, acc_ref)
+    assert np.array_equal(y, y_ref)
+    assert np.array_equal(q, q_ref)
+
+
+def test_fc_4096_cubed_checksum(plb, ctx):
+    """Largest sweep shape: the oracle would need minutes, so check the column sums instead:
+    sum_m acc[m, :] == (sum_m x[m, :]) @ w, exact in int64."""
+    x, wq, ws, bias = fc_case(99, 4096, 4096, 4096)
+    fc = plb.Fc(ctx, wq, ws, 0.02, bias)
+    acc = fc.acc_i32(dev(x))
+    ctx.sync()
+    got = acc.to(torch.int64).sum(dim=0).cpu().numpy()
+    want = x.astype(np.int64).sum(axis=0) @ wq.astype(np.int64)
+    assert np.array_equal(got, want)
+    rows = [0, 1, 2047, 4095]
+    assert np.array_equal(acc[rows].cpu().numpy(), O.fc_acc_i32(x[rows], wq))
+
+
+def test_fc_errors(plb, ctx):
+    x, wq, ws, bias = fc_case(1, 4, 64, 8)
+    with pytest.raises(plb.PlbError):
+        plb.Fc(ctx, wq, ws[:3], 0.02, bias)
+    fc = plb.Fc(ctx, wq, ws, 0.02, bias)
+    assert fc.run(torch.empty((0, 64), dtype=torch.int8, device="cuda")).shape == (0, 8)

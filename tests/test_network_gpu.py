@@ -1,0 +1,65 @@
+"""Whole-network parity: ResNet-50 v1.5 and MobileNetV1 int8 on the GPU against the oracle
+forward pass, tensor by tensor, bit for bit."""
+import importlib
+import os
+import sys
+
+import numpy as np
+import pytest
+import torch
+
+import net_oracle
+from helpers import ROOT
+
+pytestmark = pytest.mark.gpu
+
+
+def nets():
+    sys.path.insert(0, os.path.join(ROOT, "paddle-lite_b200"))
+    return importlib.import_module("paddle-lite_b200.networks")
+
+
+@pytest.mark.parametrize("name", ["mobilenet_v1", "resnet50"])
+def test_network_bit_exact(plb, ctx, name):
+    N = nets()
+    spec = N.SPECS[name]()
+    qnet = N.build_quantized(spec, seed=7, calib_images=4, device="cuda")
+    batch = 2
+    rng = np.random.default_rng(99)
+    images = rng.standard_normal((batch,) + spec["image"]).astype(np.float32)
+    runner = N.Runner(plb, ctx, qnet, batch)
+    logits = runner.forward(torch.from_numpy(images).cuda())
+    ctx.sync()
+    want = net_oracle.forward(qnet, images)
+    for key, ref in want.items():
+        if key not in runner.buf:
+            continue
+        got = runner.buf[key].cpu().numpy()
+        if got.ndim == 4:
+            got = got.transpose(0, 3, 1, 2)[:, :ref.shape[1]]
+        assert np.array_equal(got, ref), "tensor %s differs from the oracle (%d of %d elements)" % (
+            key, int((got != ref).sum()), ref.size)
+    assert np.array_equal(logits.cpu().numpy(), want["logits"])
+    assert np.isfinite(want["logits"]).all() and np.abs(want["logits"]).max() > 0
+
+
+def test_graph_replay_matches_eager(plb, ctx):
+    """The benchmark replays the forward pass as a CUDA graph; the replay must give the same
+    logits as the eager enqueue."""
+    N = nets()
+    spec = N.SPECS["mobilenet_v1"]()
+    qnet = N.build_quantized(spec, seed=3, calib_images=2, device="cuda")
+    stream = torch.cuda.Stream()
+    c2 = plb.Context(0, stream=stream)
+    runner = N.Runner(plb, c2, qnet, 4)
+    images = torch.randn((4,) + spec["image"], device="cuda")
+    with torch.cuda.stream(stream):
+        eager = runner.forward(images).clone()
+        c2.sync()
+        g = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(g, stream=stream):
+            runner.forward(images)
+        runner.buf["logits"].zero_()
+        g.replay()
+        c2.sync()
+    assert torch.equal(runner.buf["logits"], eager)
