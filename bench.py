@@ -12,8 +12,9 @@ data path).  Prints ONE JSON line on rank 0:
              launching stream (max over ranks)
   e2e        the same with host buffers: every step copies that step's fp32 images from pinned
              host memory and reads the logits back (copies overlap the previous step's compute)
-  roofline   of the dominant kernel (the tcgen05 implicit GEMM): algorithmic bytes of all its
-             launches in a step / their measured duration, against the measured HBM peak
+  roofline   of the dominant kernel (the tcgen05 implicit GEMM): algorithmic bytes of its
+             launches in a step (every conv/fc layer after the stem) / their measured duration,
+             against the measured HBM peak
   cpu_baseline  the reference's own x86 int8 path (oracle/_ref, built from the reference
              sources) on a bounded sample of the same workload, all host threads
 
@@ -108,8 +109,7 @@ def layer_bytes(spec, batch):
             ih, iw = hw[op["src"]]
             oh, ow = (ih + 2 * op["p"] - op["k"]) // op["s"] + 1, (iw + 2 * op["p"] - op["k"]) // op["s"] + 1
             groups = op.get("groups", 1)
-            cin_stored = 32 if op["src"] == "x" else op["cin"]
-            b = batch * ih * iw * cin_stored + op["cout"] * (op["cin"] // groups) * op["k"] ** 2 + 8 * op["cout"]
+            b = batch * ih * iw * op["cin"] + op["cout"] * (op["cin"] // groups) * op["k"] ** 2 + 8 * op["cout"]
             if op["op"] == "conv":
                 b += batch * oh * ow * op["cout"] * (1 if op["out"] == "i8" else 4)
                 hw[op["dst"]] = (oh, ow)
@@ -120,7 +120,7 @@ def layer_bytes(spec, batch):
                         b += batch * oh * ow * op["cout"] * size
                         hw[op[key]] = (oh, ow)
             m = batch * oh * ow * op["cout"] * (op["cin"] // groups) * op["k"] ** 2
-            if groups == 1:
+            if groups == 1 and op["src"] != "x":  # the stem runs with its staging kernel in the head
                 total_bytes += b
                 macs += m
                 launches += 1
@@ -306,7 +306,7 @@ def main():
         # graph of the tensor-core launches alone, for the roofline of the dominant kernel
         g_tc = torch.cuda.CUDAGraph()
         with torch.cuda.graph(g_tc, stream=stream):
-            for st in runner.steps:
+            for st in runner.steps[1:]:
                 if st[0] == "conv" and st[1].desc.groups == 1:
                     st[1].run_nhwc(runner.buf[st[2]], out=runner.buf[st[3]])
                 elif st[0] == "conv_add_relu":

@@ -103,6 +103,13 @@ int plb_conv_run(plb_conv* conv, const int8_t* x, void* y, int batch);
 /* Same arithmetic on channels-last tensors, no layout staging: x [batch,h,w,cin] int8 with
  * cin a multiple of 32 (depthwise: 16), y [batch,ho,wo,cout]. */
 int plb_conv_run_nhwc(plb_conv* conv, const int8_t* x, void* y, int batch);
+/* First layer of a network: x is the fp32 NCHW image [batch,cin,h,w].  Quantises it with the
+ * layer's input_scale (the `calib` op the reference inserts in front of the first int8 layer,
+ * lite/core/optimizer/mir/type_precision_cast_pass.cc:75-105, arithmetic of
+ * lite/backends/x86/math/calib.cc:25-151), stages it in the ctx workspace and runs the layer;
+ * y is channels-last [batch,ho,wo,cout].  Layers with few input channels (cin*kw <= 32, e.g.
+ * RGB stems) are staged row-folded so the tensor cores see 32-byte pixels. */
+int plb_conv_run_image_f32(plb_conv* conv, const float* x, void* y, int batch);
 /* Test hook: the raw int32 accumulators, NCHW [batch,cout,ho,wo] (bit-exact check). */
 int plb_conv_acc_i32(plb_conv* conv, const int8_t* x, int32_t* acc, int batch);
 /* conv (fp32 value, no activation of its own) + fp32 residual + ReLU, then optionally the

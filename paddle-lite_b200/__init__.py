@@ -59,6 +59,7 @@ SYMBOLS = {
     "plb_conv_run": (C.c_int, [_P, _P, _P, C.c_int]),
     "plb_conv_run_nhwc": (C.c_int, [_P, _P, _P, C.c_int]),
     "plb_conv_acc_i32": (C.c_int, [_P, _P, _P, C.c_int]),
+    "plb_conv_run_image_f32": (C.c_int, [_P, _P, _P, C.c_int]),
     "plb_conv_run_nhwc_add_relu": (C.c_int, [_P, _P, _P, _P, _P, C.c_float, C.c_int]),
     "plb_conv_out_dims": (C.c_int, [_P, C.POINTER(C.c_int), C.POINTER(C.c_int)]),
     "plb_conv_destroy": (None, [_P]),
@@ -260,6 +261,16 @@ class Conv:
             (n, self.ho, self.wo, self.desc.cout), dtype=torch.int8 if self.out_is_i8 else torch.float32,
             device=x.device)
         _check(lib().plb_conv_run_nhwc(self.handle, _dev_ptr(x), _dev_ptr(y), n))
+        return y
+
+    def run_image_f32(self, x, out=None):
+        """x [N,Cin,H,W] float32 (NCHW image) -> [N,Ho,Wo,Cout]; calib + staging + layer."""
+        import torch
+        n = x.shape[0]
+        y = out if out is not None else torch.empty(
+            (n, self.ho, self.wo, self.desc.cout), dtype=torch.int8 if self.out_is_i8 else torch.float32,
+            device=x.device)
+        _check(lib().plb_conv_run_image_f32(self.handle, _dev_ptr(x), _dev_ptr(y), n))
         return y
 
     def run_nhwc_add_relu(self, x, residual=None, next_scale=None, want_f32=True, out_f32=None, out_i8=None):

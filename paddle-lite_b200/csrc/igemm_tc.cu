@@ -7,19 +7,23 @@
 // (lite/backends/x86/math/avx/conv_utils.cc:1349-1398,
 //  lite/backends/x86/math/gemm_s8u8_compute.h:65-106, gemm_s8u8_kernel.cc:353-891).
 //
-// Persistent CTA (one per SM) of 10 warps:
-//   warps 0-7  epilogue: warp w reads TMEM lane quadrant w%4 and the 32-column chunks of
-//              parity w/4, so two warps share each quadrant;
-//   warp 8     TMA producer (one elected lane) filling a ring of operand stages;
-//   warp 9     TMEM allocation + MMA issue (one elected lane), two accumulator buffers so
-//              the epilogue of one tile overlaps the main loop of the next.
+// Persistent CTA (one per SM) of 18 warps:
+//   warps 0-15 epilogue, four groups of four warps (warp w reads TMEM lane quadrant w%4).
+//              With channel tiles of up to 128 there are four accumulator buffers and each
+//              group drains every fourth tile; with 256-wide tiles there are two buffers and
+//              two groups share a tile by 32-column chunks;
+//   warp 16    TMA producer (one elected lane) filling a ring of operand stages;
+//   warp 17    TMEM allocation + MMA issue (one elected lane); the epilogue of one tile
+//              overlaps the main loops of the following ones.
 // Tile = 128 output pixels x BN output channels, K consumed KC bytes per pipeline stage
 // (KC = 32/64/128 = the TMA swizzle span), 32 bytes of K per tcgen05.mma.
 // Every mbarrier wait is bounded; a wait that runs out records a fault in the ctx status
 // word and the CTA drains and exits instead of hanging.
 #include "igemm_tc.cuh"
 
+#include <algorithm>
 #include <cstdlib>
+#include <utility>
 
 namespace plb {
 
@@ -27,11 +31,13 @@ namespace {
 
 constexpr int kTileM = 128;
 constexpr int kMaxStages = 8;
-constexpr int kEpilogueWarps = 8;
-constexpr int kProducerWarp = 8;
-constexpr int kMmaWarp = 9;
-constexpr int kThreads = 320;
-constexpr int kCtrlBytes = 256 + 4 * 256 * 4;  // barriers + tmem slot, then 2 x (scale, bias) staging
+constexpr int kEpilogueGroups = 4;              // groups of 4 warps (one per TMEM lane quadrant)
+constexpr int kEpilogueWarps = 4 * kEpilogueGroups;
+constexpr int kProducerWarp = kEpilogueWarps;
+constexpr int kMmaWarp = kEpilogueWarps + 1;
+constexpr int kThreads = 32 * (kEpilogueWarps + 2);
+constexpr int kMaxAccBufs = 4;
+constexpr int kCtrlBytes = 256;                 // barriers + tmem slot
 constexpr uint32_t kWaitLimit = 1u << 22;      // polls before a wait is declared lost
 
 struct IgemmArgs {
@@ -174,13 +180,80 @@ __device__ __forceinline__ uint64_t make_smem_desc(uint32_t addr, int kc) {
 // ---------------------------------------------------------------- epilogue of 32 columns
 // One thread owns one output row (pixel) and 32 consecutive output channels of it, i.e. one
 // full 32-byte sector of an int8 row or one full 128-byte line of an fp32 row.
-__device__ __forceinline__ void epilogue_store32(const IgemmArgs& a, const uint32_t (&r)[32],
-                                                 long row, int col, const float* s_scale,
-                                                 const float* s_bias) {
+//
+// Rounding to int8 avoids the slow float->int conversion pipe: after clamping to
+// [-127, 127] the value is added to 1.5 * 2^23, whose ulp is 1, so the addition itself rounds
+// to nearest-even and leaves the two's-complement result in the low mantissa byte.
+
+constexpr float kRoundMagic = 12582912.f;  // 1.5 * 2^23
+
+template <int ACT>
+__device__ __forceinline__ uint32_t quant_byte(float v, float alpha) {
+  // clamp(rne(act(v)), -127, 127); rounding and clamping commute because the bounds are integers
+  if (ACT == PLB_ACT_NONE) {
+    v = fminf(fmaxf(v, -127.f), 127.f);
+  } else if (ACT == PLB_ACT_RELU) {
+    v = fminf(fmaxf(v, 0.f), 127.f);
+  } else if (ACT == PLB_ACT_RELU6) {
+    v = fminf(fmaxf(v, 0.f), alpha);  // alpha already limited to 127 by the caller
+  } else {
+    v = v <= 0.f ? alpha * v : v;
+    v = fminf(fmaxf(v, -127.f), 127.f);
+  }
+  return __float_as_uint(v + kRoundMagic);
+}
+
+__device__ __forceinline__ uint32_t pack_low_bytes(uint32_t a, uint32_t b, uint32_t c, uint32_t d) {
+  return __byte_perm(__byte_perm(a, b, 0x0040), __byte_perm(c, d, 0x0040), 0x5410);
+}
+
+// 256-bit global accesses: one full 32-byte sector per lane and instruction
+__device__ __forceinline__ void st_global_v8(void* p, uint32_t a, uint32_t b, uint32_t c, uint32_t d,
+                                             uint32_t e, uint32_t f, uint32_t g, uint32_t h) {
+  asm volatile("st.global.v8.b32 [%0], {%1, %2, %3, %4, %5, %6, %7, %8};" ::"l"(p), "r"(a), "r"(b),
+               "r"(c), "r"(d), "r"(e), "r"(f), "r"(g), "r"(h)
+               : "memory");
+}
+__device__ __forceinline__ void st_global_v8f(float* p, float4 lo, float4 hi) {
+  asm volatile("st.global.v8.f32 [%0], {%1, %2, %3, %4, %5, %6, %7, %8};" ::"l"(p), "f"(lo.x),
+               "f"(lo.y), "f"(lo.z), "f"(lo.w), "f"(hi.x), "f"(hi.y), "f"(hi.z), "f"(hi.w)
+               : "memory");
+}
+__device__ __forceinline__ void ld_global_v8f(const float* p, float* out) {
+  asm volatile("ld.global.v8.f32 {%0, %1, %2, %3, %4, %5, %6, %7}, [%8];"
+               : "=f"(out[0]), "=f"(out[1]), "=f"(out[2]), "=f"(out[3]), "=f"(out[4]), "=f"(out[5]),
+                 "=f"(out[6]), "=f"(out[7])
+               : "l"(p));
+}
+
+template <int ACT>
+__device__ __forceinline__ float act_f32(float v, float alpha) {
+  if (ACT == PLB_ACT_RELU) return fmaxf(v, 0.f);
+  if (ACT == PLB_ACT_RELU6) return fminf(fmaxf(v, 0.f), alpha);
+  if (ACT == PLB_ACT_LEAKY) return v <= 0.f ? alpha * v : v;
+  return v;
+}
+
+// Residual values of one 32-column chunk, fetched before the accumulator is read so that
+// the global-memory latency overlaps the wait for the tensor cores.
+__device__ __forceinline__ void load_residual32(const IgemmArgs& a, long row, int col, float (&res)[32]) {
   const int ncols = a.cout - col < 32 ? a.cout - col : 32;
-  if (ncols <= 0) return;
+  const float* src = a.residual + row * a.ldy + col;
+  if (ncols == 32 && (a.ldy & 7) == 0) {
+#pragma unroll
+    for (int j = 0; j < 4; ++j) ld_global_v8f(src + 8 * j, &res[8 * j]);
+  } else {
+#pragma unroll
+    for (int j = 0; j < 32; ++j) res[j] = j < ncols ? src[j] : 0.f;
+  }
+}
+
+template <int MODE, int ACT>
+__device__ __forceinline__ void epilogue_store32(const IgemmArgs& a, const uint32_t (&r)[32],
+                                                 const float (&res)[32], long row, int col) {
+  const int ncols = a.cout - col < 32 ? a.cout - col : 32;
   const bool full = ncols == 32;
-  if (a.out_mode == OUT_ACC) {
+  if (MODE == OUT_ACC) {
     int32_t* dst = static_cast<int32_t*>(a.y) + row * a.ldy + col;
     if (full && (a.ldy & 3) == 0) {
 #pragma unroll
@@ -194,84 +267,26 @@ __device__ __forceinline__ void epilogue_store32(const IgemmArgs& a, const uint3
     }
     return;
   }
-  float v[32];
-#pragma unroll
-  for (int j = 0; j < 32; j += 4) {
-    const float4 sc = *reinterpret_cast<const float4*>(s_scale + j);
-    const float4 bi = *reinterpret_cast<const float4*>(s_bias + j);
-    v[j] = fmaf(static_cast<float>(static_cast<int>(r[j])), sc.x, bi.x);
-    v[j + 1] = fmaf(static_cast<float>(static_cast<int>(r[j + 1])), sc.y, bi.y);
-    v[j + 2] = fmaf(static_cast<float>(static_cast<int>(r[j + 2])), sc.z, bi.z);
-    v[j + 3] = fmaf(static_cast<float>(static_cast<int>(r[j + 3])), sc.w, bi.w);
-  }
-  if (a.out_mode == OUT_ADD_RELU) {
-    if (a.residual != nullptr) {
-      const float* res = a.residual + row * a.ldy + col;
-      if (full && (a.ldy & 3) == 0) {
-#pragma unroll
-        for (int j = 0; j < 32; j += 4) {
-          const float4 t = *reinterpret_cast<const float4*>(res + j);
-          v[j] += t.x; v[j + 1] += t.y; v[j + 2] += t.z; v[j + 3] += t.w;
-        }
-      } else {
-#pragma unroll
-        for (int j = 0; j < 32; ++j)
-          if (j < ncols) v[j] += res[j];
-      }
-    }
-#pragma unroll
-    for (int j = 0; j < 32; ++j) v[j] = v[j] > 0.f ? v[j] : 0.f;
-    if (a.y_f32 != nullptr) {
-      float* dst = a.y_f32 + row * a.ldy + col;
-      if (full && (a.ldy & 3) == 0) {
-#pragma unroll
-        for (int j = 0; j < 32; j += 4)
-          *reinterpret_cast<float4*>(dst + j) = make_float4(v[j], v[j + 1], v[j + 2], v[j + 3]);
-      } else {
-#pragma unroll
-        for (int j = 0; j < 32; ++j)
-          if (j < ncols) dst[j] = v[j];
-      }
-    }
-    if (a.y_i8 != nullptr) {
-      int8_t* dst = a.y_i8 + row * a.ldy + col;
-      uint32_t q[8];
-#pragma unroll
-      for (int j = 0; j < 8; ++j)
-        q[j] = pack4(calib_i8(v[4 * j], a.inv_next_scale), calib_i8(v[4 * j + 1], a.inv_next_scale),
-                     calib_i8(v[4 * j + 2], a.inv_next_scale), calib_i8(v[4 * j + 3], a.inv_next_scale));
-      if (full && (a.ldy & 15) == 0) {
-        *reinterpret_cast<uint4*>(dst) = make_uint4(q[0], q[1], q[2], q[3]);
-        *reinterpret_cast<uint4*>(dst + 16) = make_uint4(q[4], q[5], q[6], q[7]);
-      } else {
-#pragma unroll
-        for (int j = 0; j < 32; ++j)
-          if (j < ncols) dst[j] = static_cast<int8_t>(q[j >> 2] >> (8 * (j & 3)));
-      }
-    }
-    return;
-  }
-#pragma unroll
-  for (int j = 0; j < 32; ++j) v[j] = act_apply(v[j], a.act, a.alpha);
-  if (a.out_mode == OUT_F32) {
-    float* dst = static_cast<float*>(a.y) + row * a.ldy + col;
-    if (full && (a.ldy & 3) == 0) {
-#pragma unroll
-      for (int j = 0; j < 32; j += 4)
-        *reinterpret_cast<float4*>(dst + j) = make_float4(v[j], v[j + 1], v[j + 2], v[j + 3]);
-    } else {
-#pragma unroll
-      for (int j = 0; j < 32; ++j)
-        if (j < ncols) dst[j] = v[j];
-    }
-  } else {  // OUT_I8
-    int8_t* dst = static_cast<int8_t*>(a.y) + row * a.ldy + col;
+  // per-channel scale and bias: every lane reads the same addresses (one broadcast request);
+  // the arrays are padded so that a ragged last tile may read past cout
+  const float4* sc4 = reinterpret_cast<const float4*>(a.scale + col);
+  const float4* bi4 = reinterpret_cast<const float4*>(a.bias + col);
+  if (MODE == OUT_I8) {
+    const float alpha = ACT == PLB_ACT_RELU6 ? fminf(a.alpha, 127.f) : a.alpha;
     uint32_t q[8];
 #pragma unroll
-    for (int j = 0; j < 8; ++j)
-      q[j] = pack4(requant_i8(v[4 * j]), requant_i8(v[4 * j + 1]), requant_i8(v[4 * j + 2]),
-                   requant_i8(v[4 * j + 3]));
-    if (full && (a.ldy & 15) == 0) {
+    for (int j = 0; j < 8; ++j) {
+      const float4 sc = __ldg(sc4 + j), bi = __ldg(bi4 + j);
+      q[j] = pack_low_bytes(
+          quant_byte<ACT>(fmaf(__int2float_rn((int)r[4 * j]), sc.x, bi.x), alpha),
+          quant_byte<ACT>(fmaf(__int2float_rn((int)r[4 * j + 1]), sc.y, bi.y), alpha),
+          quant_byte<ACT>(fmaf(__int2float_rn((int)r[4 * j + 2]), sc.z, bi.z), alpha),
+          quant_byte<ACT>(fmaf(__int2float_rn((int)r[4 * j + 3]), sc.w, bi.w), alpha));
+    }
+    int8_t* dst = static_cast<int8_t*>(a.y) + row * a.ldy + col;
+    if (full && (a.ldy & 31) == 0) {
+      st_global_v8(dst, q[0], q[1], q[2], q[3], q[4], q[5], q[6], q[7]);
+    } else if (full && (a.ldy & 15) == 0) {
       *reinterpret_cast<uint4*>(dst) = make_uint4(q[0], q[1], q[2], q[3]);
       *reinterpret_cast<uint4*>(dst + 16) = make_uint4(q[4], q[5], q[6], q[7]);
     } else if (full && (a.ldy & 3) == 0) {
@@ -282,15 +297,91 @@ __device__ __forceinline__ void epilogue_store32(const IgemmArgs& a, const uint3
       for (int j = 0; j < 32; ++j)
         if (j < ncols) dst[j] = static_cast<int8_t>(q[j >> 2] >> (8 * (j & 3)));
     }
+    return;
+  }
+  if (MODE == OUT_F32) {
+    float* dst = static_cast<float*>(a.y) + row * a.ldy + col;
+    const bool vec8 = full && (a.ldy & 7) == 0;
+    const bool vec4 = full && (a.ldy & 3) == 0;
+#pragma unroll
+    for (int j = 0; j < 8; j += 2) {
+      float4 v[2];
+#pragma unroll
+      for (int h = 0; h < 2; ++h) {
+        const float4 sc = __ldg(sc4 + j + h), bi = __ldg(bi4 + j + h);
+        v[h].x = act_f32<ACT>(fmaf(__int2float_rn((int)r[4 * (j + h)]), sc.x, bi.x), a.alpha);
+        v[h].y = act_f32<ACT>(fmaf(__int2float_rn((int)r[4 * (j + h) + 1]), sc.y, bi.y), a.alpha);
+        v[h].z = act_f32<ACT>(fmaf(__int2float_rn((int)r[4 * (j + h) + 2]), sc.z, bi.z), a.alpha);
+        v[h].w = act_f32<ACT>(fmaf(__int2float_rn((int)r[4 * (j + h) + 3]), sc.w, bi.w), a.alpha);
+      }
+      if (vec8) {
+        st_global_v8f(dst + 4 * j, v[0], v[1]);
+      } else if (vec4) {
+        *reinterpret_cast<float4*>(dst + 4 * j) = v[0];
+        *reinterpret_cast<float4*>(dst + 4 * j + 4) = v[1];
+      } else {
+        const float t[8] = {v[0].x, v[0].y, v[0].z, v[0].w, v[1].x, v[1].y, v[1].z, v[1].w};
+#pragma unroll
+        for (int e = 0; e < 8; ++e)
+          if (4 * j + e < ncols) dst[4 * j + e] = t[e];
+      }
+    }
+    return;
+  }
+  // OUT_ADD_RELU: fp32 value + residual, ReLU, optional fp32 store, optional calib to int8
+  {
+    const long off = row * a.ldy + col;
+    const bool vec8 = full && (a.ldy & 7) == 0;
+    uint32_t q[8];
+#pragma unroll
+    for (int j = 0; j < 8; j += 2) {
+      float4 v[2];
+#pragma unroll
+      for (int h = 0; h < 2; ++h) {
+        const float4 sc = __ldg(sc4 + j + h), bi = __ldg(bi4 + j + h);
+        const int b = 4 * (j + h);
+        v[h].x = fmaxf(fmaf(__int2float_rn((int)r[b]), sc.x, bi.x) + res[b], 0.f);
+        v[h].y = fmaxf(fmaf(__int2float_rn((int)r[b + 1]), sc.y, bi.y) + res[b + 1], 0.f);
+        v[h].z = fmaxf(fmaf(__int2float_rn((int)r[b + 2]), sc.z, bi.z) + res[b + 2], 0.f);
+        v[h].w = fmaxf(fmaf(__int2float_rn((int)r[b + 3]), sc.w, bi.w) + res[b + 3], 0.f);
+        // calib of the next layer: sat(rne(max(v * inv_scale, -127))); v >= 0 here
+        q[j + h] = pack_low_bytes(__float_as_uint(fminf(v[h].x * a.inv_next_scale, 127.f) + kRoundMagic),
+                                  __float_as_uint(fminf(v[h].y * a.inv_next_scale, 127.f) + kRoundMagic),
+                                  __float_as_uint(fminf(v[h].z * a.inv_next_scale, 127.f) + kRoundMagic),
+                                  __float_as_uint(fminf(v[h].w * a.inv_next_scale, 127.f) + kRoundMagic));
+      }
+      if (a.y_f32 != nullptr) {
+        float* dst = a.y_f32 + off + 4 * j;
+        if (vec8) {
+          st_global_v8f(dst, v[0], v[1]);
+        } else {
+          const float t[8] = {v[0].x, v[0].y, v[0].z, v[0].w, v[1].x, v[1].y, v[1].z, v[1].w};
+#pragma unroll
+          for (int e = 0; e < 8; ++e)
+            if (4 * j + e < ncols) dst[e] = t[e];
+        }
+      }
+    }
+    if (a.y_i8 != nullptr) {
+      int8_t* dst = a.y_i8 + off;
+      if (full && (a.ldy & 31) == 0) {
+        st_global_v8(dst, q[0], q[1], q[2], q[3], q[4], q[5], q[6], q[7]);
+      } else {
+#pragma unroll
+        for (int j = 0; j < 32; ++j)
+          if (j < ncols) dst[j] = static_cast<int8_t>(q[j >> 2] >> (8 * (j & 3)));
+      }
+    }
   }
 }
 
 // ---------------------------------------------------------------- the kernel
 // Persistent: one CTA per SM walks tiles t = blockIdx.x, blockIdx.x + gridDim.x, ...;
 // consecutive tile ids share the same 128 pixels (channel tile fastest) so that CTAs running
-// side by side hit the same activation rows in L2.  The operand ring and the two TMEM
-// accumulator buffers run across tile boundaries: the producer prefetches the next tile
-// while the epilogue warps drain the previous one.
+// side by side hit the same activation rows in L2.  The operand ring and the TMEM
+// accumulator buffers run across tile boundaries: the producer prefetches the next tiles
+// while the epilogue groups drain the previous ones.
+template <int MODE, int ACT>
 __global__ void __launch_bounds__(kThreads, 1)
     igemm_i8_tc_kernel(const __grid_constant__ CUtensorMap tmA,
                        const __grid_constant__ CUtensorMap tmB, const IgemmArgs a) {
@@ -304,29 +395,29 @@ __global__ void __launch_bounds__(kThreads, 1)
   uint8_t* ctrl = smem + a.stages * stage_bytes;
   uint64_t* full_bar = reinterpret_cast<uint64_t*>(ctrl);
   uint64_t* empty_bar = full_bar + kMaxStages;
-  uint64_t* acc_full = empty_bar + kMaxStages;   // [2] accumulator buffer ready for the epilogue
-  uint64_t* acc_empty = acc_full + 2;            // [2] accumulator buffer drained
-  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(acc_empty + 2);
+  uint64_t* acc_full = empty_bar + kMaxStages;     // [4] accumulator buffer ready for its epilogue group(s)
+  uint64_t* acc_empty = acc_full + kMaxAccBufs;    // [4] accumulator buffer drained
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(acc_empty + kMaxAccBufs);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
-  float* s_scale = reinterpret_cast<float*>(ctrl + 256);  // [2][256]
-  float* s_bias = s_scale + 512;                           // [2][256]
 
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
 
-  // TMEM: two accumulator buffers of acc_cols columns each
+  // TMEM: nb accumulator buffers of acc_cols columns each (512 columns in total at most)
   uint32_t acc_cols = 32;
   while (acc_cols < static_cast<uint32_t>(a.bn)) acc_cols <<= 1;
-  const uint32_t tmem_cols = acc_cols * 2;
+  const int nb = acc_cols <= 128 ? 4 : 2;
+  const int gpb = kEpilogueGroups / nb;  // epilogue groups sharing one buffer (split by columns)
+  const uint32_t tmem_cols = acc_cols * nb < 32 ? 32 : acc_cols * nb;
 
   if (threadIdx.x == kProducerWarp * 32) {
     for (int s = 0; s < a.stages; ++s) {
       mbar_init(smem_u32(&full_bar[s]), 1);
       mbar_init(smem_u32(&empty_bar[s]), 1);
     }
-    for (int b = 0; b < 2; ++b) {
+    for (int b = 0; b < nb; ++b) {
       mbar_init(smem_u32(&acc_full[b]), 1);
-      mbar_init(smem_u32(&acc_empty[b]), kEpilogueWarps);
+      mbar_init(smem_u32(&acc_empty[b]), 4 * gpb);
     }
     *abort_flag = 0;
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
@@ -396,8 +487,8 @@ __global__ void __launch_bounds__(kThreads, 1)
       int ks_global = 0, it = 0;
       bool ok = true;
       for (int tile = blockIdx.x; tile < a.num_tiles && ok; tile += gridDim.x, ++it) {
-        const int buf = it & 1;
-        ok = mbar_wait(smem_u32(&acc_empty[buf]), ((it >> 1) & 1) ^ 1, abort_flag, a.status,
+        const int buf = it % nb;
+        ok = mbar_wait(smem_u32(&acc_empty[buf]), ((it / nb) & 1) ^ 1, abort_flag, a.status,
                        FAULT_WAIT_ACCUM);
         if (!ok) break;
         tc_fence_after();
@@ -421,43 +512,51 @@ __global__ void __launch_bounds__(kThreads, 1)
       }
     }
   } else {
-    // ------------------------------------------------------------ epilogue warps 0..7
-    const int quad = warp & 3;   // TMEM lane quadrant this warp may read
-    const int half = warp >> 2;  // which 32-column chunks (even / odd) this warp takes
-    int it = 0;
+    // ------------------------------------------------------------ epilogue groups
+    const int group = warp >> 2;     // 0..3
+    const int quad = warp & 3;       // TMEM lane quadrant this warp may read
+    const int my_buf = group / gpb;  // the accumulator buffer this group drains
+    const int col_par = group % gpb; // which 32-column chunks of it
     bool ok = true;
-    for (int tile = blockIdx.x; tile < a.num_tiles && ok; tile += gridDim.x, ++it) {
-      const int buf = it & 1;
+    for (int it = my_buf; ok; it += nb) {
+      const long tile_l = static_cast<long>(blockIdx.x) + static_cast<long>(it) * gridDim.x;
+      if (tile_l >= a.num_tiles) break;
+      const int tile = static_cast<int>(tile_l);
       const int m0 = (tile / a.tiles_n) * kTileM;
       const int n0 = (tile % a.tiles_n) * a.bn;
-      float* sc = s_scale + buf * 256;
-      float* bi = s_bias + buf * 256;
-      if (a.out_mode != OUT_ACC) {
-        for (int i = threadIdx.x; i < 256; i += kEpilogueWarps * 32) {
-          const int c = n0 + i;
-          const bool in = i < a.bn && c < a.cout;
-          sc[i] = in ? a.scale[c] : 0.f;
-          bi[i] = in ? a.bias[c] : 0.f;
+      const long row = static_cast<long>(m0) + quad * 32 + lane;
+      const uint32_t lane_addr = tmem_base + my_buf * acc_cols + (static_cast<uint32_t>(quad * 32) << 16);
+      bool waited = false;
+      for (int c = col_par * 32; c < a.bn; c += 32 * gpb) {
+        if (n0 + c >= a.cout) break;  // warp-uniform
+        float res[32];
+        if (MODE == OUT_ADD_RELU) {
+          if (a.residual != nullptr && row < a.m_total) {
+            load_residual32(a, row, n0 + c, res);
+          } else {
+#pragma unroll
+            for (int j = 0; j < 32; ++j) res[j] = 0.f;
+          }
         }
+        if (!waited) {
+          ok = mbar_wait(smem_u32(&acc_full[my_buf]), (it / nb) & 1, abort_flag, a.status, FAULT_WAIT_ACCUM);
+          tc_fence_after();
+          waited = true;
+          if (!ok) break;
+        }
+        uint32_t r[32];
+        tc_ld32(lane_addr + static_cast<uint32_t>(c), r);
+        tc_wait_ld();
+        if (row < a.m_total) epilogue_store32<MODE, ACT>(a, r, res, row, n0 + c);
       }
-      asm volatile("bar.sync 1, 256;" ::: "memory");
-      ok = mbar_wait(smem_u32(&acc_full[buf]), (it >> 1) & 1, abort_flag, a.status, FAULT_WAIT_ACCUM);
-      tc_fence_after();
-      if (ok) {
-        const long row = static_cast<long>(m0) + quad * 32 + lane;
-        const uint32_t lane_addr = tmem_base + buf * acc_cols + (static_cast<uint32_t>(quad * 32) << 16);
-        for (int c = half * 32; c < a.bn; c += 64) {
-          if (n0 + c >= a.cout) break;  // warp-uniform
-          uint32_t r[32];
-          tc_ld32(lane_addr + static_cast<uint32_t>(c), r);
-          tc_wait_ld();
-          if (row < a.m_total) epilogue_store32(a, r, row, n0 + c, sc + c, bi + c);
-        }
+      if (!waited) {  // tile entirely outside the channel range for this group: still consume the phase
+        ok = mbar_wait(smem_u32(&acc_full[my_buf]), (it / nb) & 1, abort_flag, a.status, FAULT_WAIT_ACCUM);
+        tc_fence_after();
       }
       // this warp no longer reads the buffer: let the MMA warp overwrite it
       tc_fence_before();
       __syncwarp();
-      if (lane == 0) mbar_arrive(smem_u32(&acc_empty[buf]));
+      if (lane == 0) mbar_arrive(smem_u32(&acc_empty[my_buf]));
     }
   }
   tc_fence_before();
@@ -468,6 +567,27 @@ __global__ void __launch_bounds__(kThreads, 1)
     asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base),
                  "r"(tmem_cols)
                  : "memory");
+  }
+}
+
+typedef void (*IgemmKernel)(const CUtensorMap, const CUtensorMap, const IgemmArgs);
+
+template <int MODE>
+IgemmKernel pick_act(int act) {
+  switch (act) {
+    case PLB_ACT_RELU: return igemm_i8_tc_kernel<MODE, PLB_ACT_RELU>;
+    case PLB_ACT_RELU6: return igemm_i8_tc_kernel<MODE, PLB_ACT_RELU6>;
+    case PLB_ACT_LEAKY: return igemm_i8_tc_kernel<MODE, PLB_ACT_LEAKY>;
+    default: return igemm_i8_tc_kernel<MODE, PLB_ACT_NONE>;
+  }
+}
+
+IgemmKernel pick_kernel(int mode, int act) {
+  switch (mode) {
+    case OUT_F32: return pick_act<OUT_F32>(act);
+    case OUT_I8: return pick_act<OUT_I8>(act);
+    case OUT_ACC: return igemm_i8_tc_kernel<OUT_ACC, PLB_ACT_NONE>;
+    default: return igemm_i8_tc_kernel<OUT_ADD_RELU, PLB_ACT_NONE>;
   }
 }
 
@@ -622,18 +742,19 @@ int igemm_tc_launch(plb_ctx* ctx, const IgemmProblem& p) {
 
   const size_t smem = static_cast<size_t>(stages) * stage_bytes + kCtrlBytes + 1024;
   if (smem > 227 * 1024) return fail(PLB_E_UNSUPPORTED, "pipeline needs %zu bytes of shared memory", smem);
-  static size_t configured_smem[64] = {0};  // per device: the attribute belongs to the context
-  const int dev_slot = ctx->device & 63;
-  if (smem > configured_smem[dev_slot]) {
-    PLB_CUDA(cudaFuncSetAttribute(igemm_i8_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                  227 * 1024));
-    configured_smem[dev_slot] = 227 * 1024;
+  IgemmKernel kernel = pick_kernel(p.out_mode, p.epi.act);
+  // the attribute belongs to (function, device): remember which pairs have been configured
+  static std::vector<std::pair<const void*, int>> configured;
+  const std::pair<const void*, int> key(reinterpret_cast<const void*>(kernel), ctx->device);
+  if (std::find(configured.begin(), configured.end(), key) == configured.end()) {
+    PLB_CUDA(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024));
+    configured.push_back(key);
   }
   const long tiles = static_cast<long>(tiles_m) * a.tiles_n;
   if (tiles > 0x7fffffffL) return fail(PLB_E_UNSUPPORTED, "too many tiles");
   a.num_tiles = static_cast<int>(tiles);
   const unsigned grid = static_cast<unsigned>(tiles < ctx->sm_count ? tiles : ctx->sm_count);
-  igemm_i8_tc_kernel<<<grid, kThreads, smem, ctx->stream>>>(tmA, tmB, a);
+  kernel<<<grid, kThreads, smem, ctx->stream>>>(tmA, tmB, a);
   PLB_CUDA(cudaGetLastError());
   ctx->launches++;
   return PLB_OK;

@@ -247,6 +247,36 @@ __global__ void __launch_bounds__(kBlock)
   }
 }
 
+// Row-folded staging for stem layers with few input channels (cin * kw <= 32):
+// y[n][h][q][s*cin + c] = x[n][c][h][q*stride_w - pad_l + s*dil_w] (0 outside the image, 0 for
+// the unused tail of the 32-byte pixel).  The kw taps of one filter row then sit in the
+// channel dimension and the convolution becomes kh x 1 with 32 input channels.
+template <typename T>
+__global__ void __launch_bounds__(kBlock)
+    fold_rows_kernel(const T* __restrict__ x, int8_t* __restrict__ y, int c, int h, int w, int wo, int kw,
+                     int stride_w, int pad_l, int dil_w, float inv, long total) {
+  const long idx = static_cast<long>(blockIdx.x) * kBlock + threadIdx.x;
+  if (idx >= total) return;
+  const int q = static_cast<int>(idx % wo);
+  const int hh = static_cast<int>((idx / wo) % h);
+  const long n = idx / (static_cast<long>(wo) * h);
+  uint32_t words[8] = {0, 0, 0, 0, 0, 0, 0, 0};
+  const int w0 = q * stride_w - pad_l;
+  for (int s = 0; s < kw; ++s) {
+    const int iw = w0 + s * dil_w;
+    if (iw < 0 || iw >= w) continue;
+    for (int cc = 0; cc < c; ++cc) {
+      const T raw = x[((n * c + cc) * h + hh) * static_cast<long>(w) + iw];
+      const int v = sizeof(T) == 1 ? static_cast<int>(raw) : calib_i8(static_cast<float>(raw), inv);
+      const int j = s * c + cc;
+      words[j >> 2] |= static_cast<uint32_t>(v & 0xff) << (8 * (j & 3));
+    }
+  }
+  uint4* dst = reinterpret_cast<uint4*>(y + idx * 32);
+  dst[0] = make_uint4(words[0], words[1], words[2], words[3]);
+  dst[1] = make_uint4(words[4], words[5], words[6], words[7]);
+}
+
 // [n,hw,c] -> [n,c,hw], 32x32 element tiles.
 template <typename T>
 __global__ void nhwc_to_nchw_kernel(const T* __restrict__ x, T* __restrict__ y, int c, int hw) {
@@ -393,6 +423,22 @@ int calib_nchw_f32_to_nhwc_i8_launch(plb_ctx* ctx, const float* x, int8_t* y, in
   const int hw = h * w;
   dim3 grid((hw + 63) / 64, (cpad + 31) / 32, n);
   to_nhwc_i8_kernel<float><<<grid, kBlock, 0, ctx->stream>>>(x, y, c, hw, cpad, 1.f / scale);
+  PLB_CUDA(cudaGetLastError());
+  ctx->launches++;
+  return PLB_OK;
+}
+
+int fold_rows_launch(plb_ctx* ctx, const void* x, int x_is_f32, int8_t* y, int n, int c, int h, int w,
+                     int wo, int kw, int stride_w, int pad_l, int dil_w, float scale) {
+  const long total = static_cast<long>(n) * h * wo;
+  if (total == 0) return PLB_OK;
+  if (c * kw > 32) return fail(PLB_E_INVALID, "row folding needs cin * kw <= 32");
+  if (x_is_f32)
+    fold_rows_kernel<float><<<blocks_for(total), kBlock, 0, ctx->stream>>>(
+        static_cast<const float*>(x), y, c, h, w, wo, kw, stride_w, pad_l, dil_w, 1.f / scale, total);
+  else
+    fold_rows_kernel<int8_t><<<blocks_for(total), kBlock, 0, ctx->stream>>>(
+        static_cast<const int8_t*>(x), y, c, h, w, wo, kw, stride_w, pad_l, dil_w, 1.f, total);
   PLB_CUDA(cudaGetLastError());
   ctx->launches++;
   return PLB_OK;

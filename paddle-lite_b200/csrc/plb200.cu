@@ -104,6 +104,7 @@ struct plb_conv {
   plb_conv_desc d;
   int ho = 0, wo = 0;
   int kind = 0;        // 0 tensor core, 1 direct, 2 depthwise
+  bool fold = false;   // stem layer: the kw taps of a filter row are folded into the channels
   int cin_pad = 0;     // channel stride of the NHWC staging input
   int cg_pad = 0;      // filter row length per tap
   DeviceBuf w;         // repacked filter
@@ -231,6 +232,21 @@ int plb_conv_prepare(plb_ctx* ctx, const plb_conv_desc* desc, const int8_t* filt
     packed.assign(static_cast<size_t>(taps) * c->cg_pad, 0);  // [tap][channel]
     for (int ch = 0; ch < d.cout; ++ch)
       for (int t = 0; t < taps; ++t) packed[static_cast<size_t>(t) * c->cg_pad + ch] = filter_h[ch * taps + t];
+  } else if (d.groups == 1 && d.impl != PLB_IMPL_DIRECT && d.kw > 1 && d.cin * d.kw <= 32 &&
+             d.stride_w <= 8) {
+    // stem layer (e.g. RGB input): fold the kw taps of each filter row into the channel
+    // dimension, [cout][kh][s*cin + c], and run a kh x 1 convolution over staged rows
+    c->kind = 0;
+    c->fold = true;
+    c->cin_pad = 32;
+    c->cg_pad = 32;
+    packed.assign(static_cast<size_t>(d.cout) * d.kh * 32, 0);
+    for (int co = 0; co < d.cout; ++co)
+      for (int ci = 0; ci < d.cin; ++ci)
+        for (int r = 0; r < d.kh; ++r)
+          for (int sx = 0; sx < d.kw; ++sx)
+            packed[(static_cast<size_t>(co) * d.kh + r) * 32 + sx * d.cin + ci] =
+                filter_h[((static_cast<size_t>(co) * d.cin + ci) * d.kh + r) * d.kw + sx];
   } else if (d.groups == 1) {
     c->cin_pad = static_cast<int>(align_up(d.cin, 32));
     c->cg_pad = c->cin_pad;
@@ -254,7 +270,7 @@ int plb_conv_prepare(plb_ctx* ctx, const plb_conv_desc* desc, const int8_t* filt
           packed[(static_cast<size_t>(co) * taps + t) * cig + ci] =
               filter_h[(static_cast<size_t>(co) * cig + ci) * taps + t];
   }
-  if (c->kind == 0) {
+  if (c->kind == 0 && !c->fold) {
     // shape rules of the tensor-core kernel that do not depend on pointers
     IgemmProblem probe;
     memset(&probe, 0, sizeof(probe));
@@ -300,7 +316,8 @@ void plb_conv_destroy(plb_conv* conv) {
 
 size_t plb_conv_workspace_bytes(const plb_conv* conv, int batch) {
   if (!conv || batch <= 0) return 0;
-  const size_t x_bytes = align_up(static_cast<size_t>(batch) * conv->d.h * conv->d.w * conv->cin_pad, 256);
+  const size_t x_bytes = align_up(
+      static_cast<size_t>(batch) * conv->d.h * (conv->fold ? conv->wo : conv->d.w) * conv->cin_pad, 256);
   const size_t y_bytes = align_up(static_cast<size_t>(batch) * conv->ho * conv->wo * conv->d.cout * 4, 256);
   return x_bytes + y_bytes;
 }
@@ -324,6 +341,9 @@ int conv_core(plb_conv* c, const int8_t* x, int batch, const OutSpec& out) {
     p.kh = d.kh; p.kw = d.kw; p.stride_h = d.stride_h; p.stride_w = d.stride_w;
     p.pad_t = d.pad_top; p.pad_b = d.pad_bottom; p.pad_l = d.pad_left; p.pad_r = d.pad_right;
     p.dil_h = d.dil_h; p.dil_w = d.dil_w;
+    if (c->fold) {  // x is the row-folded staging tensor [batch, h, wo, 32]
+      p.w = c->wo; p.kw = 1; p.stride_w = 1; p.pad_l = 0; p.pad_r = 0; p.dil_w = 1;
+    }
     p.ho = c->ho; p.wo = c->wo;
     p.m_total = batch * c->ho * c->wo;
     p.b = c->w.as<int8_t>();
@@ -364,12 +384,18 @@ int conv_run_nchw(plb_conv* c, const int8_t* x, void* y, int batch, int mode) {
   plb_ctx* ctx = c->ctx;
   const plb_conv_desc& d = c->d;
   PLB_CUDA(cudaSetDevice(ctx->device));
-  const size_t x_bytes = align_up(static_cast<size_t>(batch) * d.h * d.w * c->cin_pad, 256);
+  const size_t x_bytes =
+      align_up(static_cast<size_t>(batch) * d.h * (c->fold ? c->wo : d.w) * c->cin_pad, 256);
   int rc = ctx->reserve(plb_conv_workspace_bytes(c, batch));
   if (rc) return rc;
   int8_t* xs = static_cast<int8_t*>(ctx->ws);
   void* ys = static_cast<uint8_t*>(ctx->ws) + x_bytes;
-  if ((rc = nchw_to_nhwc_i8_launch(ctx, x, xs, batch, d.cin, d.h, d.w, c->cin_pad))) return rc;
+  if (c->fold)
+    rc = fold_rows_launch(ctx, x, 0, xs, batch, d.cin, d.h, d.w, c->wo, d.kw, d.stride_w, d.pad_left,
+                          d.dil_w, 1.f);
+  else
+    rc = nchw_to_nhwc_i8_launch(ctx, x, xs, batch, d.cin, d.h, d.w, c->cin_pad);
+  if (rc) return rc;
   OutSpec o = out_spec(c, mode, ys);
   if ((rc = conv_core(c, xs, batch, o))) return rc;
   return nhwc_to_nchw_launch(ctx, ys, y, batch, d.cout, c->ho, c->wo, mode == OUT_I8 ? 1 : 4);
@@ -407,6 +433,29 @@ int plb_conv_run_nhwc(plb_conv* conv, const int8_t* x, void* y, int batch) {
   PLB_CUDA(cudaSetDevice(conv->ctx->device));
   OutSpec o = out_spec(conv, conv->d.out_dtype == PLB_OUT_I8 ? OUT_I8 : OUT_F32, y);
   return conv_core(conv, x, batch, o);
+}
+
+int plb_conv_run_image_f32(plb_conv* conv, const float* x, void* y, int batch) {
+  PLB_REQUIRE(conv != nullptr, "null argument");
+  PLB_REQUIRE(batch >= 0, "negative batch");
+  if (batch == 0) return PLB_OK;
+  PLB_REQUIRE(x && y, "null argument");
+  plb_ctx* ctx = conv->ctx;
+  const plb_conv_desc& d = conv->d;
+  PLB_CUDA(cudaSetDevice(ctx->device));
+  const size_t x_bytes =
+      align_up(static_cast<size_t>(batch) * d.h * (conv->fold ? conv->wo : d.w) * conv->cin_pad, 256);
+  int rc = ctx->reserve(x_bytes);
+  if (rc) return rc;
+  int8_t* xs = static_cast<int8_t*>(ctx->ws);
+  if (conv->fold)
+    rc = fold_rows_launch(ctx, x, 1, xs, batch, d.cin, d.h, d.w, conv->wo, d.kw, d.stride_w, d.pad_left,
+                          d.dil_w, d.in_scale);
+  else
+    rc = calib_nchw_f32_to_nhwc_i8_launch(ctx, x, xs, batch, d.cin, d.h, d.w, conv->cin_pad, d.in_scale);
+  if (rc) return rc;
+  OutSpec o = out_spec(conv, d.out_dtype == PLB_OUT_I8 ? OUT_I8 : OUT_F32, y);
+  return conv_core(conv, xs, batch, o);
 }
 
 int plb_conv_run_nhwc_add_relu(plb_conv* conv, const int8_t* x, const float* residual, float* y_f32,

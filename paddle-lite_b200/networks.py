@@ -177,7 +177,7 @@ class Runner:
         dev = "cuda:%d" % ctx.device
         c, h, w = spec["image"]
         self.hw = {"x": (h, w)}
-        self.buf = {"x": torch.empty((batch, h, w, 32), dtype=torch.int8, device=dev)}
+        self.buf = {}
         self.steps = []
         self.image_shape = (batch, c, h, w)
         for op in spec["ops"]:
@@ -186,8 +186,6 @@ class Runner:
                 L = qnet["layers"][op["name"]]
                 ih, iw = self.hw[op["src"]]
                 wq = L["wq"]
-                if op["src"] == "x":  # image is stored with 32 channels, the extra ones are zero
-                    wq = np.concatenate([wq, np.zeros((wq.shape[0], 32 - wq.shape[1]) + wq.shape[2:], np.int8)], 1)
                 in_s = float(scales[op["src"]])
                 if kind == "conv":
                     out_s = float(scales[op["dst"]]) if op["out"] == "i8" else None
@@ -197,7 +195,7 @@ class Runner:
                     dt = torch.int8 if out_s is not None else torch.float32
                     self.buf[op["dst"]] = torch.empty((batch, conv.ho, conv.wo, op["cout"]), dtype=dt, device=dev)
                     self.hw[op["dst"]] = (conv.ho, conv.wo)
-                    self.steps.append(("conv", conv, op["src"], op["dst"]))
+                    self.steps.append(("conv_image" if op["src"] == "x" else "conv", conv, op["src"], op["dst"]))
                 else:
                     conv = plb.Conv(ctx, wq, L["ws"], in_s, L["bias"], in_hw=(ih, iw))
                     shape = (batch, conv.ho, conv.wo, op["cout"])
@@ -234,13 +232,16 @@ class Runner:
         return self.forward_body()
 
     def forward_head(self, image_f32_nchw):
-        """calib + layout staging of the fp32 image (the only reader of the input tensor)."""
-        self.ctx.calib_nchw_f32_to_nhwc_i8(image_f32_nchw, 32, self.in_scale, out=self.buf["x"])
+        """First layer: calib + staging of the fp32 image and the stem convolution (the only
+        reader of the input tensor)."""
+        st = self.steps[0]
+        assert st[0] == "conv_image"
+        st[1].run_image_f32(image_f32_nchw, out=self.buf[st[3]])
 
     def forward_body(self):
-        """Everything after the image has been quantised; touches only preallocated buffers."""
+        """Everything after the first layer; touches only preallocated buffers."""
         b, ctx = self.buf, self.ctx
-        for st in self.steps:
+        for st in self.steps[1:]:
             if st[0] == "conv":
                 st[1].run_nhwc(b[st[2]], out=b[st[3]])
             elif st[0] == "conv_add_relu":
