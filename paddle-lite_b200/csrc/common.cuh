@@ -64,6 +64,34 @@ struct EpiParams {
 #ifdef __CUDACC__
 namespace plb {
 
+// Programmatic dependent launch: every kernel of the library is launched with the
+// programmatic-stream-serialization attribute, so its blocks may start while the previous
+// kernel on the stream is still draining.  A kernel therefore (1) lets its own dependents
+// start early and (2) waits for the previous grid to finish and flush before it touches
+// global memory.  Both instructions are no-ops for a kernel launched without the attribute.
+__device__ __forceinline__ void pdl_sync_with_previous_kernel() {
+  asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+  asm volatile("griddepcontrol.wait;" ::: "memory");
+}
+
+bool pdl_enabled();  // PLB_PDL=0 in the environment turns the launch attribute off
+
+template <typename... KArgs, typename... Args>
+cudaError_t launch_kernel(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem,
+                          cudaStream_t stream, Args... args) {
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = grid;
+  cfg.blockDim = block;
+  cfg.dynamicSmemBytes = smem;
+  cfg.stream = stream;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[0].val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = pdl_enabled() ? 1 : 0;
+  return cudaLaunchKernelEx(&cfg, kernel, KArgs(args)...);
+}
+
 __device__ __forceinline__ float act_apply(float v, int act, float alpha) {
   // gemm_fuse_relu_bias of the reference (gemm_s8u8_kernel.cc:31-55)
   if (act == PLB_ACT_RELU) return v > 0.f ? v : 0.f;

@@ -37,7 +37,7 @@ constexpr int kProducerWarp = kEpilogueWarps;
 constexpr int kMmaWarp = kEpilogueWarps + 1;
 constexpr int kThreads = 32 * (kEpilogueWarps + 2);
 constexpr int kMaxAccBufs = 4;
-constexpr int kCtrlBytes = 256;                 // barriers + tmem slot
+constexpr int kCtrlBytes = 512;                 // barriers + tmem slot
 constexpr uint32_t kWaitLimit = 1u << 22;      // polls before a wait is declared lost
 
 struct IgemmArgs {
@@ -47,6 +47,7 @@ struct IgemmArgs {
   int taps, kw;
   int ho, wo, stride_h, stride_w, pad_t, pad_l, dil_h, dil_w;
   int tiles_n, num_tiles;
+  int staging_bytes, staging_w_bytes;  // epilogue staging in front of the operand ring
   int out_mode, ldy;
   void* y;
   const float* scale;
@@ -375,19 +376,124 @@ __device__ __forceinline__ void epilogue_store32(const IgemmArgs& a, const uint3
   }
 }
 
+// ---------------------------------------------------------------- epilogue through shared memory
+// With one lane per output row every global access of a warp touches 32 different lines, which
+// makes the load/store unit (32 wavefronts per instruction) the limit of the fp32 epilogues.
+// When the output geometry allows it the epilogue therefore moves its global traffic with
+// TMA: the fp32 residual tile of a chunk is fetched by cp.async.bulk.tensor into a 128-byte
+// swizzled staging tile, results are written to staging tiles and leave with TMA stores
+// (bulk async-group), which also clip ragged rows at the end of the tensor.
+__device__ __forceinline__ void tma_store_2d(const CUtensorMap* map, uint32_t src, int c0, int c1) {
+  asm volatile("cp.async.bulk.tensor.2d.global.shared::cta.bulk_group [%0, {%2, %3}], [%1];" ::"l"(
+                   reinterpret_cast<uint64_t>(map)),
+               "r"(src), "r"(c0), "r"(c1)
+               : "memory");
+}
+__device__ __forceinline__ void bulk_commit() {
+  asm volatile("cp.async.bulk.commit_group;" ::: "memory");
+}
+__device__ __forceinline__ void bulk_wait_read_all() {
+  asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory");
+}
+__device__ __forceinline__ void bulk_wait_all() {
+  asm volatile("cp.async.bulk.wait_group 0;" ::: "memory");
+}
+__device__ __forceinline__ void fence_proxy_async_smem() {
+  asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+}
+__device__ __forceinline__ float4 lds128f(uint32_t addr) {
+  float4 v;
+  asm volatile("ld.shared.v4.f32 {%0, %1, %2, %3}, [%4];" : "=f"(v.x), "=f"(v.y), "=f"(v.z), "=f"(v.w) : "r"(addr));
+  return v;
+}
+__device__ __forceinline__ void sts128(uint32_t addr, uint32_t a, uint32_t b, uint32_t c, uint32_t d) {
+  asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(addr), "r"(a), "r"(b), "r"(c), "r"(d) : "memory");
+}
+
+// One 32-column chunk of one row, staged.  st_w: this warp's 32 x 128-byte fp32 tile (128-byte
+// swizzle: 16-byte chunk j of row r lives at chunk j ^ (r & 7)), holding the residual on entry
+// for OUT_ADD_RELU and the fp32 / int32 result on exit.  st_b_row: address of this lane's row in
+// the int8 staging tile, byte_chunk0 the index of the first 16-byte chunk to write and
+// b_swz_mask the xor mask of that tile's swizzle (7 for 128-byte rows, 0 otherwise).
+template <int MODE, int ACT>
+__device__ __forceinline__ void epilogue_chunk_staged(const IgemmArgs& a, const uint32_t (&r)[32], int lane,
+                                                      int col, uint32_t st_w, uint32_t st_b_row,
+                                                      int byte_chunk0, int b_swz_mask, bool have_res) {
+  const uint32_t w_row = st_w + lane * 128;
+  const int sw = lane & 7;
+  if (MODE == OUT_ACC) {
+#pragma unroll
+    for (int j = 0; j < 8; ++j) sts128(w_row + ((j ^ sw) << 4), r[4 * j], r[4 * j + 1], r[4 * j + 2], r[4 * j + 3]);
+    return;
+  }
+  const float4* sc4 = reinterpret_cast<const float4*>(a.scale + col);
+  const float4* bi4 = reinterpret_cast<const float4*>(a.bias + col);
+  if (MODE == OUT_F32) {
+#pragma unroll
+    for (int j = 0; j < 8; ++j) {
+      const float4 sc = __ldg(sc4 + j), bi = __ldg(bi4 + j);
+      const float x = act_f32<ACT>(fmaf(__int2float_rn((int)r[4 * j]), sc.x, bi.x), a.alpha);
+      const float y = act_f32<ACT>(fmaf(__int2float_rn((int)r[4 * j + 1]), sc.y, bi.y), a.alpha);
+      const float z = act_f32<ACT>(fmaf(__int2float_rn((int)r[4 * j + 2]), sc.z, bi.z), a.alpha);
+      const float w = act_f32<ACT>(fmaf(__int2float_rn((int)r[4 * j + 3]), sc.w, bi.w), a.alpha);
+      sts128(w_row + ((j ^ sw) << 4), __float_as_uint(x), __float_as_uint(y), __float_as_uint(z), __float_as_uint(w));
+    }
+    return;
+  }
+  uint32_t q[8];
+  if (MODE == OUT_I8) {
+    const float alpha = ACT == PLB_ACT_RELU6 ? fminf(a.alpha, 127.f) : a.alpha;
+#pragma unroll
+    for (int j = 0; j < 8; ++j) {
+      const float4 sc = __ldg(sc4 + j), bi = __ldg(bi4 + j);
+      q[j] = pack_low_bytes(
+          quant_byte<ACT>(fmaf(__int2float_rn((int)r[4 * j]), sc.x, bi.x), alpha),
+          quant_byte<ACT>(fmaf(__int2float_rn((int)r[4 * j + 1]), sc.y, bi.y), alpha),
+          quant_byte<ACT>(fmaf(__int2float_rn((int)r[4 * j + 2]), sc.z, bi.z), alpha),
+          quant_byte<ACT>(fmaf(__int2float_rn((int)r[4 * j + 3]), sc.w, bi.w), alpha));
+    }
+  } else {  // OUT_ADD_RELU
+#pragma unroll
+    for (int j = 0; j < 8; ++j) {
+      const float4 sc = __ldg(sc4 + j), bi = __ldg(bi4 + j);
+      const uint32_t addr = w_row + ((j ^ sw) << 4);
+      float4 t = make_float4(0.f, 0.f, 0.f, 0.f);
+      if (have_res) t = lds128f(addr);
+      const float x = fmaxf(fmaf(__int2float_rn((int)r[4 * j]), sc.x, bi.x) + t.x, 0.f);
+      const float y = fmaxf(fmaf(__int2float_rn((int)r[4 * j + 1]), sc.y, bi.y) + t.y, 0.f);
+      const float z = fmaxf(fmaf(__int2float_rn((int)r[4 * j + 2]), sc.z, bi.z) + t.z, 0.f);
+      const float w = fmaxf(fmaf(__int2float_rn((int)r[4 * j + 3]), sc.w, bi.w) + t.w, 0.f);
+      if (a.y_f32 != nullptr)
+        sts128(addr, __float_as_uint(x), __float_as_uint(y), __float_as_uint(z), __float_as_uint(w));
+      q[j] = pack_low_bytes(__float_as_uint(fminf(x * a.inv_next_scale, 127.f) + kRoundMagic),
+                            __float_as_uint(fminf(y * a.inv_next_scale, 127.f) + kRoundMagic),
+                            __float_as_uint(fminf(z * a.inv_next_scale, 127.f) + kRoundMagic),
+                            __float_as_uint(fminf(w * a.inv_next_scale, 127.f) + kRoundMagic));
+    }
+    if (a.y_i8 == nullptr) return;
+  }
+  sts128(st_b_row + (((byte_chunk0) ^ b_swz_mask) << 4), q[0], q[1], q[2], q[3]);
+  sts128(st_b_row + (((byte_chunk0 + 1) ^ b_swz_mask) << 4), q[4], q[5], q[6], q[7]);
+}
+
 // ---------------------------------------------------------------- the kernel
 // Persistent: one CTA per SM walks tiles t = blockIdx.x, blockIdx.x + gridDim.x, ...;
 // consecutive tile ids share the same 128 pixels (channel tile fastest) so that CTAs running
 // side by side hit the same activation rows in L2.  The operand ring and the TMEM
 // accumulator buffers run across tile boundaries: the producer prefetches the next tiles
 // while the epilogue groups drain the previous ones.
-template <int MODE, int ACT>
+template <int MODE, int ACT, bool STAGED>
 __global__ void __launch_bounds__(kThreads, 1)
     igemm_i8_tc_kernel(const __grid_constant__ CUtensorMap tmA,
-                       const __grid_constant__ CUtensorMap tmB, const IgemmArgs a) {
+                       const __grid_constant__ CUtensorMap tmB,
+                       const __grid_constant__ CUtensorMap tmRes,
+                       const __grid_constant__ CUtensorMap tmOutW,
+                       const __grid_constant__ CUtensorMap tmOutB, const IgemmArgs a) {
   extern __shared__ uint8_t smem_raw[];
   const uint32_t raw_addr = smem_u32(smem_raw);
-  uint8_t* smem = smem_raw + (((raw_addr + 1023u) & ~1023u) - raw_addr);
+  uint8_t* smem_al = smem_raw + (((raw_addr + 1023u) & ~1023u) - raw_addr);
+  // [epilogue staging: wide tiles, byte tiles][operand ring][barriers]
+  uint8_t* smem = smem_al + a.staging_bytes;
 
   const int stage_a = kTileM * a.kc;
   const int stage_b = a.bn * a.kc;
@@ -397,7 +503,8 @@ __global__ void __launch_bounds__(kThreads, 1)
   uint64_t* empty_bar = full_bar + kMaxStages;
   uint64_t* acc_full = empty_bar + kMaxStages;     // [4] accumulator buffer ready for its epilogue group(s)
   uint64_t* acc_empty = acc_full + kMaxAccBufs;    // [4] accumulator buffer drained
-  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(acc_empty + kMaxAccBufs);
+  uint64_t* res_bar = acc_empty + kMaxAccBufs;     // [16] one per epilogue warp: residual tile landed
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(res_bar + kEpilogueWarps);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
 
   const int warp = threadIdx.x >> 5;
@@ -419,6 +526,7 @@ __global__ void __launch_bounds__(kThreads, 1)
       mbar_init(smem_u32(&acc_full[b]), 1);
       mbar_init(smem_u32(&acc_empty[b]), 4 * gpb);
     }
+    for (int w = 0; w < kEpilogueWarps; ++w) mbar_init(smem_u32(&res_bar[w]), 1);
     *abort_flag = 0;
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     asm volatile("prefetch.tensormap [%0];" ::"l"(reinterpret_cast<uint64_t>(&tmA)) : "memory");
@@ -435,6 +543,8 @@ __global__ void __launch_bounds__(kThreads, 1)
   __syncthreads();
   tc_fence_after();
   const uint32_t tmem_base = *tmem_slot;
+  // the set-up above overlapped the previous kernel's tail; from here on global memory is touched
+  pdl_sync_with_previous_kernel();
 
   if (warp == kProducerWarp) {
     // ------------------------------------------------------------ TMA producer
@@ -516,7 +626,15 @@ __global__ void __launch_bounds__(kThreads, 1)
     const int group = warp >> 2;     // 0..3
     const int quad = warp & 3;       // TMEM lane quadrant this warp may read
     const int my_buf = group / gpb;  // the accumulator buffer this group drains
-    const int col_par = group % gpb; // which 32-column chunks of it
+    const int col_par = group % gpb; // which part of its columns
+    // staged I/O: this warp's staging tiles and bookkeeping
+    const uint32_t st_w = smem_u32(smem_al) + warp * 4096;
+    const int wq = a.bn / gpb;       // columns (= int8 bytes per row) this group owns in a tile
+    const uint32_t st_b = smem_u32(smem_al) + a.staging_w_bytes + warp * 4096;
+    const int b_swz = wq == 128 ? (lane & 7) : 0;
+    const uint32_t my_res_bar = smem_u32(&res_bar[warp]);
+    uint32_t res_phase = 0;
+    bool stores_pending = false;
     bool ok = true;
     for (int it = my_buf; ok; it += nb) {
       const long tile_l = static_cast<long>(blockIdx.x) + static_cast<long>(it) * gridDim.x;
@@ -527,29 +645,85 @@ __global__ void __launch_bounds__(kThreads, 1)
       const long row = static_cast<long>(m0) + quad * 32 + lane;
       const uint32_t lane_addr = tmem_base + my_buf * acc_cols + (static_cast<uint32_t>(quad * 32) << 16);
       bool waited = false;
-      for (int c = col_par * 32; c < a.bn; c += 32 * gpb) {
-        if (n0 + c >= a.cout) break;  // warp-uniform
-        float res[32];
-        if (MODE == OUT_ADD_RELU) {
-          if (a.residual != nullptr && row < a.m_total) {
-            load_residual32(a, row, n0 + c, res);
-          } else {
-#pragma unroll
-            for (int j = 0; j < 32; ++j) res[j] = 0.f;
+      if (STAGED) {
+        const int row0 = m0 + quad * 32;
+        const bool active = row0 < a.m_total;  // warp-uniform: some row of this quadrant exists
+        const bool use_w = MODE == OUT_F32 || MODE == OUT_ACC || (MODE == OUT_ADD_RELU && a.y_f32 != nullptr);
+        const bool have_res = MODE == OUT_ADD_RELU && a.residual != nullptr;
+        const bool use_b = MODE == OUT_I8 || (MODE == OUT_ADD_RELU && a.y_i8 != nullptr);
+        const int cbase = col_par * wq;
+        bool wrote_b = false;
+        for (int c = cbase; c < cbase + wq; c += 32) {
+          if (n0 + c >= a.cout) break;  // warp-uniform
+          if (active && stores_pending && (use_w || have_res || c == cbase)) {
+            // the staging tiles are about to be overwritten: earlier stores must have read them
+            if (lane == 0) bulk_wait_read_all();
+            __syncwarp();
+            stores_pending = false;
+          }
+          if (active && have_res && lane == 0) {
+            mbar_expect_tx(my_res_bar, 4096);
+            tma_load_2d(st_w, &tmRes, my_res_bar, n0 + c, row0);
+          }
+          if (!waited) {
+            ok = mbar_wait(smem_u32(&acc_full[my_buf]), (it / nb) & 1, abort_flag, a.status, FAULT_WAIT_ACCUM);
+            tc_fence_after();
+            waited = true;
+            if (!ok) break;
+          }
+          uint32_t r[32];
+          tc_ld32(lane_addr + static_cast<uint32_t>(c), r);
+          tc_wait_ld();
+          if (active) {
+            if (have_res) {
+              ok = mbar_wait(my_res_bar, res_phase, abort_flag, a.status, FAULT_WAIT_FULL);
+              res_phase ^= 1;
+              if (!ok) break;
+            }
+            epilogue_chunk_staged<MODE, ACT>(a, r, lane, n0 + c, st_w, st_b + lane * wq, (c - cbase) >> 4, b_swz,
+                                             have_res);
+            fence_proxy_async_smem();
+            __syncwarp();
+            if (use_w && lane == 0) {
+              tma_store_2d(&tmOutW, st_w, n0 + c, row0);
+              bulk_commit();
+            }
+            if (use_w) stores_pending = true;
+            wrote_b = use_b;
           }
         }
-        if (!waited) {
-          ok = mbar_wait(smem_u32(&acc_full[my_buf]), (it / nb) & 1, abort_flag, a.status, FAULT_WAIT_ACCUM);
-          tc_fence_after();
-          waited = true;
-          if (!ok) break;
+        if (wrote_b) {
+          if (lane == 0) {
+            tma_store_2d(&tmOutB, st_b, n0 + cbase, row0);
+            bulk_commit();
+          }
+          stores_pending = true;
         }
-        uint32_t r[32];
-        tc_ld32(lane_addr + static_cast<uint32_t>(c), r);
-        tc_wait_ld();
-        if (row < a.m_total) epilogue_store32<MODE, ACT>(a, r, res, row, n0 + c);
+      } else {
+        for (int c = col_par * 32; c < a.bn; c += 32 * gpb) {
+          if (n0 + c >= a.cout) break;  // warp-uniform
+          float res[32];
+          if (MODE == OUT_ADD_RELU) {
+            if (a.residual != nullptr && row < a.m_total) {
+              load_residual32(a, row, n0 + c, res);
+            } else {
+#pragma unroll
+              for (int j = 0; j < 32; ++j) res[j] = 0.f;
+            }
+          }
+          if (!waited) {
+            ok = mbar_wait(smem_u32(&acc_full[my_buf]), (it / nb) & 1, abort_flag, a.status, FAULT_WAIT_ACCUM);
+            tc_fence_after();
+            waited = true;
+            if (!ok) break;
+          }
+          uint32_t r[32];
+          tc_ld32(lane_addr + static_cast<uint32_t>(c), r);
+          tc_wait_ld();
+          if (row < a.m_total) epilogue_store32<MODE, ACT>(a, r, res, row, n0 + c);
+        }
       }
-      if (!waited) {  // tile entirely outside the channel range for this group: still consume the phase
+      if (!waited && ok) {  // nothing to do for this group in this tile: still consume the phase
         ok = mbar_wait(smem_u32(&acc_full[my_buf]), (it / nb) & 1, abort_flag, a.status, FAULT_WAIT_ACCUM);
         tc_fence_after();
       }
@@ -558,6 +732,7 @@ __global__ void __launch_bounds__(kThreads, 1)
       __syncwarp();
       if (lane == 0) mbar_arrive(smem_u32(&acc_empty[my_buf]));
     }
+    if (STAGED && lane == 0) bulk_wait_all();  // staging memory must outlive the stores reading it
   }
   tc_fence_before();
   __syncthreads();
@@ -570,25 +745,31 @@ __global__ void __launch_bounds__(kThreads, 1)
   }
 }
 
-typedef void (*IgemmKernel)(const CUtensorMap, const CUtensorMap, const IgemmArgs);
+typedef void (*IgemmKernel)(const CUtensorMap, const CUtensorMap, const CUtensorMap, const CUtensorMap,
+                            const CUtensorMap, const IgemmArgs);
 
-template <int MODE>
+template <int MODE, bool STAGED>
 IgemmKernel pick_act(int act) {
   switch (act) {
-    case PLB_ACT_RELU: return igemm_i8_tc_kernel<MODE, PLB_ACT_RELU>;
-    case PLB_ACT_RELU6: return igemm_i8_tc_kernel<MODE, PLB_ACT_RELU6>;
-    case PLB_ACT_LEAKY: return igemm_i8_tc_kernel<MODE, PLB_ACT_LEAKY>;
-    default: return igemm_i8_tc_kernel<MODE, PLB_ACT_NONE>;
+    case PLB_ACT_RELU: return igemm_i8_tc_kernel<MODE, PLB_ACT_RELU, STAGED>;
+    case PLB_ACT_RELU6: return igemm_i8_tc_kernel<MODE, PLB_ACT_RELU6, STAGED>;
+    case PLB_ACT_LEAKY: return igemm_i8_tc_kernel<MODE, PLB_ACT_LEAKY, STAGED>;
+    default: return igemm_i8_tc_kernel<MODE, PLB_ACT_NONE, STAGED>;
   }
 }
 
-IgemmKernel pick_kernel(int mode, int act) {
+template <bool STAGED>
+IgemmKernel pick_mode(int mode, int act) {
   switch (mode) {
-    case OUT_F32: return pick_act<OUT_F32>(act);
-    case OUT_I8: return pick_act<OUT_I8>(act);
-    case OUT_ACC: return igemm_i8_tc_kernel<OUT_ACC, PLB_ACT_NONE>;
-    default: return igemm_i8_tc_kernel<OUT_ADD_RELU, PLB_ACT_NONE>;
+    case OUT_F32: return pick_act<OUT_F32, STAGED>(act);
+    case OUT_I8: return pick_act<OUT_I8, STAGED>(act);
+    case OUT_ACC: return igemm_i8_tc_kernel<OUT_ACC, PLB_ACT_NONE, STAGED>;
+    default: return igemm_i8_tc_kernel<OUT_ADD_RELU, PLB_ACT_NONE, STAGED>;
   }
+}
+
+IgemmKernel pick_kernel(int mode, int act, bool staged) {
+  return staged ? pick_mode<true>(mode, act) : pick_mode<false>(mode, act);
 }
 
 // ---------------------------------------------------------------- host side
@@ -682,8 +863,23 @@ int igemm_tc_launch(plb_ctx* ctx, const IgemmProblem& p) {
   a.bn = bn;
   a.tiles_n = (p.cout + bn - 1) / bn;
   const int stage_bytes = (kTileM + bn) * a.kc;
-  // one CTA per SM: spend (almost) all shared memory on the operand ring
-  int stages = (200 * 1024) / stage_bytes;
+  // Staged (TMA) epilogue I/O needs power-of-two channel tiles, 16-byte aligned rows and bases.
+  const bool want_w = p.out_mode == OUT_F32 || p.out_mode == OUT_ACC ||
+                      (p.out_mode == OUT_ADD_RELU && (p.y_f32 != nullptr || p.residual != nullptr));
+  const bool want_b = p.out_mode == OUT_I8 || (p.out_mode == OUT_ADD_RELU && p.y_i8 != nullptr);
+  auto aligned16 = [](const void* q) { return (reinterpret_cast<uintptr_t>(q) & 15) == 0; };
+  bool staged = env_int("PLB_TC_STAGED", 1) != 0 && (bn == 32 || bn == 64 || bn == 128 || bn == 256);
+  if (want_w && (p.ldy % 4 != 0)) staged = false;
+  if (want_b && (p.ldy % 16 != 0)) staged = false;
+  if (p.out_mode == OUT_ADD_RELU) {
+    if (!aligned16(p.residual) || !aligned16(p.y_f32) || !aligned16(p.y_i8)) staged = false;
+  } else if (!aligned16(p.y)) {
+    staged = false;
+  }
+  a.staging_w_bytes = staged && want_w ? kEpilogueWarps * 4096 : 0;
+  a.staging_bytes = a.staging_w_bytes + (staged && want_b ? kEpilogueWarps * 4096 : 0);
+  // one CTA per SM: spend (almost) all remaining shared memory on the operand ring
+  int stages = (224 * 1024 - a.staging_bytes - kCtrlBytes) / stage_bytes;
   stages = env_int("PLB_TC_STAGES", stages);
   if (stages > kMaxStages) stages = kMaxStages;
   if (stages < 2) stages = 2;
@@ -740,9 +936,40 @@ int igemm_tc_launch(plb_ctx* ctx, const IgemmProblem& p) {
     if (r != CUDA_SUCCESS) return fail(PLB_E_CUDA, "cuTensorMapEncodeIm2col failed: %d", (int)r);
   }
 
-  const size_t smem = static_cast<size_t>(stages) * stage_bytes + kCtrlBytes + 1024;
+  // output-side tensor maps: [m_total, ldy] matrices, 32-row boxes
+  alignas(64) CUtensorMap tmRes = tmB, tmOutW = tmB, tmOutB = tmB;  // unused ones stay valid copies
+  if (staged) {
+    auto encode_out = [&](CUtensorMap* tm, const void* base, int elem_bytes, int box_cols,
+                          CUtensorMapSwizzle swz) -> CUresult {
+      cuuint64_t dims[2] = {static_cast<cuuint64_t>(p.cout), static_cast<cuuint64_t>(p.m_total)};
+      cuuint64_t strides[1] = {static_cast<cuuint64_t>(p.ldy) * elem_bytes};
+      cuuint32_t box[2] = {static_cast<cuuint32_t>(box_cols), 32};
+      cuuint32_t estr[2] = {1, 1};
+      return g_encode_tiled(tm, elem_bytes == 1 ? CU_TENSOR_MAP_DATA_TYPE_UINT8 : CU_TENSOR_MAP_DATA_TYPE_UINT32,
+                            2, const_cast<void*>(base), dims, strides, box, estr,
+                            CU_TENSOR_MAP_INTERLEAVE_NONE, swz, CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
+                            CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    };
+    CUresult r = CUDA_SUCCESS;
+    const int acc_cols = bn <= 32 ? 32 : (bn <= 64 ? 64 : (bn <= 128 ? 128 : 256));
+    const int wq = bn / (acc_cols <= 128 ? 1 : 2);  // int8 bytes per staged row
+    if (p.out_mode == OUT_ADD_RELU) {
+      if (p.residual) r = encode_out(&tmRes, p.residual, 4, 32, CU_TENSOR_MAP_SWIZZLE_128B);
+      if (r == CUDA_SUCCESS && p.y_f32) r = encode_out(&tmOutW, p.y_f32, 4, 32, CU_TENSOR_MAP_SWIZZLE_128B);
+      if (r == CUDA_SUCCESS && p.y_i8)
+        r = encode_out(&tmOutB, p.y_i8, 1, wq, wq == 128 ? CU_TENSOR_MAP_SWIZZLE_128B : CU_TENSOR_MAP_SWIZZLE_NONE);
+    } else if (p.out_mode == OUT_I8) {
+      r = encode_out(&tmOutB, p.y, 1, wq, wq == 128 ? CU_TENSOR_MAP_SWIZZLE_128B : CU_TENSOR_MAP_SWIZZLE_NONE);
+    } else {
+      r = encode_out(&tmOutW, p.y, 4, 32, CU_TENSOR_MAP_SWIZZLE_128B);
+    }
+    if (r != CUDA_SUCCESS) return fail(PLB_E_CUDA, "cuTensorMapEncodeTiled(output) failed: %d", (int)r);
+  }
+
+  const size_t smem = static_cast<size_t>(a.staging_bytes) + static_cast<size_t>(stages) * stage_bytes +
+                      kCtrlBytes + 1024;
   if (smem > 227 * 1024) return fail(PLB_E_UNSUPPORTED, "pipeline needs %zu bytes of shared memory", smem);
-  IgemmKernel kernel = pick_kernel(p.out_mode, p.epi.act);
+  IgemmKernel kernel = pick_kernel(p.out_mode, p.epi.act, staged);
   // the attribute belongs to (function, device): remember which pairs have been configured
   static std::vector<std::pair<const void*, int>> configured;
   const std::pair<const void*, int> key(reinterpret_cast<const void*>(kernel), ctx->device);
@@ -754,8 +981,8 @@ int igemm_tc_launch(plb_ctx* ctx, const IgemmProblem& p) {
   if (tiles > 0x7fffffffL) return fail(PLB_E_UNSUPPORTED, "too many tiles");
   a.num_tiles = static_cast<int>(tiles);
   const unsigned grid = static_cast<unsigned>(tiles < ctx->sm_count ? tiles : ctx->sm_count);
-  kernel<<<grid, kThreads, smem, ctx->stream>>>(tmA, tmB, a);
-  PLB_CUDA(cudaGetLastError());
+  PLB_CUDA(launch_kernel(kernel, dim3(grid), dim3(kThreads), smem, ctx->stream, tmA, tmB, tmRes, tmOutW,
+                         tmOutB, a));
   ctx->launches++;
   return PLB_OK;
 }

@@ -59,6 +59,7 @@ __device__ __forceinline__ void emit(const OutDev& o, long row, int col, int acc
 __global__ void __launch_bounds__(kBlock)
     conv_direct_kernel(const ConvGeom g, const int8_t* __restrict__ x, const int8_t* __restrict__ w,
                        const OutDev o, const long total) {
+  pdl_sync_with_previous_kernel();
   const long idx = static_cast<long>(blockIdx.x) * kBlock + threadIdx.x;
   if (idx >= total) return;
   const int co = static_cast<int>(idx % g.cout);
@@ -95,6 +96,7 @@ __global__ void __launch_bounds__(kBlock)
 __global__ void __launch_bounds__(kBlock)
     dwconv_kernel(const ConvGeom g, const int8_t* __restrict__ x, const int8_t* __restrict__ w,
                   const OutDev o, const long total, const int cquads) {
+  pdl_sync_with_previous_kernel();
   const long idx = static_cast<long>(blockIdx.x) * kBlock + threadIdx.x;
   if (idx >= total) return;
   const int cq = static_cast<int>(idx % cquads);
@@ -144,6 +146,7 @@ __global__ void __launch_bounds__(kBlock)
     sparse_i8_kernel(const SparseGeom g, const int8_t* __restrict__ x, const int* __restrict__ row_ptr,
                      const int* __restrict__ col, const int8_t* __restrict__ val, const EpiParams e,
                      void* __restrict__ y) {
+  pdl_sync_with_previous_kernel();
   const int p = (blockIdx.x * kBlock + threadIdx.x) * VEC;
   if (p >= g.hw) return;
   const int oc = blockIdx.y;
@@ -189,6 +192,7 @@ __global__ void __launch_bounds__(kBlock)
                       const int* __restrict__ col, const float* __restrict__ val,
                       const float* __restrict__ bias, const int act, const float alpha,
                       float* __restrict__ y) {
+  pdl_sync_with_previous_kernel();
   const int p = blockIdx.x * kBlock + threadIdx.x;
   if (p >= g.hw) return;
   const int oc = blockIdx.y;
@@ -203,12 +207,14 @@ __global__ void __launch_bounds__(kBlock)
 // ------------------------------------------------------------------ glue
 __global__ void calib_f32_to_i8_kernel(const float* __restrict__ x, int8_t* __restrict__ q, size_t n,
                                        float inv) {
+  pdl_sync_with_previous_kernel();
   const size_t stride = static_cast<size_t>(gridDim.x) * blockDim.x;
   for (size_t i = static_cast<size_t>(blockIdx.x) * blockDim.x + threadIdx.x; i < n; i += stride)
     q[i] = static_cast<int8_t>(calib_i8(x[i], inv));
 }
 __global__ void calib_i8_to_f32_kernel(const int8_t* __restrict__ q, float* __restrict__ y, size_t n,
                                        float scale) {
+  pdl_sync_with_previous_kernel();
   const size_t stride = static_cast<size_t>(gridDim.x) * blockDim.x;
   for (size_t i = static_cast<size_t>(blockIdx.x) * blockDim.x + threadIdx.x; i < n; i += stride)
     y[i] = static_cast<float>(q[i]) * scale;
@@ -220,6 +226,7 @@ template <typename T>
 __global__ void __launch_bounds__(kBlock)
     to_nhwc_i8_kernel(const T* __restrict__ x, int8_t* __restrict__ y, int c, int hw, int cpad,
                       float inv) {
+  pdl_sync_with_previous_kernel();
   __shared__ int8_t tile[32][64 + 4];
   const long n = blockIdx.z;
   const int c0 = blockIdx.y * 32, p0 = blockIdx.x * 64;
@@ -255,6 +262,7 @@ template <typename T>
 __global__ void __launch_bounds__(kBlock)
     fold_rows_kernel(const T* __restrict__ x, int8_t* __restrict__ y, int c, int h, int w, int wo, int kw,
                      int stride_w, int pad_l, int dil_w, float inv, long total) {
+  pdl_sync_with_previous_kernel();
   const long idx = static_cast<long>(blockIdx.x) * kBlock + threadIdx.x;
   if (idx >= total) return;
   const int q = static_cast<int>(idx % wo);
@@ -280,6 +288,7 @@ __global__ void __launch_bounds__(kBlock)
 // [n,hw,c] -> [n,c,hw], 32x32 element tiles.
 template <typename T>
 __global__ void nhwc_to_nchw_kernel(const T* __restrict__ x, T* __restrict__ y, int c, int hw) {
+  pdl_sync_with_previous_kernel();
   __shared__ T tile[32][33];
   const long n = blockIdx.z;
   const int c0 = blockIdx.y * 32, p0 = blockIdx.x * 32;
@@ -297,6 +306,7 @@ __global__ void nhwc_to_nchw_kernel(const T* __restrict__ x, T* __restrict__ y, 
 __global__ void __launch_bounds__(kBlock)
     maxpool_nhwc_i8_kernel(const int8_t* __restrict__ x, int8_t* __restrict__ y, int c4, int h, int w,
                            int ho, int wo, int k, int stride, int pad, long total) {
+  pdl_sync_with_previous_kernel();
   const long idx = static_cast<long>(blockIdx.x) * kBlock + threadIdx.x;
   if (idx >= total) return;
   const int cq = static_cast<int>(idx % c4);
@@ -321,6 +331,7 @@ __global__ void __launch_bounds__(kBlock)
 // x [n,hw,c] -> y [n,c] = (sum over hw in ascending order) / hw; optional calib to int8.
 __global__ void global_avgpool_kernel(const float* __restrict__ x, float* __restrict__ y,
                                       int8_t* __restrict__ q, int hw, int c, float inv, long total) {
+  pdl_sync_with_previous_kernel();
   const long idx = static_cast<long>(blockIdx.x) * blockDim.x + threadIdx.x;
   if (idx >= total) return;
   const long n = idx / c;
@@ -341,7 +352,7 @@ int conv_direct_launch(plb_ctx* ctx, const ConvGeom& g, const int8_t* x, const i
                        const OutSpec& out) {
   const long total = static_cast<long>(g.batch) * g.ho * g.wo * g.cout;
   if (total == 0) return PLB_OK;
-  conv_direct_kernel<<<blocks_for(total), kBlock, 0, ctx->stream>>>(g, x, w_rsc, to_dev(out), total);
+  PLB_CUDA(launch_kernel(conv_direct_kernel, dim3(blocks_for(total)), dim3(kBlock), 0, ctx->stream, g, x, w_rsc, to_dev(out), total));
   PLB_CUDA(cudaGetLastError());
   ctx->launches++;
   return PLB_OK;
@@ -352,7 +363,7 @@ int dwconv_launch(plb_ctx* ctx, const ConvGeom& g, const int8_t* x, const int8_t
   const int cquads = (g.cout + 3) / 4;
   const long total = static_cast<long>(g.batch) * g.ho * g.wo * cquads;
   if (total == 0) return PLB_OK;
-  dwconv_kernel<<<blocks_for(total), kBlock, 0, ctx->stream>>>(g, x, w_tc, to_dev(out), total, cquads);
+  PLB_CUDA(launch_kernel(dwconv_kernel, dim3(blocks_for(total)), dim3(kBlock), 0, ctx->stream, g, x, w_tc, to_dev(out), total, cquads));
   PLB_CUDA(cudaGetLastError());
   ctx->launches++;
   return PLB_OK;
@@ -368,18 +379,14 @@ int sparse_csr_launch(plb_ctx* ctx, const SparseGeom& g, const void* x, const in
                       (reinterpret_cast<uintptr_t>(y) & 3) == 0;
     if (vec4) {
       dim3 grid((g.hw / 4 + kBlock - 1) / kBlock, g.cout, g.batch);
-      sparse_i8_kernel<4><<<grid, kBlock, 0, ctx->stream>>>(
-          g, static_cast<const int8_t*>(x), row_ptr, col, static_cast<const int8_t*>(val), epi, y);
+      PLB_CUDA(launch_kernel(sparse_i8_kernel<4>, dim3(grid), dim3(kBlock), 0, ctx->stream, g, static_cast<const int8_t*>(x), row_ptr, col, static_cast<const int8_t*>(val), epi, y));
     } else {
       dim3 grid((g.hw + kBlock - 1) / kBlock, g.cout, g.batch);
-      sparse_i8_kernel<1><<<grid, kBlock, 0, ctx->stream>>>(
-          g, static_cast<const int8_t*>(x), row_ptr, col, static_cast<const int8_t*>(val), epi, y);
+      PLB_CUDA(launch_kernel(sparse_i8_kernel<1>, dim3(grid), dim3(kBlock), 0, ctx->stream, g, static_cast<const int8_t*>(x), row_ptr, col, static_cast<const int8_t*>(val), epi, y));
     }
   } else {
     dim3 grid((g.hw + kBlock - 1) / kBlock, g.cout, g.batch);
-    sparse_f32_kernel<<<grid, kBlock, 0, ctx->stream>>>(
-        g, static_cast<const float*>(x), row_ptr, col, static_cast<const float*>(val), bias_raw,
-        epi.act, epi.alpha, static_cast<float*>(y));
+    PLB_CUDA(launch_kernel(sparse_f32_kernel, dim3(grid), dim3(kBlock), 0, ctx->stream, g, static_cast<const float*>(x), row_ptr, col, static_cast<const float*>(val), bias_raw, epi.act, epi.alpha, static_cast<float*>(y)));
   }
   PLB_CUDA(cudaGetLastError());
   ctx->launches++;
@@ -389,7 +396,7 @@ int sparse_csr_launch(plb_ctx* ctx, const SparseGeom& g, const void* x, const in
 int calib_f32_to_i8_launch(plb_ctx* ctx, const float* x, int8_t* q, size_t n, float scale) {
   if (n == 0) return PLB_OK;
   const unsigned blocks = static_cast<unsigned>(std::min<size_t>((n + kBlock - 1) / kBlock, 148 * 16));
-  calib_f32_to_i8_kernel<<<blocks, kBlock, 0, ctx->stream>>>(x, q, n, 1.f / scale);
+  PLB_CUDA(launch_kernel(calib_f32_to_i8_kernel, dim3(blocks), dim3(kBlock), 0, ctx->stream, x, q, n, 1.f / scale));
   PLB_CUDA(cudaGetLastError());
   ctx->launches++;
   return PLB_OK;
@@ -398,7 +405,7 @@ int calib_f32_to_i8_launch(plb_ctx* ctx, const float* x, int8_t* q, size_t n, fl
 int calib_i8_to_f32_launch(plb_ctx* ctx, const int8_t* q, float* y, size_t n, float scale) {
   if (n == 0) return PLB_OK;
   const unsigned blocks = static_cast<unsigned>(std::min<size_t>((n + kBlock - 1) / kBlock, 148 * 16));
-  calib_i8_to_f32_kernel<<<blocks, kBlock, 0, ctx->stream>>>(q, y, n, scale);
+  PLB_CUDA(launch_kernel(calib_i8_to_f32_kernel, dim3(blocks), dim3(kBlock), 0, ctx->stream, q, y, n, scale));
   PLB_CUDA(cudaGetLastError());
   ctx->launches++;
   return PLB_OK;
@@ -410,7 +417,7 @@ int nchw_to_nhwc_i8_launch(plb_ctx* ctx, const int8_t* x, int8_t* y, int n, int 
   if (cpad % 8 || cpad < c) return fail(PLB_E_INVALID, "cpad must be a multiple of 8 and >= c");
   const int hw = h * w;
   dim3 grid((hw + 63) / 64, (cpad + 31) / 32, n);
-  to_nhwc_i8_kernel<int8_t><<<grid, kBlock, 0, ctx->stream>>>(x, y, c, hw, cpad, 1.f);
+  PLB_CUDA(launch_kernel(to_nhwc_i8_kernel<int8_t>, dim3(grid), dim3(kBlock), 0, ctx->stream, x, y, c, hw, cpad, 1.f));
   PLB_CUDA(cudaGetLastError());
   ctx->launches++;
   return PLB_OK;
@@ -422,7 +429,7 @@ int calib_nchw_f32_to_nhwc_i8_launch(plb_ctx* ctx, const float* x, int8_t* y, in
   if (cpad % 8 || cpad < c) return fail(PLB_E_INVALID, "cpad must be a multiple of 8 and >= c");
   const int hw = h * w;
   dim3 grid((hw + 63) / 64, (cpad + 31) / 32, n);
-  to_nhwc_i8_kernel<float><<<grid, kBlock, 0, ctx->stream>>>(x, y, c, hw, cpad, 1.f / scale);
+  PLB_CUDA(launch_kernel(to_nhwc_i8_kernel<float>, dim3(grid), dim3(kBlock), 0, ctx->stream, x, y, c, hw, cpad, 1.f / scale));
   PLB_CUDA(cudaGetLastError());
   ctx->launches++;
   return PLB_OK;
@@ -434,11 +441,9 @@ int fold_rows_launch(plb_ctx* ctx, const void* x, int x_is_f32, int8_t* y, int n
   if (total == 0) return PLB_OK;
   if (c * kw > 32) return fail(PLB_E_INVALID, "row folding needs cin * kw <= 32");
   if (x_is_f32)
-    fold_rows_kernel<float><<<blocks_for(total), kBlock, 0, ctx->stream>>>(
-        static_cast<const float*>(x), y, c, h, w, wo, kw, stride_w, pad_l, dil_w, 1.f / scale, total);
+    PLB_CUDA(launch_kernel(fold_rows_kernel<float>, dim3(blocks_for(total)), dim3(kBlock), 0, ctx->stream, static_cast<const float*>(x), y, c, h, w, wo, kw, stride_w, pad_l, dil_w, 1.f / scale, total));
   else
-    fold_rows_kernel<int8_t><<<blocks_for(total), kBlock, 0, ctx->stream>>>(
-        static_cast<const int8_t*>(x), y, c, h, w, wo, kw, stride_w, pad_l, dil_w, 1.f, total);
+    PLB_CUDA(launch_kernel(fold_rows_kernel<int8_t>, dim3(blocks_for(total)), dim3(kBlock), 0, ctx->stream, static_cast<const int8_t*>(x), y, c, h, w, wo, kw, stride_w, pad_l, dil_w, 1.f, total));
   PLB_CUDA(cudaGetLastError());
   ctx->launches++;
   return PLB_OK;
@@ -450,11 +455,9 @@ int nhwc_to_nchw_launch(plb_ctx* ctx, const void* x, void* y, int n, int c, int 
   const int hw = h * w;
   dim3 grid((hw + 31) / 32, (c + 31) / 32, n), block(32, 8);
   if (elem_bytes == 1)
-    nhwc_to_nchw_kernel<int8_t><<<grid, block, 0, ctx->stream>>>(
-        static_cast<const int8_t*>(x), static_cast<int8_t*>(y), c, hw);
+    PLB_CUDA(launch_kernel(nhwc_to_nchw_kernel<int8_t>, dim3(grid), dim3(block), 0, ctx->stream, static_cast<const int8_t*>(x), static_cast<int8_t*>(y), c, hw));
   else if (elem_bytes == 4)
-    nhwc_to_nchw_kernel<int32_t><<<grid, block, 0, ctx->stream>>>(
-        static_cast<const int32_t*>(x), static_cast<int32_t*>(y), c, hw);
+    PLB_CUDA(launch_kernel(nhwc_to_nchw_kernel<int32_t>, dim3(grid), dim3(block), 0, ctx->stream, static_cast<const int32_t*>(x), static_cast<int32_t*>(y), c, hw));
   else
     return fail(PLB_E_INVALID, "element size must be 1 or 4");
   PLB_CUDA(cudaGetLastError());
@@ -468,8 +471,7 @@ int maxpool_nhwc_i8_launch(plb_ctx* ctx, const int8_t* x, int8_t* y, int n, int 
   const int ho = (h + 2 * pad - k) / stride + 1, wo = (w + 2 * pad - k) / stride + 1;
   const long total = static_cast<long>(n) * ho * wo * (c / 4);
   if (total == 0) return PLB_OK;
-  maxpool_nhwc_i8_kernel<<<blocks_for(total), kBlock, 0, ctx->stream>>>(x, y, c / 4, h, w, ho, wo, k,
-                                                                         stride, pad, total);
+  PLB_CUDA(launch_kernel(maxpool_nhwc_i8_kernel, dim3(blocks_for(total)), dim3(kBlock), 0, ctx->stream, x, y, c / 4, h, w, ho, wo, k, stride, pad, total));
   PLB_CUDA(cudaGetLastError());
   ctx->launches++;
   return PLB_OK;
@@ -479,8 +481,7 @@ int global_avgpool_nhwc_f32_launch(plb_ctx* ctx, const float* x, float* y, int8_
                                    int c, float scale) {
   const long total = static_cast<long>(n) * c;
   if (total == 0) return PLB_OK;
-  global_avgpool_kernel<<<blocks_for(total), kBlock, 0, ctx->stream>>>(x, y, q, hw, c, 1.f / scale,
-                                                                        total);
+  PLB_CUDA(launch_kernel(global_avgpool_kernel, dim3(blocks_for(total)), dim3(kBlock), 0, ctx->stream, x, y, q, hw, c, 1.f / scale, total));
   PLB_CUDA(cudaGetLastError());
   ctx->launches++;
   return PLB_OK;

@@ -2,6 +2,7 @@
 // Host-side planning only; the arithmetic lives in igemm_tc.cu and kernels_simple.cu.
 #include <algorithm>
 #include <cmath>
+#include <cstdlib>
 #include <memory>
 
 #include "igemm_tc.cuh"
@@ -19,6 +20,14 @@ int fail(int code, const char* fmt, ...) {
   va_end(ap);
   g_last_error = buf;
   return code;
+}
+
+bool pdl_enabled() {
+  static const bool on = [] {
+    const char* v = std::getenv("PLB_PDL");
+    return !(v && v[0] == '0');
+  }();
+  return on;
 }
 
 namespace {

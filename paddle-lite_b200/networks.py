@@ -168,18 +168,29 @@ def build_quantized(spec, seed=1234, calib_images=16, device="cpu"):
 # ----------------------------------------------------------------------------- GPU runner
 class Runner:
     """Holds the prepared layers and all activation buffers for one batch size on one GPU and
-    enqueues a whole forward pass on the context's stream (no allocation, no host sync)."""
+    enqueues a whole forward pass on the context's stream (no allocation, no host sync).
 
-    def __init__(self, plb, ctx, qnet, batch):
+    `micro_batch` (a divisor of `batch`) makes the step run depth-first over slices of that
+    many images through the same set of activation buffers: every intermediate tensor of a
+    slice is then small enough to stay in the 126 MB L2 between the layer that writes it and
+    the layer that reads it, instead of making a round trip through HBM."""
+
+    def __init__(self, plb, ctx, qnet, batch, micro_batch=None):
         import torch
-        self.plb, self.ctx, self.q, self.batch = plb, ctx, qnet, batch
+        self.plb, self.ctx, self.q = plb, ctx, qnet
+        self.full_batch = batch
+        micro_batch = micro_batch or batch
+        if batch % micro_batch:
+            raise ValueError("micro_batch must divide batch")
+        self.micro_batch = micro_batch
+        full_batch, batch = batch, micro_batch
         spec, scales = qnet["spec"], qnet["scales"]
         dev = "cuda:%d" % ctx.device
         c, h, w = spec["image"]
         self.hw = {"x": (h, w)}
         self.buf = {}
         self.steps = []
-        self.image_shape = (batch, c, h, w)
+        self.image_shape = (full_batch, c, h, w)
         for op in spec["ops"]:
             kind = op["op"]
             if kind in ("conv", "conv_add_relu"):
@@ -225,11 +236,18 @@ class Runner:
                 self.buf[op["dst"]] = torch.empty((batch, op["n"]), dtype=torch.float32, device=dev)
                 self.steps.append(("fc", fc, op["src"], op["dst"]))
         self.in_scale = float(scales["x"])
+        self.logits = torch.empty((full_batch, self.buf["logits"].shape[1]), dtype=torch.float32, device=dev)
+        self.buf["logits"] = self.logits[:batch]
 
     def forward(self, image_f32_nchw):
-        """image_f32_nchw: device float32 [batch,3,224,224].  Returns the fp32 logits buffer."""
-        self.forward_head(image_f32_nchw)
-        return self.forward_body()
+        """image_f32_nchw: device float32 [batch,3,224,224].  Returns the fp32 logits [batch,1000]."""
+        mb = self.micro_batch
+        for i in range(0, self.full_batch, mb):
+            self.buf["logits"] = self.logits[i:i + mb]
+            self.forward_head(image_f32_nchw[i:i + mb])
+            self.forward_body()
+        self.buf["logits"] = self.logits[:mb]
+        return self.logits
 
     def forward_head(self, image_f32_nchw):
         """First layer: calib + staging of the fp32 image and the stem convolution (the only
