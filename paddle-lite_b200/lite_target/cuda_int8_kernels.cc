@@ -1,0 +1,310 @@
+// Paddle-Lite kernels of the new target: `kCUDA` / `kInt8` / `kNCHW` conv2d,
+// depthwise_conv2d, fc and sparse_conv2d implemented on the plb200 C ABI.
+//
+// This file is compiled AGAINST THE REFERENCE HEADERS (it is the code a maintainer adds to
+// the reference tree as lite/kernels/cuda/int8_kernels.cc); it registers through the
+// reference's own REGISTER_LITE_KERNEL macro (lite/core/op_registry.h:268-291), takes its
+// parameters from operators::ConvParam / FcParam / SparseConvParam
+// (lite/operators/op_params.h:403-455, :100-118, :373-400) and follows the life cycle of
+// KernelBase::Launch (lite/core/kernel.h:84-124): PrepareForRun() once, then Run().
+// Registration names, aliases and tensor bindings mirror the x86 int8 kernels
+// (lite/kernels/x86/conv_compute.cc:509-553, lite/kernels/x86/fc_compute.cc:296-308) and the
+// ARM sparse kernels (lite/kernels/arm/sparse_conv_compute.cc:393-430).
+//
+// Tensors handed to these kernels hold DEVICE memory (TargetType::kCUDA buffers, e.g. wrapped
+// with lite::Buffer(void*, TargetType, size_t), lite/core/memory.h:98-99); filters, scales
+// and biases are read on the host at PrepareForRun, exactly like the x86 kernels do.
+#include <memory>
+#include <vector>
+
+#include "include/plb200.h"
+#include "lite/core/kernel.h"
+#include "lite/core/op_registry.h"
+#include "lite/operators/op_params.h"
+
+namespace paddle {
+namespace lite {
+namespace kernels {
+namespace cuda {
+
+// One context per process and device stream.  The reference creates Context<TARGET> objects in
+// ContextScheduler (lite/core/context.h:430-484); until that has a kCUDA case the kernels share
+// this one (stream 0 of device 0, or the stream given through SetPlbStream()).
+inline plb_ctx*& SharedCtx() {
+  static plb_ctx* ctx = nullptr;
+  return ctx;
+}
+inline plb_ctx* GetCtx() {
+  if (SharedCtx() == nullptr) {
+    CHECK_EQ(plb_ctx_create(0, nullptr, &SharedCtx()), PLB_OK) << plb_last_error();
+  }
+  return SharedCtx();
+}
+#define PLB_CHECK(call) CHECK_EQ((call), PLB_OK) << plb_last_error()
+
+inline int ActCode(const operators::ActivationParam& act, float* alpha) {
+  *alpha = 0.f;
+  if (!act.has_active) return PLB_ACT_NONE;
+  switch (act.active_type) {
+    case lite_api::ActivationType::kRelu:
+      return PLB_ACT_RELU;
+    case lite_api::ActivationType::kRelu6:
+      *alpha = act.Relu_clipped_coef;
+      return PLB_ACT_RELU6;
+    case lite_api::ActivationType::kLeakyRelu:
+      *alpha = act.Leaky_relu_alpha;
+      return PLB_ACT_LEAKY;
+    default:
+      return PLB_ACT_NONE;  // the x86 int8 kernel ignores other types as well
+  }
+}
+
+template <PrecisionType OutType>
+class ConvInt8Compute : public KernelLite<TARGET(kCUDA), PRECISION(kInt8)> {
+ public:
+  using param_t = operators::ConvParam;
+
+  void PrepareForRun() override {
+    auto& param = this->Param<param_t>();
+    auto x_dims = param.x->dims();
+    auto w_dims = param.filter->dims();
+    auto paddings = *param.paddings;
+    auto dilations = *param.dilations;
+    plb_conv_desc d{};
+    d.cin = x_dims[1];
+    d.h = x_dims[2];
+    d.w = x_dims[3];
+    d.cout = w_dims[0];
+    d.kh = w_dims[2];
+    d.kw = w_dims[3];
+    d.stride_h = param.strides[0];
+    d.stride_w = param.strides[1];
+    d.pad_top = paddings[0];
+    d.pad_bottom = paddings[1];
+    d.pad_left = paddings[2];
+    d.pad_right = paddings[3];
+    d.dil_h = dilations[0];
+    d.dil_w = dilations[1];
+    d.groups = param.groups;
+    d.act = ActCode(param.activation_param, &d.act_alpha);
+    d.in_scale = param.input_scale;
+    d.out_scale = param.output_scale;
+    d.out_dtype = OutType == PRECISION(kInt8) ? PLB_OUT_I8 : PLB_OUT_F32;
+    d.leaky_compat = 1;  // the drop-in reproduces conv_compute.cc:394
+    d.impl = PLB_IMPL_AUTO;
+    const float* bias = param.bias ? param.bias->template data<float>() : nullptr;
+    plb_conv* conv = nullptr;
+    PLB_CHECK(plb_conv_prepare(GetCtx(), &d, param.filter->template data<int8_t>(),
+                               param.weight_scale.data(), static_cast<int>(param.weight_scale.size()),
+                               bias, &conv));
+    conv_.reset(conv);
+    in_h_ = d.h;
+    in_w_ = d.w;
+  }
+
+  void ReInitWhenNeeded() override {
+    // a prepared layer is bound to its input height/width; re-plan when they change
+    auto x_dims = this->Param<param_t>().x->dims();
+    if (conv_ && (x_dims[2] != in_h_ || x_dims[3] != in_w_)) PrepareForRun();
+  }
+
+  void Run() override {
+    auto& param = this->Param<param_t>();
+    const int batch = param.x->dims()[0];
+    void* out = OutType == PRECISION(kInt8)
+                    ? static_cast<void*>(param.output->template mutable_data<int8_t>(TARGET(kCUDA)))
+                    : static_cast<void*>(param.output->template mutable_data<float>(TARGET(kCUDA)));
+    PLB_CHECK(plb_conv_run(conv_.get(), param.x->template data<int8_t>(), out, batch));
+  }
+
+ private:
+  struct Deleter {
+    void operator()(plb_conv* p) const { plb_conv_destroy(p); }
+  };
+  std::unique_ptr<plb_conv, Deleter> conv_;
+  int64_t in_h_{0}, in_w_{0};
+};
+
+template <PrecisionType OutType>
+class FcInt8Compute : public KernelLite<TARGET(kCUDA), PRECISION(kInt8)> {
+ public:
+  using param_t = operators::FcParam;
+
+  void PrepareForRun() override {
+    auto& param = this->Param<param_t>();
+    auto w_dims = param.w->dims();
+    const int k = w_dims[0], n = w_dims[1];
+    int act = PLB_ACT_NONE;
+    float alpha = 0.f;
+    if (param.activation_type == "relu") act = PLB_ACT_RELU;
+    if (param.activation_type == "relu6") {
+      act = PLB_ACT_RELU6;
+      alpha = param.alpha;
+    }
+    const float* bias = param.bias ? param.bias->template data<float>() : nullptr;
+    plb_fc* fc = nullptr;
+    PLB_CHECK(plb_fc_prepare(GetCtx(), k, n, act, alpha, param.input_scale, param.output_scale,
+                             OutType == PRECISION(kInt8) ? PLB_OUT_I8 : PLB_OUT_F32,
+                             param.w->template data<int8_t>(), param.weight_scale.data(),
+                             static_cast<int>(param.weight_scale.size()), bias, &fc));
+    fc_.reset(fc);
+  }
+
+  void Run() override {
+    auto& param = this->Param<param_t>();
+    const int m = param.input->dims().count(0, param.in_num_col_dims);
+    void* out = OutType == PRECISION(kInt8)
+                    ? static_cast<void*>(param.output->template mutable_data<int8_t>(TARGET(kCUDA)))
+                    : static_cast<void*>(param.output->template mutable_data<float>(TARGET(kCUDA)));
+    PLB_CHECK(plb_fc_run(fc_.get(), param.input->template data<int8_t>(), out, m));
+  }
+
+ private:
+  struct Deleter {
+    void operator()(plb_fc* p) const { plb_fc_destroy(p); }
+  };
+  std::unique_ptr<plb_fc, Deleter> fc_;
+};
+
+template <PrecisionType InType, PrecisionType OutType>
+class SparseConvCompute : public KernelLite<TARGET(kCUDA), InType> {
+ public:
+  using param_t = operators::SparseConvParam;
+
+  void PrepareForRun() override {
+    auto& param = this->template Param<param_t>();
+    auto x_dims = param.x->dims();
+    plb_sparse_desc d{};
+    d.cin = x_dims[1];
+    d.h = x_dims[2];
+    d.w = x_dims[3];
+    d.cout = param.oc_nonzeros->dims()[0];
+    d.is_int8 = InType == PRECISION(kInt8);
+    d.out_dtype = OutType == PRECISION(kInt8) ? PLB_OUT_I8 : PLB_OUT_F32;
+    d.flag_semi = param.flag_semi;
+    d.first_ic = param.first_ic;
+    d.act = ActCode(param.activation_param, &d.act_alpha);
+    d.in_scale = param.input_scale;
+    d.out_scale = param.output_scale;
+    d.leaky_compat = 1;  // sparse_conv_compute.cc:86-90 divides the slope as well
+    d.impl = PLB_IMPL_AUTO;
+    const void* nz = d.is_int8 ? static_cast<const void*>(param.nonzero_weights->template data<int8_t>())
+                               : static_cast<const void*>(param.nonzero_weights->template data<float>());
+    const float* bias = param.bias ? param.bias->template data<float>() : nullptr;
+    plb_sparse* sp = nullptr;
+    PLB_CHECK(plb_sparse_prepare(GetCtx(), &d, nz, static_cast<int>(param.nonzero_weights->numel()),
+                                 param.oc_nonzeros->template data<uint32_t>(),
+                                 param.diffs->template data<int32_t>(),
+                                 static_cast<int>(param.diffs->numel()), param.weight_scale.data(),
+                                 static_cast<int>(param.weight_scale.size()), bias, &sp));
+    sp_.reset(sp);
+  }
+
+  void Run() override {
+    auto& param = this->template Param<param_t>();
+    const int batch = param.x->dims()[0];
+    const void* x = InType == PRECISION(kInt8) ? static_cast<const void*>(param.x->template data<int8_t>())
+                                               : static_cast<const void*>(param.x->template data<float>());
+    void* out = OutType == PRECISION(kInt8)
+                    ? static_cast<void*>(param.output->template mutable_data<int8_t>(TARGET(kCUDA)))
+                    : static_cast<void*>(param.output->template mutable_data<float>(TARGET(kCUDA)));
+    PLB_CHECK(plb_sparse_run(sp_.get(), x, out, batch));
+  }
+
+ private:
+  struct Deleter {
+    void operator()(plb_sparse* p) const { plb_sparse_destroy(p); }
+  };
+  std::unique_ptr<plb_sparse, Deleter> sp_;
+};
+
+}  // namespace cuda
+}  // namespace kernels
+}  // namespace lite
+}  // namespace paddle
+
+namespace plbk = paddle::lite::kernels::cuda;
+typedef plbk::ConvInt8Compute<PRECISION(kInt8)> CudaConvInt8_Int8;
+typedef plbk::ConvInt8Compute<PRECISION(kFloat)> CudaConvInt8_Fp32;
+typedef plbk::FcInt8Compute<PRECISION(kInt8)> CudaFcInt8_Int8;
+typedef plbk::FcInt8Compute<PRECISION(kFloat)> CudaFcInt8_Fp32;
+typedef plbk::SparseConvCompute<PRECISION(kFloat), PRECISION(kFloat)> CudaSparseConvFp32;
+typedef plbk::SparseConvCompute<PRECISION(kInt8), PRECISION(kFloat)> CudaSparseConvInt8Fp32;
+typedef plbk::SparseConvCompute<PRECISION(kInt8), PRECISION(kInt8)> CudaSparseConvInt8Int8;
+
+#define PLB_T(prec) LiteType::GetTensorTy(TARGET(kCUDA), PRECISION(prec))
+
+REGISTER_LITE_KERNEL(conv2d, kCUDA, kInt8, kNCHW, CudaConvInt8_Int8, int8_out)
+    .BindInput("Input", {PLB_T(kInt8)})
+    .BindInput("SecondInput", {PLB_T(kInt8)})
+    .BindInput("Bias", {PLB_T(kFloat)})
+    .BindInput("Filter", {PLB_T(kInt8)})
+    .BindOutput("Output", {PLB_T(kInt8)})
+    .BindPaddleOpVersion("conv2d", 1)
+    .Finalize();
+
+REGISTER_LITE_KERNEL(conv2d, kCUDA, kInt8, kNCHW, CudaConvInt8_Fp32, fp32_out)
+    .BindInput("Input", {PLB_T(kInt8)})
+    .BindInput("SecondInput", {PLB_T(kInt8)})
+    .BindInput("Bias", {PLB_T(kFloat)})
+    .BindInput("Filter", {PLB_T(kInt8)})
+    .BindOutput("Output", {PLB_T(kFloat)})
+    .BindPaddleOpVersion("conv2d", 1)
+    .Finalize();
+
+REGISTER_LITE_KERNEL(depthwise_conv2d, kCUDA, kInt8, kNCHW, CudaConvInt8_Int8, int8_out)
+    .BindInput("Input", {PLB_T(kInt8)})
+    .BindInput("Bias", {PLB_T(kFloat)})
+    .BindInput("Filter", {PLB_T(kInt8)})
+    .BindOutput("Output", {PLB_T(kInt8)})
+    .BindPaddleOpVersion("depthwise_conv2d", 1)
+    .Finalize();
+
+REGISTER_LITE_KERNEL(depthwise_conv2d, kCUDA, kInt8, kNCHW, CudaConvInt8_Fp32, fp32_out)
+    .BindInput("Input", {PLB_T(kInt8)})
+    .BindInput("Bias", {PLB_T(kFloat)})
+    .BindInput("Filter", {PLB_T(kInt8)})
+    .BindOutput("Output", {PLB_T(kFloat)})
+    .BindPaddleOpVersion("depthwise_conv2d", 1)
+    .Finalize();
+
+REGISTER_LITE_KERNEL(fc, kCUDA, kInt8, kNCHW, CudaFcInt8_Int8, int8_out)
+    .BindInput("Input", {PLB_T(kInt8)})
+    .BindInput("Bias", {PLB_T(kFloat)})
+    .BindInput("W", {PLB_T(kInt8)})
+    .BindOutput("Out", {PLB_T(kInt8)})
+    .Finalize();
+
+REGISTER_LITE_KERNEL(fc, kCUDA, kInt8, kNCHW, CudaFcInt8_Fp32, fp32_out)
+    .BindInput("Input", {PLB_T(kInt8)})
+    .BindInput("Bias", {PLB_T(kFloat)})
+    .BindInput("W", {PLB_T(kInt8)})
+    .BindOutput("Out", {PLB_T(kFloat)})
+    .Finalize();
+
+REGISTER_LITE_KERNEL(sparse_conv2d, kCUDA, kFloat, kNCHW, CudaSparseConvFp32, def)
+    .BindInput("Input", {PLB_T(kFloat)})
+    .BindInput("NonZeroWeights", {PLB_T(kFloat)})
+    .BindInput("OcNonZeros", {PLB_T(kInt32)})
+    .BindInput("Diffs", {PLB_T(kInt32)})
+    .BindInput("Bias", {PLB_T(kFloat)})
+    .BindOutput("Output", {PLB_T(kFloat)})
+    .Finalize();
+
+REGISTER_LITE_KERNEL(sparse_conv2d, kCUDA, kInt8, kNCHW, CudaSparseConvInt8Fp32, int8_fp32_out)
+    .BindInput("Input", {PLB_T(kInt8)})
+    .BindInput("NonZeroWeights", {PLB_T(kInt8)})
+    .BindInput("OcNonZeros", {PLB_T(kInt32)})
+    .BindInput("Diffs", {PLB_T(kInt32)})
+    .BindInput("Bias", {PLB_T(kFloat)})
+    .BindOutput("Output", {PLB_T(kFloat)})
+    .Finalize();
+
+REGISTER_LITE_KERNEL(sparse_conv2d, kCUDA, kInt8, kNCHW, CudaSparseConvInt8Int8, int8_int8_out)
+    .BindInput("Input", {PLB_T(kInt8)})
+    .BindInput("NonZeroWeights", {PLB_T(kInt8)})
+    .BindInput("OcNonZeros", {PLB_T(kInt32)})
+    .BindInput("Diffs", {PLB_T(kInt32)})
+    .BindInput("Bias", {PLB_T(kFloat)})
+    .BindOutput("Output", {PLB_T(kInt8)})
+    .Finalize();
