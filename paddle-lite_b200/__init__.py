@@ -121,8 +121,10 @@ class Context:
 
     def __init__(self, device=0, stream=None):
         import torch
+        import weakref
         self.device = device
         self._stream = stream if stream is not None else torch.cuda.current_stream(device)
+        self._children = weakref.WeakSet()  # prepared layers; they must be destroyed before the ctx
         self.handle = _P()
         _check(lib().plb_ctx_create(device, C.c_void_p(self._stream.cuda_stream), C.byref(self.handle)))
 
@@ -139,6 +141,8 @@ class Context:
 
     def close(self):
         if self.handle:
+            for child in list(self._children):
+                child.close()
             lib().plb_ctx_destroy(self.handle)
             self.handle = _P()
 
@@ -229,6 +233,7 @@ class Conv:
         self.handle = _P()
         _check(lib().plb_conv_prepare(ctx.handle, C.byref(d), _np_ptr(f), _np_ptr(ws), int(ws.size),
                                       _np_ptr(b), C.byref(self.handle)))
+        ctx._children.add(self)
         ho, wo = C.c_int(), C.c_int()
         _check(lib().plb_conv_out_dims(self.handle, C.byref(ho), C.byref(wo)))
         self.ho, self.wo = ho.value, wo.value
@@ -315,6 +320,7 @@ class Fc:
                                     out_scale if out_scale is not None else 1.0,
                                     OUT_I8 if self.out_is_i8 else OUT_F32, _np_ptr(w), _np_ptr(ws),
                                     int(ws.size), _np_ptr(b), C.byref(self.handle)))
+        ctx._children.add(self)
 
     def run(self, x, out=None):
         import torch
@@ -372,6 +378,7 @@ class SparseConv:
         _check(lib().plb_sparse_prepare(ctx.handle, C.byref(d), _np_ptr(nz), int(nz.size), _np_ptr(cum),
                                         _np_ptr(df), int(df.size), _np_ptr(ws),
                                         0 if ws is None else int(ws.size), _np_ptr(b), C.byref(self.handle)))
+        ctx._children.add(self)
 
     def run(self, x, out=None):
         import torch
