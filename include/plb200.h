@@ -110,6 +110,23 @@ int plb_conv_run_nhwc(plb_conv* conv, const int8_t* x, void* y, int batch);
  * y is channels-last [batch,ho,wo,cout].  Layers with few input channels (cin*kw <= 32, e.g.
  * RGB stems) are staged row-folded so the tensor cores see 32-byte pixels. */
 int plb_conv_run_image_f32(plb_conv* conv, const float* x, void* y, int batch);
+/* plb_conv_run without any device allocation.  No counterpart in the reference: this entry
+ * exists for hosts that must not have a library allocate behind their back — a serving loop
+ * in which a cudaMalloc would synchronise the whole device and stall the other predictors
+ * sharing the GPU, or a runtime that has given all device memory to its own planned arena
+ * (what memory_optimize_pass does for the reference's buffers).  The NCHW<->channels-last
+ * staging that plb_conv_run keeps in the ctx workspace lives here in a fixed array inside the
+ * library image: 8 MiB, held by every GPU that loads the library until the process exits.
+ *   - a call whose staging (plb_conv_workspace_bytes(conv, batch)) exceeds 8 MiB is rejected
+ *     with PLB_E_INVALID and a message that names both sizes; nothing is launched.
+ *   - the first call on a device looks up the array's device address
+ *     (cudaGetSymbolAddress); make that first call before starting any stream capture.
+ *   - all calls of the process on one device share the array, and it keeps whatever the last
+ *     call left there.  Every byte a call reads it has written first, so consecutive calls on
+ *     one stream are safe; calls that can overlap on the GPU (different streams or contexts)
+ *     race on it and must be serialised by the caller.
+ * Same arguments and result as plb_conv_run. */
+int plb_conv_run_static(plb_conv* conv, const int8_t* x, void* y, int batch);
 /* Test hook: the raw int32 accumulators, NCHW [batch,cout,ho,wo] (bit-exact check). */
 int plb_conv_acc_i32(plb_conv* conv, const int8_t* x, int32_t* acc, int batch);
 /* conv (fp32 value, no activation of its own) + fp32 residual + ReLU, then optionally the

@@ -59,6 +59,7 @@ SYMBOLS = {
     "plb_conv_run": (C.c_int, [_P, _P, _P, C.c_int]),
     "plb_conv_run_nhwc": (C.c_int, [_P, _P, _P, C.c_int]),
     "plb_conv_acc_i32": (C.c_int, [_P, _P, _P, C.c_int]),
+    "plb_conv_run_static": (C.c_int, [_P, _P, _P, C.c_int]),
     "plb_conv_run_image_f32": (C.c_int, [_P, _P, _P, C.c_int]),
     "plb_conv_run_nhwc_add_relu": (C.c_int, [_P, _P, _P, _P, _P, C.c_float, C.c_int]),
     "plb_conv_out_dims": (C.c_int, [_P, C.POINTER(C.c_int), C.POINTER(C.c_int)]),
@@ -257,6 +258,12 @@ class Conv:
         y = torch.empty((n, self.desc.cout, self.ho, self.wo), dtype=torch.int32, device=x.device)
         _check(lib().plb_conv_acc_i32(self.handle, _dev_ptr(x), _dev_ptr(y), n))
         return y
+
+    def run_static(self, x, out):
+        """plb_conv_run_static: like run(), staged in the library's built-in 8 MiB scratch, no
+        device allocation by the library.  `out` must be supplied by the caller."""
+        _check(lib().plb_conv_run_static(self.handle, _dev_ptr(x), _dev_ptr(out), x.shape[0]))
+        return out
 
     def run_nhwc(self, x, out=None):
         """x [N,H,W,Cin] int8 -> [N,Ho,Wo,Cout]."""

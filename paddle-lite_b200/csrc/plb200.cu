@@ -141,6 +141,14 @@ struct plb_sparse {
   plb_conv* dense = nullptr;  // densified tensor-core variant
 };
 
+// ------------------------------------------------------------------ scratch that is never allocated
+// Staging memory of plb_conv_run_static(): part of the library image, so every GPU that loads
+// the library holds these bytes until the process exits.  In host code this name is only a
+// handle; the device address is looked up once per device with cudaGetSymbolAddress().
+constexpr size_t kStaticScratchBytes = size_t(8) << 20;
+static __device__ __align__(256) unsigned char g_static_scratch[kStaticScratchBytes];
+static void* g_static_scratch_addr[64] = {nullptr};  // per device ordinal
+
 extern "C" {
 
 const char* plb_last_error(void) { return g_last_error.c_str(); }
@@ -465,6 +473,48 @@ int plb_conv_run_image_f32(plb_conv* conv, const float* x, void* y, int batch) {
   if (rc) return rc;
   OutSpec o = out_spec(conv, d.out_dtype == PLB_OUT_I8 ? OUT_I8 : OUT_F32, y);
   return conv_core(conv, xs, batch, o);
+}
+
+int plb_conv_run_static(plb_conv* conv, const int8_t* x, void* y, int batch) {
+  PLB_REQUIRE(conv != nullptr, "null argument");
+  PLB_REQUIRE(batch >= 0, "negative batch");
+  if (batch == 0) return PLB_OK;
+  PLB_REQUIRE(x && y, "null argument");
+  plb_ctx* ctx = conv->ctx;
+  const plb_conv_desc& d = conv->d;
+  const size_t need = plb_conv_workspace_bytes(conv, batch);
+  if (need > kStaticScratchBytes)
+    return fail(PLB_E_INVALID,
+                "plb_conv_run_static: %d image(s) of this layer need %zu bytes of staging, the built-in "
+                "scratch holds %zu; use plb_conv_run or a smaller batch",
+                batch, need, kStaticScratchBytes);
+  PLB_REQUIRE(ctx->device >= 0 && ctx->device < 64, "device ordinal %d not supported here", ctx->device);
+  PLB_CUDA(cudaSetDevice(ctx->device));
+  if (g_static_scratch_addr[ctx->device] == nullptr) {
+    // first call on this device: resolve the device address of the array (the host-side name
+    // is not a device pointer)
+    void* addr = nullptr;
+    PLB_CUDA(cudaGetSymbolAddress(&addr, g_static_scratch));
+    g_static_scratch_addr[ctx->device] = addr;
+  }
+  unsigned char* base = static_cast<unsigned char*>(g_static_scratch_addr[ctx->device]);
+  const size_t x_bytes =
+      align_up(static_cast<size_t>(batch) * d.h * (conv->fold ? conv->wo : d.w) * conv->cin_pad, 256);
+  int8_t* xs = reinterpret_cast<int8_t*>(base);
+  void* ys = base + x_bytes;
+  // Both staging regions are written in full before they are read (the staging kernels also
+  // write the zero padding channels), so nothing of a previous call's contents is observed.
+  int rc;
+  if (conv->fold)
+    rc = fold_rows_launch(ctx, x, 0, xs, batch, d.cin, d.h, d.w, conv->wo, d.kw, d.stride_w, d.pad_left,
+                          d.dil_w, 1.f);
+  else
+    rc = nchw_to_nhwc_i8_launch(ctx, x, xs, batch, d.cin, d.h, d.w, conv->cin_pad);
+  if (rc) return rc;
+  const int mode = d.out_dtype == PLB_OUT_I8 ? OUT_I8 : OUT_F32;
+  OutSpec o = out_spec(conv, mode, ys);
+  if ((rc = conv_core(conv, xs, batch, o))) return rc;
+  return nhwc_to_nchw_launch(ctx, ys, y, batch, d.cout, conv->ho, conv->wo, mode == OUT_I8 ? 1 : 4);
 }
 
 int plb_conv_run_nhwc_add_relu(plb_conv* conv, const int8_t* x, const float* residual, float* y_f32,
