@@ -30,14 +30,15 @@ namespace plb {
 namespace {
 
 constexpr int kTileM = 128;
-constexpr int kMaxStages = 8;
+constexpr int kMaxStages = 16;
 constexpr int kEpilogueGroups = 4;              // groups of 4 warps (one per TMEM lane quadrant)
 constexpr int kEpilogueWarps = 4 * kEpilogueGroups;
 constexpr int kProducerWarp = kEpilogueWarps;
 constexpr int kMmaWarp = kEpilogueWarps + 1;
 constexpr int kThreads = 32 * (kEpilogueWarps + 2);
 constexpr int kMaxAccBufs = 4;
-constexpr int kCtrlBytes = 512;                 // barriers + tmem slot
+constexpr int kCtrlBytes = 1024;                // barriers + tmem slot
+constexpr int kMaxResidentB = 56 * 1024;        // filters up to this size stay in shared memory for the whole kernel
 constexpr uint32_t kWaitLimit = 1u << 22;      // polls before a wait is declared lost
 
 struct IgemmArgs {
@@ -48,6 +49,8 @@ struct IgemmArgs {
   int ho, wo, stride_h, stride_w, pad_t, pad_l, dil_h, dil_w;
   int tiles_n, num_tiles;
   int staging_bytes, staging_w_bytes;  // epilogue staging in front of the operand ring
+  int stage_b_warp;                    // bytes of int8 staging per epilogue warp
+  int resident_b;                      // whole filter of this CTA's channel tile kept in shared memory
   int out_mode, ldy;
   void* y;
   const float* scale;
@@ -492,19 +495,20 @@ __global__ void __launch_bounds__(kThreads, 1)
   extern __shared__ uint8_t smem_raw[];
   const uint32_t raw_addr = smem_u32(smem_raw);
   uint8_t* smem_al = smem_raw + (((raw_addr + 1023u) & ~1023u) - raw_addr);
-  // [epilogue staging: wide tiles, byte tiles][operand ring][barriers]
-  uint8_t* smem = smem_al + a.staging_bytes;
-
+  // [epilogue staging: wide tiles, byte tiles][resident filter][operand ring][barriers]
   const int stage_a = kTileM * a.kc;
   const int stage_b = a.bn * a.kc;
-  const int stage_bytes = stage_a + stage_b;
+  uint8_t* smem_bres = smem_al + a.staging_bytes;
+  uint8_t* smem = smem_bres + (a.resident_b ? a.ksteps * stage_b : 0);
+  const int stage_bytes = a.resident_b ? stage_a : stage_a + stage_b;
   uint8_t* ctrl = smem + a.stages * stage_bytes;
   uint64_t* full_bar = reinterpret_cast<uint64_t*>(ctrl);
   uint64_t* empty_bar = full_bar + kMaxStages;
   uint64_t* acc_full = empty_bar + kMaxStages;     // [4] accumulator buffer ready for its epilogue group(s)
   uint64_t* acc_empty = acc_full + kMaxAccBufs;    // [4] accumulator buffer drained
   uint64_t* res_bar = acc_empty + kMaxAccBufs;     // [16] one per epilogue warp: residual tile landed
-  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(res_bar + kEpilogueWarps);
+  uint64_t* bres_bar = res_bar + kEpilogueWarps;   // resident filter landed
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bres_bar + 1);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
 
   const int warp = threadIdx.x >> 5;
@@ -527,6 +531,7 @@ __global__ void __launch_bounds__(kThreads, 1)
       mbar_init(smem_u32(&acc_empty[b]), 4 * gpb);
     }
     for (int w = 0; w < kEpilogueWarps; ++w) mbar_init(smem_u32(&res_bar[w]), 1);
+    mbar_init(smem_u32(bres_bar), 1);
     *abort_flag = 0;
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     asm volatile("prefetch.tensormap [%0];" ::"l"(reinterpret_cast<uint64_t>(&tmA)) : "memory");
@@ -548,41 +553,65 @@ __global__ void __launch_bounds__(kThreads, 1)
 
   if (warp == kProducerWarp) {
     // ------------------------------------------------------------ TMA producer
+    // One thread issues every operand copy of this CTA, so the loop body is kept free of
+    // divisions: ring position, tap and channel-chunk counters advance incrementally.
     if (lane == 0) {
-      int ks_global = 0;
+      int s = 0;
+      uint32_t empty_parity = 1;  // a fresh barrier passes a wait on parity 1
       bool ok = true;
-      for (int tile = blockIdx.x; tile < a.num_tiles && ok; tile += gridDim.x) {
-        const int m0 = (tile / a.tiles_n) * kTileM;
-        const int n0 = (tile % a.tiles_n) * a.bn;
-        int cn = 0, ch = 0, cw = 0;
-        if (a.im2col) {
-          const int q = m0 % a.wo;
-          const int p = (m0 / a.wo) % a.ho;
-          cn = m0 / (a.wo * a.ho);
-          cw = q * a.stride_w - a.pad_l;
-          ch = p * a.stride_h - a.pad_t;
+      const uint32_t smem_base = smem_u32(smem);
+      if (a.resident_b) {
+        // small filter, one channel tile: fetch all of it once; the ring then carries activations only
+        const uint32_t bar = smem_u32(bres_bar);
+        mbar_expect_tx(bar, static_cast<uint32_t>(a.ksteps * stage_b));
+        for (int ks = 0; ks < a.ksteps; ++ks) {
+          const uint32_t dst = smem_u32(smem_bres) + ks * stage_b;
+          tma_load_2d(dst, &tmB, bar, ks * a.kc, 0);
         }
-        for (int ks = 0; ks < a.ksteps; ++ks, ++ks_global) {
-          const int s = ks_global % a.stages;
-          const uint32_t parity = ((ks_global / a.stages) & 1) ^ 1;
-          ok = mbar_wait(smem_u32(&empty_bar[s]), parity, abort_flag, a.status, FAULT_WAIT_EMPTY);
+      }
+      for (int tile = blockIdx.x; tile < a.num_tiles && ok; tile += gridDim.x) {
+        const int tile_m = tile / a.tiles_n;
+        const int m0 = tile_m * kTileM;
+        const int n0 = (tile - tile_m * a.tiles_n) * a.bn;
+        int q0 = 0, p0 = 0, cn = 0;
+        if (a.im2col) {
+          q0 = m0 % a.wo;
+          const int t = m0 / a.wo;
+          p0 = t % a.ho;
+          cn = t / a.ho;
+        }
+        const int cw = q0 * a.stride_w - a.pad_l;
+        const int ch = p0 * a.stride_h - a.pad_t;
+        int r = 0, sx = 0, cc = 0, kb = 0;  // filter row, filter column, channel chunk, K offset in B
+        for (int ks = 0; ks < a.ksteps; ++ks) {
+          ok = mbar_wait(smem_u32(&empty_bar[s]), empty_parity, abort_flag, a.status, FAULT_WAIT_EMPTY);
           if (!ok) break;
           const uint32_t bar = smem_u32(&full_bar[s]);
           mbar_expect_tx(bar, static_cast<uint32_t>(stage_bytes));
-          const uint32_t dst_a = smem_u32(smem + s * stage_bytes);
+          const uint32_t dst_a = smem_base + s * stage_bytes;
           const uint32_t dst_b = dst_a + stage_a;
-          const int tap = ks / a.cchunks;
-          const int c0 = (ks - tap * a.cchunks) * a.kc;
-          if (a.im2col) {
-            const int r = tap / a.kw;
-            const int sx = tap - r * a.kw;
-            tma_load_im2col_4d(dst_a, &tmA, bar, c0, cw, ch, cn,
-                               static_cast<uint16_t>(sx * a.dil_w),
-                               static_cast<uint16_t>(r * a.dil_h));
-          } else {
-            tma_load_2d(dst_a, &tmA, bar, c0, m0);
+          {
+            if (a.im2col) {
+              tma_load_im2col_4d(dst_a, &tmA, bar, cc * a.kc, cw, ch, cn,
+                                 static_cast<uint16_t>(sx * a.dil_w),
+                                 static_cast<uint16_t>(r * a.dil_h));
+            } else {
+              tma_load_2d(dst_a, &tmA, bar, kb, m0);
+            }
+            if (!a.resident_b) tma_load_2d(dst_b, &tmB, bar, kb, n0);
           }
-          tma_load_2d(dst_b, &tmB, bar, tap * a.cchunks * a.kc + c0, n0);
+          kb += a.kc;
+          if (++cc == a.cchunks) {
+            cc = 0;
+            if (++sx == a.kw) {
+              sx = 0;
+              ++r;
+            }
+          }
+          if (++s == a.stages) {
+            s = 0;
+            empty_parity ^= 1;
+          }
         }
       }
     }
@@ -594,29 +623,43 @@ __global__ void __launch_bounds__(kThreads, 1)
                              (static_cast<uint32_t>(a.bn >> 3) << 17) |
                              (static_cast<uint32_t>(kTileM >> 4) << 24);
       const int mma_per_stage = a.kc / 32;
-      int ks_global = 0, it = 0;
+      const uint32_t smem_base = smem_u32(smem);
+      const uint64_t desc_hi = make_smem_desc(0, a.kc) & 0xFFFFFFFF00000000ull;  // layout, stride: constant
+      const int nb_mask = nb - 1, nb_shift = nb == 4 ? 2 : 1;
+      int s = 0, it = 0;
+      uint32_t full_parity = 0;
       bool ok = true;
+      if (a.resident_b) {
+        ok = mbar_wait(smem_u32(bres_bar), 0, abort_flag, a.status, FAULT_WAIT_FULL);
+        tc_fence_after();
+      }
+      const uint32_t bres_base = smem_u32(smem_bres);
       for (int tile = blockIdx.x; tile < a.num_tiles && ok; tile += gridDim.x, ++it) {
-        const int buf = it % nb;
-        ok = mbar_wait(smem_u32(&acc_empty[buf]), ((it / nb) & 1) ^ 1, abort_flag, a.status,
+        const int buf = it & nb_mask;
+        ok = mbar_wait(smem_u32(&acc_empty[buf]), ((it >> nb_shift) & 1) ^ 1, abort_flag, a.status,
                        FAULT_WAIT_ACCUM);
         if (!ok) break;
         tc_fence_after();
         const uint32_t d_tmem = tmem_base + buf * acc_cols;
-        for (int ks = 0; ks < a.ksteps; ++ks, ++ks_global) {
-          const int s = ks_global % a.stages;
-          const uint32_t parity = (ks_global / a.stages) & 1;
-          ok = mbar_wait(smem_u32(&full_bar[s]), parity, abort_flag, a.status, FAULT_WAIT_FULL);
+        uint32_t accumulate = 0;
+        for (int ks = 0; ks < a.ksteps; ++ks) {
+          ok = mbar_wait(smem_u32(&full_bar[s]), full_parity, abort_flag, a.status, FAULT_WAIT_FULL);
           if (!ok) break;
           tc_fence_after();
-          const uint32_t addr_a = smem_u32(smem + s * stage_bytes);
-          const uint64_t adesc = make_smem_desc(addr_a, a.kc);
-          const uint64_t bdesc = make_smem_desc(addr_a + stage_a, a.kc);
+          const uint32_t addr_a = smem_base + s * stage_bytes;
+          const uint64_t adesc = desc_hi | (((addr_a >> 4) & 0x3FFFu) | (1u << 16));
+          const uint32_t addr_b = a.resident_b ? bres_base + ks * stage_b : addr_a + stage_a;
+          const uint64_t bdesc = desc_hi | (((addr_b >> 4) & 0x3FFFu) | (1u << 16));
           for (int j = 0; j < mma_per_stage; ++j) {
             // advance 32 bytes of K inside the swizzle span: +2 in the (addr >> 4) field
-            tc_mma_i8(d_tmem, adesc + 2u * j, bdesc + 2u * j, idesc, (ks | j) != 0 ? 1u : 0u);
+            tc_mma_i8(d_tmem, adesc + 2u * j, bdesc + 2u * j, idesc, accumulate);
+            accumulate = 1;
           }
           tc_commit(smem_u32(&empty_bar[s]));  // frees the stage when these MMAs retire
+          if (++s == a.stages) {
+            s = 0;
+            full_parity ^= 1;
+          }
         }
         tc_commit(smem_u32(&acc_full[buf]));  // accumulator complete (or drained on a fault)
       }
@@ -627,10 +670,11 @@ __global__ void __launch_bounds__(kThreads, 1)
     const int quad = warp & 3;       // TMEM lane quadrant this warp may read
     const int my_buf = group / gpb;  // the accumulator buffer this group drains
     const int col_par = group % gpb; // which part of its columns
+    const int nb_shift = nb == 4 ? 2 : 1;
     // staged I/O: this warp's staging tiles and bookkeeping
     const uint32_t st_w = smem_u32(smem_al) + warp * 4096;
     const int wq = a.bn / gpb;       // columns (= int8 bytes per row) this group owns in a tile
-    const uint32_t st_b = smem_u32(smem_al) + a.staging_w_bytes + warp * 4096;
+    const uint32_t st_b = smem_u32(smem_al) + a.staging_w_bytes + warp * a.stage_b_warp;
     const int b_swz = wq == 128 ? (lane & 7) : 0;
     const uint32_t my_res_bar = smem_u32(&res_bar[warp]);
     uint32_t res_phase = 0;
@@ -666,7 +710,7 @@ __global__ void __launch_bounds__(kThreads, 1)
             tma_load_2d(st_w, &tmRes, my_res_bar, n0 + c, row0);
           }
           if (!waited) {
-            ok = mbar_wait(smem_u32(&acc_full[my_buf]), (it / nb) & 1, abort_flag, a.status, FAULT_WAIT_ACCUM);
+            ok = mbar_wait(smem_u32(&acc_full[my_buf]), (it >> nb_shift) & 1, abort_flag, a.status, FAULT_WAIT_ACCUM);
             tc_fence_after();
             waited = true;
             if (!ok) break;
@@ -712,7 +756,7 @@ __global__ void __launch_bounds__(kThreads, 1)
             }
           }
           if (!waited) {
-            ok = mbar_wait(smem_u32(&acc_full[my_buf]), (it / nb) & 1, abort_flag, a.status, FAULT_WAIT_ACCUM);
+            ok = mbar_wait(smem_u32(&acc_full[my_buf]), (it >> nb_shift) & 1, abort_flag, a.status, FAULT_WAIT_ACCUM);
             tc_fence_after();
             waited = true;
             if (!ok) break;
@@ -724,7 +768,7 @@ __global__ void __launch_bounds__(kThreads, 1)
         }
       }
       if (!waited && ok) {  // nothing to do for this group in this tile: still consume the phase
-        ok = mbar_wait(smem_u32(&acc_full[my_buf]), (it / nb) & 1, abort_flag, a.status, FAULT_WAIT_ACCUM);
+        ok = mbar_wait(smem_u32(&acc_full[my_buf]), (it >> nb_shift) & 1, abort_flag, a.status, FAULT_WAIT_ACCUM);
         tc_fence_after();
       }
       // this warp no longer reads the buffer: let the MMA warp overwrite it
@@ -877,9 +921,20 @@ int igemm_tc_launch(plb_ctx* ctx, const IgemmProblem& p) {
     staged = false;
   }
   a.staging_w_bytes = staged && want_w ? kEpilogueWarps * 4096 : 0;
-  a.staging_bytes = a.staging_w_bytes + (staged && want_b ? kEpilogueWarps * 4096 : 0);
+  {
+    const int acc_cols_h = bn <= 32 ? 32 : (bn <= 64 ? 64 : (bn <= 128 ? 128 : 256));
+    const int wq_h = bn / (acc_cols_h <= 128 ? 1 : 2);
+    // 32 rows of wq bytes per warp; 128-byte-swizzled tiles (wq = 128) need 1 KiB alignment, which 4 KiB keeps
+    a.stage_b_warp = staged && want_b ? (wq_h == 128 ? 4096 : 32 * wq_h) : 0;
+  }
+  a.staging_bytes = (a.staging_w_bytes + kEpilogueWarps * a.stage_b_warp + 1023) / 1024 * 1024;
+  const int tiles_n_h = (p.cout + bn - 1) / bn;
+  const int resident_bytes = a.ksteps * bn * a.kc;
+  a.resident_b = env_int("PLB_TC_RESIDENT", 1) != 0 && tiles_n_h == 1 && resident_bytes <= kMaxResidentB &&
+                 tiles_m > ctx->sm_count;  // worth it only when a CTA walks several tiles
+  const int ring_stage_bytes = a.resident_b ? kTileM * a.kc : stage_bytes;
   // one CTA per SM: spend (almost) all remaining shared memory on the operand ring
-  int stages = (224 * 1024 - a.staging_bytes - kCtrlBytes) / stage_bytes;
+  int stages = (225 * 1024 - a.staging_bytes - kCtrlBytes - (a.resident_b ? resident_bytes : 0)) / ring_stage_bytes;
   stages = env_int("PLB_TC_STAGES", stages);
   if (stages > kMaxStages) stages = kMaxStages;
   if (stages < 2) stages = 2;
@@ -966,8 +1021,8 @@ int igemm_tc_launch(plb_ctx* ctx, const IgemmProblem& p) {
     if (r != CUDA_SUCCESS) return fail(PLB_E_CUDA, "cuTensorMapEncodeTiled(output) failed: %d", (int)r);
   }
 
-  const size_t smem = static_cast<size_t>(a.staging_bytes) + static_cast<size_t>(stages) * stage_bytes +
-                      kCtrlBytes + 1024;
+  const size_t smem = static_cast<size_t>(a.staging_bytes) + (a.resident_b ? resident_bytes : 0) +
+                      static_cast<size_t>(stages) * ring_stage_bytes + kCtrlBytes + 1024;
   if (smem > 227 * 1024) return fail(PLB_E_UNSUPPORTED, "pipeline needs %zu bytes of shared memory", smem);
   IgemmKernel kernel = pick_kernel(p.out_mode, p.epi.act, staged);
   // the attribute belongs to (function, device): remember which pairs have been configured

@@ -137,6 +137,144 @@ __global__ void __launch_bounds__(kBlock)
     if (c0 + j < g.cout) emit(o, m, c0 + j, acc[j]);
 }
 
+// ------------------------------------------------------------------ depthwise 3x3, register tiled
+// One thread = 4 consecutive channels x a 2 x 4 patch of output pixels.  Every input word is
+// loaded and unpacked once and feeds all taps of all outputs it belongs to; the arithmetic is
+// fp32 FMA on integer values (|sum| <= 9*127*127 < 2^24, so the sums are exact and
+// (float)acc is the same number the int32 path would convert), which runs at twice the issue
+// rate of integer multiply-add.  Bytes are unpacked with one byte-permute into the mantissa
+// of 2^23 and one subtraction (no int->float conversions).
+constexpr float kByteMagic = 8388608.f + 128.f;
+
+__device__ __forceinline__ void unpack4(uint32_t word, float (&out)[4]) {
+  const uint32_t u = word ^ 0x80808080u;  // bias to unsigned
+  out[0] = __uint_as_float(__byte_perm(u, 0x4B000000u, 0x7540)) - kByteMagic;
+  out[1] = __uint_as_float(__byte_perm(u, 0x4B000000u, 0x7541)) - kByteMagic;
+  out[2] = __uint_as_float(__byte_perm(u, 0x4B000000u, 0x7542)) - kByteMagic;
+  out[3] = __uint_as_float(__byte_perm(u, 0x4B000000u, 0x7543)) - kByteMagic;
+}
+
+template <int ACT>
+__device__ __forceinline__ float dw_act(float v, float alpha) {
+  if (ACT == PLB_ACT_RELU) return fmaxf(v, 0.f);
+  if (ACT == PLB_ACT_RELU6) return fminf(fmaxf(v, 0.f), alpha);
+  if (ACT == PLB_ACT_LEAKY) return v <= 0.f ? alpha * v : v;
+  return v;
+}
+
+template <int S, int ACT, bool OUT_IS_I8>
+__global__ void __launch_bounds__(kBlock)
+    dwconv3x3_kernel(const ConvGeom g, const int8_t* __restrict__ x, const int8_t* __restrict__ w,
+                     const OutDev o, const int cquads, const int tiles_x, const int tiles_y, const long total) {
+  pdl_sync_with_previous_kernel();
+  constexpr int TH = S == 1 ? 2 : 1, TW = 4;  // keeps the register count of both strides near 120
+  constexpr int IH = (TH - 1) * S + 3, IW = (TW - 1) * S + 3;
+  long idx = static_cast<long>(blockIdx.x) * kBlock + threadIdx.x;
+  if (idx >= total) return;
+  const int cq = static_cast<int>(idx % cquads);
+  idx /= cquads;
+  const int tx = static_cast<int>(idx % tiles_x);
+  idx /= tiles_x;
+  const int ty = static_cast<int>(idx % tiles_y);
+  const long n = idx / tiles_y;
+  const int oh0 = ty * TH, ow0 = tx * TW;
+  const int c0 = cq * 4;
+
+  float wf[9][4];
+#pragma unroll
+  for (int t = 0; t < 9; ++t)
+    unpack4(*reinterpret_cast<const uint32_t*>(w + static_cast<long>(t) * g.cg_pad + c0), wf[t]);
+
+  float acc[TH][TW][4];
+#pragma unroll
+  for (int a = 0; a < TH; ++a)
+#pragma unroll
+    for (int b = 0; b < TW; ++b)
+#pragma unroll
+      for (int c = 0; c < 4; ++c) acc[a][b][c] = 0.f;
+
+  const int ih0 = oh0 * S - g.pad_t, iw0 = ow0 * S - g.pad_l;
+  const int8_t* xn = x + n * g.h * static_cast<long>(g.w) * g.cin_stride + c0;
+  // all loads of the patch are issued before any arithmetic: one register per 4 input bytes
+  uint32_t raw[IH][IW];
+#pragma unroll
+  for (int iy = 0; iy < IH; ++iy) {
+    const int ih = ih0 + iy;
+    const bool row_ok = ih >= 0 && ih < g.h;
+#pragma unroll
+    for (int ix = 0; ix < IW; ++ix) {
+      const int iw = iw0 + ix;
+      raw[iy][ix] = 0;
+      if (row_ok && iw >= 0 && iw < g.w)
+        raw[iy][ix] = __ldg(reinterpret_cast<const uint32_t*>(xn + (static_cast<long>(ih) * g.w + iw) * g.cin_stride));
+    }
+  }
+#pragma unroll
+  for (int iy = 0; iy < IH; ++iy) {
+    float in[IW][4];
+#pragma unroll
+    for (int ix = 0; ix < IW; ++ix) unpack4(raw[iy][ix], in[ix]);
+#pragma unroll
+    for (int oy = 0; oy < TH; ++oy) {
+      const int r = iy - oy * S;  // filter row this input row meets for output row oy
+      if (r < 0 || r > 2) continue;
+#pragma unroll
+      for (int ox = 0; ox < TW; ++ox)
+#pragma unroll
+        for (int sx = 0; sx < 3; ++sx)
+#pragma unroll
+          for (int c = 0; c < 4; ++c) acc[oy][ox][c] = fmaf(in[ox * S + sx][c], wf[r * 3 + sx][c], acc[oy][ox][c]);
+    }
+  }
+
+  const float4 sc = *reinterpret_cast<const float4*>(o.scale + c0);
+  const float4 bi = *reinterpret_cast<const float4*>(o.bias + c0);
+  const float alpha = OUT_IS_I8 && ACT == PLB_ACT_RELU6 ? fminf(o.alpha, 127.f) : o.alpha;
+#pragma unroll
+  for (int oy = 0; oy < TH; ++oy) {
+    const int oh = oh0 + oy;
+    if (oh >= g.ho) continue;
+#pragma unroll
+    for (int ox = 0; ox < TW; ++ox) {
+      const int ow = ow0 + ox;
+      if (ow >= g.wo) continue;
+      const long m = (n * g.ho + oh) * g.wo + ow;
+      float v[4] = {fmaf(acc[oy][ox][0], sc.x, bi.x), fmaf(acc[oy][ox][1], sc.y, bi.y),
+                    fmaf(acc[oy][ox][2], sc.z, bi.z), fmaf(acc[oy][ox][3], sc.w, bi.w)};
+      if (OUT_IS_I8) {
+        uint32_t q[4];
+#pragma unroll
+        for (int c = 0; c < 4; ++c) {
+          float t = v[c];
+          if (ACT == PLB_ACT_NONE) t = fminf(fmaxf(t, -127.f), 127.f);
+          else if (ACT == PLB_ACT_RELU) t = fminf(fmaxf(t, 0.f), 127.f);
+          else if (ACT == PLB_ACT_RELU6) t = fminf(fmaxf(t, 0.f), alpha);
+          else { t = t <= 0.f ? alpha * t : t; t = fminf(fmaxf(t, -127.f), 127.f); }
+          q[c] = __float_as_uint(t + 12582912.f);  // round to nearest even, result in the low byte
+        }
+        *reinterpret_cast<uint32_t*>(static_cast<int8_t*>(o.y) + m * o.ldy + c0) =
+            __byte_perm(__byte_perm(q[0], q[1], 0x0040), __byte_perm(q[2], q[3], 0x0040), 0x5410);
+      } else {
+        *reinterpret_cast<float4*>(static_cast<float*>(o.y) + m * o.ldy + c0) =
+            make_float4(dw_act<ACT>(v[0], alpha), dw_act<ACT>(v[1], alpha), dw_act<ACT>(v[2], alpha),
+                        dw_act<ACT>(v[3], alpha));
+      }
+    }
+  }
+}
+
+typedef void (*DwKernel)(const ConvGeom, const int8_t*, const int8_t*, const OutDev, const int, const int,
+                         const int, const long);
+template <int S, bool I8>
+DwKernel pick_dw_act(int act) {
+  switch (act) {
+    case PLB_ACT_RELU: return dwconv3x3_kernel<S, PLB_ACT_RELU, I8>;
+    case PLB_ACT_RELU6: return dwconv3x3_kernel<S, PLB_ACT_RELU6, I8>;
+    case PLB_ACT_LEAKY: return dwconv3x3_kernel<S, PLB_ACT_LEAKY, I8>;
+    default: return dwconv3x3_kernel<S, PLB_ACT_NONE, I8>;
+  }
+}
+
 // ------------------------------------------------------------------ sparse 1x1 convolution
 // NCHW.  grid = (pixel blocks, cout, batch).  Each thread owns VEC consecutive pixels of one
 // output channel and walks that channel's non-zero weights in ascending input channel, the
@@ -254,30 +392,37 @@ __global__ void __launch_bounds__(kBlock)
   }
 }
 
-// Row-folded staging for stem layers with few input channels (cin * kw <= 32):
-// y[n][h][q][s*cin + c] = x[n][c][h][q*stride_w - pad_l + s*dil_w] (0 outside the image, 0 for
-// the unused tail of the 32-byte pixel).  The kw taps of one filter row then sit in the
-// channel dimension and the convolution becomes kh x 1 with 32 input channels.
+// Folded staging for stem layers with few input channels (cin * kw <= 32).  One staged pixel
+// (t, q) holds, for fh = stride_h consecutive input rows, the kw taps of the filter row and the
+// input channels:  y[n][t][q][e*32 + s*cin + c] = x[n][c][t*fh - pad_t + e][q*stride_w - pad_l + s*dil_w]
+// (0 outside the image and in the unused tail of each 32-byte group).  The convolution then
+// becomes ceil(kh/fh) x 1, stride 1, no padding, over fh*32 "channels": output row p reads
+// staged rows p .. p + ceil(kh/fh) - 1.
 template <typename T>
 __global__ void __launch_bounds__(kBlock)
-    fold_rows_kernel(const T* __restrict__ x, int8_t* __restrict__ y, int c, int h, int w, int wo, int kw,
-                     int stride_w, int pad_l, int dil_w, float inv, long total) {
+    fold_rows_kernel(const T* __restrict__ x, int8_t* __restrict__ y, int c, int h, int w, int ht, int wo,
+                     int kw, int fh, int stride_w, int pad_t, int pad_l, int dil_w, float inv, long total) {
   pdl_sync_with_previous_kernel();
   const long idx = static_cast<long>(blockIdx.x) * kBlock + threadIdx.x;
-  if (idx >= total) return;
-  const int q = static_cast<int>(idx % wo);
-  const int hh = static_cast<int>((idx / wo) % h);
-  const long n = idx / (static_cast<long>(wo) * h);
+  if (idx >= total) return;  // one thread per (n, t, q, e)
+  const int e = static_cast<int>(idx % fh);
+  const long pix = idx / fh;
+  const int q = static_cast<int>(pix % wo);
+  const int t = static_cast<int>((pix / wo) % ht);
+  const long n = pix / (static_cast<long>(wo) * ht);
   uint32_t words[8] = {0, 0, 0, 0, 0, 0, 0, 0};
-  const int w0 = q * stride_w - pad_l;
-  for (int s = 0; s < kw; ++s) {
-    const int iw = w0 + s * dil_w;
-    if (iw < 0 || iw >= w) continue;
-    for (int cc = 0; cc < c; ++cc) {
-      const T raw = x[((n * c + cc) * h + hh) * static_cast<long>(w) + iw];
-      const int v = sizeof(T) == 1 ? static_cast<int>(raw) : calib_i8(static_cast<float>(raw), inv);
-      const int j = s * c + cc;
-      words[j >> 2] |= static_cast<uint32_t>(v & 0xff) << (8 * (j & 3));
+  const int hh = t * fh - pad_t + e;
+  if (hh >= 0 && hh < h) {
+    const int w0 = q * stride_w - pad_l;
+    for (int s = 0; s < kw; ++s) {
+      const int iw = w0 + s * dil_w;
+      if (iw < 0 || iw >= w) continue;
+      for (int cc = 0; cc < c; ++cc) {
+        const T raw = x[((n * c + cc) * h + hh) * static_cast<long>(w) + iw];
+        const int v = sizeof(T) == 1 ? static_cast<int>(raw) : calib_i8(static_cast<float>(raw), inv);
+        const int j = s * c + cc;
+        words[j >> 2] |= static_cast<uint32_t>(v & 0xff) << (8 * (j & 3));
+      }
     }
   }
   uint4* dst = reinterpret_cast<uint4*>(y + idx * 32);
@@ -328,6 +473,35 @@ __global__ void __launch_bounds__(kBlock)
   reinterpret_cast<uint32_t*>(y)[m * c4 + cq] = best;
 }
 
+// 16 channels (one 128-bit word) per thread
+__global__ void __launch_bounds__(kBlock)
+    maxpool_nhwc_i8_v16_kernel(const int8_t* __restrict__ x, int8_t* __restrict__ y, int c16, int h, int w,
+                               int ho, int wo, int k, int stride, int pad, long total) {
+  pdl_sync_with_previous_kernel();
+  const long idx = static_cast<long>(blockIdx.x) * kBlock + threadIdx.x;
+  if (idx >= total) return;
+  const int cq = static_cast<int>(idx % c16);
+  const long m = idx / c16;
+  const int ow = static_cast<int>(m % wo);
+  const int oh = static_cast<int>((m / wo) % ho);
+  const long n = m / (static_cast<long>(wo) * ho);
+  uint4 best = make_uint4(0x80808080u, 0x80808080u, 0x80808080u, 0x80808080u);
+  for (int r = 0; r < k; ++r) {
+    const int ih = oh * stride - pad + r;
+    if (ih < 0 || ih >= h) continue;
+    for (int s = 0; s < k; ++s) {
+      const int iw = ow * stride - pad + s;
+      if (iw < 0 || iw >= w) continue;
+      const uint4 v = reinterpret_cast<const uint4*>(x)[((n * h + ih) * w + iw) * c16 + cq];
+      best.x = __vmaxs4(best.x, v.x);
+      best.y = __vmaxs4(best.y, v.y);
+      best.z = __vmaxs4(best.z, v.z);
+      best.w = __vmaxs4(best.w, v.w);
+    }
+  }
+  reinterpret_cast<uint4*>(y)[m * c16 + cq] = best;
+}
+
 // x [n,hw,c] -> y [n,c] = (sum over hw in ascending order) / hw; optional calib to int8.
 __global__ void global_avgpool_kernel(const float* __restrict__ x, float* __restrict__ y,
                                       int8_t* __restrict__ q, int hw, int c, float inv, long total) {
@@ -360,6 +534,22 @@ int conv_direct_launch(plb_ctx* ctx, const ConvGeom& g, const int8_t* x, const i
 
 int dwconv_launch(plb_ctx* ctx, const ConvGeom& g, const int8_t* x, const int8_t* w_tc,
                   const OutSpec& out) {
+  const bool tiled = g.kh == 3 && g.kw == 3 && g.dil_h == 1 && g.dil_w == 1 && g.stride_h == g.stride_w &&
+                     (g.stride_h == 1 || g.stride_h == 2) && (out.mode == OUT_I8 || out.mode == OUT_F32) &&
+                     g.cout % 4 == 0 && out.ldy % 4 == 0 && g.cin_stride % 4 == 0 && g.cg_pad % 4 == 0;
+  if (tiled) {
+    const int cq = g.cout / 4;
+    const int tiles_x = (g.wo + 3) / 4, tiles_y = g.stride_h == 1 ? (g.ho + 1) / 2 : g.ho;
+    const long total = static_cast<long>(g.batch) * tiles_y * tiles_x * cq;
+    if (total == 0) return PLB_OK;
+    const bool i8 = out.mode == OUT_I8;
+    DwKernel k = g.stride_h == 1 ? (i8 ? pick_dw_act<1, true>(out.epi.act) : pick_dw_act<1, false>(out.epi.act))
+                                 : (i8 ? pick_dw_act<2, true>(out.epi.act) : pick_dw_act<2, false>(out.epi.act));
+    PLB_CUDA(launch_kernel(k, dim3(blocks_for(total)), dim3(kBlock), 0, ctx->stream, g, x, w_tc, to_dev(out),
+                           cq, tiles_x, tiles_y, total));
+    ctx->launches++;
+    return PLB_OK;
+  }
   const int cquads = (g.cout + 3) / 4;
   const long total = static_cast<long>(g.batch) * g.ho * g.wo * cquads;
   if (total == 0) return PLB_OK;
@@ -436,15 +626,19 @@ int calib_nchw_f32_to_nhwc_i8_launch(plb_ctx* ctx, const float* x, int8_t* y, in
 }
 
 int fold_rows_launch(plb_ctx* ctx, const void* x, int x_is_f32, int8_t* y, int n, int c, int h, int w,
-                     int wo, int kw, int stride_w, int pad_l, int dil_w, float scale) {
-  const long total = static_cast<long>(n) * h * wo;
+                     int ht, int wo, int kw, int fh, int stride_w, int pad_t, int pad_l, int dil_w,
+                     float scale) {
+  const long total = static_cast<long>(n) * ht * wo * fh;
   if (total == 0) return PLB_OK;
   if (c * kw > 32) return fail(PLB_E_INVALID, "row folding needs cin * kw <= 32");
   if (x_is_f32)
-    PLB_CUDA(launch_kernel(fold_rows_kernel<float>, dim3(blocks_for(total)), dim3(kBlock), 0, ctx->stream, static_cast<const float*>(x), y, c, h, w, wo, kw, stride_w, pad_l, dil_w, 1.f / scale, total));
+    PLB_CUDA(launch_kernel(fold_rows_kernel<float>, dim3(blocks_for(total)), dim3(kBlock), 0, ctx->stream,
+                           static_cast<const float*>(x), y, c, h, w, ht, wo, kw, fh, stride_w, pad_t, pad_l,
+                           dil_w, 1.f / scale, total));
   else
-    PLB_CUDA(launch_kernel(fold_rows_kernel<int8_t>, dim3(blocks_for(total)), dim3(kBlock), 0, ctx->stream, static_cast<const int8_t*>(x), y, c, h, w, wo, kw, stride_w, pad_l, dil_w, 1.f, total));
-  PLB_CUDA(cudaGetLastError());
+    PLB_CUDA(launch_kernel(fold_rows_kernel<int8_t>, dim3(blocks_for(total)), dim3(kBlock), 0, ctx->stream,
+                           static_cast<const int8_t*>(x), y, c, h, w, ht, wo, kw, fh, stride_w, pad_t, pad_l,
+                           dil_w, 1.f, total));
   ctx->launches++;
   return PLB_OK;
 }
@@ -469,6 +663,14 @@ int maxpool_nhwc_i8_launch(plb_ctx* ctx, const int8_t* x, int8_t* y, int n, int 
                            int k, int stride, int pad) {
   if (c % 4) return fail(PLB_E_UNSUPPORTED, "max pool needs a channel count that is a multiple of 4");
   const int ho = (h + 2 * pad - k) / stride + 1, wo = (w + 2 * pad - k) / stride + 1;
+  if (c % 16 == 0 && (reinterpret_cast<uintptr_t>(x) & 15) == 0 && (reinterpret_cast<uintptr_t>(y) & 15) == 0) {
+    const long total16 = static_cast<long>(n) * ho * wo * (c / 16);
+    if (total16 == 0) return PLB_OK;
+    PLB_CUDA(launch_kernel(maxpool_nhwc_i8_v16_kernel, dim3(blocks_for(total16)), dim3(kBlock), 0, ctx->stream,
+                           x, y, c / 16, h, w, ho, wo, k, stride, pad, total16));
+    ctx->launches++;
+    return PLB_OK;
+  }
   const long total = static_cast<long>(n) * ho * wo * (c / 4);
   if (total == 0) return PLB_OK;
   PLB_CUDA(launch_kernel(maxpool_nhwc_i8_kernel, dim3(blocks_for(total)), dim3(kBlock), 0, ctx->stream, x, y, c / 4, h, w, ho, wo, k, stride, pad, total));

@@ -49,9 +49,11 @@ int calib_f32_to_i8_launch(plb_ctx* ctx, const float* x, int8_t* q, size_t n, fl
 int calib_i8_to_f32_launch(plb_ctx* ctx, const int8_t* q, float* y, size_t n, float scale);
 int nchw_to_nhwc_i8_launch(plb_ctx* ctx, const int8_t* x, int8_t* y, int n, int c, int h, int w,
                            int cpad);
-// Stem staging: int8 or fp32 (quantised with `scale`) NCHW -> row-folded [n,h,wo,32] int8.
+// Stem staging: int8 or fp32 (quantised with `scale`) NCHW -> folded [n, ht, wo, fh*32] int8
+// (fh input rows x kw taps x cin channels per staged pixel; see fold_rows_kernel).
 int fold_rows_launch(plb_ctx* ctx, const void* x, int x_is_f32, int8_t* y, int n, int c, int h, int w,
-                     int wo, int kw, int stride_w, int pad_l, int dil_w, float scale);
+                     int ht, int wo, int kw, int fh, int stride_w, int pad_t, int pad_l, int dil_w,
+                     float scale);
 int nhwc_to_nchw_launch(plb_ctx* ctx, const void* x, void* y, int n, int c, int h, int w,
                         int elem_bytes);
 int calib_nchw_f32_to_nhwc_i8_launch(plb_ctx* ctx, const float* x, int8_t* y, int n, int c, int h,

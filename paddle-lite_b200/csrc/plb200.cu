@@ -113,7 +113,10 @@ struct plb_conv {
   plb_conv_desc d;
   int ho = 0, wo = 0;
   int kind = 0;        // 0 tensor core, 1 direct, 2 depthwise
-  bool fold = false;   // stem layer: the kw taps of a filter row are folded into the channels
+  bool fold = false;   // stem layer: kw taps x fold_h rows of the filter are folded into the channels
+  int fold_h = 1;      // input rows per staged pixel (= stride_h)
+  int fold_kh = 0;     // filter rows of the folded convolution, ceil(kh / fold_h)
+  int fold_ht = 0;     // rows of the staged tensor, ho + fold_kh - 1
   int cin_pad = 0;     // channel stride of the NHWC staging input
   int cg_pad = 0;      // filter row length per tap
   DeviceBuf w;         // repacked filter
@@ -250,20 +253,24 @@ int plb_conv_prepare(plb_ctx* ctx, const plb_conv_desc* desc, const int8_t* filt
     for (int ch = 0; ch < d.cout; ++ch)
       for (int t = 0; t < taps; ++t) packed[static_cast<size_t>(t) * c->cg_pad + ch] = filter_h[ch * taps + t];
   } else if (d.groups == 1 && d.impl != PLB_IMPL_DIRECT && d.kw > 1 && d.cin * d.kw <= 32 &&
-             d.stride_w <= 8) {
+             d.stride_w <= 8 && d.dil_h == 1 && (d.stride_h == 1 || d.stride_h == 2 || d.stride_h == 4)) {
     // stem layer (e.g. RGB input): fold the kw taps of each filter row into the channel
     // dimension, [cout][kh][s*cin + c], and run a kh x 1 convolution over staged rows
     c->kind = 0;
     c->fold = true;
-    c->cin_pad = 32;
-    c->cg_pad = 32;
-    packed.assign(static_cast<size_t>(d.cout) * d.kh * 32, 0);
+    c->fold_h = d.stride_h;
+    c->fold_kh = (d.kh + c->fold_h - 1) / c->fold_h;
+    c->fold_ht = ho + c->fold_kh - 1;
+    c->cin_pad = 32 * c->fold_h;
+    c->cg_pad = c->cin_pad;
+    // [cout][j][e*32 + s*cin + ci] = filter[co][ci][r = j*fold_h + e][s], zero for r >= kh
+    packed.assign(static_cast<size_t>(d.cout) * c->fold_kh * c->cin_pad, 0);
     for (int co = 0; co < d.cout; ++co)
       for (int ci = 0; ci < d.cin; ++ci)
         for (int r = 0; r < d.kh; ++r)
           for (int sx = 0; sx < d.kw; ++sx)
-            packed[(static_cast<size_t>(co) * d.kh + r) * 32 + sx * d.cin + ci] =
-                filter_h[((static_cast<size_t>(co) * d.cin + ci) * d.kh + r) * d.kw + sx];
+            packed[(static_cast<size_t>(co) * c->fold_kh + r / c->fold_h) * c->cin_pad + (r % c->fold_h) * 32 +
+                   sx * d.cin + ci] = filter_h[((static_cast<size_t>(co) * d.cin + ci) * d.kh + r) * d.kw + sx];
   } else if (d.groups == 1) {
     c->cin_pad = static_cast<int>(align_up(d.cin, 32));
     c->cg_pad = c->cin_pad;
@@ -331,10 +338,16 @@ void plb_conv_destroy(plb_conv* conv) {
   delete conv;
 }
 
+// bytes of the staged (channels-last or row-folded) input of `batch` images
+static size_t staged_input_bytes(const plb_conv* conv, int batch) {
+  const size_t pixels = conv->fold ? static_cast<size_t>(conv->fold_ht) * conv->wo
+                                   : static_cast<size_t>(conv->d.h) * conv->d.w;
+  return align_up(static_cast<size_t>(batch) * pixels * conv->cin_pad, 256);
+}
+
 size_t plb_conv_workspace_bytes(const plb_conv* conv, int batch) {
   if (!conv || batch <= 0) return 0;
-  const size_t x_bytes = align_up(
-      static_cast<size_t>(batch) * conv->d.h * (conv->fold ? conv->wo : conv->d.w) * conv->cin_pad, 256);
+  const size_t x_bytes = staged_input_bytes(conv, batch);
   const size_t y_bytes = align_up(static_cast<size_t>(batch) * conv->ho * conv->wo * conv->d.cout * 4, 256);
   return x_bytes + y_bytes;
 }
@@ -358,8 +371,12 @@ int conv_core(plb_conv* c, const int8_t* x, int batch, const OutSpec& out) {
     p.kh = d.kh; p.kw = d.kw; p.stride_h = d.stride_h; p.stride_w = d.stride_w;
     p.pad_t = d.pad_top; p.pad_b = d.pad_bottom; p.pad_l = d.pad_left; p.pad_r = d.pad_right;
     p.dil_h = d.dil_h; p.dil_w = d.dil_w;
-    if (c->fold) {  // x is the row-folded staging tensor [batch, h, wo, 32]
-      p.w = c->wo; p.kw = 1; p.stride_w = 1; p.pad_l = 0; p.pad_r = 0; p.dil_w = 1;
+    if (c->fold) {  // x is the folded staging tensor [batch, fold_ht, wo, 32*fold_h]: plain kh' x 1 convolution
+      p.h = c->fold_ht; p.w = c->wo;
+      p.kh = c->fold_kh; p.kw = 1;
+      p.stride_h = 1; p.stride_w = 1;
+      p.pad_t = p.pad_b = p.pad_l = p.pad_r = 0;
+      p.dil_h = 1; p.dil_w = 1;
     }
     p.ho = c->ho; p.wo = c->wo;
     p.m_total = batch * c->ho * c->wo;
@@ -401,15 +418,14 @@ int conv_run_nchw(plb_conv* c, const int8_t* x, void* y, int batch, int mode) {
   plb_ctx* ctx = c->ctx;
   const plb_conv_desc& d = c->d;
   PLB_CUDA(cudaSetDevice(ctx->device));
-  const size_t x_bytes =
-      align_up(static_cast<size_t>(batch) * d.h * (c->fold ? c->wo : d.w) * c->cin_pad, 256);
+  const size_t x_bytes = staged_input_bytes(c, batch);
   int rc = ctx->reserve(plb_conv_workspace_bytes(c, batch));
   if (rc) return rc;
   int8_t* xs = static_cast<int8_t*>(ctx->ws);
   void* ys = static_cast<uint8_t*>(ctx->ws) + x_bytes;
   if (c->fold)
-    rc = fold_rows_launch(ctx, x, 0, xs, batch, d.cin, d.h, d.w, c->wo, d.kw, d.stride_w, d.pad_left,
-                          d.dil_w, 1.f);
+    rc = fold_rows_launch(ctx, x, 0, xs, batch, d.cin, d.h, d.w, c->fold_ht, c->wo, d.kw, c->fold_h,
+                          d.stride_w, d.pad_top, d.pad_left, d.dil_w, 1.f);
   else
     rc = nchw_to_nhwc_i8_launch(ctx, x, xs, batch, d.cin, d.h, d.w, c->cin_pad);
   if (rc) return rc;
@@ -460,14 +476,13 @@ int plb_conv_run_image_f32(plb_conv* conv, const float* x, void* y, int batch) {
   plb_ctx* ctx = conv->ctx;
   const plb_conv_desc& d = conv->d;
   PLB_CUDA(cudaSetDevice(ctx->device));
-  const size_t x_bytes =
-      align_up(static_cast<size_t>(batch) * d.h * (conv->fold ? conv->wo : d.w) * conv->cin_pad, 256);
+  const size_t x_bytes = staged_input_bytes(conv, batch);
   int rc = ctx->reserve(x_bytes);
   if (rc) return rc;
   int8_t* xs = static_cast<int8_t*>(ctx->ws);
   if (conv->fold)
-    rc = fold_rows_launch(ctx, x, 1, xs, batch, d.cin, d.h, d.w, conv->wo, d.kw, d.stride_w, d.pad_left,
-                          d.dil_w, d.in_scale);
+    rc = fold_rows_launch(ctx, x, 1, xs, batch, d.cin, d.h, d.w, conv->fold_ht, conv->wo, d.kw, conv->fold_h,
+                          d.stride_w, d.pad_top, d.pad_left, d.dil_w, d.in_scale);
   else
     rc = calib_nchw_f32_to_nhwc_i8_launch(ctx, x, xs, batch, d.cin, d.h, d.w, conv->cin_pad, d.in_scale);
   if (rc) return rc;
@@ -498,16 +513,15 @@ int plb_conv_run_static(plb_conv* conv, const int8_t* x, void* y, int batch) {
     g_static_scratch_addr[ctx->device] = addr;
   }
   unsigned char* base = static_cast<unsigned char*>(g_static_scratch_addr[ctx->device]);
-  const size_t x_bytes =
-      align_up(static_cast<size_t>(batch) * d.h * (conv->fold ? conv->wo : d.w) * conv->cin_pad, 256);
+  const size_t x_bytes = staged_input_bytes(conv, batch);
   int8_t* xs = reinterpret_cast<int8_t*>(base);
   void* ys = base + x_bytes;
   // Both staging regions are written in full before they are read (the staging kernels also
   // write the zero padding channels), so nothing of a previous call's contents is observed.
   int rc;
   if (conv->fold)
-    rc = fold_rows_launch(ctx, x, 0, xs, batch, d.cin, d.h, d.w, conv->wo, d.kw, d.stride_w, d.pad_left,
-                          d.dil_w, 1.f);
+    rc = fold_rows_launch(ctx, x, 0, xs, batch, d.cin, d.h, d.w, conv->fold_ht, conv->wo, d.kw, conv->fold_h,
+                          d.stride_w, d.pad_top, d.pad_left, d.dil_w, 1.f);
   else
     rc = nchw_to_nhwc_i8_launch(ctx, x, xs, batch, d.cin, d.h, d.w, conv->cin_pad);
   if (rc) return rc;

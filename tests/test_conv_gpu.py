@@ -169,12 +169,15 @@ def test_nhwc_entry_and_fused_add_relu(plb, ctx):
     assert np.array_equal(yq.cpu().numpy().transpose(0, 3, 1, 2), q_ref)
 
 
-@pytest.mark.parametrize("cin,k,s,p", [(3, 7, 2, 3), (3, 3, 2, 1), (4, 5, 1, 2), (16, 3, 1, 1)])
-def test_image_entry(plb, ctx, cin, k, s, p):
+@pytest.mark.parametrize("cin,k,s,p,hw", [(3, 7, 2, 3, (37, 41)), (3, 3, 2, 1, (37, 41)), (4, 5, 1, 2, (37, 41)),
+                                          (16, 3, 1, 1, (37, 41)), (3, 7, 2, 3, (64, 48)), (3, 3, 2, 1, (50, 32)),
+                                          (3, 7, 2, 3, (224, 224))])
+def test_image_entry(plb, ctx, cin, k, s, p, hw):
     """fp32 NCHW image -> calib -> first layer, channels-last output; stems with cin*kw <= 32 take
-    the row-folded staging, the last case the plain one."""
+    the row-folded staging (pre-swizzled and fed by bulk copies when the output width is a
+    multiple of 8, as in the last three cases), (16,3,1,1) the plain one."""
     rng = np.random.default_rng(cin * 10 + k)
-    img = rng.standard_normal((3, cin, 37, 41)).astype(np.float32)
+    img = rng.standard_normal((3, cin) + hw).astype(np.float32)
     in_s = float(np.abs(img).max() / 127)
     wq, ws = O.quantize_per_channel((rng.standard_normal((64, cin, k, k)) * 0.1).astype(np.float32))
     bias = (rng.standard_normal(64) * 0.1).astype(np.float32)
@@ -183,7 +186,7 @@ def test_image_entry(plb, ctx, cin, k, s, p):
     y_ref = O.conv_int8(xq, wq, ws, in_s, bias, O.ACT_RELU, **kw)
     out_s = float(np.abs(y_ref).max() / 127)
     q_ref = O.conv_int8(xq, wq, ws, in_s, bias, O.ACT_RELU, out_scale=out_s, **kw)
-    conv = plb.Conv(ctx, wq, ws, in_s, bias, in_hw=(37, 41), act=1, out_scale=out_s, **kw)
+    conv = plb.Conv(ctx, wq, ws, in_s, bias, in_hw=hw, act=1, out_scale=out_s, **kw)
     got = conv.run_image_f32(dev(img)).cpu().numpy().transpose(0, 3, 1, 2)
     got_nchw = conv.run(dev(xq)).cpu().numpy()
     ctx.sync()
