@@ -144,3 +144,22 @@ def test_semi_detection_rule():
     assert O.sparse_zeros(w)["flag_semi"] == 1
     w2 = (rng.integers(1, 5, (16, 32)) * (rng.random((16, 32)) < 0.2)).astype(np.int8)
     assert O.sparse_zeros(w2)["flag_semi"] == 0
+
+
+@pytest.mark.parametrize("dtype", [np.int8, np.float32])
+@pytest.mark.parametrize("semi", [False, True])
+@pytest.mark.parametrize("m,k", [(7, 12), (8, 16), (5, 1), (64, 109)])
+def test_numpy_encoder_of_the_package_matches_the_oracle_encoder(dtype, semi, m, k):
+    """paddle-lite_b200/sparse_format.py (numpy) and oracle/plb_oracle.c (C) restate the same pass
+    independently; they must produce identical tensors."""
+    import importlib
+    S = importlib.import_module("paddle-lite_b200.sparse_format")
+    rng = np.random.default_rng(m * 31 + k)
+    w = (rng.integers(-5, 6, (m, k)) * (rng.random((m, k)) < 0.3)).astype(dtype)
+    if m > 3:
+        w[2] = 0
+    a, b = S.encode(w, 6, semi=semi), O.sparse_encode(w, 6, semi=semi)
+    assert a["first_ic"] == b["first_ic"] and a["flag_semi"] == b["flag_semi"]
+    assert np.array_equal(a["nonzero_weights"], b["nonzero_weights"])
+    assert np.array_equal(a["oc_nonzeros"], b["oc_nonzeros"])
+    assert np.array_equal(a["diffs"], b["diffs"])
