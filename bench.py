@@ -25,7 +25,6 @@ import importlib
 import json
 import os
 import statistics
-import subprocess
 import sys
 import threading
 import time
@@ -49,52 +48,71 @@ def measured_peaks():
 
 
 class ClockSampler:
-    """Samples SM clocks and throttle reasons with nvidia-smi while the timed region runs."""
-    FIELDS = ("clocks.sm,clocks.max.sm,clocks_event_reasons.hw_slowdown,"
-              "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,"
-              "clocks_event_reasons.sw_power_cap")
+    """Samples SM clocks and throttle reasons of one GPU while a timed region runs (NVML reads
+    from a background thread every few milliseconds; nothing is ever set)."""
 
     def __init__(self, index):
-        self.index, self.proc, self.lines = index, None, []
+        self.index, self.samples, self.stop_flag, self.thread, self.err = index, [], False, None, None
 
     def start(self):
         try:
-            self.proc = subprocess.Popen(
-                ["nvidia-smi", "-i", str(self.index), "--query-gpu=" + self.FIELDS,
-                 "--format=csv,noheader,nounits", "-lms", "100"], stdout=subprocess.PIPE, text=True)
-            self.thread = threading.Thread(target=self._read, daemon=True)
-            self.thread.start()
-        except OSError:
-            self.proc = None
+            import pynvml
+            pynvml.nvmlInit()
+            self.nv = pynvml
+            self.handle = pynvml.nvmlDeviceGetHandleByIndex(self.index)
+            self.max_mhz = pynvml.nvmlDeviceGetMaxClockInfo(self.handle, pynvml.NVML_CLOCK_SM)
+        except Exception as exc:  # no NVML: report that instead of inventing numbers
+            self.err = str(exc)
+            return
+        self.thread = threading.Thread(target=self._poll, daemon=True)
+        self.thread.start()
 
-    def _read(self):
-        for line in self.proc.stdout:
-            self.lines.append(line.strip())
-
-    def stop(self):
-        if not self.proc:
-            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
-        self.proc.terminate()
-        try:
-            self.proc.wait(timeout=5)
-        except subprocess.TimeoutExpired:
-            self.proc.kill()
-        sm, mx, reasons = [], [], set()
-        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
-        for line in self.lines:
-            parts = [p.strip() for p in line.split(",")]
-            if len(parts) < 6:
-                continue
+    def _poll(self):
+        nv = self.nv
+        while not self.stop_flag:
             try:
-                sm.append(float(parts[0]))
-                mx.append(float(parts[1]))
-            except ValueError:
-                continue
-            for name, val in zip(names, parts[2:6]):
-                if val.lower().startswith("active"):
-                    reasons.add(name)
-        return {"sm_mhz": statistics.median(sm) if sm else None,
-                "sm_max_mhz": max(mx) if mx else None, "reasons": sorted(reasons), "samples": len(sm)}
+                mhz = nv.nvmlDeviceGetClockInfo(self.handle, nv.NVML_CLOCK_SM)
+                reasons = nv.nvmlDeviceGetCurrentClocksEventReasons(self.handle) \
+                    if hasattr(nv, "nvmlDeviceGetCurrentClocksEventReasons") \
+                    else nv.nvmlDeviceGetCurrentClocksThrottleReasons(self.handle)
+                self.samples.append((time.perf_counter(), mhz, reasons))
+            except Exception as exc:
+                self.err = str(exc)
+                return
+            time.sleep(0.004)
+
+    def stop(self, t_begin=None, t_end=None):
+        self.stop_flag = True
+        if self.thread:
+            self.thread.join(timeout=2)
+        if not self.samples:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["clock sampling unavailable: %s" % self.err],
+                    "samples": 0}
+        sel = [s for s in self.samples if (t_begin is None or s[0] >= t_begin) and (t_end is None or s[0] <= t_end)]
+        if not sel:  # region shorter than one poll: take the sample closest to it
+            mid = 0.5 * ((t_begin or 0) + (t_end or 0))
+            sel = [min(self.samples, key=lambda s: abs(s[0] - mid))]
+        nv = self.nv
+        names = {"hw_slowdown": getattr(nv, "nvmlClocksThrottleReasonHwSlowdown", 0x8),
+                 "hw_thermal_slowdown": getattr(nv, "nvmlClocksThrottleReasonHwThermalSlowdown", 0x40),
+                 "sw_thermal_slowdown": getattr(nv, "nvmlClocksThrottleReasonSwThermalSlowdown", 0x20),
+                 "sw_power_cap": getattr(nv, "nvmlClocksThrottleReasonSwPowerCap", 0x4)}
+        seen = set()
+        for _, _, bits in sel:
+            for name, mask in names.items():
+                if bits & mask:
+                    seen.add(name)
+        return {"sm_mhz": statistics.median([s[1] for s in sel]), "sm_max_mhz": self.max_mhz,
+                "reasons": sorted(seen), "samples": len(sel)}
+
+
+def _nvml_index(local_rank):
+    """NVML enumerates physical GPUs; honour CUDA_VISIBLE_DEVICES when it lists ordinals."""
+    vis = os.environ.get("CUDA_VISIBLE_DEVICES", "")
+    ids = [v.strip() for v in vis.split(",") if v.strip()]
+    if local_rank < len(ids) and ids[local_rank].isdigit():
+        return int(ids[local_rank])
+    return local_rank
 
 
 def layer_bytes(spec, batch):
@@ -318,18 +336,20 @@ def main():
                     st[1].run(runner.buf[st[2]], out=runner.buf[st[3]])
 
         # ---- device-resident throughput
+        sampler = ClockSampler(_nvml_index(local_rank))
+        sampler.start()
         for _ in range(warmup):
             g_full.replay()
         barrier()
-        sampler = ClockSampler(local_rank)
-        sampler.start()
         e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        t_begin = time.perf_counter()
         e0.record(stream)
         for _ in range(args.steps):
             g_full.replay()
         e1.record(stream)
         barrier()
-        clocks = sampler.stop()
+        t_end = time.perf_counter()
+        clocks = sampler.stop(t_begin, t_end)
         ms_total = max_over_ranks(e0.elapsed_time(e1))
         ms_step = ms_total / args.steps
         value = args.gpus * batch / (ms_step / 1e3)

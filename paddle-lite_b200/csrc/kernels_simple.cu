@@ -392,6 +392,117 @@ __global__ void __launch_bounds__(kBlock)
   }
 }
 
+// ---- fast int8 layout staging: 128-pixel x CT-channel tiles through shared memory, 128-bit
+// global accesses on the pixel-contiguous (NCHW) side, 4x4 byte transposes with prmt in registers.
+// The shared tile is [pixel][17 words] (CT <= 64 channels): odd pitch keeps the row-wise phase
+// conflict-free and the strided phase at four-way conflicts.
+constexpr int kTilePix = 128;
+constexpr int kTilePitchW = 17;  // words per pixel row of the shared tile
+
+__device__ __forceinline__ void transpose4x4(uint32_t a, uint32_t b, uint32_t c, uint32_t d, uint32_t (&w)[4]) {
+  const uint32_t t0 = __byte_perm(a, b, 0x5140), t1 = __byte_perm(a, b, 0x7362);
+  const uint32_t t2 = __byte_perm(c, d, 0x5140), t3 = __byte_perm(c, d, 0x7362);
+  w[0] = __byte_perm(t0, t2, 0x5410);
+  w[1] = __byte_perm(t0, t2, 0x7632);
+  w[2] = __byte_perm(t1, t3, 0x5410);
+  w[3] = __byte_perm(t1, t3, 0x7632);
+}
+
+// x [n,c,hw] -> y [n,hw,cpad].  grid = (pixel strips, channel tiles, n); block = 256 threads =
+// 8 warps; a warp handles 4 channel quads x 8 segments of 16 pixels.  hw % 16 == 0.
+__global__ void __launch_bounds__(kBlock)
+    nchw_to_nhwc_i8_fast_kernel(const int8_t* __restrict__ x, int8_t* __restrict__ y, int c, int hw, int cpad,
+                                int ct) {
+  pdl_sync_with_previous_kernel();
+  extern __shared__ uint32_t tile_smem[];
+  const int cquads = ct / 4;                 // channel quads per tile (8 or 16)
+  const int warps_per_strip = cquads / 4;    // 2 or 4
+  const int strips = 8 / warps_per_strip;    // 128-pixel strips per block
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const long n = blockIdx.z;
+  const int c0 = blockIdx.y * ct;
+  const int p_block = blockIdx.x * strips * kTilePix;
+  {
+    const int strip = warp / warps_per_strip;
+    const int cq = (warp % warps_per_strip) * 4 + (lane >> 3);
+    const int seg = lane & 7;
+    const int p = p_block + strip * kTilePix + seg * 16;
+    uint4 rows[4];
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      const int ch = c0 + cq * 4 + j;
+      rows[j] = make_uint4(0, 0, 0, 0);
+      if (ch < c && p < hw) rows[j] = __ldg(reinterpret_cast<const uint4*>(x + (n * c + ch) * static_cast<long>(hw) + p));
+    }
+    const uint32_t* r0 = reinterpret_cast<const uint32_t*>(&rows[0]);
+    const uint32_t* r1 = reinterpret_cast<const uint32_t*>(&rows[1]);
+    const uint32_t* r2 = reinterpret_cast<const uint32_t*>(&rows[2]);
+    const uint32_t* r3 = reinterpret_cast<const uint32_t*>(&rows[3]);
+    uint32_t* dst = tile_smem + (strip * kTilePix + seg * 16) * kTilePitchW + cq;
+#pragma unroll
+    for (int g = 0; g < 4; ++g) {
+      uint32_t w[4];
+      transpose4x4(r0[g], r1[g], r2[g], r3[g], w);
+#pragma unroll
+      for (int i = 0; i < 4; ++i) dst[(g * 4 + i) * kTilePitchW] = w[i];
+    }
+  }
+  __syncthreads();
+  const int words = strips * kTilePix * cquads;
+  for (int wi = threadIdx.x; wi < words; wi += kBlock) {
+    const int pix = wi / cquads, q = wi - pix * cquads;
+    const int p = p_block + pix;
+    if (p < hw && c0 + q * 4 < cpad)
+      *reinterpret_cast<uint32_t*>(y + (n * hw + p) * static_cast<long>(cpad) + c0 + q * 4) =
+          tile_smem[pix * kTilePitchW + q];
+  }
+}
+
+// x [n,hw,c] -> y [n,c,hw], int8, c % 4 == 0, hw % 16 == 0: the inverse of the kernel above.
+__global__ void __launch_bounds__(kBlock)
+    nhwc_to_nchw_i8_fast_kernel(const int8_t* __restrict__ x, int8_t* __restrict__ y, int c, int hw, int ct) {
+  pdl_sync_with_previous_kernel();
+  extern __shared__ uint32_t tile_smem[];
+  const int cquads = ct / 4;
+  const int warps_per_strip = cquads / 4;
+  const int strips = 8 / warps_per_strip;
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const long n = blockIdx.z;
+  const int c0 = blockIdx.y * ct;
+  const int p_block = blockIdx.x * strips * kTilePix;
+  const int words = strips * kTilePix * cquads;
+  for (int wi = threadIdx.x; wi < words; wi += kBlock) {
+    const int pix = wi / cquads, q = wi - pix * cquads;
+    const int p = p_block + pix;
+    uint32_t v = 0;
+    if (p < hw && c0 + q * 4 < c)
+      v = __ldg(reinterpret_cast<const uint32_t*>(x + (n * hw + p) * static_cast<long>(c) + c0 + q * 4));
+    tile_smem[pix * kTilePitchW + q] = v;
+  }
+  __syncthreads();
+  const int strip = warp / warps_per_strip;
+  const int cq = (warp % warps_per_strip) * 4 + (lane >> 3);
+  const int seg = lane & 7;
+  const int p = p_block + strip * kTilePix + seg * 16;
+  const uint32_t* src = tile_smem + (strip * kTilePix + seg * 16) * kTilePitchW + cq;
+  uint32_t out[4][4];  // [channel j][group g] = 4 pixels of channel j
+#pragma unroll
+  for (int g = 0; g < 4; ++g) {
+    uint32_t w[4];
+    transpose4x4(src[(g * 4 + 0) * kTilePitchW], src[(g * 4 + 1) * kTilePitchW], src[(g * 4 + 2) * kTilePitchW],
+                 src[(g * 4 + 3) * kTilePitchW], w);
+#pragma unroll
+    for (int j = 0; j < 4; ++j) out[j][g] = w[j];
+  }
+#pragma unroll
+  for (int j = 0; j < 4; ++j) {
+    const int ch = c0 + cq * 4 + j;
+    if (ch < c && p < hw)
+      *reinterpret_cast<uint4*>(y + (n * c + ch) * static_cast<long>(hw) + p) =
+          make_uint4(out[j][0], out[j][1], out[j][2], out[j][3]);
+  }
+}
+
 // Folded staging for stem layers with few input channels (cin * kw <= 32).  One staged pixel
 // (t, q) holds, for fh = stride_h consecutive input rows, the kw taps of the filter row and the
 // input channels:  y[n][t][q][e*32 + s*cin + c] = x[n][c][t*fh - pad_t + e][q*stride_w - pad_l + s*dil_w]
@@ -606,6 +717,16 @@ int nchw_to_nhwc_i8_launch(plb_ctx* ctx, const int8_t* x, int8_t* y, int n, int 
   if (n == 0) return PLB_OK;
   if (cpad % 8 || cpad < c) return fail(PLB_E_INVALID, "cpad must be a multiple of 8 and >= c");
   const int hw = h * w;
+  if (hw % 16 == 0 && cpad % 32 == 0 && (reinterpret_cast<uintptr_t>(x) & 15) == 0 &&
+      (reinterpret_cast<uintptr_t>(y) & 3) == 0) {
+    const int ct = cpad % 64 == 0 ? 64 : 32;
+    const int strips = 8 / (ct / 16);
+    dim3 fgrid((hw + strips * kTilePix - 1) / (strips * kTilePix), cpad / ct, n);
+    const size_t smem = static_cast<size_t>(strips) * kTilePix * kTilePitchW * 4;
+    PLB_CUDA(launch_kernel(nchw_to_nhwc_i8_fast_kernel, fgrid, dim3(kBlock), smem, ctx->stream, x, y, c, hw, cpad, ct));
+    ctx->launches++;
+    return PLB_OK;
+  }
   dim3 grid((hw + 63) / 64, (cpad + 31) / 32, n);
   PLB_CUDA(launch_kernel(to_nhwc_i8_kernel<int8_t>, dim3(grid), dim3(kBlock), 0, ctx->stream, x, y, c, hw, cpad, 1.f));
   PLB_CUDA(cudaGetLastError());
@@ -647,6 +768,17 @@ int nhwc_to_nchw_launch(plb_ctx* ctx, const void* x, void* y, int n, int c, int 
                         int elem_bytes) {
   if (n == 0) return PLB_OK;
   const int hw = h * w;
+  if (elem_bytes == 1 && hw % 16 == 0 && c % 4 == 0 && (reinterpret_cast<uintptr_t>(y) & 15) == 0 &&
+      (reinterpret_cast<uintptr_t>(x) & 3) == 0) {
+    const int ct = c >= 64 ? 64 : 32;
+    const int strips = 8 / (ct / 16);
+    dim3 fgrid((hw + strips * kTilePix - 1) / (strips * kTilePix), (c + ct - 1) / ct, n);
+    const size_t smem = static_cast<size_t>(strips) * kTilePix * kTilePitchW * 4;
+    PLB_CUDA(launch_kernel(nhwc_to_nchw_i8_fast_kernel, fgrid, dim3(kBlock), smem, ctx->stream,
+                           static_cast<const int8_t*>(x), static_cast<int8_t*>(y), c, hw, ct));
+    ctx->launches++;
+    return PLB_OK;
+  }
   dim3 grid((hw + 31) / 32, (c + 31) / 32, n), block(32, 8);
   if (elem_bytes == 1)
     PLB_CUDA(launch_kernel(nhwc_to_nchw_kernel<int8_t>, dim3(grid), dim3(block), 0, ctx->stream, static_cast<const int8_t*>(x), static_cast<int8_t*>(y), c, hw));

@@ -125,6 +125,67 @@ class ConvInt8Compute : public KernelLite<TARGET(kCUDA), PRECISION(kInt8)> {
   int64_t in_h_{0}, in_w_{0};
 };
 
+// The same layer on channels-last tensors (DATALAYOUT(kNHWC)).  Registered next to the NCHW
+// kernels so that the reference's own type_layout_cast_pass
+// (lite/core/optimizer/mir/type_layout_cast_pass.cc) inserts `layout` ops at the edges of a run
+// of these kernels only, and consecutive int8 layers exchange NHWC tensors without any staging.
+template <PrecisionType OutType>
+class ConvInt8NhwcCompute : public KernelLite<TARGET(kCUDA), PRECISION(kInt8), DATALAYOUT(kNHWC)> {
+ public:
+  using param_t = operators::ConvParam;
+
+  void PrepareForRun() override {
+    auto& param = this->Param<param_t>();
+    auto x_dims = param.x->dims();  // the op keeps logical NCHW dims; only the memory is channels-last
+    auto w_dims = param.filter->dims();
+    auto paddings = *param.paddings;
+    auto dilations = *param.dilations;
+    plb_conv_desc d{};
+    d.cin = x_dims[1];
+    d.h = x_dims[2];
+    d.w = x_dims[3];
+    d.cout = w_dims[0];
+    d.kh = w_dims[2];
+    d.kw = w_dims[3];
+    d.stride_h = param.strides[0];
+    d.stride_w = param.strides[1];
+    d.pad_top = paddings[0];
+    d.pad_bottom = paddings[1];
+    d.pad_left = paddings[2];
+    d.pad_right = paddings[3];
+    d.dil_h = dilations[0];
+    d.dil_w = dilations[1];
+    d.groups = param.groups;
+    d.act = ActCode(param.activation_param, &d.act_alpha);
+    d.in_scale = param.input_scale;
+    d.out_scale = param.output_scale;
+    d.out_dtype = OutType == PRECISION(kInt8) ? PLB_OUT_I8 : PLB_OUT_F32;
+    d.leaky_compat = 1;
+    d.impl = PLB_IMPL_AUTO;
+    const float* bias = param.bias ? param.bias->template data<float>() : nullptr;
+    plb_conv* conv = nullptr;
+    PLB_CHECK(plb_conv_prepare(GetCtx(), &d, param.filter->template data<int8_t>(),
+                               param.weight_scale.data(), static_cast<int>(param.weight_scale.size()),
+                               bias, &conv));
+    conv_.reset(conv);
+  }
+
+  void Run() override {
+    auto& param = this->Param<param_t>();
+    const int batch = param.x->dims()[0];
+    void* out = OutType == PRECISION(kInt8)
+                    ? static_cast<void*>(param.output->template mutable_data<int8_t>(TARGET(kCUDA)))
+                    : static_cast<void*>(param.output->template mutable_data<float>(TARGET(kCUDA)));
+    PLB_CHECK(plb_conv_run_nhwc(conv_.get(), param.x->template data<int8_t>(), out, batch));
+  }
+
+ private:
+  struct Deleter {
+    void operator()(plb_conv* p) const { plb_conv_destroy(p); }
+  };
+  std::unique_ptr<plb_conv, Deleter> conv_;
+};
+
 template <PrecisionType OutType>
 class FcInt8Compute : public KernelLite<TARGET(kCUDA), PRECISION(kInt8)> {
  public:
@@ -250,6 +311,36 @@ REGISTER_LITE_KERNEL(conv2d, kCUDA, kInt8, kNCHW, CudaConvInt8_Fp32, fp32_out)
     .BindInput("Filter", {PLB_T(kInt8)})
     .BindOutput("Output", {PLB_T(kFloat)})
     .BindPaddleOpVersion("conv2d", 1)
+    .Finalize();
+
+typedef plbk::ConvInt8NhwcCompute<PRECISION(kInt8)> CudaConvInt8Nhwc_Int8;
+typedef plbk::ConvInt8NhwcCompute<PRECISION(kFloat)> CudaConvInt8Nhwc_Fp32;
+#define PLB_TN(prec) LiteType::GetTensorTy(TARGET(kCUDA), PRECISION(prec), DATALAYOUT(kNHWC))
+
+REGISTER_LITE_KERNEL(conv2d, kCUDA, kInt8, kNHWC, CudaConvInt8Nhwc_Int8, int8_out_nhwc)
+    .BindInput("Input", {PLB_TN(kInt8)})
+    .BindInput("SecondInput", {PLB_TN(kInt8)})
+    .BindInput("Bias", {PLB_T(kFloat)})
+    .BindInput("Filter", {PLB_T(kInt8)})
+    .BindOutput("Output", {PLB_TN(kInt8)})
+    .BindPaddleOpVersion("conv2d", 1)
+    .Finalize();
+
+REGISTER_LITE_KERNEL(conv2d, kCUDA, kInt8, kNHWC, CudaConvInt8Nhwc_Fp32, fp32_out_nhwc)
+    .BindInput("Input", {PLB_TN(kInt8)})
+    .BindInput("SecondInput", {PLB_TN(kInt8)})
+    .BindInput("Bias", {PLB_T(kFloat)})
+    .BindInput("Filter", {PLB_T(kInt8)})
+    .BindOutput("Output", {PLB_TN(kFloat)})
+    .BindPaddleOpVersion("conv2d", 1)
+    .Finalize();
+
+REGISTER_LITE_KERNEL(depthwise_conv2d, kCUDA, kInt8, kNHWC, CudaConvInt8Nhwc_Int8, int8_out_nhwc)
+    .BindInput("Input", {PLB_TN(kInt8)})
+    .BindInput("Bias", {PLB_T(kFloat)})
+    .BindInput("Filter", {PLB_T(kInt8)})
+    .BindOutput("Output", {PLB_TN(kInt8)})
+    .BindPaddleOpVersion("depthwise_conv2d", 1)
     .Finalize();
 
 REGISTER_LITE_KERNEL(depthwise_conv2d, kCUDA, kInt8, kNCHW, CudaConvInt8_Int8, int8_out)

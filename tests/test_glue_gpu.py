@@ -12,7 +12,9 @@ def dev(a):
     return torch.from_numpy(np.ascontiguousarray(a)).cuda()
 
 
-@pytest.mark.parametrize("n,c,h,w,cpad", [(2, 3, 17, 9, 32), (1, 64, 8, 8, 64), (3, 40, 5, 7, 48), (1, 130, 3, 3, 160)])
+@pytest.mark.parametrize("n,c,h,w,cpad", [(2, 3, 17, 9, 32), (1, 64, 8, 8, 64), (3, 40, 5, 7, 48), (1, 130, 3, 3, 160),
+                                          (2, 32, 16, 16, 32), (1, 100, 8, 12, 128), (2, 256, 4, 8, 256),
+                                          (3, 3, 16, 16, 32), (1, 128, 56, 56, 128)])
 def test_layout_roundtrip(plb, ctx, n, c, h, w, cpad):
     rng = np.random.default_rng(c)
     x = rng.integers(-128, 128, (n, c, h, w), dtype=np.int8)
