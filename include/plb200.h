@@ -70,6 +70,9 @@ size_t plb_conv_workspace_bytes(const plb_conv* conv, int batch);
 const char* plb_last_error(void);
 /* Number of kernels this library has launched on the ctx since creation. */
 long plb_ctx_launch_count(const plb_ctx* ctx);
+/* How many of those were tensor-core convolutions in window mode (each input pixel of a tile
+ * fetched once and shared by all filter taps).  For tests and tuning; no reference counterpart. */
+long plb_ctx_window_launch_count(const plb_ctx* ctx);
 
 /* ------------------------------------------------------------------ conv2d / depthwise_conv2d
  * plb_conv_desc carries what operators::ConvParam holds for an int8 kernel

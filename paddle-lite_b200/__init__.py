@@ -11,7 +11,8 @@ import ctypes as C
 import os
 
 HERE = os.path.dirname(os.path.abspath(__file__))
-LIB_PATH = os.path.join(HERE, "libplb200.so")
+# PLB200_LIBRARY selects another build of the same library (e.g. one compiled with extra diagnostics)
+LIB_PATH = os.environ.get("PLB200_LIBRARY") or os.path.join(HERE, "libplb200.so")
 
 OK, E_INVALID, E_UNSUPPORTED, E_CUDA, E_DEVICE, E_NOMEM = range(6)
 ACT_NONE, ACT_RELU, ACT_RELU6, ACT_LEAKY = 0, 1, 2, 3
@@ -55,6 +56,7 @@ SYMBOLS = {
     "plb_conv_workspace_bytes": (C.c_size_t, [_P, C.c_int]),
     "plb_last_error": (C.c_char_p, []),
     "plb_ctx_launch_count": (C.c_long, [_P]),
+    "plb_ctx_window_launch_count": (C.c_long, [_P]),
     "plb_conv_prepare": (C.c_int, [_P, C.POINTER(ConvDesc), _P, _P, C.c_int, _P, C.POINTER(_P)]),
     "plb_conv_run": (C.c_int, [_P, _P, _P, C.c_int]),
     "plb_conv_run_nhwc": (C.c_int, [_P, _P, _P, C.c_int]),
@@ -134,6 +136,9 @@ class Context:
 
     def launch_count(self):
         return lib().plb_ctx_launch_count(self.handle)
+
+    def window_launch_count(self):
+        return lib().plb_ctx_window_launch_count(self.handle)
 
     def set_workspace(self, tensor):
         self._ws = tensor

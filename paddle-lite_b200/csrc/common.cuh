@@ -50,6 +50,7 @@ struct plb_ctx {
   size_t ws_bytes = 0;
   bool ws_owned = false;
   long launches = 0;
+  long window_launches = 0;     // tensor-core convolutions that ran in window (slab) mode
   int reserve(size_t bytes);    // make ws at least `bytes`
 };
 

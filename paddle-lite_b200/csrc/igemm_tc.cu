@@ -51,6 +51,14 @@ struct IgemmArgs {
   int staging_bytes, staging_w_bytes;  // epilogue staging in front of the operand ring
   int stage_b_warp;                    // bytes of int8 staging per epilogue warp
   int resident_b;                      // whole filter of this CTA's channel tile kept in shared memory
+  int resident_bytes;                  // its size, rounded up to 1 KiB
+  // slab mode (stride-1 filters with several taps): a pipeline stage holds the input window of a
+  // 16 x 8 pixel output tile once and every tap reads it through a shifted matrix descriptor
+  int slab, kh;
+  int slab_w;                          // window width in pixels = 8 + (kw-1)*dil_w
+  int slab_rows;                       // window pixels = slab_w * (16 + (kh-1)*dil_h)
+  int plane_bytes;                     // one channel chunk of the window, rounded up to 1 KiB
+  int tiles_x, tiles_y;                // output tiles per image
   int out_mode, ldy;
   void* y;
   const float* scale;
@@ -62,7 +70,24 @@ struct IgemmArgs {
   int8_t* y_i8;
   float inv_next_scale;
   int* status;
+#ifdef PLB_TC_TIMING
+  long long* timing;  // [grid][16] cycle counters
+#endif
 };
+
+// Optional per-role cycle accounting (build with -DPLB_TC_TIMING; never part of the shipped library):
+// each role of a CTA sums the cycles it spends in its waits and the host prints the averages.
+#ifdef PLB_TC_TIMING
+#define TT_DECL(n) long long tt_acc[n] = {}; long long tt_t0 = 0
+#define TT_START() tt_t0 = clock64()
+#define TT_STOP(i) tt_acc[i] += clock64() - tt_t0
+#define TT_FLUSH(base, n) do { for (int tt_i = 0; tt_i < (n); ++tt_i) a.timing[blockIdx.x * 16 + (base) + tt_i] = tt_acc[tt_i]; } while (0)
+#else
+#define TT_DECL(n)
+#define TT_START()
+#define TT_STOP(i)
+#define TT_FLUSH(base, n)
+#endif
 
 // ---------------------------------------------------------------- PTX wrappers
 __device__ __forceinline__ uint32_t smem_u32(const void* p) {
@@ -121,36 +146,109 @@ __device__ __forceinline__ void tma_load_im2col_4d(uint32_t dst, const CUtensorM
       "h"(off_h)
       : "memory");
 }
+__device__ __forceinline__ void tma_load_4d(uint32_t dst, const CUtensorMap* map, uint32_t bar, int c0,
+                                            int c1, int c2, int c3) {
+  asm volatile(
+      "cp.async.bulk.tensor.4d.shared::cluster.global.mbarrier::complete_tx::bytes"
+      " [%0], [%1, {%3, %4, %5, %6}], [%2];" ::"r"(dst),
+      "l"(reinterpret_cast<uint64_t>(map)), "r"(bar), "r"(c0), "r"(c1), "r"(c2), "r"(c3)
+      : "memory");
+}
+// Predicated forms for the producer warp (see tc_mma_i8_halves).
+__device__ __forceinline__ void mbar_expect_tx_if(uint32_t bar, uint32_t bytes, bool issue) {
+  asm volatile(
+      "{\n\t"
+      ".reg .pred q;\n\t"
+      "setp.ne.b32 q, %2, 0;\n\t"
+      "@q mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;\n\t"
+      "}" ::"r"(bar),
+      "r"(bytes), "r"(static_cast<uint32_t>(issue))
+      : "memory");
+}
+__device__ __forceinline__ void tma_load_2d_if(uint32_t dst, const CUtensorMap* map, uint32_t bar, int c0, int c1,
+                                               bool issue) {
+  asm volatile(
+      "{\n\t"
+      ".reg .pred q;\n\t"
+      "setp.ne.b32 q, %5, 0;\n\t"
+      "@q cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes"
+      " [%0], [%1, {%3, %4}], [%2];\n\t"
+      "}" ::"r"(dst),
+      "l"(reinterpret_cast<uint64_t>(map)), "r"(bar), "r"(c0), "r"(c1), "r"(static_cast<uint32_t>(issue))
+      : "memory");
+}
+__device__ __forceinline__ void tma_load_4d_if(uint32_t dst, const CUtensorMap* map, uint32_t bar, int c0, int c1,
+                                               int c2, int c3, bool issue) {
+  asm volatile(
+      "{\n\t"
+      ".reg .pred q;\n\t"
+      "setp.ne.b32 q, %7, 0;\n\t"
+      "@q cp.async.bulk.tensor.4d.shared::cluster.global.mbarrier::complete_tx::bytes"
+      " [%0], [%1, {%3, %4, %5, %6}], [%2];\n\t"
+      "}" ::"r"(dst),
+      "l"(reinterpret_cast<uint64_t>(map)), "r"(bar), "r"(c0), "r"(c1), "r"(c2), "r"(c3),
+      "r"(static_cast<uint32_t>(issue))
+      : "memory");
+}
+__device__ __forceinline__ void tma_load_im2col_4d_if(uint32_t dst, const CUtensorMap* map, uint32_t bar, int c,
+                                                      int w, int h, int n, uint16_t off_w, uint16_t off_h,
+                                                      bool issue) {
+  asm volatile(
+      "{\n\t"
+      ".reg .pred q;\n\t"
+      "setp.ne.b32 q, %9, 0;\n\t"
+      "@q cp.async.bulk.tensor.4d.shared::cluster.global.im2col.mbarrier::complete_tx::bytes"
+      " [%0], [%1, {%3, %4, %5, %6}], [%2], {%7, %8};\n\t"
+      "}" ::"r"(dst),
+      "l"(reinterpret_cast<uint64_t>(map)), "r"(bar), "r"(c), "r"(w), "r"(h), "r"(n), "h"(off_w), "h"(off_h),
+      "r"(static_cast<uint32_t>(issue))
+      : "memory");
+}
 __device__ __forceinline__ void tc_fence_before() {
   asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
 }
 __device__ __forceinline__ void tc_fence_after() {
   asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
 }
-__device__ __forceinline__ void tc_mma_i8(uint32_t d_tmem, uint64_t adesc, uint64_t bdesc,
-                                          uint32_t idesc, uint32_t accumulate) {
+// tcgen05.mma with the two shared-memory descriptors given as 32-bit halves (the high halves are loop constants).
+// Issued by the lane(s) whose `issue` flag is set: the role loops run warp-uniformly and only the
+// instruction itself is predicated, which keeps its operands warp-uniform values.
+__device__ __forceinline__ void tc_mma_i8_halves(uint32_t d_tmem, uint32_t a_lo, uint32_t a_hi, uint32_t b_lo,
+                                                 uint32_t b_hi, uint32_t idesc, uint32_t accumulate, bool issue) {
+  asm volatile(
+      "{\n\t"
+      ".reg .pred p, q;\n\t"
+      ".reg .b64 da, db;\n\t"
+      "setp.ne.b32 p, %6, 0;\n\t"
+      "setp.ne.b32 q, %7, 0;\n\t"
+      "mov.b64 da, {%1, %2};\n\t"
+      "mov.b64 db, {%3, %4};\n\t"
+      "@q tcgen05.mma.cta_group::1.kind::i8 [%0], da, db, %5, p;\n\t"
+      "}" ::"r"(d_tmem),
+      "r"(a_lo), "r"(a_hi), "r"(b_lo), "r"(b_hi), "r"(idesc), "r"(accumulate), "r"(static_cast<uint32_t>(issue))
+      : "memory");
+}
+__device__ __forceinline__ void tc_commit_if(uint32_t bar, bool issue) {
+  asm volatile(
+      "{\n\t"
+      ".reg .pred q;\n\t"
+      "setp.ne.b32 q, %1, 0;\n\t"
+      "@q tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];\n\t"
+      "}" ::"r"(bar),
+      "r"(static_cast<uint32_t>(issue))
+      : "memory");
+}
+// One lane of a converged warp (the same one on every call).
+__device__ __forceinline__ bool elect_one() {
+  uint32_t pred;
   asm volatile(
       "{\n\t"
       ".reg .pred p;\n\t"
-      "setp.ne.b32 p, %4, 0;\n\t"
-      "tcgen05.mma.cta_group::1.kind::i8 [%0], %1, %2, %3, p;\n\t"
-      "}" ::"r"(d_tmem),
-      "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate)
-      : "memory");
-}
-__device__ __forceinline__ void tc_commit(uint32_t bar) {
-  asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar)
-               : "memory");
-}
-__device__ __forceinline__ void tc_ld16(uint32_t taddr, uint32_t (&r)[16]) {
-  asm volatile(
-      "tcgen05.ld.sync.aligned.32x32b.x16.b32 "
-      "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15}, [%16];"
-      : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]),
-        "=r"(r[7]), "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]),
-        "=r"(r[14]), "=r"(r[15])
-      : "r"(taddr)
-      : "memory");
+      "elect.sync _|p, 0xffffffff;\n\t"
+      "selp.u32 %0, 1, 0, p;\n\t"
+      "}"
+      : "=r"(pred));
+  return pred != 0;
 }
 __device__ __forceinline__ void tc_ld32(uint32_t taddr, uint32_t (&r)[32]) {
   asm volatile(
@@ -392,6 +490,13 @@ __device__ __forceinline__ void tma_store_2d(const CUtensorMap* map, uint32_t sr
                "r"(src), "r"(c0), "r"(c1)
                : "memory");
 }
+__device__ __forceinline__ void tma_store_4d(const CUtensorMap* map, uint32_t src, int c0, int c1, int c2,
+                                             int c3) {
+  asm volatile("cp.async.bulk.tensor.4d.global.shared::cta.bulk_group [%0, {%2, %3, %4, %5}], [%1];" ::"l"(
+                   reinterpret_cast<uint64_t>(map)),
+               "r"(src), "r"(c0), "r"(c1), "r"(c2), "r"(c3)
+               : "memory");
+}
 __device__ __forceinline__ void bulk_commit() {
   asm volatile("cp.async.bulk.commit_group;" ::: "memory");
 }
@@ -499,8 +604,8 @@ __global__ void __launch_bounds__(kThreads, 1)
   const int stage_a = kTileM * a.kc;
   const int stage_b = a.bn * a.kc;
   uint8_t* smem_bres = smem_al + a.staging_bytes;
-  uint8_t* smem = smem_bres + (a.resident_b ? a.ksteps * stage_b : 0);
-  const int stage_bytes = a.resident_b ? stage_a : stage_a + stage_b;
+  uint8_t* smem = smem_bres + a.resident_bytes;
+  const int stage_bytes = a.slab ? a.cchunks * a.plane_bytes : (a.resident_b ? stage_a : stage_a + stage_b);
   uint8_t* ctrl = smem + a.stages * stage_bytes;
   uint64_t* full_bar = reinterpret_cast<uint64_t*>(ctrl);
   uint64_t* empty_bar = full_bar + kMaxStages;
@@ -553,117 +658,194 @@ __global__ void __launch_bounds__(kThreads, 1)
 
   if (warp == kProducerWarp) {
     // ------------------------------------------------------------ TMA producer
-    // One thread issues every operand copy of this CTA, so the loop body is kept free of
-    // divisions: ring position, tap and channel-chunk counters advance incrementally.
-    if (lane == 0) {
-      int s = 0;
-      uint32_t empty_parity = 1;  // a fresh barrier passes a wait on parity 1
-      bool ok = true;
-      const uint32_t smem_base = smem_u32(smem);
-      if (a.resident_b) {
-        // small filter, one channel tile: fetch all of it once; the ring then carries activations only
-        const uint32_t bar = smem_u32(bres_bar);
-        mbar_expect_tx(bar, static_cast<uint32_t>(a.ksteps * stage_b));
-        for (int ks = 0; ks < a.ksteps; ++ks) {
-          const uint32_t dst = smem_u32(smem_bres) + ks * stage_b;
-          tma_load_2d(dst, &tmB, bar, ks * a.kc, 0);
-        }
+    // The whole warp walks the loop (so that addresses and coordinates stay warp-uniform values)
+    // and one elected lane issues the copies.  The loop body is free of divisions: ring position,
+    // tap and channel-chunk counters advance incrementally.
+    const bool leader = elect_one();
+    TT_DECL(2);
+#ifdef PLB_TC_TIMING
+    const long long tt_begin = clock64();
+#endif
+    int s = 0;
+    uint32_t empty_parity = 1;  // a fresh barrier passes a wait on parity 1
+    bool ok = true;
+    const uint32_t smem_base = smem_u32(smem);
+    if (a.resident_b && leader) {
+      // small filter, one channel tile: fetch all of it once; the ring then carries activations only
+      const uint32_t bar = smem_u32(bres_bar);
+      mbar_expect_tx(bar, static_cast<uint32_t>(a.ksteps * stage_b));
+      for (int ks = 0; ks < a.ksteps; ++ks) {
+        const uint32_t dst = smem_u32(smem_bres) + ks * stage_b;
+        tma_load_2d(dst, &tmB, bar, ks * a.kc, 0);
       }
-      for (int tile = blockIdx.x; tile < a.num_tiles && ok; tile += gridDim.x) {
-        const int tile_m = tile / a.tiles_n;
-        const int m0 = tile_m * kTileM;
-        const int n0 = (tile - tile_m * a.tiles_n) * a.bn;
-        int q0 = 0, p0 = 0, cn = 0;
+    }
+    __syncwarp();
+    for (int tile = blockIdx.x; a.slab && tile < a.num_tiles && ok; tile += gridDim.x) {
+      // one window per tile: rows ty*16 - pad_t ..., columns tx*8 - pad_l ...; cells outside the
+      // image are filled with zeros by the copy engine
+      const int tile_m = tile / a.tiles_n;
+      const int tx = tile_m % a.tiles_x;
+      const int t = tile_m / a.tiles_x;
+      const int ty = t % a.tiles_y;
+      const int img = t / a.tiles_y;
+      TT_START();
+      ok = mbar_wait(smem_u32(&empty_bar[s]), empty_parity, abort_flag, a.status, FAULT_WAIT_EMPTY);
+      TT_STOP(0);
+      if (!ok) break;
+      const uint32_t bar = smem_u32(&full_bar[s]);
+      const uint32_t dst = smem_base + s * stage_bytes;
+      mbar_expect_tx_if(bar, static_cast<uint32_t>(a.cchunks * a.slab_rows * a.kc), leader);
+      for (int cc = 0; cc < a.cchunks; ++cc)
+        tma_load_4d_if(dst + cc * a.plane_bytes, &tmA, bar, cc * a.kc, tx * 8 - a.pad_l, ty * 16 - a.pad_t, img,
+                       leader);
+      if (++s == a.stages) {
+        s = 0;
+        empty_parity ^= 1;
+      }
+    }
+    for (int tile = blockIdx.x; !a.slab && tile < a.num_tiles && ok; tile += gridDim.x) {
+      const int tile_m = tile / a.tiles_n;
+      const int m0 = tile_m * kTileM;
+      const int n0 = (tile - tile_m * a.tiles_n) * a.bn;
+      int q0 = 0, p0 = 0, cn = 0;
+      if (a.im2col) {
+        q0 = m0 % a.wo;
+        const int t = m0 / a.wo;
+        p0 = t % a.ho;
+        cn = t / a.ho;
+      }
+      const int cw = q0 * a.stride_w - a.pad_l;
+      const int ch = p0 * a.stride_h - a.pad_t;
+      int r = 0, sx = 0, cc = 0, kb = 0;  // filter row, filter column, channel chunk, K offset in B
+      for (int ks = 0; ks < a.ksteps; ++ks) {
+        TT_START();
+        ok = mbar_wait(smem_u32(&empty_bar[s]), empty_parity, abort_flag, a.status, FAULT_WAIT_EMPTY);
+        TT_STOP(0);
+        if (!ok) break;
+        const uint32_t bar = smem_u32(&full_bar[s]);
+        const uint32_t dst_a = smem_base + s * stage_bytes;
+        const uint32_t dst_b = dst_a + stage_a;
+        mbar_expect_tx_if(bar, static_cast<uint32_t>(stage_bytes), leader);
         if (a.im2col) {
-          q0 = m0 % a.wo;
-          const int t = m0 / a.wo;
-          p0 = t % a.ho;
-          cn = t / a.ho;
+          tma_load_im2col_4d_if(dst_a, &tmA, bar, cc * a.kc, cw, ch, cn, static_cast<uint16_t>(sx * a.dil_w),
+                                static_cast<uint16_t>(r * a.dil_h), leader);
+        } else {
+          tma_load_2d_if(dst_a, &tmA, bar, kb, m0, leader);
         }
-        const int cw = q0 * a.stride_w - a.pad_l;
-        const int ch = p0 * a.stride_h - a.pad_t;
-        int r = 0, sx = 0, cc = 0, kb = 0;  // filter row, filter column, channel chunk, K offset in B
-        for (int ks = 0; ks < a.ksteps; ++ks) {
-          ok = mbar_wait(smem_u32(&empty_bar[s]), empty_parity, abort_flag, a.status, FAULT_WAIT_EMPTY);
-          if (!ok) break;
-          const uint32_t bar = smem_u32(&full_bar[s]);
-          mbar_expect_tx(bar, static_cast<uint32_t>(stage_bytes));
-          const uint32_t dst_a = smem_base + s * stage_bytes;
-          const uint32_t dst_b = dst_a + stage_a;
-          {
-            if (a.im2col) {
-              tma_load_im2col_4d(dst_a, &tmA, bar, cc * a.kc, cw, ch, cn,
-                                 static_cast<uint16_t>(sx * a.dil_w),
-                                 static_cast<uint16_t>(r * a.dil_h));
-            } else {
-              tma_load_2d(dst_a, &tmA, bar, kb, m0);
-            }
-            if (!a.resident_b) tma_load_2d(dst_b, &tmB, bar, kb, n0);
+        if (!a.resident_b) tma_load_2d_if(dst_b, &tmB, bar, kb, n0, leader);
+        kb += a.kc;
+        if (++cc == a.cchunks) {
+          cc = 0;
+          if (++sx == a.kw) {
+            sx = 0;
+            ++r;
           }
-          kb += a.kc;
-          if (++cc == a.cchunks) {
-            cc = 0;
-            if (++sx == a.kw) {
-              sx = 0;
-              ++r;
-            }
-          }
-          if (++s == a.stages) {
-            s = 0;
-            empty_parity ^= 1;
-          }
+        }
+        if (++s == a.stages) {
+          s = 0;
+          empty_parity ^= 1;
         }
       }
     }
+#ifdef PLB_TC_TIMING
+    tt_acc[1] = clock64() - tt_begin;
+#endif
+    if (lane == 0) TT_FLUSH(0, 2);
   } else if (warp == kMmaWarp) {
     // ------------------------------------------------------------ MMA issuer
-    if (lane == 0) {
-      // instruction descriptor: D=s32, A=B=s8, both K-major, N=bn, M=128
-      const uint32_t idesc = (2u << 4) | (1u << 7) | (1u << 10) |
-                             (static_cast<uint32_t>(a.bn >> 3) << 17) |
-                             (static_cast<uint32_t>(kTileM >> 4) << 24);
-      const int mma_per_stage = a.kc / 32;
-      const uint32_t smem_base = smem_u32(smem);
-      const uint64_t desc_hi = make_smem_desc(0, a.kc) & 0xFFFFFFFF00000000ull;  // layout, stride: constant
-      const int nb_mask = nb - 1, nb_shift = nb == 4 ? 2 : 1;
-      int s = 0, it = 0;
-      uint32_t full_parity = 0;
-      bool ok = true;
-      if (a.resident_b) {
-        ok = mbar_wait(smem_u32(bres_bar), 0, abort_flag, a.status, FAULT_WAIT_FULL);
-        tc_fence_after();
-      }
-      const uint32_t bres_base = smem_u32(smem_bres);
-      for (int tile = blockIdx.x; tile < a.num_tiles && ok; tile += gridDim.x, ++it) {
-        const int buf = it & nb_mask;
-        ok = mbar_wait(smem_u32(&acc_empty[buf]), ((it >> nb_shift) & 1) ^ 1, abort_flag, a.status,
-                       FAULT_WAIT_ACCUM);
+    // Again the whole warp runs the loop and an elected lane issues: matrix descriptors are
+    // warp-uniform values, built from 32-bit halves with as few instructions per MMA as possible
+    // (a 128 x 64 x 32 MMA occupies the tensor core for only ~57 cycles).
+    const bool leader = elect_one();
+    TT_DECL(4);
+    // instruction descriptor: D=s32, A=B=s8, both K-major, N=bn, M=128
+    const uint32_t idesc = (2u << 4) | (1u << 7) | (1u << 10) | (static_cast<uint32_t>(a.bn >> 3) << 17) |
+                           (static_cast<uint32_t>(kTileM >> 4) << 24);
+    const int mma_per_stage = a.kc / 32;
+    const uint32_t smem_base = smem_u32(smem);
+    const uint32_t hi_b = static_cast<uint32_t>(make_smem_desc(0, a.kc) >> 32);  // layout, 8-row group stride
+    // window mode: the 8-row groups of A are one window row (slab_w pixels) apart
+    const uint32_t hi_a = a.slab ? ((hi_b & 0xFFFFC000u) | ((static_cast<uint32_t>(a.slab_w * a.kc) >> 4) & 0x3FFFu)) : hi_b;
+    const uint32_t lo_flags = 1u << 16;  // leading-dimension byte offset field (unused by swizzled K-major tiles)
+    const int nb_mask = nb - 1, nb_shift = nb == 4 ? 2 : 1;
+    int s = 0, it = 0;
+    uint32_t full_parity = 0;
+    bool ok = true;
+    if (a.resident_b) {
+      ok = mbar_wait(smem_u32(bres_bar), 0, abort_flag, a.status, FAULT_WAIT_FULL);
+      tc_fence_after();
+    }
+    const uint32_t bres_lo = ((smem_u32(smem_bres) >> 4) & 0x3FFFu) | lo_flags;
+    const uint32_t stage_b_lo = static_cast<uint32_t>(stage_b) >> 4;
+    const uint32_t stage_lo = static_cast<uint32_t>(stage_bytes) >> 4;
+    const uint32_t ring_lo = ((smem_base >> 4) & 0x3FFFu) | lo_flags;
+    for (int tile = blockIdx.x; tile < a.num_tiles && ok; tile += gridDim.x, ++it) {
+      const int buf = it & nb_mask;
+      TT_START();
+      ok = mbar_wait(smem_u32(&acc_empty[buf]), ((it >> nb_shift) & 1) ^ 1, abort_flag, a.status, FAULT_WAIT_ACCUM);
+      TT_STOP(0);
+      if (!ok) break;
+      tc_fence_after();
+      const uint32_t d_tmem = tmem_base + buf * acc_cols;
+      uint32_t accumulate = 0;
+      if (a.slab) {
+        TT_START();
+        ok = mbar_wait(smem_u32(&full_bar[s]), full_parity, abort_flag, a.status, FAULT_WAIT_FULL);
+        TT_STOP(1);
         if (!ok) break;
         tc_fence_after();
-        const uint32_t d_tmem = tmem_base + buf * acc_cols;
-        uint32_t accumulate = 0;
-        for (int ks = 0; ks < a.ksteps; ++ks) {
-          ok = mbar_wait(smem_u32(&full_bar[s]), full_parity, abort_flag, a.status, FAULT_WAIT_FULL);
-          if (!ok) break;
-          tc_fence_after();
-          const uint32_t addr_a = smem_base + s * stage_bytes;
-          const uint64_t adesc = desc_hi | (((addr_a >> 4) & 0x3FFFu) | (1u << 16));
-          const uint32_t addr_b = a.resident_b ? bres_base + ks * stage_b : addr_a + stage_a;
-          const uint64_t bdesc = desc_hi | (((addr_b >> 4) & 0x3FFFu) | (1u << 16));
-          for (int j = 0; j < mma_per_stage; ++j) {
-            // advance 32 bytes of K inside the swizzle span: +2 in the (addr >> 4) field
-            tc_mma_i8(d_tmem, adesc + 2u * j, bdesc + 2u * j, idesc, accumulate);
-            accumulate = 1;
-          }
-          tc_commit(smem_u32(&empty_bar[s]));  // frees the stage when these MMAs retire
-          if (++s == a.stages) {
-            s = 0;
-            full_parity ^= 1;
+        TT_START();
+        // Tile row g (8 pixels) is window row g + r*dil_h starting at column sx*dil_w.  The swizzle
+        // is a function of the shared-memory address, so a start address shifted by whole
+        // pixels addresses the same bytes the copy engine wrote.
+        const uint32_t slab_lo = ring_lo + s * stage_lo;
+        const uint32_t row_lo = static_cast<uint32_t>(a.slab_w * a.kc * a.dil_h) >> 4;
+        const uint32_t col_lo = static_cast<uint32_t>(a.dil_w * a.kc) >> 4;
+        const uint32_t plane_lo = static_cast<uint32_t>(a.plane_bytes) >> 4;
+        uint32_t b_lo = bres_lo;
+        uint32_t row_a = slab_lo;
+        for (int r = 0; r < a.kh; ++r, row_a += row_lo) {
+          uint32_t tap_a = row_a;
+          for (int sx = 0; sx < a.kw; ++sx, tap_a += col_lo) {
+            uint32_t a_lo = tap_a;
+            for (int cc = 0; cc < a.cchunks; ++cc, a_lo += plane_lo, b_lo += stage_b_lo) {
+              for (int j = 0; j < mma_per_stage; ++j) {
+                tc_mma_i8_halves(d_tmem, a_lo + 2u * j, hi_a, b_lo + 2u * j, hi_b, idesc, accumulate, leader);
+                accumulate = 1;
+              }
+            }
           }
         }
-        tc_commit(smem_u32(&acc_full[buf]));  // accumulator complete (or drained on a fault)
+        tc_commit_if(smem_u32(&empty_bar[s]), leader);
+        TT_STOP(2);
+        if (++s == a.stages) {
+          s = 0;
+          full_parity ^= 1;
+        }
       }
+      uint32_t b_res_lo = bres_lo;
+      for (int ks = 0; !a.slab && ks < a.ksteps; ++ks, b_res_lo += stage_b_lo) {
+        TT_START();
+        ok = mbar_wait(smem_u32(&full_bar[s]), full_parity, abort_flag, a.status, FAULT_WAIT_FULL);
+        TT_STOP(1);
+        if (!ok) break;
+        tc_fence_after();
+        const uint32_t a_lo = ring_lo + s * stage_lo;
+        const uint32_t b_lo = a.resident_b ? b_res_lo : a_lo + (static_cast<uint32_t>(stage_a) >> 4);
+        // advance 32 bytes of K inside the swizzle span: +2 in the (addr >> 4) field
+        for (int j = 0; j < mma_per_stage; ++j) {
+          tc_mma_i8_halves(d_tmem, a_lo + 2u * j, hi_a, b_lo + 2u * j, hi_b, idesc, accumulate, leader);
+          accumulate = 1;
+        }
+        tc_commit_if(smem_u32(&empty_bar[s]), leader);  // frees the stage when these MMAs retire
+        if (++s == a.stages) {
+          s = 0;
+          full_parity ^= 1;
+        }
+      }
+      tc_commit_if(smem_u32(&acc_full[buf]), leader);  // accumulator complete (or drained on a fault)
     }
+    if (lane == 0) TT_FLUSH(2, 4);
   } else {
     // ------------------------------------------------------------ epilogue groups
     const int group = warp >> 2;     // 0..3
@@ -680,6 +862,7 @@ __global__ void __launch_bounds__(kThreads, 1)
     uint32_t res_phase = 0;
     bool stores_pending = false;
     bool ok = true;
+    TT_DECL(4);
     for (int it = my_buf; ok; it += nb) {
       const long tile_l = static_cast<long>(blockIdx.x) + static_cast<long>(it) * gridDim.x;
       if (tile_l >= a.num_tiles) break;
@@ -691,7 +874,16 @@ __global__ void __launch_bounds__(kThreads, 1)
       bool waited = false;
       if (STAGED) {
         const int row0 = m0 + quad * 32;
-        const bool active = row0 < a.m_total;  // warp-uniform: some row of this quadrant exists
+        // slab tiles are 16 x 8 pixels: this quadrant owns tile rows quad*4 .. quad*4+3
+        int s_w = 0, s_h = 0, s_img = 0;
+        if (a.slab) {
+          const int tile_m = tile / a.tiles_n;
+          s_w = (tile_m % a.tiles_x) * 8;
+          const int t = tile_m / a.tiles_x;
+          s_h = (t % a.tiles_y) * 16 + quad * 4;
+          s_img = t / a.tiles_y;
+        }
+        const bool active = a.slab ? s_h < a.ho : row0 < a.m_total;  // warp-uniform: some row of this quadrant exists
         const bool use_w = MODE == OUT_F32 || MODE == OUT_ACC || (MODE == OUT_ADD_RELU && a.y_f32 != nullptr);
         const bool have_res = MODE == OUT_ADD_RELU && a.residual != nullptr;
         const bool use_b = MODE == OUT_I8 || (MODE == OUT_ADD_RELU && a.y_i8 != nullptr);
@@ -701,23 +893,31 @@ __global__ void __launch_bounds__(kThreads, 1)
           if (n0 + c >= a.cout) break;  // warp-uniform
           if (active && stores_pending && (use_w || have_res || c == cbase)) {
             // the staging tiles are about to be overwritten: earlier stores must have read them
+            TT_START();
             if (lane == 0) bulk_wait_read_all();
             __syncwarp();
+            TT_STOP(1);
             stores_pending = false;
           }
           if (active && have_res && lane == 0) {
             mbar_expect_tx(my_res_bar, 4096);
-            tma_load_2d(st_w, &tmRes, my_res_bar, n0 + c, row0);
+            if (a.slab) tma_load_4d(st_w, &tmRes, my_res_bar, n0 + c, s_w, s_h, s_img);
+            else tma_load_2d(st_w, &tmRes, my_res_bar, n0 + c, row0);
           }
           if (!waited) {
+            TT_START();
             ok = mbar_wait(smem_u32(&acc_full[my_buf]), (it >> nb_shift) & 1, abort_flag, a.status, FAULT_WAIT_ACCUM);
+            TT_STOP(0);
             tc_fence_after();
             waited = true;
             if (!ok) break;
           }
+          TT_START();
           uint32_t r[32];
           tc_ld32(lane_addr + static_cast<uint32_t>(c), r);
           tc_wait_ld();
+          TT_STOP(2);
+          TT_START();
           if (active) {
             if (have_res) {
               ok = mbar_wait(my_res_bar, res_phase, abort_flag, a.status, FAULT_WAIT_FULL);
@@ -729,16 +929,19 @@ __global__ void __launch_bounds__(kThreads, 1)
             fence_proxy_async_smem();
             __syncwarp();
             if (use_w && lane == 0) {
-              tma_store_2d(&tmOutW, st_w, n0 + c, row0);
+              if (a.slab) tma_store_4d(&tmOutW, st_w, n0 + c, s_w, s_h, s_img);
+              else tma_store_2d(&tmOutW, st_w, n0 + c, row0);
               bulk_commit();
             }
             if (use_w) stores_pending = true;
             wrote_b = use_b;
           }
+          TT_STOP(3);
         }
         if (wrote_b) {
           if (lane == 0) {
-            tma_store_2d(&tmOutB, st_b, n0 + cbase, row0);
+            if (a.slab) tma_store_4d(&tmOutB, st_b, n0 + cbase, s_w, s_h, s_img);
+            else tma_store_2d(&tmOutB, st_b, n0 + cbase, row0);
             bulk_commit();
           }
           stores_pending = true;
@@ -777,6 +980,7 @@ __global__ void __launch_bounds__(kThreads, 1)
       if (lane == 0) mbar_arrive(smem_u32(&acc_empty[my_buf]));
     }
     if (STAGED && lane == 0) bulk_wait_all();  // staging memory must outlive the stores reading it
+    if (warp == 0 && lane == 0) TT_FLUSH(6, 4);
   }
   tc_fence_before();
   __syncthreads();
@@ -929,12 +1133,37 @@ int igemm_tc_launch(plb_ctx* ctx, const IgemmProblem& p) {
   }
   a.staging_bytes = (a.staging_w_bytes + kEpilogueWarps * a.stage_b_warp + 1023) / 1024 * 1024;
   const int tiles_n_h = (p.cout + bn - 1) / bn;
-  const int resident_bytes = a.ksteps * bn * a.kc;
-  a.resident_b = env_int("PLB_TC_RESIDENT", 1) != 0 && tiles_n_h == 1 && resident_bytes <= kMaxResidentB &&
-                 tiles_m > ctx->sm_count;  // worth it only when a CTA walks several tiles
-  const int ring_stage_bytes = a.resident_b ? kTileM * a.kc : stage_bytes;
+  const int resident_bytes = (a.ksteps * bn * a.kc + 1023) / 1024 * 1024;
+  const bool can_resident = env_int("PLB_TC_RESIDENT", 1) != 0 && tiles_n_h == 1 && resident_bytes <= kMaxResidentB;
+  a.resident_b = can_resident && tiles_m > ctx->sm_count;  // worth it only when a CTA walks several tiles
+  // Slab mode: stride-1 filters with several taps read each input pixel once per tile instead of
+  // once per tap.  Output tiles are 16 x 8 pixels, so images much smaller than that waste too
+  // many accumulator rows.
+  int tiles_m_eff = tiles_m;
+  if (p.im2col && a.taps > 1 && p.stride_h == 1 && p.stride_w == 1 && staged && can_resident) {
+    const int tx = (p.wo + 7) / 8, ty = (p.ho + 15) / 16;
+    const int sw_px = 8 + (p.kw - 1) * p.dil_w, sh_px = 16 + (p.kh - 1) * p.dil_h;
+    const double waste = static_cast<double>(tx) * 8 * ty * 16 / (static_cast<double>(p.wo) * p.ho);
+    const int plane = (sw_px * sh_px * a.kc + 1023) / 1024 * 1024;
+    const bool fits = sw_px <= 256 && sh_px <= 256 && sw_px * a.kc <= 0x3FFF * 16 &&
+                      2 * a.cchunks * plane + resident_bytes + a.staging_bytes + kCtrlBytes + 1024 <= 225 * 1024;
+    const int dflt = waste <= 1.35 && fits && a.resident_b;
+    if (fits && env_int("PLB_TC_SLAB", dflt) != 0) {
+      a.slab = 1;
+      a.resident_b = 1;
+      a.kh = p.kh;
+      a.slab_w = sw_px;
+      a.slab_rows = sw_px * sh_px;
+      a.plane_bytes = plane;
+      a.tiles_x = tx;
+      a.tiles_y = ty;
+      tiles_m_eff = p.batch * tx * ty;
+    }
+  }
+  a.resident_bytes = a.resident_b ? resident_bytes : 0;
+  const int ring_stage_bytes = a.slab ? a.cchunks * a.plane_bytes : (a.resident_b ? kTileM * a.kc : stage_bytes);
   // one CTA per SM: spend (almost) all remaining shared memory on the operand ring
-  int stages = (225 * 1024 - a.staging_bytes - kCtrlBytes - (a.resident_b ? resident_bytes : 0)) / ring_stage_bytes;
+  int stages = (225 * 1024 - a.staging_bytes - kCtrlBytes - a.resident_bytes) / ring_stage_bytes;
   stages = env_int("PLB_TC_STAGES", stages);
   if (stages > kMaxStages) stages = kMaxStages;
   if (stages < 2) stages = 2;
@@ -965,7 +1194,21 @@ int igemm_tc_launch(plb_ctx* ctx, const IgemmProblem& p) {
                                 CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
     if (r != CUDA_SUCCESS) return fail(PLB_E_CUDA, "cuTensorMapEncodeTiled(filter) failed: %d", (int)r);
   }
-  if (!p.im2col) {
+  if (a.slab) {
+    // plain tiled view of the NHWC input: a box is one channel chunk of a tile's input window
+    cuuint64_t dims[4] = {static_cast<cuuint64_t>(p.cin_pad), static_cast<cuuint64_t>(p.w),
+                          static_cast<cuuint64_t>(p.h), static_cast<cuuint64_t>(p.batch)};
+    cuuint64_t strides[3] = {static_cast<cuuint64_t>(p.cin_pad),
+                             static_cast<cuuint64_t>(p.cin_pad) * p.w,
+                             static_cast<cuuint64_t>(p.cin_pad) * p.w * p.h};
+    cuuint32_t box[4] = {static_cast<cuuint32_t>(a.kc), static_cast<cuuint32_t>(a.slab_w),
+                         static_cast<cuuint32_t>(a.slab_rows / a.slab_w), 1};
+    cuuint32_t estr[4] = {1, 1, 1, 1};
+    CUresult r = g_encode_tiled(&tmA, CU_TENSOR_MAP_DATA_TYPE_UINT8, 4, const_cast<int8_t*>(p.a), dims,
+                                strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE, sw,
+                                CU_TENSOR_MAP_L2_PROMOTION_L2_128B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    if (r != CUDA_SUCCESS) return fail(PLB_E_CUDA, "cuTensorMapEncodeTiled(input window) failed: %d", (int)r);
+  } else if (!p.im2col) {
     cuuint64_t dims[2] = {static_cast<cuuint64_t>(p.cin_pad), static_cast<cuuint64_t>(p.m_total)};
     cuuint64_t strides[1] = {static_cast<cuuint64_t>(p.cin_pad)};
     cuuint32_t box[2] = {static_cast<cuuint32_t>(a.kc), static_cast<cuuint32_t>(kTileM)};
@@ -996,6 +1239,19 @@ int igemm_tc_launch(plb_ctx* ctx, const IgemmProblem& p) {
   if (staged) {
     auto encode_out = [&](CUtensorMap* tm, const void* base, int elem_bytes, int box_cols,
                           CUtensorMapSwizzle swz) -> CUresult {
+      if (a.slab) {
+        // [batch, ho, wo, ldy]: a warp's 32 rows are 4 tile rows of 8 pixels
+        const cuuint64_t row = static_cast<cuuint64_t>(p.ldy) * elem_bytes;
+        cuuint64_t dims4[4] = {static_cast<cuuint64_t>(p.cout), static_cast<cuuint64_t>(p.wo),
+                               static_cast<cuuint64_t>(p.ho), static_cast<cuuint64_t>(p.batch)};
+        cuuint64_t strides4[3] = {row, row * p.wo, row * p.wo * p.ho};
+        cuuint32_t box4[4] = {static_cast<cuuint32_t>(box_cols), 8, 4, 1};
+        cuuint32_t estr4[4] = {1, 1, 1, 1};
+        return g_encode_tiled(tm, elem_bytes == 1 ? CU_TENSOR_MAP_DATA_TYPE_UINT8 : CU_TENSOR_MAP_DATA_TYPE_UINT32,
+                              4, const_cast<void*>(base), dims4, strides4, box4, estr4,
+                              CU_TENSOR_MAP_INTERLEAVE_NONE, swz, CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
+                              CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+      }
       cuuint64_t dims[2] = {static_cast<cuuint64_t>(p.cout), static_cast<cuuint64_t>(p.m_total)};
       cuuint64_t strides[1] = {static_cast<cuuint64_t>(p.ldy) * elem_bytes};
       cuuint32_t box[2] = {static_cast<cuuint32_t>(box_cols), 32};
@@ -1021,7 +1277,7 @@ int igemm_tc_launch(plb_ctx* ctx, const IgemmProblem& p) {
     if (r != CUDA_SUCCESS) return fail(PLB_E_CUDA, "cuTensorMapEncodeTiled(output) failed: %d", (int)r);
   }
 
-  const size_t smem = static_cast<size_t>(a.staging_bytes) + (a.resident_b ? resident_bytes : 0) +
+  const size_t smem = static_cast<size_t>(a.staging_bytes) + a.resident_bytes +
                       static_cast<size_t>(stages) * ring_stage_bytes + kCtrlBytes + 1024;
   if (smem > 227 * 1024) return fail(PLB_E_UNSUPPORTED, "pipeline needs %zu bytes of shared memory", smem);
   IgemmKernel kernel = pick_kernel(p.out_mode, p.epi.act, staged);
@@ -1032,13 +1288,36 @@ int igemm_tc_launch(plb_ctx* ctx, const IgemmProblem& p) {
     PLB_CUDA(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024));
     configured.push_back(key);
   }
-  const long tiles = static_cast<long>(tiles_m) * a.tiles_n;
+  const long tiles = static_cast<long>(tiles_m_eff) * a.tiles_n;
   if (tiles > 0x7fffffffL) return fail(PLB_E_UNSUPPORTED, "too many tiles");
   a.num_tiles = static_cast<int>(tiles);
   const unsigned grid = static_cast<unsigned>(tiles < ctx->sm_count ? tiles : ctx->sm_count);
+#ifdef PLB_TC_TIMING
+  static long long* d_timing = nullptr;
+  if (!d_timing) PLB_CUDA(cudaMalloc(&d_timing, 256 * 16 * sizeof(long long)));
+  PLB_CUDA(cudaMemsetAsync(d_timing, 0, 256 * 16 * sizeof(long long), ctx->stream));
+  a.timing = d_timing;
+#endif
   PLB_CUDA(launch_kernel(kernel, dim3(grid), dim3(kThreads), smem, ctx->stream, tmA, tmB, tmRes, tmOutW,
                          tmOutB, a));
+#ifdef PLB_TC_TIMING
+  if (env_int("PLB_TC_TIMING_PRINT", 0)) {
+    std::vector<long long> h(256 * 16);
+    PLB_CUDA(cudaStreamSynchronize(ctx->stream));
+    PLB_CUDA(cudaMemcpy(h.data(), d_timing, h.size() * sizeof(long long), cudaMemcpyDeviceToHost));
+    double avg[16] = {};
+    for (unsigned b = 0; b < grid; ++b)
+      for (int i = 0; i < 16; ++i) avg[i] += static_cast<double>(h[b * 16 + i]) / grid;
+    fprintf(stderr,
+            "[tc timing] tiles %ld grid %u slab %d bn %d kc %d ksteps %d stages %d | producer: wait_empty %.0f total %.0f | "
+            "mma: wait_acc_empty %.0f wait_full %.0f issue %.0f | epilogue warp0: wait_acc_full %.0f wait_store_read %.0f "
+            "tmem_ld %.0f math+store %.0f (cycles per CTA)\n",
+            tiles, grid, a.slab, a.bn, a.kc, a.ksteps, a.stages, avg[0], avg[1], avg[2], avg[3], avg[4], avg[6], avg[7],
+            avg[8], avg[9]);
+  }
+#endif
   ctx->launches++;
+  if (a.slab) ctx->window_launches++;
   return PLB_OK;
 }
 

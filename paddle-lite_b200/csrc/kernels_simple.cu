@@ -324,6 +324,78 @@ __global__ void __launch_bounds__(kBlock)
   }
 }
 
+// Bytes a,b,c,d[i] -> w[i] = {a[i], b[i], c[i], d[i]}: a 4x4 byte transpose in 6 permutes.
+__device__ __forceinline__ void transpose4x4(uint32_t a, uint32_t b, uint32_t c, uint32_t d, uint32_t (&w)[4]) {
+  const uint32_t t0 = __byte_perm(a, b, 0x5140), t1 = __byte_perm(a, b, 0x7362);
+  const uint32_t t2 = __byte_perm(c, d, 0x5140), t3 = __byte_perm(c, d, 0x7362);
+  w[0] = __byte_perm(t0, t2, 0x5410);
+  w[1] = __byte_perm(t0, t2, 0x7632);
+  w[2] = __byte_perm(t1, t3, 0x5410);
+  w[3] = __byte_perm(t1, t3, 0x7632);
+}
+
+// ---- int8 sparse 1x1, shared-memory slab + dp4a.
+// A block owns 1024 consecutive pixels of one image: it stages x[all cin][1024] in shared memory
+// once, then each thread produces every output channel for its 4 pixels.  Non-zeros are walked in
+// groups of four (ascending input channel, zero padded): four 32-bit shared loads fetch 4 pixels
+// of the 4 input channels, a 4x4 byte transpose turns them into one word per pixel, and one dp4a
+// per pixel accumulates the 4 products.  Integer sums, so the order does not matter.
+__global__ void __launch_bounds__(kBlock)
+    sparse_i8_slab_kernel(const SparseGeom g, const int8_t* __restrict__ x, const int* __restrict__ grp_ptr,
+                          const uint2* __restrict__ grp_idx, const uint32_t* __restrict__ grp_w,
+                          const EpiParams e, void* __restrict__ y) {
+  pdl_sync_with_previous_kernel();
+  extern __shared__ uint32_t slab[];  // [cin][256 words]
+  const long n = blockIdx.y;
+  const int p0 = blockIdx.x * 1024;
+  const int8_t* xb = x + n * g.cin * static_cast<long>(g.hw);
+  for (int c = 0; c < g.cin; ++c) {
+    const int p = p0 + threadIdx.x * 4;
+    uint32_t v = 0;
+    if (p < g.hw) v = __ldg(reinterpret_cast<const uint32_t*>(xb + static_cast<long>(c) * g.hw + p));
+    slab[c * 256 + threadIdx.x] = v;
+  }
+  __syncthreads();
+  const int p = p0 + threadIdx.x * 4;
+  if (p >= g.hw) return;
+  const uint32_t* col = slab + threadIdx.x;
+  const bool relu6 = e.act == PLB_ACT_RELU6, i8 = g.out_mode == OUT_I8;
+  for (int oc = 0; oc < g.cout; ++oc) {
+    int acc0 = 0, acc1 = 0, acc2 = 0, acc3 = 0;
+    const int g1 = grp_ptr[oc + 1];
+    for (int t = grp_ptr[oc]; t < g1; ++t) {
+      const uint2 idx = __ldg(grp_idx + t);
+      const uint32_t wv = __ldg(grp_w + t);
+      uint32_t px[4];
+      transpose4x4(col[(idx.x & 0xffffu) * 256], col[(idx.x >> 16) * 256], col[(idx.y & 0xffffu) * 256],
+                   col[(idx.y >> 16) * 256], px);
+      acc0 = __dp4a(static_cast<int>(px[0]), static_cast<int>(wv), acc0);
+      acc1 = __dp4a(static_cast<int>(px[1]), static_cast<int>(wv), acc1);
+      acc2 = __dp4a(static_cast<int>(px[2]), static_cast<int>(wv), acc2);
+      acc3 = __dp4a(static_cast<int>(px[3]), static_cast<int>(wv), acc3);
+    }
+    const float sc = e.scale[oc], bi = e.bias[oc];
+    float v0 = act_apply(fmaf(static_cast<float>(acc0), sc, bi), e.act, e.alpha);
+    float v1 = act_apply(fmaf(static_cast<float>(acc1), sc, bi), e.act, e.alpha);
+    float v2 = act_apply(fmaf(static_cast<float>(acc2), sc, bi), e.act, e.alpha);
+    float v3 = act_apply(fmaf(static_cast<float>(acc3), sc, bi), e.act, e.alpha);
+    (void)relu6;
+    const long off = (n * g.cout + oc) * static_cast<long>(g.hw) + p;
+    if (i8) {
+      // clamp, then round to nearest even with the 1.5*2^23 trick (result in the low byte)
+      v0 = fminf(fmaxf(v0, -127.f), 127.f) + 12582912.f;
+      v1 = fminf(fmaxf(v1, -127.f), 127.f) + 12582912.f;
+      v2 = fminf(fmaxf(v2, -127.f), 127.f) + 12582912.f;
+      v3 = fminf(fmaxf(v3, -127.f), 127.f) + 12582912.f;
+      *reinterpret_cast<uint32_t*>(static_cast<int8_t*>(y) + off) =
+          __byte_perm(__byte_perm(__float_as_uint(v0), __float_as_uint(v1), 0x0040),
+                      __byte_perm(__float_as_uint(v2), __float_as_uint(v3), 0x0040), 0x5410);
+    } else {
+      *reinterpret_cast<float4*>(static_cast<float*>(y) + off) = make_float4(v0, v1, v2, v3);
+    }
+  }
+}
+
 // fp32: accumulator starts at the bias, one fused multiply-add per non-zero weight.
 __global__ void __launch_bounds__(kBlock)
     sparse_f32_kernel(const SparseGeom g, const float* __restrict__ x, const int* __restrict__ row_ptr,
@@ -340,6 +412,73 @@ __global__ void __launch_bounds__(kBlock)
   const int t1 = row_ptr[oc + 1];
   for (int t = row_ptr[oc]; t < t1; ++t) v = fmaf(val[t], xb[static_cast<long>(col[t]) * g.hw], v);
   y[(n * g.cout + oc) * static_cast<long>(g.hw) + p] = act_apply(v, act, alpha);
+}
+
+// fp32 with the input slab in shared memory: a block stages x[all cin][256*VEC pixels] of one
+// image and each thread walks every output channel for VEC consecutive pixels.  Per pixel the
+// sum is formed exactly as above: bias first, then one fmaf per non-zero in stored order.
+template <int VEC>
+__global__ void __launch_bounds__(kBlock)
+    sparse_f32_slab_kernel(const SparseGeom g, const float* __restrict__ x, const int* __restrict__ row_ptr,
+                           const int* __restrict__ col, const float* __restrict__ val,
+                           const float* __restrict__ bias, const int act, const float alpha,
+                           float* __restrict__ y) {
+  pdl_sync_with_previous_kernel();
+  extern __shared__ uint32_t slab[];
+  float* sl = reinterpret_cast<float*>(slab);  // [cin][256*VEC]
+  constexpr int kPix = kBlock * VEC;
+  const long n = blockIdx.y;
+  const int p = blockIdx.x * kPix + threadIdx.x * VEC;
+  const float* xb = x + n * g.cin * static_cast<long>(g.hw);
+  for (int c = 0; c < g.cin; ++c) {
+    float v[VEC];
+#pragma unroll
+    for (int i = 0; i < VEC; ++i) v[i] = 0.f;
+    if (p < g.hw) {
+      const float* src = xb + static_cast<long>(c) * g.hw + p;
+      if (VEC == 4) {
+        const float4 t = __ldg(reinterpret_cast<const float4*>(src));
+        v[0] = t.x; v[1 % VEC] = t.y; v[2 % VEC] = t.z; v[3 % VEC] = t.w;
+      } else if (VEC == 2) {
+        const float2 t = __ldg(reinterpret_cast<const float2*>(src));
+        v[0] = t.x; v[1 % VEC] = t.y;
+      } else {
+        v[0] = __ldg(src);
+      }
+    }
+#pragma unroll
+    for (int i = 0; i < VEC; ++i) sl[c * kPix + threadIdx.x * VEC + i] = v[i];
+  }
+  __syncthreads();
+  if (p >= g.hw) return;
+  const float* colp = sl + threadIdx.x * VEC;
+  for (int oc = 0; oc < g.cout; ++oc) {
+    float acc[VEC];
+    const float b = bias ? bias[oc] : 0.f;
+#pragma unroll
+    for (int i = 0; i < VEC; ++i) acc[i] = b;
+    const int t1 = row_ptr[oc + 1];
+    for (int t = row_ptr[oc]; t < t1; ++t) {
+      const float wv = __ldg(val + t);
+      const float* xs = colp + __ldg(col + t) * kPix;
+      if (VEC == 4) {
+        const float4 xv = *reinterpret_cast<const float4*>(xs);
+        acc[0] = fmaf(wv, xv.x, acc[0]); acc[1 % VEC] = fmaf(wv, xv.y, acc[1 % VEC]);
+        acc[2 % VEC] = fmaf(wv, xv.z, acc[2 % VEC]); acc[3 % VEC] = fmaf(wv, xv.w, acc[3 % VEC]);
+      } else if (VEC == 2) {
+        const float2 xv = *reinterpret_cast<const float2*>(xs);
+        acc[0] = fmaf(wv, xv.x, acc[0]); acc[1 % VEC] = fmaf(wv, xv.y, acc[1 % VEC]);
+      } else {
+        acc[0] = fmaf(wv, xs[0], acc[0]);
+      }
+    }
+#pragma unroll
+    for (int i = 0; i < VEC; ++i) acc[i] = act_apply(acc[i], act, alpha);
+    float* dst = y + (n * g.cout + oc) * static_cast<long>(g.hw) + p;
+    if (VEC == 4) *reinterpret_cast<float4*>(dst) = make_float4(acc[0], acc[1 % VEC], acc[2 % VEC], acc[3 % VEC]);
+    else if (VEC == 2) *reinterpret_cast<float2*>(dst) = make_float2(acc[0], acc[1 % VEC]);
+    else dst[0] = acc[0];
+  }
 }
 
 // ------------------------------------------------------------------ glue
@@ -398,15 +537,6 @@ __global__ void __launch_bounds__(kBlock)
 // conflict-free and the strided phase at four-way conflicts.
 constexpr int kTilePix = 128;
 constexpr int kTilePitchW = 17;  // words per pixel row of the shared tile
-
-__device__ __forceinline__ void transpose4x4(uint32_t a, uint32_t b, uint32_t c, uint32_t d, uint32_t (&w)[4]) {
-  const uint32_t t0 = __byte_perm(a, b, 0x5140), t1 = __byte_perm(a, b, 0x7362);
-  const uint32_t t2 = __byte_perm(c, d, 0x5140), t3 = __byte_perm(c, d, 0x7362);
-  w[0] = __byte_perm(t0, t2, 0x5410);
-  w[1] = __byte_perm(t0, t2, 0x7632);
-  w[2] = __byte_perm(t1, t3, 0x5410);
-  w[3] = __byte_perm(t1, t3, 0x7632);
-}
 
 // x [n,c,hw] -> y [n,hw,cpad].  grid = (pixel strips, channel tiles, n); block = 256 threads =
 // 8 warps; a warp handles 4 channel quads x 8 segments of 16 pixels.  hw % 16 == 0.
@@ -670,6 +800,23 @@ int dwconv_launch(plb_ctx* ctx, const ConvGeom& g, const int8_t* x, const int8_t
   return PLB_OK;
 }
 
+int sparse_slab_supported(const SparseGeom& g, const void* x, const void* y) {
+  return g.is_int8 && g.hw % 4 == 0 && g.cin <= 160 && g.cin < 65536 && g.batch <= 65535 &&
+         (reinterpret_cast<uintptr_t>(x) & 3) == 0 && (reinterpret_cast<uintptr_t>(y) & 15) == 0;
+}
+
+int sparse_slab_launch(plb_ctx* ctx, const SparseGeom& g, const int8_t* x, const int* grp_ptr,
+                       const void* grp_idx, const void* grp_w, const EpiParams& epi, void* y) {
+  if (g.batch == 0 || g.hw == 0) return PLB_OK;
+  const size_t smem = static_cast<size_t>(g.cin) * 1024;
+  PLB_CUDA(cudaFuncSetAttribute(sparse_i8_slab_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 164 * 1024));
+  dim3 grid((g.hw + 1023) / 1024, g.batch);
+  PLB_CUDA(launch_kernel(sparse_i8_slab_kernel, grid, dim3(kBlock), smem, ctx->stream, g, x, grp_ptr,
+                         static_cast<const uint2*>(grp_idx), static_cast<const uint32_t*>(grp_w), epi, y));
+  ctx->launches++;
+  return PLB_OK;
+}
+
 int sparse_csr_launch(plb_ctx* ctx, const SparseGeom& g, const void* x, const int* row_ptr,
                       const int* col, const void* val, const float* bias_raw, const EpiParams& epi,
                       void* y) {
@@ -685,6 +832,16 @@ int sparse_csr_launch(plb_ctx* ctx, const SparseGeom& g, const void* x, const in
       dim3 grid((g.hw + kBlock - 1) / kBlock, g.cout, g.batch);
       PLB_CUDA(launch_kernel(sparse_i8_kernel<1>, dim3(grid), dim3(kBlock), 0, ctx->stream, g, static_cast<const int8_t*>(x), row_ptr, col, static_cast<const int8_t*>(val), epi, y));
     }
+  } else if (g.cin <= 160 && g.batch <= 65535 && g.hw > 0) {
+    // shared-memory slab variant: as many pixels per thread as 160 KB of slab and the alignment allow
+    int vec = g.cin <= 40 ? 4 : g.cin <= 80 ? 2 : 1;
+    const uintptr_t align = reinterpret_cast<uintptr_t>(x) | reinterpret_cast<uintptr_t>(y);
+    while (vec > 1 && (g.hw % vec || (align & (4 * vec - 1)))) vec >>= 1;
+    const size_t smem = static_cast<size_t>(g.cin) * kBlock * vec * 4;
+    auto kern = vec == 4 ? sparse_f32_slab_kernel<4> : vec == 2 ? sparse_f32_slab_kernel<2> : sparse_f32_slab_kernel<1>;
+    PLB_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, 164 * 1024));
+    dim3 grid((g.hw + kBlock * vec - 1) / (kBlock * vec), g.batch);
+    PLB_CUDA(launch_kernel(kern, grid, dim3(kBlock), smem, ctx->stream, g, static_cast<const float*>(x), row_ptr, col, static_cast<const float*>(val), bias_raw, epi.act, epi.alpha, static_cast<float*>(y)));
   } else {
     dim3 grid((g.hw + kBlock - 1) / kBlock, g.cout, g.batch);
     PLB_CUDA(launch_kernel(sparse_f32_kernel, dim3(grid), dim3(kBlock), 0, ctx->stream, g, static_cast<const float*>(x), row_ptr, col, static_cast<const float*>(val), bias_raw, epi.act, epi.alpha, static_cast<float*>(y)));

@@ -45,6 +45,12 @@ int sparse_csr_launch(plb_ctx* ctx, const SparseGeom& g, const void* x, const in
                       const int* col, const void* val, const float* bias_raw, const EpiParams& epi,
                       void* y);
 
+// int8 variant that stages the input slab in shared memory and walks non-zeros four at a time
+// with dp4a (grp_ptr [cout+1], grp_idx = 4 x uint16 input channels, grp_w = 4 x int8 weights).
+int sparse_slab_supported(const SparseGeom& g, const void* x, const void* y);
+int sparse_slab_launch(plb_ctx* ctx, const SparseGeom& g, const int8_t* x, const int* grp_ptr,
+                       const void* grp_idx, const void* grp_w, const EpiParams& epi, void* y);
+
 int calib_f32_to_i8_launch(plb_ctx* ctx, const float* x, int8_t* q, size_t n, float scale);
 int calib_i8_to_f32_launch(plb_ctx* ctx, const int8_t* q, float* y, size_t n, float scale);
 int nchw_to_nhwc_i8_launch(plb_ctx* ctx, const int8_t* x, int8_t* y, int n, int c, int h, int w,

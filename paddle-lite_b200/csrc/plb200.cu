@@ -139,6 +139,7 @@ struct plb_sparse {
   plb_sparse_desc d;
   int nnz = 0;
   DeviceBuf row_ptr, col, val, bias_raw;
+  DeviceBuf grp_ptr, grp_idx, grp_w;  // int8: non-zeros in groups of four for the slab kernel
   DeviceBuf scale, bias;
   float alpha = 0.f;
   plb_conv* dense = nullptr;  // densified tensor-core variant
@@ -211,6 +212,7 @@ int plb_ctx_set_workspace(plb_ctx* ctx, void* dptr, size_t bytes) {
 }
 
 long plb_ctx_launch_count(const plb_ctx* ctx) { return ctx ? ctx->launches : 0; }
+long plb_ctx_window_launch_count(const plb_ctx* ctx) { return ctx ? ctx->window_launches : 0; }
 
 // ------------------------------------------------------------------ conv
 
@@ -734,6 +736,27 @@ int plb_sparse_prepare(plb_ctx* ctx, const plb_sparse_desc* desc, const void* no
   else rc = s->val.upload(valf.data(), valf.size() * sizeof(float));
   if (rc) return rc;
   if (d.is_int8) {
+    std::vector<int> gptr(d.cout + 1, 0);
+    std::vector<uint32_t> gidx, gw;
+    for (int oc = 0; oc < d.cout; ++oc) {
+      const auto& r = rows[oc];
+      for (size_t t = 0; t < r.size(); t += 4) {
+        uint32_t ic[4] = {0, 0, 0, 0}, wv = 0;
+        for (size_t j = 0; j < 4 && t + j < r.size(); ++j) {
+          ic[j] = static_cast<uint32_t>(r[t + j].first);
+          wv |= (static_cast<uint32_t>(static_cast<int>(r[t + j].second)) & 0xffu) << (8 * j);
+        }
+        gidx.push_back(ic[0] | (ic[1] << 16));
+        gidx.push_back(ic[2] | (ic[3] << 16));
+        gw.push_back(wv);
+      }
+      gptr[oc + 1] = static_cast<int>(gw.size());
+    }
+    if ((rc = s->grp_ptr.upload(gptr.data(), gptr.size() * sizeof(int)))) return rc;
+    if ((rc = s->grp_idx.upload(gidx.data(), gidx.size() * sizeof(uint32_t)))) return rc;
+    if ((rc = s->grp_w.upload(gw.data(), gw.size() * sizeof(uint32_t)))) return rc;
+  }
+  if (d.is_int8) {
     Folded f = fold(d.cout, wscale_h, n_wscale, bias_h, d.in_scale,
                     d.out_dtype == PLB_OUT_I8 ? d.out_scale : 1.f, d.act, d.act_alpha, d.leaky_compat);
     const bool i8 = d.out_dtype == PLB_OUT_I8;
@@ -775,6 +798,9 @@ int plb_sparse_run(plb_sparse* sp, const void* x, void* y, int batch) {
   g.out_mode = sp->d.out_dtype == PLB_OUT_I8 ? OUT_I8 : OUT_F32;
   EpiParams e;
   e.scale = sp->scale.as<float>(); e.bias = sp->bias.as<float>(); e.act = sp->d.act; e.alpha = sp->alpha;
+  if (sparse_slab_supported(g, x, y))
+    return sparse_slab_launch(sp->ctx, g, static_cast<const int8_t*>(x), sp->grp_ptr.as<int>(), sp->grp_idx.p,
+                              sp->grp_w.p, e, y);
   return sparse_csr_launch(sp->ctx, g, x, sp->row_ptr.as<int>(), sp->col.as<int>(), sp->val.p,
                            sp->bias_raw.as<float>(), e, y);
 }

@@ -81,6 +81,30 @@ def test_dense_conv_bit_exact(plb, ctx, case, impl):
              impl=impl)
 
 
+# (n, cin, h, w, cout, k, pads, dil, act)
+WINDOW_CASES = [
+    (2, 64, 56, 56, 64, 3, (1, 1, 1, 1), (1, 1), 1),      # the 3x3 layers of the first residual stage
+    (3, 128, 14, 14, 32, 3, (1, 1, 1, 1), (1, 1), 1),     # 128-byte rows, image smaller than a tile
+    (1, 96, 12, 19, 64, 3, (1, 1, 1, 1), (1, 1), 0),      # three 32-byte channel chunks, ragged tiles
+    (2, 64, 20, 13, 32, (3, 2), (0, 1, 2, 0), (2, 1), 2),  # asymmetric padding, dilation, 3x2 filter
+    (1, 32, 17, 23, 64, 5, (2, 2, 2, 2), (1, 1), 3),      # 5x5
+    (1, 40, 9, 9, 32, 3, (0, 0, 0, 0), (1, 1), 0),        # no padding, channels padded to 64
+]
+
+
+@pytest.mark.parametrize("case", WINDOW_CASES, ids=lambda c: "x".join(map(str, c[:5])))
+def test_window_mode_bit_exact(plb, ctx, case, monkeypatch):
+    """Stride-1 filters in window mode (one fetch of a tile's input window, taps addressed by
+    shifted matrix descriptors), forced on for shapes the heuristic would leave to im2col."""
+    monkeypatch.setenv("PLB_TC_SLAB", "1")
+    monkeypatch.setenv("PLB_TC_BN", "256")  # one channel tile even though the problem is small
+    n, cin, h, w, cout, k, pads, dil, act = case
+    xq, in_s, wq, ws, bias = conv_case(hash(case[:5]) % 10000, n, cin, h, w, cout, k)
+    before = ctx.window_launch_count()
+    run_case(plb, ctx, xq, in_s, wq, ws, bias, pads=pads, dil=dil, act=act, alpha=6.0 if act == 2 else 0.1)
+    assert ctx.window_launch_count() >= before + 3, "window mode was not taken"
+
+
 def test_asymmetric_pad_dilation(plb, ctx):
     xq, in_s, wq, ws, bias = conv_case(77, 2, 32, 13, 10, 32, (3, 2))
     for impl in (1, 0):
@@ -165,6 +189,29 @@ def test_nhwc_entry_and_fused_add_relu(plb, ctx):
     assert np.array_equal(y, y_ref)
     yf, yq = conv.run_nhwc_add_relu(x_nhwc, dev(np.ascontiguousarray(res.transpose(0, 2, 3, 1))), next_s)
     ctx.sync()
+    assert np.array_equal(yf.cpu().numpy().transpose(0, 3, 1, 2), s_ref)
+    assert np.array_equal(yq.cpu().numpy().transpose(0, 3, 1, 2), q_ref)
+
+
+def test_window_mode_fused_add_relu(plb, ctx, monkeypatch):
+    """conv3x3 + residual add + relu + calib in window mode: residual tiles and both outputs move
+    through the four-dimensional tensor maps."""
+    monkeypatch.setenv("PLB_TC_SLAB", "1")
+    monkeypatch.setenv("PLB_TC_BN", "256")
+    xq, in_s, wq, ws, bias = conv_case(21, 2, 64, 21, 18, 64, 3)
+    acc = O.conv_acc_i32(xq, wq, pads=(1, 1, 1, 1))
+    y_ref = O.epilogue(acc, ws, in_s, bias, O.ACT_NONE, 0.0)
+    rng = np.random.default_rng(4)
+    res = rng.standard_normal(y_ref.shape).astype(np.float32)
+    s_ref = np.maximum(y_ref + res, np.float32(0))
+    next_s = float(np.abs(s_ref).max() / 127)
+    q_ref = O.calib_f32_to_i8(s_ref, next_s)
+    x_nhwc = dev(np.ascontiguousarray(xq.transpose(0, 2, 3, 1)))
+    conv = plb.Conv(ctx, wq, ws, in_s, bias, in_hw=(21, 18), pads=(1, 1, 1, 1))
+    before = ctx.window_launch_count()
+    yf, yq = conv.run_nhwc_add_relu(x_nhwc, dev(np.ascontiguousarray(res.transpose(0, 2, 3, 1))), next_s)
+    ctx.sync()
+    assert ctx.window_launch_count() == before + 1
     assert np.array_equal(yf.cpu().numpy().transpose(0, 3, 1, 2), s_ref)
     assert np.array_equal(yq.cpu().numpy().transpose(0, 3, 1, 2), q_ref)
 
