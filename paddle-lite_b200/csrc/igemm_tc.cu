@@ -136,16 +136,6 @@ __device__ __forceinline__ void tma_load_2d(uint32_t dst, const CUtensorMap* map
       "l"(reinterpret_cast<uint64_t>(map)), "r"(bar), "r"(c0), "r"(c1)
       : "memory");
 }
-__device__ __forceinline__ void tma_load_im2col_4d(uint32_t dst, const CUtensorMap* map,
-                                                   uint32_t bar, int c, int w, int h, int n,
-                                                   uint16_t off_w, uint16_t off_h) {
-  asm volatile(
-      "cp.async.bulk.tensor.4d.shared::cluster.global.im2col.mbarrier::complete_tx::bytes"
-      " [%0], [%1, {%3, %4, %5, %6}], [%2], {%7, %8};" ::"r"(dst),
-      "l"(reinterpret_cast<uint64_t>(map)), "r"(bar), "r"(c), "r"(w), "r"(h), "r"(n), "h"(off_w),
-      "h"(off_h)
-      : "memory");
-}
 __device__ __forceinline__ void tma_load_4d(uint32_t dst, const CUtensorMap* map, uint32_t bar, int c0,
                                             int c1, int c2, int c3) {
   asm volatile(
@@ -584,6 +574,39 @@ __device__ __forceinline__ void epilogue_chunk_staged(const IgemmArgs& a, const 
   sts128(st_b_row + (((byte_chunk0 + 1) ^ b_swz_mask) << 4), q[4], q[5], q[6], q[7]);
 }
 
+// ---------------------------------------------------------------- MMA issue sequences
+// A 128 x 64 x 32 MMA keeps the tensor core busy for under 60 cycles, so the issuing warp can
+// afford only a handful of instructions per MMA: the sequences below are fully unrolled for the
+// common shapes, which turns every descriptor into "loop-invariant base + constant".
+
+// MPS MMAs covering one K step (MPS * 32 bytes of K) of one pair of operand tiles.
+template <int MPS>
+__device__ __forceinline__ void issue_kstep(uint32_t d_tmem, uint32_t a_lo, uint32_t hi_a, uint32_t b_lo,
+                                            uint32_t hi_b, uint32_t idesc, uint32_t accumulate, bool leader) {
+  tc_mma_i8_halves(d_tmem, a_lo, hi_a, b_lo, hi_b, idesc, accumulate, leader);
+#pragma unroll
+  for (int j = 1; j < MPS; ++j) tc_mma_i8_halves(d_tmem, a_lo + 2u * j, hi_a, b_lo + 2u * j, hi_b, idesc, 1u, leader);
+}
+
+// All taps of one window-mode tile: KH x KW taps, CC channel chunks, MPS MMAs per chunk.
+template <int KH, int KW, int CC, int MPS>
+__device__ __forceinline__ void issue_window(uint32_t d_tmem, uint32_t slab_lo, uint32_t row_lo, uint32_t col_lo,
+                                             uint32_t plane_lo, uint32_t hi_a, uint32_t b_lo, uint32_t stage_b_lo,
+                                             uint32_t hi_b, uint32_t idesc, bool leader) {
+#pragma unroll
+  for (int r = 0; r < KH; ++r) {
+#pragma unroll
+    for (int sx = 0; sx < KW; ++sx) {
+#pragma unroll
+      for (int cc = 0; cc < CC; ++cc) {
+        const int ks = (r * KW + sx) * CC + cc;
+        issue_kstep<MPS>(d_tmem, slab_lo + r * row_lo + sx * col_lo + cc * plane_lo, hi_a, b_lo + ks * stage_b_lo, hi_b,
+                         idesc, ks > 0 ? 1u : 0u, leader);
+      }
+    }
+  }
+}
+
 // ---------------------------------------------------------------- the kernel
 // Persistent: one CTA per SM walks tiles t = blockIdx.x, blockIdx.x + gridDim.x, ...;
 // consecutive tile ids share the same 128 pixels (channel tile fastest) so that CTAs running
@@ -768,6 +791,16 @@ __global__ void __launch_bounds__(kThreads, 1)
     const uint32_t hi_a = a.slab ? ((hi_b & 0xFFFFC000u) | ((static_cast<uint32_t>(a.slab_w * a.kc) >> 4) & 0x3FFFu)) : hi_b;
     const uint32_t lo_flags = 1u << 16;  // leading-dimension byte offset field (unused by swizzled K-major tiles)
     const int nb_mask = nb - 1, nb_shift = nb == 4 ? 2 : 1;
+    // window mode: descriptor steps per filter row / filter column / channel chunk
+    const uint32_t row_lo = static_cast<uint32_t>(a.slab_w * a.kc * a.dil_h) >> 4;
+    const uint32_t col_lo = static_cast<uint32_t>(a.dil_w * a.kc) >> 4;
+    const uint32_t plane_lo = static_cast<uint32_t>(a.plane_bytes) >> 4;
+    int window_shape = 0;  // which unrolled issue sequence applies
+    if (a.slab && a.kh == 3 && a.kw == 3) {
+      if (a.cchunks == 1 && mma_per_stage == 2) window_shape = 1;
+      if (a.cchunks == 1 && mma_per_stage == 4) window_shape = 2;
+      if (a.cchunks == 2 && mma_per_stage == 4) window_shape = 3;
+    }
     int s = 0, it = 0;
     uint32_t full_parity = 0;
     bool ok = true;
@@ -799,19 +832,24 @@ __global__ void __launch_bounds__(kThreads, 1)
         // is a function of the shared-memory address, so a start address shifted by whole
         // pixels addresses the same bytes the copy engine wrote.
         const uint32_t slab_lo = ring_lo + s * stage_lo;
-        const uint32_t row_lo = static_cast<uint32_t>(a.slab_w * a.kc * a.dil_h) >> 4;
-        const uint32_t col_lo = static_cast<uint32_t>(a.dil_w * a.kc) >> 4;
-        const uint32_t plane_lo = static_cast<uint32_t>(a.plane_bytes) >> 4;
-        uint32_t b_lo = bres_lo;
-        uint32_t row_a = slab_lo;
-        for (int r = 0; r < a.kh; ++r, row_a += row_lo) {
-          uint32_t tap_a = row_a;
-          for (int sx = 0; sx < a.kw; ++sx, tap_a += col_lo) {
-            uint32_t a_lo = tap_a;
-            for (int cc = 0; cc < a.cchunks; ++cc, a_lo += plane_lo, b_lo += stage_b_lo) {
-              for (int j = 0; j < mma_per_stage; ++j) {
-                tc_mma_i8_halves(d_tmem, a_lo + 2u * j, hi_a, b_lo + 2u * j, hi_b, idesc, accumulate, leader);
-                accumulate = 1;
+        if (window_shape == 1) {
+          issue_window<3, 3, 1, 2>(d_tmem, slab_lo, row_lo, col_lo, plane_lo, hi_a, bres_lo, stage_b_lo, hi_b, idesc, leader);
+        } else if (window_shape == 2) {
+          issue_window<3, 3, 1, 4>(d_tmem, slab_lo, row_lo, col_lo, plane_lo, hi_a, bres_lo, stage_b_lo, hi_b, idesc, leader);
+        } else if (window_shape == 3) {
+          issue_window<3, 3, 2, 4>(d_tmem, slab_lo, row_lo, col_lo, plane_lo, hi_a, bres_lo, stage_b_lo, hi_b, idesc, leader);
+        } else {
+          uint32_t b_lo = bres_lo;
+          uint32_t row_a = slab_lo;
+          for (int r = 0; r < a.kh; ++r, row_a += row_lo) {
+            uint32_t tap_a = row_a;
+            for (int sx = 0; sx < a.kw; ++sx, tap_a += col_lo) {
+              uint32_t a_lo = tap_a;
+              for (int cc = 0; cc < a.cchunks; ++cc, a_lo += plane_lo, b_lo += stage_b_lo) {
+                for (int j = 0; j < mma_per_stage; ++j) {
+                  tc_mma_i8_halves(d_tmem, a_lo + 2u * j, hi_a, b_lo + 2u * j, hi_b, idesc, accumulate, leader);
+                  accumulate = 1;
+                }
               }
             }
           }
@@ -833,11 +871,13 @@ __global__ void __launch_bounds__(kThreads, 1)
         const uint32_t a_lo = ring_lo + s * stage_lo;
         const uint32_t b_lo = a.resident_b ? b_res_lo : a_lo + (static_cast<uint32_t>(stage_a) >> 4);
         // advance 32 bytes of K inside the swizzle span: +2 in the (addr >> 4) field
-        for (int j = 0; j < mma_per_stage; ++j) {
-          tc_mma_i8_halves(d_tmem, a_lo + 2u * j, hi_a, b_lo + 2u * j, hi_b, idesc, accumulate, leader);
-          accumulate = 1;
-        }
+        TT_START();
+        if (mma_per_stage == 4) issue_kstep<4>(d_tmem, a_lo, hi_a, b_lo, hi_b, idesc, accumulate, leader);
+        else if (mma_per_stage == 2) issue_kstep<2>(d_tmem, a_lo, hi_a, b_lo, hi_b, idesc, accumulate, leader);
+        else issue_kstep<1>(d_tmem, a_lo, hi_a, b_lo, hi_b, idesc, accumulate, leader);
+        accumulate = 1;
         tc_commit_if(smem_u32(&empty_bar[s]), leader);  // frees the stage when these MMAs retire
+        TT_STOP(2);
         if (++s == a.stages) {
           s = 0;
           full_parity ^= 1;
