@@ -796,6 +796,7 @@ __global__ void __launch_bounds__(kThreads, 1)
     const uint32_t col_lo = static_cast<uint32_t>(a.dil_w * a.kc) >> 4;
     const uint32_t plane_lo = static_cast<uint32_t>(a.plane_bytes) >> 4;
     int window_shape = 0;  // which unrolled issue sequence applies
+    if (a.slab && a.kh == 4 && a.kw == 1 && a.cchunks == 1 && mma_per_stage == 2) window_shape = 4;  // row-folded 7x7 stem
     if (a.slab && a.kh == 3 && a.kw == 3) {
       if (a.cchunks == 1 && mma_per_stage == 2) window_shape = 1;
       if (a.cchunks == 1 && mma_per_stage == 4) window_shape = 2;
@@ -838,6 +839,8 @@ __global__ void __launch_bounds__(kThreads, 1)
           issue_window<3, 3, 1, 4>(d_tmem, slab_lo, row_lo, col_lo, plane_lo, hi_a, bres_lo, stage_b_lo, hi_b, idesc, leader);
         } else if (window_shape == 3) {
           issue_window<3, 3, 2, 4>(d_tmem, slab_lo, row_lo, col_lo, plane_lo, hi_a, bres_lo, stage_b_lo, hi_b, idesc, leader);
+        } else if (window_shape == 4) {
+          issue_window<4, 1, 1, 2>(d_tmem, slab_lo, row_lo, col_lo, plane_lo, hi_a, bres_lo, stage_b_lo, hi_b, idesc, leader);
         } else {
           uint32_t b_lo = bres_lo;
           uint32_t row_a = slab_lo;

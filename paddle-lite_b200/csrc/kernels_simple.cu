@@ -671,6 +671,90 @@ __global__ void __launch_bounds__(kBlock)
   dst[1] = make_uint4(words[4], words[5], words[6], words[7]);
 }
 
+// Same layout through shared memory: a block takes kFoldGroup staged rows of one image, i.e.
+// kFoldGroup * fh input rows of every channel, quantises them once into row buffers laid out as
+// [pixel][channel] bytes (with the left/right zero padding), where the kw*cin bytes a staged pixel
+// needs are contiguous, and then copies one unaligned 32-byte window per (staged pixel, folded
+// row).  Lanes are ordered so that a warp writes 1 KiB of consecutive staged bytes.  dil_w == 1.
+constexpr int kFoldGroup = 4;
+
+__device__ __forceinline__ int8_t fold_quant(float v, float inv) {
+  // calib: sat(rne(max(x * inv, -127))); rounding by adding 1.5 * 2^23
+  const float f = fminf(fmaxf(v * inv, -127.f), 127.f) + 12582912.f;
+  return static_cast<int8_t>(__float_as_uint(f) & 0xffu);
+}
+__device__ __forceinline__ int8_t fold_quant(int8_t v, float) { return v; }
+
+template <typename T>
+__global__ void __launch_bounds__(kBlock)
+    fold_rows_fast_kernel(const T* __restrict__ x, int8_t* __restrict__ y, int c, int h, int w, int ht, int wo,
+                          int kw, int fh, int stride_w, int pad_t, int pad_l, float inv, int row_words, int vec4) {
+  pdl_sync_with_previous_kernel();
+  extern __shared__ uint32_t rowbuf[];  // [rows][row_words]
+  int8_t* rb = reinterpret_cast<int8_t*>(rowbuf);
+  const int t0 = blockIdx.x * kFoldGroup;
+  const long n = blockIdx.y;
+  const int rows = min(kFoldGroup, ht - t0) * fh;  // folded input rows this block stages
+  const int hh0 = t0 * fh - pad_t;
+  for (int i = threadIdx.x; i < rows * row_words; i += kBlock) rowbuf[i] = 0;
+  __syncthreads();
+  const int pix = (wo - 1) * stride_w + kw;  // padded pixels a row buffer holds
+  if (vec4 && sizeof(T) == 4) {
+    const int w4 = w >> 2;
+    const int items = rows * c * w4;
+    for (int i = threadIdx.x; i < items; i += kBlock) {
+      const int v4 = i % w4;
+      const int rc = i / w4;
+      const int cc = rc % c, r = rc / c;
+      const int hh = hh0 + r;
+      if (hh < 0 || hh >= h) continue;
+      const float4 v = __ldg(reinterpret_cast<const float4*>(x + ((n * c + cc) * h + hh) * static_cast<long>(w)) + v4);
+      const float f[4] = {v.x, v.y, v.z, v.w};
+      int8_t* dst = rb + r * row_words * 4 + cc;
+#pragma unroll
+      for (int k = 0; k < 4; ++k) {
+        const int pos = v4 * 4 + k + pad_l;
+        if (pos < pix) dst[pos * c] = fold_quant(f[k], inv);
+      }
+    }
+  } else {
+    const int items = rows * c * w;
+    for (int i = threadIdx.x; i < items; i += kBlock) {
+      const int iw = i % w;
+      const int rc = i / w;
+      const int cc = rc % c, r = rc / c;
+      const int hh = hh0 + r;
+      const int pos = iw + pad_l;
+      if (hh < 0 || hh >= h || pos >= pix) continue;
+      rb[r * row_words * 4 + pos * c + cc] = fold_quant(x[((n * c + cc) * h + hh) * static_cast<long>(w) + iw], inv);
+    }
+  }
+  __syncthreads();
+  const int gb = kw * c;  // meaningful bytes of a 32-byte group
+  const int per_t = wo * fh;
+  const int outs = (rows / fh) * per_t;
+  for (int i = threadIdx.x; i < outs; i += kBlock) {
+    const int tl = i / per_t;
+    const int qe = i - tl * per_t;
+    const int q = qe / fh, e = qe - q * fh;
+    const int off = q * stride_w * c;
+    const uint32_t* src = rowbuf + (tl * fh + e) * row_words + (off >> 2);
+    const int sh = (off & 3) * 8;
+    uint32_t a[9], o[8];
+#pragma unroll
+    for (int k = 0; k < 9; ++k) a[k] = src[k];
+#pragma unroll
+    for (int k = 0; k < 8; ++k) {
+      const uint32_t v = __funnelshift_r(a[k], a[k + 1], sh);
+      const int rem = gb - 4 * k;  // bytes of this word that belong to the group
+      o[k] = rem >= 4 ? v : (rem <= 0 ? 0u : (v & ((1u << (8 * rem)) - 1u)));
+    }
+    uint4* dst = reinterpret_cast<uint4*>(y + (((n * ht + t0 + tl) * wo + q) * static_cast<long>(fh) + e) * 32);
+    dst[0] = make_uint4(o[0], o[1], o[2], o[3]);
+    dst[1] = make_uint4(o[4], o[5], o[6], o[7]);
+  }
+}
+
 // [n,hw,c] -> [n,c,hw], 32x32 element tiles.
 template <typename T>
 __global__ void nhwc_to_nchw_kernel(const T* __restrict__ x, T* __restrict__ y, int c, int hw) {
@@ -909,6 +993,23 @@ int fold_rows_launch(plb_ctx* ctx, const void* x, int x_is_f32, int8_t* y, int n
   const long total = static_cast<long>(n) * ht * wo * fh;
   if (total == 0) return PLB_OK;
   if (c * kw > 32) return fail(PLB_E_INVALID, "row folding needs cin * kw <= 32");
+  // row buffer: the padded pixels of one input row plus 9 words of slack for the window reads
+  const int row_words = (((wo - 1) * stride_w + kw) * c + 3) / 4 + 9;
+  if (dil_w == 1 && static_cast<size_t>(row_words) * 4 * kFoldGroup * fh <= 40 * 1024 && n <= 65535) {
+    dim3 grid(static_cast<unsigned>((ht + kFoldGroup - 1) / kFoldGroup), static_cast<unsigned>(n));
+    const size_t smem = static_cast<size_t>(row_words) * 4 * kFoldGroup * fh;
+    const int vec4 = w % 4 == 0 && (reinterpret_cast<uintptr_t>(x) & 15) == 0;
+    if (x_is_f32)
+      PLB_CUDA(launch_kernel(fold_rows_fast_kernel<float>, grid, dim3(kBlock), smem, ctx->stream,
+                             static_cast<const float*>(x), y, c, h, w, ht, wo, kw, fh, stride_w, pad_t, pad_l,
+                             1.f / scale, row_words, vec4));
+    else
+      PLB_CUDA(launch_kernel(fold_rows_fast_kernel<int8_t>, grid, dim3(kBlock), smem, ctx->stream,
+                             static_cast<const int8_t*>(x), y, c, h, w, ht, wo, kw, fh, stride_w, pad_t, pad_l, 1.f,
+                             row_words, 0));
+    ctx->launches++;
+    return PLB_OK;
+  }
   if (x_is_f32)
     PLB_CUDA(launch_kernel(fold_rows_kernel<float>, dim3(blocks_for(total)), dim3(kBlock), 0, ctx->stream,
                            static_cast<const float*>(x), y, c, h, w, ht, wo, kw, fh, stride_w, pad_t, pad_l,
