@@ -50,6 +50,7 @@ struct IgemmArgs {
   int tiles_n, num_tiles;
   int staging_bytes, staging_w_bytes;  // epilogue staging in front of the operand ring
   int stage_b_warp;                    // bytes of int8 staging per epilogue warp
+  int acc_bufs;                        // TMEM accumulator buffers (epilogue groups per buffer = 4 / acc_bufs)
   int resident_b;                      // whole filter of this CTA's channel tile kept in shared memory
   int resident_bytes;                  // its size, rounded up to 1 KiB
   // slab mode (stride-1 filters with several taps): a pipeline stage holds the input window of a
@@ -620,6 +621,9 @@ __global__ void __launch_bounds__(kThreads, 1)
                        const __grid_constant__ CUtensorMap tmRes,
                        const __grid_constant__ CUtensorMap tmOutW,
                        const __grid_constant__ CUtensorMap tmOutB, const IgemmArgs a) {
+#ifdef PLB_TC_TIMING
+  const long long tt_entry = clock64();
+#endif
   extern __shared__ uint8_t smem_raw[];
   const uint32_t raw_addr = smem_u32(smem_raw);
   uint8_t* smem_al = smem_raw + (((raw_addr + 1023u) & ~1023u) - raw_addr);
@@ -645,7 +649,7 @@ __global__ void __launch_bounds__(kThreads, 1)
   // TMEM: nb accumulator buffers of acc_cols columns each (512 columns in total at most)
   uint32_t acc_cols = 32;
   while (acc_cols < static_cast<uint32_t>(a.bn)) acc_cols <<= 1;
-  const int nb = acc_cols <= 128 ? 4 : 2;
+  const int nb = a.acc_bufs;  // 4 or 2 (2 when the tile is 256 wide or a CTA has only a tile or two to do)
   const int gpb = kEpilogueGroups / nb;  // epilogue groups sharing one buffer (split by columns)
   const uint32_t tmem_cols = acc_cols * nb < 32 ? 32 : acc_cols * nb;
 
@@ -678,6 +682,9 @@ __global__ void __launch_bounds__(kThreads, 1)
   const uint32_t tmem_base = *tmem_slot;
   // the set-up above overlapped the previous kernel's tail; from here on global memory is touched
   pdl_sync_with_previous_kernel();
+#ifdef PLB_TC_TIMING
+  if (threadIdx.x == 0) a.timing[blockIdx.x * 16 + 10] = clock64() - tt_entry;  // prologue + wait for the previous kernel
+#endif
 
   if (warp == kProducerWarp) {
     // ------------------------------------------------------------ TMA producer
@@ -809,6 +816,10 @@ __global__ void __launch_bounds__(kThreads, 1)
       ok = mbar_wait(smem_u32(bres_bar), 0, abort_flag, a.status, FAULT_WAIT_FULL);
       tc_fence_after();
     }
+#ifdef PLB_TC_TIMING
+    if (lane == 0) a.timing[blockIdx.x * 16 + 11] = clock64() - tt_entry;  // resident filter landed
+    bool tt_first = true;
+#endif
     const uint32_t bres_lo = ((smem_u32(smem_bres) >> 4) & 0x3FFFu) | lo_flags;
     const uint32_t stage_b_lo = static_cast<uint32_t>(stage_b) >> 4;
     const uint32_t stage_lo = static_cast<uint32_t>(stage_bytes) >> 4;
@@ -870,6 +881,10 @@ __global__ void __launch_bounds__(kThreads, 1)
         ok = mbar_wait(smem_u32(&full_bar[s]), full_parity, abort_flag, a.status, FAULT_WAIT_FULL);
         TT_STOP(1);
         if (!ok) break;
+#ifdef PLB_TC_TIMING
+        if (tt_first && lane == 0) a.timing[blockIdx.x * 16 + 12] = clock64() - tt_entry;  // first operands landed
+        tt_first = false;
+#endif
         tc_fence_after();
         const uint32_t a_lo = ring_lo + s * stage_lo;
         const uint32_t b_lo = a.resident_b ? b_res_lo : a_lo + (static_cast<uint32_t>(stage_a) >> 4);
@@ -889,6 +904,9 @@ __global__ void __launch_bounds__(kThreads, 1)
       tc_commit_if(smem_u32(&acc_full[buf]), leader);  // accumulator complete (or drained on a fault)
     }
     if (lane == 0) TT_FLUSH(2, 4);
+#ifdef PLB_TC_TIMING
+    if (lane == 0) a.timing[blockIdx.x * 16 + 13] = clock64() - tt_entry;  // all MMAs issued
+#endif
   } else {
     // ------------------------------------------------------------ epilogue groups
     const int group = warp >> 2;     // 0..3
@@ -1024,6 +1042,9 @@ __global__ void __launch_bounds__(kThreads, 1)
     }
     if (STAGED && lane == 0) bulk_wait_all();  // staging memory must outlive the stores reading it
     if (warp == 0 && lane == 0) TT_FLUSH(6, 4);
+#ifdef PLB_TC_TIMING
+    if (warp == 0 && lane == 0) a.timing[blockIdx.x * 16 + 14] = clock64() - tt_entry;  // epilogue warp 0 finished
+#endif
   }
   tc_fence_before();
   __syncthreads();
@@ -1168,9 +1189,20 @@ int igemm_tc_launch(plb_ctx* ctx, const IgemmProblem& p) {
     staged = false;
   }
   a.staging_w_bytes = staged && want_w ? kEpilogueWarps * 4096 : 0;
+  // With many tiles per CTA four accumulator buffers keep every epilogue group on its own tile;
+  // with one or two tiles the drain of the last tile is what is left exposed, so two groups
+  // share a tile (by column halves) and finish it in half the time.
   {
-    const int acc_cols_h = bn <= 32 ? 32 : (bn <= 64 ? 64 : (bn <= 128 ? 128 : 256));
-    const int wq_h = bn / (acc_cols_h <= 128 ? 1 : 2);
+    const long tiles_total = static_cast<long>(tiles_m) * ((p.cout + bn - 1) / bn);
+    const bool few = tiles_total <= 2L * ctx->sm_count;
+    a.acc_bufs = bn > 128 ? 2 : (few && bn >= 64 ? 2 : 4);
+    a.acc_bufs = env_int("PLB_TC_ACC_BUFS", a.acc_bufs);
+    if (a.acc_bufs != 2 && a.acc_bufs != 4) return fail(PLB_E_INVALID, "accumulator buffers must be 2 or 4");
+    if (a.acc_bufs == 4 && bn > 128) a.acc_bufs = 2;
+    if (a.acc_bufs == 2 && bn < 64) a.acc_bufs = 4;
+  }
+  {
+    const int wq_h = bn / (kEpilogueGroups / a.acc_bufs);
     // 32 rows of wq bytes per warp; 128-byte-swizzled tiles (wq = 128) need 1 KiB alignment, which 4 KiB keeps
     a.stage_b_warp = staged && want_b ? (wq_h == 128 ? 4096 : 32 * wq_h) : 0;
   }
@@ -1305,8 +1337,7 @@ int igemm_tc_launch(plb_ctx* ctx, const IgemmProblem& p) {
                             CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
     };
     CUresult r = CUDA_SUCCESS;
-    const int acc_cols = bn <= 32 ? 32 : (bn <= 64 ? 64 : (bn <= 128 ? 128 : 256));
-    const int wq = bn / (acc_cols <= 128 ? 1 : 2);  // int8 bytes per staged row
+    const int wq = bn / (kEpilogueGroups / a.acc_bufs);  // int8 bytes per staged row
     if (p.out_mode == OUT_ADD_RELU) {
       if (p.residual) r = encode_out(&tmRes, p.residual, 4, 32, CU_TENSOR_MAP_SWIZZLE_128B);
       if (r == CUDA_SUCCESS && p.y_f32) r = encode_out(&tmOutW, p.y_f32, 4, 32, CU_TENSOR_MAP_SWIZZLE_128B);
@@ -1354,9 +1385,10 @@ int igemm_tc_launch(plb_ctx* ctx, const IgemmProblem& p) {
     fprintf(stderr,
             "[tc timing] tiles %ld grid %u slab %d bn %d kc %d ksteps %d stages %d | producer: wait_empty %.0f total %.0f | "
             "mma: wait_acc_empty %.0f wait_full %.0f issue %.0f | epilogue warp0: wait_acc_full %.0f wait_store_read %.0f "
-            "tmem_ld %.0f math+store %.0f (cycles per CTA)\n",
+            "tmem_ld %.0f math+store %.0f | since entry: roles start %.0f, filter resident %.0f, first operands %.0f, "
+            "MMAs issued %.0f, epilogue warp0 done %.0f (cycles per CTA)\n",
             tiles, grid, a.slab, a.bn, a.kc, a.ksteps, a.stages, avg[0], avg[1], avg[2], avg[3], avg[4], avg[6], avg[7],
-            avg[8], avg[9]);
+            avg[8], avg[9], avg[10], avg[11], avg[12], avg[13], avg[14]);
   }
 #endif
   ctx->launches++;
