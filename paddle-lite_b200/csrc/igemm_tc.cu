@@ -50,6 +50,7 @@ struct IgemmArgs {
   int tiles_n, num_tiles;
   int staging_bytes, staging_w_bytes;  // epilogue staging in front of the operand ring
   int stage_b_warp;                    // bytes of int8 staging per epilogue warp
+  int res_prefetch;                    // OUT_ADD_RELU: two residual staging tiles per warp, one chunk fetched ahead
   int acc_bufs;                        // TMEM accumulator buffers (epilogue groups per buffer = 4 / acc_bufs)
   int resident_b;                      // whole filter of this CTA's channel tile kept in shared memory
   int resident_bytes;                  // its size, rounded up to 1 KiB
@@ -638,8 +639,8 @@ __global__ void __launch_bounds__(kThreads, 1)
   uint64_t* empty_bar = full_bar + kMaxStages;
   uint64_t* acc_full = empty_bar + kMaxStages;     // [4] accumulator buffer ready for its epilogue group(s)
   uint64_t* acc_empty = acc_full + kMaxAccBufs;    // [4] accumulator buffer drained
-  uint64_t* res_bar = acc_empty + kMaxAccBufs;     // [16] one per epilogue warp: residual tile landed
-  uint64_t* bres_bar = res_bar + kEpilogueWarps;   // resident filter landed
+  uint64_t* res_bar = acc_empty + kMaxAccBufs;     // [2][16] per epilogue warp and staging tile: residual landed
+  uint64_t* bres_bar = res_bar + 2 * kEpilogueWarps;  // resident filter landed
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bres_bar + 1);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
 
@@ -662,7 +663,7 @@ __global__ void __launch_bounds__(kThreads, 1)
       mbar_init(smem_u32(&acc_full[b]), 1);
       mbar_init(smem_u32(&acc_empty[b]), 4 * gpb);
     }
-    for (int w = 0; w < kEpilogueWarps; ++w) mbar_init(smem_u32(&res_bar[w]), 1);
+    for (int w = 0; w < 2 * kEpilogueWarps; ++w) mbar_init(smem_u32(&res_bar[w]), 1);
     mbar_init(smem_u32(bres_bar), 1);
     *abort_flag = 0;
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
@@ -921,6 +922,12 @@ __global__ void __launch_bounds__(kThreads, 1)
     const int b_swz = wq == 128 ? (lane & 7) : 0;
     const uint32_t my_res_bar = smem_u32(&res_bar[warp]);
     uint32_t res_phase = 0;
+    // residual prefetch: two staging tiles per warp (8 KiB apart per warp), one barrier each
+    const uint32_t pf_tile[2] = {smem_u32(smem_al) + warp * 8192, smem_u32(smem_al) + warp * 8192 + 4096};
+    const uint32_t pf_bar[2] = {smem_u32(&res_bar[warp]), smem_u32(&res_bar[kEpilogueWarps + warp])};
+    uint32_t pf_phase[2] = {0, 0};
+    int pf_cur = 0;
+    bool pf_ready = false;
     bool stores_pending = false;
     bool ok = true;
     TT_DECL(4);
@@ -933,7 +940,97 @@ __global__ void __launch_bounds__(kThreads, 1)
       const long row = static_cast<long>(m0) + quad * 32 + lane;
       const uint32_t lane_addr = tmem_base + my_buf * acc_cols + (static_cast<uint32_t>(quad * 32) << 16);
       bool waited = false;
-      if (STAGED) {
+      if (STAGED && MODE == OUT_ADD_RELU && a.res_prefetch) {
+        // Residual convolutions are bound by the latency of the residual fetch: each chunk needs
+        // its 4 KiB residual tile before it can do anything.  With two staging tiles per warp the
+        // tile of the following chunk (of this or the warp's next output tile) is requested
+        // while the current one is computed and stored.  Flat GEMM tiles only.
+        const int row0 = m0 + quad * 32;
+        const bool active = row0 < a.m_total;
+        const int cbase = col_par * wq;
+        for (int c = cbase; c < cbase + wq; c += 32) {
+          if (n0 + c >= a.cout) break;  // warp-uniform
+          bool drained = false;
+          if (active && !pf_ready) {
+            // nothing was requested ahead for this chunk (first chunk of the warp)
+            if (stores_pending) {
+              if (lane == 0) bulk_wait_read_all();
+              __syncwarp();
+              stores_pending = false;
+              drained = true;
+            }
+            if (lane == 0) {
+              mbar_expect_tx(pf_bar[pf_cur], 4096);
+              tma_load_2d(pf_tile[pf_cur], &tmRes, pf_bar[pf_cur], n0 + c, row0);
+            }
+          }
+          if (!waited) {
+            TT_START();
+            ok = mbar_wait(smem_u32(&acc_full[my_buf]), (it >> nb_shift) & 1, abort_flag, a.status, FAULT_WAIT_ACCUM);
+            TT_STOP(0);
+            tc_fence_after();
+            waited = true;
+            if (!ok) break;
+          }
+          TT_START();
+          uint32_t r[32];
+          tc_ld32(lane_addr + static_cast<uint32_t>(c), r);
+          tc_wait_ld();
+          TT_STOP(2);
+          // where is this warp's next chunk?
+          int nc = c + 32, nrow0 = row0, ncol;
+          bool nvalid = true;
+          if (nc >= cbase + wq || n0 + nc >= a.cout) {
+            const long ntile = tile_l + static_cast<long>(nb) * gridDim.x;
+            nvalid = ntile < a.num_tiles;
+            const int nt = static_cast<int>(nvalid ? ntile : 0);
+            nrow0 = (nt / a.tiles_n) * kTileM + quad * 32;
+            nc = cbase;
+            ncol = (nt % a.tiles_n) * a.bn + nc;
+          } else {
+            ncol = n0 + nc;
+          }
+          nvalid = nvalid && ncol < a.cout && nrow0 < a.m_total;
+          TT_START();
+          if (nvalid) {
+            // the other staging tile was last read by the stores of the previous chunk
+            if (stores_pending && !drained) {
+              if (lane == 0) bulk_wait_read_all();
+              __syncwarp();
+              stores_pending = false;
+              drained = true;
+            }
+            if (lane == 0) {
+              mbar_expect_tx(pf_bar[pf_cur ^ 1], 4096);
+              tma_load_2d(pf_tile[pf_cur ^ 1], &tmRes, pf_bar[pf_cur ^ 1], ncol, nrow0);
+            }
+          }
+          TT_STOP(1);
+          TT_START();
+          if (active) {
+            ok = mbar_wait(pf_bar[pf_cur], pf_phase[pf_cur], abort_flag, a.status, FAULT_WAIT_FULL);
+            pf_phase[pf_cur] ^= 1;
+            if (!ok) break;
+            if (stores_pending && !drained) {  // the int8 staging rows are rewritten below
+              if (lane == 0) bulk_wait_read_all();
+              __syncwarp();
+              stores_pending = false;
+            }
+            epilogue_chunk_staged<MODE, ACT>(a, r, lane, n0 + c, pf_tile[pf_cur], st_b + lane * 32, 0, 0, true);
+            fence_proxy_async_smem();
+            __syncwarp();
+            if (lane == 0) {
+              if (a.y_f32 != nullptr) tma_store_2d(&tmOutW, pf_tile[pf_cur], n0 + c, row0);
+              if (a.y_i8 != nullptr) tma_store_2d(&tmOutB, st_b, n0 + c, row0);
+              bulk_commit();
+            }
+            stores_pending = true;
+          }
+          TT_STOP(3);
+          pf_ready = nvalid;
+          pf_cur ^= 1;
+        }
+      } else if (STAGED) {
         const int row0 = m0 + quad * 32;
         // slab tiles are 16 x 8 pixels: this quadrant owns tile rows quad*4 .. quad*4+3
         int s_w = 0, s_h = 0, s_img = 0;
@@ -1174,7 +1271,6 @@ int igemm_tc_launch(plb_ctx* ctx, const IgemmProblem& p) {
   if (bn < 16 || bn > 256 || bn % 16) return fail(PLB_E_INVALID, "bad channel tile %d", bn);
   a.bn = bn;
   a.tiles_n = (p.cout + bn - 1) / bn;
-  const int stage_bytes = (kTileM + bn) * a.kc;
   // Staged (TMA) epilogue I/O needs power-of-two channel tiles, 16-byte aligned rows and bases.
   const bool want_w = p.out_mode == OUT_F32 || p.out_mode == OUT_ACC ||
                       (p.out_mode == OUT_ADD_RELU && (p.y_f32 != nullptr || p.residual != nullptr));
@@ -1188,7 +1284,12 @@ int igemm_tc_launch(plb_ctx* ctx, const IgemmProblem& p) {
   } else if (!aligned16(p.y)) {
     staged = false;
   }
-  a.staging_w_bytes = staged && want_w ? kEpilogueWarps * 4096 : 0;
+  // Fetching the residual one chunk ahead pays when a CTA has only a few tiles (latency bound);
+  // long runs are bandwidth bound and do better with the wider int8 stores of the plain path.
+  const bool short_run = static_cast<long>(tiles_m) * ((p.cout + bn - 1) / bn) <= 3L * ctx->sm_count;
+  a.res_prefetch = staged && p.out_mode == OUT_ADD_RELU && p.residual != nullptr && !p.im2col &&
+                   env_int("PLB_TC_RES_PREFETCH", short_run ? 1 : 0) != 0;
+  a.staging_w_bytes = staged && want_w ? kEpilogueWarps * (a.res_prefetch ? 8192 : 4096) : 0;
   // With many tiles per CTA four accumulator buffers keep every epilogue group on its own tile;
   // with one or two tiles the drain of the last tile is what is left exposed, so two groups
   // share a tile (by column halves) and finish it in half the time.
@@ -1205,8 +1306,17 @@ int igemm_tc_launch(plb_ctx* ctx, const IgemmProblem& p) {
     const int wq_h = bn / (kEpilogueGroups / a.acc_bufs);
     // 32 rows of wq bytes per warp; 128-byte-swizzled tiles (wq = 128) need 1 KiB alignment, which 4 KiB keeps
     a.stage_b_warp = staged && want_b ? (wq_h == 128 ? 4096 : 32 * wq_h) : 0;
+    if (a.res_prefetch && want_b) a.stage_b_warp = 1024;  // int8 results leave chunk by chunk (32 rows x 32 bytes)
   }
   a.staging_bytes = (a.staging_w_bytes + kEpilogueWarps * a.stage_b_warp + 1023) / 1024 * 1024;
+  if (a.res_prefetch) {
+    // the doubled staging leaves less room for the operand ring: shorter K steps keep three stages
+    while (a.kc > 32 && (225 * 1024 - a.staging_bytes - kCtrlBytes) / ((kTileM + bn) * a.kc) < 3) {
+      a.kc /= 2;
+      a.cchunks = p.cin_pad / a.kc;
+      a.ksteps = a.taps * a.cchunks;
+    }
+  }
   const int tiles_n_h = (p.cout + bn - 1) / bn;
   const int resident_bytes = (a.ksteps * bn * a.kc + 1023) / 1024 * 1024;
   const bool can_resident = env_int("PLB_TC_RESIDENT", 1) != 0 && tiles_n_h == 1 && resident_bytes <= kMaxResidentB;
@@ -1236,6 +1346,7 @@ int igemm_tc_launch(plb_ctx* ctx, const IgemmProblem& p) {
     }
   }
   a.resident_bytes = a.resident_b ? resident_bytes : 0;
+  const int stage_bytes = (kTileM + bn) * a.kc;
   const int ring_stage_bytes = a.slab ? a.cchunks * a.plane_bytes : (a.resident_b ? kTileM * a.kc : stage_bytes);
   // one CTA per SM: spend (almost) all remaining shared memory on the operand ring
   int stages = (225 * 1024 - a.staging_bytes - kCtrlBytes - a.resident_bytes) / ring_stage_bytes;
@@ -1341,8 +1452,10 @@ int igemm_tc_launch(plb_ctx* ctx, const IgemmProblem& p) {
     if (p.out_mode == OUT_ADD_RELU) {
       if (p.residual) r = encode_out(&tmRes, p.residual, 4, 32, CU_TENSOR_MAP_SWIZZLE_128B);
       if (r == CUDA_SUCCESS && p.y_f32) r = encode_out(&tmOutW, p.y_f32, 4, 32, CU_TENSOR_MAP_SWIZZLE_128B);
-      if (r == CUDA_SUCCESS && p.y_i8)
-        r = encode_out(&tmOutB, p.y_i8, 1, wq, wq == 128 ? CU_TENSOR_MAP_SWIZZLE_128B : CU_TENSOR_MAP_SWIZZLE_NONE);
+      if (r == CUDA_SUCCESS && p.y_i8) {
+        if (a.res_prefetch) r = encode_out(&tmOutB, p.y_i8, 1, 32, CU_TENSOR_MAP_SWIZZLE_NONE);
+        else r = encode_out(&tmOutB, p.y_i8, 1, wq, wq == 128 ? CU_TENSOR_MAP_SWIZZLE_128B : CU_TENSOR_MAP_SWIZZLE_NONE);
+      }
     } else if (p.out_mode == OUT_I8) {
       r = encode_out(&tmOutB, p.y, 1, wq, wq == 128 ? CU_TENSOR_MAP_SWIZZLE_128B : CU_TENSOR_MAP_SWIZZLE_NONE);
     } else {
