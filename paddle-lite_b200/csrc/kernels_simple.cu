@@ -138,20 +138,23 @@ __global__ void __launch_bounds__(kBlock)
 }
 
 // ------------------------------------------------------------------ depthwise 3x3, register tiled
-// One thread = 4 consecutive channels x a 2 x 4 patch of output pixels.  Every input word is
-// loaded and unpacked once and feeds all taps of all outputs it belongs to; the arithmetic is
-// fp32 FMA on integer values (|sum| <= 9*127*127 < 2^24, so the sums are exact and
-// (float)acc is the same number the int32 path would convert), which runs at twice the issue
-// rate of integer multiply-add.  Bytes are unpacked with one byte-permute into the mantissa
-// of 2^23 and one subtraction (no int->float conversions).
-constexpr float kByteMagic = 8388608.f + 128.f;
+// One thread = 4 consecutive channels (one 32-bit word of an NHWC pixel) x a 2 x 4 (stride 1) or
+// 1 x 4 (stride 2) patch of output pixels.  Every input word is loaded once.  The words of four
+// neighbouring pixels are byte-transposed, so that a register holds four consecutive pixels of
+// ONE channel; a filter row is packed the same way as (w0, w1, w2, 0), and one dp4a then adds a
+// whole filter row to an output: 3 dp4a per output instead of 9 multiply-adds plus unpacking.
+// The window of output column j starts j*stride bytes into the transposed row (funnel shift).
+// |sum| <= 9*127*127 < 2^22, so int -> float goes through the mantissa of 1.5*2^23 exactly,
+// without the slow conversion pipe.
 
-__device__ __forceinline__ void unpack4(uint32_t word, float (&out)[4]) {
-  const uint32_t u = word ^ 0x80808080u;  // bias to unsigned
-  out[0] = __uint_as_float(__byte_perm(u, 0x4B000000u, 0x7540)) - kByteMagic;
-  out[1] = __uint_as_float(__byte_perm(u, 0x4B000000u, 0x7541)) - kByteMagic;
-  out[2] = __uint_as_float(__byte_perm(u, 0x4B000000u, 0x7542)) - kByteMagic;
-  out[3] = __uint_as_float(__byte_perm(u, 0x4B000000u, 0x7543)) - kByteMagic;
+// Bytes a,b,c,d[i] -> w[i] = {a[i], b[i], c[i], d[i]}: a 4x4 byte transpose in 6 permutes.
+__device__ __forceinline__ void transpose4x4(uint32_t a, uint32_t b, uint32_t c, uint32_t d, uint32_t (&w)[4]) {
+  const uint32_t t0 = __byte_perm(a, b, 0x5140), t1 = __byte_perm(a, b, 0x7362);
+  const uint32_t t2 = __byte_perm(c, d, 0x5140), t3 = __byte_perm(c, d, 0x7362);
+  w[0] = __byte_perm(t0, t2, 0x5410);
+  w[1] = __byte_perm(t0, t2, 0x7632);
+  w[2] = __byte_perm(t1, t3, 0x5410);
+  w[3] = __byte_perm(t1, t3, 0x7632);
 }
 
 template <int ACT>
@@ -167,8 +170,8 @@ __global__ void __launch_bounds__(kBlock)
     dwconv3x3_kernel(const ConvGeom g, const int8_t* __restrict__ x, const int8_t* __restrict__ w,
                      const OutDev o, const int cquads, const int tiles_x, const int tiles_y, const long total) {
   pdl_sync_with_previous_kernel();
-  constexpr int TH = S == 1 ? 2 : 1, TW = 4;  // keeps the register count of both strides near 120
-  constexpr int IH = (TH - 1) * S + 3, IW = (TW - 1) * S + 3;
+  constexpr int TH = S == 1 ? 2 : 1, TW = 4;
+  constexpr int IH = (TH - 1) * S + 3, IW = (TW - 1) * S + 3;  // 4 x 6 or 3 x 9 input pixels
   long idx = static_cast<long>(blockIdx.x) * kBlock + threadIdx.x;
   if (idx >= total) return;
   const int cq = static_cast<int>(idx % cquads);
@@ -180,18 +183,21 @@ __global__ void __launch_bounds__(kBlock)
   const int oh0 = ty * TH, ow0 = tx * TW;
   const int c0 = cq * 4;
 
-  float wf[9][4];
+  // filter rows as (w0, w1, w2, 0) per channel
+  uint32_t wr[3][4];
 #pragma unroll
-  for (int t = 0; t < 9; ++t)
-    unpack4(*reinterpret_cast<const uint32_t*>(w + static_cast<long>(t) * g.cg_pad + c0), wf[t]);
+  for (int r = 0; r < 3; ++r)
+    transpose4x4(__ldg(reinterpret_cast<const uint32_t*>(w + static_cast<long>(r * 3 + 0) * g.cg_pad + c0)),
+                 __ldg(reinterpret_cast<const uint32_t*>(w + static_cast<long>(r * 3 + 1) * g.cg_pad + c0)),
+                 __ldg(reinterpret_cast<const uint32_t*>(w + static_cast<long>(r * 3 + 2) * g.cg_pad + c0)), 0u, wr[r]);
 
-  float acc[TH][TW][4];
+  int acc[TH][TW][4];
 #pragma unroll
   for (int a = 0; a < TH; ++a)
 #pragma unroll
     for (int b = 0; b < TW; ++b)
 #pragma unroll
-      for (int c = 0; c < 4; ++c) acc[a][b][c] = 0.f;
+      for (int c = 0; c < 4; ++c) acc[a][b][c] = 0;
 
   const int ih0 = oh0 * S - g.pad_t, iw0 = ow0 * S - g.pad_l;
   const int8_t* xn = x + n * g.h * static_cast<long>(g.w) * g.cin_stride + c0;
@@ -211,9 +217,33 @@ __global__ void __launch_bounds__(kBlock)
   }
 #pragma unroll
   for (int iy = 0; iy < IH; ++iy) {
-    float in[IW][4];
+    // win[j][c]: bytes = the three input pixels under output column j (fourth byte meets weight 0)
+    uint32_t win[TW][4];
+    uint32_t ta[4];
+    transpose4x4(raw[iy][0], raw[iy][1], raw[iy][2], raw[iy][3], ta);
+    if (S == 1) {
+      // pixels 4 and 5 of the row: only their two low bytes per channel are ever multiplied
+      const uint32_t t0 = __byte_perm(raw[iy][4], raw[iy][5], 0x5140), t1 = __byte_perm(raw[iy][4], raw[iy][5], 0x7362);
+      const uint32_t tb[4] = {t0, t0 >> 16, t1, t1 >> 16};
 #pragma unroll
-    for (int ix = 0; ix < IW; ++ix) unpack4(raw[iy][ix], in[ix]);
+      for (int c = 0; c < 4; ++c) {
+        win[0][c] = ta[c];
+        win[1][c] = __funnelshift_r(ta[c], tb[c], 8);
+        win[2][c] = __funnelshift_r(ta[c], tb[c], 16);
+        win[3][c] = __funnelshift_r(ta[c], tb[c], 24);
+      }
+    } else {
+      uint32_t tb[4];
+      transpose4x4(raw[iy][4], raw[iy][5], raw[iy][6], raw[iy][7], tb);
+      const uint32_t last = raw[iy][IW - 1];
+#pragma unroll
+      for (int c = 0; c < 4; ++c) {
+        win[0][c] = ta[c];
+        win[1][c] = __funnelshift_r(ta[c], tb[c], 16);
+        win[2][c] = tb[c];
+        win[3][c] = __funnelshift_r(tb[c], last >> (8 * c), 16);
+      }
+    }
 #pragma unroll
     for (int oy = 0; oy < TH; ++oy) {
       const int r = iy - oy * S;  // filter row this input row meets for output row oy
@@ -221,9 +251,8 @@ __global__ void __launch_bounds__(kBlock)
 #pragma unroll
       for (int ox = 0; ox < TW; ++ox)
 #pragma unroll
-        for (int sx = 0; sx < 3; ++sx)
-#pragma unroll
-          for (int c = 0; c < 4; ++c) acc[oy][ox][c] = fmaf(in[ox * S + sx][c], wf[r * 3 + sx][c], acc[oy][ox][c]);
+        for (int c = 0; c < 4; ++c)
+          acc[oy][ox][c] = __dp4a(static_cast<int>(win[ox][c]), static_cast<int>(wr[r][c]), acc[oy][ox][c]);
     }
   }
 
@@ -239,8 +268,10 @@ __global__ void __launch_bounds__(kBlock)
       const int ow = ow0 + ox;
       if (ow >= g.wo) continue;
       const long m = (n * g.ho + oh) * g.wo + ow;
-      float v[4] = {fmaf(acc[oy][ox][0], sc.x, bi.x), fmaf(acc[oy][ox][1], sc.y, bi.y),
-                    fmaf(acc[oy][ox][2], sc.z, bi.z), fmaf(acc[oy][ox][3], sc.w, bi.w)};
+      float f[4];
+#pragma unroll
+      for (int c = 0; c < 4; ++c) f[c] = __int_as_float(acc[oy][ox][c] + 0x4B400000) - 12582912.f;  // exact (float)acc
+      float v[4] = {fmaf(f[0], sc.x, bi.x), fmaf(f[1], sc.y, bi.y), fmaf(f[2], sc.z, bi.z), fmaf(f[3], sc.w, bi.w)};
       if (OUT_IS_I8) {
         uint32_t q[4];
 #pragma unroll
@@ -322,16 +353,6 @@ __global__ void __launch_bounds__(kBlock)
       static_cast<float*>(y)[off + j] =
           act_apply(fmaf(static_cast<float>(acc[j]), sc, bi), e.act, e.alpha);
   }
-}
-
-// Bytes a,b,c,d[i] -> w[i] = {a[i], b[i], c[i], d[i]}: a 4x4 byte transpose in 6 permutes.
-__device__ __forceinline__ void transpose4x4(uint32_t a, uint32_t b, uint32_t c, uint32_t d, uint32_t (&w)[4]) {
-  const uint32_t t0 = __byte_perm(a, b, 0x5140), t1 = __byte_perm(a, b, 0x7362);
-  const uint32_t t2 = __byte_perm(c, d, 0x5140), t3 = __byte_perm(c, d, 0x7362);
-  w[0] = __byte_perm(t0, t2, 0x5410);
-  w[1] = __byte_perm(t0, t2, 0x7632);
-  w[2] = __byte_perm(t1, t3, 0x5410);
-  w[3] = __byte_perm(t1, t3, 0x7632);
 }
 
 // ---- int8 sparse 1x1, shared-memory slab + dp4a.

@@ -172,10 +172,13 @@ def test_prepare_errors(plb, ctx):
         plb.Conv(ctx, wq, ws, -1.0, bias, in_hw=(8, 8))
 
 
-def test_nhwc_entry_and_fused_add_relu(plb, ctx):
+@pytest.mark.parametrize("prefetch", ["0", "1"])
+def test_nhwc_entry_and_fused_add_relu(plb, ctx, prefetch, monkeypatch):
     """Channels-last entry points: same values as the NCHW path; the fused conv + add + relu +
-    calib equals the unfused oracle sequence bit for bit."""
-    xq, in_s, wq, ws, bias = conv_case(15, 2, 64, 14, 14, 128, 1)
+    calib equals the unfused oracle sequence bit for bit, with the residual tiles fetched in
+    step with the chunks or one chunk ahead."""
+    monkeypatch.setenv("PLB_TC_RES_PREFETCH", prefetch)
+    xq, in_s, wq, ws, bias = conv_case(15, 3, 64, 14, 14, 128, 1)
     acc = O.conv_acc_i32(xq, wq)
     y_ref = O.epilogue(acc, ws, in_s, bias, O.ACT_NONE, 0.0)
     rng = np.random.default_rng(3)
