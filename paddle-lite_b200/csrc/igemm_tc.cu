@@ -37,6 +37,7 @@ constexpr int kProducerWarp = kEpilogueWarps;
 constexpr int kMmaWarp = kEpilogueWarps + 1;
 constexpr int kThreads = 32 * (kEpilogueWarps + 2);
 constexpr int kMaxAccBufs = 4;
+constexpr int kMaxBStages = 8;                  // filter ring of window mode with a streamed filter
 constexpr int kCtrlBytes = 1024;                // barriers + tmem slot
 constexpr int kMaxResidentB = 56 * 1024;        // filters up to this size stay in shared memory for the whole kernel
 constexpr uint32_t kWaitLimit = 1u << 22;      // polls before a wait is declared lost
@@ -61,6 +62,10 @@ struct IgemmArgs {
   int slab_rows;                       // window pixels = slab_w * (16 + (kh-1)*dil_h)
   int plane_bytes;                     // one channel chunk of the window, rounded up to 1 KiB
   int tiles_x, tiles_y;                // output tiles per image
+  // window mode with a filter too large to stay resident: the filter streams through its own ring,
+  // kgroup K steps per TMA box (a 3-D box: K step is the outermost box dimension)
+  int b_stream, kgroup, b_stages;
+  int pair;                            // two consecutive tiles of a CTA share one pass over the filter stream
   int out_mode, ldy;
   void* y;
   const float* scale;
@@ -167,6 +172,18 @@ __device__ __forceinline__ void tma_load_2d_if(uint32_t dst, const CUtensorMap* 
       " [%0], [%1, {%3, %4}], [%2];\n\t"
       "}" ::"r"(dst),
       "l"(reinterpret_cast<uint64_t>(map)), "r"(bar), "r"(c0), "r"(c1), "r"(static_cast<uint32_t>(issue))
+      : "memory");
+}
+__device__ __forceinline__ void tma_load_3d_if(uint32_t dst, const CUtensorMap* map, uint32_t bar, int c0, int c1,
+                                               int c2, bool issue) {
+  asm volatile(
+      "{\n\t"
+      ".reg .pred q;\n\t"
+      "setp.ne.b32 q, %6, 0;\n\t"
+      "@q cp.async.bulk.tensor.3d.shared::cluster.global.mbarrier::complete_tx::bytes"
+      " [%0], [%1, {%3, %4, %5}], [%2];\n\t"
+      "}" ::"r"(dst),
+      "l"(reinterpret_cast<uint64_t>(map)), "r"(bar), "r"(c0), "r"(c1), "r"(c2), "r"(static_cast<uint32_t>(issue))
       : "memory");
 }
 __device__ __forceinline__ void tma_load_4d_if(uint32_t dst, const CUtensorMap* map, uint32_t bar, int c0, int c1,
@@ -634,14 +651,18 @@ __global__ void __launch_bounds__(kThreads, 1)
   uint8_t* smem_bres = smem_al + a.staging_bytes;
   uint8_t* smem = smem_bres + a.resident_bytes;
   const int stage_bytes = a.slab ? a.cchunks * a.plane_bytes : (a.resident_b ? stage_a : stage_a + stage_b);
-  uint8_t* ctrl = smem + a.stages * stage_bytes;
+  uint8_t* smem_bring = smem + a.stages * stage_bytes;  // filter ring (window mode with a streamed filter)
+  const int bstage_bytes = a.b_stream ? a.kgroup * stage_b : 0;
+  uint8_t* ctrl = smem_bring + a.b_stages * bstage_bytes;
   uint64_t* full_bar = reinterpret_cast<uint64_t*>(ctrl);
   uint64_t* empty_bar = full_bar + kMaxStages;
   uint64_t* acc_full = empty_bar + kMaxStages;     // [4] accumulator buffer ready for its epilogue group(s)
   uint64_t* acc_empty = acc_full + kMaxAccBufs;    // [4] accumulator buffer drained
   uint64_t* res_bar = acc_empty + kMaxAccBufs;     // [2][16] per epilogue warp and staging tile: residual landed
   uint64_t* bres_bar = res_bar + 2 * kEpilogueWarps;  // resident filter landed
-  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bres_bar + 1);
+  uint64_t* bfull_bar = bres_bar + 1;                 // [8] filter ring
+  uint64_t* bempty_bar = bfull_bar + kMaxBStages;
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bempty_bar + kMaxBStages);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
 
   const int warp = threadIdx.x >> 5;
@@ -665,6 +686,10 @@ __global__ void __launch_bounds__(kThreads, 1)
     }
     for (int w = 0; w < 2 * kEpilogueWarps; ++w) mbar_init(smem_u32(&res_bar[w]), 1);
     mbar_init(smem_u32(bres_bar), 1);
+    for (int t = 0; t < kMaxBStages; ++t) {
+      mbar_init(smem_u32(&bfull_bar[t]), 1);
+      mbar_init(smem_u32(&bempty_bar[t]), 1);
+    }
     *abort_flag = 0;
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     asm volatile("prefetch.tensormap [%0];" ::"l"(reinterpret_cast<uint64_t>(&tmA)) : "memory");
@@ -711,6 +736,35 @@ __global__ void __launch_bounds__(kThreads, 1)
       }
     }
     __syncwarp();
+    // filter stream of one tile (window mode with a streamed filter): ksteps / kgroup boxes of
+    // kgroup K steps each into the filter ring
+    int sb = 0;
+    uint32_t bempty_parity = 1;
+#ifdef PLB_TC_TIMING
+    long long tt_bwait = 0;
+#endif
+    const uint32_t bring_base = smem_u32(smem_bring);
+    auto stream_filter = [&](int n0) -> bool {
+      for (int m = 0; m < a.ksteps; m += a.kgroup) {
+#ifdef PLB_TC_TIMING
+        const long long tb0 = clock64();
+#endif
+        if (!mbar_wait(smem_u32(&bempty_bar[sb]), bempty_parity, abort_flag, a.status, FAULT_WAIT_EMPTY)) return false;
+#ifdef PLB_TC_TIMING
+        tt_bwait += clock64() - tb0;
+#endif
+        const uint32_t bar = smem_u32(&bfull_bar[sb]);
+        mbar_expect_tx_if(bar, static_cast<uint32_t>(bstage_bytes), leader);
+        tma_load_3d_if(bring_base + sb * bstage_bytes, &tmB, bar, 0, n0, m, leader);
+        if (++sb == a.b_stages) {
+          sb = 0;
+          bempty_parity ^= 1;
+        }
+      }
+      return true;
+    };
+    bool have_prev = false;
+    int prev_n0 = 0, local = 0;
     for (int tile = blockIdx.x; a.slab && tile < a.num_tiles && ok; tile += gridDim.x) {
       // one window per tile: rows ty*16 - pad_t ..., columns tx*8 - pad_l ...; cells outside the
       // image are filled with zeros by the copy engine
@@ -733,7 +787,25 @@ __global__ void __launch_bounds__(kThreads, 1)
         s = 0;
         empty_parity ^= 1;
       }
+      if (a.b_stream) {
+        // One pass of the filter stream serves a unit = one tile, or two consecutive tiles of this
+        // CTA (pair mode; they have the same channel block).  With four or more window stages the
+        // windows run one unit ahead of the filter stream.
+        const bool unit_done = !a.pair || (local & 1) || tile + static_cast<int>(gridDim.x) >= a.num_tiles;
+        ++local;
+        if (unit_done) {
+          const int n0 = (tile - tile_m * a.tiles_n) * a.bn;
+          if (a.stages >= 2 * (a.pair ? 2 : 1)) {
+            if (have_prev) ok = stream_filter(prev_n0);
+            prev_n0 = n0;
+            have_prev = true;
+          } else {
+            ok = stream_filter(n0);
+          }
+        }
+      }
     }
+    if (a.slab && a.b_stream && have_prev && ok) ok = stream_filter(prev_n0);
     for (int tile = blockIdx.x; !a.slab && tile < a.num_tiles && ok; tile += gridDim.x) {
       const int tile_m = tile / a.tiles_n;
       const int m0 = tile_m * kTileM;
@@ -782,6 +854,9 @@ __global__ void __launch_bounds__(kThreads, 1)
     tt_acc[1] = clock64() - tt_begin;
 #endif
     if (lane == 0) TT_FLUSH(0, 2);
+#ifdef PLB_TC_TIMING
+    if (lane == 0) a.timing[blockIdx.x * 16 + 15] = tt_bwait;
+#endif
   } else if (warp == kMmaWarp) {
     // ------------------------------------------------------------ MMA issuer
     // Again the whole warp runs the loop and an elected lane issues: matrix descriptors are
@@ -812,6 +887,10 @@ __global__ void __launch_bounds__(kThreads, 1)
     }
     int s = 0, it = 0;
     uint32_t full_parity = 0;
+    int sb = 0;
+    uint32_t bfull_parity = 0;
+    const uint32_t bring_lo = ((smem_u32(smem_bring) >> 4) & 0x3FFFu) | lo_flags;
+    const uint32_t bstage_lo = static_cast<uint32_t>(bstage_bytes) >> 4;
     bool ok = true;
     if (a.resident_b) {
       ok = mbar_wait(smem_u32(bres_bar), 0, abort_flag, a.status, FAULT_WAIT_FULL);
@@ -826,7 +905,7 @@ __global__ void __launch_bounds__(kThreads, 1)
     const uint32_t stage_lo = static_cast<uint32_t>(stage_bytes) >> 4;
     const uint32_t ring_lo = ((smem_base >> 4) & 0x3FFFu) | lo_flags;
     for (int tile = blockIdx.x; tile < a.num_tiles && ok; tile += gridDim.x, ++it) {
-      const int buf = it & nb_mask;
+      int buf = it & nb_mask;
       TT_START();
       ok = mbar_wait(smem_u32(&acc_empty[buf]), ((it >> nb_shift) & 1) ^ 1, abort_flag, a.status, FAULT_WAIT_ACCUM);
       TT_STOP(0);
@@ -845,7 +924,82 @@ __global__ void __launch_bounds__(kThreads, 1)
         // is a function of the shared-memory address, so a start address shifted by whole
         // pixels addresses the same bytes the copy engine wrote.
         const uint32_t slab_lo = ring_lo + s * stage_lo;
-        if (window_shape == 1) {
+        if (a.b_stream) {
+          // Pair mode: the CTA's next tile (same channel block) is accumulated in the next TMEM buffer
+          // from its own window during the same pass over the filter stream, which halves the
+          // filter bytes fetched per output.
+          const bool pair = a.pair && tile + static_cast<int>(gridDim.x) < a.num_tiles;
+          int s2 = s + 1 == a.stages ? 0 : s + 1;
+          uint32_t d_tmem2 = 0, slab2_delta = 0;
+          if (pair) {
+            const int buf2 = (it + 1) & nb_mask;
+            ok = mbar_wait(smem_u32(&acc_empty[buf2]), (((it + 1) >> nb_shift) & 1) ^ 1, abort_flag, a.status,
+                           FAULT_WAIT_ACCUM);
+            if (!ok) break;
+            ok = mbar_wait(smem_u32(&full_bar[s2]), s2 == 0 ? full_parity ^ 1 : full_parity, abort_flag, a.status,
+                           FAULT_WAIT_FULL);
+            if (!ok) break;
+            tc_fence_after();
+            d_tmem2 = tmem_base + buf2 * acc_cols;
+            slab2_delta = (ring_lo + s2 * stage_lo) - slab_lo;  // modular difference of the descriptor fields
+          }
+          // K steps in filter order (filter row, filter column, channel chunk); every kgroup of them
+          // shares one box of the filter ring
+          uint32_t row_a = slab_lo, tap_a = slab_lo, a_lo = slab_lo;
+          int sx = 0, cc = 0;
+          for (int m = 0; m < a.ksteps && ok; m += a.kgroup) {
+            TT_STOP(2);
+            TT_START();
+            ok = mbar_wait(smem_u32(&bfull_bar[sb]), bfull_parity, abort_flag, a.status, FAULT_WAIT_FULL);
+            TT_STOP(3);
+            TT_START();
+            if (!ok) break;
+            tc_fence_after();
+            uint32_t b_lo = bring_lo + sb * bstage_lo;
+            for (int g = 0; g < a.kgroup; ++g, b_lo += stage_b_lo) {
+              if (mma_per_stage == 4) issue_kstep<4>(d_tmem, a_lo, hi_a, b_lo, hi_b, idesc, accumulate, leader);
+              else if (mma_per_stage == 2) issue_kstep<2>(d_tmem, a_lo, hi_a, b_lo, hi_b, idesc, accumulate, leader);
+              else issue_kstep<1>(d_tmem, a_lo, hi_a, b_lo, hi_b, idesc, accumulate, leader);
+              if (pair) {
+                const uint32_t a2 = a_lo + slab2_delta;
+                if (mma_per_stage == 4) issue_kstep<4>(d_tmem2, a2, hi_a, b_lo, hi_b, idesc, accumulate, leader);
+                else if (mma_per_stage == 2) issue_kstep<2>(d_tmem2, a2, hi_a, b_lo, hi_b, idesc, accumulate, leader);
+                else issue_kstep<1>(d_tmem2, a2, hi_a, b_lo, hi_b, idesc, accumulate, leader);
+              }
+              accumulate = 1;
+              a_lo += plane_lo;
+              if (++cc == a.cchunks) {
+                cc = 0;
+                tap_a += col_lo;
+                if (++sx == a.kw) {
+                  sx = 0;
+                  row_a += row_lo;
+                  tap_a = row_a;
+                }
+                a_lo = tap_a;
+              }
+            }
+            tc_commit_if(smem_u32(&bempty_bar[sb]), leader);
+            if (++sb == a.b_stages) {
+              sb = 0;
+              bfull_parity ^= 1;
+            }
+          }
+          if (!ok) break;
+          if (pair) {
+            // the first tile of the pair is complete: release its window and publish its accumulator
+            // here; the common tail below does the same for the second tile
+            tc_commit_if(smem_u32(&empty_bar[s]), leader);
+            tc_commit_if(smem_u32(&acc_full[buf]), leader);
+            if (++s == a.stages) {
+              s = 0;
+              full_parity ^= 1;
+            }
+            tile += gridDim.x;
+            ++it;
+            buf = it & nb_mask;
+          }
+        } else if (window_shape == 1) {
           issue_window<3, 3, 1, 2>(d_tmem, slab_lo, row_lo, col_lo, plane_lo, hi_a, bres_lo, stage_b_lo, hi_b, idesc, leader);
         } else if (window_shape == 2) {
           issue_window<3, 3, 1, 4>(d_tmem, slab_lo, row_lo, col_lo, plane_lo, hi_a, bres_lo, stage_b_lo, hi_b, idesc, leader);
@@ -1325,17 +1479,49 @@ int igemm_tc_launch(plb_ctx* ctx, const IgemmProblem& p) {
   // once per tap.  Output tiles are 16 x 8 pixels, so images much smaller than that waste too
   // many accumulator rows.
   int tiles_m_eff = tiles_m;
-  if (p.im2col && a.taps > 1 && p.stride_h == 1 && p.stride_w == 1 && staged && can_resident) {
+  int slab_stages = 0;
+  if (p.im2col && a.taps > 1 && p.stride_h == 1 && p.stride_w == 1 && staged) {
     const int tx = (p.wo + 7) / 8, ty = (p.ho + 15) / 16;
     const int sw_px = 8 + (p.kw - 1) * p.dil_w, sh_px = 16 + (p.kh - 1) * p.dil_h;
     const double waste = static_cast<double>(tx) * 8 * ty * 16 / (static_cast<double>(p.wo) * p.ho);
     const int plane = (sw_px * sh_px * a.kc + 1023) / 1024 * 1024;
-    const bool fits = sw_px <= 256 && sh_px <= 256 && sw_px * a.kc <= 0x3FFF * 16 &&
-                      2 * a.cchunks * plane + resident_bytes + a.staging_bytes + kCtrlBytes + 1024 <= 225 * 1024;
-    const int dflt = waste <= 1.35 && fits && a.resident_b;
+    const bool geom_ok = sw_px <= 256 && sh_px <= 256 && sw_px * a.kc <= 0x3FFF * 16;
+    const int room = 225 * 1024 - a.staging_bytes - kCtrlBytes - 1024;
+    bool fits = geom_ok && can_resident && 2 * a.cchunks * plane + resident_bytes <= room;
+    bool stream = false;
+    // Off unless asked for (PLB_TC_BSTREAM=1): measured on 128->128 and 256->256 3x3 layers it is no
+    // faster than im2col mode, because with 128-wide tiles every MMA reads 8 KiB of shared memory in
+    // 64 cycles, which is the whole shared-memory bandwidth; the copies into the ring slow it further.
+    if (geom_ok && !fits && env_int("PLB_TC_BSTREAM", 0) != 0) {
+      // The filter does not fit beside the windows: stream it through its own ring, kgroup K steps
+      // per box.  Preferred: four window stages (two pairs of tiles in flight) and at least two
+      // filter boxes; else two window stages.  Larger boxes first (fewer TMA instructions).
+      const int bstep = bn * a.kc;
+      const int slab_stage = a.cchunks * plane;
+      for (int want_slabs = 4; want_slabs >= 2 && !stream; want_slabs -= 2) {
+        for (int g = a.ksteps; g >= 1 && !stream; --g) {
+          if (a.ksteps % g || g * bstep > 48 * 1024) continue;
+          if (want_slabs * slab_stage + 2 * g * bstep > room) continue;
+          stream = fits = true;
+          a.kgroup = g;
+          slab_stages = want_slabs;
+          int bst = (room - want_slabs * slab_stage) / (g * bstep);
+          a.b_stages = bst > kMaxBStages ? kMaxBStages : bst;
+        }
+      }
+    }
+    const int dflt = waste <= 1.35 && fits && (stream || a.resident_b);
     if (fits && env_int("PLB_TC_SLAB", dflt) != 0) {
       a.slab = 1;
-      a.resident_b = 1;
+      a.resident_b = stream ? 0 : 1;
+      a.b_stream = stream ? 1 : 0;
+      // pairs need the CTA's consecutive tiles to share the channel block
+      {
+        const long tn = (p.cout + bn - 1) / bn;
+        const long total = static_cast<long>(p.batch) * tx * ty * tn;
+        const long grid_h = total < ctx->sm_count ? total : ctx->sm_count;
+        a.pair = stream && env_int("PLB_TC_PAIR", 1) != 0 && grid_h % tn == 0 && total > grid_h;
+      }
       a.kh = p.kh;
       a.slab_w = sw_px;
       a.slab_rows = sw_px * sh_px;
@@ -1353,6 +1539,8 @@ int igemm_tc_launch(plb_ctx* ctx, const IgemmProblem& p) {
   stages = env_int("PLB_TC_STAGES", stages);
   if (stages > kMaxStages) stages = kMaxStages;
   if (stages < 2) stages = 2;
+  if (a.b_stream) stages = slab_stages;
+  else a.b_stages = 0, a.kgroup = 1;
   a.stages = stages;
   a.ho = p.ho; a.wo = p.wo;
   a.stride_h = p.stride_h; a.stride_w = p.stride_w;
@@ -1369,7 +1557,18 @@ int igemm_tc_launch(plb_ctx* ctx, const IgemmProblem& p) {
   alignas(64) CUtensorMap tmA;
   alignas(64) CUtensorMap tmB;
   const CUtensorMapSwizzle sw = swizzle_for(a.kc);
-  {
+  if (a.b_stream) {
+    // filter as [K step][cout][kc]: one box = kgroup K steps of bn channels
+    const cuuint64_t kbytes = static_cast<cuuint64_t>(a.taps) * p.cin_pad;
+    cuuint64_t dims[3] = {static_cast<cuuint64_t>(a.kc), static_cast<cuuint64_t>(p.cout), kbytes / a.kc};
+    cuuint64_t strides[2] = {kbytes, static_cast<cuuint64_t>(a.kc)};
+    cuuint32_t box[3] = {static_cast<cuuint32_t>(a.kc), static_cast<cuuint32_t>(bn), static_cast<cuuint32_t>(a.kgroup)};
+    cuuint32_t estr[3] = {1, 1, 1};
+    CUresult r = g_encode_tiled(&tmB, CU_TENSOR_MAP_DATA_TYPE_UINT8, 3, const_cast<int8_t*>(p.b), dims,
+                                strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE, sw,
+                                CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    if (r != CUDA_SUCCESS) return fail(PLB_E_CUDA, "cuTensorMapEncodeTiled(filter stream) failed: %d", (int)r);
+  } else {
     // filter: [cout, taps*cin_pad] bytes, box = kc x bn
     cuuint64_t dims[2] = {static_cast<cuuint64_t>(a.taps) * p.cin_pad, static_cast<cuuint64_t>(p.cout)};
     cuuint64_t strides[1] = {static_cast<cuuint64_t>(a.taps) * p.cin_pad};
@@ -1465,7 +1664,8 @@ int igemm_tc_launch(plb_ctx* ctx, const IgemmProblem& p) {
   }
 
   const size_t smem = static_cast<size_t>(a.staging_bytes) + a.resident_bytes +
-                      static_cast<size_t>(stages) * ring_stage_bytes + kCtrlBytes + 1024;
+                      static_cast<size_t>(stages) * ring_stage_bytes +
+                      static_cast<size_t>(a.b_stages) * a.kgroup * bn * a.kc + kCtrlBytes + 1024;
   if (smem > 227 * 1024) return fail(PLB_E_UNSUPPORTED, "pipeline needs %zu bytes of shared memory", smem);
   IgemmKernel kernel = pick_kernel(p.out_mode, p.epi.act, staged);
   // the attribute belongs to (function, device): remember which pairs have been configured
@@ -1497,10 +1697,10 @@ int igemm_tc_launch(plb_ctx* ctx, const IgemmProblem& p) {
       for (int i = 0; i < 16; ++i) avg[i] += static_cast<double>(h[b * 16 + i]) / grid;
     fprintf(stderr,
             "[tc timing] tiles %ld grid %u slab %d bn %d kc %d ksteps %d stages %d | producer: wait_empty %.0f total %.0f | "
-            "mma: wait_acc_empty %.0f wait_full %.0f issue %.0f | epilogue warp0: wait_acc_full %.0f wait_store_read %.0f "
+            "mma: wait_acc_empty %.0f wait_full %.0f issue %.0f wait_filter %.0f (producer wait_filter_slot %.0f) | epilogue warp0: wait_acc_full %.0f wait_store_read %.0f "
             "tmem_ld %.0f math+store %.0f | since entry: roles start %.0f, filter resident %.0f, first operands %.0f, "
             "MMAs issued %.0f, epilogue warp0 done %.0f (cycles per CTA)\n",
-            tiles, grid, a.slab, a.bn, a.kc, a.ksteps, a.stages, avg[0], avg[1], avg[2], avg[3], avg[4], avg[6], avg[7],
+            tiles, grid, a.slab, a.bn, a.kc, a.ksteps, a.stages, avg[0], avg[1], avg[2], avg[3], avg[4], avg[5], avg[15], avg[6], avg[7],
             avg[8], avg[9], avg[10], avg[11], avg[12], avg[13], avg[14]);
   }
 #endif

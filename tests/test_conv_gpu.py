@@ -89,6 +89,12 @@ WINDOW_CASES = [
     (2, 64, 20, 13, 32, (3, 2), (0, 1, 2, 0), (2, 1), 2),  # asymmetric padding, dilation, 3x2 filter
     (1, 32, 17, 23, 64, 5, (2, 2, 2, 2), (1, 1), 3),      # 5x5
     (1, 40, 9, 9, 32, 3, (0, 0, 0, 0), (1, 1), 0),        # no padding, channels padded to 64
+    (2, 128, 28, 28, 128, 3, (1, 1, 1, 1), (1, 1), 1),    # filter too large to stay resident: streamed, 3 K steps per box
+    (1, 256, 14, 14, 256, 3, (1, 1, 1, 1), (1, 1), 1),    # two channel chunks, 256-wide tile, streamed filter
+    (1, 64, 20, 20, 320, 3, (1, 1, 1, 1), (1, 1), 2),     # streamed filter, ragged second channel tile (64 of 256)
+    (1, 32, 12, 12, 320, (2, 3), (1, 0, 1, 1), (1, 1), 0),  # two channel tiles: every window is fetched twice
+    (24, 128, 28, 28, 128, 3, (1, 1, 1, 1), (1, 1), 1),   # 192 tiles on 148 CTAs: some CTAs run a pair of tiles per filter pass
+    (41, 64, 14, 14, 512, 3, (1, 1, 1, 1), (1, 1), 0),    # pairs with two channel tiles, odd tile counts per CTA
 ]
 
 
@@ -97,6 +103,7 @@ def test_window_mode_bit_exact(plb, ctx, case, monkeypatch):
     """Stride-1 filters in window mode (one fetch of a tile's input window, taps addressed by
     shifted matrix descriptors), forced on for shapes the heuristic would leave to im2col."""
     monkeypatch.setenv("PLB_TC_SLAB", "1")
+    monkeypatch.setenv("PLB_TC_BSTREAM", "1")  # filters that do not fit in shared memory stream through their own ring
     monkeypatch.setenv("PLB_TC_BN", "256")  # one channel tile even though the problem is small
     n, cin, h, w, cout, k, pads, dil, act = case
     xq, in_s, wq, ws, bias = conv_case(hash(case[:5]) % 10000, n, cin, h, w, cout, k)
