@@ -175,7 +175,7 @@ typedef struct plb_sparse_desc {
   float act_alpha;
   float in_scale, out_scale;
   int leaky_compat;
-  int impl; /* PLB_IMPL_AUTO | PLB_IMPL_DIRECT (walk the encoding) | PLB_IMPL_TC (densified) */
+  int impl; /* PLB_IMPL_AUTO (int8 with >= 32 channels: densified, else walk) | PLB_IMPL_DIRECT (walk the encoding) | PLB_IMPL_TC (densified) */
 } plb_sparse_desc;
 int plb_sparse_prepare(plb_ctx* ctx, const plb_sparse_desc* desc, const void* nonzero_weights_h,
                        int n_weights, const uint32_t* oc_nonzeros_h, const int32_t* diffs_h,
@@ -190,6 +190,12 @@ void plb_sparse_destroy(plb_sparse* sp);
 int plb_calib_f32_to_i8(plb_ctx* ctx, const float* x, int8_t* q, size_t n, float scale);
 /* calib int8 -> fp32 (calib.cc:153-239). */
 int plb_calib_i8_to_f32(plb_ctx* ctx, const int8_t* q, float* y, size_t n, float scale);
+/* Host <-> device copies on the ctx stream: what the io_copy kernels of a target do with
+ * TargetWrapper<T>::MemcpySync (lite/kernels/xpu/io_copy_compute.cc:54-116, CopySync in
+ * lite/core/memory.h:65-93).  h2d is enqueued (the host buffer must stay valid until the stream
+ * reaches it; pinned memory makes it asynchronous), d2h returns when the bytes are on the host. */
+int plb_copy_h2d(plb_ctx* ctx, void* dst_device, const void* src_host, size_t bytes);
+int plb_copy_d2h(plb_ctx* ctx, void* dst_host, const void* src_device, size_t bytes);
 /* layout staging: [n,c,h,w] <-> [n,h,w,cpad] (extra channels are zero / dropped). */
 int plb_nchw_to_nhwc_i8(plb_ctx* ctx, const int8_t* x, int8_t* y, int n, int c, int h, int w,
                         int cpad);
@@ -204,6 +210,10 @@ int plb_maxpool_nhwc_i8(plb_ctx* ctx, const int8_t* x, int8_t* y, int n, int c, 
 /* global average pool of fp32 NHWC [n,h*w,c] -> [n,c], then calib to int8 when q != NULL. */
 int plb_global_avgpool_nhwc_f32(plb_ctx* ctx, const float* x, float* y, int8_t* q, int n, int hw,
                                 int c, float scale);
+/* softmax over the last axis of a [rows, cols] fp32 matrix (the classifier head after fc):
+ * y = exp(max(x - rowmax, -64)) / sum, the shift-and-clip form of
+ * lite/backends/x86/math/softmax_impl.h:36-41, :110-131 (axis = last, num_remain = 1). */
+int plb_softmax_f32(plb_ctx* ctx, const float* x, float* y, int rows, int cols);
 
 #ifdef __cplusplus
 }

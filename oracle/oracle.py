@@ -160,6 +160,14 @@ def calib_i8_to_f32(q, scale):
     return y
 
 
+def softmax(x):
+    x = np.ascontiguousarray(x, dtype=np.float32)
+    rows, cols = x.shape
+    y = np.empty_like(x)
+    lib().orc_softmax_f32(_p(x, C.c_float), _p(y, C.c_float), rows, cols)
+    return y
+
+
 def maxpool_i8(x, k=3, s=2, p=1):
     x = np.ascontiguousarray(x, dtype=np.int8)
     n, c, h, w = x.shape

@@ -501,6 +501,31 @@ int orc_sparse_conv_f64(const float* x, const float* dense, const float* bias, d
 
 /* ------------------------------------------------ fp32 glue between layers */
 
+/* softmax over the last axis, the x86 form (lite/backends/x86/math/softmax_impl.h:110-131):
+ * shift by the row maximum, clip the shifted logits at -64, exponentiate, scale by 1/sum.
+ * exp and the sum are evaluated in double here; the CUDA kernel and the reference's polynomial
+ * vec_exp both stay within 1e-5 relative of this. */
+int orc_softmax_f32(const float* x, float* y, int rows, int cols) {
+  for (int r = 0; r < rows; ++r) {
+    const float* xr = x + (long)r * cols;
+    float* yr = y + (long)r * cols;
+    float m = xr[0];
+    for (int i = 1; i < cols; ++i) m = xr[i] > m ? xr[i] : m;
+    double s = 0.0;
+    for (int i = 0; i < cols; ++i) {
+      float d = xr[i] - m;
+      d = d < -64.f ? -64.f : d;
+      s += exp((double)d);
+    }
+    for (int i = 0; i < cols; ++i) {
+      float d = xr[i] - m;
+      d = d < -64.f ? -64.f : d;
+      yr[i] = (float)(exp((double)d) / s);
+    }
+  }
+  return 0;
+}
+
 /* max pool on int8 NCHW (pool2d max, exclusive padding = ignore out-of-range taps). */
 int orc_maxpool_i8(const int8_t* x, int8_t* y, int n, int c, int h, int w, int k, int s, int p) {
   const int ho = (h + 2 * p - k) / s + 1, wo = (w + 2 * p - k) / s + 1;

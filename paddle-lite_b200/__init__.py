@@ -76,6 +76,9 @@ SYMBOLS = {
     "plb_sparse_run": (C.c_int, [_P, _P, _P, C.c_int]),
     "plb_sparse_destroy": (None, [_P]),
     "plb_calib_f32_to_i8": (C.c_int, [_P, _P, _P, C.c_size_t, C.c_float]),
+    "plb_softmax_f32": (C.c_int, [_P, _P, _P, C.c_int, C.c_int]),
+    "plb_copy_h2d": (C.c_int, [_P, _P, _P, C.c_size_t]),
+    "plb_copy_d2h": (C.c_int, [_P, _P, _P, C.c_size_t]),
     "plb_calib_i8_to_f32": (C.c_int, [_P, _P, _P, C.c_size_t, C.c_float]),
     "plb_nchw_to_nhwc_i8": (C.c_int, [_P, _P, _P, C.c_int, C.c_int, C.c_int, C.c_int, C.c_int]),
     "plb_nhwc_to_nchw": (C.c_int, [_P, _P, _P, C.c_int, C.c_int, C.c_int, C.c_int, C.c_int]),
@@ -200,6 +203,14 @@ class Context:
         ho, wo = (h + 2 * pad - k) // stride + 1, (w + 2 * pad - k) // stride + 1
         y = out if out is not None else torch.empty((n, ho, wo, c), dtype=torch.int8, device=x.device)
         _check(lib().plb_maxpool_nhwc_i8(self.handle, _dev_ptr(x), _dev_ptr(y), n, c, h, w, k, stride, pad))
+        return y
+
+    def softmax(self, x, out=None):
+        """Row softmax of a [rows, cols] fp32 tensor (reference form: shift by the row max, clip at -64)."""
+        import torch
+        rows, cols = x.shape
+        y = out if out is not None else torch.empty_like(x)
+        _check(lib().plb_softmax_f32(self.handle, _dev_ptr(x), _dev_ptr(y), rows, cols))
         return y
 
     def global_avgpool_nhwc_f32(self, x, scale=None, out_f32=None, out_i8=None):

@@ -1164,6 +1164,8 @@ __global__ void __launch_bounds__(kThreads, 1)
           if (active) {
             ok = mbar_wait(pf_bar[pf_cur], pf_phase[pf_cur], abort_flag, a.status, FAULT_WAIT_FULL);
             pf_phase[pf_cur] ^= 1;
+            TT_STOP(1);
+            TT_START();
             if (!ok) break;
             if (stores_pending && !drained) {  // the int8 staging rows are rewritten below
               if (lane == 0) bulk_wait_read_all();
@@ -1234,6 +1236,8 @@ __global__ void __launch_bounds__(kThreads, 1)
             if (have_res) {
               ok = mbar_wait(my_res_bar, res_phase, abort_flag, a.status, FAULT_WAIT_FULL);
               res_phase ^= 1;
+              TT_STOP(1);
+              TT_START();
               if (!ok) break;
             }
             epilogue_chunk_staged<MODE, ACT>(a, r, lane, n0 + c, st_w, st_b + lane * wq, (c - cbase) >> 4, b_swz,
@@ -1697,7 +1701,7 @@ int igemm_tc_launch(plb_ctx* ctx, const IgemmProblem& p) {
       for (int i = 0; i < 16; ++i) avg[i] += static_cast<double>(h[b * 16 + i]) / grid;
     fprintf(stderr,
             "[tc timing] tiles %ld grid %u slab %d bn %d kc %d ksteps %d stages %d | producer: wait_empty %.0f total %.0f | "
-            "mma: wait_acc_empty %.0f wait_full %.0f issue %.0f wait_filter %.0f (producer wait_filter_slot %.0f) | epilogue warp0: wait_acc_full %.0f wait_store_read %.0f "
+            "mma: wait_acc_empty %.0f wait_full %.0f issue %.0f wait_filter %.0f (producer wait_filter_slot %.0f) | epilogue warp0: wait_acc_full %.0f wait_stores+residual %.0f "
             "tmem_ld %.0f math+store %.0f | since entry: roles start %.0f, filter resident %.0f, first operands %.0f, "
             "MMAs issued %.0f, epilogue warp0 done %.0f (cycles per CTA)\n",
             tiles, grid, a.slab, a.bn, a.kc, a.ksteps, a.stages, avg[0], avg[1], avg[2], avg[3], avg[4], avg[5], avg[15], avg[6], avg[7],

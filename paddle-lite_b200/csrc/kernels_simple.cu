@@ -956,6 +956,57 @@ int sparse_csr_launch(plb_ctx* ctx, const SparseGeom& g, const void* x, const in
   return PLB_OK;
 }
 
+// Row softmax over the last axis: y = exp(max(x - rowmax, -64)) / sum.  One block per row; the
+// row lives in registers between the passes (up to 8 values per thread), longer rows re-read it.
+__global__ void __launch_bounds__(kBlock)
+    softmax_rows_kernel(const float* __restrict__ x, float* __restrict__ y, int cols) {
+  pdl_sync_with_previous_kernel();
+  __shared__ float red[kBlock / 32];
+  __shared__ float bcast;
+  const float* xr = x + static_cast<long>(blockIdx.x) * cols;
+  float* yr = y + static_cast<long>(blockIdx.x) * cols;
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  float m = -3.402823466e38f;
+  for (int i = threadIdx.x; i < cols; i += kBlock) m = fmaxf(m, xr[i]);
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) m = fmaxf(m, __shfl_xor_sync(0xffffffffu, m, o));
+  if (lane == 0) red[warp] = m;
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    float t = red[0];
+    for (int i = 1; i < kBlock / 32; ++i) t = fmaxf(t, red[i]);
+    bcast = t;
+  }
+  __syncthreads();
+  m = bcast;
+  float s = 0.f;
+  for (int i = threadIdx.x; i < cols; i += kBlock) {
+    const float e = expf(fmaxf(xr[i] - m, -64.f));
+    yr[i] = e;
+    s += e;
+  }
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) s += __shfl_xor_sync(0xffffffffu, s, o);
+  __syncthreads();  // everyone has read bcast
+  if (lane == 0) red[warp] = s;
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    float t = 0.f;
+    for (int i = 0; i < kBlock / 32; ++i) t += red[i];
+    bcast = 1.f / t;
+  }
+  __syncthreads();
+  const float inv = bcast;
+  for (int i = threadIdx.x; i < cols; i += kBlock) yr[i] *= inv;
+}
+
+int softmax_rows_launch(plb_ctx* ctx, const float* x, float* y, int rows, int cols) {
+  if (rows == 0) return PLB_OK;
+  PLB_CUDA(launch_kernel(softmax_rows_kernel, dim3(static_cast<unsigned>(rows)), dim3(kBlock), 0, ctx->stream, x, y, cols));
+  ctx->launches++;
+  return PLB_OK;
+}
+
 int calib_f32_to_i8_launch(plb_ctx* ctx, const float* x, int8_t* q, size_t n, float scale) {
   if (n == 0) return PLB_OK;
   const unsigned blocks = static_cast<unsigned>(std::min<size_t>((n + kBlock - 1) / kBlock, 148 * 16));

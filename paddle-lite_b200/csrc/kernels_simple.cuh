@@ -51,6 +51,7 @@ int sparse_slab_supported(const SparseGeom& g, const void* x, const void* y);
 int sparse_slab_launch(plb_ctx* ctx, const SparseGeom& g, const int8_t* x, const int* grp_ptr,
                        const void* grp_idx, const void* grp_w, const EpiParams& epi, void* y);
 
+int softmax_rows_launch(plb_ctx* ctx, const float* x, float* y, int rows, int cols);
 int calib_f32_to_i8_launch(plb_ctx* ctx, const float* x, int8_t* q, size_t n, float scale);
 int calib_i8_to_f32_launch(plb_ctx* ctx, const int8_t* q, float* y, size_t n, float scale);
 int nchw_to_nhwc_i8_launch(plb_ctx* ctx, const int8_t* x, int8_t* y, int n, int c, int h, int w,

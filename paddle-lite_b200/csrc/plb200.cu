@@ -354,6 +354,13 @@ size_t plb_conv_workspace_bytes(const plb_conv* conv, int batch) {
   return x_bytes + y_bytes;
 }
 
+int plb_softmax_f32(plb_ctx* ctx, const float* x, float* y, int rows, int cols) {
+  PLB_REQUIRE(ctx && (rows == 0 || (x && y)), "null argument");
+  PLB_REQUIRE(rows >= 0 && cols > 0, "bad dims");
+  PLB_CUDA(cudaSetDevice(ctx->device));
+  return softmax_rows_launch(ctx, x, y, rows, cols);
+}
+
 }  // extern "C"
 
 namespace {
@@ -763,7 +770,10 @@ int plb_sparse_prepare(plb_ctx* ctx, const plb_sparse_desc* desc, const void* no
     if ((rc = s->scale.upload(i8 ? f.scale_i8.data() : f.scale_f32.data(), sizeof(float) * d.cout))) return rc;
     if ((rc = s->bias.upload(i8 ? f.bias_i8.data() : f.bias_f32.data(), sizeof(float) * d.cout))) return rc;
     s->alpha = i8 ? f.alpha_i8 : f.alpha_f32;
-    if (d.impl == PLB_IMPL_TC) {
+    // AUTO: at 20 % density the tensor cores beat walking the non-zeros on CUDA cores from 32
+    // channels up (both give the same integer sums, hence the same outputs); DIRECT keeps the walk.
+    const bool want_dense = d.impl == PLB_IMPL_TC || (d.impl == PLB_IMPL_AUTO && d.cin >= 32 && d.cout >= 32);
+    if (want_dense) {
       // densified variant: the same weights as a dense 1x1 filter on the tensor cores
       std::vector<int8_t> dense(static_cast<size_t>(d.cout) * d.cin, 0);
       for (int oc = 0; oc < d.cout; ++oc)
@@ -774,7 +784,9 @@ int plb_sparse_prepare(plb_ctx* ctx, const plb_sparse_desc* desc, const void* no
       cd.stride_h = cd.stride_w = 1; cd.dil_h = cd.dil_w = 1; cd.groups = 1;
       cd.act = d.act; cd.act_alpha = d.act_alpha; cd.in_scale = d.in_scale; cd.out_scale = d.out_scale;
       cd.out_dtype = d.out_dtype; cd.leaky_compat = d.leaky_compat; cd.impl = PLB_IMPL_TC;
-      if ((rc = plb_conv_prepare(ctx, &cd, dense.data(), wscale_h, n_wscale, bias_h, &s->dense))) return rc;
+      rc = plb_conv_prepare(ctx, &cd, dense.data(), wscale_h, n_wscale, bias_h, &s->dense);
+      if (rc && d.impl == PLB_IMPL_TC) return rc;
+      if (rc) s->dense = nullptr;  // AUTO: shapes the tensor-core path cannot take keep the walk
     }
   } else {
     if (bias_h && (rc = s->bias_raw.upload(bias_h, sizeof(float) * d.cout))) return rc;
@@ -820,6 +832,23 @@ int plb_calib_f32_to_i8(plb_ctx* ctx, const float* x, int8_t* q, size_t n, float
   PLB_REQUIRE(scale > 0.f, "scale must be positive");
   PLB_CUDA(cudaSetDevice(ctx->device));
   return calib_f32_to_i8_launch(ctx, x, q, n, scale);
+}
+
+int plb_copy_h2d(plb_ctx* ctx, void* dst_device, const void* src_host, size_t bytes) {
+  PLB_REQUIRE(ctx && (bytes == 0 || (dst_device && src_host)), "null argument");
+  if (bytes == 0) return PLB_OK;
+  PLB_CUDA(cudaSetDevice(ctx->device));
+  PLB_CUDA(cudaMemcpyAsync(dst_device, src_host, bytes, cudaMemcpyHostToDevice, ctx->stream));
+  return PLB_OK;
+}
+
+int plb_copy_d2h(plb_ctx* ctx, void* dst_host, const void* src_device, size_t bytes) {
+  PLB_REQUIRE(ctx && (bytes == 0 || (dst_host && src_device)), "null argument");
+  if (bytes == 0) return PLB_OK;
+  PLB_CUDA(cudaSetDevice(ctx->device));
+  PLB_CUDA(cudaMemcpyAsync(dst_host, src_device, bytes, cudaMemcpyDeviceToHost, ctx->stream));
+  PLB_CUDA(cudaStreamSynchronize(ctx->stream));
+  return PLB_OK;
 }
 
 int plb_calib_i8_to_f32(plb_ctx* ctx, const int8_t* q, float* y, size_t n, float scale) {

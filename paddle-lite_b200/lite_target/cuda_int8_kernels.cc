@@ -279,6 +279,73 @@ class SparseConvCompute : public KernelLite<TARGET(kCUDA), InType> {
   std::unique_ptr<plb_sparse, Deleter> sp_;
 };
 
+// calib fp32 <-> int8 between layers (mirrors lite/kernels/x86/calib_compute.cc:28-36, :156-168;
+// operators::CalibParam, lite/operators/op_params.h:74-78).
+class CalibFp32ToInt8Compute : public KernelLite<TARGET(kCUDA), PRECISION(kInt8)> {
+ public:
+  void Run() override {
+    auto& param = this->Param<operators::CalibParam>();
+    PLB_CHECK(plb_calib_f32_to_i8(GetCtx(), param.input->template data<float>(),
+                                  param.output->template mutable_data<int8_t>(TARGET(kCUDA)),
+                                  static_cast<size_t>(param.input->numel()), param.scale));
+  }
+};
+class CalibInt8ToFp32Compute : public KernelLite<TARGET(kCUDA), PRECISION(kInt8)> {
+ public:
+  void Run() override {
+    auto& param = this->Param<operators::CalibParam>();
+    PLB_CHECK(plb_calib_i8_to_f32(GetCtx(), param.input->template data<int8_t>(),
+                                  param.output->template mutable_data<float>(TARGET(kCUDA)),
+                                  static_cast<size_t>(param.input->numel()), param.scale));
+  }
+};
+
+// softmax over the last axis of an fp32 tensor (classifier head; operators::SoftmaxParam,
+// lite/operators/op_params.h:292-297; x86 kernel lite/kernels/x86/softmax_compute.h).
+class SoftmaxCompute : public KernelLite<TARGET(kCUDA), PRECISION(kFloat)> {
+ public:
+  void Run() override {
+    auto& param = this->Param<operators::SoftmaxParam>();
+    auto dims = param.x->dims();
+    const int rank = static_cast<int>(dims.size());
+    const int axis = param.axis < 0 ? param.axis + rank : param.axis;
+    CHECK_EQ(axis, rank - 1) << "the kCUDA softmax kernel handles the last axis";
+    const int cols = static_cast<int>(dims[rank - 1]);
+    const int rows = static_cast<int>(dims.production() / cols);
+    PLB_CHECK(plb_softmax_f32(GetCtx(), param.x->template data<float>(),
+                              param.output->template mutable_data<float>(TARGET(kCUDA)), rows, cols));
+  }
+};
+
+// io_copy host <-> device (mirrors lite/kernels/xpu/io_copy_compute.cc:54-116; operators::IoCopyParam,
+// lite/operators/op_params.h:60-66).  The destination keeps the source's dims, precision and LoD.
+class IoCopyHostToCudaCompute : public KernelLite<TARGET(kCUDA), PRECISION(kAny), DATALAYOUT(kAny)> {
+ public:
+  void Run() override {
+    auto& param = this->Param<operators::IoCopyParam>();
+    CHECK(param.x != nullptr && param.y != nullptr) << "io_copy handles single tensors";
+    const size_t bytes = param.x->memory_size();
+    param.y->Resize(param.x->dims());
+    param.y->set_precision(param.x->precision());
+    param.y->set_lod(param.x->lod());
+    void* dst = param.y->mutable_data(TARGET(kCUDA), bytes);
+    PLB_CHECK(plb_copy_h2d(GetCtx(), dst, param.x->raw_data(), bytes));
+  }
+};
+class IoCopyCudaToHostCompute : public KernelLite<TARGET(kCUDA), PRECISION(kAny), DATALAYOUT(kAny)> {
+ public:
+  void Run() override {
+    auto& param = this->Param<operators::IoCopyParam>();
+    CHECK(param.x != nullptr && param.y != nullptr) << "io_copy handles single tensors";
+    const size_t bytes = param.x->memory_size();
+    param.y->Resize(param.x->dims());
+    param.y->set_precision(param.x->precision());
+    param.y->set_lod(param.x->lod());
+    void* dst = param.y->mutable_data(TARGET(kHost), bytes);
+    PLB_CHECK(plb_copy_d2h(GetCtx(), dst, param.x->raw_data(), bytes));
+  }
+};
+
 }  // namespace cuda
 }  // namespace kernels
 }  // namespace lite
@@ -398,4 +465,46 @@ REGISTER_LITE_KERNEL(sparse_conv2d, kCUDA, kInt8, kNCHW, CudaSparseConvInt8Int8,
     .BindInput("Diffs", {PLB_T(kInt32)})
     .BindInput("Bias", {PLB_T(kFloat)})
     .BindOutput("Output", {PLB_T(kInt8)})
+    .Finalize();
+
+// calib between fp32 and int8 layers (x86 registrations: lite/kernels/x86/calib_compute.cc:153-168)
+REGISTER_LITE_KERNEL(calib, kCUDA, kInt8, kNCHW, plbk::CalibFp32ToInt8Compute, fp32_to_int8)
+    .BindInput("Input", {PLB_T(kFloat)})
+    .BindOutput("Out", {PLB_T(kInt8)})
+    .Finalize();
+REGISTER_LITE_KERNEL(calib, kCUDA, kInt8, kNCHW, plbk::CalibInt8ToFp32Compute, int8_to_fp32)
+    .BindInput("Input", {PLB_T(kInt8)})
+    .BindOutput("Out", {PLB_T(kFloat)})
+    .Finalize();
+REGISTER_LITE_KERNEL(calib_once, kCUDA, kInt8, kNCHW, plbk::CalibFp32ToInt8Compute, fp32_to_int8)
+    .BindInput("Input", {PLB_T(kFloat)})
+    .BindOutput("Out", {PLB_T(kInt8)})
+    .Finalize();
+REGISTER_LITE_KERNEL(calib_once, kCUDA, kInt8, kNCHW, plbk::CalibInt8ToFp32Compute, int8_to_fp32)
+    .BindInput("Input", {PLB_T(kInt8)})
+    .BindOutput("Out", {PLB_T(kFloat)})
+    .Finalize();
+
+// host <-> device copies (XPU registrations: lite/kernels/xpu/io_copy_compute.cc:175-269)
+#define PLB_ANY(target) LiteType::GetTensorTy(TARGET(target), PRECISION(kAny), DATALAYOUT(kAny))
+REGISTER_LITE_KERNEL(io_copy, kCUDA, kAny, kAny, plbk::IoCopyHostToCudaCompute, host_to_device)
+    .BindInput("Input", {PLB_ANY(kHost)})
+    .BindOutput("Out", {PLB_ANY(kCUDA)})
+    .Finalize();
+REGISTER_LITE_KERNEL(io_copy, kCUDA, kAny, kAny, plbk::IoCopyCudaToHostCompute, device_to_host)
+    .BindInput("Input", {PLB_ANY(kCUDA)})
+    .BindOutput("Out", {PLB_ANY(kHost)})
+    .Finalize();
+REGISTER_LITE_KERNEL(io_copy_once, kCUDA, kAny, kAny, plbk::IoCopyHostToCudaCompute, host_to_device)
+    .BindInput("Input", {PLB_ANY(kHost)})
+    .BindOutput("Out", {PLB_ANY(kCUDA)})
+    .Finalize();
+REGISTER_LITE_KERNEL(io_copy_once, kCUDA, kAny, kAny, plbk::IoCopyCudaToHostCompute, device_to_host)
+    .BindInput("Input", {PLB_ANY(kCUDA)})
+    .BindOutput("Out", {PLB_ANY(kHost)})
+    .Finalize();
+
+REGISTER_LITE_KERNEL(softmax, kCUDA, kFloat, kNCHW, plbk::SoftmaxCompute, def)
+    .BindInput("X", {PLB_T(kFloat)})
+    .BindOutput("Out", {PLB_T(kFloat)})
     .Finalize();

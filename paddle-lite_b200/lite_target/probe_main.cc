@@ -210,6 +210,81 @@ int main() {
     std::printf("fc fp32_out: %zu of %zu outputs differ\n", bad, want.size());
     failures += bad != 0;
   }
+  // ---------------------------------------------------------------- io_copy -> calib -> calib -> io_copy
+  // host fp32 -> device (io_copy/host_to_device) -> int8 (calib/fp32_to_int8) -> fp32
+  // (calib/int8_to_fp32) -> host (io_copy/device_to_host), as type_precision_cast_pass and the
+  // io_copy pass chain them around an int8 sub-graph
+  {
+    const int n = 5000;
+    const float scale = 0.037f;
+    std::vector<float> src(n);
+    for (auto& v : src) v = 0.01f * rnd(-600, 600);
+    std::vector<float> want(n);
+    for (int i = 0; i < n; ++i) {
+      float v = src[i] * (1.f / scale);
+      v = v > -127.f ? v : -127.f;
+      float r = std::nearbyintf(v);
+      r = r > 127.f ? 127.f : r;
+      want[i] = r * scale;
+    }
+    void *d_f = nullptr, *d_q = nullptr, *d_g = nullptr;
+    CUDA_OK(cudaMalloc(&d_f, n * 4));
+    CUDA_OK(cudaMalloc(&d_q, n));
+    CUDA_OK(cudaMalloc(&d_g, n * 4));
+    Tensor h_in, t_f, t_q, t_g, h_out;
+    h_in.Resize(DDim(std::vector<int64_t>{n}));
+    h_in.set_precision(PRECISION(kFloat));
+    std::copy(src.begin(), src.end(), h_in.mutable_data<float>());
+    wrap_device(&t_f, d_f, n * 4, {n}, PRECISION(kFloat));
+    wrap_device(&t_q, d_q, n, {n}, PRECISION(kInt8));
+    wrap_device(&t_g, d_g, n * 4, {n}, PRECISION(kFloat));
+    auto pick = [](const char* op, paddle::lite_api::PrecisionType prec, paddle::lite_api::DataLayoutType layout,
+                   const char* alias) -> std::unique_ptr<KernelBase> {
+      auto list = KernelRegistry::Global().Create(op, TARGET(kCUDA), prec, layout);
+      for (auto& k : list)
+        if (k->alias() == alias) return std::move(k);
+      return nullptr;
+    };
+    auto run = [](std::unique_ptr<KernelBase>& k) {
+      k->SetContext(std::unique_ptr<paddle::lite::KernelContext>(new paddle::lite::KernelContext));
+      k->Launch();
+    };
+    auto k_in = pick("io_copy", PRECISION(kAny), DATALAYOUT(kAny), "host_to_device");
+    auto k_q = pick("calib", PRECISION(kInt8), DATALAYOUT(kNCHW), "fp32_to_int8");
+    auto k_f = pick("calib", PRECISION(kInt8), DATALAYOUT(kNCHW), "int8_to_fp32");
+    auto k_out = pick("io_copy", PRECISION(kAny), DATALAYOUT(kAny), "device_to_host");
+    if (!k_in || !k_q || !k_f || !k_out) {
+      std::printf("FAIL: io_copy / calib kernels are not in the KernelRegistry\n");
+      return 1;
+    }
+    paddle::lite::operators::IoCopyParam p_in{};
+    p_in.x = &h_in;
+    p_in.y = &t_f;
+    k_in->SetParam(p_in);
+    run(k_in);
+    paddle::lite::operators::CalibParam p_q{};
+    p_q.input = &t_f;
+    p_q.output = &t_q;
+    p_q.scale = scale;
+    k_q->SetParam(p_q);
+    run(k_q);
+    paddle::lite::operators::CalibParam p_f{};
+    p_f.input = &t_q;
+    p_f.output = &t_g;
+    p_f.scale = scale;
+    k_f->SetParam(p_f);
+    run(k_f);
+    paddle::lite::operators::IoCopyParam p_out{};
+    p_out.x = &t_g;
+    p_out.y = &h_out;
+    k_out->SetParam(p_out);
+    run(k_out);
+    const float* got = h_out.data<float>();
+    size_t bad = 0;
+    for (int i = 0; i < n; ++i) bad += got[i] != want[i];
+    std::printf("io_copy -> calib -> calib -> io_copy: %zu of %d values differ\n", bad, n);
+    failures += bad != 0;
+  }
   std::printf(failures ? "PROBE FAILED\n" : "PROBE OK\n");
   return failures ? 1 : 0;
 }

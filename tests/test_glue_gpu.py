@@ -3,7 +3,7 @@ import numpy as np
 import pytest
 import torch
 
-from helpers import O
+from helpers import O, assert_f32_close
 
 pytestmark = pytest.mark.gpu
 
@@ -59,3 +59,19 @@ def test_pooling(plb, ctx):
     ctx.sync()
     assert np.array_equal(avg.cpu().numpy(), want)
     assert np.array_equal(q.cpu().numpy(), O.calib_f32_to_i8(want, 0.01))
+
+
+@pytest.mark.parametrize("rows,cols", [(128, 1000), (3, 7), (2, 5000), (0, 10)])
+def test_softmax_rows(plb, ctx, rows, cols):
+    """fp32 tolerance of the path: 1e-5 relative (largest output as floor) against the oracle's
+    double-precision evaluation of the reference form."""
+    rng = np.random.default_rng(rows * 31 + cols)
+    x = (rng.standard_normal((rows, cols)) * 6).astype(np.float32)
+    if rows > 1:
+        x[1, 0] = 150.0
+    y = ctx.softmax(torch.from_numpy(x).cuda()).cpu().numpy()
+    ctx.sync()
+    if rows == 0:
+        return
+    want = O.softmax(x)
+    assert_f32_close(y, want, rel=1e-5, floor=float(want.max()))

@@ -163,3 +163,15 @@ def test_numpy_encoder_of_the_package_matches_the_oracle_encoder(dtype, semi, m,
     assert np.array_equal(a["nonzero_weights"], b["nonzero_weights"])
     assert np.array_equal(a["oc_nonzeros"], b["oc_nonzeros"])
     assert np.array_equal(a["diffs"], b["diffs"])
+
+
+def test_softmax_oracle_matches_numpy():
+    rng = np.random.default_rng(5)
+    x = (rng.standard_normal((7, 1000)) * 8).astype(np.float32)
+    x[3, 10] = 200.0  # everything else in that row is clipped at -64
+    y = O.softmax(x)
+    d = (x - x.max(axis=1, keepdims=True)).astype(np.float64)  # the shift is a float subtraction, as in the reference
+    e = np.exp(np.maximum(d, -64.0))
+    want = e / e.sum(axis=1, keepdims=True)
+    assert np.allclose(y, want, rtol=1e-6, atol=0)
+    assert np.allclose(y.sum(axis=1), 1.0, atol=1e-5)

@@ -27,7 +27,7 @@ def sparse_weights(seed, cout, cin, semi, keep=0.2):
 SHAPES = [(32, 64, 12, 2), (128, 128, 14, 2), (256, 256, 7, 3), (109, 33, 5, 1), (512, 512, 7, 1)]
 
 
-@pytest.mark.parametrize("impl", [1, 2], ids=["walk", "densified"])
+@pytest.mark.parametrize("impl", [1, 2, 0], ids=["walk", "densified", "auto"])
 @pytest.mark.parametrize("semi", [False, True], ids=["unstructured", "semi"])
 @pytest.mark.parametrize("cin,cout,side,batch", SHAPES)
 def test_sparse_int8(plb, ctx, cin, cout, side, batch, semi, impl):
