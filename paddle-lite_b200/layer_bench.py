@@ -6,6 +6,7 @@
     python paddle-lite_b200/layer_bench.py fc     --m 4096 --kdim 4096 --n 4096 [--out i8|f32]
     python paddle-lite_b200/layer_bench.py sparse --cin 128 --cout 128 --hw 56 --batch 256 [--fp32] [--semi] [--impl walk|dense]
     python paddle-lite_b200/layer_bench.py fc-sweep | sparse-sweep      # the shapes of the benchmark configs
+    python paddle-lite_b200/layer_bench.py int8-peak                    # library int8 GEMM (cuBLASLt via torch._int_mm) as a measured denominator
 
 Prints one JSON line per layer: microseconds per launch (CUDA events on the launching stream,
 after a warm-up that also brings the clocks up), algorithmic bytes and operations, and the
@@ -69,7 +70,7 @@ def report(name, us, nbytes, ops, extra=None):
 
 def main():
     ap = argparse.ArgumentParser()
-    ap.add_argument("kind", choices=["conv", "dw", "fc", "sparse", "fc-sweep", "sparse-sweep"])
+    ap.add_argument("kind", choices=["conv", "dw", "fc", "sparse", "fc-sweep", "sparse-sweep", "int8-peak"])
     ap.add_argument("--cin", type=int, default=64)
     ap.add_argument("--cout", type=int, default=64)
     ap.add_argument("--hw", type=int, default=56)
@@ -163,6 +164,14 @@ def main():
                2.0 * nnz * hw * hw * batch, {"nnz": nnz})
         ctx.sync()
 
+    if args.kind == "int8-peak":
+        # not a kernel of this library: the vendor int8 GEMM on the same GPU, as a measured tensor-core denominator
+        for n in (4096, 8192):
+            a = torch.randint(-127, 128, (n, n), dtype=torch.int8, device="cuda")
+            b = torch.randint(-127, 128, (n, n), dtype=torch.int8, device="cuda").t().contiguous().t()
+            us = time_launches(lambda: torch._int_mm(a, b), args.iters, args.warm)
+            report("cublaslt int8 gemm %d^3 (int32 out)" % n, us, 2 * n * n + 4 * n * n, 2.0 * n ** 3)
+        return
     if args.kind == "conv":
         conv_layer(args.cin, args.hw, args.cout, args.k, args.stride, args.pad, args.batch, args.out)
     elif args.kind == "dw":
