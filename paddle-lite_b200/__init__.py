@@ -205,6 +205,14 @@ class Context:
         _check(lib().plb_maxpool_nhwc_i8(self.handle, _dev_ptr(x), _dev_ptr(y), n, c, h, w, k, stride, pad))
         return y
 
+    def copy_h2d(self, dst, src_host):
+        """Enqueue a host -> device copy of a C-contiguous numpy array into `dst` on the ctx stream."""
+        _check(lib().plb_copy_h2d(self.handle, _dev_ptr(dst), C.c_void_p(src_host.ctypes.data), src_host.nbytes))
+
+    def copy_d2h(self, dst_host, src):
+        """Device -> host copy into a C-contiguous numpy array; returns when the bytes have arrived."""
+        _check(lib().plb_copy_d2h(self.handle, C.c_void_p(dst_host.ctypes.data), _dev_ptr(src), dst_host.nbytes))
+
     def softmax(self, x, out=None):
         """Row softmax of a [rows, cols] fp32 tensor (reference form: shift by the row max, clip at -64)."""
         import torch

@@ -172,14 +172,15 @@ __global__ void __launch_bounds__(kBlock)
   pdl_sync_with_previous_kernel();
   constexpr int TH = S == 1 ? 2 : 1, TW = 4;
   constexpr int IH = (TH - 1) * S + 3, IW = (TW - 1) * S + 3;  // 4 x 6 or 3 x 9 input pixels
-  long idx = static_cast<long>(blockIdx.x) * kBlock + threadIdx.x;
-  if (idx >= total) return;
-  const int cq = static_cast<int>(idx % cquads);
-  idx /= cquads;
-  const int tx = static_cast<int>(idx % tiles_x);
-  idx /= tiles_x;
-  const int ty = static_cast<int>(idx % tiles_y);
-  const long n = idx / tiles_y;
+  // grid = (channel quads x tile columns, tile rows, images): one division per thread
+  const int idx = blockIdx.x * kBlock + threadIdx.x;
+  if (idx >= cquads * tiles_x) return;
+  const int tx = idx / cquads;
+  const int cq = idx - tx * cquads;
+  const int ty = blockIdx.y;
+  const long n = blockIdx.z;
+  (void)tiles_y;
+  (void)total;
   const int oh0 = ty * TH, ow0 = tx * TW;
   const int c0 = cq * 4;
 
@@ -203,16 +204,28 @@ __global__ void __launch_bounds__(kBlock)
   const int8_t* xn = x + n * g.h * static_cast<long>(g.w) * g.cin_stride + c0;
   // all loads of the patch are issued before any arithmetic: one register per 4 input bytes
   uint32_t raw[IH][IW];
+  if (ih0 >= 0 && ih0 + IH <= g.h && iw0 >= 0 && iw0 + IW <= g.w) {
+    // interior patch: no bounds tests, one pointer per row
+    const int8_t* row = xn + (static_cast<long>(ih0) * g.w + iw0) * g.cin_stride;
+    const long row_step = static_cast<long>(g.w) * g.cin_stride;
 #pragma unroll
-  for (int iy = 0; iy < IH; ++iy) {
-    const int ih = ih0 + iy;
-    const bool row_ok = ih >= 0 && ih < g.h;
+    for (int iy = 0; iy < IH; ++iy, row += row_step) {
 #pragma unroll
-    for (int ix = 0; ix < IW; ++ix) {
-      const int iw = iw0 + ix;
-      raw[iy][ix] = 0;
-      if (row_ok && iw >= 0 && iw < g.w)
-        raw[iy][ix] = __ldg(reinterpret_cast<const uint32_t*>(xn + (static_cast<long>(ih) * g.w + iw) * g.cin_stride));
+      for (int ix = 0; ix < IW; ++ix)
+        raw[iy][ix] = __ldg(reinterpret_cast<const uint32_t*>(row + ix * g.cin_stride));
+    }
+  } else {
+#pragma unroll
+    for (int iy = 0; iy < IH; ++iy) {
+      const int ih = ih0 + iy;
+      const bool row_ok = ih >= 0 && ih < g.h;
+#pragma unroll
+      for (int ix = 0; ix < IW; ++ix) {
+        const int iw = iw0 + ix;
+        raw[iy][ix] = 0;
+        if (row_ok && iw >= 0 && iw < g.w)
+          raw[iy][ix] = __ldg(reinterpret_cast<const uint32_t*>(xn + (static_cast<long>(ih) * g.w + iw) * g.cin_stride));
+      }
     }
   }
 #pragma unroll
@@ -891,8 +904,10 @@ int dwconv_launch(plb_ctx* ctx, const ConvGeom& g, const int8_t* x, const int8_t
     const bool i8 = out.mode == OUT_I8;
     DwKernel k = g.stride_h == 1 ? (i8 ? pick_dw_act<1, true>(out.epi.act) : pick_dw_act<1, false>(out.epi.act))
                                  : (i8 ? pick_dw_act<2, true>(out.epi.act) : pick_dw_act<2, false>(out.epi.act));
-    PLB_CUDA(launch_kernel(k, dim3(blocks_for(total)), dim3(kBlock), 0, ctx->stream, g, x, w_tc, to_dev(out),
-                           cq, tiles_x, tiles_y, total));
+    if (tiles_y > 65535 || g.batch > 65535) return fail(PLB_E_UNSUPPORTED, "depthwise 3x3: more than 65535 tile rows or images");
+    dim3 grid(static_cast<unsigned>((static_cast<long>(cq) * tiles_x + kBlock - 1) / kBlock), static_cast<unsigned>(tiles_y),
+              static_cast<unsigned>(g.batch));
+    PLB_CUDA(launch_kernel(k, grid, dim3(kBlock), 0, ctx->stream, g, x, w_tc, to_dev(out), cq, tiles_x, tiles_y, total));
     ctx->launches++;
     return PLB_OK;
   }

@@ -75,3 +75,16 @@ def test_softmax_rows(plb, ctx, rows, cols):
         return
     want = O.softmax(x)
     assert_f32_close(y, want, rel=1e-5, floor=float(want.max()))
+
+
+def test_copies_follow_the_ctx_stream(plb, ctx):
+    """io_copy pair: h2d is ordered before the kernels that follow it on the ctx stream, d2h
+    returns with the data."""
+    rng = np.random.default_rng(9)
+    src = rng.standard_normal(100003).astype(np.float32)
+    d = torch.empty(src.size, dtype=torch.float32, device="cuda")
+    ctx.copy_h2d(d, src)
+    q = ctx.calib_f32_to_i8(d, 0.05)
+    back = np.empty(src.size, dtype=np.int8)
+    ctx.copy_d2h(back, q)
+    assert np.array_equal(back, O.calib_f32_to_i8(src, 0.05))
