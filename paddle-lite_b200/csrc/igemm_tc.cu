@@ -626,6 +626,26 @@ __device__ __forceinline__ void issue_window(uint32_t d_tmem, uint32_t slab_lo, 
   }
 }
 
+// Any filter size with CC channel chunks and MPS MMAs per chunk unrolled: the loops over the taps
+// stay, everything inside a tap is "tap base + constant".
+template <int CC, int MPS>
+__device__ __forceinline__ void issue_window_taps(int kh, int kw, uint32_t d_tmem, uint32_t slab_lo, uint32_t row_lo,
+                                                  uint32_t col_lo, uint32_t plane_lo, uint32_t hi_a, uint32_t b_lo,
+                                                  uint32_t stage_b_lo, uint32_t hi_b, uint32_t idesc, bool leader) {
+  uint32_t accumulate = 0;
+  uint32_t row_a = slab_lo;
+  for (int r = 0; r < kh; ++r, row_a += row_lo) {
+    uint32_t tap_a = row_a;
+    for (int sx = 0; sx < kw; ++sx, tap_a += col_lo, b_lo += CC * stage_b_lo) {
+#pragma unroll
+      for (int cc = 0; cc < CC; ++cc) {
+        issue_kstep<MPS>(d_tmem, tap_a + cc * plane_lo, hi_a, b_lo + cc * stage_b_lo, hi_b, idesc, accumulate, leader);
+        accumulate = 1;
+      }
+    }
+  }
+}
+
 // ---------------------------------------------------------------- the kernel
 // Persistent: one CTA per SM walks tiles t = blockIdx.x, blockIdx.x + gridDim.x, ...;
 // consecutive tile ids share the same 128 pixels (channel tile fastest) so that CTAs running
@@ -879,7 +899,14 @@ __global__ void __launch_bounds__(kThreads, 1)
     const uint32_t col_lo = static_cast<uint32_t>(a.dil_w * a.kc) >> 4;
     const uint32_t plane_lo = static_cast<uint32_t>(a.plane_bytes) >> 4;
     int window_shape = 0;  // which unrolled issue sequence applies
+    if (a.slab && !a.b_stream) {  // other filter sizes: taps in a loop, the inside of a tap unrolled
+      if (a.cchunks == 1 && mma_per_stage == 1) window_shape = 11;
+      if (a.cchunks == 1 && mma_per_stage == 2) window_shape = 12;
+      if (a.cchunks == 1 && mma_per_stage == 4) window_shape = 14;
+      if (a.cchunks == 2 && mma_per_stage == 4) window_shape = 24;
+    }
     if (a.slab && a.kh == 4 && a.kw == 1 && a.cchunks == 1 && mma_per_stage == 2) window_shape = 4;  // row-folded 7x7 stem
+    if (a.slab && a.kh == 2 && a.kw == 1 && a.cchunks == 1 && mma_per_stage == 2) window_shape = 5;  // row-folded 3x3 stem
     if (a.slab && a.kh == 3 && a.kw == 3) {
       if (a.cchunks == 1 && mma_per_stage == 2) window_shape = 1;
       if (a.cchunks == 1 && mma_per_stage == 4) window_shape = 2;
@@ -1007,6 +1034,16 @@ __global__ void __launch_bounds__(kThreads, 1)
           issue_window<3, 3, 2, 4>(d_tmem, slab_lo, row_lo, col_lo, plane_lo, hi_a, bres_lo, stage_b_lo, hi_b, idesc, leader);
         } else if (window_shape == 4) {
           issue_window<4, 1, 1, 2>(d_tmem, slab_lo, row_lo, col_lo, plane_lo, hi_a, bres_lo, stage_b_lo, hi_b, idesc, leader);
+        } else if (window_shape == 5) {
+          issue_window<2, 1, 1, 2>(d_tmem, slab_lo, row_lo, col_lo, plane_lo, hi_a, bres_lo, stage_b_lo, hi_b, idesc, leader);
+        } else if (window_shape == 11) {
+          issue_window_taps<1, 1>(a.kh, a.kw, d_tmem, slab_lo, row_lo, col_lo, plane_lo, hi_a, bres_lo, stage_b_lo, hi_b, idesc, leader);
+        } else if (window_shape == 12) {
+          issue_window_taps<1, 2>(a.kh, a.kw, d_tmem, slab_lo, row_lo, col_lo, plane_lo, hi_a, bres_lo, stage_b_lo, hi_b, idesc, leader);
+        } else if (window_shape == 14) {
+          issue_window_taps<1, 4>(a.kh, a.kw, d_tmem, slab_lo, row_lo, col_lo, plane_lo, hi_a, bres_lo, stage_b_lo, hi_b, idesc, leader);
+        } else if (window_shape == 24) {
+          issue_window_taps<2, 4>(a.kh, a.kw, d_tmem, slab_lo, row_lo, col_lo, plane_lo, hi_a, bres_lo, stage_b_lo, hi_b, idesc, leader);
         } else {
           uint32_t b_lo = bres_lo;
           uint32_t row_a = slab_lo;
