@@ -695,25 +695,30 @@ __global__ void __launch_bounds__(kThreads, 1)
   const int gpb = kEpilogueGroups / nb;  // epilogue groups sharing one buffer (split by columns)
   const uint32_t tmem_cols = acc_cols * nb < 32 ? 32 : acc_cols * nb;
 
-  if (threadIdx.x == kProducerWarp * 32) {
-    for (int s = 0; s < a.stages; ++s) {
-      mbar_init(smem_u32(&full_bar[s]), 1);
-      mbar_init(smem_u32(&empty_bar[s]), 1);
+  if (warp == kProducerWarp) {
+    // All barriers live in one array (full .. bempty); the lanes of this warp initialise them in
+    // parallel (a single thread took ~1 us for the 89 of them).  Only the "accumulator drained"
+    // barriers expect more than one arrival.
+    constexpr int kBarriers = 2 * kMaxStages + 2 * kMaxAccBufs + 2 * kEpilogueWarps + 1 + 2 * kMaxBStages;
+    const int first_acc_empty = 2 * kMaxStages + kMaxAccBufs;
+    for (int i = lane; i < kBarriers; i += 32) {
+      const bool drained = i >= first_acc_empty && i < first_acc_empty + kMaxAccBufs;
+      mbar_init(smem_u32(&full_bar[i]), drained ? 4 * gpb : 1);
     }
-    for (int b = 0; b < nb; ++b) {
-      mbar_init(smem_u32(&acc_full[b]), 1);
-      mbar_init(smem_u32(&acc_empty[b]), 4 * gpb);
-    }
-    for (int w = 0; w < 2 * kEpilogueWarps; ++w) mbar_init(smem_u32(&res_bar[w]), 1);
-    mbar_init(smem_u32(bres_bar), 1);
-    for (int t = 0; t < kMaxBStages; ++t) {
-      mbar_init(smem_u32(&bfull_bar[t]), 1);
-      mbar_init(smem_u32(&bempty_bar[t]), 1);
-    }
-    *abort_flag = 0;
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
-    asm volatile("prefetch.tensormap [%0];" ::"l"(reinterpret_cast<uint64_t>(&tmA)) : "memory");
-    asm volatile("prefetch.tensormap [%0];" ::"l"(reinterpret_cast<uint64_t>(&tmB)) : "memory");
+    if (lane == 0) {
+      *abort_flag = 0;
+      asm volatile("prefetch.tensormap [%0];" ::"l"(reinterpret_cast<uint64_t>(&tmA)) : "memory");
+      asm volatile("prefetch.tensormap [%0];" ::"l"(reinterpret_cast<uint64_t>(&tmB)) : "memory");
+    }
+    __syncwarp();
+    if (a.resident_b && lane == 0) {
+      // small filter, one channel tile: fetch all of it once; the ring then carries activations only.
+      // Filters are not written by the preceding kernel, so this copy does not wait for it.
+      const uint32_t bar = smem_u32(bres_bar);
+      mbar_expect_tx(bar, static_cast<uint32_t>(a.ksteps * stage_b));
+      for (int ks = 0; ks < a.ksteps; ++ks) tma_load_2d(smem_u32(smem_bres) + ks * stage_b, &tmB, bar, ks * a.kc, 0);
+    }
   }
   if (warp == kMmaWarp) {
     asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(
@@ -746,16 +751,6 @@ __global__ void __launch_bounds__(kThreads, 1)
     uint32_t empty_parity = 1;  // a fresh barrier passes a wait on parity 1
     bool ok = true;
     const uint32_t smem_base = smem_u32(smem);
-    if (a.resident_b && leader) {
-      // small filter, one channel tile: fetch all of it once; the ring then carries activations only
-      const uint32_t bar = smem_u32(bres_bar);
-      mbar_expect_tx(bar, static_cast<uint32_t>(a.ksteps * stage_b));
-      for (int ks = 0; ks < a.ksteps; ++ks) {
-        const uint32_t dst = smem_u32(smem_bres) + ks * stage_b;
-        tma_load_2d(dst, &tmB, bar, ks * a.kc, 0);
-      }
-    }
-    __syncwarp();
     // filter stream of one tile (window mode with a streamed filter): ksteps / kgroup boxes of
     // kgroup K steps each into the filter ring
     int sb = 0;
