@@ -216,6 +216,16 @@ def cpu_baseline(qnet, spec, sample_images, repeats=1):
 
 
 # --------------------------------------------------------------------------- main
+# DRAM read + write bytes per tcgen05 launch, from the ncu capture summarised in
+# profiles/bench_resnet50_b128_dram_traffic.md.  Traffic does not scale with the batch (small batches
+# stay in L2), so only the captured workload has a number.
+CAPTURED_TRAFFIC = {("resnet50", 128): 126.9e6}
+
+
+def captured_traffic(net, batch):
+    return CAPTURED_TRAFFIC.get((net, batch))
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -402,7 +412,9 @@ def main():
                      "ms_per_step": e2e_ms_step},
                 gpu_launches=int(launches_per_step * args.steps),
                 roofline={"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s",
-                          "frac": achieved / peak, "traffic": None, "peak_source": peak_kind + " copy bandwidth",
+                          "frac": achieved / peak, "traffic": captured_traffic(args.net, batch),
+                          "traffic_unit": "bytes per launch (DRAM read + write, ncu capture of this workload)",
+                          "peak_source": peak_kind + " copy bandwidth",
                           "kernel": "igemm_i8_tc_kernel", "launches_per_step": tc_launches,
                           "algorithmic_bytes_per_launch": total_bytes / tc_launches,
                           "avg_launch_us": 1e3 * tc_ms_step / tc_launches,
