@@ -68,3 +68,25 @@ def test_fc_errors(plb, ctx):
         plb.Fc(ctx, wq, ws[:3], 0.02, bias)
     fc = plb.Fc(ctx, wq, ws, 0.02, bias)
     assert fc.run(torch.empty((0, 64), dtype=torch.int8, device="cuda")).shape == (0, 8)
+
+
+@pytest.mark.parametrize("k,below", [(256, True), (288, False)])
+def test_extreme_accumulators(plb, ctx, k, below):
+    """Largest possible accumulators, on both sides of 2^22 (where float spacing is still below 1)
+    and beyond: all weights +-127, inputs -128 / 127.  k = 256: |acc| <= 4 161 536; k = 288: 4 681 728."""
+    m, n = 64, 64
+    w = np.where(np.arange(n)[None, :] % 2 == 0, 127, -127).astype(np.int8) * np.ones((k, 1), np.int8)
+    x = np.where(np.arange(m)[:, None] % 2 == 0, -128, 127).astype(np.int8) * np.ones((1, k), np.int8)
+    x[5, ::3] = 0
+    ws = np.full(n, 1e-6, np.float32)
+    bias = np.linspace(-1, 1, n).astype(np.float32)
+    acc_ref = O.fc_acc_i32(x, w)
+    assert (np.abs(acc_ref).max() < 2 ** 22) == below
+    y_ref = O.epilogue(acc_ref, ws, 0.5, bias, O.ACT_NONE, 0.0)
+    q_ref = O.epilogue(acc_ref, ws, 0.5, bias, O.ACT_NONE, 0.0, out_scale=0.02)
+    xd = dev(x)
+    y = plb.Fc(ctx, w, ws, 0.5, bias).run(xd).cpu().numpy()
+    q = plb.Fc(ctx, w, ws, 0.5, bias, out_scale=0.02).run(xd).cpu().numpy()
+    ctx.sync()
+    assert np.array_equal(y, y_ref)
+    assert np.array_equal(q, q_ref)
