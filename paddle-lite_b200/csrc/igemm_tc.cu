@@ -1274,8 +1274,10 @@ __global__ void __launch_bounds__(kThreads, 1)
             }
             epilogue_chunk_staged<MODE, ACT>(a, r, lane, n0 + c, st_w, st_b + lane * wq, (c - cbase) >> 4, b_swz,
                                              have_res);
-            fence_proxy_async_smem();
-            __syncwarp();
+            if (use_w) {  // make this chunk's staging writes visible to the copy engine
+              fence_proxy_async_smem();
+              __syncwarp();
+            }
             if (use_w && lane == 0) {
               if (a.slab) tma_store_4d(&tmOutW, st_w, n0 + c, s_w, s_h, s_img);
               else tma_store_2d(&tmOutW, st_w, n0 + c, row0);
@@ -1287,6 +1289,10 @@ __global__ void __launch_bounds__(kThreads, 1)
           TT_STOP(3);
         }
         if (wrote_b) {
+          if (!use_w) {  // int8-only output: one fence per tile instead of one per chunk
+            fence_proxy_async_smem();
+            __syncwarp();
+          }
           if (lane == 0) {
             if (a.slab) tma_store_4d(&tmOutB, st_b, n0 + cbase, s_w, s_h, s_img);
             else tma_store_2d(&tmOutB, st_b, n0 + cbase, row0);
