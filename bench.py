@@ -122,7 +122,13 @@ def layer_bytes(spec, batch):
     hw = {"x": (h, w)}
     total_bytes, macs, launches = 0, 0, 0
     per_layer = []
+    # projection shortcuts that run inside the block's last launch
+    shortcuts = importlib.import_module("paddle-lite_b200.networks").fusable_shortcuts(spec)
     for op in spec["ops"]:
+        if op["op"] == "conv" and op["dst"] in shortcuts:
+            ih, iw = hw[op["src"]]
+            hw[op["dst"]] = ((ih - 1) // op["s"] + 1, (iw - 1) // op["s"] + 1)
+            continue
         if op["op"] in ("conv", "conv_add_relu"):
             ih, iw = hw[op["src"]]
             oh, ow = (ih + 2 * op["p"] - op["k"]) // op["s"] + 1, (iw + 2 * op["p"] - op["k"]) // op["s"] + 1
@@ -132,12 +138,19 @@ def layer_bytes(spec, batch):
                 b += batch * oh * ow * op["cout"] * (1 if op["out"] == "i8" else 4)
                 hw[op["dst"]] = (oh, ow)
             else:
-                b += batch * oh * ow * op["cout"] * 4  # residual read
+                if op["residual"] in shortcuts:
+                    # fused block tail: the shortcut's input pixels and filter instead of a residual tensor
+                    sc = shortcuts[op["residual"]]
+                    b += batch * oh * ow * sc["cin"] + sc["cout"] * sc["cin"] + 8 * sc["cout"]
+                else:
+                    b += batch * oh * ow * op["cout"] * 4  # residual read
                 for key, size in (("dst_f32", 4), ("dst_i8", 1)):
                     if op[key]:
                         b += batch * oh * ow * op["cout"] * size
                         hw[op[key]] = (oh, ow)
             m = batch * oh * ow * op["cout"] * (op["cin"] // groups) * op["k"] ** 2
+            if op["op"] == "conv_add_relu" and op["residual"] in shortcuts:
+                m += batch * oh * ow * op["cout"] * shortcuts[op["residual"]]["cin"]
             if groups == 1 and op["src"] != "x":  # the stem runs with its staging kernel in the head
                 total_bytes += b
                 macs += m
@@ -342,6 +355,11 @@ def main():
                     conv.run_nhwc_add_relu(runner.buf[src], runner.buf[res], next_s, want_f32=df is not None,
                                            out_f32=runner.buf[df] if df else None,
                                            out_i8=runner.buf[dq] if dq else None)
+                elif st[0] == "block_add_relu":
+                    _, conv, src, sc_conv, sc_src, df, dq, next_s = st
+                    conv.run_nhwc_block_add_relu(runner.buf[src], sc_conv, runner.buf[sc_src], next_s,
+                                                 want_f32=df is not None, out_f32=runner.buf[df] if df else None,
+                                                 out_i8=runner.buf[dq] if dq else None)
                 elif st[0] == "fc":
                     st[1].run(runner.buf[st[2]], out=runner.buf[st[3]])
 

@@ -141,6 +141,16 @@ int plb_conv_acc_i32(plb_conv* conv, const int8_t* x, int32_t* acc, int batch);
  *   y_i8     [batch,ho,wo,cout] int8  (nullable = not stored), q = calib(y, next_scale) */
 int plb_conv_run_nhwc_add_relu(plb_conv* conv, const int8_t* x, const float* residual,
                                float* y_f32, int8_t* y_i8, float next_scale, int batch);
+/* A whole projection block tail in one launch: y = relu(conv(x) + shortcut(x_shortcut)), where both
+ * are unpadded 1x1 convolutions with the same output shape (the shortcut may have a stride) and no
+ * activation of their own, i.e. the reference sequence  conv2d(fp32_out) [main], conv2d(fp32_out)
+ * [shortcut], elementwise_add + relu, calib  with the shortcut's fp32 tensor never written.  The
+ * shortcut value is fma(acc2, ws2*in_s2, bias2) exactly as its own fp32_out kernel computes it, so
+ * the outputs are bit-identical to the unfused sequence.  Both layers prepared with
+ * out_dtype = PLB_OUT_F32 on the same ctx; x and x_shortcut channels-last.  A graph-level fusion of
+ * the kind the reference's MIR fusion passes perform; it has no single-kernel counterpart there. */
+int plb_conv_run_nhwc_block_add_relu(plb_conv* conv, const int8_t* x, plb_conv* shortcut, const int8_t* x_shortcut,
+                                     float* y_f32, int8_t* y_i8, float next_scale, int batch);
 int plb_conv_out_dims(const plb_conv* conv, int* ho, int* wo);
 void plb_conv_destroy(plb_conv* conv);
 

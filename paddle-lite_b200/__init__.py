@@ -64,6 +64,7 @@ SYMBOLS = {
     "plb_conv_run_static": (C.c_int, [_P, _P, _P, C.c_int]),
     "plb_conv_run_image_f32": (C.c_int, [_P, _P, _P, C.c_int]),
     "plb_conv_run_nhwc_add_relu": (C.c_int, [_P, _P, _P, _P, _P, C.c_float, C.c_int]),
+    "plb_conv_run_nhwc_block_add_relu": (C.c_int, [_P, _P, _P, _P, _P, _P, C.c_float, C.c_int]),
     "plb_conv_out_dims": (C.c_int, [_P, C.POINTER(C.c_int), C.POINTER(C.c_int)]),
     "plb_conv_destroy": (None, [_P]),
     "plb_fc_prepare": (C.c_int, [_P, C.c_int, C.c_int, C.c_int, C.c_float, C.c_float, C.c_float, C.c_int,
@@ -320,6 +321,22 @@ class Conv:
         _check(lib().plb_conv_run_nhwc_add_relu(self.handle, _dev_ptr(x), _dev_ptr(residual), _dev_ptr(yf),
                                                 _dev_ptr(yq), next_scale if next_scale is not None else 1.0,
                                                 n))
+        return yf, yq
+
+    def run_nhwc_block_add_relu(self, x, shortcut, x_shortcut, next_scale=None, want_f32=True, out_f32=None,
+                                out_i8=None):
+        """relu(self(x) + shortcut(x_shortcut)) in one launch (both unpadded 1x1 fp32-out layers without
+        activation); returns (fp32 tensor or None, int8 calib(next_scale) tensor or None)."""
+        import torch
+        n = x.shape[0]
+        shape = (n, self.ho, self.wo, self.desc.cout)
+        yf = out_f32 if out_f32 is not None else (
+            torch.empty(shape, dtype=torch.float32, device=x.device) if want_f32 else None)
+        yq = out_i8 if out_i8 is not None else (
+            torch.empty(shape, dtype=torch.int8, device=x.device) if next_scale is not None else None)
+        _check(lib().plb_conv_run_nhwc_block_add_relu(self.handle, _dev_ptr(x), shortcut.handle, _dev_ptr(x_shortcut),
+                                                      _dev_ptr(yf), _dev_ptr(yq),
+                                                      next_scale if next_scale is not None else 1.0, n))
         return yf, yq
 
     def close(self):

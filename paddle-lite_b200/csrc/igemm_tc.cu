@@ -65,6 +65,12 @@ struct IgemmArgs {
   // window mode with a filter too large to stay resident: the filter streams through its own ring,
   // kgroup K steps per TMA box (a 3-D box: K step is the outermost box dimension)
   int b_stream, kgroup, b_stages;
+  // dual mode (OUT_ADD_RELU): a second 1x1 GEMM (the shortcut convolution of a residual block)
+  // accumulates into the columns next to the main accumulator; the epilogue turns it into the
+  // residual value fma(acc2, scale2, bias2) instead of reading a residual tensor
+  int dual, ksteps2, cchunks2, im2col2, stride2_h, stride2_w;
+  const float* scale2;
+  const float* bias2;
   int pair;                            // two consecutive tiles of a CTA share one pass over the filter stream
   int out_mode, ldy;
   void* y;
@@ -88,7 +94,7 @@ struct IgemmArgs {
 #define TT_DECL(n) long long tt_acc[n] = {}; long long tt_t0 = 0
 #define TT_START() tt_t0 = clock64()
 #define TT_STOP(i) tt_acc[i] += clock64() - tt_t0
-#define TT_FLUSH(base, n) do { for (int tt_i = 0; tt_i < (n); ++tt_i) a.timing[blockIdx.x * 16 + (base) + tt_i] = tt_acc[tt_i]; } while (0)
+#define TT_FLUSH(base, n) do { for (int tt_i = 0; tt_i < (n); ++tt_i) a.timing[blockIdx.x * 24 + (base) + tt_i] = tt_acc[tt_i]; } while (0)
 #else
 #define TT_DECL(n)
 #define TT_START()
@@ -658,7 +664,9 @@ __global__ void __launch_bounds__(kThreads, 1)
                        const __grid_constant__ CUtensorMap tmB,
                        const __grid_constant__ CUtensorMap tmRes,
                        const __grid_constant__ CUtensorMap tmOutW,
-                       const __grid_constant__ CUtensorMap tmOutB, const IgemmArgs a) {
+                       const __grid_constant__ CUtensorMap tmOutB,
+                       const __grid_constant__ CUtensorMap tmA2,
+                       const __grid_constant__ CUtensorMap tmB2, const IgemmArgs a) {
 #ifdef PLB_TC_TIMING
   const long long tt_entry = clock64();
 #endif
@@ -693,7 +701,8 @@ __global__ void __launch_bounds__(kThreads, 1)
   while (acc_cols < static_cast<uint32_t>(a.bn)) acc_cols <<= 1;
   const int nb = a.acc_bufs;  // 4 or 2 (2 when the tile is 256 wide or a CTA has only a tile or two to do)
   const int gpb = kEpilogueGroups / nb;  // epilogue groups sharing one buffer (split by columns)
-  const uint32_t tmem_cols = acc_cols * nb < 32 ? 32 : acc_cols * nb;
+  const uint32_t acc_stride = a.dual ? 2 * acc_cols : acc_cols;  // dual mode: main and shortcut accumulators side by side
+  const uint32_t tmem_cols = acc_stride * nb < 32 ? 32 : acc_stride * nb;
 
   if (warp == kProducerWarp) {
     // All barriers live in one array (full .. bempty); the lanes of this warp initialise them in
@@ -734,7 +743,7 @@ __global__ void __launch_bounds__(kThreads, 1)
   // the set-up above overlapped the previous kernel's tail; from here on global memory is touched
   pdl_sync_with_previous_kernel();
 #ifdef PLB_TC_TIMING
-  if (threadIdx.x == 0) a.timing[blockIdx.x * 16 + 10] = clock64() - tt_entry;  // prologue + wait for the previous kernel
+  if (threadIdx.x == 0) a.timing[blockIdx.x * 24 + 10] = clock64() - tt_entry;  // prologue + wait for the previous kernel
 #endif
 
   if (warp == kProducerWarp) {
@@ -826,7 +835,7 @@ __global__ void __launch_bounds__(kThreads, 1)
       const int m0 = tile_m * kTileM;
       const int n0 = (tile - tile_m * a.tiles_n) * a.bn;
       int q0 = 0, p0 = 0, cn = 0;
-      if (a.im2col) {
+      if (a.im2col || (a.dual && a.im2col2)) {
         q0 = m0 % a.wo;
         const int t = m0 / a.wo;
         p0 = t % a.ho;
@@ -864,13 +873,28 @@ __global__ void __launch_bounds__(kThreads, 1)
           empty_parity ^= 1;
         }
       }
+      // dual mode: the K steps of the shortcut GEMM follow (1x1 filter, stride stride2, no padding)
+      for (int ks = 0; a.dual && ok && ks < a.ksteps2; ++ks) {
+        ok = mbar_wait(smem_u32(&empty_bar[s]), empty_parity, abort_flag, a.status, FAULT_WAIT_EMPTY);
+        if (!ok) break;
+        const uint32_t bar = smem_u32(&full_bar[s]);
+        const uint32_t dst_a = smem_base + s * stage_bytes;
+        mbar_expect_tx_if(bar, static_cast<uint32_t>(stage_bytes), leader);
+        if (a.im2col2) tma_load_im2col_4d_if(dst_a, &tmA2, bar, ks * a.kc, q0 * a.stride2_w, p0 * a.stride2_h, cn, 0, 0, leader);
+        else tma_load_2d_if(dst_a, &tmA2, bar, ks * a.kc, m0, leader);
+        tma_load_2d_if(dst_a + stage_a, &tmB2, bar, ks * a.kc, n0, leader);
+        if (++s == a.stages) {
+          s = 0;
+          empty_parity ^= 1;
+        }
+      }
     }
 #ifdef PLB_TC_TIMING
     tt_acc[1] = clock64() - tt_begin;
 #endif
     if (lane == 0) TT_FLUSH(0, 2);
 #ifdef PLB_TC_TIMING
-    if (lane == 0) a.timing[blockIdx.x * 16 + 15] = tt_bwait;
+    if (lane == 0) a.timing[blockIdx.x * 24 + 15] = tt_bwait;
 #endif
   } else if (warp == kMmaWarp) {
     // ------------------------------------------------------------ MMA issuer
@@ -919,7 +943,7 @@ __global__ void __launch_bounds__(kThreads, 1)
       tc_fence_after();
     }
 #ifdef PLB_TC_TIMING
-    if (lane == 0) a.timing[blockIdx.x * 16 + 11] = clock64() - tt_entry;  // resident filter landed
+    if (lane == 0) a.timing[blockIdx.x * 24 + 11] = clock64() - tt_entry;  // resident filter landed
     bool tt_first = true;
 #endif
     const uint32_t bres_lo = ((smem_u32(smem_bres) >> 4) & 0x3FFFu) | lo_flags;
@@ -933,7 +957,7 @@ __global__ void __launch_bounds__(kThreads, 1)
       TT_STOP(0);
       if (!ok) break;
       tc_fence_after();
-      const uint32_t d_tmem = tmem_base + buf * acc_cols;
+      const uint32_t d_tmem = tmem_base + buf * acc_stride;
       uint32_t accumulate = 0;
       if (a.slab) {
         TT_START();
@@ -962,7 +986,7 @@ __global__ void __launch_bounds__(kThreads, 1)
                            FAULT_WAIT_FULL);
             if (!ok) break;
             tc_fence_after();
-            d_tmem2 = tmem_base + buf2 * acc_cols;
+            d_tmem2 = tmem_base + buf2 * acc_stride;
             slab2_delta = (ring_lo + s2 * stage_lo) - slab_lo;  // modular difference of the descriptor fields
           }
           // K steps in filter order (filter row, filter column, channel chunk); every kgroup of them
@@ -1069,7 +1093,7 @@ __global__ void __launch_bounds__(kThreads, 1)
         TT_STOP(1);
         if (!ok) break;
 #ifdef PLB_TC_TIMING
-        if (tt_first && lane == 0) a.timing[blockIdx.x * 16 + 12] = clock64() - tt_entry;  // first operands landed
+        if (tt_first && lane == 0) a.timing[blockIdx.x * 24 + 12] = clock64() - tt_entry;  // first operands landed
         tt_first = false;
 #endif
         tc_fence_after();
@@ -1088,11 +1112,29 @@ __global__ void __launch_bounds__(kThreads, 1)
           full_parity ^= 1;
         }
       }
+      // dual mode: the shortcut GEMM accumulates into the columns next to the main accumulator
+      accumulate = 0;
+      for (int ks = 0; a.dual && ok && ks < a.ksteps2; ++ks) {
+        ok = mbar_wait(smem_u32(&full_bar[s]), full_parity, abort_flag, a.status, FAULT_WAIT_FULL);
+        if (!ok) break;
+        tc_fence_after();
+        const uint32_t a_lo = ring_lo + s * stage_lo;
+        const uint32_t b_lo = a_lo + (static_cast<uint32_t>(stage_a) >> 4);
+        if (mma_per_stage == 4) issue_kstep<4>(d_tmem + acc_cols, a_lo, hi_a, b_lo, hi_b, idesc, accumulate, leader);
+        else if (mma_per_stage == 2) issue_kstep<2>(d_tmem + acc_cols, a_lo, hi_a, b_lo, hi_b, idesc, accumulate, leader);
+        else issue_kstep<1>(d_tmem + acc_cols, a_lo, hi_a, b_lo, hi_b, idesc, accumulate, leader);
+        accumulate = 1;
+        tc_commit_if(smem_u32(&empty_bar[s]), leader);
+        if (++s == a.stages) {
+          s = 0;
+          full_parity ^= 1;
+        }
+      }
       tc_commit_if(smem_u32(&acc_full[buf]), leader);  // accumulator complete (or drained on a fault)
     }
     if (lane == 0) TT_FLUSH(2, 4);
 #ifdef PLB_TC_TIMING
-    if (lane == 0) a.timing[blockIdx.x * 16 + 13] = clock64() - tt_entry;  // all MMAs issued
+    if (lane == 0) a.timing[blockIdx.x * 24 + 13] = clock64() - tt_entry;  // all MMAs issued
 #endif
   } else {
     // ------------------------------------------------------------ epilogue groups
@@ -1117,6 +1159,9 @@ __global__ void __launch_bounds__(kThreads, 1)
     bool stores_pending = false;
     bool ok = true;
     TT_DECL(4);
+#ifdef PLB_TC_TIMING
+    long long tt_fence = 0, tt_issue = 0;
+#endif
     for (int it = my_buf; ok; it += nb) {
       const long tile_l = static_cast<long>(blockIdx.x) + static_cast<long>(it) * gridDim.x;
       if (tile_l >= a.num_tiles) break;
@@ -1124,7 +1169,7 @@ __global__ void __launch_bounds__(kThreads, 1)
       const int m0 = (tile / a.tiles_n) * kTileM;
       const int n0 = (tile % a.tiles_n) * a.bn;
       const long row = static_cast<long>(m0) + quad * 32 + lane;
-      const uint32_t lane_addr = tmem_base + my_buf * acc_cols + (static_cast<uint32_t>(quad * 32) << 16);
+      const uint32_t lane_addr = tmem_base + my_buf * acc_stride + (static_cast<uint32_t>(quad * 32) << 16);
       bool waited = false;
       if (STAGED && MODE == OUT_ADD_RELU && a.res_prefetch) {
         // Residual convolutions are bound by the latency of the residual fetch: each chunk needs
@@ -1231,7 +1276,8 @@ __global__ void __launch_bounds__(kThreads, 1)
         }
         const bool active = a.slab ? s_h < a.ho : row0 < a.m_total;  // warp-uniform: some row of this quadrant exists
         const bool use_w = MODE == OUT_F32 || MODE == OUT_ACC || (MODE == OUT_ADD_RELU && a.y_f32 != nullptr);
-        const bool have_res = MODE == OUT_ADD_RELU && a.residual != nullptr;
+        const bool dual = MODE == OUT_ADD_RELU && a.dual != 0;  // residual = the shortcut GEMM in the next TMEM columns
+        const bool have_res = MODE == OUT_ADD_RELU && (a.residual != nullptr || dual);
         const bool use_b = MODE == OUT_I8 || (MODE == OUT_ADD_RELU && a.y_i8 != nullptr);
         const int cbase = col_par * wq;
         bool wrote_b = false;
@@ -1245,7 +1291,7 @@ __global__ void __launch_bounds__(kThreads, 1)
             TT_STOP(1);
             stores_pending = false;
           }
-          if (active && have_res && lane == 0) {
+          if (active && have_res && !dual && lane == 0) {
             mbar_expect_tx(my_res_bar, 4096);
             if (a.slab) tma_load_4d(st_w, &tmRes, my_res_bar, n0 + c, s_w, s_h, s_img);
             else tma_load_2d(st_w, &tmRes, my_res_bar, n0 + c, row0);
@@ -1265,7 +1311,25 @@ __global__ void __launch_bounds__(kThreads, 1)
           TT_STOP(2);
           TT_START();
           if (active) {
-            if (have_res) {
+            if (dual) {
+              // shortcut value of this chunk: fma(acc2, scale2, bias2) exactly as its own fp32-out
+              // convolution would have stored it, written where a fetched residual tile would be
+              uint32_t r2[32];
+              tc_ld32(lane_addr + acc_cols + static_cast<uint32_t>(c), r2);
+              tc_wait_ld();
+              const float4* sc4 = reinterpret_cast<const float4*>(a.scale2 + n0 + c);
+              const float4* bi4 = reinterpret_cast<const float4*>(a.bias2 + n0 + c);
+              const uint32_t w_row = st_w + lane * 128;
+#pragma unroll
+              for (int j = 0; j < 8; ++j) {
+                const float4 sc = __ldg(sc4 + j), bi = __ldg(bi4 + j);
+                sts128(w_row + ((j ^ (lane & 7)) << 4),
+                       __float_as_uint(fmaf(__int2float_rn((int)r2[4 * j]), sc.x, bi.x)),
+                       __float_as_uint(fmaf(__int2float_rn((int)r2[4 * j + 1]), sc.y, bi.y)),
+                       __float_as_uint(fmaf(__int2float_rn((int)r2[4 * j + 2]), sc.z, bi.z)),
+                       __float_as_uint(fmaf(__int2float_rn((int)r2[4 * j + 3]), sc.w, bi.w)));
+              }
+            } else if (have_res) {
               ok = mbar_wait(my_res_bar, res_phase, abort_flag, a.status, FAULT_WAIT_FULL);
               res_phase ^= 1;
               TT_STOP(1);
@@ -1274,15 +1338,28 @@ __global__ void __launch_bounds__(kThreads, 1)
             }
             epilogue_chunk_staged<MODE, ACT>(a, r, lane, n0 + c, st_w, st_b + lane * wq, (c - cbase) >> 4, b_swz,
                                              have_res);
+#ifdef PLB_TC_TIMING
+            const long long tf0 = clock64();
+#endif
             if (use_w) {  // make this chunk's staging writes visible to the copy engine
               fence_proxy_async_smem();
               __syncwarp();
             }
+#ifdef PLB_TC_TIMING
+            tt_fence += clock64() - tf0;
+#endif
+#ifdef PLB_TC_TIMING
+            const long long ti0 = clock64();
+#endif
             if (use_w && lane == 0) {
               if (a.slab) tma_store_4d(&tmOutW, st_w, n0 + c, s_w, s_h, s_img);
               else tma_store_2d(&tmOutW, st_w, n0 + c, row0);
               bulk_commit();
             }
+#ifdef PLB_TC_TIMING
+            __syncwarp();
+            tt_issue += clock64() - ti0;
+#endif
             if (use_w) stores_pending = true;
             wrote_b = use_b;
           }
@@ -1336,7 +1413,13 @@ __global__ void __launch_bounds__(kThreads, 1)
     if (STAGED && lane == 0) bulk_wait_all();  // staging memory must outlive the stores reading it
     if (warp == 0 && lane == 0) TT_FLUSH(6, 4);
 #ifdef PLB_TC_TIMING
-    if (warp == 0 && lane == 0) a.timing[blockIdx.x * 16 + 14] = clock64() - tt_entry;  // epilogue warp 0 finished
+    if (warp == 0 && lane == 0) {
+      a.timing[blockIdx.x * 24 + 16] = tt_fence;
+      a.timing[blockIdx.x * 24 + 17] = tt_issue;
+    }
+#endif
+#ifdef PLB_TC_TIMING
+    if (warp == 0 && lane == 0) a.timing[blockIdx.x * 24 + 14] = clock64() - tt_entry;  // epilogue warp 0 finished
 #endif
   }
   tc_fence_before();
@@ -1351,7 +1434,7 @@ __global__ void __launch_bounds__(kThreads, 1)
 }
 
 typedef void (*IgemmKernel)(const CUtensorMap, const CUtensorMap, const CUtensorMap, const CUtensorMap,
-                            const CUtensorMap, const IgemmArgs);
+                            const CUtensorMap, const CUtensorMap, const CUtensorMap, const IgemmArgs);
 
 template <int MODE, bool STAGED>
 IgemmKernel pick_act(int act) {
@@ -1453,12 +1536,21 @@ int igemm_tc_launch(plb_ctx* ctx, const IgemmProblem& p) {
   a.m_total = p.m_total;
   a.cout = p.cout;
   a.kc = pick_kc(p.cin_pad);
+  const bool dual = p.a2 != nullptr;
+  if (dual) {
+    if (p.out_mode != OUT_ADD_RELU || p.residual != nullptr || p.im2col || p.b2 == nullptr || p.cin_pad2 % 32 != 0 ||
+        (reinterpret_cast<uintptr_t>(p.a2) & 15) || (reinterpret_cast<uintptr_t>(p.b2) & 15))
+      return fail(PLB_E_UNSUPPORTED, "dual mode needs a flat main GEMM in add+relu mode without a residual tensor");
+    const int kc2 = pick_kc(p.cin_pad2);
+    if (kc2 < a.kc) a.kc = kc2;  // both GEMMs share the stage geometry
+  }
   a.cchunks = p.cin_pad / a.kc;
   a.taps = p.im2col ? p.kh * p.kw : 1;
   a.kw = p.im2col ? p.kw : 1;
   a.ksteps = a.taps * a.cchunks;
   const int cout16 = (p.cout + 15) / 16 * 16;
   int bn = cout16 < 256 ? cout16 : 256;
+  if (dual && bn > 128) bn = 128;  // two accumulators per tile and still two tiles in flight
   // small problems: shrink the channel tile until the grid covers the SMs
   const int tiles_m = (p.m_total + kTileM - 1) / kTileM;
   while (bn > 32 && tiles_m * ((cout16 + bn - 1) / bn) < ctx->sm_count && (bn / 2) % 16 == 0) bn /= 2;
@@ -1469,7 +1561,7 @@ int igemm_tc_launch(plb_ctx* ctx, const IgemmProblem& p) {
   a.tiles_n = (p.cout + bn - 1) / bn;
   // Staged (TMA) epilogue I/O needs power-of-two channel tiles, 16-byte aligned rows and bases.
   const bool want_w = p.out_mode == OUT_F32 || p.out_mode == OUT_ACC ||
-                      (p.out_mode == OUT_ADD_RELU && (p.y_f32 != nullptr || p.residual != nullptr));
+                      (p.out_mode == OUT_ADD_RELU && (p.y_f32 != nullptr || p.residual != nullptr || dual));
   const bool want_b = p.out_mode == OUT_I8 || (p.out_mode == OUT_ADD_RELU && p.y_i8 != nullptr);
   auto aligned16 = [](const void* q) { return (reinterpret_cast<uintptr_t>(q) & 15) == 0; };
   bool staged = env_int("PLB_TC_STAGED", 1) != 0 && (bn == 32 || bn == 64 || bn == 128 || bn == 256);
@@ -1494,6 +1586,7 @@ int igemm_tc_launch(plb_ctx* ctx, const IgemmProblem& p) {
     const bool few = tiles_total <= 2L * ctx->sm_count;
     a.acc_bufs = bn > 128 ? 2 : (few && bn >= 64 ? 2 : 4);
     a.acc_bufs = env_int("PLB_TC_ACC_BUFS", a.acc_bufs);
+    if (dual) a.acc_bufs = 2;
     if (a.acc_bufs != 2 && a.acc_bufs != 4) return fail(PLB_E_INVALID, "accumulator buffers must be 2 or 4");
     if (a.acc_bufs == 4 && bn > 128) a.acc_bufs = 2;
     if (a.acc_bufs == 2 && bn < 64) a.acc_bufs = 4;
@@ -1515,7 +1608,7 @@ int igemm_tc_launch(plb_ctx* ctx, const IgemmProblem& p) {
   }
   const int tiles_n_h = (p.cout + bn - 1) / bn;
   const int resident_bytes = (a.ksteps * bn * a.kc + 1023) / 1024 * 1024;
-  const bool can_resident = env_int("PLB_TC_RESIDENT", 1) != 0 && tiles_n_h == 1 && resident_bytes <= kMaxResidentB;
+  const bool can_resident = env_int("PLB_TC_RESIDENT", 1) != 0 && tiles_n_h == 1 && resident_bytes <= kMaxResidentB && !dual;
   a.resident_b = can_resident && tiles_m > ctx->sm_count;  // worth it only when a CTA walks several tiles
   // Slab mode: stride-1 filters with several taps read each input pixel once per tile instead of
   // once per tap.  Output tiles are 16 x 8 pixels, so images much smaller than that waste too
@@ -1595,6 +1688,18 @@ int igemm_tc_launch(plb_ctx* ctx, const IgemmProblem& p) {
   a.residual = p.residual; a.y_f32 = p.y_f32; a.y_i8 = p.y_i8;
   a.inv_next_scale = p.inv_next_scale;
   a.status = ctx->d_status;
+  if (dual) {
+    if (!staged) return fail(PLB_E_UNSUPPORTED, "dual mode needs the staged epilogue (16-byte aligned rows, power-of-two tile)");
+    a.dual = 1;
+    a.cchunks2 = p.cin_pad2 / a.kc;
+    a.ksteps2 = a.cchunks2;
+    a.im2col2 = p.im2col2;
+    a.stride2_h = p.stride2_h;
+    a.stride2_w = p.stride2_w;
+    a.scale2 = p.scale2;
+    a.bias2 = p.bias2;
+    a.ho = p.ho; a.wo = p.wo;
+  }
 
   alignas(64) CUtensorMap tmA;
   alignas(64) CUtensorMap tmB;
@@ -1661,6 +1766,40 @@ int igemm_tc_launch(plb_ctx* ctx, const IgemmProblem& p) {
     if (r != CUDA_SUCCESS) return fail(PLB_E_CUDA, "cuTensorMapEncodeIm2col failed: %d", (int)r);
   }
 
+  alignas(64) CUtensorMap tmA2 = tmB, tmB2 = tmB;
+  if (dual) {
+    cuuint64_t dims[2] = {static_cast<cuuint64_t>(p.cin_pad2), static_cast<cuuint64_t>(p.cout)};
+    cuuint64_t strides[1] = {static_cast<cuuint64_t>(p.cin_pad2)};
+    cuuint32_t box[2] = {static_cast<cuuint32_t>(a.kc), static_cast<cuuint32_t>(bn)};
+    cuuint32_t estr[2] = {1, 1};
+    CUresult r = g_encode_tiled(&tmB2, CU_TENSOR_MAP_DATA_TYPE_UINT8, 2, const_cast<int8_t*>(p.b2), dims, strides, box,
+                                estr, CU_TENSOR_MAP_INTERLEAVE_NONE, sw, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                                CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    if (r != CUDA_SUCCESS) return fail(PLB_E_CUDA, "cuTensorMapEncodeTiled(shortcut filter) failed: %d", (int)r);
+    if (!p.im2col2) {
+      cuuint64_t adims[2] = {static_cast<cuuint64_t>(p.cin_pad2), static_cast<cuuint64_t>(p.m_total)};
+      cuuint32_t abox[2] = {static_cast<cuuint32_t>(a.kc), static_cast<cuuint32_t>(kTileM)};
+      r = g_encode_tiled(&tmA2, CU_TENSOR_MAP_DATA_TYPE_UINT8, 2, const_cast<int8_t*>(p.a2), adims, strides, abox, estr,
+                         CU_TENSOR_MAP_INTERLEAVE_NONE, sw, CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
+                         CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+      if (r != CUDA_SUCCESS) return fail(PLB_E_CUDA, "cuTensorMapEncodeTiled(shortcut input) failed: %d", (int)r);
+    } else {
+      // 1x1 filter read with a stride: the im2col traversal with no halo
+      cuuint64_t adims[4] = {static_cast<cuuint64_t>(p.cin_pad2), static_cast<cuuint64_t>(p.w2),
+                             static_cast<cuuint64_t>(p.h2), static_cast<cuuint64_t>(p.batch)};
+      cuuint64_t astr[3] = {static_cast<cuuint64_t>(p.cin_pad2), static_cast<cuuint64_t>(p.cin_pad2) * p.w2,
+                            static_cast<cuuint64_t>(p.cin_pad2) * p.w2 * p.h2};
+      // no halo: the bounding box is the whole image, base pixels advance by the stride
+      int lower[2] = {0, 0};
+      int upper[2] = {0, 0};
+      cuuint32_t aestr[4] = {1, static_cast<cuuint32_t>(p.stride2_w), static_cast<cuuint32_t>(p.stride2_h), 1};
+      r = g_encode_im2col(&tmA2, CU_TENSOR_MAP_DATA_TYPE_UINT8, 4, const_cast<int8_t*>(p.a2), adims, astr, lower, upper,
+                          static_cast<cuuint32_t>(a.kc), static_cast<cuuint32_t>(kTileM), aestr,
+                          CU_TENSOR_MAP_INTERLEAVE_NONE, sw, CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
+                          CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+      if (r != CUDA_SUCCESS) return fail(PLB_E_CUDA, "cuTensorMapEncodeIm2col(shortcut input) failed: %d", (int)r);
+    }
+  }
   // output-side tensor maps: [m_total, ldy] matrices, 32-row boxes
   alignas(64) CUtensorMap tmRes = tmB, tmOutW = tmB, tmOutB = tmB;  // unused ones stay valid copies
   if (staged) {
@@ -1723,27 +1862,27 @@ int igemm_tc_launch(plb_ctx* ctx, const IgemmProblem& p) {
   const unsigned grid = static_cast<unsigned>(tiles < ctx->sm_count ? tiles : ctx->sm_count);
 #ifdef PLB_TC_TIMING
   static long long* d_timing = nullptr;
-  if (!d_timing) PLB_CUDA(cudaMalloc(&d_timing, 256 * 16 * sizeof(long long)));
-  PLB_CUDA(cudaMemsetAsync(d_timing, 0, 256 * 16 * sizeof(long long), ctx->stream));
+  if (!d_timing) PLB_CUDA(cudaMalloc(&d_timing, 256 * 24 * sizeof(long long)));
+  PLB_CUDA(cudaMemsetAsync(d_timing, 0, 256 * 24 * sizeof(long long), ctx->stream));
   a.timing = d_timing;
 #endif
   PLB_CUDA(launch_kernel(kernel, dim3(grid), dim3(kThreads), smem, ctx->stream, tmA, tmB, tmRes, tmOutW,
-                         tmOutB, a));
+                         tmOutB, tmA2, tmB2, a));
 #ifdef PLB_TC_TIMING
   if (env_int("PLB_TC_TIMING_PRINT", 0)) {
-    std::vector<long long> h(256 * 16);
+    std::vector<long long> h(256 * 24);
     PLB_CUDA(cudaStreamSynchronize(ctx->stream));
     PLB_CUDA(cudaMemcpy(h.data(), d_timing, h.size() * sizeof(long long), cudaMemcpyDeviceToHost));
-    double avg[16] = {};
+    double avg[24] = {};
     for (unsigned b = 0; b < grid; ++b)
-      for (int i = 0; i < 16; ++i) avg[i] += static_cast<double>(h[b * 16 + i]) / grid;
+      for (int i = 0; i < 24; ++i) avg[i] += static_cast<double>(h[b * 24 + i]) / grid;
     fprintf(stderr,
             "[tc timing] tiles %ld grid %u slab %d bn %d kc %d ksteps %d stages %d | producer: wait_empty %.0f total %.0f | "
             "mma: wait_acc_empty %.0f wait_full %.0f issue %.0f wait_filter %.0f (producer wait_filter_slot %.0f) | epilogue warp0: wait_acc_full %.0f wait_stores+residual %.0f "
-            "tmem_ld %.0f math+store %.0f | since entry: roles start %.0f, filter resident %.0f, first operands %.0f, "
+            "tmem_ld %.0f math+store %.0f (of which fence %.0f, store issue %.0f) | since entry: roles start %.0f, filter resident %.0f, first operands %.0f, "
             "MMAs issued %.0f, epilogue warp0 done %.0f (cycles per CTA)\n",
             tiles, grid, a.slab, a.bn, a.kc, a.ksteps, a.stages, avg[0], avg[1], avg[2], avg[3], avg[4], avg[5], avg[15], avg[6], avg[7],
-            avg[8], avg[9], avg[10], avg[11], avg[12], avg[13], avg[14]);
+            avg[8], avg[9], avg[16], avg[17], avg[10], avg[11], avg[12], avg[13], avg[14]);
   }
 #endif
   ctx->launches++;

@@ -36,6 +36,15 @@ struct IgemmProblem {
   float* y_f32;           // OUT_ADD_RELU, nullable
   int8_t* y_i8;           // OUT_ADD_RELU, nullable
   float inv_next_scale;   // OUT_ADD_RELU: 1 / scale of the next layer's input
+  // Dual mode (OUT_ADD_RELU with a flat main GEMM and no residual tensor): the residual value is a
+  // second 1x1 GEMM, D2[m, n] = sum_k A2[m, k] * B2[n, k], turned into fma(D2, scale2, bias2) --
+  // the shortcut convolution of a residual block, computed in the same launch.
+  const int8_t* a2;       // nullptr: no second GEMM.  Flat [m_total, cin_pad2], or (im2col2) NHWC [batch, h2, w2, cin_pad2]
+  int im2col2;            // 1: A2 is read at pixel (oh * stride2_h, ow * stride2_w) of an h2 x w2 image
+  int h2, w2, cin_pad2, stride2_h, stride2_w;
+  const int8_t* b2;       // [cout, cin_pad2]
+  const float* scale2;    // [cout] folded ws * in_s of the shortcut
+  const float* bias2;     // [cout]
 };
 
 // Whether the tensor-core kernel can take this problem (shape and alignment rules).

@@ -26,6 +26,12 @@ struct OutSpec {
   float* y_f32;
   int8_t* y_i8;
   float inv_next_scale;
+  // tensor-core path only: shortcut GEMM of a residual block computed in the same launch (see IgemmProblem)
+  const int8_t* a2;
+  const int8_t* b2;
+  int im2col2, h2, w2, cin_pad2, stride2_h, stride2_w;
+  const float* scale2;
+  const float* bias2;
 };
 
 // Generic grouped convolution, NHWC in / NHWC out, one thread per output value.

@@ -394,6 +394,8 @@ int conv_core(plb_conv* c, const int8_t* x, int batch, const OutSpec& out) {
     p.out_mode = out.mode; p.y = out.y; p.ldy = out.ldy; p.epi = out.epi;
     p.residual = out.residual; p.y_f32 = out.y_f32; p.y_i8 = out.y_i8;
     p.inv_next_scale = out.inv_next_scale;
+    p.a2 = out.a2; p.b2 = out.b2; p.im2col2 = out.im2col2; p.h2 = out.h2; p.w2 = out.w2; p.cin_pad2 = out.cin_pad2;
+    p.stride2_h = out.stride2_h; p.stride2_w = out.stride2_w; p.scale2 = out.scale2; p.bias2 = out.bias2;
     return igemm_tc_launch(ctx, p);
   }
   ConvGeom g;
@@ -554,6 +556,40 @@ int plb_conv_run_nhwc_add_relu(plb_conv* conv, const int8_t* x, const float* res
   o.y_f32 = y_f32;
   o.y_i8 = y_i8;
   o.inv_next_scale = y_i8 ? 1.f / next_scale : 0.f;
+  return conv_core(conv, x, batch, o);
+}
+
+int plb_conv_run_nhwc_block_add_relu(plb_conv* conv, const int8_t* x, plb_conv* shortcut, const int8_t* x_shortcut,
+                                     float* y_f32, int8_t* y_i8, float next_scale, int batch) {
+  PLB_REQUIRE(conv && x && shortcut && x_shortcut, "null argument");
+  PLB_REQUIRE(y_f32 || y_i8, "at least one output is required");
+  PLB_REQUIRE(!y_i8 || next_scale > 0.f, "next_scale must be positive");
+  PLB_REQUIRE(batch >= 0, "negative batch");
+  PLB_REQUIRE(conv->ctx == shortcut->ctx, "both layers must belong to the same ctx");
+  const plb_conv_desc& m = conv->d;
+  const plb_conv_desc& s = shortcut->d;
+  PLB_REQUIRE(conv->kind == 0 && shortcut->kind == 0 && !conv->fold && !shortcut->fold, "both layers must be dense tensor-core layers");
+  PLB_REQUIRE(m.kh == 1 && m.kw == 1 && m.stride_h == 1 && m.stride_w == 1 && m.pad_top == 0 && m.pad_bottom == 0 &&
+                  m.pad_left == 0 && m.pad_right == 0,
+              "the main layer must be a 1x1, stride-1, unpadded convolution");
+  PLB_REQUIRE(s.kh == 1 && s.kw == 1 && s.pad_top == 0 && s.pad_bottom == 0 && s.pad_left == 0 && s.pad_right == 0,
+              "the shortcut layer must be an unpadded 1x1 convolution");
+  PLB_REQUIRE(m.cout == s.cout && conv->ho == shortcut->ho && conv->wo == shortcut->wo, "the two layers must produce the same shape");
+  PLB_REQUIRE(m.act == PLB_ACT_NONE && s.act == PLB_ACT_NONE, "neither layer may have an activation of its own");
+  PLB_REQUIRE(conv->cin_pad == m.cin && shortcut->cin_pad == s.cin, "channels-last entry needs cin to be a multiple of 32");
+  if (batch == 0) return PLB_OK;
+  PLB_CUDA(cudaSetDevice(conv->ctx->device));
+  OutSpec o = out_spec(conv, OUT_ADD_RELU, nullptr);
+  o.y_f32 = y_f32;
+  o.y_i8 = y_i8;
+  o.inv_next_scale = y_i8 ? 1.f / next_scale : 0.f;
+  o.a2 = x_shortcut;
+  o.b2 = shortcut->w.as<int8_t>();
+  o.im2col2 = (s.stride_h != 1 || s.stride_w != 1) ? 1 : 0;
+  o.h2 = s.h; o.w2 = s.w; o.cin_pad2 = shortcut->cin_pad;
+  o.stride2_h = s.stride_h; o.stride2_w = s.stride_w;
+  o.scale2 = shortcut->scale_f32.as<float>();
+  o.bias2 = shortcut->bias_f32.as<float>();
   return conv_core(conv, x, batch, o);
 }
 

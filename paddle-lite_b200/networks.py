@@ -166,6 +166,30 @@ def build_quantized(spec, seed=1234, calib_images=16, device="cpu"):
 
 
 # ----------------------------------------------------------------------------- GPU runner
+def fusable_shortcuts(spec):
+    """Projection shortcuts that can run inside the launch of the block's last convolution
+    (plb_conv_run_nhwc_block_add_relu): an unpadded 1x1 conv with fp32 output and no activation
+    whose only reader is the residual input of a conv_add_relu whose own conv is 1x1, stride 1.
+    Returns {tensor name: shortcut op}."""
+    readers = {}
+    for op in spec["ops"]:
+        for key in ("src", "residual"):
+            if key in op:
+                readers.setdefault(op[key], []).append((op, key))
+    out = {}
+    for op in spec["ops"]:
+        if op["op"] != "conv" or op.get("out") != "f32" or op["k"] != 1 or op["p"] != 0 or op["act"] != ACT_NONE:
+            continue
+        if op.get("groups", 1) != 1 or op["cin"] % 32:
+            continue
+        r = readers.get(op["dst"], [])
+        if len(r) == 1 and r[0][1] == "residual" and r[0][0]["op"] == "conv_add_relu":
+            main = r[0][0]
+            if main["k"] == 1 and main["s"] == 1 and main["p"] == 0 and main["cin"] % 32 == 0:
+                out[op["dst"]] = op
+    return out
+
+
 class Runner:
     """Holds the prepared layers and all activation buffers for one batch size on one GPU and
     enqueues a whole forward pass on the context's stream (no allocation, no host sync).
@@ -175,7 +199,7 @@ class Runner:
     slice is then small enough to stay in the 126 MB L2 between the layer that writes it and
     the layer that reads it, instead of making a round trip through HBM."""
 
-    def __init__(self, plb, ctx, qnet, batch, micro_batch=None):
+    def __init__(self, plb, ctx, qnet, batch, micro_batch=None, fuse_blocks=True):
         import torch
         self.plb, self.ctx, self.q = plb, ctx, qnet
         self.full_batch = batch
@@ -191,6 +215,8 @@ class Runner:
         self.buf = {}
         self.steps = []
         self.image_shape = (full_batch, c, h, w)
+        shortcuts = fusable_shortcuts(spec) if fuse_blocks else {}
+        shortcut_convs = {}
         for op in spec["ops"]:
             kind = op["op"]
             if kind in ("conv", "conv_add_relu"):
@@ -206,6 +232,11 @@ class Runner:
                     dt = torch.int8 if out_s is not None else torch.float32
                     self.buf[op["dst"]] = torch.empty((batch, conv.ho, conv.wo, op["cout"]), dtype=dt, device=dev)
                     self.hw[op["dst"]] = (conv.ho, conv.wo)
+                    if op["dst"] in shortcuts:
+                        # runs inside the launch of the block's last conv; its fp32 tensor is never written
+                        shortcut_convs[op["dst"]] = (conv, op["src"])
+                        del self.buf[op["dst"]]
+                        continue
                     self.steps.append(("conv_image" if op["src"] == "x" else "conv", conv, op["src"], op["dst"]))
                 else:
                     conv = plb.Conv(ctx, wq, L["ws"], in_s, L["bias"], in_hw=(ih, iw))
@@ -217,8 +248,13 @@ class Runner:
                         self.buf[op["dst_i8"]] = torch.empty(shape, dtype=torch.int8, device=dev)
                         self.hw[op["dst_i8"]] = (conv.ho, conv.wo)
                     next_s = float(scales[op["dst_i8"]]) if op["dst_i8"] else None
-                    self.steps.append(("conv_add_relu", conv, op["src"], op["residual"], op["dst_f32"],
-                                       op["dst_i8"], next_s))
+                    if op["residual"] in shortcut_convs:
+                        sc_conv, sc_src = shortcut_convs[op["residual"]]
+                        self.steps.append(("block_add_relu", conv, op["src"], sc_conv, sc_src, op["dst_f32"],
+                                           op["dst_i8"], next_s))
+                    else:
+                        self.steps.append(("conv_add_relu", conv, op["src"], op["residual"], op["dst_f32"],
+                                           op["dst_i8"], next_s))
             elif kind == "maxpool":
                 ih, iw = self.hw[op["src"]]
                 oh, ow = (ih + 2 * op["p"] - op["k"]) // op["s"] + 1, (iw + 2 * op["p"] - op["k"]) // op["s"] + 1
@@ -266,6 +302,10 @@ class Runner:
                 _, conv, src, res, df, dq, next_s = st
                 conv.run_nhwc_add_relu(b[src], b[res], next_s, want_f32=df is not None,
                                        out_f32=b[df] if df else None, out_i8=b[dq] if dq else None)
+            elif st[0] == "block_add_relu":
+                _, conv, src, sc_conv, sc_src, df, dq, next_s = st
+                conv.run_nhwc_block_add_relu(b[src], sc_conv, b[sc_src], next_s, want_f32=df is not None,
+                                             out_f32=b[df] if df else None, out_i8=b[dq] if dq else None)
             elif st[0] == "maxpool":
                 ctx.maxpool_nhwc_i8(b[st[1]], st[3], st[4], st[5], out=b[st[2]])
             elif st[0] == "avgpool_calib":

@@ -203,6 +203,32 @@ def test_nhwc_entry_and_fused_add_relu(plb, ctx, prefetch, monkeypatch):
     assert np.array_equal(yq.cpu().numpy().transpose(0, 3, 1, 2), q_ref)
 
 
+@pytest.mark.parametrize("n,cin_m,cin_s,hw,cout,stride", [(3, 64, 64, 14, 256, 1), (2, 128, 256, 28, 512, 2),
+                                                         (5, 32, 96, 9, 64, 2), (1, 256, 512, 7, 320, 1)])
+def test_block_add_relu_equals_the_unfused_sequence(plb, ctx, n, cin_m, cin_s, hw, cout, stride):
+    """Projection-block tail in one launch: relu(main 1x1 conv + strided 1x1 shortcut conv) and its
+    calib, bit-identical to conv(fp32_out), conv(fp32_out), add, relu, calib through the oracle."""
+    hs = hw * stride - (stride - 1) * (n % 2)  # shortcut input: even and odd sizes
+    xm, in_m, wm, wsm, bm = conv_case(31 + cout, n, cin_m, hw, hw, cout, 1)
+    xs, in_s, wsh, wss, bs = conv_case(32 + cout, n, cin_s, hs, hs, cout, 1)
+    y_main = O.epilogue(O.conv_acc_i32(xm, wm), wsm, in_m, bm, O.ACT_NONE, 0.0)
+    y_short = O.epilogue(O.conv_acc_i32(xs, wsh, stride=(stride, stride)), wss, in_s, bs, O.ACT_NONE, 0.0)
+    assert y_short.shape == y_main.shape
+    s_ref = np.maximum(y_main + y_short, np.float32(0))
+    next_s = float(np.abs(s_ref).max() / 127)
+    q_ref = O.calib_f32_to_i8(s_ref, next_s)
+    main = plb.Conv(ctx, wm, wsm, in_m, bm, in_hw=(hw, hw))
+    short = plb.Conv(ctx, wsh, wss, in_s, bs, in_hw=(hs, hs), stride=(stride, stride))
+    nhwc = lambda a: dev(np.ascontiguousarray(a.transpose(0, 2, 3, 1)))  # noqa: E731
+    yf, yq = main.run_nhwc_block_add_relu(nhwc(xm), short, nhwc(xs), next_s)
+    ctx.sync()
+    assert np.array_equal(yf.cpu().numpy().transpose(0, 3, 1, 2), s_ref)
+    assert np.array_equal(yq.cpu().numpy().transpose(0, 3, 1, 2), q_ref)
+    _, yq2 = main.run_nhwc_block_add_relu(nhwc(xm), short, nhwc(xs), next_s, want_f32=False)
+    ctx.sync()
+    assert np.array_equal(yq2.cpu().numpy().transpose(0, 3, 1, 2), q_ref)
+
+
 def test_window_mode_fused_add_relu(plb, ctx, monkeypatch):
     """conv3x3 + residual add + relu + calib in window mode: residual tiles and both outputs move
     through the four-dimensional tensor maps."""
