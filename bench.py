@@ -124,6 +124,8 @@ def layer_bytes(spec, batch):
     per_layer = []
     # projection shortcuts that run inside the block's last launch
     shortcuts = importlib.import_module("paddle-lite_b200.networks").fusable_shortcuts(spec)
+    if os.environ.get("PLB_FUSE_BLOCKS", "1") == "0":
+        shortcuts = {}
     for op in spec["ops"]:
         if op["op"] == "conv" and op["dst"] in shortcuts:
             ih, iw = hw[op["src"]]

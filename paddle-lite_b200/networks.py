@@ -14,6 +14,8 @@ There are no model files: weights are seeded He-init, activation scales come fro
 calibration pass over seeded N(0,1) images (set-up work, done with torch ops; the timed path
 is only the C-ABI library).
 """
+import os
+
 import numpy as np
 
 ACT_NONE, ACT_RELU = 0, 1
@@ -215,6 +217,8 @@ class Runner:
         self.buf = {}
         self.steps = []
         self.image_shape = (full_batch, c, h, w)
+        if os.environ.get("PLB_FUSE_BLOCKS", "1") == "0":  # A/B switch for measurements
+            fuse_blocks = False
         shortcuts = fusable_shortcuts(spec) if fuse_blocks else {}
         shortcut_convs = {}
         for op in spec["ops"]:
