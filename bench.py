@@ -234,7 +234,7 @@ def cpu_baseline(qnet, spec, sample_images, repeats=1):
 # DRAM read + write bytes per tcgen05 launch, from the ncu capture summarised in
 # profiles/bench_resnet50_b128_dram_traffic.md.  Traffic does not scale with the batch (small batches
 # stay in L2), so only the captured workload has a number.
-CAPTURED_TRAFFIC = {("resnet50", 128): 126.9e6}
+CAPTURED_TRAFFIC = {("resnet50", 128): 111.6e6}
 
 
 def captured_traffic(net, batch):
