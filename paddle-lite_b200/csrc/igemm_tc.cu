@@ -1304,6 +1304,26 @@ __global__ void __launch_bounds__(kThreads, 1)
             waited = true;
             if (!ok) break;
           }
+          if (active && dual) {
+            // shortcut value of this chunk: fma(acc2, scale2, bias2) exactly as its own fp32-out
+            // convolution would have stored it, written where a fetched residual tile would be
+            // (done before the main accumulator is read, to keep both out of the registers at once)
+            uint32_t r2[32];
+            tc_ld32(lane_addr + acc_cols + static_cast<uint32_t>(c), r2);
+            tc_wait_ld();
+            const float4* sc4 = reinterpret_cast<const float4*>(a.scale2 + n0 + c);
+            const float4* bi4 = reinterpret_cast<const float4*>(a.bias2 + n0 + c);
+            const uint32_t w_row = st_w + lane * 128;
+#pragma unroll
+            for (int j = 0; j < 8; ++j) {
+              const float4 sc = __ldg(sc4 + j), bi = __ldg(bi4 + j);
+              sts128(w_row + ((j ^ (lane & 7)) << 4),
+                     __float_as_uint(fmaf(__int2float_rn((int)r2[4 * j]), sc.x, bi.x)),
+                     __float_as_uint(fmaf(__int2float_rn((int)r2[4 * j + 1]), sc.y, bi.y)),
+                     __float_as_uint(fmaf(__int2float_rn((int)r2[4 * j + 2]), sc.z, bi.z)),
+                     __float_as_uint(fmaf(__int2float_rn((int)r2[4 * j + 3]), sc.w, bi.w)));
+            }
+          }
           TT_START();
           uint32_t r[32];
           tc_ld32(lane_addr + static_cast<uint32_t>(c), r);
@@ -1312,23 +1332,6 @@ __global__ void __launch_bounds__(kThreads, 1)
           TT_START();
           if (active) {
             if (dual) {
-              // shortcut value of this chunk: fma(acc2, scale2, bias2) exactly as its own fp32-out
-              // convolution would have stored it, written where a fetched residual tile would be
-              uint32_t r2[32];
-              tc_ld32(lane_addr + acc_cols + static_cast<uint32_t>(c), r2);
-              tc_wait_ld();
-              const float4* sc4 = reinterpret_cast<const float4*>(a.scale2 + n0 + c);
-              const float4* bi4 = reinterpret_cast<const float4*>(a.bias2 + n0 + c);
-              const uint32_t w_row = st_w + lane * 128;
-#pragma unroll
-              for (int j = 0; j < 8; ++j) {
-                const float4 sc = __ldg(sc4 + j), bi = __ldg(bi4 + j);
-                sts128(w_row + ((j ^ (lane & 7)) << 4),
-                       __float_as_uint(fmaf(__int2float_rn((int)r2[4 * j]), sc.x, bi.x)),
-                       __float_as_uint(fmaf(__int2float_rn((int)r2[4 * j + 1]), sc.y, bi.y)),
-                       __float_as_uint(fmaf(__int2float_rn((int)r2[4 * j + 2]), sc.z, bi.z)),
-                       __float_as_uint(fmaf(__int2float_rn((int)r2[4 * j + 3]), sc.w, bi.w)));
-              }
             } else if (have_res) {
               ok = mbar_wait(my_res_bar, res_phase, abort_flag, a.status, FAULT_WAIT_FULL);
               res_phase ^= 1;
