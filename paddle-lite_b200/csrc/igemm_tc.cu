@@ -537,7 +537,7 @@ __device__ __forceinline__ void sts128(uint32_t addr, uint32_t a, uint32_t b, ui
 // swizzle: 16-byte chunk j of row r lives at chunk j ^ (r & 7)), holding the residual on entry
 // for OUT_ADD_RELU and the fp32 / int32 result on exit.  st_b_row: address of this lane's row in
 // the int8 staging tile, byte_chunk0 the index of the first 16-byte chunk to write and
-// b_swz_mask the xor mask of that tile's swizzle (7 for 128-byte rows, 0 otherwise).
+// b_swz_mask the xor mask of that row in the tile's swizzle (see b_swz at the call site).
 template <int MODE, int ACT>
 __device__ __forceinline__ void epilogue_chunk_staged(const IgemmArgs& a, const uint32_t (&r)[32], int lane,
                                                       int col, uint32_t st_w, uint32_t st_b_row,
@@ -1147,7 +1147,9 @@ __global__ void __launch_bounds__(kThreads, 1)
     const uint32_t st_w = smem_u32(smem_al) + warp * 4096;
     const int wq = a.bn / gpb;       // columns (= int8 bytes per row) this group owns in a tile
     const uint32_t st_b = smem_u32(smem_al) + a.staging_w_bytes + warp * a.stage_b_warp;
-    const int b_swz = wq == 128 ? (lane & 7) : 0;
+    // int8 staging rows are wq bytes long and swizzled with span wq (as the store's tensor map is):
+    // 16-byte chunk j of row r lives at j ^ (r & 7), j ^ ((r >> 1) & 3) or j ^ ((r >> 2) & 1)
+    const int b_swz = wq == 128 ? (lane & 7) : (wq == 64 ? ((lane >> 1) & 3) : (wq == 32 ? ((lane >> 2) & 1) : 0));
     const uint32_t my_res_bar = smem_u32(&res_bar[warp]);
     uint32_t res_phase = 0;
     // residual prefetch: two staging tiles per warp (8 KiB apart per warp), one barrier each
@@ -1498,6 +1500,13 @@ CUtensorMapSwizzle swizzle_for(int kc) {
                    : (kc == 64 ? CU_TENSOR_MAP_SWIZZLE_64B : CU_TENSOR_MAP_SWIZZLE_32B);
 }
 
+// swizzle of a staging tile whose rows are `bytes` long (no swizzle for other lengths)
+CUtensorMapSwizzle swizzle_for_bytes(int bytes) {
+  return bytes == 128 ? CU_TENSOR_MAP_SWIZZLE_128B
+                      : (bytes == 64 ? CU_TENSOR_MAP_SWIZZLE_64B
+                                     : (bytes == 32 ? CU_TENSOR_MAP_SWIZZLE_32B : CU_TENSOR_MAP_SWIZZLE_NONE));
+}
+
 int env_int(const char* name, int dflt) {
   const char* v = std::getenv(name);
   return v && *v ? std::atoi(v) : dflt;
@@ -1837,10 +1846,10 @@ int igemm_tc_launch(plb_ctx* ctx, const IgemmProblem& p) {
       if (r == CUDA_SUCCESS && p.y_f32) r = encode_out(&tmOutW, p.y_f32, 4, 32, CU_TENSOR_MAP_SWIZZLE_128B);
       if (r == CUDA_SUCCESS && p.y_i8) {
         if (a.res_prefetch) r = encode_out(&tmOutB, p.y_i8, 1, 32, CU_TENSOR_MAP_SWIZZLE_NONE);
-        else r = encode_out(&tmOutB, p.y_i8, 1, wq, wq == 128 ? CU_TENSOR_MAP_SWIZZLE_128B : CU_TENSOR_MAP_SWIZZLE_NONE);
+        else r = encode_out(&tmOutB, p.y_i8, 1, wq, swizzle_for_bytes(wq));
       }
     } else if (p.out_mode == OUT_I8) {
-      r = encode_out(&tmOutB, p.y, 1, wq, wq == 128 ? CU_TENSOR_MAP_SWIZZLE_128B : CU_TENSOR_MAP_SWIZZLE_NONE);
+      r = encode_out(&tmOutB, p.y, 1, wq, swizzle_for_bytes(wq));
     } else {
       r = encode_out(&tmOutW, p.y, 4, 32, CU_TENSOR_MAP_SWIZZLE_128B);
     }

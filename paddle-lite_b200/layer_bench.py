@@ -3,6 +3,7 @@
 
     python paddle-lite_b200/layer_bench.py conv   --cin 64 --hw 56 --cout 64 --k 3 --pad 1 --batch 128 [--out i8|f32|addrelu]
     python paddle-lite_b200/layer_bench.py dw     --cin 32 --hw 112 --stride 1 --batch 128
+    python paddle-lite_b200/layer_bench.py block  --cin 64 --cin2 64 --hw 56 --cout 256 --stride 1 --batch 128   # projection-block tail
     python paddle-lite_b200/layer_bench.py fc     --m 4096 --kdim 4096 --n 4096 [--out i8|f32]
     python paddle-lite_b200/layer_bench.py sparse --cin 128 --cout 128 --hw 56 --batch 256 [--fp32] [--semi] [--impl walk|dense]
     python paddle-lite_b200/layer_bench.py fc-sweep | sparse-sweep      # the shapes of the benchmark configs
@@ -70,7 +71,8 @@ def report(name, us, nbytes, ops, extra=None):
 
 def main():
     ap = argparse.ArgumentParser()
-    ap.add_argument("kind", choices=["conv", "dw", "fc", "sparse", "fc-sweep", "sparse-sweep", "int8-peak"])
+    ap.add_argument("kind", choices=["conv", "dw", "block", "fc", "sparse", "fc-sweep", "sparse-sweep", "int8-peak"])
+    ap.add_argument("--cin2", type=int, default=64, help="block: input channels of the shortcut conv")
     ap.add_argument("--cin", type=int, default=64)
     ap.add_argument("--cout", type=int, default=64)
     ap.add_argument("--hw", type=int, default=56)
@@ -171,6 +173,25 @@ def main():
             b = torch.randint(-127, 128, (n, n), dtype=torch.int8, device="cuda").t().contiguous().t()
             us = time_launches(lambda: torch._int_mm(a, b), args.iters, args.warm)
             report("cublaslt int8 gemm %d^3 (int32 out)" % n, us, 2 * n * n + 4 * n * n, 2.0 * n ** 3)
+        return
+    if args.kind == "block":
+        # relu(1x1 conv(x) + strided 1x1 shortcut(x2)) + calib in one launch, fp32 and int8 outputs
+        hw, s2 = args.hw, args.stride
+        wm = rng.integers(-127, 128, (args.cout, args.cin, 1, 1), dtype=np.int8)
+        wsh = rng.integers(-127, 128, (args.cout, args.cin2, 1, 1), dtype=np.int8)
+        main = plb.Conv(ctx, wm, [0.001], 0.02, None, in_hw=(hw, hw))
+        short = plb.Conv(ctx, wsh, [0.001], 0.02, None, in_hw=(hw * s2, hw * s2), stride=(s2, s2))
+        xm = torch.randint(-127, 128, (args.batch, hw, hw, args.cin), dtype=torch.int8, device="cuda")
+        xs = torch.randint(-127, 128, (args.batch, hw * s2, hw * s2, args.cin2), dtype=torch.int8, device="cuda")
+        yf = torch.empty((args.batch, hw, hw, args.cout), device="cuda")
+        yq = torch.empty((args.batch, hw, hw, args.cout), dtype=torch.int8, device="cuda")
+        us = time_launches(lambda: main.run_nhwc_block_add_relu(xm, short, xs, 0.05, out_f32=yf, out_i8=yq),
+                           args.iters, args.warm)
+        pix = args.batch * hw * hw
+        report("block %d->%d + %d->%d(s%d) %dx%d b%d" % (args.cin, args.cout, args.cin2, args.cout, s2, hw, hw, args.batch),
+               us, pix * (args.cin + args.cin2 + 5 * args.cout) + args.cout * (args.cin + args.cin2),
+               2.0 * pix * args.cout * (args.cin + args.cin2))
+        ctx.sync()
         return
     if args.kind == "conv":
         conv_layer(args.cin, args.hw, args.cout, args.k, args.stride, args.pad, args.batch, args.out)
