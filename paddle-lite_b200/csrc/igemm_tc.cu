@@ -1565,9 +1565,12 @@ int igemm_tc_launch(plb_ctx* ctx, const IgemmProblem& p) {
   if (dual && bn > 128) bn = 128;  // two accumulators per tile and still two tiles in flight
   // small problems: shrink the channel tile until the grid covers the SMs
   const int tiles_m = (p.m_total + kTileM - 1) / kTileM;
-  while (bn > 32 && tiles_m * ((cout16 + bn - 1) / bn) < ctx->sm_count && (bn / 2) % 16 == 0) bn /= 2;
+  // (the epilogue works in chunks of 32 columns, so a tile that is not the last one of its row of
+  // tiles must be a multiple of 32 wide: halve only down to such widths)
+  while (bn > 32 && tiles_m * ((cout16 + bn - 1) / bn) < ctx->sm_count && (bn / 2) % 32 == 0) bn /= 2;
   bn = env_int("PLB_TC_BN", bn);
   if (bn > cout16) bn = cout16;
+  if (bn < cout16 && bn % 32) bn = bn / 32 * 32;
   if (bn < 16 || bn > 256 || bn % 16) return fail(PLB_E_INVALID, "bad channel tile %d", bn);
   a.bn = bn;
   a.tiles_n = (p.cout + bn - 1) / bn;

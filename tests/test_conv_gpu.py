@@ -293,3 +293,38 @@ def test_linearity_at_full_size(plb, ctx):
     assert torch.equal(a1 + a2, a3)
     # spot-check one image against the oracle
     assert np.array_equal(a3[5:6].cpu().numpy(), O.conv_acc_i32((x1 + x2)[5:6], wq, pads=(1, 1, 1, 1)))
+
+
+def _random_cases(count, seed):
+    rng = np.random.default_rng(seed)
+    cases = []
+    while len(cases) < count:
+        k = (int(rng.choice([1, 1, 2, 3, 3, 5])), int(rng.choice([1, 1, 2, 3, 3, 5])))
+        s = (int(rng.choice([1, 1, 2])), int(rng.choice([1, 1, 2])))
+        dil = (int(rng.choice([1, 1, 2])), int(rng.choice([1, 1, 2])))
+        pads = tuple(int(v) for v in rng.integers(0, 3, 4))
+        n = int(rng.integers(1, 5))
+        cin = int(rng.choice([3, 16, 32, 40, 64, 96, 128]))
+        cout = int(rng.choice([8, 24, 32, 64, 72, 128, 160, 256]))
+        h, w = int(rng.integers(5, 30)), int(rng.integers(5, 30))
+        ho = (h + pads[0] + pads[1] - dil[0] * (k[0] - 1) - 1) // s[0] + 1
+        wo = (w + pads[2] + pads[3] - dil[1] * (k[1] - 1) - 1) // s[1] + 1
+        if ho < 1 or wo < 1:
+            continue
+        cases.append((n, cin, h, w, cout, k, s, pads, dil, int(rng.integers(0, 4))))
+    return cases
+
+
+@pytest.mark.parametrize("force_window", ["0", "1"])
+@pytest.mark.parametrize("case", _random_cases(24, 2024), ids=lambda c: "n%dc%dh%dw%do%dk%dx%d" % (c[:5] + c[5]))
+def test_random_geometries(plb, ctx, case, force_window, monkeypatch):
+    """Seeded random geometries (filter size, stride, dilation, asymmetric padding, ragged channel
+    counts, every activation) through accumulators, fp32-out and int8-out, once with the default
+    choice of operand mode and once with window mode forced wherever it applies."""
+    if force_window == "1":
+        monkeypatch.setenv("PLB_TC_SLAB", "1")
+        monkeypatch.setenv("PLB_TC_BSTREAM", "1")
+    n, cin, h, w, cout, k, s, pads, dil, act = case
+    xq, in_s, wq, ws, bias = conv_case(hash(case[:5]) % 10000, n, cin, h, w, cout, k)
+    run_case(plb, ctx, xq, in_s, wq, ws, bias, stride=s, pads=pads, dil=dil, act=act,
+             alpha=6.0 if act == 2 else 0.1)
