@@ -328,3 +328,24 @@ def test_random_geometries(plb, ctx, case, force_window, monkeypatch):
     xq, in_s, wq, ws, bias = conv_case(hash(case[:5]) % 10000, n, cin, h, w, cout, k)
     run_case(plb, ctx, xq, in_s, wq, ws, bias, stride=s, pads=pads, dil=dil, act=act,
              alpha=6.0 if act == 2 else 0.1)
+
+
+def _random_dw(count, seed):
+    rng = np.random.default_rng(seed)
+    out = []
+    for _ in range(count):
+        k = int(rng.choice([3, 3, 3, 5]))
+        out.append((int(rng.integers(1, 4)), int(rng.choice([4, 8, 24, 32, 64, 100, 128])), int(rng.integers(4, 40)),
+                    int(rng.integers(4, 40)), k, int(rng.choice([1, 2])), int(rng.integers(0, k // 2 + 2)),
+                    int(rng.integers(0, 4))))
+    return out
+
+
+@pytest.mark.parametrize("case", _random_dw(16, 5), ids=lambda c: "n%dc%dh%dw%dk%ds%dp%da%d" % c)
+def test_random_depthwise(plb, ctx, case):
+    n, c, h, w, k, s, p, act = case
+    if (h + 2 * p - k) // s + 1 < 1 or (w + 2 * p - k) // s + 1 < 1:
+        pytest.skip("empty output")
+    xq, in_s, wq, ws, bias = conv_case(hash(case) % 10000, n, c, h, w, c, k, groups=c, w_std=0.3)
+    run_case(plb, ctx, xq, in_s, wq, ws, bias, stride=(s, s), pads=(p, p, p, p), groups=c, act=act,
+             alpha=6.0 if act == 2 else 0.1)

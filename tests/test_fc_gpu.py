@@ -90,3 +90,24 @@ def test_extreme_accumulators(plb, ctx, k, below):
     ctx.sync()
     assert np.array_equal(y, y_ref)
     assert np.array_equal(q, q_ref)
+
+
+def _random_fc(count, seed):
+    rng = np.random.default_rng(seed)
+    return [(int(rng.integers(1, 300)), int(rng.choice([32, 64, 96, 100, 160, 256, 512, 1000])),
+             int(rng.choice([8, 17, 40, 80, 96, 160, 250, 320, 1000]))) for _ in range(count)]
+
+
+@pytest.mark.parametrize("m,k,n", _random_fc(16, 77))
+def test_random_fc_shapes(plb, ctx, m, k, n):
+    x, wq, ws, bias = fc_case(m + k + n, m, k, n)
+    acc_ref = O.fc_acc_i32(x, wq)
+    y_ref = O.epilogue(acc_ref, ws, 0.02, bias, O.ACT_RELU, 0.0)
+    out_s = float(max(np.abs(y_ref).max(), 1e-6) / 127)
+    q_ref = O.epilogue(acc_ref, ws, 0.02, bias, O.ACT_RELU, 0.0, out_scale=out_s)
+    xd = dev(x)
+    y = plb.Fc(ctx, wq, ws, 0.02, bias, O.ACT_RELU).run(xd).cpu().numpy()
+    q = plb.Fc(ctx, wq, ws, 0.02, bias, O.ACT_RELU, out_scale=out_s).run(xd).cpu().numpy()
+    ctx.sync()
+    assert np.array_equal(y, y_ref)
+    assert np.array_equal(q, q_ref)
