@@ -276,7 +276,8 @@ def main():
         import torch
         torch.set_num_threads(os.cpu_count() or 1)
         qnet = networks.build_quantized(spec, seed=1234, calib_images=4, device="cpu")
-        sample = args.cpu_sample or max(os.cpu_count() or 1, 8)
+        # one step = 4 images per host thread (≈ 2-3 s of CPU work), so the default 3 + 20 steps take about a minute
+        sample = args.cpu_sample or 4 * max(os.cpu_count() or 1, 8)
         times = []
         for i in range(warmup + args.steps):
             cb = cpu_baseline(qnet, spec, sample)
@@ -444,7 +445,8 @@ def main():
         if not args.no_cpu_baseline and args.gpus == 1:
             try:
                 cpu_q = networks.build_quantized(spec, seed=1234, calib_images=4, device="cuda")
-                sample = args.cpu_sample or max(os.cpu_count() or 1, 8)
+                # bounded sample: 16 images per host thread, about 10 s of CPU work
+                sample = args.cpu_sample or 16 * max(os.cpu_count() or 1, 8)
                 cb = cpu_baseline(cpu_q, spec, sample)
                 cb.pop("seconds", None)
                 line["cpu_baseline"] = cb
