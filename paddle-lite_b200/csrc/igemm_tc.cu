@@ -715,10 +715,12 @@ __global__ void __launch_bounds__(kThreads, 1)
       mbar_init(smem_u32(&full_bar[i]), drained ? 4 * gpb : 1);
     }
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
-    if (lane == 0) {
-      *abort_flag = 0;
-      asm volatile("prefetch.tensormap [%0];" ::"l"(reinterpret_cast<uint64_t>(&tmA)) : "memory");
-      asm volatile("prefetch.tensormap [%0];" ::"l"(reinterpret_cast<uint64_t>(&tmB)) : "memory");
+    if (lane == 0) *abort_flag = 0;
+    {
+      // descriptor prefetch, one map per lane (unused maps are valid copies of the filter map)
+      const CUtensorMap* map = lane == 0 ? &tmA : lane == 1 ? &tmB : lane == 2 ? &tmRes : lane == 3 ? &tmOutW
+                               : lane == 4 ? &tmOutB : lane == 5 ? &tmA2 : &tmB2;
+      if (lane < 7) asm volatile("prefetch.tensormap [%0];" ::"l"(reinterpret_cast<uint64_t>(map)) : "memory");
     }
     __syncwarp();
     if (a.resident_b && lane == 0) {
