@@ -4,6 +4,7 @@
 #include "kernels_simple.cuh"
 
 #include "igemm_tc.cuh"
+#include <cstdlib>
 
 namespace plb {
 
@@ -316,6 +317,274 @@ DwKernel pick_dw_act(int act) {
     case PLB_ACT_RELU6: return dwconv3x3_kernel<S, PLB_ACT_RELU6, I8>;
     case PLB_ACT_LEAKY: return dwconv3x3_kernel<S, PLB_ACT_LEAKY, I8>;
     default: return dwconv3x3_kernel<S, PLB_ACT_NONE, I8>;
+  }
+}
+
+// ------------------------------------------------------------------ depthwise 3x3, column strips
+// Same arithmetic as dwconv3x3_kernel, other traversal: a thread owns 4 channels x 4 output columns
+// and slides DOWN a strip of output rows.  Every input row of the strip is loaded, transposed and
+// shifted once and meets all three filter rows (stride 1) in the same step; accumulator rows rotate
+// through registers with compile-time indices, and the row completed by a step is requantised and
+// stored in that step.  Column predicates, pointers and the filter are set up once per strip, so
+// that the per-output cost is the 3 dp4a, the 5-instruction requantiser and little else.
+// Accumulators start at the bit pattern of 1.5*2^23: the integer sum then IS the float 1.5*2^23 + sum.
+
+constexpr int kDwMagic = 0x4B400000;
+
+// fp32 work is done two channels at a time with the packed f32x2 instructions (same IEEE results per lane).
+template <int ACT, bool OUT_IS_I8>
+__device__ __forceinline__ void dw_emit_row(int (&a)[4][4], const float4 sc, const float4 bi, const float alpha,
+                                            void* __restrict__ y, const long yoff, const int ldy, const int ncols) {
+  const float2 magic = make_float2(12582912.f, 12582912.f), neg_magic = make_float2(-12582912.f, -12582912.f);
+#pragma unroll
+  for (int ox = 0; ox < 4; ++ox) {
+    const float2 v01 = __ffma2_rn(__fadd2_rn(make_float2(__int_as_float(a[ox][0]), __int_as_float(a[ox][1])), neg_magic),
+                                  make_float2(sc.x, sc.y), make_float2(bi.x, bi.y));
+    const float2 v23 = __ffma2_rn(__fadd2_rn(make_float2(__int_as_float(a[ox][2]), __int_as_float(a[ox][3])), neg_magic),
+                                  make_float2(sc.z, sc.w), make_float2(bi.z, bi.w));
+    float v[4] = {v01.x, v01.y, v23.x, v23.y};
+#pragma unroll
+    for (int c = 0; c < 4; ++c) a[ox][c] = kDwMagic;
+    if (ox >= ncols) continue;
+    if (OUT_IS_I8) {
+#pragma unroll
+      for (int c = 0; c < 4; ++c) {
+        float t = v[c];
+        if (ACT == PLB_ACT_NONE) t = fminf(fmaxf(t, -127.f), 127.f);
+        else if (ACT == PLB_ACT_RELU) t = fminf(fmaxf(t, 0.f), 127.f);
+        else if (ACT == PLB_ACT_RELU6) t = fminf(fmaxf(t, 0.f), alpha);
+        else { t = t <= 0.f ? alpha * t : t; t = fminf(fmaxf(t, -127.f), 127.f); }
+        v[c] = t;
+      }
+      // + 1.5*2^23: round to nearest even, result in the low byte
+      const float2 q01 = __fadd2_rn(make_float2(v[0], v[1]), magic), q23 = __fadd2_rn(make_float2(v[2], v[3]), magic);
+      *reinterpret_cast<uint32_t*>(static_cast<int8_t*>(y) + yoff + static_cast<long>(ox) * ldy) =
+          __byte_perm(__byte_perm(__float_as_uint(q01.x), __float_as_uint(q01.y), 0x0040),
+                      __byte_perm(__float_as_uint(q23.x), __float_as_uint(q23.y), 0x0040), 0x5410);
+    } else {
+      *reinterpret_cast<float4*>(static_cast<float*>(y) + yoff + static_cast<long>(ox) * ldy) =
+          make_float4(dw_act<ACT>(v[0], alpha), dw_act<ACT>(v[1], alpha), dw_act<ACT>(v[2], alpha),
+                      dw_act<ACT>(v[3], alpha));
+    }
+  }
+}
+
+// One input row of a strip: IW words.  rok is the same for all threads of a block (a uniform branch);
+// the column mask is per thread.
+template <int S>
+__device__ __forceinline__ void dw_load_raw(const int8_t* __restrict__ p, const int cs, const bool rok,
+                                            const uint32_t colmask, uint32_t (&raw)[3 * S + 3]) {
+  constexpr int IW = 3 * S + 3;
+#pragma unroll
+  for (int ix = 0; ix < IW; ++ix) raw[ix] = 0;
+  if (rok) {
+#pragma unroll
+    for (int ix = 0; ix < IW; ++ix)
+      if ((colmask >> ix) & 1u) raw[ix] = __ldg(reinterpret_cast<const uint32_t*>(p + ix * cs));
+  }
+}
+
+// The words of a row -> the four 3-pixel windows of every channel (win[ox][c]).
+template <int S>
+__device__ __forceinline__ void dw_make_win(const uint32_t (&raw)[3 * S + 3], uint32_t (&win)[4][4]) {
+  constexpr int IW = 3 * S + 3;
+  uint32_t ta[4];
+  transpose4x4(raw[0], raw[1], raw[2], raw[3], ta);
+  if (S == 1) {
+    const uint32_t t0 = __byte_perm(raw[4], raw[5], 0x5140), t1 = __byte_perm(raw[4], raw[5], 0x7362);
+    const uint32_t tb[4] = {t0, t0 >> 16, t1, t1 >> 16};
+#pragma unroll
+    for (int c = 0; c < 4; ++c) {
+      win[0][c] = ta[c];
+      win[1][c] = __funnelshift_r(ta[c], tb[c], 8);
+      win[2][c] = __funnelshift_r(ta[c], tb[c], 16);
+      win[3][c] = __funnelshift_r(ta[c], tb[c], 24);
+    }
+  } else {
+    uint32_t tb[4];
+    transpose4x4(raw[4], raw[5], raw[6], raw[7], tb);
+    const uint32_t last = raw[IW - 1];
+#pragma unroll
+    for (int c = 0; c < 4; ++c) {
+      win[0][c] = ta[c];
+      win[1][c] = __funnelshift_r(ta[c], tb[c], 16);
+      win[2][c] = tb[c];
+      win[3][c] = __funnelshift_r(tb[c], last >> (8 * c), 16);
+    }
+  }
+}
+
+__device__ __forceinline__ void dw_mac(int (&a)[4][4], const uint32_t (&win)[4][4], const uint32_t (&wr)[4]) {
+#pragma unroll
+  for (int ox = 0; ox < 4; ++ox)
+#pragma unroll
+    for (int c = 0; c < 4; ++c) a[ox][c] = __dp4a(static_cast<int>(win[ox][c]), static_cast<int>(wr[c]), a[ox][c]);
+}
+
+constexpr int kDwBlock = 128;  // four blocks per SM at <= 128 registers: finer scheduling than two of 256
+
+template <int S, int ACT, bool OUT_IS_I8, int CS>
+__global__ void __launch_bounds__(kDwBlock, 4)
+    dwconv3x3_strip_kernel(const ConvGeom g, const int8_t* __restrict__ x, const int8_t* __restrict__ w,
+                           const OutDev o, const int cquads, const int tiles_x, const int strip_rows) {
+  pdl_sync_with_previous_kernel();
+  constexpr int IW = 3 * S + 3;
+  const int idx = blockIdx.x * kDwBlock + threadIdx.x;
+  if (idx >= cquads * tiles_x) return;
+  const int tx = idx / cquads;
+  const int cq = idx - tx * cquads;
+  const int oh0 = blockIdx.y * strip_rows;
+  const int rows = min(strip_rows, g.ho - oh0);
+  const long n = blockIdx.z;
+  const int ow0 = tx * 4, c0 = cq * 4;
+  // CS != 0: pixel pitch of input and output known at compile time (immediate load / store offsets)
+  const int cs = CS ? CS : g.cin_stride;
+  const int ldy = CS ? CS : o.ldy;
+
+  uint32_t wr[3][4];
+#pragma unroll
+  for (int r = 0; r < 3; ++r)
+    transpose4x4(__ldg(reinterpret_cast<const uint32_t*>(w + static_cast<long>(r * 3 + 0) * g.cg_pad + c0)),
+                 __ldg(reinterpret_cast<const uint32_t*>(w + static_cast<long>(r * 3 + 1) * g.cg_pad + c0)),
+                 __ldg(reinterpret_cast<const uint32_t*>(w + static_cast<long>(r * 3 + 2) * g.cg_pad + c0)), 0u, wr[r]);
+  const float4 sc = *reinterpret_cast<const float4*>(o.scale + c0);
+  const float4 bi = *reinterpret_cast<const float4*>(o.bias + c0);
+  const float alpha = OUT_IS_I8 && ACT == PLB_ACT_RELU6 ? fminf(o.alpha, 127.f) : o.alpha;
+
+  const int ih0 = oh0 * S - g.pad_t, iw0 = ow0 * S - g.pad_l;
+  uint32_t colmask = 0;
+#pragma unroll
+  for (int ix = 0; ix < IW; ++ix)
+    if (iw0 + ix >= 0 && iw0 + ix < g.w) colmask |= 1u << ix;
+  const long row_step = static_cast<long>(g.w) * cs;
+  // byte offset of (image n, input row ih0, column iw0, channel c0); rows / columns outside the image
+  // are never dereferenced
+  const int8_t* xrow = x + (((n * g.h + ih0) * g.w + iw0) * static_cast<long>(cs) + c0);
+  const int ncols = g.wo - ow0;
+  long yoff = ((n * g.ho + oh0) * g.wo + ow0) * static_cast<long>(ldy) + c0;
+  const long yrow = static_cast<long>(g.wo) * ldy;
+  const int in_rows = (rows - 1) * S + 3;  // input rows this strip touches
+
+  uint32_t win[4][4];
+  if (S == 1) {
+    // step iy (P = iy % 3): filter row 0 -> output row iy, row 1 -> iy-1, row 2 -> iy-2 (then complete)
+    int acc[3][4][4];
+#pragma unroll
+    for (int p = 0; p < 3; ++p)
+#pragma unroll
+      for (int a = 0; a < 4; ++a)
+#pragma unroll
+        for (int c = 0; c < 4; ++c) acc[p][a][c] = kDwMagic;
+    // the three rows of the next iteration are fetched while this iteration's rows are used
+    uint32_t cur[3][6], nxt[3][6];
+#pragma unroll
+    for (int P = 0; P < 3; ++P) {
+      dw_load_raw<1>(xrow, cs, P < in_rows && static_cast<unsigned>(ih0 + P) < static_cast<unsigned>(g.h), colmask, cur[P]);
+      xrow += row_step;
+    }
+    for (int iy = 0; iy < in_rows; iy += 3) {
+#pragma unroll
+      for (int P = 0; P < 3; ++P) {
+        const int ir = iy + 3 + P;
+        dw_load_raw<1>(xrow, cs, ir < in_rows && static_cast<unsigned>(ih0 + ir) < static_cast<unsigned>(g.h), colmask, nxt[P]);
+        xrow += row_step;
+      }
+#pragma unroll
+      for (int P = 0; P < 3; ++P) {
+        const int ir = iy + P;
+        dw_make_win<1>(cur[P], win);
+        dw_mac(acc[P], win, wr[0]);
+        dw_mac(acc[(P + 2) % 3], win, wr[1]);
+        dw_mac(acc[(P + 1) % 3], win, wr[2]);
+        const int oy = ir - 2;
+        if (oy >= 0 && oy < rows) {
+          dw_emit_row<ACT, OUT_IS_I8>(acc[(P + 1) % 3], sc, bi, alpha, o.y, yoff, ldy, ncols);
+          yoff += yrow;
+        } else {
+#pragma unroll
+          for (int a = 0; a < 4; ++a)
+#pragma unroll
+            for (int c = 0; c < 4; ++c) acc[(P + 1) % 3][a][c] = kDwMagic;
+        }
+      }
+#pragma unroll
+      for (int P = 0; P < 3; ++P)
+#pragma unroll
+        for (int ix = 0; ix < 6; ++ix) cur[P][ix] = nxt[P][ix];
+    }
+  } else {
+    // input row 2k: filter row 0 of output k and filter row 2 of output k-1 (then complete); row 2k+1: filter row 1
+    int acc[2][4][4];
+#pragma unroll
+    for (int p = 0; p < 2; ++p)
+#pragma unroll
+      for (int a = 0; a < 4; ++a)
+#pragma unroll
+        for (int c = 0; c < 4; ++c) acc[p][a][c] = kDwMagic;
+    // two rows (one output row) are fetched ahead of the two in use
+    uint32_t cur[2][9], nxt[2][9];
+#pragma unroll
+    for (int P = 0; P < 2; ++P) {
+      dw_load_raw<2>(xrow, cs, P < in_rows && static_cast<unsigned>(ih0 + P) < static_cast<unsigned>(g.h), colmask, cur[P]);
+      xrow += row_step;
+    }
+    for (int iy = 0; iy < in_rows; iy += 4) {
+#pragma unroll
+      for (int P = 0; P < 2; ++P) {
+        const int ir = iy + 2 * P;
+#pragma unroll
+        for (int q = 0; q < 2; ++q) {
+          const int in = ir + 2 + q;
+          dw_load_raw<2>(xrow, cs, in < in_rows && static_cast<unsigned>(ih0 + in) < static_cast<unsigned>(g.h), colmask, nxt[q]);
+          xrow += row_step;
+        }
+        dw_make_win<2>(cur[0], win);
+        dw_mac(acc[P], win, wr[0]);
+        dw_mac(acc[P ^ 1], win, wr[2]);
+        const int oy = (ir >> 1) - 1;
+        if (oy >= 0 && oy < rows) {
+          dw_emit_row<ACT, OUT_IS_I8>(acc[P ^ 1], sc, bi, alpha, o.y, yoff, ldy, ncols);
+          yoff += yrow;
+        } else {
+#pragma unroll
+          for (int a = 0; a < 4; ++a)
+#pragma unroll
+            for (int c = 0; c < 4; ++c) acc[P ^ 1][a][c] = kDwMagic;
+        }
+        dw_make_win<2>(cur[1], win);
+        dw_mac(acc[P], win, wr[1]);
+#pragma unroll
+        for (int q = 0; q < 2; ++q)
+#pragma unroll
+          for (int ix = 0; ix < 9; ++ix) cur[q][ix] = nxt[q][ix];
+      }
+    }
+  }
+}
+
+typedef void (*DwStripKernel)(const ConvGeom, const int8_t*, const int8_t*, const OutDev, const int, const int,
+                              const int);
+template <int S, bool I8, int CS>
+DwStripKernel pick_dw_strip_act(int act) {
+  switch (act) {
+    case PLB_ACT_RELU: return dwconv3x3_strip_kernel<S, PLB_ACT_RELU, I8, CS>;
+    case PLB_ACT_RELU6: return dwconv3x3_strip_kernel<S, PLB_ACT_RELU6, I8, CS>;
+    case PLB_ACT_LEAKY: return dwconv3x3_strip_kernel<S, PLB_ACT_LEAKY, I8, CS>;
+    default: return dwconv3x3_strip_kernel<S, PLB_ACT_NONE, I8, CS>;
+  }
+}
+// int8 output with the usual channel counts as pixel pitch gets the compile-time-pitch variants
+template <int S>
+DwStripKernel pick_dw_strip(bool i8, int act, int pitch) {
+  if (!i8) return pick_dw_strip_act<S, false, 0>(act);
+  switch (pitch) {
+    case 32: return pick_dw_strip_act<S, true, 32>(act);
+    case 64: return pick_dw_strip_act<S, true, 64>(act);
+    case 128: return pick_dw_strip_act<S, true, 128>(act);
+    case 256: return pick_dw_strip_act<S, true, 256>(act);
+    case 512: return pick_dw_strip_act<S, true, 512>(act);
+    case 1024: return pick_dw_strip_act<S, true, 1024>(act);
+    default: return pick_dw_strip_act<S, true, 0>(act);
   }
 }
 
@@ -902,6 +1171,34 @@ int dwconv_launch(plb_ctx* ctx, const ConvGeom& g, const int8_t* x, const int8_t
     const long total = static_cast<long>(g.batch) * tiles_y * tiles_x * cq;
     if (total == 0) return PLB_OK;
     const bool i8 = out.mode == OUT_I8;
+    // column-strip kernel (default): long strips (few halo rows) as long as every SM still gets two blocks
+    const char* strip_env = std::getenv("PLB_DW_STRIP");
+    int strip = strip_env ? std::atoi(strip_env) : -1;
+    const long bx = (static_cast<long>(cq) * tiles_x + kDwBlock - 1) / kDwBlock;
+    if (strip < 0) {
+      // rows per strip: a block costs (input rows it reads) and the blocks run in waves of four per SM
+      const long slots = 4L * ctx->sm_count;
+      long best = -1;
+      for (int ns = 1; ns <= g.ho; ++ns) {
+        const int rows = (g.ho + ns - 1) / ns;
+        if (rows > 32 && ns < g.ho) continue;
+        if ((g.ho + rows - 1) / rows != ns) continue;
+        const long waves = (bx * ns * g.batch + slots - 1) / slots;
+        const long cost = waves * ((rows - 1) * g.stride_h + 3 + 2);  // + a block's fixed part, about two rows
+        if (best < 0 || cost < best) best = cost, strip = rows;
+        if (rows <= 2) break;
+      }
+    }
+    if (strip > 0) {
+      const int strips = (g.ho + strip - 1) / strip;
+      if (strips > 65535 || g.batch > 65535) return fail(PLB_E_UNSUPPORTED, "depthwise 3x3: more than 65535 strips or images");
+      const int pitch = g.cin_stride == static_cast<int>(out.ldy) ? g.cin_stride : 0;
+      DwStripKernel ks = g.stride_h == 1 ? pick_dw_strip<1>(i8, out.epi.act, pitch) : pick_dw_strip<2>(i8, out.epi.act, pitch);
+      dim3 grid(static_cast<unsigned>(bx), static_cast<unsigned>(strips), static_cast<unsigned>(g.batch));
+      PLB_CUDA(launch_kernel(ks, grid, dim3(kDwBlock), 0, ctx->stream, g, x, w_tc, to_dev(out), cq, tiles_x, strip));
+      ctx->launches++;
+      return PLB_OK;
+    }
     DwKernel k = g.stride_h == 1 ? (i8 ? pick_dw_act<1, true>(out.epi.act) : pick_dw_act<1, false>(out.epi.act))
                                  : (i8 ? pick_dw_act<2, true>(out.epi.act) : pick_dw_act<2, false>(out.epi.act));
     if (tiles_y > 65535 || g.batch > 65535) return fail(PLB_E_UNSUPPORTED, "depthwise 3x3: more than 65535 tile rows or images");
