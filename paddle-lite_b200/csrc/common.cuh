@@ -60,6 +60,8 @@ struct EpiParams {
   const float* bias;    // [C] folded bias(/out_s), zeros when absent
   int act;              // PLB_ACT_*
   float alpha;          // already divided by out_s where the reference does so
+  int acc_small = 0;    // 1: 128 * (largest sum of |w| over one output channel) < 2^22, so every accumulator is
+                        // below 2^22 in magnitude and converts to float exactly through the mantissa trick
 };
 
 #ifdef __CUDACC__

@@ -78,6 +78,8 @@ struct IgemmArgs {
   const float* bias;
   int act;
   float alpha;
+  int acc_small;                       // every |accumulator| < 2^22 (proven from the filter by the host)
+  int sb_off, sb_cols;                 // scale / bias tables copied to shared memory (offset in the staging area; 0 columns = not)
   const float* residual;
   float* y_f32;
   int8_t* y_i8;
@@ -304,24 +306,60 @@ __device__ __forceinline__ uint64_t make_smem_desc(uint32_t addr, int kc) {
 
 constexpr float kRoundMagic = 12582912.f;  // 1.5 * 2^23
 
-template <int ACT>
-__device__ __forceinline__ uint32_t quant_byte(float v, float alpha) {
-  // clamp(rne(act(v)), -127, 127); rounding and clamping commute because the bounds are integers
-  if (ACT == PLB_ACT_NONE) {
-    v = fminf(fmaxf(v, -127.f), 127.f);
-  } else if (ACT == PLB_ACT_RELU) {
-    v = fminf(fmaxf(v, 0.f), 127.f);
-  } else if (ACT == PLB_ACT_RELU6) {
-    v = fminf(fmaxf(v, 0.f), alpha);  // alpha already limited to 127 by the caller
-  } else {
-    v = v <= 0.f ? alpha * v : v;
-    v = fminf(fmaxf(v, -127.f), 127.f);
-  }
-  return __float_as_uint(v + kRoundMagic);
-}
-
 __device__ __forceinline__ uint32_t pack_low_bytes(uint32_t a, uint32_t b, uint32_t c, uint32_t d) {
   return __byte_perm(__byte_perm(a, b, 0x0040), __byte_perm(c, d, 0x0040), 0x5410);
+}
+
+// Four int32 accumulators -> four requantised bytes clamp(rne(act(fmaf(float(acc), scale, bias))), -127, 127),
+// in about half the instructions of the straightforward sequence and with bit-identical results:
+// * fp32 work on two values per instruction (f32x2 forms of add and fma, IEEE per lane);
+// * SMALL (the host has proven |acc| < 2^22 from the filter): int -> float through the mantissa of
+//   1.5 * 2^23 (one integer add and one fp add, exact) instead of the quarter-rate conversion pipe;
+// * clamping after the rounding add, on the bit pattern: the pattern of a float is monotonic in
+//   its value, so min / max against (magic + bound) clamp every finite input, also those outside
+//   the range in which the rounding add is exact; rounding and clamping commute because the bounds
+//   are integers.  `ub` = upper bound (127, or rne(min(alpha, 127)) for ReLU6).
+constexpr int kMagicBits = 0x4B400000;  // bit pattern of kRoundMagic
+
+template <int ACT>
+__device__ __forceinline__ uint32_t clamp_rounded(float t, int ub) {
+  const int b = __float_as_int(t);
+  if (ACT == PLB_ACT_RELU) return static_cast<uint32_t>(__viaddmin_s32_relu(b, -kMagicBits, ub));  // ub = 127 >= 0
+  if (ACT == PLB_ACT_RELU6) return static_cast<uint32_t>(min(__viaddmax_s32(b, -kMagicBits, 0), ub));
+  return static_cast<uint32_t>(max(__viaddmin_s32(b, -kMagicBits, 127), -127));
+}
+
+template <int ACT, bool SMALL>
+__device__ __forceinline__ uint32_t quant4(const uint32_t* r, const float4 sc, const float4 bi, const float alpha,
+                                           const int ub) {
+  float2 f01, f23;
+  if (SMALL) {
+    const float2 nm = make_float2(-kRoundMagic, -kRoundMagic);
+    f01 = __fadd2_rn(make_float2(__int_as_float(static_cast<int>(r[0]) + kMagicBits),
+                                 __int_as_float(static_cast<int>(r[1]) + kMagicBits)), nm);
+    f23 = __fadd2_rn(make_float2(__int_as_float(static_cast<int>(r[2]) + kMagicBits),
+                                 __int_as_float(static_cast<int>(r[3]) + kMagicBits)), nm);
+  } else {
+    f01 = make_float2(__int2float_rn(static_cast<int>(r[0])), __int2float_rn(static_cast<int>(r[1])));
+    f23 = make_float2(__int2float_rn(static_cast<int>(r[2])), __int2float_rn(static_cast<int>(r[3])));
+  }
+  float2 v01 = __ffma2_rn(f01, make_float2(sc.x, sc.y), make_float2(bi.x, bi.y));
+  float2 v23 = __ffma2_rn(f23, make_float2(sc.z, sc.w), make_float2(bi.z, bi.w));
+  if (ACT == PLB_ACT_LEAKY) {
+    v01.x = v01.x <= 0.f ? alpha * v01.x : v01.x;
+    v01.y = v01.y <= 0.f ? alpha * v01.y : v01.y;
+    v23.x = v23.x <= 0.f ? alpha * v23.x : v23.x;
+    v23.y = v23.y <= 0.f ? alpha * v23.y : v23.y;
+  }
+  const float2 m2 = make_float2(kRoundMagic, kRoundMagic);
+  const float2 t01 = __fadd2_rn(v01, m2), t23 = __fadd2_rn(v23, m2);
+  return pack_low_bytes(clamp_rounded<ACT>(t01.x, ub), clamp_rounded<ACT>(t01.y, ub), clamp_rounded<ACT>(t23.x, ub),
+                        clamp_rounded<ACT>(t23.y, ub));
+}
+
+template <int ACT>
+__device__ __forceinline__ int quant_upper_bound(float alpha) {
+  return ACT == PLB_ACT_RELU6 ? __float2int_rn(fminf(alpha, 127.f)) : 127;
 }
 
 // 256-bit global accesses: one full 32-byte sector per lane and instruction
@@ -389,16 +427,14 @@ __device__ __forceinline__ void epilogue_store32(const IgemmArgs& a, const uint3
   const float4* sc4 = reinterpret_cast<const float4*>(a.scale + col);
   const float4* bi4 = reinterpret_cast<const float4*>(a.bias + col);
   if (MODE == OUT_I8) {
-    const float alpha = ACT == PLB_ACT_RELU6 ? fminf(a.alpha, 127.f) : a.alpha;
+    const int ub = quant_upper_bound<ACT>(a.alpha);
     uint32_t q[8];
+    if (a.acc_small) {
 #pragma unroll
-    for (int j = 0; j < 8; ++j) {
-      const float4 sc = __ldg(sc4 + j), bi = __ldg(bi4 + j);
-      q[j] = pack_low_bytes(
-          quant_byte<ACT>(fmaf(__int2float_rn((int)r[4 * j]), sc.x, bi.x), alpha),
-          quant_byte<ACT>(fmaf(__int2float_rn((int)r[4 * j + 1]), sc.y, bi.y), alpha),
-          quant_byte<ACT>(fmaf(__int2float_rn((int)r[4 * j + 2]), sc.z, bi.z), alpha),
-          quant_byte<ACT>(fmaf(__int2float_rn((int)r[4 * j + 3]), sc.w, bi.w), alpha));
+      for (int j = 0; j < 8; ++j) q[j] = quant4<ACT, true>(&r[4 * j], __ldg(sc4 + j), __ldg(bi4 + j), a.alpha, ub);
+    } else {
+#pragma unroll
+      for (int j = 0; j < 8; ++j) q[j] = quant4<ACT, false>(&r[4 * j], __ldg(sc4 + j), __ldg(bi4 + j), a.alpha, ub);
     }
     int8_t* dst = static_cast<int8_t*>(a.y) + row * a.ldy + col;
     if (full && (a.ldy & 31) == 0) {
@@ -539,9 +575,9 @@ __device__ __forceinline__ void sts128(uint32_t addr, uint32_t a, uint32_t b, ui
 // the int8 staging tile, byte_chunk0 the index of the first 16-byte chunk to write and
 // b_swz_mask the xor mask of that row in the tile's swizzle (see b_swz at the call site).
 template <int MODE, int ACT>
-__device__ __forceinline__ void epilogue_chunk_staged(const IgemmArgs& a, const uint32_t (&r)[32], int lane,
-                                                      int col, uint32_t st_w, uint32_t st_b_row,
-                                                      int byte_chunk0, int b_swz_mask, bool have_res) {
+__device__ __forceinline__ void epilogue_chunk_staged(const IgemmArgs& a, const float* scale, const float* bias,
+                                                      const uint32_t (&r)[32], int lane, int col, uint32_t st_w,
+                                                      uint32_t st_b_row, int byte_chunk0, int b_swz_mask, bool have_res) {
   const uint32_t w_row = st_w + lane * 128;
   const int sw = lane & 7;
   if (MODE == OUT_ACC) {
@@ -549,12 +585,13 @@ __device__ __forceinline__ void epilogue_chunk_staged(const IgemmArgs& a, const 
     for (int j = 0; j < 8; ++j) sts128(w_row + ((j ^ sw) << 4), r[4 * j], r[4 * j + 1], r[4 * j + 2], r[4 * j + 3]);
     return;
   }
-  const float4* sc4 = reinterpret_cast<const float4*>(a.scale + col);
-  const float4* bi4 = reinterpret_cast<const float4*>(a.bias + col);
+  // scale / bias: the CTA's shared-memory copy (all lanes read the same address: a broadcast) or global memory
+  const float4* sc4 = reinterpret_cast<const float4*>(scale + col);
+  const float4* bi4 = reinterpret_cast<const float4*>(bias + col);
   if (MODE == OUT_F32) {
 #pragma unroll
     for (int j = 0; j < 8; ++j) {
-      const float4 sc = __ldg(sc4 + j), bi = __ldg(bi4 + j);
+      const float4 sc = sc4[j], bi = bi4[j];
       const float x = act_f32<ACT>(fmaf(__int2float_rn((int)r[4 * j]), sc.x, bi.x), a.alpha);
       const float y = act_f32<ACT>(fmaf(__int2float_rn((int)r[4 * j + 1]), sc.y, bi.y), a.alpha);
       const float z = act_f32<ACT>(fmaf(__int2float_rn((int)r[4 * j + 2]), sc.z, bi.z), a.alpha);
@@ -565,20 +602,18 @@ __device__ __forceinline__ void epilogue_chunk_staged(const IgemmArgs& a, const 
   }
   uint32_t q[8];
   if (MODE == OUT_I8) {
-    const float alpha = ACT == PLB_ACT_RELU6 ? fminf(a.alpha, 127.f) : a.alpha;
+    const int ub = quant_upper_bound<ACT>(a.alpha);
+    if (a.acc_small) {
 #pragma unroll
-    for (int j = 0; j < 8; ++j) {
-      const float4 sc = __ldg(sc4 + j), bi = __ldg(bi4 + j);
-      q[j] = pack_low_bytes(
-          quant_byte<ACT>(fmaf(__int2float_rn((int)r[4 * j]), sc.x, bi.x), alpha),
-          quant_byte<ACT>(fmaf(__int2float_rn((int)r[4 * j + 1]), sc.y, bi.y), alpha),
-          quant_byte<ACT>(fmaf(__int2float_rn((int)r[4 * j + 2]), sc.z, bi.z), alpha),
-          quant_byte<ACT>(fmaf(__int2float_rn((int)r[4 * j + 3]), sc.w, bi.w), alpha));
+      for (int j = 0; j < 8; ++j) q[j] = quant4<ACT, true>(&r[4 * j], sc4[j], bi4[j], a.alpha, ub);
+    } else {
+#pragma unroll
+      for (int j = 0; j < 8; ++j) q[j] = quant4<ACT, false>(&r[4 * j], sc4[j], bi4[j], a.alpha, ub);
     }
   } else {  // OUT_ADD_RELU
 #pragma unroll
     for (int j = 0; j < 8; ++j) {
-      const float4 sc = __ldg(sc4 + j), bi = __ldg(bi4 + j);
+      const float4 sc = sc4[j], bi = bi4[j];
       const uint32_t addr = w_row + ((j ^ sw) << 4);
       float4 t = make_float4(0.f, 0.f, 0.f, 0.f);
       if (have_res) t = lds128f(addr);
@@ -695,6 +730,31 @@ __global__ void __launch_bounds__(kThreads, 1)
 
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
+
+  // Per-channel scale and bias of all output channels in shared memory: an epilogue chunk then
+  // reads them with broadcast shared loads instead of waiting for L2 (the tables are layer
+  // constants, not written by the preceding kernel, so they are copied before the wait for it).
+  const float* ep_scale = a.scale;
+  const float* ep_bias = a.bias;
+  const float* ep_scale2 = a.scale2;
+  const float* ep_bias2 = a.bias2;
+  if (a.sb_cols > 0) {
+    float* sb = reinterpret_cast<float*>(smem_al + a.sb_off);
+    for (int i = threadIdx.x; i < a.sb_cols; i += kThreads) {
+      sb[i] = __ldg(a.scale + i);
+      sb[a.sb_cols + i] = __ldg(a.bias + i);
+      if (a.dual) {
+        sb[2 * a.sb_cols + i] = __ldg(a.scale2 + i);
+        sb[3 * a.sb_cols + i] = __ldg(a.bias2 + i);
+      }
+    }
+    ep_scale = sb;
+    ep_bias = sb + a.sb_cols;
+    if (a.dual) {
+      ep_scale2 = sb + 2 * a.sb_cols;
+      ep_bias2 = sb + 3 * a.sb_cols;
+    }
+  }
 
   // TMEM: nb accumulator buffers of acc_cols columns each (512 columns in total at most)
   uint32_t acc_cols = 32;
@@ -1253,7 +1313,7 @@ __global__ void __launch_bounds__(kThreads, 1)
               __syncwarp();
               stores_pending = false;
             }
-            epilogue_chunk_staged<MODE, ACT>(a, r, lane, n0 + c, pf_tile[pf_cur], st_b + lane * 32, 0, 0, true);
+            epilogue_chunk_staged<MODE, ACT>(a, ep_scale, ep_bias, r, lane, n0 + c, pf_tile[pf_cur], st_b + lane * 32, 0, 0, true);
             fence_proxy_async_smem();
             __syncwarp();
             if (lane == 0) {
@@ -1315,12 +1375,12 @@ __global__ void __launch_bounds__(kThreads, 1)
             uint32_t r2[32];
             tc_ld32(lane_addr + acc_cols + static_cast<uint32_t>(c), r2);
             tc_wait_ld();
-            const float4* sc4 = reinterpret_cast<const float4*>(a.scale2 + n0 + c);
-            const float4* bi4 = reinterpret_cast<const float4*>(a.bias2 + n0 + c);
+            const float4* sc4 = reinterpret_cast<const float4*>(ep_scale2 + n0 + c);
+            const float4* bi4 = reinterpret_cast<const float4*>(ep_bias2 + n0 + c);
             const uint32_t w_row = st_w + lane * 128;
 #pragma unroll
             for (int j = 0; j < 8; ++j) {
-              const float4 sc = __ldg(sc4 + j), bi = __ldg(bi4 + j);
+              const float4 sc = sc4[j], bi = bi4[j];
               sts128(w_row + ((j ^ (lane & 7)) << 4),
                      __float_as_uint(fmaf(__int2float_rn((int)r2[4 * j]), sc.x, bi.x)),
                      __float_as_uint(fmaf(__int2float_rn((int)r2[4 * j + 1]), sc.y, bi.y)),
@@ -1343,8 +1403,8 @@ __global__ void __launch_bounds__(kThreads, 1)
               TT_START();
               if (!ok) break;
             }
-            epilogue_chunk_staged<MODE, ACT>(a, r, lane, n0 + c, st_w, st_b + lane * wq, (c - cbase) >> 4, b_swz,
-                                             have_res);
+            epilogue_chunk_staged<MODE, ACT>(a, ep_scale, ep_bias, r, lane, n0 + c, st_w, st_b + lane * wq,
+                                             (c - cbase) >> 4, b_swz, have_res);
 #ifdef PLB_TC_TIMING
             const long long tf0 = clock64();
 #endif
@@ -1614,7 +1674,13 @@ int igemm_tc_launch(plb_ctx* ctx, const IgemmProblem& p) {
     a.stage_b_warp = staged && want_b ? (wq_h == 128 ? 4096 : 32 * wq_h) : 0;
     if (a.res_prefetch && want_b) a.stage_b_warp = 1024;  // int8 results leave chunk by chunk (32 rows x 32 bytes)
   }
-  a.staging_bytes = (a.staging_w_bytes + kEpilogueWarps * a.stage_b_warp + 1023) / 1024 * 1024;
+  a.sb_off = a.staging_w_bytes + kEpilogueWarps * a.stage_b_warp;
+  a.sb_cols = 0;
+  if (staged && p.out_mode != OUT_ACC && env_int("PLB_TC_SB_SMEM", 1) != 0) {
+    const int cols = (p.cout + 31) / 32 * 32;  // the device arrays are readable up to the next multiple of 64 floats
+    if (cols * 8 * (dual ? 2 : 1) <= 16 * 1024) a.sb_cols = cols;
+  }
+  a.staging_bytes = (a.sb_off + a.sb_cols * 8 * (dual ? 2 : 1) + 1023) / 1024 * 1024;
   if (a.res_prefetch) {
     // the doubled staging leaves less room for the operand ring: shorter K steps keep three stages
     while (a.kc > 32 && (225 * 1024 - a.staging_bytes - kCtrlBytes) / ((kTileM + bn) * a.kc) < 3) {
@@ -1702,6 +1768,7 @@ int igemm_tc_launch(plb_ctx* ctx, const IgemmProblem& p) {
   a.ldy = p.ldy;
   a.y = p.y;
   a.scale = p.epi.scale; a.bias = p.epi.bias; a.act = p.epi.act; a.alpha = p.epi.alpha;
+  a.acc_small = p.epi.acc_small && env_int("PLB_TC_ACC_SMALL", 1) != 0;
   a.residual = p.residual; a.y_f32 = p.y_f32; a.y_i8 = p.y_i8;
   a.inv_next_scale = p.inv_next_scale;
   a.status = ctx->d_status;
@@ -1861,9 +1928,17 @@ int igemm_tc_launch(plb_ctx* ctx, const IgemmProblem& p) {
     if (r != CUDA_SUCCESS) return fail(PLB_E_CUDA, "cuTensorMapEncodeTiled(output) failed: %d", (int)r);
   }
 
-  const size_t smem = static_cast<size_t>(a.staging_bytes) + a.resident_bytes +
-                      static_cast<size_t>(stages) * ring_stage_bytes +
-                      static_cast<size_t>(a.b_stages) * a.kgroup * bn * a.kc + kCtrlBytes + 1024;
+  auto smem_needed = [&]() {
+    return static_cast<size_t>(a.staging_bytes) + a.resident_bytes + static_cast<size_t>(stages) * ring_stage_bytes +
+           static_cast<size_t>(a.b_stages) * a.kgroup * bn * a.kc + kCtrlBytes + 1024;
+  };
+  if (smem_needed() > 227 * 1024 && a.sb_cols > 0) {
+    // a pipeline sized to the last kilobyte (minimum ring next to a large resident filter): the
+    // scale / bias tables stay in global memory
+    a.sb_cols = 0;
+    a.staging_bytes = (a.sb_off + 1023) / 1024 * 1024;
+  }
+  const size_t smem = smem_needed();
   if (smem > 227 * 1024) return fail(PLB_E_UNSUPPORTED, "pipeline needs %zu bytes of shared memory", smem);
   IgemmKernel kernel = pick_kernel(p.out_mode, p.epi.act, staged);
   // the attribute belongs to (function, device): remember which pairs have been configured

@@ -122,6 +122,7 @@ struct plb_conv {
   DeviceBuf w;         // repacked filter
   DeviceBuf scale_f32, bias_f32, scale_i8, bias_i8;
   float alpha_f32 = 0.f, alpha_i8 = 0.f;
+  bool acc_small = false;  // 128 * max over channels of sum |w| < 2^22: accumulators convert to float exactly by the mantissa trick
 };
 
 struct plb_fc {
@@ -132,6 +133,7 @@ struct plb_fc {
   DeviceBuf wt;  // [n, k_pad]
   DeviceBuf scale_f32, bias_f32, scale_i8, bias_i8;
   float alpha_f32 = 0.f, alpha_i8 = 0.f;
+  bool acc_small = false;
 };
 
 struct plb_sparse {
@@ -246,6 +248,16 @@ int plb_conv_prepare(plb_ctx* ctx, const plb_conv_desc* desc, const int8_t* filt
   const int cig = d.cin / d.groups;
   const bool depthwise = d.groups == d.cin && d.cin == d.cout;
   const int taps = d.kh * d.kw;
+  {
+    long worst = 0;
+    const size_t per_channel = static_cast<size_t>(cig) * taps;
+    for (int co = 0; co < d.cout; ++co) {
+      long sum = 0;
+      for (size_t i = 0; i < per_channel; ++i) sum += std::abs(static_cast<int>(filter_h[co * per_channel + i]));
+      worst = std::max(worst, sum);
+    }
+    c->acc_small = worst * 128 < (1L << 22);
+  }
   std::vector<int8_t> packed;
   if (depthwise && d.impl != PLB_IMPL_TC) {
     c->kind = 2;
@@ -422,6 +434,7 @@ OutSpec out_spec(const plb_conv* c, int mode, void* y) {
     o.epi.alpha = c->alpha_f32;
   }
   o.epi.act = c->d.act;
+  o.epi.acc_small = c->acc_small ? 1 : 0;
   return o;
 }
 
@@ -618,6 +631,15 @@ int plb_fc_prepare(plb_ctx* ctx, int k, int n, int act, float act_alpha, float i
   std::vector<int8_t> wt(static_cast<size_t>(n) * f->k_pad, 0);  // [n][k]: K-major rows
   for (int kk = 0; kk < k; ++kk)
     for (int j = 0; j < n; ++j) wt[static_cast<size_t>(j) * f->k_pad + kk] = w_h[static_cast<size_t>(kk) * n + j];
+  {
+    long worst = 0;
+    for (int j = 0; j < n; ++j) {
+      long sum = 0;
+      for (int kk = 0; kk < k; ++kk) sum += std::abs(static_cast<int>(wt[static_cast<size_t>(j) * f->k_pad + kk]));
+      worst = std::max(worst, sum);
+    }
+    f->acc_small = worst * 128 < (1L << 22);
+  }
   int rc = f->wt.upload(wt.data(), wt.size());
   if (rc) return rc;
   Folded fo = fold(n, wscale_h, n_wscale, bias_h, in_scale, out_dtype == PLB_OUT_I8 ? out_scale : 1.f,
@@ -643,6 +665,7 @@ static int fc_run_mode(plb_fc* f, const int8_t* x, void* y, int m, int mode) {
     e.scale = f->scale_f32.as<float>(); e.bias = f->bias_f32.as<float>(); e.alpha = f->alpha_f32;
   }
   e.act = f->act;
+  e.acc_small = f->acc_small ? 1 : 0;
   if (f->tc && (reinterpret_cast<uintptr_t>(x) & 15) == 0) {
     IgemmProblem p;
     memset(&p, 0, sizeof(p));

@@ -63,3 +63,30 @@ def test_graph_replay_matches_eager(plb, ctx):
         g.replay()
         c2.sync()
     assert torch.equal(runner.buf["logits"], eager)
+
+
+@pytest.mark.parametrize("name,batch", [("resnet50", 128), ("mobilenet_v1", 256)])
+def test_benchmark_batch_matches_small_batch(plb, ctx, name, batch):
+    """The plan of a layer (tile width, accumulator buffers, resident filter, window mode, strip
+    height) depends on the batch.  At the benchmark's batch every tensor of image i must equal the
+    same tensor of the two-image run, which the test above ties to the oracle bit for bit."""
+    N = nets()
+    spec = N.SPECS[name]()
+    qnet = N.build_quantized(spec, seed=7, calib_images=4, device="cuda")
+    rng = np.random.default_rng(99)
+    two = torch.from_numpy(rng.standard_normal((2,) + spec["image"]).astype(np.float32)).cuda()
+    small = N.Runner(plb, ctx, qnet, 2)
+    small.forward(two)
+    ctx.sync()
+    big = N.Runner(plb, ctx, qnet, batch)
+    big.forward(two.repeat(batch // 2, 1, 1, 1))
+    ctx.sync()
+    checked = 0
+    for key, ref in small.buf.items():
+        if key not in big.buf or ref.shape[1:] != big.buf[key].shape[1:]:
+            continue
+        got = big.buf[key]
+        for first in (0, batch - 2):
+            assert torch.equal(got[first:first + 2], ref), "tensor %s differs at images %d.." % (key, first)
+        checked += 1
+    assert checked > 10
