@@ -311,27 +311,27 @@ __device__ __forceinline__ uint32_t pack_low_bytes(uint32_t a, uint32_t b, uint3
 }
 
 // Four int32 accumulators -> four requantised bytes clamp(rne(act(fmaf(float(acc), scale, bias))), -127, 127),
-// in about half the instructions of the straightforward sequence and with bit-identical results:
+// with fewer instructions than the straightforward sequence and bit-identical results:
 // * fp32 work on two values per instruction (f32x2 forms of add and fma, IEEE per lane);
 // * SMALL (the host has proven |acc| < 2^22 from the filter): int -> float through the mantissa of
 //   1.5 * 2^23 (one integer add and one fp add, exact) instead of the quarter-rate conversion pipe;
-// * clamping after the rounding add, on the bit pattern: the pattern of a float is monotonic in
-//   its value, so min / max against (magic + bound) clamp every finite input, also those outside
-//   the range in which the rounding add is exact; rounding and clamping commute because the bounds
-//   are integers.  `ub` = upper bound (127, or rne(min(alpha, 127)) for ReLU6).
+// * rounding by adding 1.5 * 2^23 AFTER the clamp to [-127, 127] (rounding and clamping commute because
+//   the bounds are integers; the add is exact only inside that range, and clamping the bit pattern
+//   afterwards instead would need an integer subtraction that overflows for v in (-2^24.6, -2^23.6)).
 constexpr int kMagicBits = 0x4B400000;  // bit pattern of kRoundMagic
 
 template <int ACT>
-__device__ __forceinline__ uint32_t clamp_rounded(float t, int ub) {
-  const int b = __float_as_int(t);
-  if (ACT == PLB_ACT_RELU) return static_cast<uint32_t>(__viaddmin_s32_relu(b, -kMagicBits, ub));  // ub = 127 >= 0
-  if (ACT == PLB_ACT_RELU6) return static_cast<uint32_t>(min(__viaddmax_s32(b, -kMagicBits, 0), ub));
-  return static_cast<uint32_t>(max(__viaddmin_s32(b, -kMagicBits, 127), -127));
+__device__ __forceinline__ float clamp_act(float v, float alpha, float ub) {
+  if (ACT == PLB_ACT_NONE) return fminf(fmaxf(v, -127.f), 127.f);
+  if (ACT == PLB_ACT_RELU) return fminf(fmaxf(v, 0.f), 127.f);
+  if (ACT == PLB_ACT_RELU6) return fminf(fmaxf(v, 0.f), ub);  // ub = alpha limited to [-127, 127]
+  v = v <= 0.f ? alpha * v : v;
+  return fminf(fmaxf(v, -127.f), 127.f);
 }
 
 template <int ACT, bool SMALL>
 __device__ __forceinline__ uint32_t quant4(const uint32_t* r, const float4 sc, const float4 bi, const float alpha,
-                                           const int ub) {
+                                           const float ub) {
   float2 f01, f23;
   if (SMALL) {
     const float2 nm = make_float2(-kRoundMagic, -kRoundMagic);
@@ -343,23 +343,17 @@ __device__ __forceinline__ uint32_t quant4(const uint32_t* r, const float4 sc, c
     f01 = make_float2(__int2float_rn(static_cast<int>(r[0])), __int2float_rn(static_cast<int>(r[1])));
     f23 = make_float2(__int2float_rn(static_cast<int>(r[2])), __int2float_rn(static_cast<int>(r[3])));
   }
-  float2 v01 = __ffma2_rn(f01, make_float2(sc.x, sc.y), make_float2(bi.x, bi.y));
-  float2 v23 = __ffma2_rn(f23, make_float2(sc.z, sc.w), make_float2(bi.z, bi.w));
-  if (ACT == PLB_ACT_LEAKY) {
-    v01.x = v01.x <= 0.f ? alpha * v01.x : v01.x;
-    v01.y = v01.y <= 0.f ? alpha * v01.y : v01.y;
-    v23.x = v23.x <= 0.f ? alpha * v23.x : v23.x;
-    v23.y = v23.y <= 0.f ? alpha * v23.y : v23.y;
-  }
+  const float2 v01 = __ffma2_rn(f01, make_float2(sc.x, sc.y), make_float2(bi.x, bi.y));
+  const float2 v23 = __ffma2_rn(f23, make_float2(sc.z, sc.w), make_float2(bi.z, bi.w));
   const float2 m2 = make_float2(kRoundMagic, kRoundMagic);
-  const float2 t01 = __fadd2_rn(v01, m2), t23 = __fadd2_rn(v23, m2);
-  return pack_low_bytes(clamp_rounded<ACT>(t01.x, ub), clamp_rounded<ACT>(t01.y, ub), clamp_rounded<ACT>(t23.x, ub),
-                        clamp_rounded<ACT>(t23.y, ub));
+  const float2 t01 = __fadd2_rn(make_float2(clamp_act<ACT>(v01.x, alpha, ub), clamp_act<ACT>(v01.y, alpha, ub)), m2);
+  const float2 t23 = __fadd2_rn(make_float2(clamp_act<ACT>(v23.x, alpha, ub), clamp_act<ACT>(v23.y, alpha, ub)), m2);
+  return pack_low_bytes(__float_as_uint(t01.x), __float_as_uint(t01.y), __float_as_uint(t23.x), __float_as_uint(t23.y));
 }
 
 template <int ACT>
-__device__ __forceinline__ int quant_upper_bound(float alpha) {
-  return ACT == PLB_ACT_RELU6 ? __float2int_rn(fminf(alpha, 127.f)) : 127;
+__device__ __forceinline__ float quant_upper_bound(float alpha) {
+  return ACT == PLB_ACT_RELU6 ? fmaxf(fminf(alpha, 127.f), -127.f) : 127.f;  // a (senseless) negative bound still ends in [-127, 127]
 }
 
 // 256-bit global accesses: one full 32-byte sector per lane and instruction
@@ -427,7 +421,7 @@ __device__ __forceinline__ void epilogue_store32(const IgemmArgs& a, const uint3
   const float4* sc4 = reinterpret_cast<const float4*>(a.scale + col);
   const float4* bi4 = reinterpret_cast<const float4*>(a.bias + col);
   if (MODE == OUT_I8) {
-    const int ub = quant_upper_bound<ACT>(a.alpha);
+    const float ub = quant_upper_bound<ACT>(a.alpha);
     uint32_t q[8];
     if (a.acc_small) {
 #pragma unroll
@@ -602,7 +596,7 @@ __device__ __forceinline__ void epilogue_chunk_staged(const IgemmArgs& a, const 
   }
   uint32_t q[8];
   if (MODE == OUT_I8) {
-    const int ub = quant_upper_bound<ACT>(a.alpha);
+    const float ub = quant_upper_bound<ACT>(a.alpha);
     if (a.acc_small) {
 #pragma unroll
       for (int j = 0; j < 8; ++j) q[j] = quant4<ACT, true>(&r[4 * j], sc4[j], bi4[j], a.alpha, ub);

@@ -272,7 +272,7 @@ __global__ void __launch_bounds__(kBlock)
 
   const float4 sc = *reinterpret_cast<const float4*>(o.scale + c0);
   const float4 bi = *reinterpret_cast<const float4*>(o.bias + c0);
-  const float alpha = OUT_IS_I8 && ACT == PLB_ACT_RELU6 ? fminf(o.alpha, 127.f) : o.alpha;
+  const float alpha = OUT_IS_I8 && ACT == PLB_ACT_RELU6 ? fmaxf(fminf(o.alpha, 127.f), -127.f) : o.alpha;
 #pragma unroll
   for (int oy = 0; oy < TH; ++oy) {
     const int oh = oh0 + oy;
@@ -331,19 +331,10 @@ DwKernel pick_dw_act(int act) {
 
 constexpr int kDwMagic = 0x4B400000;
 
-// clamp(rounded value, act bounds) on the bit pattern of (value + 1.5*2^23); ub = 127, or rne(min(alpha, 127)) for ReLU6
-template <int ACT>
-__device__ __forceinline__ uint32_t dw_clamp(float t, int ub) {
-  const int b = __float_as_int(t);
-  if (ACT == PLB_ACT_RELU) return static_cast<uint32_t>(__viaddmin_s32_relu(b, -kDwMagic, ub));
-  if (ACT == PLB_ACT_RELU6) return static_cast<uint32_t>(min(__viaddmax_s32(b, -kDwMagic, 0), ub));
-  return static_cast<uint32_t>(max(__viaddmin_s32(b, -kDwMagic, 127), -127));
-}
-
 // fp32 work is done two channels at a time with the packed f32x2 instructions (same IEEE results per lane).
 template <int ACT, bool OUT_IS_I8>
 __device__ __forceinline__ void dw_emit_row(int (&a)[4][4], const float4 sc, const float4 bi, const float alpha,
-                                            const int ub, void* __restrict__ y, const long yoff, const int ldy,
+                                            const float ub, void* __restrict__ y, const long yoff, const int ldy,
                                             const int ncols) {
   const float2 magic = make_float2(12582912.f, 12582912.f), neg_magic = make_float2(-12582912.f, -12582912.f);
 #pragma unroll
@@ -357,16 +348,20 @@ __device__ __forceinline__ void dw_emit_row(int (&a)[4][4], const float4 sc, con
     for (int c = 0; c < 4; ++c) a[ox][c] = kDwMagic;
     if (ox >= ncols) continue;
     if (OUT_IS_I8) {
-      if (ACT == PLB_ACT_LEAKY) {
 #pragma unroll
-        for (int c = 0; c < 4; ++c) v[c] = v[c] <= 0.f ? alpha * v[c] : v[c];
+      for (int c = 0; c < 4; ++c) {
+        float t = v[c];
+        if (ACT == PLB_ACT_NONE) t = fminf(fmaxf(t, -127.f), 127.f);
+        else if (ACT == PLB_ACT_RELU) t = fminf(fmaxf(t, 0.f), 127.f);
+        else if (ACT == PLB_ACT_RELU6) t = fminf(fmaxf(t, 0.f), ub);
+        else { t = t <= 0.f ? alpha * t : t; t = fminf(fmaxf(t, -127.f), 127.f); }
+        v[c] = t;
       }
-      // + 1.5*2^23 rounds to nearest even; the clamp then works on the bit pattern (monotonic in the
-      // value, so it also catches inputs outside the range in which the rounding add is exact)
+      // + 1.5*2^23 (after the clamp, where the add is exact): round to nearest even, result in the low byte
       const float2 q01 = __fadd2_rn(make_float2(v[0], v[1]), magic), q23 = __fadd2_rn(make_float2(v[2], v[3]), magic);
       *reinterpret_cast<uint32_t*>(static_cast<int8_t*>(y) + yoff + static_cast<long>(ox) * ldy) =
-          __byte_perm(__byte_perm(dw_clamp<ACT>(q01.x, ub), dw_clamp<ACT>(q01.y, ub), 0x0040),
-                      __byte_perm(dw_clamp<ACT>(q23.x, ub), dw_clamp<ACT>(q23.y, ub), 0x0040), 0x5410);
+          __byte_perm(__byte_perm(__float_as_uint(q01.x), __float_as_uint(q01.y), 0x0040),
+                      __byte_perm(__float_as_uint(q23.x), __float_as_uint(q23.y), 0x0040), 0x5410);
     } else {
       *reinterpret_cast<float4*>(static_cast<float*>(y) + yoff + static_cast<long>(ox) * ldy) =
           make_float4(dw_act<ACT>(v[0], alpha), dw_act<ACT>(v[1], alpha), dw_act<ACT>(v[2], alpha),
@@ -456,7 +451,7 @@ __global__ void __launch_bounds__(kDwBlock, 4)
   const float4 sc = *reinterpret_cast<const float4*>(o.scale + c0);
   const float4 bi = *reinterpret_cast<const float4*>(o.bias + c0);
   const float alpha = o.alpha;
-  const int ub = ACT == PLB_ACT_RELU6 ? __float2int_rn(fminf(o.alpha, 127.f)) : 127;
+  const float ub = ACT == PLB_ACT_RELU6 ? fmaxf(fminf(o.alpha, 127.f), -127.f) : 127.f;
 
   const int ih0 = oh0 * S - g.pad_t, iw0 = ow0 * S - g.pad_l;
   uint32_t colmask = 0;

@@ -349,3 +349,40 @@ def test_random_depthwise(plb, ctx, case):
     xq, in_s, wq, ws, bias = conv_case(hash(case) % 10000, n, c, h, w, c, k, groups=c, w_std=0.3)
     run_case(plb, ctx, xq, in_s, wq, ws, bias, stride=(s, s), pads=(p, p, p, p), groups=c, act=act,
              alpha=6.0 if act == 2 else 0.1)
+
+
+@pytest.mark.parametrize("strip", ["0", "1", "3", "4", "7", "32"])
+@pytest.mark.parametrize("shape", [(2, 32, 13, 17, 1, 1, 1), (1, 64, 29, 9, 2, 1, 2), (3, 8, 7, 7, 1, 0, 3),
+                                   (1, 128, 14, 14, 2, 1, 0), (1, 24, 5, 33, 1, 2, 1)],
+                         ids=lambda s: "n%dc%dh%dw%ds%dp%da%d" % s)
+def test_depthwise_strip_heights(plb, ctx, shape, strip, monkeypatch):
+    """Depthwise 3x3 through the column-strip kernel with forced strip heights (ragged last strip,
+    strips shorter than the filter, one strip for the whole image) and through the register-tiled
+    kernel it replaced ("0"): all bit-identical to the oracle."""
+    monkeypatch.setenv("PLB_DW_STRIP", strip)
+    n, c, h, w, s, p, act = shape
+    xq, in_s, wq, ws, bias = conv_case(4242 + h * w + c, n, c, h, w, c, 3, groups=c, w_std=0.3)
+    run_case(plb, ctx, xq, in_s, wq, ws, bias, stride=(s, s), pads=(p, p, p, p), groups=c, act=act,
+             alpha=6.0 if act == 2 else 0.1)
+
+
+@pytest.mark.parametrize("act,alpha", [(0, 0.0), (1, 0.0), (2, 6.0), (2, 1e9), (2, -3.0), (3, 0.1), (3, -2.5)])
+def test_requantiser_extremes(plb, ctx, act, alpha):
+    """int8 outputs whose pre-clamp values leave the range in which the rounding add is exact
+    (|v| up to 2^27 through a large scale), for every activation, odd ReLU6 bounds included; the
+    tensor-core path (1x1, 64 channels: small-accumulator conversion) and the depthwise path."""
+    rng = np.random.default_rng(17)
+    for groups, cin, k in ((1, 64, 1), (64, 64, 3)):
+        xq = rng.integers(-127, 128, (2, cin, 9, 11), dtype=np.int8)
+        wq = rng.integers(-127, 128, (64, cin // groups, k, k), dtype=np.int8)
+        ws = np.full(64, 1.0, np.float32)
+        ws[::3] = 1e-4
+        bias = rng.standard_normal(64).astype(np.float32) * 100
+        kw = dict(stride=(1, 1), pads=(k // 2,) * 4, groups=groups)
+        acc_ref = O.conv_acc_i32(xq, wq, **kw)
+        for out_s in (1.0, 1e-3, 37.5):
+            q_ref = O.epilogue(acc_ref, ws, 0.5, bias, act, alpha, out_scale=out_s)
+            conv8 = plb.Conv(ctx, wq, ws, 0.5, bias, in_hw=xq.shape[2:], act=act, alpha=alpha, out_scale=out_s, **kw)
+            q = conv8.run(dev(xq))
+            ctx.sync()
+            assert np.array_equal(q.cpu().numpy(), q_ref), "groups %d out_scale %g" % (groups, out_s)
