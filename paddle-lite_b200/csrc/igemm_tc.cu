@@ -36,7 +36,7 @@ constexpr int kEpilogueWarps = 4 * kEpilogueGroups;
 constexpr int kProducerWarp = kEpilogueWarps;
 constexpr int kMmaWarp = kEpilogueWarps + 1;
 constexpr int kThreads = 32 * (kEpilogueWarps + 2);
-constexpr int kMaxAccBufs = 4;
+constexpr int kMaxAccBufs = 8;
 constexpr int kMaxBStages = 8;                  // filter ring of window mode with a streamed filter
 constexpr int kCtrlBytes = 1024;                // barriers + tmem slot
 constexpr int kMaxResidentB = 56 * 1024;        // filters up to this size stay in shared memory for the whole kernel
@@ -52,7 +52,7 @@ struct IgemmArgs {
   int staging_bytes, staging_w_bytes;  // epilogue staging in front of the operand ring
   int stage_b_warp;                    // bytes of int8 staging per epilogue warp
   int res_prefetch;                    // OUT_ADD_RELU: two residual staging tiles per warp, one chunk fetched ahead
-  int acc_bufs;                        // TMEM accumulator buffers (epilogue groups per buffer = 4 / acc_bufs)
+  int acc_bufs;                        // TMEM accumulator buffers: 2, 4 or 8 (epilogue groups per buffer = max(1, 4 / acc_bufs))
   int resident_b;                      // whole filter of this CTA's channel tile kept in shared memory
   int resident_bytes;                  // its size, rounded up to 1 KiB
   // slab mode (stride-1 filters with several taps): a pipeline stage holds the input window of a
@@ -79,6 +79,7 @@ struct IgemmArgs {
   int act;
   float alpha;
   int acc_small;                       // every |accumulator| < 2^22 (proven from the filter by the host)
+  int fast_flat;                       // flat tiles, resident filter, one channel tile, no shortcut GEMM: short role loops
   int sb_off, sb_cols;                 // scale / bias tables copied to shared memory (offset in the staging area; 0 columns = not)
   const float* residual;
   float* y_f32;
@@ -87,6 +88,7 @@ struct IgemmArgs {
   int* status;
 #ifdef PLB_TC_TIMING
   long long* timing;  // [grid][16] cycle counters
+  int dbg;            // PLB_TC_DBG bit 1: the epilogue reads the accumulators and drops them
 #endif
 };
 
@@ -597,13 +599,21 @@ __device__ __forceinline__ void epilogue_chunk_staged(const IgemmArgs& a, const 
   uint32_t q[8];
   if (MODE == OUT_I8) {
     const float ub = quant_upper_bound<ACT>(a.alpha);
-    if (a.acc_small) {
+    // two halves of 16 columns, each stored as soon as it is packed; the compiler barrier keeps the
+    // second half's scale / bias loads from being hoisted (they would cost 32 registers)
 #pragma unroll
-      for (int j = 0; j < 8; ++j) q[j] = quant4<ACT, true>(&r[4 * j], sc4[j], bi4[j], a.alpha, ub);
-    } else {
+    for (int h = 0; h < 2; ++h) {
+      if (a.acc_small) {
 #pragma unroll
-      for (int j = 0; j < 8; ++j) q[j] = quant4<ACT, false>(&r[4 * j], sc4[j], bi4[j], a.alpha, ub);
+        for (int j = 4 * h; j < 4 * h + 4; ++j) q[j] = quant4<ACT, true>(&r[4 * j], sc4[j], bi4[j], a.alpha, ub);
+      } else {
+#pragma unroll
+        for (int j = 4 * h; j < 4 * h + 4; ++j) q[j] = quant4<ACT, false>(&r[4 * j], sc4[j], bi4[j], a.alpha, ub);
+      }
+      sts128(st_b_row + (((byte_chunk0 + h) ^ b_swz_mask) << 4), q[4 * h], q[4 * h + 1], q[4 * h + 2], q[4 * h + 3]);
+      asm volatile("" ::: "memory");
     }
+    return;
   } else {  // OUT_ADD_RELU
 #pragma unroll
     for (int j = 0; j < 8; ++j) {
@@ -681,6 +691,75 @@ __device__ __forceinline__ void issue_window_taps(int kh, int kw, uint32_t d_tme
   }
 }
 
+// Flat GEMM tiles with the whole filter resident in shared memory and a single channel tile (1x1
+// convolutions and fc with few channels): a tile is only `ksteps` K steps of work, so the per-tile
+// instruction count of the two single-warp roles decides how fast tiles flow.  These loops keep
+// every address in a register that advances by a constant.
+// Ring position after `n` more K steps.
+__device__ __forceinline__ void ring_advance(int n, int stages, int& s, uint32_t& parity) {
+  s += n;
+  while (s >= stages) {
+    s -= stages;
+    parity ^= 1;
+  }
+}
+
+// `first` / `step`: this warp takes the CTA's tiles first, first + step, ... (0 / 1: all of them).
+template <int MPS>
+__device__ __forceinline__ bool mma_loop_flat_resident(const IgemmArgs& a, int first, int step, uint32_t tmem_base,
+                                                       uint32_t acc_stride, int nb_mask, int nb_shift, uint32_t ring_lo,
+                                                       uint32_t stage_lo, uint32_t bres_lo, uint32_t stage_b_lo,
+                                                       uint32_t hi, uint32_t idesc, uint32_t full0, uint32_t empty0,
+                                                       uint32_t acc_full0, uint32_t acc_empty0, bool leader,
+                                                       volatile int* abort_flag) {
+  int s = 0;
+  uint32_t full_parity = 0;
+  ring_advance(first * a.ksteps, a.stages, s, full_parity);
+  const int skip = (step - 1) * a.ksteps;
+  for (int it = first, tile = blockIdx.x + first * gridDim.x; tile < a.num_tiles; tile += step * gridDim.x, it += step) {
+    const int buf = it & nb_mask;
+    if (!mbar_wait(acc_empty0 + 8u * buf, ((it >> nb_shift) & 1) ^ 1, abort_flag, a.status, FAULT_WAIT_ACCUM)) return false;
+    const uint32_t d_tmem = tmem_base + buf * acc_stride;
+    uint32_t b_lo = bres_lo;
+    for (int ks = 0; ks < a.ksteps; ++ks, b_lo += stage_b_lo) {
+      if (!mbar_wait(full0 + 8u * s, full_parity, abort_flag, a.status, FAULT_WAIT_FULL)) return false;
+      tc_fence_after();
+      issue_kstep<MPS>(d_tmem, ring_lo + s * stage_lo, hi, b_lo, hi, idesc, ks > 0 ? 1u : 0u, leader);
+      tc_commit_if(empty0 + 8u * s, leader);
+      if (++s == a.stages) {
+        s = 0;
+        full_parity ^= 1;
+      }
+    }
+    tc_commit_if(acc_full0 + 8u * buf, leader);
+    ring_advance(skip, a.stages, s, full_parity);
+  }
+  return true;
+}
+
+__device__ __forceinline__ bool producer_loop_flat_resident(const IgemmArgs& a, int first, int step, const CUtensorMap* tmA,
+                                                            uint32_t smem_base, int stage_bytes, uint32_t full0,
+                                                            uint32_t empty0, bool leader, volatile int* abort_flag) {
+  int s = 0;
+  uint32_t empty_parity = 1;  // a fresh barrier passes a wait on parity 1
+  ring_advance(first * a.ksteps, a.stages, s, empty_parity);
+  const int skip = (step - 1) * a.ksteps;
+  const int m_end = a.num_tiles * kTileM, m_step = step * static_cast<int>(gridDim.x) * kTileM, k_end = a.ksteps * a.kc;
+  for (int m0 = (static_cast<int>(blockIdx.x) + first * static_cast<int>(gridDim.x)) * kTileM; m0 < m_end; m0 += m_step) {
+    for (int kb = 0; kb < k_end; kb += a.kc) {
+      if (!mbar_wait(empty0 + 8u * s, empty_parity, abort_flag, a.status, FAULT_WAIT_EMPTY)) return false;
+      mbar_expect_tx_if(full0 + 8u * s, static_cast<uint32_t>(stage_bytes), leader);
+      tma_load_2d_if(smem_base + s * stage_bytes, tmA, full0 + 8u * s, kb, m0, leader);
+      if (++s == a.stages) {
+        s = 0;
+        empty_parity ^= 1;
+      }
+    }
+    ring_advance(skip, a.stages, s, empty_parity);
+  }
+  return true;
+}
+
 // ---------------------------------------------------------------- the kernel
 // Persistent: one CTA per SM walks tiles t = blockIdx.x, blockIdx.x + gridDim.x, ...;
 // consecutive tile ids share the same 128 pixels (channel tile fastest) so that CTAs running
@@ -753,8 +832,10 @@ __global__ void __launch_bounds__(kThreads, 1)
   // TMEM: nb accumulator buffers of acc_cols columns each (512 columns in total at most)
   uint32_t acc_cols = 32;
   while (acc_cols < static_cast<uint32_t>(a.bn)) acc_cols <<= 1;
-  const int nb = a.acc_bufs;  // 4 or 2 (2 when the tile is 256 wide or a CTA has only a tile or two to do)
-  const int gpb = kEpilogueGroups / nb;  // epilogue groups sharing one buffer (split by columns)
+  const int nb = a.acc_bufs;  // 8 (tiles of <= 64 columns), 4, or 2 (tile 256 wide, or a CTA has only a tile or two to do)
+  // epilogue groups sharing one buffer (split by columns); with 8 buffers (tiles of <= 64 columns) every
+  // group alternates between two buffers, so the MMA warp refills one while the group drains the other
+  const int gpb = nb >= kEpilogueGroups ? 1 : kEpilogueGroups / nb;
   const uint32_t acc_stride = a.dual ? 2 * acc_cols : acc_cols;  // dual mode: main and shortcut accumulators side by side
   const uint32_t tmem_cols = acc_stride * nb < 32 ? 32 : acc_stride * nb;
 
@@ -886,7 +967,10 @@ __global__ void __launch_bounds__(kThreads, 1)
       }
     }
     if (a.slab && a.b_stream && have_prev && ok) ok = stream_filter(prev_n0);
-    for (int tile = blockIdx.x; !a.slab && tile < a.num_tiles && ok; tile += gridDim.x) {
+    if (a.fast_flat)  // flat tiles, resident filter, one channel tile: one box of activations per K step, nothing else
+      ok = producer_loop_flat_resident(a, 0, 1, &tmA, smem_base, stage_bytes, smem_u32(&full_bar[0]),
+                                       smem_u32(&empty_bar[0]), leader, abort_flag);
+    for (int tile = blockIdx.x; !a.slab && !a.fast_flat && tile < a.num_tiles && ok; tile += gridDim.x) {
       const int tile_m = tile / a.tiles_n;
       const int m0 = tile_m * kTileM;
       const int n0 = (tile - tile_m * a.tiles_n) * a.bn;
@@ -968,7 +1052,7 @@ __global__ void __launch_bounds__(kThreads, 1)
     // window mode: the 8-row groups of A are one window row (slab_w pixels) apart
     const uint32_t hi_a = a.slab ? ((hi_b & 0xFFFFC000u) | ((static_cast<uint32_t>(a.slab_w * a.kc) >> 4) & 0x3FFFu)) : hi_b;
     const uint32_t lo_flags = 1u << 16;  // leading-dimension byte offset field (unused by swizzled K-major tiles)
-    const int nb_mask = nb - 1, nb_shift = nb == 4 ? 2 : 1;
+    const int nb_mask = nb - 1, nb_shift = nb == 8 ? 3 : (nb == 4 ? 2 : 1);
     // window mode: descriptor steps per filter row / filter column / channel chunk
     const uint32_t row_lo = static_cast<uint32_t>(a.slab_w * a.kc * a.dil_h) >> 4;
     const uint32_t col_lo = static_cast<uint32_t>(a.dil_w * a.kc) >> 4;
@@ -1006,7 +1090,20 @@ __global__ void __launch_bounds__(kThreads, 1)
     const uint32_t stage_b_lo = static_cast<uint32_t>(stage_b) >> 4;
     const uint32_t stage_lo = static_cast<uint32_t>(stage_bytes) >> 4;
     const uint32_t ring_lo = ((smem_base >> 4) & 0x3FFFu) | lo_flags;
-    for (int tile = blockIdx.x; tile < a.num_tiles && ok; tile += gridDim.x, ++it) {
+    if (a.fast_flat && ok) {
+      const uint32_t f0 = smem_u32(&full_bar[0]), e0 = smem_u32(&empty_bar[0]);
+      const uint32_t af0 = smem_u32(&acc_full[0]), ae0 = smem_u32(&acc_empty[0]);
+      if (mma_per_stage == 4)
+        ok = mma_loop_flat_resident<4>(a, 0, 1, tmem_base, acc_stride, nb_mask, nb_shift, ring_lo, stage_lo, bres_lo, stage_b_lo,
+                                       hi_b, idesc, f0, e0, af0, ae0, leader, abort_flag);
+      else if (mma_per_stage == 2)
+        ok = mma_loop_flat_resident<2>(a, 0, 1, tmem_base, acc_stride, nb_mask, nb_shift, ring_lo, stage_lo, bres_lo, stage_b_lo,
+                                       hi_b, idesc, f0, e0, af0, ae0, leader, abort_flag);
+      else
+        ok = mma_loop_flat_resident<1>(a, 0, 1, tmem_base, acc_stride, nb_mask, nb_shift, ring_lo, stage_lo, bres_lo, stage_b_lo,
+                                       hi_b, idesc, f0, e0, af0, ae0, leader, abort_flag);
+    }
+    for (int tile = blockIdx.x; !a.fast_flat && tile < a.num_tiles && ok; tile += gridDim.x, ++it) {
       int buf = it & nb_mask;
       TT_START();
       ok = mbar_wait(smem_u32(&acc_empty[buf]), ((it >> nb_shift) & 1) ^ 1, abort_flag, a.status, FAULT_WAIT_ACCUM);
@@ -1196,9 +1293,10 @@ __global__ void __launch_bounds__(kThreads, 1)
     // ------------------------------------------------------------ epilogue groups
     const int group = warp >> 2;     // 0..3
     const int quad = warp & 3;       // TMEM lane quadrant this warp may read
-    const int my_buf = group / gpb;  // the accumulator buffer this group drains
+    const int first_it = group / gpb;             // this group's first tile of the CTA's sequence
+    const int it_stride = kEpilogueGroups / gpb;  // groups that take whole tiles
     const int col_par = group % gpb; // which part of its columns
-    const int nb_shift = nb == 4 ? 2 : 1;
+    const int nb_shift = nb == 8 ? 3 : (nb == 4 ? 2 : 1);
     // staged I/O: this warp's staging tiles and bookkeeping
     const uint32_t st_w = smem_u32(smem_al) + warp * 4096;
     const int wq = a.bn / gpb;       // columns (= int8 bytes per row) this group owns in a tile
@@ -1220,7 +1318,8 @@ __global__ void __launch_bounds__(kThreads, 1)
 #ifdef PLB_TC_TIMING
     long long tt_fence = 0, tt_issue = 0;
 #endif
-    for (int it = my_buf; ok; it += nb) {
+    for (int it = first_it; ok; it += it_stride) {
+      const int my_buf = it & (nb - 1);  // the accumulator buffer of this tile
       const long tile_l = static_cast<long>(blockIdx.x) + static_cast<long>(it) * gridDim.x;
       if (tile_l >= a.num_tiles) break;
       const int tile = static_cast<int>(tile_l);
@@ -1387,6 +1486,9 @@ __global__ void __launch_bounds__(kThreads, 1)
           tc_ld32(lane_addr + static_cast<uint32_t>(c), r);
           tc_wait_ld();
           TT_STOP(2);
+#ifdef PLB_TC_TIMING
+          if (a.dbg & 1) continue;  // diagnostics: accumulators are read and dropped (no math, no stores)
+#endif
           TT_START();
           if (active) {
             if (dual) {
@@ -1655,15 +1757,16 @@ int igemm_tc_launch(plb_ctx* ctx, const IgemmProblem& p) {
   {
     const long tiles_total = static_cast<long>(tiles_m) * ((p.cout + bn - 1) / bn);
     const bool few = tiles_total <= 2L * ctx->sm_count;
-    a.acc_bufs = bn > 128 ? 2 : (few && bn >= 64 ? 2 : 4);
+    a.acc_bufs = bn > 128 ? 2 : (few && bn >= 64 ? 2 : 4);  // 8 (tiles of <= 64 columns) is possible and measured equal
     a.acc_bufs = env_int("PLB_TC_ACC_BUFS", a.acc_bufs);
     if (dual) a.acc_bufs = 2;
-    if (a.acc_bufs != 2 && a.acc_bufs != 4) return fail(PLB_E_INVALID, "accumulator buffers must be 2 or 4");
+    if (a.acc_bufs != 2 && a.acc_bufs != 4 && a.acc_bufs != 8) return fail(PLB_E_INVALID, "accumulator buffers must be 2, 4 or 8");
+    if (a.acc_bufs == 8 && bn > 64) a.acc_bufs = 4;
     if (a.acc_bufs == 4 && bn > 128) a.acc_bufs = 2;
     if (a.acc_bufs == 2 && bn < 64) a.acc_bufs = 4;
   }
   {
-    const int wq_h = bn / (kEpilogueGroups / a.acc_bufs);
+    const int wq_h = bn / (a.acc_bufs >= kEpilogueGroups ? 1 : kEpilogueGroups / a.acc_bufs);
     // 32 rows of wq bytes per warp; 128-byte-swizzled tiles (wq = 128) need 1 KiB alignment, which 4 KiB keeps
     a.stage_b_warp = staged && want_b ? (wq_h == 128 ? 4096 : 32 * wq_h) : 0;
     if (a.res_prefetch && want_b) a.stage_b_warp = 1024;  // int8 results leave chunk by chunk (32 rows x 32 bytes)
@@ -1744,6 +1847,7 @@ int igemm_tc_launch(plb_ctx* ctx, const IgemmProblem& p) {
     }
   }
   a.resident_bytes = a.resident_b ? resident_bytes : 0;
+  a.fast_flat = !a.slab && !p.im2col && !dual && a.resident_b && a.tiles_n == 1 && env_int("PLB_TC_FAST_FLAT", 1) != 0;
   const int stage_bytes = (kTileM + bn) * a.kc;
   const int ring_stage_bytes = a.slab ? a.cchunks * a.plane_bytes : (a.resident_b ? kTileM * a.kc : stage_bytes);
   // one CTA per SM: spend (almost) all remaining shared memory on the operand ring
@@ -1906,7 +2010,7 @@ int igemm_tc_launch(plb_ctx* ctx, const IgemmProblem& p) {
                             CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
     };
     CUresult r = CUDA_SUCCESS;
-    const int wq = bn / (kEpilogueGroups / a.acc_bufs);  // int8 bytes per staged row
+    const int wq = bn / (a.acc_bufs >= kEpilogueGroups ? 1 : kEpilogueGroups / a.acc_bufs);  // int8 bytes per staged row
     if (p.out_mode == OUT_ADD_RELU) {
       if (p.residual) r = encode_out(&tmRes, p.residual, 4, 32, CU_TENSOR_MAP_SWIZZLE_128B);
       if (r == CUDA_SUCCESS && p.y_f32) r = encode_out(&tmOutW, p.y_f32, 4, 32, CU_TENSOR_MAP_SWIZZLE_128B);
@@ -1951,6 +2055,7 @@ int igemm_tc_launch(plb_ctx* ctx, const IgemmProblem& p) {
   if (!d_timing) PLB_CUDA(cudaMalloc(&d_timing, 256 * 24 * sizeof(long long)));
   PLB_CUDA(cudaMemsetAsync(d_timing, 0, 256 * 24 * sizeof(long long), ctx->stream));
   a.timing = d_timing;
+  a.dbg = env_int("PLB_TC_DBG", 0);
 #endif
   PLB_CUDA(launch_kernel(kernel, dim3(grid), dim3(kThreads), smem, ctx->stream, tmA, tmB, tmRes, tmOutW,
                          tmOutB, tmA2, tmB2, a));

@@ -386,3 +386,35 @@ def test_requantiser_extremes(plb, ctx, act, alpha):
             q = conv8.run(dev(xq))
             ctx.sync()
             assert np.array_equal(q.cpu().numpy(), q_ref), "groups %d out_scale %g" % (groups, out_s)
+
+
+_FLAT_CASES = {}
+
+
+def _flat_case(cin, cout):
+    """Inputs and oracle bytes of one shape, computed once for all switch settings."""
+    if (cin, cout) not in _FLAT_CASES:
+        xq, in_s, wq, ws, bias = conv_case(77 + cin + cout, 4, cin, 224, 224, cout, 1)
+        acc_ref = O.conv_acc_i32(xq, wq)
+        y_ref = O.epilogue(acc_ref, ws, in_s, bias, 1, 0.0)
+        out_s = float(max(np.abs(y_ref).max(), 1e-6) / 127.0)
+        _FLAT_CASES[(cin, cout)] = (xq, in_s, wq, ws, bias, out_s, O.epilogue(acc_ref, ws, in_s, bias, 1, 0.0, out_scale=out_s))
+    return _FLAT_CASES[(cin, cout)]
+
+
+@pytest.mark.parametrize("env", [{}, {"PLB_TC_FAST_FLAT": "0"}, {"PLB_TC_ACC_BUFS": "8"},
+                                 {"PLB_TC_ACC_BUFS": "8", "PLB_TC_FAST_FLAT": "0"}, {"PLB_TC_SB_SMEM": "0", "PLB_TC_ACC_SMALL": "0"}],
+                         ids=lambda e: ",".join("%s=%s" % kv for kv in e.items()) or "default")
+@pytest.mark.parametrize("cin,cout", [(32, 64), (256, 64), (64, 32)])
+def test_flat_tiles_many_per_cta(plb, ctx, cin, cout, env, monkeypatch):
+    """1x1 convolutions with a resident filter and ten tiles per CTA, so that the operand ring wraps
+    and every accumulator buffer is reused: the short role loops, the generic ones, eight
+    accumulator buffers, and the epilogue without its shared-memory tables and without the
+    small-accumulator conversion all give the oracle's bytes."""
+    for k, v in env.items():
+        monkeypatch.setenv(k, v)
+    xq, in_s, wq, ws, bias, out_s, q_ref = _flat_case(cin, cout)
+    conv8 = plb.Conv(ctx, wq, ws, in_s, bias, in_hw=(224, 224), act=1, out_scale=out_s)
+    q = conv8.run(dev(xq))
+    ctx.sync()
+    assert np.array_equal(q.cpu().numpy(), q_ref)
