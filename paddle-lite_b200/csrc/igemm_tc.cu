@@ -1318,13 +1318,15 @@ __global__ void __launch_bounds__(kThreads, 1)
 #ifdef PLB_TC_TIMING
     long long tt_fence = 0, tt_issue = 0;
 #endif
+    // one channel tile (flat 1x1 layers with few channels, where a tile is little work): no divisions per tile
+    const bool one_n = MODE != OUT_ADD_RELU && !a.slab && a.tiles_n == 1;
     for (int it = first_it; ok; it += it_stride) {
       const int my_buf = it & (nb - 1);  // the accumulator buffer of this tile
       const long tile_l = static_cast<long>(blockIdx.x) + static_cast<long>(it) * gridDim.x;
       if (tile_l >= a.num_tiles) break;
       const int tile = static_cast<int>(tile_l);
-      const int m0 = (tile / a.tiles_n) * kTileM;
-      const int n0 = (tile % a.tiles_n) * a.bn;
+      const int m0 = (one_n ? tile : tile / a.tiles_n) * kTileM;
+      const int n0 = one_n ? 0 : (tile % a.tiles_n) * a.bn;
       const long row = static_cast<long>(m0) + quad * 32 + lane;
       const uint32_t lane_addr = tmem_base + my_buf * acc_stride + (static_cast<uint32_t>(quad * 32) << 16);
       bool waited = false;
