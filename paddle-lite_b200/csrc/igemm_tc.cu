@@ -805,22 +805,14 @@ __global__ void __launch_bounds__(kThreads, 1)
   const int lane = threadIdx.x & 31;
 
   // Per-channel scale and bias of all output channels in shared memory: an epilogue chunk then
-  // reads them with broadcast shared loads instead of waiting for L2 (the tables are layer
-  // constants, not written by the preceding kernel, so they are copied before the wait for it).
+  // reads them with broadcast shared loads instead of waiting for L2.  The epilogue warps copy the
+  // tables at the start of their role (see there), off the path of the producer and MMA warps.
   const float* ep_scale = a.scale;
   const float* ep_bias = a.bias;
   const float* ep_scale2 = a.scale2;
   const float* ep_bias2 = a.bias2;
   if (a.sb_cols > 0) {
     float* sb = reinterpret_cast<float*>(smem_al + a.sb_off);
-    for (int i = threadIdx.x; i < a.sb_cols; i += kThreads) {
-      sb[i] = __ldg(a.scale + i);
-      sb[a.sb_cols + i] = __ldg(a.bias + i);
-      if (a.dual) {
-        sb[2 * a.sb_cols + i] = __ldg(a.scale2 + i);
-        sb[3 * a.sb_cols + i] = __ldg(a.bias2 + i);
-      }
-    }
     ep_scale = sb;
     ep_bias = sb + a.sb_cols;
     if (a.dual) {
@@ -1291,6 +1283,21 @@ __global__ void __launch_bounds__(kThreads, 1)
 #endif
   } else {
     // ------------------------------------------------------------ epilogue groups
+    if (a.sb_cols > 0) {
+      // The tables are layer constants (not written by the preceding kernel).  Only the epilogue warps
+      // need them, and long after this point, so the copy costs the other roles nothing; all 16 epilogue
+      // warps reach this barrier exactly once, before any of their exits.
+      float* sb = reinterpret_cast<float*>(smem_al + a.sb_off);
+      for (int i = threadIdx.x; i < a.sb_cols; i += 32 * kEpilogueWarps) {
+        sb[i] = __ldg(a.scale + i);
+        sb[a.sb_cols + i] = __ldg(a.bias + i);
+        if (a.dual) {
+          sb[2 * a.sb_cols + i] = __ldg(a.scale2 + i);
+          sb[3 * a.sb_cols + i] = __ldg(a.bias2 + i);
+        }
+      }
+      asm volatile("bar.sync 1, %0;" ::"n"(32 * kEpilogueWarps) : "memory");
+    }
     const int group = warp >> 2;     // 0..3
     const int quad = warp & 3;       // TMEM lane quadrant this warp may read
     const int first_it = group / gpb;             // this group's first tile of the CTA's sequence
