@@ -484,6 +484,8 @@ __global__ void __launch_bounds__(kDwBlock, 4)
       dw_load_raw<1>(xrow, cs, P < in_rows && static_cast<unsigned>(ih0 + P) < static_cast<unsigned>(g.h), colmask, cur[P]);
       xrow += row_step;
     }
+    // unrolled by two: the copy of the prefetched rows into the current ones becomes a renaming
+#pragma unroll 2
     for (int iy = 0; iy < in_rows; iy += 3) {
 #pragma unroll
       for (int P = 0; P < 3; ++P) {
