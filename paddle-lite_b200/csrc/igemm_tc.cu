@@ -79,6 +79,7 @@ struct IgemmArgs {
   int act;
   float alpha;
   int acc_small;                       // every |accumulator| < 2^22 (proven from the filter by the host)
+  int fast_window;                     // window tiles of a row-folded stem layer (shapes 4x1 / 2x1, two MMAs per tap): short role loops
   int fast_flat;                       // flat tiles, resident filter, one channel tile, no shortcut GEMM: short role loops
   int sb_off, sb_cols;                 // scale / bias tables copied to shared memory (offset in the staging area; 0 columns = not)
   const float* residual;
@@ -760,6 +761,70 @@ __device__ __forceinline__ bool producer_loop_flat_resident(const IgemmArgs& a, 
   return true;
 }
 
+// Window-mode tiles of the row-folded stem layers (a handful of MMAs per tile, resident filter, one
+// channel tile, one window box per tile): the same short loops as for flat tiles.  The window position
+// (tx, ty, image) advances by the decomposition of gridDim.x with carries instead of divisions.
+__device__ __forceinline__ bool producer_loop_window_resident(const IgemmArgs& a, const CUtensorMap* tmA, uint32_t smem_base,
+                                                              int stage_bytes, uint32_t full0, uint32_t empty0, bool leader,
+                                                              volatile int* abort_flag) {
+  int s = 0;
+  uint32_t empty_parity = 1;
+  int tx = static_cast<int>(blockIdx.x) % a.tiles_x;
+  int ty = (static_cast<int>(blockIdx.x) / a.tiles_x) % a.tiles_y;
+  int img = (static_cast<int>(blockIdx.x) / a.tiles_x) / a.tiles_y;
+  const int dtx = static_cast<int>(gridDim.x) % a.tiles_x;
+  const int dty = (static_cast<int>(gridDim.x) / a.tiles_x) % a.tiles_y;
+  const int dimg = (static_cast<int>(gridDim.x) / a.tiles_x) / a.tiles_y;
+  const uint32_t bytes = static_cast<uint32_t>(a.slab_rows * a.kc);
+  for (int tile = blockIdx.x; tile < a.num_tiles; tile += gridDim.x) {
+    if (!mbar_wait(empty0 + 8u * s, empty_parity, abort_flag, a.status, FAULT_WAIT_EMPTY)) return false;
+    mbar_expect_tx_if(full0 + 8u * s, bytes, leader);
+    tma_load_4d_if(smem_base + s * stage_bytes, tmA, full0 + 8u * s, 0, tx * 8 - a.pad_l, ty * 16 - a.pad_t, img, leader);
+    if (++s == a.stages) {
+      s = 0;
+      empty_parity ^= 1;
+    }
+    tx += dtx;
+    ty += dty;
+    img += dimg;
+    if (tx >= a.tiles_x) {
+      tx -= a.tiles_x;
+      ++ty;
+    }
+    if (ty >= a.tiles_y) {
+      ty -= a.tiles_y;
+      ++img;
+    }
+  }
+  return true;
+}
+
+template <int KH, int KW, int MPS>
+__device__ __forceinline__ bool mma_loop_window_resident(const IgemmArgs& a, uint32_t tmem_base, uint32_t acc_stride,
+                                                         int nb_mask, int nb_shift, uint32_t ring_lo, uint32_t stage_lo,
+                                                         uint32_t row_lo, uint32_t col_lo, uint32_t hi_a, uint32_t bres_lo,
+                                                         uint32_t stage_b_lo, uint32_t hi_b, uint32_t idesc, uint32_t full0,
+                                                         uint32_t empty0, uint32_t acc_full0, uint32_t acc_empty0,
+                                                         bool leader, volatile int* abort_flag) {
+  int s = 0, it = 0;
+  uint32_t full_parity = 0;
+  for (int tile = blockIdx.x; tile < a.num_tiles; tile += gridDim.x, ++it) {
+    const int buf = it & nb_mask;
+    if (!mbar_wait(acc_empty0 + 8u * buf, ((it >> nb_shift) & 1) ^ 1, abort_flag, a.status, FAULT_WAIT_ACCUM)) return false;
+    if (!mbar_wait(full0 + 8u * s, full_parity, abort_flag, a.status, FAULT_WAIT_FULL)) return false;
+    tc_fence_after();
+    issue_window<KH, KW, 1, MPS>(tmem_base + buf * acc_stride, ring_lo + s * stage_lo, row_lo, col_lo, 0u, hi_a, bres_lo,
+                                 stage_b_lo, hi_b, idesc, leader);
+    tc_commit_if(empty0 + 8u * s, leader);
+    tc_commit_if(acc_full0 + 8u * buf, leader);
+    if (++s == a.stages) {
+      s = 0;
+      full_parity ^= 1;
+    }
+  }
+  return true;
+}
+
 // ---------------------------------------------------------------- the kernel
 // Persistent: one CTA per SM walks tiles t = blockIdx.x, blockIdx.x + gridDim.x, ...;
 // consecutive tile ids share the same 128 pixels (channel tile fastest) so that CTAs running
@@ -918,7 +983,10 @@ __global__ void __launch_bounds__(kThreads, 1)
     };
     bool have_prev = false;
     int prev_n0 = 0, local = 0;
-    for (int tile = blockIdx.x; a.slab && tile < a.num_tiles && ok; tile += gridDim.x) {
+    if (a.fast_window)
+      ok = producer_loop_window_resident(a, &tmA, smem_base, stage_bytes, smem_u32(&full_bar[0]), smem_u32(&empty_bar[0]),
+                                         leader, abort_flag);
+    for (int tile = blockIdx.x; a.slab && !a.fast_window && tile < a.num_tiles && ok; tile += gridDim.x) {
       // one window per tile: rows ty*16 - pad_t ..., columns tx*8 - pad_l ...; cells outside the
       // image are filled with zeros by the copy engine
       const int tile_m = tile / a.tiles_n;
@@ -1095,7 +1163,17 @@ __global__ void __launch_bounds__(kThreads, 1)
         ok = mma_loop_flat_resident<1>(a, 0, 1, tmem_base, acc_stride, nb_mask, nb_shift, ring_lo, stage_lo, bres_lo, stage_b_lo,
                                        hi_b, idesc, f0, e0, af0, ae0, leader, abort_flag);
     }
-    for (int tile = blockIdx.x; !a.fast_flat && tile < a.num_tiles && ok; tile += gridDim.x, ++it) {
+    if (a.fast_window && ok) {
+      const uint32_t f0 = smem_u32(&full_bar[0]), e0 = smem_u32(&empty_bar[0]);
+      const uint32_t af0 = smem_u32(&acc_full[0]), ae0 = smem_u32(&acc_empty[0]);
+      if (a.kh == 4)
+        ok = mma_loop_window_resident<4, 1, 2>(a, tmem_base, acc_stride, nb_mask, nb_shift, ring_lo, stage_lo, row_lo, col_lo,
+                                               hi_a, bres_lo, stage_b_lo, hi_b, idesc, f0, e0, af0, ae0, leader, abort_flag);
+      else
+        ok = mma_loop_window_resident<2, 1, 2>(a, tmem_base, acc_stride, nb_mask, nb_shift, ring_lo, stage_lo, row_lo, col_lo,
+                                               hi_a, bres_lo, stage_b_lo, hi_b, idesc, f0, e0, af0, ae0, leader, abort_flag);
+    }
+    for (int tile = blockIdx.x; !a.fast_flat && !a.fast_window && tile < a.num_tiles && ok; tile += gridDim.x, ++it) {
       int buf = it & nb_mask;
       TT_START();
       ok = mbar_wait(smem_u32(&acc_empty[buf]), ((it >> nb_shift) & 1) ^ 1, abort_flag, a.status, FAULT_WAIT_ACCUM);
@@ -1856,6 +1934,8 @@ int igemm_tc_launch(plb_ctx* ctx, const IgemmProblem& p) {
     }
   }
   a.resident_bytes = a.resident_b ? resident_bytes : 0;
+  a.fast_window = a.slab && !a.b_stream && a.resident_b && a.tiles_n == 1 && a.cchunks == 1 && a.kc == 64 && a.kw == 1 &&
+                  (a.kh == 4 || a.kh == 2) && !dual && env_int("PLB_TC_FAST_WINDOW", 1) != 0;
   a.fast_flat = !a.slab && !p.im2col && !dual && a.resident_b && a.tiles_n == 1 && env_int("PLB_TC_FAST_FLAT", 1) != 0;
   const int stage_bytes = (kTileM + bn) * a.kc;
   const int ring_stage_bytes = a.slab ? a.cchunks * a.plane_bytes : (a.resident_b ? kTileM * a.kc : stage_bytes);
