@@ -90,3 +90,22 @@ def test_benchmark_batch_matches_small_batch(plb, ctx, name, batch):
             assert torch.equal(got[first:first + 2], ref), "tensor %s differs at images %d.." % (key, first)
         checked += 1
     assert checked > 10
+
+
+@pytest.mark.parametrize("name,batch", [("mobilenet_v1", 40), ("resnet50", 24)])
+def test_stem_role_loops_agree(plb, ctx, name, batch, monkeypatch):
+    """The stem's window tiles run through short producer / MMA loops; the generic loops
+    (PLB_TC_FAST_WINDOW=0) must give the same tensors (several tiles per CTA at this batch)."""
+    N = nets()
+    spec = N.SPECS[name]()
+    qnet = N.build_quantized(spec, seed=5, calib_images=2, device="cuda")
+    images = torch.randn((batch,) + spec["image"], device="cuda")
+    fast = N.Runner(plb, ctx, qnet, batch)
+    fast.forward(images)
+    ctx.sync()
+    monkeypatch.setenv("PLB_TC_FAST_WINDOW", "0")
+    generic = N.Runner(plb, ctx, qnet, batch)
+    generic.forward(images)
+    ctx.sync()
+    for key, ref in generic.buf.items():
+        assert torch.equal(fast.buf[key], ref), "tensor %s differs between the role loops" % key
