@@ -80,7 +80,7 @@ struct IgemmArgs {
   float alpha;
   int acc_small;                       // every |accumulator| < 2^22 (proven from the filter by the host)
   int fast_window;                     // window tiles of a row-folded stem layer (shapes 4x1 / 2x1, two MMAs per tap): short role loops
-  int fast_flat;                       // flat tiles, resident filter, one channel tile, no shortcut GEMM: short role loops
+  int fast_flat;                       // flat tiles without a shortcut GEMM: short role loops
   int sb_off, sb_cols;                 // scale / bias tables copied to shared memory (offset in the staging area; 0 columns = not)
   const float* residual;
   float* y_f32;
@@ -692,40 +692,30 @@ __device__ __forceinline__ void issue_window_taps(int kh, int kw, uint32_t d_tme
   }
 }
 
-// Flat GEMM tiles with the whole filter resident in shared memory and a single channel tile (1x1
-// convolutions and fc with few channels): a tile is only `ksteps` K steps of work, so the per-tile
-// instruction count of the two single-warp roles decides how fast tiles flow.  These loops keep
-// every address in a register that advances by a constant.
-// Ring position after `n` more K steps.
-__device__ __forceinline__ void ring_advance(int n, int stages, int& s, uint32_t& parity) {
-  s += n;
-  while (s >= stages) {
-    s -= stages;
-    parity ^= 1;
-  }
-}
-
-// `first` / `step`: this warp takes the CTA's tiles first, first + step, ... (0 / 1: all of them).
+// Flat GEMM tiles (1x1 convolutions and fc; resident or streamed filter, any number of channel tiles): with
+// few channels a tile is only a K step or two of work, so the per-tile instruction count of the two
+// single-warp roles decides how fast tiles flow.  These loops keep the bookkeeping to a minimum: no
+// divisions, no mode branches.  The MMA warp does not need to know which tile it is working on: with a streamed filter the B tile sits behind the A tile of
+// the same stage, with a resident one at K step ks of the resident copy.
 template <int MPS>
-__device__ __forceinline__ bool mma_loop_flat_resident(const IgemmArgs& a, int first, int step, uint32_t tmem_base,
-                                                       uint32_t acc_stride, int nb_mask, int nb_shift, uint32_t ring_lo,
-                                                       uint32_t stage_lo, uint32_t bres_lo, uint32_t stage_b_lo,
-                                                       uint32_t hi, uint32_t idesc, uint32_t full0, uint32_t empty0,
-                                                       uint32_t acc_full0, uint32_t acc_empty0, bool leader,
-                                                       volatile int* abort_flag) {
-  int s = 0;
+__device__ __forceinline__ bool mma_loop_flat(const IgemmArgs& a, uint32_t tmem_base, uint32_t acc_stride, int nb_mask,
+                                              int nb_shift, uint32_t ring_lo, uint32_t stage_lo, uint32_t stage_a_lo,
+                                              uint32_t bres_lo, uint32_t stage_b_lo, uint32_t hi, uint32_t idesc,
+                                              uint32_t full0, uint32_t empty0, uint32_t acc_full0, uint32_t acc_empty0,
+                                              bool leader, volatile int* abort_flag) {
+  int s = 0, it = 0;
   uint32_t full_parity = 0;
-  ring_advance(first * a.ksteps, a.stages, s, full_parity);
-  const int skip = (step - 1) * a.ksteps;
-  for (int it = first, tile = blockIdx.x + first * gridDim.x; tile < a.num_tiles; tile += step * gridDim.x, it += step) {
+  const bool resident = a.resident_b != 0;
+  for (int tile = blockIdx.x; tile < a.num_tiles; tile += gridDim.x, ++it) {
     const int buf = it & nb_mask;
     if (!mbar_wait(acc_empty0 + 8u * buf, ((it >> nb_shift) & 1) ^ 1, abort_flag, a.status, FAULT_WAIT_ACCUM)) return false;
     const uint32_t d_tmem = tmem_base + buf * acc_stride;
-    uint32_t b_lo = bres_lo;
-    for (int ks = 0; ks < a.ksteps; ++ks, b_lo += stage_b_lo) {
+    uint32_t b_res = bres_lo;
+    for (int ks = 0; ks < a.ksteps; ++ks, b_res += stage_b_lo) {
       if (!mbar_wait(full0 + 8u * s, full_parity, abort_flag, a.status, FAULT_WAIT_FULL)) return false;
       tc_fence_after();
-      issue_kstep<MPS>(d_tmem, ring_lo + s * stage_lo, hi, b_lo, hi, idesc, ks > 0 ? 1u : 0u, leader);
+      const uint32_t a_lo = ring_lo + s * stage_lo;
+      issue_kstep<MPS>(d_tmem, a_lo, hi, resident ? b_res : a_lo + stage_a_lo, hi, idesc, ks > 0 ? 1u : 0u, leader);
       tc_commit_if(empty0 + 8u * s, leader);
       if (++s == a.stages) {
         s = 0;
@@ -733,30 +723,39 @@ __device__ __forceinline__ bool mma_loop_flat_resident(const IgemmArgs& a, int f
       }
     }
     tc_commit_if(acc_full0 + 8u * buf, leader);
-    ring_advance(skip, a.stages, s, full_parity);
   }
   return true;
 }
 
-__device__ __forceinline__ bool producer_loop_flat_resident(const IgemmArgs& a, int first, int step, const CUtensorMap* tmA,
-                                                            uint32_t smem_base, int stage_bytes, uint32_t full0,
-                                                            uint32_t empty0, bool leader, volatile int* abort_flag) {
+// The producer's (row block, channel tile) advance by the decomposition of gridDim.x with a carry.
+__device__ __forceinline__ bool producer_loop_flat(const IgemmArgs& a, const CUtensorMap* tmA, const CUtensorMap* tmB,
+                                                   uint32_t smem_base, int stage_bytes, int stage_a, uint32_t full0,
+                                                   uint32_t empty0, bool leader, volatile int* abort_flag) {
   int s = 0;
   uint32_t empty_parity = 1;  // a fresh barrier passes a wait on parity 1
-  ring_advance(first * a.ksteps, a.stages, s, empty_parity);
-  const int skip = (step - 1) * a.ksteps;
-  const int m_end = a.num_tiles * kTileM, m_step = step * static_cast<int>(gridDim.x) * kTileM, k_end = a.ksteps * a.kc;
-  for (int m0 = (static_cast<int>(blockIdx.x) + first * static_cast<int>(gridDim.x)) * kTileM; m0 < m_end; m0 += m_step) {
+  int tn = static_cast<int>(blockIdx.x) % a.tiles_n, tm = static_cast<int>(blockIdx.x) / a.tiles_n;
+  const int dn = static_cast<int>(gridDim.x) % a.tiles_n, dm = static_cast<int>(gridDim.x) / a.tiles_n;
+  const int k_end = a.ksteps * a.kc;
+  const bool resident = a.resident_b != 0;
+  for (int tile = blockIdx.x; tile < a.num_tiles; tile += gridDim.x) {
+    const int m0 = tm * kTileM, n0 = tn * a.bn;
     for (int kb = 0; kb < k_end; kb += a.kc) {
       if (!mbar_wait(empty0 + 8u * s, empty_parity, abort_flag, a.status, FAULT_WAIT_EMPTY)) return false;
+      const uint32_t dst = smem_base + s * stage_bytes;
       mbar_expect_tx_if(full0 + 8u * s, static_cast<uint32_t>(stage_bytes), leader);
-      tma_load_2d_if(smem_base + s * stage_bytes, tmA, full0 + 8u * s, kb, m0, leader);
+      tma_load_2d_if(dst, tmA, full0 + 8u * s, kb, m0, leader);
+      if (!resident) tma_load_2d_if(dst + stage_a, tmB, full0 + 8u * s, kb, n0, leader);
       if (++s == a.stages) {
         s = 0;
         empty_parity ^= 1;
       }
     }
-    ring_advance(skip, a.stages, s, empty_parity);
+    tn += dn;
+    tm += dm;
+    if (tn >= a.tiles_n) {
+      tn -= a.tiles_n;
+      ++tm;
+    }
   }
   return true;
 }
@@ -1027,9 +1026,9 @@ __global__ void __launch_bounds__(kThreads, 1)
       }
     }
     if (a.slab && a.b_stream && have_prev && ok) ok = stream_filter(prev_n0);
-    if (a.fast_flat)  // flat tiles, resident filter, one channel tile: one box of activations per K step, nothing else
-      ok = producer_loop_flat_resident(a, 0, 1, &tmA, smem_base, stage_bytes, smem_u32(&full_bar[0]),
-                                       smem_u32(&empty_bar[0]), leader, abort_flag);
+    if (a.fast_flat)  // flat tiles: one box of activations (and one of the filter, unless resident) per K step
+      ok = producer_loop_flat(a, &tmA, &tmB, smem_base, stage_bytes, stage_a, smem_u32(&full_bar[0]), smem_u32(&empty_bar[0]),
+                              leader, abort_flag);
     for (int tile = blockIdx.x; !a.slab && !a.fast_flat && tile < a.num_tiles && ok; tile += gridDim.x) {
       const int tile_m = tile / a.tiles_n;
       const int m0 = tile_m * kTileM;
@@ -1153,15 +1152,16 @@ __global__ void __launch_bounds__(kThreads, 1)
     if (a.fast_flat && ok) {
       const uint32_t f0 = smem_u32(&full_bar[0]), e0 = smem_u32(&empty_bar[0]);
       const uint32_t af0 = smem_u32(&acc_full[0]), ae0 = smem_u32(&acc_empty[0]);
+      const uint32_t stage_a_lo = static_cast<uint32_t>(stage_a) >> 4;
       if (mma_per_stage == 4)
-        ok = mma_loop_flat_resident<4>(a, 0, 1, tmem_base, acc_stride, nb_mask, nb_shift, ring_lo, stage_lo, bres_lo, stage_b_lo,
-                                       hi_b, idesc, f0, e0, af0, ae0, leader, abort_flag);
+        ok = mma_loop_flat<4>(a, tmem_base, acc_stride, nb_mask, nb_shift, ring_lo, stage_lo, stage_a_lo, bres_lo, stage_b_lo,
+                              hi_b, idesc, f0, e0, af0, ae0, leader, abort_flag);
       else if (mma_per_stage == 2)
-        ok = mma_loop_flat_resident<2>(a, 0, 1, tmem_base, acc_stride, nb_mask, nb_shift, ring_lo, stage_lo, bres_lo, stage_b_lo,
-                                       hi_b, idesc, f0, e0, af0, ae0, leader, abort_flag);
+        ok = mma_loop_flat<2>(a, tmem_base, acc_stride, nb_mask, nb_shift, ring_lo, stage_lo, stage_a_lo, bres_lo, stage_b_lo,
+                              hi_b, idesc, f0, e0, af0, ae0, leader, abort_flag);
       else
-        ok = mma_loop_flat_resident<1>(a, 0, 1, tmem_base, acc_stride, nb_mask, nb_shift, ring_lo, stage_lo, bres_lo, stage_b_lo,
-                                       hi_b, idesc, f0, e0, af0, ae0, leader, abort_flag);
+        ok = mma_loop_flat<1>(a, tmem_base, acc_stride, nb_mask, nb_shift, ring_lo, stage_lo, stage_a_lo, bres_lo, stage_b_lo,
+                              hi_b, idesc, f0, e0, af0, ae0, leader, abort_flag);
     }
     if (a.fast_window && ok) {
       const uint32_t f0 = smem_u32(&full_bar[0]), e0 = smem_u32(&empty_bar[0]);
@@ -1936,7 +1936,7 @@ int igemm_tc_launch(plb_ctx* ctx, const IgemmProblem& p) {
   a.resident_bytes = a.resident_b ? resident_bytes : 0;
   a.fast_window = a.slab && !a.b_stream && a.resident_b && a.tiles_n == 1 && a.cchunks == 1 && a.kc == 64 && a.kw == 1 &&
                   (a.kh == 4 || a.kh == 2) && !dual && env_int("PLB_TC_FAST_WINDOW", 1) != 0;
-  a.fast_flat = !a.slab && !p.im2col && !dual && a.resident_b && a.tiles_n == 1 && env_int("PLB_TC_FAST_FLAT", 1) != 0;
+  a.fast_flat = !a.slab && !p.im2col && !dual && env_int("PLB_TC_FAST_FLAT", 1) != 0;
   const int stage_bytes = (kTileM + bn) * a.kc;
   const int ring_stage_bytes = a.slab ? a.cchunks * a.plane_bytes : (a.resident_b ? kTileM * a.kc : stage_bytes);
   // one CTA per SM: spend (almost) all remaining shared memory on the operand ring
