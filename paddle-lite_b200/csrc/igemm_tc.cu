@@ -80,7 +80,8 @@ struct IgemmArgs {
   float alpha;
   int acc_small;                       // every |accumulator| < 2^22 (proven from the filter by the host)
   int fast_window;                     // window tiles of a row-folded stem layer (shapes 4x1 / 2x1, two MMAs per tap): short role loops
-  int fast_flat;                       // flat tiles without a shortcut GEMM: short role loops
+  int fast_flat;                       // flat tiles without a shortcut GEMM: short producer loop
+  int fast_mma;                        // flat or im2col tiles without a shortcut GEMM: short MMA loop
   int sb_off, sb_cols;                 // scale / bias tables copied to shared memory (offset in the staging area; 0 columns = not)
   const float* residual;
   float* y_f32;
@@ -1149,7 +1150,7 @@ __global__ void __launch_bounds__(kThreads, 1)
     const uint32_t stage_b_lo = static_cast<uint32_t>(stage_b) >> 4;
     const uint32_t stage_lo = static_cast<uint32_t>(stage_bytes) >> 4;
     const uint32_t ring_lo = ((smem_base >> 4) & 0x3FFFu) | lo_flags;
-    if (a.fast_flat && ok) {
+    if (a.fast_mma && ok) {
       const uint32_t f0 = smem_u32(&full_bar[0]), e0 = smem_u32(&empty_bar[0]);
       const uint32_t af0 = smem_u32(&acc_full[0]), ae0 = smem_u32(&acc_empty[0]);
       const uint32_t stage_a_lo = static_cast<uint32_t>(stage_a) >> 4;
@@ -1173,7 +1174,7 @@ __global__ void __launch_bounds__(kThreads, 1)
         ok = mma_loop_window_resident<2, 1, 2>(a, tmem_base, acc_stride, nb_mask, nb_shift, ring_lo, stage_lo, row_lo, col_lo,
                                                hi_a, bres_lo, stage_b_lo, hi_b, idesc, f0, e0, af0, ae0, leader, abort_flag);
     }
-    for (int tile = blockIdx.x; !a.fast_flat && !a.fast_window && tile < a.num_tiles && ok; tile += gridDim.x, ++it) {
+    for (int tile = blockIdx.x; !a.fast_mma && !a.fast_window && tile < a.num_tiles && ok; tile += gridDim.x, ++it) {
       int buf = it & nb_mask;
       TT_START();
       ok = mbar_wait(smem_u32(&acc_empty[buf]), ((it >> nb_shift) & 1) ^ 1, abort_flag, a.status, FAULT_WAIT_ACCUM);
@@ -1937,6 +1938,8 @@ int igemm_tc_launch(plb_ctx* ctx, const IgemmProblem& p) {
   a.fast_window = a.slab && !a.b_stream && a.resident_b && a.tiles_n == 1 && a.cchunks == 1 && a.kc == 64 && a.kw == 1 &&
                   (a.kh == 4 || a.kh == 2) && !dual && env_int("PLB_TC_FAST_WINDOW", 1) != 0;
   a.fast_flat = !a.slab && !p.im2col && !dual && env_int("PLB_TC_FAST_FLAT", 1) != 0;
+  // the MMA warp's short loop does not care how the A tile of a stage was fetched: im2col tiles take it too
+  a.fast_mma = a.fast_flat || (!a.slab && !dual && env_int("PLB_TC_FAST_MMA", 1) != 0);
   const int stage_bytes = (kTileM + bn) * a.kc;
   const int ring_stage_bytes = a.slab ? a.cchunks * a.plane_bytes : (a.resident_b ? kTileM * a.kc : stage_bytes);
   // one CTA per SM: spend (almost) all remaining shared memory on the operand ring
