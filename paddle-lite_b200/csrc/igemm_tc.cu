@@ -81,6 +81,7 @@ struct IgemmArgs {
   int acc_small;                       // every |accumulator| < 2^22 (proven from the filter by the host)
   int fast_window;                     // window tiles of a row-folded stem layer (shapes 4x1 / 2x1, two MMAs per tap): short role loops
   int fast_flat;                       // flat tiles without a shortcut GEMM: short producer loop
+  int fast_im2col, cin_bytes;          // im2col tiles without a shortcut GEMM: short producer loop; cchunks * kc
   int fast_mma;                        // flat or im2col tiles without a shortcut GEMM: short MMA loop
   int sb_off, sb_cols;                 // scale / bias tables copied to shared memory (offset in the staging area; 0 columns = not)
   const float* residual;
@@ -761,6 +762,47 @@ __device__ __forceinline__ bool producer_loop_flat(const IgemmArgs& a, const CUt
   return true;
 }
 
+// im2col tiles: the same bookkeeping, the K steps as nested loops over (filter row, filter column, channel chunk).
+__device__ __forceinline__ bool producer_loop_im2col(const IgemmArgs& a, const CUtensorMap* tmA, const CUtensorMap* tmB,
+                                                     uint32_t smem_base, int stage_bytes, int stage_a, uint32_t full0,
+                                                     uint32_t empty0, bool leader, volatile int* abort_flag) {
+  int s = 0;
+  uint32_t empty_parity = 1;
+  int tn = static_cast<int>(blockIdx.x) % a.tiles_n, tm = static_cast<int>(blockIdx.x) / a.tiles_n;
+  const int dn = static_cast<int>(gridDim.x) % a.tiles_n, dm = static_cast<int>(gridDim.x) / a.tiles_n;
+  const bool resident = a.resident_b != 0;
+  for (int tile = blockIdx.x; tile < a.num_tiles; tile += gridDim.x) {
+    const int m0 = tm * kTileM, n0 = tn * a.bn;
+    const int q0 = m0 % a.wo, t = m0 / a.wo;
+    const int p0 = t % a.ho, cn = t / a.ho;
+    const int cw = q0 * a.stride_w - a.pad_l, ch = p0 * a.stride_h - a.pad_t;
+    int kb = 0;
+    for (int r = 0, off_h = 0; r < a.kh; ++r, off_h += a.dil_h) {
+      for (int sx = 0, off_w = 0; sx < a.kw; ++sx, off_w += a.dil_w) {
+        for (int c = 0; c < a.cin_bytes; c += a.kc, kb += a.kc) {
+          if (!mbar_wait(empty0 + 8u * s, empty_parity, abort_flag, a.status, FAULT_WAIT_EMPTY)) return false;
+          const uint32_t dst = smem_base + s * stage_bytes;
+          mbar_expect_tx_if(full0 + 8u * s, static_cast<uint32_t>(stage_bytes), leader);
+          tma_load_im2col_4d_if(dst, tmA, full0 + 8u * s, c, cw, ch, cn, static_cast<uint16_t>(off_w),
+                                static_cast<uint16_t>(off_h), leader);
+          if (!resident) tma_load_2d_if(dst + stage_a, tmB, full0 + 8u * s, kb, n0, leader);
+          if (++s == a.stages) {
+            s = 0;
+            empty_parity ^= 1;
+          }
+        }
+      }
+    }
+    tn += dn;
+    tm += dm;
+    if (tn >= a.tiles_n) {
+      tn -= a.tiles_n;
+      ++tm;
+    }
+  }
+  return true;
+}
+
 // Window-mode tiles of the row-folded stem layers (a handful of MMAs per tile, resident filter, one
 // channel tile, one window box per tile): the same short loops as for flat tiles.  The window position
 // (tx, ty, image) advances by the decomposition of gridDim.x with carries instead of divisions.
@@ -1030,7 +1072,10 @@ __global__ void __launch_bounds__(kThreads, 1)
     if (a.fast_flat)  // flat tiles: one box of activations (and one of the filter, unless resident) per K step
       ok = producer_loop_flat(a, &tmA, &tmB, smem_base, stage_bytes, stage_a, smem_u32(&full_bar[0]), smem_u32(&empty_bar[0]),
                               leader, abort_flag);
-    for (int tile = blockIdx.x; !a.slab && !a.fast_flat && tile < a.num_tiles && ok; tile += gridDim.x) {
+    if (a.fast_im2col)
+      ok = producer_loop_im2col(a, &tmA, &tmB, smem_base, stage_bytes, stage_a, smem_u32(&full_bar[0]), smem_u32(&empty_bar[0]),
+                                leader, abort_flag);
+    for (int tile = blockIdx.x; !a.slab && !a.fast_flat && !a.fast_im2col && tile < a.num_tiles && ok; tile += gridDim.x) {
       const int tile_m = tile / a.tiles_n;
       const int m0 = tile_m * kTileM;
       const int n0 = (tile - tile_m * a.tiles_n) * a.bn;
@@ -1805,6 +1850,7 @@ int igemm_tc_launch(plb_ctx* ctx, const IgemmProblem& p) {
   a.cchunks = p.cin_pad / a.kc;
   a.taps = p.im2col ? p.kh * p.kw : 1;
   a.kw = p.im2col ? p.kw : 1;
+  a.kh = p.im2col ? p.kh : 1;
   a.ksteps = a.taps * a.cchunks;
   const int cout16 = (p.cout + 15) / 16 * 16;
   int bn = cout16 < 256 ? cout16 : 256;
@@ -1938,6 +1984,8 @@ int igemm_tc_launch(plb_ctx* ctx, const IgemmProblem& p) {
   a.fast_window = a.slab && !a.b_stream && a.resident_b && a.tiles_n == 1 && a.cchunks == 1 && a.kc == 64 && a.kw == 1 &&
                   (a.kh == 4 || a.kh == 2) && !dual && env_int("PLB_TC_FAST_WINDOW", 1) != 0;
   a.fast_flat = !a.slab && !p.im2col && !dual && env_int("PLB_TC_FAST_FLAT", 1) != 0;
+  a.cin_bytes = a.cchunks * a.kc;
+  a.fast_im2col = !a.slab && p.im2col && !dual && env_int("PLB_TC_FAST_IM2COL", 1) != 0;
   // the MMA warp's short loop does not care how the A tile of a stage was fetched: im2col tiles take it too
   a.fast_mma = a.fast_flat || (!a.slab && !dual && env_int("PLB_TC_FAST_MMA", 1) != 0);
   const int stage_bytes = (kTileM + bn) * a.kc;
