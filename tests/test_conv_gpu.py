@@ -418,3 +418,29 @@ def test_flat_tiles_many_per_cta(plb, ctx, cin, cout, env, monkeypatch):
     q = conv8.run(dev(xq))
     ctx.sync()
     assert np.array_equal(q.cpu().numpy(), q_ref)
+
+
+_IM2COL_CASE = {}
+
+
+@pytest.mark.parametrize("env", [{}, {"PLB_TC_FAST_IM2COL": "0"}, {"PLB_TC_FAST_MMA": "0"},
+                                 {"PLB_TC_FAST_IM2COL": "0", "PLB_TC_FAST_MMA": "0"}],
+                         ids=lambda e: ",".join("%s=%s" % kv for kv in e.items()) or "default")
+def test_im2col_role_loops_agree(plb, ctx, env, monkeypatch):
+    """A strided 3x3 convolution (im2col tiles, streamed filter, two channel tiles, several tiles
+    per CTA) through the lean and the generic producer / MMA loops: the oracle's bytes each time."""
+    for k, v in env.items():
+        monkeypatch.setenv(k, v)
+    monkeypatch.setenv("PLB_TC_BN", "64")
+    if not _IM2COL_CASE:
+        xq, in_s, wq, ws, bias = conv_case(4711, 8, 64, 112, 112, 128, 3)
+        kw = dict(stride=(2, 2), pads=(1, 1, 1, 1))
+        acc_ref = O.conv_acc_i32(xq, wq, **kw)
+        y_ref = O.epilogue(acc_ref, ws, in_s, bias, 1, 0.0)
+        out_s = float(max(np.abs(y_ref).max(), 1e-6) / 127.0)
+        _IM2COL_CASE["c"] = (xq, in_s, wq, ws, bias, kw, out_s, O.epilogue(acc_ref, ws, in_s, bias, 1, 0.0, out_scale=out_s))
+    xq, in_s, wq, ws, bias, kw, out_s, q_ref = _IM2COL_CASE["c"]
+    conv8 = plb.Conv(ctx, wq, ws, in_s, bias, in_hw=(112, 112), act=1, out_scale=out_s, **kw)
+    q = conv8.run(dev(xq))
+    ctx.sync()
+    assert np.array_equal(q.cpu().numpy(), q_ref)
