@@ -704,10 +704,11 @@ __device__ __forceinline__ bool mma_loop_flat(const IgemmArgs& a, uint32_t tmem_
                                               int nb_shift, uint32_t ring_lo, uint32_t stage_lo, uint32_t stage_a_lo,
                                               uint32_t bres_lo, uint32_t stage_b_lo, uint32_t hi, uint32_t idesc,
                                               uint32_t full0, uint32_t empty0, uint32_t acc_full0, uint32_t acc_empty0,
-                                              bool leader, volatile int* abort_flag) {
+                                              uint32_t acc2_cols, bool leader, volatile int* abort_flag) {
   int s = 0, it = 0;
   uint32_t full_parity = 0;
   const bool resident = a.resident_b != 0;
+  const int ksteps2 = a.dual ? a.ksteps2 : 0;
   for (int tile = blockIdx.x; tile < a.num_tiles; tile += gridDim.x, ++it) {
     const int buf = it & nb_mask;
     if (!mbar_wait(acc_empty0 + 8u * buf, ((it >> nb_shift) & 1) ^ 1, abort_flag, a.status, FAULT_WAIT_ACCUM)) return false;
@@ -724,6 +725,19 @@ __device__ __forceinline__ bool mma_loop_flat(const IgemmArgs& a, uint32_t tmem_
         full_parity ^= 1;
       }
     }
+    // shortcut GEMM of a fused residual block: its K steps follow in the ring (filter always streamed) and
+    // accumulate into the columns next to the main accumulator
+    for (int ks = 0; ks < ksteps2; ++ks) {
+      if (!mbar_wait(full0 + 8u * s, full_parity, abort_flag, a.status, FAULT_WAIT_FULL)) return false;
+      tc_fence_after();
+      const uint32_t a_lo = ring_lo + s * stage_lo;
+      issue_kstep<MPS>(d_tmem + acc2_cols, a_lo, hi, a_lo + stage_a_lo, hi, idesc, ks > 0 ? 1u : 0u, leader);
+      tc_commit_if(empty0 + 8u * s, leader);
+      if (++s == a.stages) {
+        s = 0;
+        full_parity ^= 1;
+      }
+    }
     tc_commit_if(acc_full0 + 8u * buf, leader);
   }
   return true;
@@ -731,10 +745,12 @@ __device__ __forceinline__ bool mma_loop_flat(const IgemmArgs& a, uint32_t tmem_
 
 // The producer's (row block, channel tile) advance by the decomposition of gridDim.x with a carry.
 __device__ __forceinline__ bool producer_loop_flat(const IgemmArgs& a, const CUtensorMap* tmA, const CUtensorMap* tmB,
-                                                   uint32_t smem_base, int stage_bytes, int stage_a, uint32_t full0,
-                                                   uint32_t empty0, bool leader, volatile int* abort_flag) {
+                                                   const CUtensorMap* tmA2, const CUtensorMap* tmB2, uint32_t smem_base,
+                                                   int stage_bytes, int stage_a, uint32_t full0, uint32_t empty0, bool leader,
+                                                   volatile int* abort_flag) {
   int s = 0;
   uint32_t empty_parity = 1;  // a fresh barrier passes a wait on parity 1
+  const int k2_end = a.dual ? a.ksteps2 * a.kc : 0;
   int tn = static_cast<int>(blockIdx.x) % a.tiles_n, tm = static_cast<int>(blockIdx.x) / a.tiles_n;
   const int dn = static_cast<int>(gridDim.x) % a.tiles_n, dm = static_cast<int>(gridDim.x) / a.tiles_n;
   const int k_end = a.ksteps * a.kc;
@@ -750,6 +766,28 @@ __device__ __forceinline__ bool producer_loop_flat(const IgemmArgs& a, const CUt
       if (++s == a.stages) {
         s = 0;
         empty_parity ^= 1;
+      }
+    }
+    if (k2_end > 0) {
+      // shortcut GEMM of a fused residual block: 1x1 filter, stride stride2, no padding, on its own input
+      int q0 = 0, p0 = 0, cn = 0;
+      if (a.im2col2) {
+        q0 = m0 % a.wo;
+        const int t = m0 / a.wo;
+        p0 = t % a.ho;
+        cn = t / a.ho;
+      }
+      for (int kb = 0; kb < k2_end; kb += a.kc) {
+        if (!mbar_wait(empty0 + 8u * s, empty_parity, abort_flag, a.status, FAULT_WAIT_EMPTY)) return false;
+        const uint32_t dst = smem_base + s * stage_bytes;
+        mbar_expect_tx_if(full0 + 8u * s, static_cast<uint32_t>(stage_bytes), leader);
+        if (a.im2col2) tma_load_im2col_4d_if(dst, tmA2, full0 + 8u * s, kb, q0 * a.stride2_w, p0 * a.stride2_h, cn, 0, 0, leader);
+        else tma_load_2d_if(dst, tmA2, full0 + 8u * s, kb, m0, leader);
+        tma_load_2d_if(dst + stage_a, tmB2, full0 + 8u * s, kb, n0, leader);
+        if (++s == a.stages) {
+          s = 0;
+          empty_parity ^= 1;
+        }
       }
     }
     tn += dn;
@@ -1070,8 +1108,8 @@ __global__ void __launch_bounds__(kThreads, 1)
     }
     if (a.slab && a.b_stream && have_prev && ok) ok = stream_filter(prev_n0);
     if (a.fast_flat)  // flat tiles: one box of activations (and one of the filter, unless resident) per K step
-      ok = producer_loop_flat(a, &tmA, &tmB, smem_base, stage_bytes, stage_a, smem_u32(&full_bar[0]), smem_u32(&empty_bar[0]),
-                              leader, abort_flag);
+      ok = producer_loop_flat(a, &tmA, &tmB, &tmA2, &tmB2, smem_base, stage_bytes, stage_a, smem_u32(&full_bar[0]),
+                              smem_u32(&empty_bar[0]), leader, abort_flag);
     if (a.fast_im2col)
       ok = producer_loop_im2col(a, &tmA, &tmB, smem_base, stage_bytes, stage_a, smem_u32(&full_bar[0]), smem_u32(&empty_bar[0]),
                                 leader, abort_flag);
@@ -1201,13 +1239,13 @@ __global__ void __launch_bounds__(kThreads, 1)
       const uint32_t stage_a_lo = static_cast<uint32_t>(stage_a) >> 4;
       if (mma_per_stage == 4)
         ok = mma_loop_flat<4>(a, tmem_base, acc_stride, nb_mask, nb_shift, ring_lo, stage_lo, stage_a_lo, bres_lo, stage_b_lo,
-                              hi_b, idesc, f0, e0, af0, ae0, leader, abort_flag);
+                              hi_b, idesc, f0, e0, af0, ae0, acc_cols, leader, abort_flag);
       else if (mma_per_stage == 2)
         ok = mma_loop_flat<2>(a, tmem_base, acc_stride, nb_mask, nb_shift, ring_lo, stage_lo, stage_a_lo, bres_lo, stage_b_lo,
-                              hi_b, idesc, f0, e0, af0, ae0, leader, abort_flag);
+                              hi_b, idesc, f0, e0, af0, ae0, acc_cols, leader, abort_flag);
       else
         ok = mma_loop_flat<1>(a, tmem_base, acc_stride, nb_mask, nb_shift, ring_lo, stage_lo, stage_a_lo, bres_lo, stage_b_lo,
-                              hi_b, idesc, f0, e0, af0, ae0, leader, abort_flag);
+                              hi_b, idesc, f0, e0, af0, ae0, acc_cols, leader, abort_flag);
     }
     if (a.fast_window && ok) {
       const uint32_t f0 = smem_u32(&full_bar[0]), e0 = smem_u32(&empty_bar[0]);
@@ -1983,7 +2021,7 @@ int igemm_tc_launch(plb_ctx* ctx, const IgemmProblem& p) {
   a.resident_bytes = a.resident_b ? resident_bytes : 0;
   a.fast_window = a.slab && !a.b_stream && a.resident_b && a.tiles_n == 1 && a.cchunks == 1 && a.kc == 64 && a.kw == 1 &&
                   (a.kh == 4 || a.kh == 2) && !dual && env_int("PLB_TC_FAST_WINDOW", 1) != 0;
-  a.fast_flat = !a.slab && !p.im2col && !dual && env_int("PLB_TC_FAST_FLAT", 1) != 0;
+  a.fast_flat = !a.slab && !p.im2col && (!dual || env_int("PLB_TC_FAST_DUAL", 1) != 0) && env_int("PLB_TC_FAST_FLAT", 1) != 0;
   a.cin_bytes = a.cchunks * a.kc;
   a.fast_im2col = !a.slab && p.im2col && !dual && env_int("PLB_TC_FAST_IM2COL", 1) != 0;
   // the MMA warp's short loop does not care how the A tile of a stage was fetched: im2col tiles take it too
