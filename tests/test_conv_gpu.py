@@ -205,9 +205,13 @@ def test_nhwc_entry_and_fused_add_relu(plb, ctx, prefetch, monkeypatch):
 
 @pytest.mark.parametrize("n,cin_m,cin_s,hw,cout,stride", [(3, 64, 64, 14, 256, 1), (2, 128, 256, 28, 512, 2),
                                                          (5, 32, 96, 9, 64, 2), (1, 256, 512, 7, 320, 1)])
-def test_block_add_relu_equals_the_unfused_sequence(plb, ctx, n, cin_m, cin_s, hw, cout, stride):
+@pytest.mark.parametrize("generic_loops", ["0", "1"])
+def test_block_add_relu_equals_the_unfused_sequence(plb, ctx, n, cin_m, cin_s, hw, cout, stride, generic_loops, monkeypatch):
     """Projection-block tail in one launch: relu(main 1x1 conv + strided 1x1 shortcut conv) and its
-    calib, bit-identical to conv(fp32_out), conv(fp32_out), add, relu, calib through the oracle."""
+    calib, bit-identical to conv(fp32_out), conv(fp32_out), add, relu, calib through the oracle;
+    through the short role loops and through the generic ones."""
+    if generic_loops == "1":
+        monkeypatch.setenv("PLB_TC_FAST_DUAL", "0")
     hs = hw * stride - (stride - 1) * (n % 2)  # shortcut input: even and odd sizes
     xm, in_m, wm, wsm, bm = conv_case(31 + cout, n, cin_m, hw, hw, cout, 1)
     xs, in_s, wsh, wss, bs = conv_case(32 + cout, n, cin_s, hs, hs, cout, 1)
