@@ -14,8 +14,10 @@
  *     not thread-safe.
  *   - tensors at this boundary use the reference layouts (NCHW activations, OIHW filters,
  *     [K,N] fc weights) unless a function says NHWC.
- *   - *_run() calls are asynchronous; plb_ctx_sync() waits and reports kernel-side faults
- *     (a pipeline wait that ran out) as PLB_E_DEVICE.
+ *   - *_run() calls are asynchronous; plb_ctx_sync() and plb_copy_d2h() wait and report
+ *     kernel-side faults (a pipeline wait that ran out) as PLB_E_DEVICE.
+ *   - tuning switches (PLB_TC_*, PLB_DW_STRIP in the environment) are read when a layer is
+ *     prepared, never on the run path.
  */
 #ifndef PLB200_H_
 #define PLB200_H_
@@ -73,6 +75,8 @@ long plb_ctx_launch_count(const plb_ctx* ctx);
 /* How many of those were tensor-core convolutions in window mode (each input pixel of a tile
  * fetched once and shared by all filter taps).  For tests and tuning; no reference counterpart. */
 long plb_ctx_window_launch_count(const plb_ctx* ctx);
+/* Bytes of layout-staging scratch the ctx currently holds (its own or the caller's).  Test hook. */
+size_t plb_ctx_workspace_size(const plb_ctx* ctx);
 
 /* ------------------------------------------------------------------ conv2d / depthwise_conv2d
  * plb_conv_desc carries what operators::ConvParam holds for an int8 kernel
@@ -123,7 +127,8 @@ int plb_conv_run_image_f32(plb_conv* conv, const float* x, void* y, int batch);
  *   - a call whose staging (plb_conv_workspace_bytes(conv, batch)) exceeds 8 MiB is rejected
  *     with PLB_E_INVALID and a message that names both sizes; nothing is launched.
  *   - the first call on a device looks up the array's device address
- *     (cudaGetSymbolAddress); make that first call before starting any stream capture.
+ *     (cudaGetSymbolAddress); make that first call before starting any stream capture.  The lookup
+ *     is guarded, so first calls may come from several host threads.
  *   - all calls of the process on one device share the array, and it keeps whatever the last
  *     call left there.  Every byte a call reads it has written first, so consecutive calls on
  *     one stream are safe; calls that can overlap on the GPU (different streams or contexts)
@@ -152,6 +157,11 @@ int plb_conv_run_nhwc_add_relu(plb_conv* conv, const int8_t* x, const float* res
 int plb_conv_run_nhwc_block_add_relu(plb_conv* conv, const int8_t* x, plb_conv* shortcut, const int8_t* x_shortcut,
                                      float* y_f32, int8_t* y_i8, float next_scale, int batch);
 int plb_conv_out_dims(const plb_conv* conv, int* ho, int* wo);
+/* A prepared layer keeps the tile plan and the TMA descriptors of the (batch, pointers) it has been
+ * run on, so that a repeated Run() costs one kernel launch on the host (the reference re-derives
+ * nothing per Run either: its GEMM objects are built in PrepareForRun, conv_compute.cc:271-288).
+ * Returns how many runs of this layer re-used a stored plan.  Test hook. */
+long plb_conv_plan_cache_hits(const plb_conv* conv);
 void plb_conv_destroy(plb_conv* conv);
 
 /* ------------------------------------------------------------------ fc
@@ -203,7 +213,8 @@ int plb_calib_i8_to_f32(plb_ctx* ctx, const int8_t* q, float* y, size_t n, float
 /* Host <-> device copies on the ctx stream: what the io_copy kernels of a target do with
  * TargetWrapper<T>::MemcpySync (lite/kernels/xpu/io_copy_compute.cc:54-116, CopySync in
  * lite/core/memory.h:65-93).  h2d is enqueued (the host buffer must stay valid until the stream
- * reaches it; pinned memory makes it asynchronous), d2h returns when the bytes are on the host. */
+ * reaches it; pinned memory makes it asynchronous), d2h returns when the bytes are on the host, or
+ * PLB_E_DEVICE when a kernel in front of the copy recorded a fault (the bytes are then garbage). */
 int plb_copy_h2d(plb_ctx* ctx, void* dst_device, const void* src_host, size_t bytes);
 int plb_copy_d2h(plb_ctx* ctx, void* dst_host, const void* src_device, size_t bytes);
 /* layout staging: [n,c,h,w] <-> [n,h,w,cpad] (extra channels are zero / dropped). */

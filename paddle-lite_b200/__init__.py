@@ -57,6 +57,8 @@ SYMBOLS = {
     "plb_last_error": (C.c_char_p, []),
     "plb_ctx_launch_count": (C.c_long, [_P]),
     "plb_ctx_window_launch_count": (C.c_long, [_P]),
+    "plb_ctx_workspace_size": (C.c_size_t, [_P]),
+    "plb_conv_plan_cache_hits": (C.c_long, [_P]),
     "plb_conv_prepare": (C.c_int, [_P, C.POINTER(ConvDesc), _P, _P, C.c_int, _P, C.POINTER(_P)]),
     "plb_conv_run": (C.c_int, [_P, _P, _P, C.c_int]),
     "plb_conv_run_nhwc": (C.c_int, [_P, _P, _P, C.c_int]),
@@ -143,6 +145,9 @@ class Context:
 
     def window_launch_count(self):
         return lib().plb_ctx_window_launch_count(self.handle)
+
+    def workspace_size(self):
+        return lib().plb_ctx_workspace_size(self.handle)
 
     def set_workspace(self, tensor):
         self._ws = tensor
@@ -266,6 +271,9 @@ class Conv:
 
     def workspace_bytes(self, batch):
         return lib().plb_conv_workspace_bytes(self.handle, batch)
+
+    def plan_cache_hits(self):
+        return lib().plb_conv_plan_cache_hits(self.handle)
 
     def run(self, x, out=None):
         """x [N,Cin,H,W] int8 cuda -> [N,Cout,Ho,Wo] int8 or float32 (NCHW, reference layout)."""

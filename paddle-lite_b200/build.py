@@ -24,22 +24,34 @@ def _nvcc():
     return "nvcc"
 
 
-def needs_build():
-    if not os.path.exists(LIB):
+def needs_build(lib=LIB):
+    if not os.path.exists(lib):
         return True
-    t = os.path.getmtime(LIB)
+    t = os.path.getmtime(lib)
     deps = [os.path.join(CSRC, s) for s in SOURCES + HEADERS] + [os.path.abspath(__file__)]
     return any(os.path.getmtime(d) > t for d in deps)
 
 
-def build(force=False, verbose=False):
-    if not force and not needs_build():
-        return LIB
+# A second build of the same sources for ONE test (tests/test_failure_path_gpu.py): pipeline waits give up
+# after a few microseconds and PLB_TC_TEST_SKIP_LOAD=1 makes one CTA drop the copies of one pipeline
+# stage, so the bounded-wait -> status word -> PLB_E_DEVICE path can be exercised without a GPU fault.
+# Selected with PLB200_LIBRARY; never loaded by default.
+FAULT_TEST_LIB = os.path.join(HERE, "libplb200_faulttest.so")
+FAULT_TEST_FLAGS = ["-DPLB_TC_FAULT_TEST", "-DPLB_TC_TEST_WAIT_LIMIT=16384"]
+
+
+def build_fault_test(force=False):
+    return build(force=force, lib=FAULT_TEST_LIB, extra_flags=FAULT_TEST_FLAGS, suffix=".faulttest.o")
+
+
+def build(force=False, verbose=False, lib=LIB, extra_flags=(), suffix=".o"):
+    if not force and not needs_build(lib):
+        return lib
     objs = []
     procs = []
-    flags = list(NVCC_FLAGS)
+    flags = list(NVCC_FLAGS) + list(extra_flags)
     for src in SOURCES:
-        obj = os.path.join(CSRC, src.replace(".cu", ".o"))
+        obj = os.path.join(CSRC, src.replace(".cu", suffix))
         cmd = [_nvcc()] + flags + (["-Xptxas", "-v"] if verbose else []) + ["-c", os.path.join(CSRC, src), "-o", obj]
         procs.append((cmd, subprocess.Popen(cmd, stdout=subprocess.PIPE, stderr=subprocess.STDOUT, text=True)))
         objs.append(obj)
@@ -49,10 +61,12 @@ def build(force=False, verbose=False):
             sys.stderr.write(out)
         if p.returncode:
             raise RuntimeError("nvcc failed: " + " ".join(cmd))
-    cmd = [_nvcc(), "-shared", "-o", LIB] + objs + ["-cudart", "static"]
+    cmd = [_nvcc(), "-shared", "-o", lib] + objs + ["-cudart", "static"]
     subprocess.run(cmd, check=True)
-    return LIB
+    return lib
 
 
 if __name__ == "__main__":
     print(build(force="--force" in sys.argv, verbose="-v" in sys.argv))
+    if "--fault-test" in sys.argv:
+        print(build_fault_test(force="--force" in sys.argv))

@@ -46,6 +46,7 @@ struct plb_ctx {
   cudaStream_t stream = nullptr;
   int sm_count = 148;
   int* d_status = nullptr;      // 2 ints on the device
+  int* h_status = nullptr;      // pinned host copy, filled by an async copy in front of every host-side wait
   void* ws = nullptr;           // layout-staging scratch
   size_t ws_bytes = 0;
   bool ws_owned = false;

@@ -23,6 +23,7 @@
 
 #include <algorithm>
 #include <cstdlib>
+#include <mutex>
 #include <utility>
 
 namespace plb {
@@ -37,10 +38,14 @@ constexpr int kProducerWarp = kEpilogueWarps;
 constexpr int kMmaWarp = kEpilogueWarps + 1;
 constexpr int kThreads = 32 * (kEpilogueWarps + 2);
 constexpr int kMaxAccBufs = 8;
-constexpr int kMaxBStages = 8;                  // filter ring of window mode with a streamed filter
 constexpr int kCtrlBytes = 1024;                // barriers + tmem slot
 constexpr int kMaxResidentB = 56 * 1024;        // filters up to this size stay in shared memory for the whole kernel
+#ifdef PLB_TC_TEST_WAIT_LIMIT
+constexpr uint32_t kWaitLimit = PLB_TC_TEST_WAIT_LIMIT;  // test build: waits give up after a few microseconds
+#else
 constexpr uint32_t kWaitLimit = 1u << 22;      // polls before a wait is declared lost
+#endif
+constexpr uint32_t kDrainLimit = 1u << 12;     // polls per barrier while a CTA that gave up waits for its copies in flight
 
 struct IgemmArgs {
   int im2col;
@@ -62,16 +67,12 @@ struct IgemmArgs {
   int slab_rows;                       // window pixels = slab_w * (16 + (kh-1)*dil_h)
   int plane_bytes;                     // one channel chunk of the window, rounded up to 1 KiB
   int tiles_x, tiles_y;                // output tiles per image
-  // window mode with a filter too large to stay resident: the filter streams through its own ring,
-  // kgroup K steps per TMA box (a 3-D box: K step is the outermost box dimension)
-  int b_stream, kgroup, b_stages;
   // dual mode (OUT_ADD_RELU): a second 1x1 GEMM (the shortcut convolution of a residual block)
   // accumulates into the columns next to the main accumulator; the epilogue turns it into the
   // residual value fma(acc2, scale2, bias2) instead of reading a residual tensor
   int dual, ksteps2, cchunks2, im2col2, stride2_h, stride2_w;
   const float* scale2;
   const float* bias2;
-  int pair;                            // two consecutive tiles of a CTA share one pass over the filter stream
   int out_mode, ldy;
   void* y;
   const float* scale;
@@ -89,25 +90,10 @@ struct IgemmArgs {
   int8_t* y_i8;
   float inv_next_scale;
   int* status;
-#ifdef PLB_TC_TIMING
-  long long* timing;  // [grid][16] cycle counters
-  int dbg;            // PLB_TC_DBG bit 1: the epilogue reads the accumulators and drops them
+#ifdef PLB_TC_FAULT_TEST
+  int test_skip_load;                  // test build: CTA 0 drops the copies of one pipeline stage
 #endif
 };
-
-// Optional per-role cycle accounting (build with -DPLB_TC_TIMING; never part of the shipped library):
-// each role of a CTA sums the cycles it spends in its waits and the host prints the averages.
-#ifdef PLB_TC_TIMING
-#define TT_DECL(n) long long tt_acc[n] = {}; long long tt_t0 = 0
-#define TT_START() tt_t0 = clock64()
-#define TT_STOP(i) tt_acc[i] += clock64() - tt_t0
-#define TT_FLUSH(base, n) do { for (int tt_i = 0; tt_i < (n); ++tt_i) a.timing[blockIdx.x * 24 + (base) + tt_i] = tt_acc[tt_i]; } while (0)
-#else
-#define TT_DECL(n)
-#define TT_START()
-#define TT_STOP(i)
-#define TT_FLUSH(base, n)
-#endif
 
 // ---------------------------------------------------------------- PTX wrappers
 __device__ __forceinline__ uint32_t smem_u32(const void* p) {
@@ -148,6 +134,13 @@ __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatil
   if (atomicCAS(status, 0, code) == 0) status[1] = static_cast<int>(blockIdx.x);
   return false;
 }
+// After a lost wait: give a copy that may still be in flight a bounded time to land.  Records nothing.
+__device__ __forceinline__ void mbar_wait_drain(uint32_t bar, uint32_t parity) {
+  for (uint32_t it = 0; it < kDrainLimit; ++it) {
+    if (mbar_try_wait(bar, parity)) return;
+    __nanosleep(64);
+  }
+}
 __device__ __forceinline__ void tma_load_2d(uint32_t dst, const CUtensorMap* map, uint32_t bar,
                                             int c0, int c1) {
   asm volatile(
@@ -185,18 +178,6 @@ __device__ __forceinline__ void tma_load_2d_if(uint32_t dst, const CUtensorMap* 
       " [%0], [%1, {%3, %4}], [%2];\n\t"
       "}" ::"r"(dst),
       "l"(reinterpret_cast<uint64_t>(map)), "r"(bar), "r"(c0), "r"(c1), "r"(static_cast<uint32_t>(issue))
-      : "memory");
-}
-__device__ __forceinline__ void tma_load_3d_if(uint32_t dst, const CUtensorMap* map, uint32_t bar, int c0, int c1,
-                                               int c2, bool issue) {
-  asm volatile(
-      "{\n\t"
-      ".reg .pred q;\n\t"
-      "setp.ne.b32 q, %6, 0;\n\t"
-      "@q cp.async.bulk.tensor.3d.shared::cluster.global.mbarrier::complete_tx::bytes"
-      " [%0], [%1, {%3, %4, %5}], [%2];\n\t"
-      "}" ::"r"(dst),
-      "l"(reinterpret_cast<uint64_t>(map)), "r"(bar), "r"(c0), "r"(c1), "r"(c2), "r"(static_cast<uint32_t>(issue))
       : "memory");
 }
 __device__ __forceinline__ void tma_load_4d_if(uint32_t dst, const CUtensorMap* map, uint32_t bar, int c0, int c1,
@@ -747,9 +728,7 @@ __device__ __forceinline__ bool mma_loop_flat(const IgemmArgs& a, uint32_t tmem_
 __device__ __forceinline__ bool producer_loop_flat(const IgemmArgs& a, const CUtensorMap* tmA, const CUtensorMap* tmB,
                                                    const CUtensorMap* tmA2, const CUtensorMap* tmB2, uint32_t smem_base,
                                                    int stage_bytes, int stage_a, uint32_t full0, uint32_t empty0, bool leader,
-                                                   volatile int* abort_flag) {
-  int s = 0;
-  uint32_t empty_parity = 1;  // a fresh barrier passes a wait on parity 1
+                                                   volatile int* abort_flag, int& s, uint32_t& empty_parity) {
   const int k2_end = a.dual ? a.ksteps2 * a.kc : 0;
   int tn = static_cast<int>(blockIdx.x) % a.tiles_n, tm = static_cast<int>(blockIdx.x) / a.tiles_n;
   const int dn = static_cast<int>(gridDim.x) % a.tiles_n, dm = static_cast<int>(gridDim.x) / a.tiles_n;
@@ -803,9 +782,8 @@ __device__ __forceinline__ bool producer_loop_flat(const IgemmArgs& a, const CUt
 // im2col tiles: the same bookkeeping, the K steps as nested loops over (filter row, filter column, channel chunk).
 __device__ __forceinline__ bool producer_loop_im2col(const IgemmArgs& a, const CUtensorMap* tmA, const CUtensorMap* tmB,
                                                      uint32_t smem_base, int stage_bytes, int stage_a, uint32_t full0,
-                                                     uint32_t empty0, bool leader, volatile int* abort_flag) {
-  int s = 0;
-  uint32_t empty_parity = 1;
+                                                     uint32_t empty0, bool leader, volatile int* abort_flag, int& s,
+                                                     uint32_t& empty_parity) {
   int tn = static_cast<int>(blockIdx.x) % a.tiles_n, tm = static_cast<int>(blockIdx.x) / a.tiles_n;
   const int dn = static_cast<int>(gridDim.x) % a.tiles_n, dm = static_cast<int>(gridDim.x) / a.tiles_n;
   const bool resident = a.resident_b != 0;
@@ -846,9 +824,7 @@ __device__ __forceinline__ bool producer_loop_im2col(const IgemmArgs& a, const C
 // (tx, ty, image) advances by the decomposition of gridDim.x with carries instead of divisions.
 __device__ __forceinline__ bool producer_loop_window_resident(const IgemmArgs& a, const CUtensorMap* tmA, uint32_t smem_base,
                                                               int stage_bytes, uint32_t full0, uint32_t empty0, bool leader,
-                                                              volatile int* abort_flag) {
-  int s = 0;
-  uint32_t empty_parity = 1;
+                                                              volatile int* abort_flag, int& s, uint32_t& empty_parity) {
   int tx = static_cast<int>(blockIdx.x) % a.tiles_x;
   int ty = (static_cast<int>(blockIdx.x) / a.tiles_x) % a.tiles_y;
   int img = (static_cast<int>(blockIdx.x) / a.tiles_x) / a.tiles_y;
@@ -920,9 +896,6 @@ __global__ void __launch_bounds__(kThreads, 1)
                        const __grid_constant__ CUtensorMap tmOutB,
                        const __grid_constant__ CUtensorMap tmA2,
                        const __grid_constant__ CUtensorMap tmB2, const IgemmArgs a) {
-#ifdef PLB_TC_TIMING
-  const long long tt_entry = clock64();
-#endif
   extern __shared__ uint8_t smem_raw[];
   const uint32_t raw_addr = smem_u32(smem_raw);
   uint8_t* smem_al = smem_raw + (((raw_addr + 1023u) & ~1023u) - raw_addr);
@@ -932,18 +905,14 @@ __global__ void __launch_bounds__(kThreads, 1)
   uint8_t* smem_bres = smem_al + a.staging_bytes;
   uint8_t* smem = smem_bres + a.resident_bytes;
   const int stage_bytes = a.slab ? a.cchunks * a.plane_bytes : (a.resident_b ? stage_a : stage_a + stage_b);
-  uint8_t* smem_bring = smem + a.stages * stage_bytes;  // filter ring (window mode with a streamed filter)
-  const int bstage_bytes = a.b_stream ? a.kgroup * stage_b : 0;
-  uint8_t* ctrl = smem_bring + a.b_stages * bstage_bytes;
+  uint8_t* ctrl = smem + a.stages * stage_bytes;
   uint64_t* full_bar = reinterpret_cast<uint64_t*>(ctrl);
   uint64_t* empty_bar = full_bar + kMaxStages;
   uint64_t* acc_full = empty_bar + kMaxStages;     // [4] accumulator buffer ready for its epilogue group(s)
   uint64_t* acc_empty = acc_full + kMaxAccBufs;    // [4] accumulator buffer drained
   uint64_t* res_bar = acc_empty + kMaxAccBufs;     // [2][16] per epilogue warp and staging tile: residual landed
   uint64_t* bres_bar = res_bar + 2 * kEpilogueWarps;  // resident filter landed
-  uint64_t* bfull_bar = bres_bar + 1;                 // [8] filter ring
-  uint64_t* bempty_bar = bfull_bar + kMaxBStages;
-  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bempty_bar + kMaxBStages);
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bres_bar + 1);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
 
   const int warp = threadIdx.x >> 5;
@@ -977,10 +946,10 @@ __global__ void __launch_bounds__(kThreads, 1)
   const uint32_t tmem_cols = acc_stride * nb < 32 ? 32 : acc_stride * nb;
 
   if (warp == kProducerWarp) {
-    // All barriers live in one array (full .. bempty); the lanes of this warp initialise them in
+    // All barriers live in one array (full .. bres); the lanes of this warp initialise them in
     // parallel (a single thread took ~1 us for the 89 of them).  Only the "accumulator drained"
     // barriers expect more than one arrival.
-    constexpr int kBarriers = 2 * kMaxStages + 2 * kMaxAccBufs + 2 * kEpilogueWarps + 1 + 2 * kMaxBStages;
+    constexpr int kBarriers = 2 * kMaxStages + 2 * kMaxAccBufs + 2 * kEpilogueWarps + 1;
     const int first_acc_empty = 2 * kMaxStages + kMaxAccBufs;
     for (int i = lane; i < kBarriers; i += 32) {
       const bool drained = i >= first_acc_empty && i < first_acc_empty + kMaxAccBufs;
@@ -1016,9 +985,6 @@ __global__ void __launch_bounds__(kThreads, 1)
   const uint32_t tmem_base = *tmem_slot;
   // the set-up above overlapped the previous kernel's tail; from here on global memory is touched
   pdl_sync_with_previous_kernel();
-#ifdef PLB_TC_TIMING
-  if (threadIdx.x == 0) a.timing[blockIdx.x * 24 + 10] = clock64() - tt_entry;  // prologue + wait for the previous kernel
-#endif
 
   if (warp == kProducerWarp) {
     // ------------------------------------------------------------ TMA producer
@@ -1026,46 +992,13 @@ __global__ void __launch_bounds__(kThreads, 1)
     // and one elected lane issues the copies.  The loop body is free of divisions: ring position,
     // tap and channel-chunk counters advance incrementally.
     const bool leader = elect_one();
-    TT_DECL(2);
-#ifdef PLB_TC_TIMING
-    const long long tt_begin = clock64();
-#endif
     int s = 0;
     uint32_t empty_parity = 1;  // a fresh barrier passes a wait on parity 1
     bool ok = true;
     const uint32_t smem_base = smem_u32(smem);
-    // filter stream of one tile (window mode with a streamed filter): ksteps / kgroup boxes of
-    // kgroup K steps each into the filter ring
-    int sb = 0;
-    uint32_t bempty_parity = 1;
-#ifdef PLB_TC_TIMING
-    long long tt_bwait = 0;
-#endif
-    const uint32_t bring_base = smem_u32(smem_bring);
-    auto stream_filter = [&](int n0) -> bool {
-      for (int m = 0; m < a.ksteps; m += a.kgroup) {
-#ifdef PLB_TC_TIMING
-        const long long tb0 = clock64();
-#endif
-        if (!mbar_wait(smem_u32(&bempty_bar[sb]), bempty_parity, abort_flag, a.status, FAULT_WAIT_EMPTY)) return false;
-#ifdef PLB_TC_TIMING
-        tt_bwait += clock64() - tb0;
-#endif
-        const uint32_t bar = smem_u32(&bfull_bar[sb]);
-        mbar_expect_tx_if(bar, static_cast<uint32_t>(bstage_bytes), leader);
-        tma_load_3d_if(bring_base + sb * bstage_bytes, &tmB, bar, 0, n0, m, leader);
-        if (++sb == a.b_stages) {
-          sb = 0;
-          bempty_parity ^= 1;
-        }
-      }
-      return true;
-    };
-    bool have_prev = false;
-    int prev_n0 = 0, local = 0;
     if (a.fast_window)
       ok = producer_loop_window_resident(a, &tmA, smem_base, stage_bytes, smem_u32(&full_bar[0]), smem_u32(&empty_bar[0]),
-                                         leader, abort_flag);
+                                         leader, abort_flag, s, empty_parity);
     for (int tile = blockIdx.x; a.slab && !a.fast_window && tile < a.num_tiles && ok; tile += gridDim.x) {
       // one window per tile: rows ty*16 - pad_t ..., columns tx*8 - pad_l ...; cells outside the
       // image are filled with zeros by the copy engine
@@ -1074,9 +1007,7 @@ __global__ void __launch_bounds__(kThreads, 1)
       const int t = tile_m / a.tiles_x;
       const int ty = t % a.tiles_y;
       const int img = t / a.tiles_y;
-      TT_START();
       ok = mbar_wait(smem_u32(&empty_bar[s]), empty_parity, abort_flag, a.status, FAULT_WAIT_EMPTY);
-      TT_STOP(0);
       if (!ok) break;
       const uint32_t bar = smem_u32(&full_bar[s]);
       const uint32_t dst = smem_base + s * stage_bytes;
@@ -1088,31 +1019,13 @@ __global__ void __launch_bounds__(kThreads, 1)
         s = 0;
         empty_parity ^= 1;
       }
-      if (a.b_stream) {
-        // One pass of the filter stream serves a unit = one tile, or two consecutive tiles of this
-        // CTA (pair mode; they have the same channel block).  With four or more window stages the
-        // windows run one unit ahead of the filter stream.
-        const bool unit_done = !a.pair || (local & 1) || tile + static_cast<int>(gridDim.x) >= a.num_tiles;
-        ++local;
-        if (unit_done) {
-          const int n0 = (tile - tile_m * a.tiles_n) * a.bn;
-          if (a.stages >= 2 * (a.pair ? 2 : 1)) {
-            if (have_prev) ok = stream_filter(prev_n0);
-            prev_n0 = n0;
-            have_prev = true;
-          } else {
-            ok = stream_filter(n0);
-          }
-        }
-      }
     }
-    if (a.slab && a.b_stream && have_prev && ok) ok = stream_filter(prev_n0);
     if (a.fast_flat)  // flat tiles: one box of activations (and one of the filter, unless resident) per K step
       ok = producer_loop_flat(a, &tmA, &tmB, &tmA2, &tmB2, smem_base, stage_bytes, stage_a, smem_u32(&full_bar[0]),
-                              smem_u32(&empty_bar[0]), leader, abort_flag);
+                              smem_u32(&empty_bar[0]), leader, abort_flag, s, empty_parity);
     if (a.fast_im2col)
       ok = producer_loop_im2col(a, &tmA, &tmB, smem_base, stage_bytes, stage_a, smem_u32(&full_bar[0]), smem_u32(&empty_bar[0]),
-                                leader, abort_flag);
+                                leader, abort_flag, s, empty_parity);
     for (int tile = blockIdx.x; !a.slab && !a.fast_flat && !a.fast_im2col && tile < a.num_tiles && ok; tile += gridDim.x) {
       const int tile_m = tile / a.tiles_n;
       const int m0 = tile_m * kTileM;
@@ -1128,13 +1041,30 @@ __global__ void __launch_bounds__(kThreads, 1)
       const int ch = p0 * a.stride_h - a.pad_t;
       int r = 0, sx = 0, cc = 0, kb = 0;  // filter row, filter column, channel chunk, K offset in B
       for (int ks = 0; ks < a.ksteps; ++ks) {
-        TT_START();
         ok = mbar_wait(smem_u32(&empty_bar[s]), empty_parity, abort_flag, a.status, FAULT_WAIT_EMPTY);
-        TT_STOP(0);
         if (!ok) break;
         const uint32_t bar = smem_u32(&full_bar[s]);
         const uint32_t dst_a = smem_base + s * stage_bytes;
         const uint32_t dst_b = dst_a + stage_a;
+#ifdef PLB_TC_FAULT_TEST
+        // Test build only: CTA 0 "loses" the copies of the first K step of its first tile (neither armed nor
+        // issued), so the MMA warp's bounded wait for that stage runs out.  Nothing traps, spins or faults.
+        if (a.test_skip_load && blockIdx.x == 0 && tile == 0 && ks == 0) {
+          kb += a.kc;
+          if (++cc == a.cchunks) {
+            cc = 0;
+            if (++sx == a.kw) {
+              sx = 0;
+              ++r;
+            }
+          }
+          if (++s == a.stages) {
+            s = 0;
+            empty_parity ^= 1;
+          }
+          continue;
+        }
+#endif
         mbar_expect_tx_if(bar, static_cast<uint32_t>(stage_bytes), leader);
         if (a.im2col) {
           tma_load_im2col_4d_if(dst_a, &tmA, bar, cc * a.kc, cw, ch, cn, static_cast<uint16_t>(sx * a.dil_w),
@@ -1172,20 +1102,21 @@ __global__ void __launch_bounds__(kThreads, 1)
         }
       }
     }
-#ifdef PLB_TC_TIMING
-    tt_acc[1] = clock64() - tt_begin;
-#endif
-    if (lane == 0) TT_FLUSH(0, 2);
-#ifdef PLB_TC_TIMING
-    if (lane == 0) a.timing[blockIdx.x * 24 + 15] = tt_bwait;
-#endif
+    if (!ok || *abort_flag) {
+      // Some role of this CTA gave up.  Copies this warp has issued may still be in flight into the ring:
+      // give each of them a bounded time to land before the CTA frees its tensor memory and exits.  Stages
+      // below s were armed in the current round (their phase has parity empty_parity ^ 1), the others in the
+      // round before.
+      for (int j = 0; j < a.stages; ++j)
+        mbar_wait_drain(smem_u32(&full_bar[j]), j < s ? (empty_parity ^ 1u) : empty_parity);
+      if (a.resident_b) mbar_wait_drain(smem_u32(bres_bar), 0);
+    }
   } else if (warp == kMmaWarp) {
     // ------------------------------------------------------------ MMA issuer
     // Again the whole warp runs the loop and an elected lane issues: matrix descriptors are
     // warp-uniform values, built from 32-bit halves with as few instructions per MMA as possible
     // (a 128 x 64 x 32 MMA occupies the tensor core for only ~57 cycles).
     const bool leader = elect_one();
-    TT_DECL(4);
     // instruction descriptor: D=s32, A=B=s8, both K-major, N=bn, M=128
     const uint32_t idesc = (2u << 4) | (1u << 7) | (1u << 10) | (static_cast<uint32_t>(a.bn >> 3) << 17) |
                            (static_cast<uint32_t>(kTileM >> 4) << 24);
@@ -1201,7 +1132,7 @@ __global__ void __launch_bounds__(kThreads, 1)
     const uint32_t col_lo = static_cast<uint32_t>(a.dil_w * a.kc) >> 4;
     const uint32_t plane_lo = static_cast<uint32_t>(a.plane_bytes) >> 4;
     int window_shape = 0;  // which unrolled issue sequence applies
-    if (a.slab && !a.b_stream) {  // other filter sizes: taps in a loop, the inside of a tap unrolled
+    if (a.slab) {  // other filter sizes: taps in a loop, the inside of a tap unrolled
       if (a.cchunks == 1 && mma_per_stage == 1) window_shape = 11;
       if (a.cchunks == 1 && mma_per_stage == 2) window_shape = 12;
       if (a.cchunks == 1 && mma_per_stage == 4) window_shape = 14;
@@ -1216,19 +1147,11 @@ __global__ void __launch_bounds__(kThreads, 1)
     }
     int s = 0, it = 0;
     uint32_t full_parity = 0;
-    int sb = 0;
-    uint32_t bfull_parity = 0;
-    const uint32_t bring_lo = ((smem_u32(smem_bring) >> 4) & 0x3FFFu) | lo_flags;
-    const uint32_t bstage_lo = static_cast<uint32_t>(bstage_bytes) >> 4;
     bool ok = true;
     if (a.resident_b) {
       ok = mbar_wait(smem_u32(bres_bar), 0, abort_flag, a.status, FAULT_WAIT_FULL);
       tc_fence_after();
     }
-#ifdef PLB_TC_TIMING
-    if (lane == 0) a.timing[blockIdx.x * 24 + 11] = clock64() - tt_entry;  // resident filter landed
-    bool tt_first = true;
-#endif
     const uint32_t bres_lo = ((smem_u32(smem_bres) >> 4) & 0x3FFFu) | lo_flags;
     const uint32_t stage_b_lo = static_cast<uint32_t>(stage_b) >> 4;
     const uint32_t stage_lo = static_cast<uint32_t>(stage_bytes) >> 4;
@@ -1259,100 +1182,20 @@ __global__ void __launch_bounds__(kThreads, 1)
     }
     for (int tile = blockIdx.x; !a.fast_mma && !a.fast_window && tile < a.num_tiles && ok; tile += gridDim.x, ++it) {
       int buf = it & nb_mask;
-      TT_START();
       ok = mbar_wait(smem_u32(&acc_empty[buf]), ((it >> nb_shift) & 1) ^ 1, abort_flag, a.status, FAULT_WAIT_ACCUM);
-      TT_STOP(0);
       if (!ok) break;
       tc_fence_after();
       const uint32_t d_tmem = tmem_base + buf * acc_stride;
       uint32_t accumulate = 0;
       if (a.slab) {
-        TT_START();
         ok = mbar_wait(smem_u32(&full_bar[s]), full_parity, abort_flag, a.status, FAULT_WAIT_FULL);
-        TT_STOP(1);
         if (!ok) break;
         tc_fence_after();
-        TT_START();
         // Tile row g (8 pixels) is window row g + r*dil_h starting at column sx*dil_w.  The swizzle
         // is a function of the shared-memory address, so a start address shifted by whole
         // pixels addresses the same bytes the copy engine wrote.
         const uint32_t slab_lo = ring_lo + s * stage_lo;
-        if (a.b_stream) {
-          // Pair mode: the CTA's next tile (same channel block) is accumulated in the next TMEM buffer
-          // from its own window during the same pass over the filter stream, which halves the
-          // filter bytes fetched per output.
-          const bool pair = a.pair && tile + static_cast<int>(gridDim.x) < a.num_tiles;
-          int s2 = s + 1 == a.stages ? 0 : s + 1;
-          uint32_t d_tmem2 = 0, slab2_delta = 0;
-          if (pair) {
-            const int buf2 = (it + 1) & nb_mask;
-            ok = mbar_wait(smem_u32(&acc_empty[buf2]), (((it + 1) >> nb_shift) & 1) ^ 1, abort_flag, a.status,
-                           FAULT_WAIT_ACCUM);
-            if (!ok) break;
-            ok = mbar_wait(smem_u32(&full_bar[s2]), s2 == 0 ? full_parity ^ 1 : full_parity, abort_flag, a.status,
-                           FAULT_WAIT_FULL);
-            if (!ok) break;
-            tc_fence_after();
-            d_tmem2 = tmem_base + buf2 * acc_stride;
-            slab2_delta = (ring_lo + s2 * stage_lo) - slab_lo;  // modular difference of the descriptor fields
-          }
-          // K steps in filter order (filter row, filter column, channel chunk); every kgroup of them
-          // shares one box of the filter ring
-          uint32_t row_a = slab_lo, tap_a = slab_lo, a_lo = slab_lo;
-          int sx = 0, cc = 0;
-          for (int m = 0; m < a.ksteps && ok; m += a.kgroup) {
-            TT_STOP(2);
-            TT_START();
-            ok = mbar_wait(smem_u32(&bfull_bar[sb]), bfull_parity, abort_flag, a.status, FAULT_WAIT_FULL);
-            TT_STOP(3);
-            TT_START();
-            if (!ok) break;
-            tc_fence_after();
-            uint32_t b_lo = bring_lo + sb * bstage_lo;
-            for (int g = 0; g < a.kgroup; ++g, b_lo += stage_b_lo) {
-              if (mma_per_stage == 4) issue_kstep<4>(d_tmem, a_lo, hi_a, b_lo, hi_b, idesc, accumulate, leader);
-              else if (mma_per_stage == 2) issue_kstep<2>(d_tmem, a_lo, hi_a, b_lo, hi_b, idesc, accumulate, leader);
-              else issue_kstep<1>(d_tmem, a_lo, hi_a, b_lo, hi_b, idesc, accumulate, leader);
-              if (pair) {
-                const uint32_t a2 = a_lo + slab2_delta;
-                if (mma_per_stage == 4) issue_kstep<4>(d_tmem2, a2, hi_a, b_lo, hi_b, idesc, accumulate, leader);
-                else if (mma_per_stage == 2) issue_kstep<2>(d_tmem2, a2, hi_a, b_lo, hi_b, idesc, accumulate, leader);
-                else issue_kstep<1>(d_tmem2, a2, hi_a, b_lo, hi_b, idesc, accumulate, leader);
-              }
-              accumulate = 1;
-              a_lo += plane_lo;
-              if (++cc == a.cchunks) {
-                cc = 0;
-                tap_a += col_lo;
-                if (++sx == a.kw) {
-                  sx = 0;
-                  row_a += row_lo;
-                  tap_a = row_a;
-                }
-                a_lo = tap_a;
-              }
-            }
-            tc_commit_if(smem_u32(&bempty_bar[sb]), leader);
-            if (++sb == a.b_stages) {
-              sb = 0;
-              bfull_parity ^= 1;
-            }
-          }
-          if (!ok) break;
-          if (pair) {
-            // the first tile of the pair is complete: release its window and publish its accumulator
-            // here; the common tail below does the same for the second tile
-            tc_commit_if(smem_u32(&empty_bar[s]), leader);
-            tc_commit_if(smem_u32(&acc_full[buf]), leader);
-            if (++s == a.stages) {
-              s = 0;
-              full_parity ^= 1;
-            }
-            tile += gridDim.x;
-            ++it;
-            buf = it & nb_mask;
-          }
-        } else if (window_shape == 1) {
+        if (window_shape == 1) {
           issue_window<3, 3, 1, 2>(d_tmem, slab_lo, row_lo, col_lo, plane_lo, hi_a, bres_lo, stage_b_lo, hi_b, idesc, leader);
         } else if (window_shape == 2) {
           issue_window<3, 3, 1, 4>(d_tmem, slab_lo, row_lo, col_lo, plane_lo, hi_a, bres_lo, stage_b_lo, hi_b, idesc, leader);
@@ -1387,7 +1230,6 @@ __global__ void __launch_bounds__(kThreads, 1)
           }
         }
         tc_commit_if(smem_u32(&empty_bar[s]), leader);
-        TT_STOP(2);
         if (++s == a.stages) {
           s = 0;
           full_parity ^= 1;
@@ -1395,25 +1237,17 @@ __global__ void __launch_bounds__(kThreads, 1)
       }
       uint32_t b_res_lo = bres_lo;
       for (int ks = 0; !a.slab && ks < a.ksteps; ++ks, b_res_lo += stage_b_lo) {
-        TT_START();
         ok = mbar_wait(smem_u32(&full_bar[s]), full_parity, abort_flag, a.status, FAULT_WAIT_FULL);
-        TT_STOP(1);
         if (!ok) break;
-#ifdef PLB_TC_TIMING
-        if (tt_first && lane == 0) a.timing[blockIdx.x * 24 + 12] = clock64() - tt_entry;  // first operands landed
-        tt_first = false;
-#endif
         tc_fence_after();
         const uint32_t a_lo = ring_lo + s * stage_lo;
         const uint32_t b_lo = a.resident_b ? b_res_lo : a_lo + (static_cast<uint32_t>(stage_a) >> 4);
         // advance 32 bytes of K inside the swizzle span: +2 in the (addr >> 4) field
-        TT_START();
         if (mma_per_stage == 4) issue_kstep<4>(d_tmem, a_lo, hi_a, b_lo, hi_b, idesc, accumulate, leader);
         else if (mma_per_stage == 2) issue_kstep<2>(d_tmem, a_lo, hi_a, b_lo, hi_b, idesc, accumulate, leader);
         else issue_kstep<1>(d_tmem, a_lo, hi_a, b_lo, hi_b, idesc, accumulate, leader);
         accumulate = 1;
         tc_commit_if(smem_u32(&empty_bar[s]), leader);  // frees the stage when these MMAs retire
-        TT_STOP(2);
         if (++s == a.stages) {
           s = 0;
           full_parity ^= 1;
@@ -1439,10 +1273,6 @@ __global__ void __launch_bounds__(kThreads, 1)
       }
       tc_commit_if(smem_u32(&acc_full[buf]), leader);  // accumulator complete (or drained on a fault)
     }
-    if (lane == 0) TT_FLUSH(2, 4);
-#ifdef PLB_TC_TIMING
-    if (lane == 0) a.timing[blockIdx.x * 24 + 13] = clock64() - tt_entry;  // all MMAs issued
-#endif
   } else {
     // ------------------------------------------------------------ epilogue groups
     if (a.sb_cols > 0) {
@@ -1483,10 +1313,6 @@ __global__ void __launch_bounds__(kThreads, 1)
     bool pf_ready = false;
     bool stores_pending = false;
     bool ok = true;
-    TT_DECL(4);
-#ifdef PLB_TC_TIMING
-    long long tt_fence = 0, tt_issue = 0;
-#endif
     // one channel tile (flat 1x1 layers with few channels, where a tile is little work): no divisions per tile
     const bool one_n = MODE != OUT_ADD_RELU && !a.slab && a.tiles_n == 1;
     for (int it = first_it; ok; it += it_stride) {
@@ -1524,18 +1350,14 @@ __global__ void __launch_bounds__(kThreads, 1)
             }
           }
           if (!waited) {
-            TT_START();
             ok = mbar_wait(smem_u32(&acc_full[my_buf]), (it >> nb_shift) & 1, abort_flag, a.status, FAULT_WAIT_ACCUM);
-            TT_STOP(0);
             tc_fence_after();
             waited = true;
             if (!ok) break;
           }
-          TT_START();
           uint32_t r[32];
           tc_ld32(lane_addr + static_cast<uint32_t>(c), r);
           tc_wait_ld();
-          TT_STOP(2);
           // where is this warp's next chunk?
           int nc = c + 32, nrow0 = row0, ncol;
           bool nvalid = true;
@@ -1550,7 +1372,6 @@ __global__ void __launch_bounds__(kThreads, 1)
             ncol = n0 + nc;
           }
           nvalid = nvalid && ncol < a.cout && nrow0 < a.m_total;
-          TT_START();
           if (nvalid) {
             // the other staging tile was last read by the stores of the previous chunk
             if (stores_pending && !drained) {
@@ -1564,13 +1385,9 @@ __global__ void __launch_bounds__(kThreads, 1)
               tma_load_2d(pf_tile[pf_cur ^ 1], &tmRes, pf_bar[pf_cur ^ 1], ncol, nrow0);
             }
           }
-          TT_STOP(1);
-          TT_START();
           if (active) {
             ok = mbar_wait(pf_bar[pf_cur], pf_phase[pf_cur], abort_flag, a.status, FAULT_WAIT_FULL);
             pf_phase[pf_cur] ^= 1;
-            TT_STOP(1);
-            TT_START();
             if (!ok) break;
             if (stores_pending && !drained) {  // the int8 staging rows are rewritten below
               if (lane == 0) bulk_wait_read_all();
@@ -1587,7 +1404,6 @@ __global__ void __launch_bounds__(kThreads, 1)
             }
             stores_pending = true;
           }
-          TT_STOP(3);
           pf_ready = nvalid;
           pf_cur ^= 1;
         }
@@ -1613,10 +1429,8 @@ __global__ void __launch_bounds__(kThreads, 1)
           if (n0 + c >= a.cout) break;  // warp-uniform
           if (active && stores_pending && (use_w || have_res || c == cbase)) {
             // the staging tiles are about to be overwritten: earlier stores must have read them
-            TT_START();
             if (lane == 0) bulk_wait_read_all();
             __syncwarp();
-            TT_STOP(1);
             stores_pending = false;
           }
           if (active && have_res && !dual && lane == 0) {
@@ -1625,9 +1439,7 @@ __global__ void __launch_bounds__(kThreads, 1)
             else tma_load_2d(st_w, &tmRes, my_res_bar, n0 + c, row0);
           }
           if (!waited) {
-            TT_START();
             ok = mbar_wait(smem_u32(&acc_full[my_buf]), (it >> nb_shift) & 1, abort_flag, a.status, FAULT_WAIT_ACCUM);
-            TT_STOP(0);
             tc_fence_after();
             waited = true;
             if (!ok) break;
@@ -1652,52 +1464,30 @@ __global__ void __launch_bounds__(kThreads, 1)
                      __float_as_uint(fmaf(__int2float_rn((int)r2[4 * j + 3]), sc.w, bi.w)));
             }
           }
-          TT_START();
           uint32_t r[32];
           tc_ld32(lane_addr + static_cast<uint32_t>(c), r);
           tc_wait_ld();
-          TT_STOP(2);
-#ifdef PLB_TC_TIMING
-          if (a.dbg & 1) continue;  // diagnostics: accumulators are read and dropped (no math, no stores)
-#endif
-          TT_START();
           if (active) {
             if (dual) {
             } else if (have_res) {
               ok = mbar_wait(my_res_bar, res_phase, abort_flag, a.status, FAULT_WAIT_FULL);
               res_phase ^= 1;
-              TT_STOP(1);
-              TT_START();
               if (!ok) break;
             }
             epilogue_chunk_staged<MODE, ACT>(a, ep_scale, ep_bias, r, lane, n0 + c, st_w, st_b + lane * wq,
                                              (c - cbase) >> 4, b_swz, have_res);
-#ifdef PLB_TC_TIMING
-            const long long tf0 = clock64();
-#endif
             if (use_w) {  // make this chunk's staging writes visible to the copy engine
               fence_proxy_async_smem();
               __syncwarp();
             }
-#ifdef PLB_TC_TIMING
-            tt_fence += clock64() - tf0;
-#endif
-#ifdef PLB_TC_TIMING
-            const long long ti0 = clock64();
-#endif
             if (use_w && lane == 0) {
               if (a.slab) tma_store_4d(&tmOutW, st_w, n0 + c, s_w, s_h, s_img);
               else tma_store_2d(&tmOutW, st_w, n0 + c, row0);
               bulk_commit();
             }
-#ifdef PLB_TC_TIMING
-            __syncwarp();
-            tt_issue += clock64() - ti0;
-#endif
             if (use_w) stores_pending = true;
             wrote_b = use_b;
           }
-          TT_STOP(3);
         }
         if (wrote_b) {
           if (!use_w) {  // int8-only output: one fence per tile instead of one per chunk
@@ -1744,17 +1534,12 @@ __global__ void __launch_bounds__(kThreads, 1)
       __syncwarp();
       if (lane == 0) mbar_arrive(smem_u32(&acc_empty[my_buf]));
     }
-    if (STAGED && lane == 0) bulk_wait_all();  // staging memory must outlive the stores reading it
-    if (warp == 0 && lane == 0) TT_FLUSH(6, 4);
-#ifdef PLB_TC_TIMING
-    if (warp == 0 && lane == 0) {
-      a.timing[blockIdx.x * 24 + 16] = tt_fence;
-      a.timing[blockIdx.x * 24 + 17] = tt_issue;
+    if (STAGED && MODE == OUT_ADD_RELU && (!ok || *abort_flag) && lane == 0) {
+      // gave up with a residual tile possibly still on its way into this warp's staging memory
+      mbar_wait_drain(pf_bar[0], a.res_prefetch ? pf_phase[0] : res_phase);
+      if (a.res_prefetch) mbar_wait_drain(pf_bar[1], pf_phase[1]);
     }
-#endif
-#ifdef PLB_TC_TIMING
-    if (warp == 0 && lane == 0) a.timing[blockIdx.x * 24 + 14] = clock64() - tt_entry;  // epilogue warp 0 finished
-#endif
+    if (STAGED && lane == 0) bulk_wait_all();  // staging memory must outlive the stores reading it
   }
   tc_fence_before();
   __syncthreads();
@@ -1841,9 +1626,60 @@ int env_int(const char* name, int dflt) {
   return v && *v ? std::atoi(v) : dflt;
 }
 
+// A switch value of -1 means "planner's choice".
+int sw_or(int value, int dflt) { return value >= 0 ? value : dflt; }
+
+// Everything one launch needs, derived once per (problem, pointers).
+struct IgemmPlan {
+  IgemmArgs a;
+  alignas(64) CUtensorMap tmA, tmB, tmRes, tmOutW, tmOutB, tmA2, tmB2;
+  IgemmKernel kernel;
+  size_t smem;
+  unsigned grid;
+};
+
+std::mutex g_configure_mutex;  // guards the driver entry points and the per-(kernel, device) attribute list
+
 int pick_kc(int cin_pad) { return cin_pad % 128 == 0 ? 128 : (cin_pad % 64 == 0 ? 64 : 32); }
 
 }  // namespace
+
+TcSwitches tc_switches_from_env() {
+  TcSwitches s;
+  s.slab = env_int("PLB_TC_SLAB", -1);
+  s.bn = env_int("PLB_TC_BN", -1);
+  s.stages = env_int("PLB_TC_STAGES", -1);
+  s.acc_bufs = env_int("PLB_TC_ACC_BUFS", -1);
+  s.resident = env_int("PLB_TC_RESIDENT", 1);
+  s.staged = env_int("PLB_TC_STAGED", 1);
+  s.res_prefetch = env_int("PLB_TC_RES_PREFETCH", -1);
+  s.acc_small = env_int("PLB_TC_ACC_SMALL", 1);
+  s.sb_smem = env_int("PLB_TC_SB_SMEM", 1);
+  s.fast_flat = env_int("PLB_TC_FAST_FLAT", 1);
+  s.fast_im2col = env_int("PLB_TC_FAST_IM2COL", 1);
+  s.fast_mma = env_int("PLB_TC_FAST_MMA", 1);
+  s.fast_dual = env_int("PLB_TC_FAST_DUAL", 1);
+  s.fast_window = env_int("PLB_TC_FAST_WINDOW", 1);
+  s.pair = env_int("PLB_TC_PAIR", -1);
+  s.nchw = env_int("PLB_TC_NCHW", -1);
+  s.dw_strip = env_int("PLB_DW_STRIP", -1);
+  return s;
+}
+
+struct IgemmPlanCache {
+  struct Entry {
+    IgemmProblem key;
+    TcSwitches sw;
+    int device;
+    IgemmPlan plan;
+  };
+  std::vector<Entry> entries;
+  size_t next = 0;  // round-robin replacement
+  long hits = 0;
+};
+IgemmPlanCache* igemm_plan_cache_create() { return new IgemmPlanCache; }
+void igemm_plan_cache_destroy(IgemmPlanCache* c) { delete c; }
+long igemm_plan_cache_hits(const IgemmPlanCache* c) { return c ? c->hits : 0; }
 
 bool igemm_tc_supported(const IgemmProblem& p, std::string* why) {
   auto no = [&](const char* msg) {
@@ -1865,13 +1701,21 @@ bool igemm_tc_supported(const IgemmProblem& p, std::string* why) {
   return true;
 }
 
-int igemm_tc_launch(plb_ctx* ctx, const IgemmProblem& p) {
+namespace {
+
+// Derives tile shapes, the shared-memory budget, the kernel instance and all tensor maps of one problem.
+int igemm_tc_plan(plb_ctx* ctx, const IgemmProblem& p, const TcSwitches& sw_, IgemmPlan* plan) {
   std::string why;
   if (!igemm_tc_supported(p, &why)) return fail(PLB_E_UNSUPPORTED, "tensor-core path: %s", why.c_str());
-  int rc = load_driver_entry_points();
-  if (rc) return rc;
+  {
+    std::lock_guard<std::mutex> lock(g_configure_mutex);
+    int rc = load_driver_entry_points();
+    if (rc) return rc;
+  }
 
-  IgemmArgs a;
+  IgemmArgs& a = plan->a;
+  CUtensorMap& tmA = plan->tmA;
+  CUtensorMap& tmB = plan->tmB;
   memset(&a, 0, sizeof(a));
   a.im2col = p.im2col;
   a.m_total = p.m_total;
@@ -1898,7 +1742,7 @@ int igemm_tc_launch(plb_ctx* ctx, const IgemmProblem& p) {
   // (the epilogue works in chunks of 32 columns, so a tile that is not the last one of its row of
   // tiles must be a multiple of 32 wide: halve only down to such widths)
   while (bn > 32 && tiles_m * ((cout16 + bn - 1) / bn) < ctx->sm_count && (bn / 2) % 32 == 0) bn /= 2;
-  bn = env_int("PLB_TC_BN", bn);
+  bn = sw_or(sw_.bn, bn);
   if (bn > cout16) bn = cout16;
   if (bn < cout16 && bn % 32) bn = bn / 32 * 32;
   if (bn < 16 || bn > 256 || bn % 16) return fail(PLB_E_INVALID, "bad channel tile %d", bn);
@@ -1909,7 +1753,7 @@ int igemm_tc_launch(plb_ctx* ctx, const IgemmProblem& p) {
                       (p.out_mode == OUT_ADD_RELU && (p.y_f32 != nullptr || p.residual != nullptr || dual));
   const bool want_b = p.out_mode == OUT_I8 || (p.out_mode == OUT_ADD_RELU && p.y_i8 != nullptr);
   auto aligned16 = [](const void* q) { return (reinterpret_cast<uintptr_t>(q) & 15) == 0; };
-  bool staged = env_int("PLB_TC_STAGED", 1) != 0 && (bn == 32 || bn == 64 || bn == 128 || bn == 256);
+  bool staged = sw_.staged != 0 && (bn == 32 || bn == 64 || bn == 128 || bn == 256);
   if (want_w && (p.ldy % 4 != 0)) staged = false;
   if (want_b && (p.ldy % 16 != 0)) staged = false;
   if (p.out_mode == OUT_ADD_RELU) {
@@ -1921,7 +1765,7 @@ int igemm_tc_launch(plb_ctx* ctx, const IgemmProblem& p) {
   // long runs are bandwidth bound and do better with the wider int8 stores of the plain path.
   const bool short_run = static_cast<long>(tiles_m) * ((p.cout + bn - 1) / bn) <= 3L * ctx->sm_count;
   a.res_prefetch = staged && p.out_mode == OUT_ADD_RELU && p.residual != nullptr && !p.im2col &&
-                   env_int("PLB_TC_RES_PREFETCH", short_run ? 1 : 0) != 0;
+                   sw_or(sw_.res_prefetch, short_run ? 1 : 0) != 0;
   a.staging_w_bytes = staged && want_w ? kEpilogueWarps * (a.res_prefetch ? 8192 : 4096) : 0;
   // With many tiles per CTA four accumulator buffers keep every epilogue group on its own tile;
   // with one or two tiles the drain of the last tile is what is left exposed, so two groups
@@ -1930,7 +1774,7 @@ int igemm_tc_launch(plb_ctx* ctx, const IgemmProblem& p) {
     const long tiles_total = static_cast<long>(tiles_m) * ((p.cout + bn - 1) / bn);
     const bool few = tiles_total <= 2L * ctx->sm_count;
     a.acc_bufs = bn > 128 ? 2 : (few && bn >= 64 ? 2 : 4);  // 8 (tiles of <= 64 columns) is possible and measured equal
-    a.acc_bufs = env_int("PLB_TC_ACC_BUFS", a.acc_bufs);
+    a.acc_bufs = sw_or(sw_.acc_bufs, a.acc_bufs);
     if (dual) a.acc_bufs = 2;
     if (a.acc_bufs != 2 && a.acc_bufs != 4 && a.acc_bufs != 8) return fail(PLB_E_INVALID, "accumulator buffers must be 2, 4 or 8");
     if (a.acc_bufs == 8 && bn > 64) a.acc_bufs = 4;
@@ -1945,7 +1789,7 @@ int igemm_tc_launch(plb_ctx* ctx, const IgemmProblem& p) {
   }
   a.sb_off = a.staging_w_bytes + kEpilogueWarps * a.stage_b_warp;
   a.sb_cols = 0;
-  if (staged && p.out_mode != OUT_ACC && env_int("PLB_TC_SB_SMEM", 1) != 0) {
+  if (staged && p.out_mode != OUT_ACC && sw_.sb_smem != 0) {
     const int cols = (p.cout + 31) / 32 * 32;  // the device arrays are readable up to the next multiple of 64 floats
     if (cols * 8 * (dual ? 2 : 1) <= 16 * 1024) a.sb_cols = cols;
   }
@@ -1960,13 +1804,12 @@ int igemm_tc_launch(plb_ctx* ctx, const IgemmProblem& p) {
   }
   const int tiles_n_h = (p.cout + bn - 1) / bn;
   const int resident_bytes = (a.ksteps * bn * a.kc + 1023) / 1024 * 1024;
-  const bool can_resident = env_int("PLB_TC_RESIDENT", 1) != 0 && tiles_n_h == 1 && resident_bytes <= kMaxResidentB && !dual;
+  const bool can_resident = sw_.resident != 0 && tiles_n_h == 1 && resident_bytes <= kMaxResidentB && !dual;
   a.resident_b = can_resident && tiles_m > ctx->sm_count;  // worth it only when a CTA walks several tiles
   // Slab mode: stride-1 filters with several taps read each input pixel once per tile instead of
   // once per tap.  Output tiles are 16 x 8 pixels, so images much smaller than that waste too
   // many accumulator rows.
   int tiles_m_eff = tiles_m;
-  int slab_stages = 0;
   if (p.im2col && a.taps > 1 && p.stride_h == 1 && p.stride_w == 1 && staged) {
     const int tx = (p.wo + 7) / 8, ty = (p.ho + 15) / 16;
     const int sw_px = 8 + (p.kw - 1) * p.dil_w, sh_px = 16 + (p.kh - 1) * p.dil_h;
@@ -1974,41 +1817,14 @@ int igemm_tc_launch(plb_ctx* ctx, const IgemmProblem& p) {
     const int plane = (sw_px * sh_px * a.kc + 1023) / 1024 * 1024;
     const bool geom_ok = sw_px <= 256 && sh_px <= 256 && sw_px * a.kc <= 0x3FFF * 16;
     const int room = 225 * 1024 - a.staging_bytes - kCtrlBytes - 1024;
-    bool fits = geom_ok && can_resident && 2 * a.cchunks * plane + resident_bytes <= room;
-    bool stream = false;
-    // Off unless asked for (PLB_TC_BSTREAM=1): measured on 128->128 and 256->256 3x3 layers it is no
-    // faster than im2col mode, because with 128-wide tiles every MMA reads 8 KiB of shared memory in
-    // 64 cycles, which is the whole shared-memory bandwidth; the copies into the ring slow it further.
-    if (geom_ok && !fits && env_int("PLB_TC_BSTREAM", 0) != 0) {
-      // The filter does not fit beside the windows: stream it through its own ring, kgroup K steps
-      // per box.  Preferred: four window stages (two pairs of tiles in flight) and at least two
-      // filter boxes; else two window stages.  Larger boxes first (fewer TMA instructions).
-      const int bstep = bn * a.kc;
-      const int slab_stage = a.cchunks * plane;
-      for (int want_slabs = 4; want_slabs >= 2 && !stream; want_slabs -= 2) {
-        for (int g = a.ksteps; g >= 1 && !stream; --g) {
-          if (a.ksteps % g || g * bstep > 48 * 1024) continue;
-          if (want_slabs * slab_stage + 2 * g * bstep > room) continue;
-          stream = fits = true;
-          a.kgroup = g;
-          slab_stages = want_slabs;
-          int bst = (room - want_slabs * slab_stage) / (g * bstep);
-          a.b_stages = bst > kMaxBStages ? kMaxBStages : bst;
-        }
-      }
-    }
-    const int dflt = waste <= 1.35 && fits && (stream || a.resident_b);
-    if (fits && env_int("PLB_TC_SLAB", dflt) != 0) {
+    const bool fits = geom_ok && can_resident && 2 * a.cchunks * plane + resident_bytes <= room;
+    // (Streaming a filter that does not fit through a ring of its own was measured on 128->128 and 256->256
+    // 3x3 layers and was no faster than im2col mode: with 128-wide tiles every MMA reads 8 KiB of shared
+    // memory in 64 cycles, the whole shared-memory bandwidth.  Window mode therefore needs a resident filter.)
+    const int dflt = waste <= 1.35 && fits && a.resident_b;
+    if (fits && sw_or(sw_.slab, dflt) != 0) {
       a.slab = 1;
-      a.resident_b = stream ? 0 : 1;
-      a.b_stream = stream ? 1 : 0;
-      // pairs need the CTA's consecutive tiles to share the channel block
-      {
-        const long tn = (p.cout + bn - 1) / bn;
-        const long total = static_cast<long>(p.batch) * tx * ty * tn;
-        const long grid_h = total < ctx->sm_count ? total : ctx->sm_count;
-        a.pair = stream && env_int("PLB_TC_PAIR", 1) != 0 && grid_h % tn == 0 && total > grid_h;
-      }
+      a.resident_b = 1;
       a.kh = p.kh;
       a.slab_w = sw_px;
       a.slab_rows = sw_px * sh_px;
@@ -2019,22 +1835,20 @@ int igemm_tc_launch(plb_ctx* ctx, const IgemmProblem& p) {
     }
   }
   a.resident_bytes = a.resident_b ? resident_bytes : 0;
-  a.fast_window = a.slab && !a.b_stream && a.resident_b && a.tiles_n == 1 && a.cchunks == 1 && a.kc == 64 && a.kw == 1 &&
-                  (a.kh == 4 || a.kh == 2) && !dual && env_int("PLB_TC_FAST_WINDOW", 1) != 0;
-  a.fast_flat = !a.slab && !p.im2col && (!dual || env_int("PLB_TC_FAST_DUAL", 1) != 0) && env_int("PLB_TC_FAST_FLAT", 1) != 0;
+  a.fast_window = a.slab && a.resident_b && a.tiles_n == 1 && a.cchunks == 1 && a.kc == 64 && a.kw == 1 &&
+                  (a.kh == 4 || a.kh == 2) && !dual && sw_.fast_window != 0;
+  a.fast_flat = !a.slab && !p.im2col && (!dual || sw_.fast_dual != 0) && sw_.fast_flat != 0;
   a.cin_bytes = a.cchunks * a.kc;
-  a.fast_im2col = !a.slab && p.im2col && !dual && env_int("PLB_TC_FAST_IM2COL", 1) != 0;
+  a.fast_im2col = !a.slab && p.im2col && !dual && sw_.fast_im2col != 0;
   // the MMA warp's short loop does not care how the A tile of a stage was fetched: im2col tiles take it too
-  a.fast_mma = a.fast_flat || (!a.slab && !dual && env_int("PLB_TC_FAST_MMA", 1) != 0);
+  a.fast_mma = a.fast_flat || (!a.slab && !dual && sw_.fast_mma != 0);
   const int stage_bytes = (kTileM + bn) * a.kc;
   const int ring_stage_bytes = a.slab ? a.cchunks * a.plane_bytes : (a.resident_b ? kTileM * a.kc : stage_bytes);
   // one CTA per SM: spend (almost) all remaining shared memory on the operand ring
   int stages = (225 * 1024 - a.staging_bytes - kCtrlBytes - a.resident_bytes) / ring_stage_bytes;
-  stages = env_int("PLB_TC_STAGES", stages);
+  stages = sw_or(sw_.stages, stages);
   if (stages > kMaxStages) stages = kMaxStages;
   if (stages < 2) stages = 2;
-  if (a.b_stream) stages = slab_stages;
-  else a.b_stages = 0, a.kgroup = 1;
   a.stages = stages;
   a.ho = p.ho; a.wo = p.wo;
   a.stride_h = p.stride_h; a.stride_w = p.stride_w;
@@ -2044,10 +1858,13 @@ int igemm_tc_launch(plb_ctx* ctx, const IgemmProblem& p) {
   a.ldy = p.ldy;
   a.y = p.y;
   a.scale = p.epi.scale; a.bias = p.epi.bias; a.act = p.epi.act; a.alpha = p.epi.alpha;
-  a.acc_small = p.epi.acc_small && env_int("PLB_TC_ACC_SMALL", 1) != 0;
+  a.acc_small = p.epi.acc_small && sw_.acc_small != 0;
   a.residual = p.residual; a.y_f32 = p.y_f32; a.y_i8 = p.y_i8;
   a.inv_next_scale = p.inv_next_scale;
   a.status = ctx->d_status;
+#ifdef PLB_TC_FAULT_TEST
+  a.test_skip_load = env_int("PLB_TC_TEST_SKIP_LOAD", 0);
+#endif
   if (dual) {
     if (!staged) return fail(PLB_E_UNSUPPORTED, "dual mode needs the staged epilogue (16-byte aligned rows, power-of-two tile)");
     a.dual = 1;
@@ -2061,21 +1878,8 @@ int igemm_tc_launch(plb_ctx* ctx, const IgemmProblem& p) {
     a.ho = p.ho; a.wo = p.wo;
   }
 
-  alignas(64) CUtensorMap tmA;
-  alignas(64) CUtensorMap tmB;
   const CUtensorMapSwizzle sw = swizzle_for(a.kc);
-  if (a.b_stream) {
-    // filter as [K step][cout][kc]: one box = kgroup K steps of bn channels
-    const cuuint64_t kbytes = static_cast<cuuint64_t>(a.taps) * p.cin_pad;
-    cuuint64_t dims[3] = {static_cast<cuuint64_t>(a.kc), static_cast<cuuint64_t>(p.cout), kbytes / a.kc};
-    cuuint64_t strides[2] = {kbytes, static_cast<cuuint64_t>(a.kc)};
-    cuuint32_t box[3] = {static_cast<cuuint32_t>(a.kc), static_cast<cuuint32_t>(bn), static_cast<cuuint32_t>(a.kgroup)};
-    cuuint32_t estr[3] = {1, 1, 1};
-    CUresult r = g_encode_tiled(&tmB, CU_TENSOR_MAP_DATA_TYPE_UINT8, 3, const_cast<int8_t*>(p.b), dims,
-                                strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE, sw,
-                                CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
-    if (r != CUDA_SUCCESS) return fail(PLB_E_CUDA, "cuTensorMapEncodeTiled(filter stream) failed: %d", (int)r);
-  } else {
+  {
     // filter: [cout, taps*cin_pad] bytes, box = kc x bn
     cuuint64_t dims[2] = {static_cast<cuuint64_t>(a.taps) * p.cin_pad, static_cast<cuuint64_t>(p.cout)};
     cuuint64_t strides[1] = {static_cast<cuuint64_t>(a.taps) * p.cin_pad};
@@ -2126,7 +1930,10 @@ int igemm_tc_launch(plb_ctx* ctx, const IgemmProblem& p) {
     if (r != CUDA_SUCCESS) return fail(PLB_E_CUDA, "cuTensorMapEncodeIm2col failed: %d", (int)r);
   }
 
-  alignas(64) CUtensorMap tmA2 = tmB, tmB2 = tmB;
+  CUtensorMap& tmA2 = plan->tmA2;
+  CUtensorMap& tmB2 = plan->tmB2;
+  tmA2 = tmB;
+  tmB2 = tmB;
   if (dual) {
     cuuint64_t dims[2] = {static_cast<cuuint64_t>(p.cin_pad2), static_cast<cuuint64_t>(p.cout)};
     cuuint64_t strides[1] = {static_cast<cuuint64_t>(p.cin_pad2)};
@@ -2161,7 +1968,10 @@ int igemm_tc_launch(plb_ctx* ctx, const IgemmProblem& p) {
     }
   }
   // output-side tensor maps: [m_total, ldy] matrices, 32-row boxes
-  alignas(64) CUtensorMap tmRes = tmB, tmOutW = tmB, tmOutB = tmB;  // unused ones stay valid copies
+  CUtensorMap& tmRes = plan->tmRes;
+  CUtensorMap& tmOutW = plan->tmOutW;
+  CUtensorMap& tmOutB = plan->tmOutB;
+  tmRes = tmOutW = tmOutB = tmB;  // unused ones stay valid copies
   if (staged) {
     auto encode_out = [&](CUtensorMap* tm, const void* base, int elem_bytes, int box_cols,
                           CUtensorMapSwizzle swz) -> CUresult {
@@ -2206,7 +2016,7 @@ int igemm_tc_launch(plb_ctx* ctx, const IgemmProblem& p) {
 
   auto smem_needed = [&]() {
     return static_cast<size_t>(a.staging_bytes) + a.resident_bytes + static_cast<size_t>(stages) * ring_stage_bytes +
-           static_cast<size_t>(a.b_stages) * a.kgroup * bn * a.kc + kCtrlBytes + 1024;
+           kCtrlBytes + 1024;
   };
   if (smem_needed() > 227 * 1024 && a.sb_cols > 0) {
     // a pipeline sized to the last kilobyte (minimum ring next to a large resident filter): the
@@ -2217,43 +2027,67 @@ int igemm_tc_launch(plb_ctx* ctx, const IgemmProblem& p) {
   const size_t smem = smem_needed();
   if (smem > 227 * 1024) return fail(PLB_E_UNSUPPORTED, "pipeline needs %zu bytes of shared memory", smem);
   IgemmKernel kernel = pick_kernel(p.out_mode, p.epi.act, staged);
-  // the attribute belongs to (function, device): remember which pairs have been configured
-  static std::vector<std::pair<const void*, int>> configured;
-  const std::pair<const void*, int> key(reinterpret_cast<const void*>(kernel), ctx->device);
-  if (std::find(configured.begin(), configured.end(), key) == configured.end()) {
-    PLB_CUDA(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024));
-    configured.push_back(key);
+  {
+    // the attribute belongs to (function, device): remember which pairs have been configured
+    std::lock_guard<std::mutex> lock(g_configure_mutex);
+    static std::vector<std::pair<const void*, int>> configured;
+    const std::pair<const void*, int> key(reinterpret_cast<const void*>(kernel), ctx->device);
+    if (std::find(configured.begin(), configured.end(), key) == configured.end()) {
+      PLB_CUDA(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024));
+      configured.push_back(key);
+    }
   }
   const long tiles = static_cast<long>(tiles_m_eff) * a.tiles_n;
   if (tiles > 0x7fffffffL) return fail(PLB_E_UNSUPPORTED, "too many tiles");
   a.num_tiles = static_cast<int>(tiles);
-  const unsigned grid = static_cast<unsigned>(tiles < ctx->sm_count ? tiles : ctx->sm_count);
-#ifdef PLB_TC_TIMING
-  static long long* d_timing = nullptr;
-  if (!d_timing) PLB_CUDA(cudaMalloc(&d_timing, 256 * 24 * sizeof(long long)));
-  PLB_CUDA(cudaMemsetAsync(d_timing, 0, 256 * 24 * sizeof(long long), ctx->stream));
-  a.timing = d_timing;
-  a.dbg = env_int("PLB_TC_DBG", 0);
-#endif
-  PLB_CUDA(launch_kernel(kernel, dim3(grid), dim3(kThreads), smem, ctx->stream, tmA, tmB, tmRes, tmOutW,
-                         tmOutB, tmA2, tmB2, a));
-#ifdef PLB_TC_TIMING
-  if (env_int("PLB_TC_TIMING_PRINT", 0)) {
-    std::vector<long long> h(256 * 24);
-    PLB_CUDA(cudaStreamSynchronize(ctx->stream));
-    PLB_CUDA(cudaMemcpy(h.data(), d_timing, h.size() * sizeof(long long), cudaMemcpyDeviceToHost));
-    double avg[24] = {};
-    for (unsigned b = 0; b < grid; ++b)
-      for (int i = 0; i < 24; ++i) avg[i] += static_cast<double>(h[b * 24 + i]) / grid;
-    fprintf(stderr,
-            "[tc timing] tiles %ld grid %u slab %d bn %d kc %d ksteps %d stages %d | producer: wait_empty %.0f total %.0f | "
-            "mma: wait_acc_empty %.0f wait_full %.0f issue %.0f wait_filter %.0f (producer wait_filter_slot %.0f) | epilogue warp0: wait_acc_full %.0f wait_stores+residual %.0f "
-            "tmem_ld %.0f math+store %.0f (of which fence %.0f, store issue %.0f) | since entry: roles start %.0f, filter resident %.0f, first operands %.0f, "
-            "MMAs issued %.0f, epilogue warp0 done %.0f (cycles per CTA)\n",
-            tiles, grid, a.slab, a.bn, a.kc, a.ksteps, a.stages, avg[0], avg[1], avg[2], avg[3], avg[4], avg[5], avg[15], avg[6], avg[7],
-            avg[8], avg[9], avg[16], avg[17], avg[10], avg[11], avg[12], avg[13], avg[14]);
+  plan->kernel = kernel;
+  plan->smem = smem;
+  plan->grid = static_cast<unsigned>(tiles < ctx->sm_count ? tiles : ctx->sm_count);
+  return PLB_OK;
+}
+
+}  // namespace
+
+int igemm_tc_launch(plb_ctx* ctx, const IgemmProblem& p, IgemmPlanCache* cache) {
+  static const TcSwitches kDefaults;
+  const TcSwitches& sw = p.sw ? *p.sw : kDefaults;
+  const IgemmPlan* plan = nullptr;
+  IgemmPlan local;
+  if (cache) {
+    for (auto& e : cache->entries) {
+      if (e.device == ctx->device && memcmp(&e.key, &p, sizeof(p)) == 0 && memcmp(&e.sw, &sw, sizeof(sw)) == 0) {
+        plan = &e.plan;
+        ++cache->hits;
+        break;
+      }
+    }
+    if (!plan) {
+      constexpr size_t kMaxEntries = 8;
+      IgemmPlanCache::Entry e;
+      memcpy(&e.key, &p, sizeof(p));
+      e.sw = sw;
+      e.device = ctx->device;
+      int rc = igemm_tc_plan(ctx, p, sw, &e.plan);
+      if (rc) return rc;
+      e.plan.a.status = nullptr;  // filled per launch: the status word belongs to the ctx
+      if (cache->entries.size() < kMaxEntries) {
+        cache->entries.push_back(e);
+        plan = &cache->entries.back().plan;
+      } else {
+        cache->entries[cache->next] = e;
+        plan = &cache->entries[cache->next].plan;
+        cache->next = (cache->next + 1) % kMaxEntries;
+      }
+    }
+  } else {
+    int rc = igemm_tc_plan(ctx, p, sw, &local);
+    if (rc) return rc;
+    plan = &local;
   }
-#endif
+  IgemmArgs a = plan->a;
+  a.status = ctx->d_status;
+  PLB_CUDA(launch_kernel(plan->kernel, dim3(plan->grid), dim3(kThreads), plan->smem, ctx->stream, plan->tmA, plan->tmB,
+                         plan->tmRes, plan->tmOutW, plan->tmOutB, plan->tmA2, plan->tmB2, a));
   ctx->launches++;
   if (a.slab) ctx->window_launches++;
   return PLB_OK;

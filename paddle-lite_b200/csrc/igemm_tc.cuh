@@ -11,6 +11,26 @@ enum OutMode : int {
   OUT_ADD_RELU = 3,  // v = fma(acc, scale, bias) + residual; relu; optional f32 and calib-int8 stores
 };
 
+// Tuning switches of the tensor-core kernel.  They are read from the environment (PLB_TC_*) ONCE,
+// when a layer is prepared, and travel with the prepared layer; -1 means "let the planner decide".
+// Nothing on the run path reads the environment.
+struct TcSwitches {
+  int slab = -1;          // PLB_TC_SLAB: window mode off (0) / forced wherever it fits (1)
+  int bn = -1;            // PLB_TC_BN: channel tile
+  int stages = -1;        // PLB_TC_STAGES: operand ring depth
+  int acc_bufs = -1;      // PLB_TC_ACC_BUFS: accumulator buffers in tensor memory (2, 4, 8)
+  int resident = 1;       // PLB_TC_RESIDENT=0: never keep the filter in shared memory
+  int staged = 1;         // PLB_TC_STAGED=0: epilogue with direct global accesses
+  int res_prefetch = -1;  // PLB_TC_RES_PREFETCH: residual tile fetched one chunk ahead
+  int acc_small = 1;      // PLB_TC_ACC_SMALL=0: int -> float through the conversion pipe always
+  int sb_smem = 1;        // PLB_TC_SB_SMEM=0: scale / bias tables stay in global memory
+  int fast_flat = 1, fast_im2col = 1, fast_mma = 1, fast_dual = 1, fast_window = 1;  // PLB_TC_FAST_*=0: generic role loops
+  int pair = -1;          // PLB_TC_PAIR: two-SM tiles (cta_group::2) off (0) / forced wherever they fit (1)
+  int nchw = -1;          // PLB_TC_NCHW: NCHW-native 1x1 kernel off (0) / forced wherever it fits (1)
+  int dw_strip = -1;      // PLB_DW_STRIP: depthwise 3x3 rows per strip (0 = the register-tiled kernel)
+};
+TcSwitches tc_switches_from_env();
+
 // One launch computes D[m, n] = sum_k A[m, k] * B[n, k] over int8 operands with int32
 // accumulation and applies the epilogue.  m indexes output pixels (or fc rows), n output
 // channels.  A is either a plain row-major [m_total, cin_pad] matrix (flat) or the
@@ -45,11 +65,20 @@ struct IgemmProblem {
   const int8_t* b2;       // [cout, cin_pad2]
   const float* scale2;    // [cout] folded ws * in_s of the shortcut
   const float* bias2;     // [cout]
+  const TcSwitches* sw;   // nullptr: defaults
 };
+
+// Plans (tile shapes, tensor maps, kernel choice) of the problems a prepared layer has been run on.
+// A run with the same pointers and sizes as an earlier one re-launches the stored plan without
+// re-deriving it or re-encoding tensor maps.  Owned by the prepared layer; not thread-safe.
+struct IgemmPlanCache;
+IgemmPlanCache* igemm_plan_cache_create();
+void igemm_plan_cache_destroy(IgemmPlanCache* c);
+long igemm_plan_cache_hits(const IgemmPlanCache* c);
 
 // Whether the tensor-core kernel can take this problem (shape and alignment rules).
 bool igemm_tc_supported(const IgemmProblem& p, std::string* why);
 // Enqueue on ctx->stream.  Returns PLB_OK or an error code.
-int igemm_tc_launch(plb_ctx* ctx, const IgemmProblem& p);
+int igemm_tc_launch(plb_ctx* ctx, const IgemmProblem& p, IgemmPlanCache* cache = nullptr);
 
 }  // namespace plb

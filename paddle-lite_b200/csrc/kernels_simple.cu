@@ -1176,8 +1176,7 @@ int dwconv_launch(plb_ctx* ctx, const ConvGeom& g, const int8_t* x, const int8_t
     if (total == 0) return PLB_OK;
     const bool i8 = out.mode == OUT_I8;
     // column-strip kernel (default): long strips (few halo rows) as long as every SM still gets two blocks
-    const char* strip_env = std::getenv("PLB_DW_STRIP");
-    int strip = strip_env ? std::atoi(strip_env) : -1;
+    int strip = g.dw_strip;  // PLB_DW_STRIP as read when the layer was prepared; -1 = cost model
     const long bx = (static_cast<long>(cq) * tiles_x + kDwBlock - 1) / kDwBlock;
     if (strip < 0) {
       // rows per strip: a block costs (input rows it reads) and the blocks run in waves of four per SM

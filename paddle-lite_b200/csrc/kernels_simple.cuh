@@ -15,6 +15,7 @@ struct ConvGeom {
   int groups;
   int ho, wo;
   int cg_pad;                 // filter row length per tap: [cout][kh][kw][cg_pad]
+  int dw_strip;               // depthwise 3x3: output rows per strip (0 = register-tiled kernel, -1 = cost model)
 };
 
 struct OutSpec {

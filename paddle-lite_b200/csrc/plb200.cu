@@ -4,6 +4,7 @@
 #include <cmath>
 #include <cstdlib>
 #include <memory>
+#include <mutex>
 
 #include "igemm_tc.cuh"
 #include "kernels_simple.cuh"
@@ -123,6 +124,9 @@ struct plb_conv {
   DeviceBuf scale_f32, bias_f32, scale_i8, bias_i8;
   float alpha_f32 = 0.f, alpha_i8 = 0.f;
   bool acc_small = false;  // 128 * max over channels of sum |w| < 2^22: accumulators convert to float exactly by the mantissa trick
+  TcSwitches sw;           // tuning switches, read from the environment when the layer was prepared
+  IgemmPlanCache* plans = nullptr;  // tile plans and tensor maps of the (batch, pointers) this layer has run on
+  ~plb_conv() { igemm_plan_cache_destroy(plans); }
 };
 
 struct plb_fc {
@@ -134,6 +138,9 @@ struct plb_fc {
   DeviceBuf scale_f32, bias_f32, scale_i8, bias_i8;
   float alpha_f32 = 0.f, alpha_i8 = 0.f;
   bool acc_small = false;
+  TcSwitches sw;
+  IgemmPlanCache* plans = nullptr;
+  ~plb_fc() { igemm_plan_cache_destroy(plans); }
 };
 
 struct plb_sparse {
@@ -154,6 +161,7 @@ struct plb_sparse {
 constexpr size_t kStaticScratchBytes = size_t(8) << 20;
 static __device__ __align__(256) unsigned char g_static_scratch[kStaticScratchBytes];
 static void* g_static_scratch_addr[64] = {nullptr};  // per device ordinal
+static std::mutex g_static_scratch_mutex;            // first-use lookups from several host threads
 
 extern "C" {
 
@@ -177,6 +185,8 @@ int plb_ctx_create(int device, void* cuda_stream, plb_ctx** out) {
   c->sm_count = prop.multiProcessorCount;
   PLB_CUDA(cudaMalloc(&c->d_status, 2 * sizeof(int)));
   PLB_CUDA(cudaMemset(c->d_status, 0, 2 * sizeof(int)));
+  PLB_CUDA(cudaMallocHost(&c->h_status, 2 * sizeof(int)));
+  c->h_status[0] = c->h_status[1] = 0;
   *out = c.release();
   return PLB_OK;
 }
@@ -187,19 +197,29 @@ void plb_ctx_destroy(plb_ctx* ctx) {
   cudaStreamSynchronize(ctx->stream);
   if (ctx->ws && ctx->ws_owned) cudaFree(ctx->ws);
   if (ctx->d_status) cudaFree(ctx->d_status);
+  if (ctx->h_status) cudaFreeHost(ctx->h_status);
   delete ctx;
+}
+
+// Waits for the ctx stream and reports (and clears) a fault recorded by a kernel.  The status word
+// rides back on the same stream in front of the wait, so a host-side wait costs one synchronisation.
+static int wait_and_check_status(plb_ctx* ctx) {
+  PLB_CUDA(cudaMemcpyAsync(ctx->h_status, ctx->d_status, 2 * sizeof(int), cudaMemcpyDeviceToHost, ctx->stream));
+  PLB_CUDA(cudaStreamSynchronize(ctx->stream));
+  if (ctx->h_status[0] != 0) {
+    const int code = ctx->h_status[0], block = ctx->h_status[1];
+    ctx->h_status[0] = ctx->h_status[1] = 0;
+    cudaMemsetAsync(ctx->d_status, 0, 2 * sizeof(int), ctx->stream);
+    cudaStreamSynchronize(ctx->stream);
+    return fail(PLB_E_DEVICE, "kernel fault %d (pipeline wait ran out) in block %d", code, block);
+  }
+  return PLB_OK;
 }
 
 int plb_ctx_sync(plb_ctx* ctx) {
   PLB_REQUIRE(ctx != nullptr, "ctx must not be null");
-  PLB_CUDA(cudaStreamSynchronize(ctx->stream));
-  int st[2] = {0, 0};
-  PLB_CUDA(cudaMemcpy(st, ctx->d_status, sizeof(st), cudaMemcpyDeviceToHost));
-  if (st[0] != 0) {
-    cudaMemset(ctx->d_status, 0, sizeof(st));
-    return fail(PLB_E_DEVICE, "kernel fault %d (pipeline wait ran out) in block %d", st[0], st[1]);
-  }
-  return PLB_OK;
+  PLB_CUDA(cudaSetDevice(ctx->device));
+  return wait_and_check_status(ctx);
 }
 
 int plb_ctx_set_workspace(plb_ctx* ctx, void* dptr, size_t bytes) {
@@ -215,6 +235,7 @@ int plb_ctx_set_workspace(plb_ctx* ctx, void* dptr, size_t bytes) {
 
 long plb_ctx_launch_count(const plb_ctx* ctx) { return ctx ? ctx->launches : 0; }
 long plb_ctx_window_launch_count(const plb_ctx* ctx) { return ctx ? ctx->window_launches : 0; }
+size_t plb_ctx_workspace_size(const plb_ctx* ctx) { return ctx ? ctx->ws_bytes : 0; }
 
 // ------------------------------------------------------------------ conv
 
@@ -245,6 +266,8 @@ int plb_conv_prepare(plb_ctx* ctx, const plb_conv_desc* desc, const int8_t* filt
   c->d = d;
   c->ho = ho;
   c->wo = wo;
+  c->sw = tc_switches_from_env();
+  c->plans = igemm_plan_cache_create();
   const int cig = d.cin / d.groups;
   const bool depthwise = d.groups == d.cin && d.cin == d.cout;
   const int taps = d.kh * d.kw;
@@ -345,6 +368,8 @@ int plb_conv_out_dims(const plb_conv* conv, int* ho, int* wo) {
   return PLB_OK;
 }
 
+long plb_conv_plan_cache_hits(const plb_conv* conv) { return conv ? igemm_plan_cache_hits(conv->plans) : 0; }
+
 void plb_conv_destroy(plb_conv* conv) {
   if (!conv) return;
   cudaSetDevice(conv->ctx->device);
@@ -408,7 +433,8 @@ int conv_core(plb_conv* c, const int8_t* x, int batch, const OutSpec& out) {
     p.inv_next_scale = out.inv_next_scale;
     p.a2 = out.a2; p.b2 = out.b2; p.im2col2 = out.im2col2; p.h2 = out.h2; p.w2 = out.w2; p.cin_pad2 = out.cin_pad2;
     p.stride2_h = out.stride2_h; p.stride2_w = out.stride2_w; p.scale2 = out.scale2; p.bias2 = out.bias2;
-    return igemm_tc_launch(ctx, p);
+    p.sw = &c->sw;
+    return igemm_tc_launch(ctx, p, c->plans);
   }
   ConvGeom g;
   g.batch = batch; g.cin = d.cin; g.h = d.h; g.w = d.w; g.cin_stride = c->cin_pad;
@@ -416,6 +442,7 @@ int conv_core(plb_conv* c, const int8_t* x, int batch, const OutSpec& out) {
   g.stride_h = d.stride_h; g.stride_w = d.stride_w; g.pad_t = d.pad_top; g.pad_l = d.pad_left;
   g.dil_h = d.dil_h; g.dil_w = d.dil_w; g.groups = d.groups; g.ho = c->ho; g.wo = c->wo;
   g.cg_pad = c->cg_pad;
+  g.dw_strip = c->sw.dw_strip;
   if (c->kind == 2) return dwconv_launch(ctx, g, x, c->w.as<int8_t>(), out);
   return conv_direct_launch(ctx, g, x, c->w.as<int8_t>(), out);
 }
@@ -529,14 +556,18 @@ int plb_conv_run_static(plb_conv* conv, const int8_t* x, void* y, int batch) {
                 batch, need, kStaticScratchBytes);
   PLB_REQUIRE(ctx->device >= 0 && ctx->device < 64, "device ordinal %d not supported here", ctx->device);
   PLB_CUDA(cudaSetDevice(ctx->device));
-  if (g_static_scratch_addr[ctx->device] == nullptr) {
-    // first call on this device: resolve the device address of the array (the host-side name
-    // is not a device pointer)
-    void* addr = nullptr;
-    PLB_CUDA(cudaGetSymbolAddress(&addr, g_static_scratch));
-    g_static_scratch_addr[ctx->device] = addr;
+  unsigned char* base = nullptr;
+  {
+    std::lock_guard<std::mutex> lock(g_static_scratch_mutex);
+    if (g_static_scratch_addr[ctx->device] == nullptr) {
+      // first call on this device: resolve the device address of the array (the host-side name
+      // is not a device pointer)
+      void* addr = nullptr;
+      PLB_CUDA(cudaGetSymbolAddress(&addr, g_static_scratch));
+      g_static_scratch_addr[ctx->device] = addr;
+    }
+    base = static_cast<unsigned char*>(g_static_scratch_addr[ctx->device]);
   }
-  unsigned char* base = static_cast<unsigned char*>(g_static_scratch_addr[ctx->device]);
   const size_t x_bytes = staged_input_bytes(conv, batch);
   int8_t* xs = reinterpret_cast<int8_t*>(base);
   void* ys = base + x_bytes;
@@ -626,6 +657,8 @@ int plb_fc_prepare(plb_ctx* ctx, int k, int n, int act, float act_alpha, float i
   f->n = n;
   f->act = act;
   f->out_dtype = out_dtype;
+  f->sw = tc_switches_from_env();
+  f->plans = igemm_plan_cache_create();
   f->tc = (k % 32) == 0;
   f->k_pad = f->tc ? k : static_cast<int>(align_up(k, 4));
   std::vector<int8_t> wt(static_cast<size_t>(n) * f->k_pad, 0);  // [n][k]: K-major rows
@@ -672,7 +705,8 @@ static int fc_run_mode(plb_fc* f, const int8_t* x, void* y, int m, int mode) {
     p.a = x; p.im2col = 0; p.cin_pad = f->k; p.kh = p.kw = 1;
     p.m_total = m; p.b = f->wt.as<int8_t>(); p.cout = f->n;
     p.out_mode = mode; p.y = y; p.ldy = f->n; p.epi = e;
-    return igemm_tc_launch(ctx, p);
+    p.sw = &f->sw;
+    return igemm_tc_launch(ctx, p, f->plans);
   }
   // rows of x are not TMA-addressable: CUDA-core kernel on the same operands
   if (f->k_pad != f->k)
@@ -681,6 +715,7 @@ static int fc_run_mode(plb_fc* f, const int8_t* x, void* y, int m, int mode) {
   memset(&g, 0, sizeof(g));
   g.batch = m; g.cin = f->k; g.h = 1; g.w = 1; g.cin_stride = f->k; g.cout = f->n; g.kh = g.kw = 1;
   g.stride_h = g.stride_w = 1; g.dil_h = g.dil_w = 1; g.groups = 1; g.ho = g.wo = 1; g.cg_pad = f->k_pad;
+  g.dw_strip = -1;
   OutSpec o;
   memset(&o, 0, sizeof(o));
   o.mode = mode; o.y = y; o.ldy = f->n; o.epi = e;
@@ -906,8 +941,8 @@ int plb_copy_d2h(plb_ctx* ctx, void* dst_host, const void* src_device, size_t by
   if (bytes == 0) return PLB_OK;
   PLB_CUDA(cudaSetDevice(ctx->device));
   PLB_CUDA(cudaMemcpyAsync(dst_host, src_device, bytes, cudaMemcpyDeviceToHost, ctx->stream));
-  PLB_CUDA(cudaStreamSynchronize(ctx->stream));
-  return PLB_OK;
+  // the bytes are only worth having if no kernel in front of them gave up: same check as plb_ctx_sync
+  return wait_and_check_status(ctx);
 }
 
 int plb_calib_i8_to_f32(plb_ctx* ctx, const int8_t* q, float* y, size_t n, float scale) {

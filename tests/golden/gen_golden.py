@@ -7,6 +7,10 @@ exact-integer oracle, and through it the CUDA kernels, against these vectors.  W
 within +-63 so that the reference's vpmaddubsw pair sums cannot saturate
 (lite/tests/math/x86_gemm_s8u8_compute_test.cc:131 does the same).
 
+A second file, ref_x86_bench_shapes.npz, holds two layers at benchmark size (the single-layer
+config 1 x 64 x 56 x 56 -> 64, 3x3, ReLU, and the (64, 2048, 1000) fc of the fc sweep), drawn from
+their own seed so that the small cases above keep their values.
+
 Usage: python tests/golden/gen_golden.py
 """
 import os
@@ -65,6 +69,35 @@ def main():
                              alpha=np.float32(alpha)).items():
             out["%s/%s" % (name, key)] = val
     path = os.path.join(os.path.dirname(os.path.abspath(__file__)), "ref_x86_cases.npz")
+    np.savez_compressed(path, **out)
+    print("wrote", path, os.path.getsize(path), "bytes")
+    bench_shapes()
+
+
+def bench_shapes():
+    """Layers at benchmark size.  Inputs are NOT stored (they would be megabytes of noise): the tests
+    redraw them with tests/helpers.py conv_case / fc_case from the stored seed and check a stored
+    checksum of the inputs first, so a generator that drifted shows up as such."""
+    sys.path.insert(0, os.path.join(ROOT, "tests"))
+    from helpers import conv_case, fc_case
+    out = {}
+    seed = 1001
+    xq, in_s, wq, ws, bias = conv_case(seed, 1, 64, 56, 56, 64, 3, qmax=63)
+    kw = dict(pads=(1, 1, 1, 1))
+    y = O.ref_conv_int8(xq, wq, ws, in_s, bias, O.ACT_RELU, 0.0, **kw)
+    out_s = float(np.abs(y).max() / 127.0)
+    q = O.ref_conv_int8(xq, wq, ws, in_s, bias, O.ACT_RELU, 0.0, out_scale=out_s, **kw)
+    out.update({"config1/seed": np.int64(seed), "config1/in_sum": np.int64(xq.astype(np.int64).sum() * 31 + wq.astype(np.int64).sum()),
+                "config1/out_s": np.float32(out_s), "config1/y_f32": y, "config1/y_i8": q})
+    seed = 1002
+    x, wq, ws, bias = fc_case(seed, 64, 2048, 1000, qmax=63)
+    y = O.ref_fc_int8(x, wq, ws, 0.02, bias, O.ACT_RELU6, 6.0)
+    out_s = float(np.abs(y).max() / 127.0)
+    q = O.ref_fc_int8(x, wq, ws, 0.02, bias, O.ACT_RELU6, 6.0, out_scale=out_s)
+    out.update({"fc64x2048x1000/seed": np.int64(seed),
+                "fc64x2048x1000/in_sum": np.int64(x.astype(np.int64).sum() * 31 + wq.astype(np.int64).sum()),
+                "fc64x2048x1000/out_s": np.float32(out_s), "fc64x2048x1000/y_f32": y, "fc64x2048x1000/y_i8": q})
+    path = os.path.join(os.path.dirname(os.path.abspath(__file__)), "ref_x86_bench_shapes.npz")
     np.savez_compressed(path, **out)
     print("wrote", path, os.path.getsize(path), "bytes")
 

@@ -89,12 +89,16 @@ WINDOW_CASES = [
     (2, 64, 20, 13, 32, (3, 2), (0, 1, 2, 0), (2, 1), 2),  # asymmetric padding, dilation, 3x2 filter
     (1, 32, 17, 23, 64, 5, (2, 2, 2, 2), (1, 1), 3),      # 5x5
     (1, 40, 9, 9, 32, 3, (0, 0, 0, 0), (1, 1), 0),        # no padding, channels padded to 64
-    (2, 128, 28, 28, 128, 3, (1, 1, 1, 1), (1, 1), 1),    # filter too large to stay resident: streamed, 3 K steps per box
-    (1, 256, 14, 14, 256, 3, (1, 1, 1, 1), (1, 1), 1),    # two channel chunks, 256-wide tile, streamed filter
-    (1, 64, 20, 20, 320, 3, (1, 1, 1, 1), (1, 1), 2),     # streamed filter, ragged second channel tile (64 of 256)
-    (1, 32, 12, 12, 320, (2, 3), (1, 0, 1, 1), (1, 1), 0),  # two channel tiles: every window is fetched twice
-    (24, 128, 28, 28, 128, 3, (1, 1, 1, 1), (1, 1), 1),   # 192 tiles on 148 CTAs: some CTAs run a pair of tiles per filter pass
-    (41, 64, 14, 14, 512, 3, (1, 1, 1, 1), (1, 1), 0),    # pairs with two channel tiles, odd tile counts per CTA
+]
+
+# stride-1 filters that are too large to stay in shared memory (or need several channel tiles): im2col mode
+LARGE_FILTER_CASES = [
+    (2, 128, 28, 28, 128, 3, (1, 1, 1, 1), (1, 1), 1),
+    (1, 256, 14, 14, 256, 3, (1, 1, 1, 1), (1, 1), 1),    # two channel chunks, 256-wide tile
+    (1, 64, 20, 20, 320, 3, (1, 1, 1, 1), (1, 1), 2),     # ragged second channel tile (64 of 256)
+    (1, 32, 12, 12, 320, (2, 3), (1, 0, 1, 1), (1, 1), 0),
+    (24, 128, 28, 28, 128, 3, (1, 1, 1, 1), (1, 1), 1),   # 192 tiles on 148 CTAs
+    (41, 64, 14, 14, 512, 3, (1, 1, 1, 1), (1, 1), 0),    # two channel tiles, odd tile counts per CTA
 ]
 
 
@@ -103,13 +107,66 @@ def test_window_mode_bit_exact(plb, ctx, case, monkeypatch):
     """Stride-1 filters in window mode (one fetch of a tile's input window, taps addressed by
     shifted matrix descriptors), forced on for shapes the heuristic would leave to im2col."""
     monkeypatch.setenv("PLB_TC_SLAB", "1")
-    monkeypatch.setenv("PLB_TC_BSTREAM", "1")  # filters that do not fit in shared memory stream through their own ring
     monkeypatch.setenv("PLB_TC_BN", "256")  # one channel tile even though the problem is small
     n, cin, h, w, cout, k, pads, dil, act = case
     xq, in_s, wq, ws, bias = conv_case(hash(case[:5]) % 10000, n, cin, h, w, cout, k)
     before = ctx.window_launch_count()
     run_case(plb, ctx, xq, in_s, wq, ws, bias, pads=pads, dil=dil, act=act, alpha=6.0 if act == 2 else 0.1)
     assert ctx.window_launch_count() >= before + 3, "window mode was not taken"
+
+
+@pytest.mark.parametrize("case", LARGE_FILTER_CASES, ids=lambda c: "x".join(map(str, c[:5])))
+def test_large_filter_bit_exact(plb, ctx, case, monkeypatch):
+    """The same kind of layer with a filter that cannot stay resident: streamed through the operand ring."""
+    monkeypatch.setenv("PLB_TC_BN", "256")
+    n, cin, h, w, cout, k, pads, dil, act = case
+    xq, in_s, wq, ws, bias = conv_case(hash(case[:5]) % 10000, n, cin, h, w, cout, k)
+    run_case(plb, ctx, xq, in_s, wq, ws, bias, pads=pads, dil=dil, act=act, alpha=6.0 if act == 2 else 0.1)
+
+
+def test_golden_config1_shape(plb, ctx):
+    """The single-layer benchmark config (1 x 64 x 56 x 56 -> 64, 3x3, pad 1, ReLU) against the committed output of
+    the reference objects, through the NCHW entry point; and bit-identical to the oracle."""
+    from helpers import golden_bench_shapes, assert_matches_reference_f32
+    g, _ = golden_bench_shapes()
+    x = dev(g["x"])
+    kw = dict(in_hw=(56, 56), pads=(1, 1, 1, 1), act=plb.ACT_RELU)
+    y = plb.Conv(ctx, g["w"], g["ws"], g["in_s"], g["bias"], **kw).run(x).cpu().numpy()
+    q = plb.Conv(ctx, g["w"], g["ws"], g["in_s"], g["bias"], out_scale=g["out_s"], **kw).run(x).cpu().numpy()
+    ctx.sync()
+    assert_matches_reference_f32(y, g["y_f32"], "config1 (CUDA)")
+    assert_i8_close(q, g["y_i8"])
+    assert np.array_equal(y, O.conv_int8(g["x"], g["w"], g["ws"], g["in_s"], g["bias"], O.ACT_RELU, pads=(1, 1, 1, 1)))
+
+
+def test_plan_is_reused(plb, ctx):
+    """A prepared layer stores the tile plan and tensor maps of the (batch, pointers) it has run on: the second run
+    with the same buffers re-launches it (and gives the same bytes), other buffers or batches get plans of their own."""
+    xq, in_s, wq, ws, bias = conv_case(99, 4, 64, 28, 28, 96, 3)
+    conv = plb.Conv(ctx, wq, ws, in_s, bias, in_hw=(28, 28), pads=(1, 1, 1, 1), act=plb.ACT_RELU, out_scale=0.05)
+    x = ctx.nchw_to_nhwc_i8(dev(xq))
+    y = torch.empty((4, 28, 28, 96), dtype=torch.int8, device="cuda")
+    conv.run_nhwc(x, out=y)
+    first = y.clone()
+    h0 = conv.plan_cache_hits()
+    y.zero_()
+    conv.run_nhwc(x, out=y)
+    assert conv.plan_cache_hits() == h0 + 1
+    assert torch.equal(y, first)
+    y2 = torch.empty_like(y)
+    conv.run_nhwc(x, out=y2)                 # another output buffer: a new plan, same result
+    assert conv.plan_cache_hits() == h0 + 1
+    assert torch.equal(y2, first)
+    conv.run_nhwc(x[:2], out=y2[:2])         # another batch
+    assert conv.plan_cache_hits() == h0 + 1
+    for _ in range(12):                      # more distinct problems than the cache holds, then the first one again
+        conv.run_nhwc(x, out=torch.empty_like(y))
+    y.zero_()
+    conv.run_nhwc(x, out=y)
+    ctx.sync()
+    assert torch.equal(y, first)
+    want = O.conv_int8(xq, wq, ws, in_s, bias, O.ACT_RELU, pads=(1, 1, 1, 1), out_scale=0.05)
+    assert np.array_equal(ctx.nhwc_to_nchw(y).cpu().numpy(), want)
 
 
 def test_asymmetric_pad_dilation(plb, ctx):
@@ -327,7 +384,6 @@ def test_random_geometries(plb, ctx, case, force_window, monkeypatch):
     choice of operand mode and once with window mode forced wherever it applies."""
     if force_window == "1":
         monkeypatch.setenv("PLB_TC_SLAB", "1")
-        monkeypatch.setenv("PLB_TC_BSTREAM", "1")
     n, cin, h, w, cout, k, s, pads, dil, act = case
     xq, in_s, wq, ws, bias = conv_case(hash(case[:5]) % 10000, n, cin, h, w, cout, k)
     run_case(plb, ctx, xq, in_s, wq, ws, bias, stride=s, pads=pads, dil=dil, act=act,

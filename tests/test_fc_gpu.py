@@ -62,6 +62,19 @@ def test_fc_4096_cubed_checksum(plb, ctx):
     assert np.array_equal(acc[rows].cpu().numpy(), O.fc_acc_i32(x[rows], wq))
 
 
+def test_golden_fc_sweep_shape(plb, ctx):
+    """(M, K, N) = (64, 2048, 1000) of the fc sweep, ReLU6, against the committed output of the reference objects."""
+    from helpers import golden_bench_shapes, assert_matches_reference_f32, assert_i8_close
+    _, g = golden_bench_shapes()
+    x = dev(g["x"])
+    y = plb.Fc(ctx, g["w"], g["ws"], g["in_s"], g["bias"], plb.ACT_RELU6, 6.0).run(x).cpu().numpy()
+    q = plb.Fc(ctx, g["w"], g["ws"], g["in_s"], g["bias"], plb.ACT_RELU6, 6.0, out_scale=g["out_s"]).run(x).cpu().numpy()
+    ctx.sync()
+    assert_matches_reference_f32(y, g["y_f32"], "fc 64x2048x1000 (CUDA)")
+    assert_i8_close(q, g["y_i8"])
+    assert np.array_equal(y, O.fc_int8(g["x"], g["w"], g["ws"], g["in_s"], g["bias"], O.ACT_RELU6, 6.0))
+
+
 def test_fc_errors(plb, ctx):
     x, wq, ws, bias = fc_case(1, 4, 64, 8)
     with pytest.raises(plb.PlbError):

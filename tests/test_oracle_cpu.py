@@ -3,7 +3,8 @@ own gemm_s8u8 + im2col objects) and, when they are built, the objects themselves
 import numpy as np
 import pytest
 
-from helpers import O, assert_f32_close, assert_i8_close, conv_case, fc_case, golden, golden_names
+from helpers import (O, assert_f32_close, assert_i8_close, assert_matches_reference_f32, conv_case, fc_case, golden,
+                     golden_bench_shapes, golden_names)
 
 DATA = golden()
 
@@ -17,6 +18,7 @@ def test_oracle_matches_golden_conv(name):
     # The reference adds a compensated bias (bias - 128*s*sum(A)) to float(acc + 128*sum(A))*s,
     # so its fp32 result carries rounding of values ~128*|sum A| times larger than y.
     assert_f32_close(y, g["y_f32"], rel=1e-5, floor=float(np.abs(g["y_f32"]).max()))
+    assert_matches_reference_f32(y, g["y_f32"], name)
     q = O.conv_int8(g["x"], g["w"], g["ws"], float(g["in_s"]), g["bias"], act, float(g["alpha"]),
                     out_scale=float(g["out_s"]), leaky_compat=True, **kw)
     assert_i8_close(q, g["y_i8"])
@@ -28,9 +30,25 @@ def test_oracle_matches_golden_fc(name):
     m, k, n, act = [int(v) for v in g["meta"]]
     y = O.fc_int8(g["x"], g["w"], g["ws"], float(g["in_s"]), g["bias"], act, float(g["alpha"]))
     assert_f32_close(y, g["y_f32"], rel=1e-5, floor=float(np.abs(g["y_f32"]).max()))
+    assert_matches_reference_f32(y, g["y_f32"], name)
     q = O.fc_int8(g["x"], g["w"], g["ws"], float(g["in_s"]), g["bias"], act, float(g["alpha"]),
                   out_scale=float(g["out_s"]))
     assert_i8_close(q, g["y_i8"])
+
+
+def test_oracle_matches_golden_bench_shapes():
+    """The single-layer benchmark config (1x64x56x56 -> 64, 3x3, pad 1, ReLU) and the (64, 2048, 1000) fc of
+    the fc sweep against the committed outputs of the reference objects (weights within +-63)."""
+    conv, fc = golden_bench_shapes()
+    y = O.conv_int8(conv["x"], conv["w"], conv["ws"], conv["in_s"], conv["bias"], O.ACT_RELU, pads=(1, 1, 1, 1))
+    assert_matches_reference_f32(y, conv["y_f32"], "config1")
+    q = O.conv_int8(conv["x"], conv["w"], conv["ws"], conv["in_s"], conv["bias"], O.ACT_RELU, pads=(1, 1, 1, 1),
+                    out_scale=conv["out_s"])
+    assert_i8_close(q, conv["y_i8"])
+    y = O.fc_int8(fc["x"], fc["w"], fc["ws"], fc["in_s"], fc["bias"], O.ACT_RELU6, 6.0)
+    assert_matches_reference_f32(y, fc["y_f32"], "fc 64x2048x1000")
+    q = O.fc_int8(fc["x"], fc["w"], fc["ws"], fc["in_s"], fc["bias"], O.ACT_RELU6, 6.0, out_scale=fc["out_s"])
+    assert_i8_close(q, fc["y_i8"])
 
 
 needs_ref = pytest.mark.skipif(not O.ref_available(), reason="reference objects not built")

@@ -75,6 +75,50 @@ def test_sparse_fp32(plb, ctx, cin, cout, side, batch, semi):
     assert_f32_close(y, y64, rel=1e-5, floor=float(np.abs(y64).max()))
 
 
+# the sparse_conv benchmark shapes: MobileNetV1 pointwise layers at batch 256, 80 % of the weights masked
+CONFIG5 = [(32, 64, 112), (128, 128, 56), (256, 256, 28), (512, 512, 14), (1024, 1024, 7)]
+
+
+@pytest.mark.parametrize("semi", [False, True], ids=["unstructured", "semi"])
+@pytest.mark.parametrize("cin,cout,side", CONFIG5)
+def test_sparse_int8_benchmark_size(plb, ctx, cin, cout, side, semi):
+    """Full benchmark size (batch 256).  The oracle cannot run 2 GOP per case in seconds, so the whole output is
+    checked through an exact integer identity and three images are checked element by element:
+    * with unit scales, no bias and no activation the fp32 output IS the int32 accumulator (|acc| < 2^24), and
+      sum over pixels of acc[n, oc, :] = sum_ic W[oc, ic] * (sum over pixels of x[n, ic, :])  -- exact in int64;
+    * images 0, 100 and 255 of the int8-out layer (per-channel scales, bias, ReLU) equal the oracle bit for bit."""
+    batch = 256
+    hw = side * side
+    wf = sparse_weights(7 * cin + cout, cout, cin, semi)
+    wq, ws = O.quantize_per_channel(wf)
+    enc = O.sparse_encode(wq, hw, semi=semi)
+    args = (enc["nonzero_weights"], enc["oc_nonzeros"], enc["diffs"], enc["first_ic"], enc["flag_semi"])
+    g = torch.Generator(device="cuda").manual_seed(cin + side)
+    x = torch.randint(-127, 128, (batch, cin, side, side), dtype=torch.int8, device="cuda", generator=g)
+    # 1. accumulators of the whole batch through the fp32-out kernel
+    ident = plb.SparseConv(ctx, *args, cin=cin, cout=cout, in_hw=(side, side), wscale=np.ones(cout, np.float32),
+                           in_scale=1.0)
+    acc = ident.run(x)
+    ctx.sync()
+    got = acc.view(batch, cout, hw).to(torch.int64).sum(dim=2).cpu().numpy()
+    xsum = x.view(batch, cin, hw).to(torch.int64).sum(dim=2).cpu().numpy()       # [batch, cin]
+    want = xsum @ wq.astype(np.int64).T                                          # [batch, cout]
+    assert np.array_equal(got, want), "pixel sums of the accumulators break the linear identity"
+    del acc
+    # 2. int8-out layer, three images against the oracle
+    rng = np.random.default_rng(cin)
+    bias = (rng.standard_normal(cout) * 0.1).astype(np.float32)
+    in_s, out_s = 0.02, 0.06
+    q = plb.SparseConv(ctx, *args, cin=cin, cout=cout, in_hw=(side, side), wscale=ws, in_scale=in_s, bias=bias,
+                       act=O.ACT_RELU, out_scale=out_s).run(x)
+    ctx.sync()
+    for n in (0, 100, 255):
+        xs = x[n:n + 1].cpu().numpy()
+        a = O.conv_acc_i32(xs, wq[:, :, None, None])
+        q_ref = O.epilogue(a, ws, in_s, bias, O.ACT_RELU, 0.0, out_scale=out_s)
+        assert np.array_equal(q[n:n + 1].cpu().numpy(), q_ref), "image %d differs from the oracle" % n
+
+
 def test_sparse_errors(plb, ctx):
     wq = np.zeros((4, 8), dtype=np.int8)
     wq[1, 3] = 5
