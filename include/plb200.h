@@ -75,6 +75,8 @@ long plb_ctx_launch_count(const plb_ctx* ctx);
 /* How many of those were tensor-core convolutions in window mode (each input pixel of a tile
  * fetched once and shared by all filter taps).  For tests and tuning; no reference counterpart. */
 long plb_ctx_window_launch_count(const plb_ctx* ctx);
+/* How many 1x1 convolutions ran directly on NCHW tensors (no layout staging passes).  For tests. */
+long plb_ctx_nchw_launch_count(const plb_ctx* ctx);
 /* Bytes of layout-staging scratch the ctx currently holds (its own or the caller's).  Test hook. */
 size_t plb_ctx_workspace_size(const plb_ctx* ctx);
 

@@ -57,6 +57,7 @@ SYMBOLS = {
     "plb_last_error": (C.c_char_p, []),
     "plb_ctx_launch_count": (C.c_long, [_P]),
     "plb_ctx_window_launch_count": (C.c_long, [_P]),
+    "plb_ctx_nchw_launch_count": (C.c_long, [_P]),
     "plb_ctx_workspace_size": (C.c_size_t, [_P]),
     "plb_conv_plan_cache_hits": (C.c_long, [_P]),
     "plb_conv_prepare": (C.c_int, [_P, C.POINTER(ConvDesc), _P, _P, C.c_int, _P, C.POINTER(_P)]),
@@ -145,6 +146,9 @@ class Context:
 
     def window_launch_count(self):
         return lib().plb_ctx_window_launch_count(self.handle)
+
+    def nchw_launch_count(self):
+        return lib().plb_ctx_nchw_launch_count(self.handle)
 
     def workspace_size(self):
         return lib().plb_ctx_workspace_size(self.handle)

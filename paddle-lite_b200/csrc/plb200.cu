@@ -6,6 +6,7 @@
 #include <memory>
 #include <mutex>
 
+#include "igemm_nchw.cuh"
 #include "igemm_tc.cuh"
 #include "kernels_simple.cuh"
 
@@ -235,6 +236,7 @@ int plb_ctx_set_workspace(plb_ctx* ctx, void* dptr, size_t bytes) {
 
 long plb_ctx_launch_count(const plb_ctx* ctx) { return ctx ? ctx->launches : 0; }
 long plb_ctx_window_launch_count(const plb_ctx* ctx) { return ctx ? ctx->window_launches : 0; }
+long plb_ctx_nchw_launch_count(const plb_ctx* ctx) { return ctx ? ctx->nchw_launches : 0; }
 size_t plb_ctx_workspace_size(const plb_ctx* ctx) { return ctx ? ctx->ws_bytes : 0; }
 
 // ------------------------------------------------------------------ conv
@@ -465,10 +467,31 @@ OutSpec out_spec(const plb_conv* c, int mode, void* y) {
   return o;
 }
 
+// Unpadded stride-1 1x1 layers can run on the NCHW tensors as they are (igemm_nchw.cu): no staging passes.
+bool nchw_native(const plb_conv* c, const int8_t* x, void* y, int batch, int mode, NchwProblem* p) {
+  const plb_conv_desc& d = c->d;
+  if (c->kind != 0 || c->fold || c->sw.nchw == 0) return false;
+  if (!(d.kh == 1 && d.kw == 1 && d.stride_h == 1 && d.stride_w == 1 && d.pad_top == 0 && d.pad_bottom == 0 &&
+        d.pad_left == 0 && d.pad_right == 0))
+    return false;
+  memset(p, 0, sizeof(*p));
+  p->x = x; p->w = c->w.as<int8_t>();
+  p->batch = batch; p->cin = d.cin; p->cin_pad = c->cin_pad; p->cout = d.cout; p->hw = d.h * d.w;
+  p->out_mode = mode; p->y = y;
+  return igemm_nchw_supported(*p, nullptr);
+}
+
 int conv_run_nchw(plb_conv* c, const int8_t* x, void* y, int batch, int mode) {
   plb_ctx* ctx = c->ctx;
   const plb_conv_desc& d = c->d;
   PLB_CUDA(cudaSetDevice(ctx->device));
+  {
+    NchwProblem np;
+    if (nchw_native(c, x, y, batch, mode, &np)) {
+      np.epi = out_spec(c, mode, y).epi;
+      return igemm_nchw_launch(ctx, np);
+    }
+  }
   const size_t x_bytes = staged_input_bytes(c, batch);
   int rc = ctx->reserve(plb_conv_workspace_bytes(c, batch));
   if (rc) return rc;

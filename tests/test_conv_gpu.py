@@ -124,6 +124,39 @@ def test_large_filter_bit_exact(plb, ctx, case, monkeypatch):
     run_case(plb, ctx, xq, in_s, wq, ws, bias, pads=pads, dil=dil, act=act, alpha=6.0 if act == 2 else 0.1)
 
 
+# (n, cin, h, w, cout, act): unpadded stride-1 1x1 layers whose images have a multiple of 16 pixels
+NCHW_1X1_CASES = [
+    (2, 32, 112, 112, 64, 1),     # first MobileNetV1 pointwise shape: one K step, 64 of 128 accumulator lanes used
+    (3, 128, 28, 28, 128, 1),     # 784 pixels: three full 256-pixel tiles and a 16-pixel one
+    (2, 256, 28, 28, 256, 2),     # two channel tiles, two K steps of 128
+    (1, 40, 8, 8, 24, 0),         # input channels padded to 64, 64 pixels, ragged channels
+    (2, 64, 20, 20, 200, 3),      # ragged second channel tile
+    (5, 1024, 4, 4, 1024, 1),     # long K, 16 pixels per image
+    (1, 96, 16, 24, 32, 1),       # three K steps of 32
+    (150, 64, 16, 16, 64, 1),     # more tiles than SMs: filter resident in shared memory, several tiles per CTA
+    (40, 512, 12, 12, 256, 1),    # streamed filter, several tiles per CTA
+]
+
+
+@pytest.mark.parametrize("case", NCHW_1X1_CASES, ids=lambda c: "x".join(map(str, c[:5])))
+def test_nchw_native_1x1(plb, ctx, case):
+    """1x1 layers through the NCHW entry point run on the NCHW tensors directly (output channels in the
+    accumulator lanes, pixels in its columns); accumulators, fp32 and int8 outputs bit-identical to the oracle."""
+    n, cin, h, w, cout, act = case
+    xq, in_s, wq, ws, bias = conv_case(hash(case) % 10000, n, cin, h, w, cout, 1)
+    before = ctx.nchw_launch_count()
+    run_case(plb, ctx, xq, in_s, wq, ws, bias, act=act, alpha=6.0 if act == 2 else 0.1)
+    assert ctx.nchw_launch_count() == before + 3, "the NCHW-native kernel was not taken"
+
+
+def test_nchw_native_switch_off(plb, ctx, monkeypatch):
+    monkeypatch.setenv("PLB_TC_NCHW", "0")
+    xq, in_s, wq, ws, bias = conv_case(3, 2, 64, 16, 16, 64, 1)
+    before = ctx.nchw_launch_count()
+    run_case(plb, ctx, xq, in_s, wq, ws, bias, act=1)
+    assert ctx.nchw_launch_count() == before
+
+
 def test_golden_config1_shape(plb, ctx):
     """The single-layer benchmark config (1 x 64 x 56 x 56 -> 64, 3x3, pad 1, ReLU) against the committed output of
     the reference objects, through the NCHW entry point; and bit-identical to the oracle."""
