@@ -44,8 +44,12 @@ struct NchwArgs {
   int bn;                 // pixels per tile: 128 or 256
   int kc, ksteps, stages;
   int tiles_m, tiles_p, num_tiles;  // channel tiles, pixel tiles per image, all tiles
-  int resident_w;         // the whole filter (a single channel tile) stays in shared memory
+  int resident_w;         // the filter rows of this CTA's channel tile stay in shared memory (every tile of a CTA has the
+                          // same channel tile when the grid size is a multiple of the number of channel tiles)
   int resident_bytes;
+  int dup;                // cout <= 64: filter rows 0..63 are loaded twice (accumulator lanes 64..127 repeat lanes 0..63)
+                          // so that all four lane quadrants, i.e. all four schedulers of the SM, share the epilogue:
+                          // quadrants 2 and 3 take the second half of a group's pixels
   const float* scale;
   const float* bias;
   float alpha;
@@ -106,7 +110,11 @@ __global__ void __launch_bounds__(kThreads, 1)
       // the filter is a layer constant: its copy does not wait for the preceding kernel
       const uint32_t bar = smem_u32(wres_bar);
       mbar_expect_tx(bar, static_cast<uint32_t>(a.ksteps * kTileCout * a.kc));
-      for (int ks = 0; ks < a.ksteps; ++ks) tma_load_2d(smem_u32(smem_wres) + ks * kTileCout * a.kc, &tmW, bar, ks * a.kc, 0);
+      const int m0 = (static_cast<int>(blockIdx.x) % a.tiles_m) * kTileCout;
+      for (int ks = 0; ks < a.ksteps; ++ks) {
+        tma_load_2d(smem_u32(smem_wres) + ks * kTileCout * a.kc, &tmW, bar, ks * a.kc, m0);
+        if (a.dup) tma_load_2d(smem_u32(smem_wres) + ks * kTileCout * a.kc + 64 * a.kc, &tmW, bar, ks * a.kc, m0);
+      }
     }
   }
   if (warp == kMmaWarp) {
@@ -138,7 +146,10 @@ __global__ void __launch_bounds__(kThreads, 1)
         const uint32_t bar = smem_u32(&full_bar[s]);
         const uint32_t dst = smem_base + s * stage_bytes;
         mbar_expect_tx_if(bar, static_cast<uint32_t>(stage_bytes), leader);
-        if (!a.resident_w) tma_load_2d_if(dst, &tmW, bar, ks * a.kc, m0, leader);
+        if (!a.resident_w) {
+          tma_load_2d_if(dst, &tmW, bar, ks * a.kc, m0, leader);
+          if (a.dup) tma_load_2d_if(dst + 64 * a.kc, &tmW, bar, ks * a.kc, m0, leader);
+        }
         // X[img][ks*kc .. +kc)[p0 .. +bn): one box per 128 pixels; rows past cin and pixels past hw arrive as zeros
         for (int h = 0; h < halves; ++h)
           tma_load_3d_if(dst + stage_a + h * a.kc * 128, &tmX, bar, p0 + 128 * h, ks * a.kc, img, leader);
@@ -208,11 +219,14 @@ __global__ void __launch_bounds__(kThreads, 1)
     // its pixels in halves.  Warp w reads tensor-memory lanes 32*(w%4) .. +31 = 32 output channels.
     const int group = warp >> 2, quad = warp & 3;
     const int buf = group >> 1, col_par = group & 1;
-    const int wq = a.bn / 2;                       // pixels (= int8 bytes per staged row) of this group
-    const int cbase = col_par * wq;
+    // pixels (= int8 bytes per staged row) of this warp: half a tile per group, halved again between the
+    // lane quadrants 0/1 and 2/3 when the accumulator rows are duplicated
+    const int wq = a.dup ? a.bn / 4 : a.bn / 2;
+    const int cbase = col_par * (a.bn / 2) + (a.dup ? (quad >> 1) * wq : 0);
+    const int row_quad = a.dup ? (quad & 1) : quad;  // which 32 output channels of the tile this warp owns
     const uint32_t st = smem_u32(smem_al) + warp * 4096;
     // int8 staging rows are wq bytes long, swizzled with span wq as the store's tensor map is
-    const int b_swz = wq == 128 ? (lane & 7) : ((lane >> 1) & 3);
+    const int b_swz = wq == 128 ? (lane & 7) : (wq == 64 ? ((lane >> 1) & 3) : ((lane >> 2) & 1));
     const float ub = quant_upper_bound<ACT>(a.alpha);
     bool stores_pending = false;
     bool ok = true;
@@ -221,7 +235,7 @@ __global__ void __launch_bounds__(kThreads, 1)
       if (tile_l >= a.num_tiles) break;
       int m0, p0, img;
       decode_tile(a, static_cast<int>(tile_l), m0, p0, img);
-      const int row0 = m0 + quad * 32;
+      const int row0 = m0 + row_quad * 32;
       const bool active = row0 < a.cout;          // warp-uniform
       const int ch = row0 + lane;
       float sc = 0.f, bi = 0.f;
@@ -353,7 +367,9 @@ bool igemm_nchw_supported(const NchwProblem& p, std::string* why) {
     return false;
   };
   if (p.out_mode != OUT_I8 && p.out_mode != OUT_F32 && p.out_mode != OUT_ACC) return no("output mode");
-  if (p.hw % 16 != 0) return no("pixels per image must be a multiple of 16 (TMA row strides)");
+  const int xp = p.x_pitch ? p.x_pitch : p.hw, yp = p.y_pitch ? p.y_pitch : p.hw;
+  if (xp % 16 != 0 || xp < p.hw) return no("input rows must be a multiple of 16 bytes apart (TMA row strides)");
+  if ((yp * (p.out_mode == OUT_I8 ? 1 : 4)) % 16 != 0 || yp < p.hw) return no("output rows must be a multiple of 16 bytes apart");
   if (p.cin_pad % 32 != 0 || p.cin > p.cin_pad) return no("filter rows must be padded to a multiple of 32 bytes");
   if (p.batch <= 0 || p.cout <= 0 || p.cin <= 0) return no("empty problem");
   if ((reinterpret_cast<uintptr_t>(p.x) & 15) || (reinterpret_cast<uintptr_t>(p.w) & 15) ||
@@ -377,6 +393,7 @@ int igemm_nchw_launch(plb_ctx* ctx, const NchwProblem& p) {
   a.kc = p.cin_pad % 128 == 0 ? 128 : (p.cin_pad % 64 == 0 ? 64 : 32);
   a.ksteps = p.cin_pad / a.kc;
   a.tiles_m = (p.cout + kTileCout - 1) / kTileCout;
+  a.dup = p.cout <= 64;
   // 256-pixel tiles halve the filter traffic per pixel; small images and small grids take 128
   a.bn = 256;
   if (p.hw <= 128 || static_cast<long>(p.batch) * ((p.hw + 255) / 256) * a.tiles_m < 2L * ctx->sm_count) a.bn = 128;
@@ -385,7 +402,8 @@ int igemm_nchw_launch(plb_ctx* ctx, const NchwProblem& p) {
   if (tiles > 0x7fffffffL) return fail(PLB_E_UNSUPPORTED, "too many tiles");
   a.num_tiles = static_cast<int>(tiles);
   const int resident_bytes = a.ksteps * kTileCout * a.kc;
-  a.resident_w = a.tiles_m == 1 && resident_bytes <= kMaxResidentW && tiles > ctx->sm_count;
+  const long grid_l = tiles < ctx->sm_count ? tiles : ctx->sm_count;
+  a.resident_w = grid_l % a.tiles_m == 0 && resident_bytes <= kMaxResidentW && tiles > grid_l;
   a.resident_bytes = a.resident_w ? resident_bytes : 0;
   const int stage_bytes = (a.resident_w ? 0 : kTileCout * a.kc) + a.kc * a.bn;
   int stages = (225 * 1024 - kStagingBytes - a.resident_bytes - kCtrlBytes) / stage_bytes;
@@ -402,7 +420,7 @@ int igemm_nchw_launch(plb_ctx* ctx, const NchwProblem& p) {
   {
     cuuint64_t dims[2] = {static_cast<cuuint64_t>(p.cin_pad), static_cast<cuuint64_t>(p.cout)};
     cuuint64_t strides[1] = {static_cast<cuuint64_t>(p.cin_pad)};
-    cuuint32_t box[2] = {static_cast<cuuint32_t>(a.kc), static_cast<cuuint32_t>(kTileCout)};
+    cuuint32_t box[2] = {static_cast<cuuint32_t>(a.kc), static_cast<cuuint32_t>(a.dup ? 64 : kTileCout)};
     cuuint32_t estr[2] = {1, 1};
     const CUtensorMapSwizzle sw = a.kc == 128 ? CU_TENSOR_MAP_SWIZZLE_128B
                                               : (a.kc == 64 ? CU_TENSOR_MAP_SWIZZLE_64B : CU_TENSOR_MAP_SWIZZLE_32B);
@@ -414,7 +432,8 @@ int igemm_nchw_launch(plb_ctx* ctx, const NchwProblem& p) {
   {
     // X as [batch][cin][hw] bytes: a box is 128 pixels of kc channels of one image
     cuuint64_t dims[3] = {static_cast<cuuint64_t>(p.hw), static_cast<cuuint64_t>(p.cin), static_cast<cuuint64_t>(p.batch)};
-    cuuint64_t strides[2] = {static_cast<cuuint64_t>(p.hw), static_cast<cuuint64_t>(p.hw) * p.cin};
+    const cuuint64_t xp = p.x_pitch ? p.x_pitch : p.hw;
+    cuuint64_t strides[2] = {xp, xp * p.cin};
     cuuint32_t box[3] = {128, static_cast<cuuint32_t>(a.kc), 1};
     cuuint32_t estr[3] = {1, 1, 1};
     CUresult r = g_encode(&tmX, CU_TENSOR_MAP_DATA_TYPE_UINT8, 3, const_cast<int8_t*>(p.x), dims, strides, box, estr,
@@ -425,12 +444,14 @@ int igemm_nchw_launch(plb_ctx* ctx, const NchwProblem& p) {
   {
     // Y as [batch][cout][hw]: a warp stores 32 channels x (bn/2 int8 pixels | 32 fp32 / int32 pixels)
     const int eb = p.out_mode == OUT_I8 ? 1 : 4;
-    const int wq = a.bn / 2;
+    const int wq = a.dup ? a.bn / 4 : a.bn / 2;
     cuuint64_t dims[3] = {static_cast<cuuint64_t>(p.hw), static_cast<cuuint64_t>(p.cout), static_cast<cuuint64_t>(p.batch)};
-    cuuint64_t strides[2] = {static_cast<cuuint64_t>(p.hw) * eb, static_cast<cuuint64_t>(p.hw) * p.cout * eb};
+    const cuuint64_t yp = p.y_pitch ? p.y_pitch : p.hw;
+    cuuint64_t strides[2] = {yp * eb, yp * p.cout * eb};
     cuuint32_t box[3] = {static_cast<cuuint32_t>(eb == 1 ? wq : 32), 32, 1};
     cuuint32_t estr[3] = {1, 1, 1};
-    const CUtensorMapSwizzle sw = (eb == 4 || wq == 128) ? CU_TENSOR_MAP_SWIZZLE_128B : CU_TENSOR_MAP_SWIZZLE_64B;
+    const CUtensorMapSwizzle sw = (eb == 4 || wq == 128) ? CU_TENSOR_MAP_SWIZZLE_128B
+                                  : (wq == 64 ? CU_TENSOR_MAP_SWIZZLE_64B : CU_TENSOR_MAP_SWIZZLE_32B);
     CUresult r = g_encode(&tmOut, eb == 1 ? CU_TENSOR_MAP_DATA_TYPE_UINT8 : CU_TENSOR_MAP_DATA_TYPE_UINT32, 3, p.y, dims,
                           strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE, sw, CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
                           CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);

@@ -9,6 +9,7 @@ struct NchwProblem {
   const int8_t* x;   // [batch][cin][hw] int8
   const int8_t* w;   // [cout][cin_pad] int8, rows zero-padded to cin_pad (multiple of 32)
   int batch, cin, cin_pad, cout, hw;
+  int x_pitch, y_pitch;  // elements between the rows (channels) of x and of y; 0 = hw (dense NCHW)
   int out_mode;      // OUT_I8 / OUT_F32 / OUT_ACC
   void* y;           // [batch][cout][hw] int8 / float / int32
   EpiParams epi;

@@ -1152,7 +1152,126 @@ __global__ void global_avgpool_kernel(const float* __restrict__ x, float* __rest
 
 unsigned blocks_for(long total) { return static_cast<unsigned>((total + kBlock - 1) / kBlock); }
 
+// ---------------------------------------------------------------- row pitch changes for TMA
+// TMA needs rows that start on 16-byte boundaries.  NCHW images whose pixel count is not a multiple of 16
+// (14 x 14, 7 x 7 ...) are therefore copied once into rows of `pitch` bytes (a multiple of 16) in front of
+// the NCHW-native tensor-core kernel and its output is copied back; both copies are small enough to be
+// served by the L2.
+
+// 16 bytes starting at any byte address, from aligned 32-bit loads; words that lie wholly at or beyond `end`
+// are not read.
+__device__ __forceinline__ uint4 load16_unaligned(const uint8_t* p, const uint8_t* end) {
+  const uintptr_t a = reinterpret_cast<uintptr_t>(p);
+  const uint32_t* w = reinterpret_cast<const uint32_t*>(a & ~static_cast<uintptr_t>(3));
+  const uint32_t shift = static_cast<uint32_t>(a & 3) * 8;
+  uint32_t v[5];
+#pragma unroll
+  for (int i = 0; i < 5; ++i) v[i] = reinterpret_cast<const uint8_t*>(w + i) < end ? __ldg(w + i) : 0u;
+  return make_uint4(__funnelshift_r(v[0], v[1], shift), __funnelshift_r(v[1], v[2], shift),
+                    __funnelshift_r(v[2], v[3], shift), __funnelshift_r(v[3], v[4], shift));
+}
+
+// src rows of `len` bytes back to back -> dst rows of `pitch` bytes (16-byte chunks; the tail of a row's last
+// chunk holds bytes of the following row, which the consumer's tensor map never reads as data).
+__global__ void __launch_bounds__(kBlock) pitch_rows_kernel(const uint8_t* __restrict__ src, uint8_t* __restrict__ dst,
+                                                            long rows, int len, int pitch, long total_chunks) {
+  pdl_sync_with_previous_kernel();
+  const long idx = static_cast<long>(blockIdx.x) * kBlock + threadIdx.x;
+  if (idx >= total_chunks) return;
+  const int cpr = pitch / 16;
+  const long row = idx / cpr;
+  const int j = static_cast<int>(idx - row * cpr);
+  const uint8_t* end = src + rows * len;
+  *reinterpret_cast<uint4*>(dst + row * pitch + 16 * j) = load16_unaligned(src + row * len + 16 * j, end);
+}
+
+// src rows of `pitch` bytes -> dst rows of `len` bytes back to back.  One thread per aligned 16 bytes of dst (the
+// rows of dst have no alignment of their own, so a thread's bytes may come from several rows); each aligned
+// 32-bit word of dst that lies inside one row is an unaligned 32-bit read of src.
+__global__ void __launch_bounds__(kBlock) unpitch_rows_i8_kernel(const uint8_t* __restrict__ src, uint8_t* __restrict__ dst,
+                                                                 unsigned len, unsigned pitch, unsigned long long total_bytes) {
+  pdl_sync_with_previous_kernel();
+  const unsigned long long f0 = 16ull * (static_cast<unsigned long long>(blockIdx.x) * kBlock + threadIdx.x);
+  if (f0 >= total_bytes) return;
+  unsigned long long row = f0 / len;
+  unsigned p = static_cast<unsigned>(f0 - row * len);
+  uint32_t out[4];
+  int full_words = 0;
+#pragma unroll
+  for (int w = 0; w < 4; ++w) {
+    const unsigned long long f = f0 + 4ull * w;
+    if (f + 4 <= total_bytes && p + 4 <= len) {
+      const uint8_t* sp = src + row * pitch + p;
+      const uintptr_t a = reinterpret_cast<uintptr_t>(sp);
+      const uint32_t* q = reinterpret_cast<const uint32_t*>(a & ~static_cast<uintptr_t>(3));
+      const uint32_t shift = static_cast<uint32_t>(a & 3) * 8;
+      const uint32_t lo = __ldg(q), hi = shift ? __ldg(q + 1) : 0u;  // a shifted read ends inside the row's pitch
+      out[w] = __funnelshift_r(lo, hi, shift);
+      ++full_words;
+      p += 4;
+      if (p == len) {
+        p = 0;
+        ++row;
+      }
+    } else {
+      uint32_t v = 0;
+      for (int e = 0; e < 4; ++e) {
+        if (f + e < total_bytes) v |= static_cast<uint32_t>(src[row * pitch + p]) << (8 * e);
+        if (++p == len) {
+          p = 0;
+          ++row;
+        }
+      }
+      out[w] = v;
+      if (f + 4 <= total_bytes) ++full_words;
+    }
+  }
+  if (full_words == 4) {
+    *reinterpret_cast<uint4*>(dst + f0) = make_uint4(out[0], out[1], out[2], out[3]);
+  } else {
+    for (int e = 0; e < 16 && f0 + e < total_bytes; ++e) dst[f0 + e] = static_cast<uint8_t>(out[e >> 2] >> (8 * (e & 3)));
+  }
+}
+
+__global__ void __launch_bounds__(kBlock) unpitch_rows_b32_kernel(const uint32_t* __restrict__ src, uint32_t* __restrict__ dst,
+                                                                  int len, int pitch, long total) {
+  pdl_sync_with_previous_kernel();
+  const long f = static_cast<long>(blockIdx.x) * kBlock + threadIdx.x;
+  if (f >= total) return;
+  const long row = f / len;
+  dst[f] = __ldg(src + row * pitch + (f - row * len));
+}
+
 }  // namespace
+
+int pitch_rows_i8_launch(plb_ctx* ctx, const void* src, void* dst, long rows, int len, int pitch) {
+  if (rows == 0) return PLB_OK;
+  if (pitch % 16 || pitch < len || (reinterpret_cast<uintptr_t>(dst) & 15))
+    return fail(PLB_E_INVALID, "row pitch must be a multiple of 16 bytes and the destination 16-byte aligned");
+  const long chunks = rows * (pitch / 16);
+  PLB_CUDA(launch_kernel(pitch_rows_kernel, dim3(blocks_for(chunks)), dim3(kBlock), 0, ctx->stream,
+                         static_cast<const uint8_t*>(src), static_cast<uint8_t*>(dst), rows, len, pitch, chunks));
+  ctx->launches++;
+  return PLB_OK;
+}
+
+int unpitch_rows_launch(plb_ctx* ctx, const void* src, void* dst, long rows, int len, int pitch, int elem_bytes) {
+  if (rows == 0) return PLB_OK;
+  const long total = rows * len;
+  if (elem_bytes == 1) {
+    if (reinterpret_cast<uintptr_t>(dst) & 15) return fail(PLB_E_INVALID, "destination must be 16-byte aligned");
+    PLB_CUDA(launch_kernel(unpitch_rows_i8_kernel, dim3(blocks_for((total + 15) / 16)), dim3(kBlock), 0, ctx->stream,
+                           static_cast<const uint8_t*>(src), static_cast<uint8_t*>(dst), static_cast<unsigned>(len),
+                           static_cast<unsigned>(pitch), static_cast<unsigned long long>(total)));
+  } else if (elem_bytes == 4) {
+    PLB_CUDA(launch_kernel(unpitch_rows_b32_kernel, dim3(blocks_for(total)), dim3(kBlock), 0, ctx->stream,
+                           static_cast<const uint32_t*>(src), static_cast<uint32_t*>(dst), len, pitch, total));
+  } else {
+    return fail(PLB_E_INVALID, "element size must be 1 or 4");
+  }
+  ctx->launches++;
+  return PLB_OK;
+}
 
 int conv_direct_launch(plb_ctx* ctx, const ConvGeom& g, const int8_t* x, const int8_t* w_rsc,
                        const OutSpec& out) {

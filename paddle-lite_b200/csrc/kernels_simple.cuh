@@ -72,6 +72,10 @@ int nhwc_to_nchw_launch(plb_ctx* ctx, const void* x, void* y, int n, int c, int 
                         int elem_bytes);
 int calib_nchw_f32_to_nhwc_i8_launch(plb_ctx* ctx, const float* x, int8_t* y, int n, int c, int h,
                                      int w, int cpad, float scale);
+// Rows of `len` bytes back to back -> rows of `pitch` bytes (multiple of 16), and back (1- or 4-byte elements;
+// len and pitch in elements there): what TMA needs for NCHW images whose pixel count is not a multiple of 16.
+int pitch_rows_i8_launch(plb_ctx* ctx, const void* src, void* dst, long rows, int len, int pitch);
+int unpitch_rows_launch(plb_ctx* ctx, const void* src, void* dst, long rows, int len, int pitch, int elem_bytes);
 int maxpool_nhwc_i8_launch(plb_ctx* ctx, const int8_t* x, int8_t* y, int n, int c, int h, int w,
                            int k, int stride, int pad);
 int global_avgpool_nhwc_f32_launch(plb_ctx* ctx, const float* x, float* y, int8_t* q, int n, int hw,

@@ -390,7 +390,11 @@ size_t plb_conv_workspace_bytes(const plb_conv* conv, int batch) {
   if (!conv || batch <= 0) return 0;
   const size_t x_bytes = staged_input_bytes(conv, batch);
   const size_t y_bytes = align_up(static_cast<size_t>(batch) * conv->ho * conv->wo * conv->d.cout * 4, 256);
-  return x_bytes + y_bytes;
+  // 1x1 layers on images whose pixel count is not a multiple of 16 stage rows of a padded pitch instead
+  const size_t hwp = align_up(static_cast<size_t>(conv->d.h) * conv->d.w, 16);
+  const size_t pitched = align_up(static_cast<size_t>(batch) * conv->d.cin * hwp, 256) +
+                         align_up(static_cast<size_t>(batch) * conv->d.cout * hwp * 4, 256);
+  return std::max(x_bytes + y_bytes, pitched);
 }
 
 int plb_softmax_f32(plb_ctx* ctx, const float* x, float* y, int rows, int cols) {
@@ -478,6 +482,17 @@ bool nchw_native(const plb_conv* c, const int8_t* x, void* y, int batch, int mod
   p->x = x; p->w = c->w.as<int8_t>();
   p->batch = batch; p->cin = d.cin; p->cin_pad = c->cin_pad; p->cout = d.cout; p->hw = d.h * d.w;
   p->out_mode = mode; p->y = y;
+  if (p->hw % 16 != 0) {
+    // Images of fewer than 100 pixels would fill under half of a 128-pixel tile: the channels-last path, whose
+    // tiles run across images, serves them better.
+    if (p->hw < 100 && c->sw.nchw != 1) return false;
+    // rows TMA cannot address: the caller stages x and y with rows a multiple of 16 bytes apart
+    p->x_pitch = static_cast<int>(align_up(p->hw, 16));
+    p->y_pitch = mode == OUT_I8 ? p->x_pitch : static_cast<int>(align_up(p->hw, 4));
+    const bool aligned = (reinterpret_cast<uintptr_t>(y) & 15) == 0;
+    p->x = nullptr; p->y = nullptr;  // filled in by the caller
+    return p->cin_pad % 32 == 0 && aligned;
+  }
   return igemm_nchw_supported(*p, nullptr);
 }
 
@@ -489,7 +504,18 @@ int conv_run_nchw(plb_conv* c, const int8_t* x, void* y, int batch, int mode) {
     NchwProblem np;
     if (nchw_native(c, x, y, batch, mode, &np)) {
       np.epi = out_spec(c, mode, y).epi;
-      return igemm_nchw_launch(ctx, np);
+      if (np.x_pitch == 0) return igemm_nchw_launch(ctx, np);
+      // pixel counts that are not a multiple of 16: re-pitch the rows into the workspace, run, copy back
+      const int eb = mode == OUT_I8 ? 1 : 4;
+      const size_t xs_bytes = align_up(static_cast<size_t>(batch) * d.cin * np.x_pitch, 256);
+      int rc = ctx->reserve(plb_conv_workspace_bytes(c, batch));
+      if (rc) return rc;
+      uint8_t* base = static_cast<uint8_t*>(ctx->ws);
+      np.x = reinterpret_cast<const int8_t*>(base);
+      np.y = base + xs_bytes;
+      if ((rc = pitch_rows_i8_launch(ctx, x, base, static_cast<long>(batch) * d.cin, np.hw, np.x_pitch))) return rc;
+      if ((rc = igemm_nchw_launch(ctx, np))) return rc;
+      return unpitch_rows_launch(ctx, np.y, y, static_cast<long>(batch) * d.cout, np.hw, np.y_pitch, eb);
     }
   }
   const size_t x_bytes = staged_input_bytes(c, batch);

@@ -135,13 +135,20 @@ NCHW_1X1_CASES = [
     (1, 96, 16, 24, 32, 1),       # three K steps of 32
     (150, 64, 16, 16, 64, 1),     # more tiles than SMs: filter resident in shared memory, several tiles per CTA
     (40, 512, 12, 12, 256, 1),    # streamed filter, several tiles per CTA
+    # pixel counts that are not multiples of 16: rows re-pitched to 16-byte multiples around the kernel
+    (2, 512, 14, 14, 512, 1),     # 196 pixels (4-byte aligned rows)
+    (3, 1024, 7, 7, 1024, 1),     # 49 pixels (rows at any byte alignment)
+    (2, 64, 9, 9, 32, 2),         # 81 pixels
+    (1, 40, 5, 7, 24, 3),         # 35 pixels, ragged channels
+    (7, 32, 1, 1, 16, 0),         # one pixel per image
 ]
 
 
 @pytest.mark.parametrize("case", NCHW_1X1_CASES, ids=lambda c: "x".join(map(str, c[:5])))
-def test_nchw_native_1x1(plb, ctx, case):
+def test_nchw_native_1x1(plb, ctx, case, monkeypatch):
     """1x1 layers through the NCHW entry point run on the NCHW tensors directly (output channels in the
     accumulator lanes, pixels in its columns); accumulators, fp32 and int8 outputs bit-identical to the oracle."""
+    monkeypatch.setenv("PLB_TC_NCHW", "1")  # also for images of fewer than 100 pixels, which default to the staged path
     n, cin, h, w, cout, act = case
     xq, in_s, wq, ws, bias = conv_case(hash(case) % 10000, n, cin, h, w, cout, 1)
     before = ctx.nchw_launch_count()
