@@ -14,9 +14,14 @@ data path).  Prints ONE JSON line on rank 0:
              host memory and reads the logits back (copies overlap the previous step's compute)
   roofline   of the dominant kernel (the tcgen05 implicit GEMM): algorithmic bytes of its
              launches in a step (every conv/fc layer after the stem) / their measured duration,
-             against the measured HBM peak
+             against the measured HBM peak (and against the nominal 8 TB/s), plus the tensor-core
+             view of the same launches and of the compute-bound class (the 3x3 convolutions)
   cpu_baseline  the reference's own x86 int8 path (oracle/_ref, built from the reference
              sources) on a bounded sample of the same workload, all host threads
+  extra      the other benchmark configurations, measured in the same process: MobileNetV1 at 32 and
+             256 images per GPU, ResNet-50 at global batch 1024 on one GPU, the per-layer table (single
+             3x3 layer, fc sweep, depthwise, sparse_conv sweep), a sustained figure (graph replays for
+             about two seconds) and the step without CUDA graphs (`--no-extras` skips all of these)
 
 `--impl reference` times only that CPU path and prints the same line shape.
 """
@@ -38,6 +43,10 @@ sys.path.insert(0, os.path.join(ROOT, "paddle-lite_b200"))
 DEFAULT_BATCH = {"resnet50": 128, "mobilenet_v1": 32}
 
 
+INT8_PEAK_TOPS = 4500.0   # dense int8 datasheet figure
+HBM_NOMINAL_GBS = 8000.0  # "about 8 TB/s" of the benchmark definition
+
+
 def measured_peaks():
     path = os.path.join(ROOT, "MEASURED_PEAKS.json")
     if os.path.exists(path):
@@ -45,6 +54,26 @@ def measured_peaks():
             d = json.load(f)
         return float(d["hbm_gbs"]), "measured"
     return 6650.0, "fallback"
+
+
+def bind_to_gpu_numa_node(nvml_index):
+    """Runs this process on the CPUs NVML reports as local to the GPU, so that the pinned host buffers
+    allocated afterwards come from the memory next to the GPU's PCIe root.  Reads topology only; sets
+    nothing on the GPU.  Returns the number of CPUs bound to, or None when NVML cannot tell."""
+    try:
+        import pynvml
+        pynvml.nvmlInit()
+        h = pynvml.nvmlDeviceGetHandleByIndex(nvml_index)
+        words = (os.cpu_count() + 63) // 64
+        mask = pynvml.nvmlDeviceGetCpuAffinity(h, words)
+        cpus = {64 * i + b for i, wd in enumerate(mask) for b in range(64) if (wd >> b) & 1}
+        allowed = os.sched_getaffinity(0)
+        cpus &= allowed
+        if cpus and cpus != allowed:
+            os.sched_setaffinity(0, cpus)
+        return len(cpus) if cpus else None
+    except Exception:
+        return None
 
 
 class ClockSampler:
@@ -231,14 +260,108 @@ def cpu_baseline(qnet, spec, sample_images, repeats=1):
 
 
 # --------------------------------------------------------------------------- main
-# DRAM read + write bytes per tcgen05 launch, from the ncu capture summarised in
-# profiles/bench_resnet50_b128_dram_traffic.md.  Traffic does not scale with the batch (small batches
-# stay in L2), so only the captured workload has a number.
-CAPTURED_TRAFFIC = {("resnet50", 128): 111.6e6}
+def graph_of(torch, stream, fn):
+    g = torch.cuda.CUDAGraph()
+    with torch.cuda.graph(g, stream=stream):
+        fn()
+    return g
 
 
-def captured_traffic(net, batch):
-    return CAPTURED_TRAFFIC.get((net, batch))
+def time_replays(torch, stream, graph, steps, sync):
+    """ms per replay, CUDA events on the launching stream."""
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    sync()
+    e0.record(stream)
+    for _ in range(steps):
+        graph.replay()
+    e1.record(stream)
+    sync()
+    return e0.elapsed_time(e1) / steps
+
+
+def tc_launches(runner, only_3x3=False):
+    """Enqueues the tensor-core launches of a step after the stem (same buffers, same order)."""
+    for st in runner.steps[1:]:
+        if st[0] == "conv" and st[1].desc.groups == 1:
+            if only_3x3 and st[1].desc.kh != 3:
+                continue
+            st[1].run_nhwc(runner.buf[st[2]], out=runner.buf[st[3]])
+        elif only_3x3:
+            continue
+        elif st[0] == "conv_add_relu":
+            _, conv, src, res, df, dq, next_s = st
+            conv.run_nhwc_add_relu(runner.buf[src], runner.buf[res], next_s, want_f32=df is not None,
+                                   out_f32=runner.buf[df] if df else None, out_i8=runner.buf[dq] if dq else None)
+        elif st[0] == "block_add_relu":
+            _, conv, src, sc_conv, sc_src, df, dq, next_s = st
+            conv.run_nhwc_block_add_relu(runner.buf[src], sc_conv, runner.buf[sc_src], next_s,
+                                         want_f32=df is not None, out_f32=runner.buf[df] if df else None,
+                                         out_i8=runner.buf[dq] if dq else None)
+        elif st[0] == "fc":
+            st[1].run(runner.buf[st[2]], out=runner.buf[st[3]])
+
+
+def measure_network(torch, plb, networks, ctx, stream, net, batch, steps, warmup, micro_batch=None):
+    """Device-resident images/s of one network at one batch on this GPU (graph replays)."""
+    spec = networks.SPECS[net]()
+    qnet = networks.build_quantized(spec, seed=1234, calib_images=16, device="cuda")
+    runner = networks.Runner(plb, ctx, qnet, batch, micro_batch=micro_batch)
+    images = torch.randn(runner.image_shape, device="cuda")
+    with torch.cuda.stream(stream):
+        n0 = ctx.launch_count()
+        runner.forward(images)
+        ctx.sync()
+        launches = ctx.launch_count() - n0
+        g = graph_of(torch, stream, lambda: runner.forward(images))
+        for _ in range(warmup):
+            g.replay()
+        ms = time_replays(torch, stream, g, steps, torch.cuda.synchronize)
+        # the same step without a CUDA graph: what a caller of Run() per layer gets
+        for _ in range(2):
+            runner.forward(images)
+        torch.cuda.synchronize()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record(stream)
+        for _ in range(max(steps // 2, 3)):
+            runner.forward(images)
+        e1.record(stream)
+        torch.cuda.synchronize()
+        eager_ms = e0.elapsed_time(e1) / max(steps // 2, 3)
+        ctx.sync()
+    out = {"workload": "%s, batch %d%s" % (spec["name"], batch, (" in slices of %d" % micro_batch) if micro_batch else ""),
+           "value": batch / (ms / 1e3), "unit": "images/s", "ms_per_step": ms, "eager_ms_per_step": eager_ms,
+           "launches_per_step": int(launches), "steps": steps}
+    del runner, images, g
+    torch.cuda.empty_cache()
+    return out
+
+
+def layer_table(plb, ctx):
+    """The per-layer configurations of the benchmark: single 3x3 layer, fc sweep, depthwise, sparse_conv sweep."""
+    import layer_bench as LB
+    L = LB.Layers(plb, ctx, iters=20, warm=0.1)
+    vendor = L.int8_peak(4096)
+    vt = vendor["TOPS"]
+    rows = [vendor, L.int8_peak(8192)]
+    rows.append(L.conv(64, 56, 64, 3, 1, 1, 1, "f32", nchw=True))        # the single-layer config, NCHW in / fp32 out
+    rows.append(L.conv(64, 56, 64, 3, 1, 1, 128, "i8"))                  # the same layer at the network's batch
+    for cin, hw in ((128, 28), (256, 14), (512, 7)):
+        rows.append(L.conv(cin, hw, cin, 3, 1, 1, 128, "i8"))
+    for m, k, n in LB.FC_SWEEP:
+        for out in ("f32", "i8"):
+            rows.append(L.fc(m, k, n, out, int8_measured_tops=vt))
+    for cin, hw, stride in ((32, 112, 1), (64, 112, 2), (128, 56, 1), (512, 14, 1)):
+        rows.append(L.conv(cin, hw, cin, 3, stride, 1, 256, "i8", groups=cin))
+    for cin, cout, hw in LB.SPARSE_SWEEP:
+        rows.append(L.sparse(cin, cout, hw, 256, False, False, "auto"))
+        rows.append(L.sparse(cin, cout, hw, 256, False, True, "auto"))
+    rows.append(L.sparse(32, 64, 112, 256, True, False, "walk"))
+    rows.append(L.sparse(128, 128, 56, 256, True, False, "walk"))
+    for r in rows:
+        r.pop("hbm_peak", None)
+        if "tensor_frac_of_vendor_gemm" not in r and r["ops"] and "cublaslt" not in r["layer"]:
+            r["tensor_frac_of_vendor_gemm"] = round(r["TOPS"] / vt, 3)
+    return rows, vt
 
 
 def main():
@@ -251,22 +374,28 @@ def main():
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--cpu-sample", type=int, default=0, help="images in the CPU baseline sample (0 = auto)")
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--no-extras", action="store_true", help="only the headline workload")
     args = ap.parse_args()
     rank = int(os.environ.get("RANK", "0"))
     world = int(os.environ.get("WORLD_SIZE", "1"))
     local_rank = int(os.environ.get("LOCAL_RANK", "0"))
-    batch = args.batch_per_gpu or DEFAULT_BATCH[args.net]
+    per_gpu = args.batch_per_gpu or DEFAULT_BATCH[args.net]
     warmup = max(args.warmup, 3)
 
     networks = importlib.import_module("paddle-lite_b200.networks")
+    sharding = importlib.import_module("paddle-lite_b200.sharding")
+    # weak scaling: the global batch grows with the number of GPUs; rank r owns a contiguous slice of it
+    global_batch = per_gpu * args.gpus
+    lo, hi = sharding.shard_slice(global_batch, rank if world > 1 else 0, max(world, 1))
+    batch = hi - lo if world > 1 else per_gpu
     spec = networks.SPECS[args.net]()
-    workload = "%s int8 PTQ, 224x224, batch %d per GPU" % (spec["name"], batch)
+    workload = "%s int8 PTQ, 224x224, batch %d per GPU" % (spec["name"], per_gpu)
     base = {"metric": "int8 %s inference throughput" % spec["name"], "unit": "images/s",
             "n_gpus": args.gpus, "steps": args.steps, "warmup": warmup, "higher_is_better": True,
             "scaling": "weak", "vs_baseline": None, "dtype": "int8 x int8 -> int32 (fp32 epilogue)",
             "data": "synthetic: seeded N(0,1) fp32 images, He-init weights quantised per channel, "
                     "activation scales from a 16-image calibration pass",
-            "config": {"workload": workload, "global_batch": batch * args.gpus, "parallelism":
+            "config": {"workload": workload, "global_batch": global_batch, "parallelism":
                        "batch-sharded replicas (dp%d), no collective" % args.gpus,
                        "l2": "per-step activations (>1 GB) exceed the 126 MB L2; no explicit flush"}}
 
@@ -302,6 +431,7 @@ def main():
     if not torch.cuda.is_available():
         raise SystemExit("bench.py needs a CUDA device (there is no CPU fallback); use --impl reference "
                          "for the CPU arm")
+    numa_cpus = bind_to_gpu_numa_node(_nvml_index(local_rank))  # before any pinned allocation
     torch.cuda.set_device(local_rank)
     if world > 1:
         dist.init_process_group("nccl", device_id=torch.device("cuda", local_rank))
@@ -321,50 +451,23 @@ def main():
     rng = np.random.default_rng(1000 + rank)
     host_images = torch.from_numpy(rng.standard_normal(runner.image_shape).astype(np.float32)).pin_memory()
     host_logits = [torch.empty((batch, 1000), dtype=torch.float32).pin_memory() for _ in range(2)]
-    dev_images = host_images.cuda()
+    dev_images = [host_images.cuda(), torch.empty(runner.image_shape, device="cuda")]
 
     def barrier():
         if world > 1:
             dist.barrier()
         torch.cuda.synchronize()
 
-    def max_over_ranks(ms):
-        if world == 1:
-            return ms
-        t = torch.tensor([ms], device="cuda", dtype=torch.float64)
-        dist.all_reduce(t, op=dist.ReduceOp.MAX)
-        return float(t.item())
-
     with torch.cuda.stream(stream):
         n0 = ctx.launch_count()
-        runner.forward(dev_images)       # eager pass: sets kernel attributes, checks for faults
+        runner.forward(dev_images[0])       # eager pass: sets kernel attributes, checks for faults
         ctx.sync()
         launches_per_step = ctx.launch_count() - n0
-        head_launches = 1
-        g_full = torch.cuda.CUDAGraph()
-        with torch.cuda.graph(g_full, stream=stream):
-            runner.forward(dev_images)
-        g_body = torch.cuda.CUDAGraph()
-        with torch.cuda.graph(g_body, stream=stream):
-            runner.forward_body()
-        # graph of the tensor-core launches alone, for the roofline of the dominant kernel
-        g_tc = torch.cuda.CUDAGraph()
-        with torch.cuda.graph(g_tc, stream=stream):
-            for st in runner.steps[1:]:
-                if st[0] == "conv" and st[1].desc.groups == 1:
-                    st[1].run_nhwc(runner.buf[st[2]], out=runner.buf[st[3]])
-                elif st[0] == "conv_add_relu":
-                    _, conv, src, res, df, dq, next_s = st
-                    conv.run_nhwc_add_relu(runner.buf[src], runner.buf[res], next_s, want_f32=df is not None,
-                                           out_f32=runner.buf[df] if df else None,
-                                           out_i8=runner.buf[dq] if dq else None)
-                elif st[0] == "block_add_relu":
-                    _, conv, src, sc_conv, sc_src, df, dq, next_s = st
-                    conv.run_nhwc_block_add_relu(runner.buf[src], sc_conv, runner.buf[sc_src], next_s,
-                                                 want_f32=df is not None, out_f32=runner.buf[df] if df else None,
-                                                 out_i8=runner.buf[dq] if dq else None)
-                elif st[0] == "fc":
-                    st[1].run(runner.buf[st[2]], out=runner.buf[st[3]])
+        g_full = graph_of(torch, stream, lambda: runner.forward(dev_images[0]))
+        g_body = graph_of(torch, stream, runner.forward_body)
+        g_tc = graph_of(torch, stream, lambda: tc_launches(runner))       # the dominant kernel's launches alone
+        has_3x3 = any(st[0] == "conv" and st[1].desc.groups == 1 and st[1].desc.kh == 3 for st in runner.steps[1:])
+        g_3x3 = graph_of(torch, stream, lambda: tc_launches(runner, only_3x3=True)) if has_3x3 else None
 
         # ---- device-resident throughput
         sampler = ClockSampler(_nvml_index(local_rank))
@@ -381,38 +484,37 @@ def main():
         barrier()
         t_end = time.perf_counter()
         clocks = sampler.stop(t_begin, t_end)
-        ms_total = max_over_ranks(e0.elapsed_time(e1))
+        value, ms_total = sharding.aggregate_throughput(batch * args.steps, e0.elapsed_time(e1))
         ms_step = ms_total / args.steps
-        value = args.gpus * batch / (ms_step / 1e3)
 
-        # ---- dominant kernel alone
+        # ---- dominant kernel alone, and the compute-bound class (3x3 convolutions) alone
         for _ in range(2):
             g_tc.replay()
-        torch.cuda.synchronize()
-        t0, t1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-        t0.record(stream)
-        for _ in range(args.steps):
-            g_tc.replay()
-        t1.record(stream)
-        torch.cuda.synchronize()
-        tc_ms_step = t0.elapsed_time(t1) / args.steps
+        tc_ms_step = time_replays(torch, stream, g_tc, args.steps, torch.cuda.synchronize)
+        c3_ms_step = None
+        if g_3x3 is not None:
+            for _ in range(2):
+                g_3x3.replay()
+            c3_ms_step = time_replays(torch, stream, g_3x3, args.steps, torch.cuda.synchronize)
 
-        # ---- end to end: pinned host images in, logits out, every step
+        # ---- end to end: pinned host images in, logits out, every step.  Two device image buffers: the
+        # copy of step i+1 runs while step i computes.
         ev_h2d = [torch.cuda.Event() for _ in range(2)]
         ev_head = [torch.cuda.Event() for _ in range(2)]
 
         def e2e_steps(n):
             for i in range(n):
+                b = i & 1
                 with torch.cuda.stream(copy_stream):
-                    if i > 0:
-                        copy_stream.wait_event(ev_head[(i - 1) & 1])  # the image buffer has been consumed
-                    dev_images.copy_(host_images, non_blocking=True)
-                    ev_h2d[i & 1].record(copy_stream)
-                stream.wait_event(ev_h2d[i & 1])
-                runner.forward_head(dev_images)
-                ev_head[i & 1].record(stream)
+                    if i >= 2:
+                        copy_stream.wait_event(ev_head[b])  # this image buffer has been consumed (two steps ago)
+                    dev_images[b].copy_(host_images, non_blocking=True)
+                    ev_h2d[b].record(copy_stream)
+                stream.wait_event(ev_h2d[b])
+                runner.forward_head(dev_images[b])
+                ev_head[b].record(stream)
                 g_body.replay()
-                host_logits[i & 1].copy_(runner.buf["logits"], non_blocking=True)
+                host_logits[b].copy_(runner.buf["logits"], non_blocking=True)
 
         e2e_steps(warmup)
         barrier()
@@ -421,26 +523,102 @@ def main():
         e2e_steps(args.steps)
         s1.record(stream)
         barrier()
-        e2e_ms_step = max_over_ranks(s0.elapsed_time(s1)) / args.steps
+        e2e_value, e2e_ms_total = sharding.aggregate_throughput(batch * args.steps, s0.elapsed_time(s1))
+        e2e_ms_step = e2e_ms_total / args.steps
+
+        # ---- the copies alone (all ranks at once, no kernels): the ceiling of the end-to-end number
+        barrier()
+        c0, c1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        c0.record(copy_stream)
+        with torch.cuda.stream(copy_stream):
+            for i in range(args.steps):
+                dev_images[i & 1].copy_(host_images, non_blocking=True)
+        c1.record(copy_stream)
+        barrier()
+        _, h2d_ms_total = sharding.aggregate_throughput(batch * args.steps, c0.elapsed_time(c1))
+        h2d_ms = h2d_ms_total / args.steps
         ctx.sync()
 
-    total_bytes, macs, tc_launches, _ = layer_bytes(spec, batch)
+    total_bytes, macs, n_tc, per_layer = layer_bytes(spec, batch)
     peak, peak_kind = measured_peaks()
     achieved = total_bytes / (tc_ms_step / 1e3) / 1e9
+    tensor_tops = 2.0 * macs / (tc_ms_step / 1e3) / 1e12
+    h2d_bytes = host_images.numel() * 4
     line = dict(base, value=value, ms_per_step=ms_step, clocks=clocks,
-                e2e={"value": args.gpus * batch / (e2e_ms_step / 1e3), "unit": "images/s",
-                     "h2d_bytes_per_step": host_images.numel() * 4, "d2h_bytes_per_step": batch * 1000 * 4,
-                     "ms_per_step": e2e_ms_step},
+                e2e={"value": e2e_value, "unit": "images/s", "h2d_bytes_per_step": h2d_bytes,
+                     "d2h_bytes_per_step": batch * 1000 * 4, "ms_per_step": e2e_ms_step,
+                     "h2d_only_ms": h2d_ms, "h2d_gbs_per_rank": h2d_bytes / (h2d_ms / 1e3) / 1e9,
+                     "ceiling_images_per_s": args.gpus * batch / (max(h2d_ms, ms_step) / 1e3),
+                     "host_cpus_bound": numa_cpus},
                 gpu_launches=int(launches_per_step * args.steps),
                 roofline={"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s",
-                          "frac": achieved / peak, "traffic": captured_traffic(args.net, batch),
-                          "traffic_unit": "bytes per launch (DRAM read + write, ncu capture of this workload)",
+                          "frac": achieved / peak, "traffic": None,
+                          "traffic_note": "no DRAM-counter capture of the current build at this size (a multi-launch "
+                                          "capture of the full-size bench is outside the profiling size rule); "
+                                          "single-layer captures are under profiles/",
+                          "frac_of_8TBs": achieved / HBM_NOMINAL_GBS,
                           "peak_source": peak_kind + " copy bandwidth",
-                          "kernel": "igemm_i8_tc_kernel", "launches_per_step": tc_launches,
-                          "algorithmic_bytes_per_launch": total_bytes / tc_launches,
-                          "avg_launch_us": 1e3 * tc_ms_step / tc_launches,
-                          "tensor_tops": 2.0 * macs / (tc_ms_step / 1e3) / 1e12,
+                          "kernel": "igemm_i8_tc_kernel", "launches_per_step": n_tc,
+                          "algorithmic_bytes_per_launch": total_bytes / n_tc,
+                          "avg_launch_us": 1e3 * tc_ms_step / n_tc,
+                          "tensor_tops": tensor_tops, "tensor_frac_of_4.5POPS": tensor_tops / INT8_PEAK_TOPS,
                           "share_of_step": tc_ms_step / ms_step})
+    if c3_ms_step is not None:
+        macs3 = sum(m for name, b, m, g in per_layer if g == 1 and name.endswith("b"))
+        bytes3 = sum(b for name, b, m, g in per_layer if g == 1 and name.endswith("b"))
+        n3 = sum(1 for name, b, m, g in per_layer if g == 1 and name.endswith("b"))
+        tops3 = 2.0 * macs3 / (c3_ms_step / 1e3) / 1e12
+        line["roofline_tensor"] = {"bound": "tensor", "kernel": "igemm_i8_tc_kernel, the %d 3x3 convolutions of a step" % n3,
+                                   "achieved": tops3, "peak": INT8_PEAK_TOPS, "unit": "TOP/s", "frac": tops3 / INT8_PEAK_TOPS,
+                                   "peak_source": "datasheet dense int8", "launches_per_step": n3,
+                                   "avg_launch_us": 1e3 * c3_ms_step / n3,
+                                   "hbm_frac_of_these_launches": bytes3 / (c3_ms_step / 1e3) / 1e9 / peak}
+    if rank == 0 and not args.no_extras and world == 1:
+        extra = {}
+        try:
+            with torch.cuda.stream(stream):
+                # sustained: graph replays for about two seconds, median of 20-step blocks, own clock samples
+                sampler = ClockSampler(_nvml_index(local_rank))
+                sampler.start()
+                t0 = time.perf_counter()
+                blocks = []
+                while time.perf_counter() - t0 < 2.0:
+                    blocks.append(time_replays(torch, stream, g_full, 20, torch.cuda.synchronize))
+                sclk = sampler.stop(t0, time.perf_counter())
+                med = statistics.median(blocks)
+                extra["sustained"] = {"seconds": round(time.perf_counter() - t0, 2), "blocks_of_20_steps": len(blocks),
+                                      "ms_per_step_median": med, "ms_per_step_min": min(blocks), "ms_per_step_max": max(blocks),
+                                      "value": batch / (med / 1e3), "unit": "images/s", "clocks": sclk}
+                # the same step launched layer by layer without a CUDA graph
+                for _ in range(2):
+                    runner.forward(dev_images[0])
+                torch.cuda.synchronize()
+                g0, g1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+                g0.record(stream)
+                for _ in range(10):
+                    runner.forward(dev_images[0])
+                g1.record(stream)
+                torch.cuda.synchronize()
+                extra["eager_ms_per_step"] = g0.elapsed_time(g1) / 10
+                ctx.sync()
+            del g_full, g_body, g_tc, g_3x3, runner
+            torch.cuda.empty_cache()
+            others = [("mobilenet_v1", 32, None), ("mobilenet_v1", 256, None), ("resnet50", 1024, 128)]
+            if args.net != "resnet50":
+                others = [("resnet50", 128, None)]
+            for net, b, mb in others:
+                key = "%s_b%d" % (net, b)
+                extra[key] = measure_network(torch, plb, networks, ctx, stream, net, b, 10 if b <= 256 else 4, 3, mb)
+            with torch.cuda.stream(stream):  # the layers' launches and the timing events on the ctx stream
+                rows, vendor_tops = layer_table(plb, ctx)
+            extra["layers"] = rows
+            extra["int8_vendor_gemm_tops"] = vendor_tops
+            line["roofline"]["tensor_frac_of_vendor_gemm"] = tensor_tops / vendor_tops
+            if "roofline_tensor" in line:
+                line["roofline_tensor"]["frac_of_vendor_gemm"] = line["roofline_tensor"]["achieved"] / vendor_tops
+        except Exception as exc:  # the extras never cost the headline line
+            extra["error"] = "%s: %s" % (type(exc).__name__, exc)
+        line["extra"] = extra
     if rank == 0:
         if not args.no_cpu_baseline and args.gpus == 1:
             try:
