@@ -47,48 +47,52 @@ void prepare(GroupGemms<T>* out, const int8_t* w, const float* wscale, const flo
   }
 }
 
+// A prepared layer = what Conv2dCompute<kInt8,*>::PrepareForRun leaves behind (conv_compute.cc:216-289,
+// :344-420): the GEMM objects with packed weights, folded scales and bias, once per kernel instance.  The
+// reference runs one kernel instance per predictor and thread (Clone()d predictors own their kernels), and a
+// GEMM object carries its own packed-B scratch (gemm_s8u8_compute.h:128-129), so a layer that is to run on
+// `threads` host threads holds that many instances, all built here, outside any timed region.
+struct PreparedConv {
+  bool out_i8;
+  int cin, h, wd, cout, kh, kw, sh, sw, pt, pb, pl, pr, dh, dw, groups;
+  int ho, wo, m, n, k;
+  bool flag_1x1;
+  int threads;
+  std::vector<int8_t> w;  // the GEMM's compute() takes the filter pointer again
+  std::vector<GroupGemms<float>> f32;
+  std::vector<GroupGemms<int8_t>> i8;
+  std::vector<std::vector<int8_t>> col;  // im2col scratch per instance
+};
+
 template <typename T>
-int conv_impl(const int8_t* x, const int8_t* w, const float* bias, T* out, int num, int cin,
-              int h, int wd, int cout, int kh, int kw, int sh, int sw, int pt, int pb, int pl,
-              int pr, int dh, int dw, int groups, const float* wscale, float in_scale,
-              float out_scale, int relu_type, float relu_alpha, int threads) {
-  const int ho = (h + pt + pb - (dh * (kh - 1) + 1)) / sh + 1;
-  const int wo = (wd + pl + pr - (dw * (kw - 1) + 1)) / sw + 1;
-  if (ho <= 0 || wo <= 0 || cin % groups || cout % groups) return -1;
-  const int m = cout / groups, n = ho * wo, k = cin / groups * kh * kw;
-  const bool flag_1x1 = kh == 1 && kw == 1 && sh == 1 && sw == 1 && pt == 0 && pb == 0 &&
-                        pl == 0 && pr == 0;
-  if (threads < 1) threads = 1;
-  if (threads > num) threads = num;
-  auto worker = [&](int tid) {
-    GroupGemms<T> gemms;
-    prepare<T>(&gemms, w, wscale, bias, groups, m, n, k, in_scale, out_scale, relu_type,
-               relu_alpha);
-    std::vector<int8_t> col;
-    if (!flag_1x1) col.resize(static_cast<size_t>(k) * n);
-    for (int b = tid; b < num; b += threads) {
-      for (int g = 0; g < groups; ++g) {
-        T* dout = out + (static_cast<long>(b) * cout + static_cast<long>(g) * m) * n;
-        const int8_t* din =
-            x + (static_cast<long>(b) * cin + static_cast<long>(g) * (cin / groups)) * h * wd;
-        const int8_t* wg = w + static_cast<long>(g) * m * k;
-        if (!flag_1x1) {
-          xm::im2col<int8_t>(din, cin / groups, h, wd, kh, kw, pt, pb, pl, pr, sh, sw, dh, dw,
-                             col.data());
-          gemms.g[g]->compute(wg, col.data(), dout);
-        } else {
-          gemms.g[g]->compute(wg, din, dout);
-        }
+void run_instance(PreparedConv* p, GroupGemms<T>& gemms, int tid, int threads, const int8_t* x, T* out, int num) {
+  for (int b = tid; b < num; b += threads) {
+    for (int g = 0; g < p->groups; ++g) {
+      T* dout = out + (static_cast<long>(b) * p->cout + static_cast<long>(g) * p->m) * p->n;
+      const int8_t* din = x + (static_cast<long>(b) * p->cin + static_cast<long>(g) * (p->cin / p->groups)) * p->h * p->wd;
+      const int8_t* wg = p->w.data() + static_cast<long>(g) * p->m * p->k;
+      if (!p->flag_1x1) {
+        xm::im2col<int8_t>(din, p->cin / p->groups, p->h, p->wd, p->kh, p->kw, p->pt, p->pb, p->pl, p->pr, p->sh,
+                           p->sw, p->dh, p->dw, p->col[tid].data());
+        gemms.g[g]->compute(wg, p->col[tid].data(), dout);
+      } else {
+        gemms.g[g]->compute(wg, din, dout);
       }
     }
-  };
-  if (threads == 1) {
-    worker(0);
-  } else {
-    std::vector<std::thread> pool;
-    for (int t = 0; t < threads; ++t) pool.emplace_back(worker, t);
-    for (auto& t : pool) t.join();
   }
+}
+
+template <typename T>
+int run_prepared(PreparedConv* p, std::vector<GroupGemms<T>>& inst, const int8_t* x, T* out, int num) {
+  int threads = p->threads < num ? p->threads : num;
+  if (threads <= 1) {
+    run_instance<T>(p, inst[0], 0, 1, x, out, num);
+    return 0;
+  }
+  std::vector<std::thread> pool;
+  for (int t = 0; t < threads; ++t)
+    pool.emplace_back([=, &inst] { run_instance<T>(p, inst[t], t, threads, x, out, num); });
+  for (auto& t : pool) t.join();
   return 0;
 }
 
@@ -99,18 +103,57 @@ extern "C" {
 // relu_type: 0 none, 1 relu, 2 relu6, 3 leaky; relu_alpha is passed to the GEMM object
 // unchanged, so an int8-out caller divides by out_scale first if it wants to mirror
 // conv_compute.cc:386-396.
+void* ref_x86_conv_prepare(const int8_t* w, const float* bias, int out_is_int8, int cin, int h, int wd, int cout,
+                           int kh, int kw, int sh, int sw, int pt, int pb, int pl, int pr, int dh, int dw, int groups,
+                           const float* wscale, float in_scale, float out_scale, int relu_type, float relu_alpha,
+                           int threads) {
+  const int ho = (h + pt + pb - (dh * (kh - 1) + 1)) / sh + 1;
+  const int wo = (wd + pl + pr - (dw * (kw - 1) + 1)) / sw + 1;
+  if (ho <= 0 || wo <= 0 || cin % groups || cout % groups) return nullptr;
+  PreparedConv* p = new PreparedConv;
+  p->out_i8 = out_is_int8 != 0;
+  p->cin = cin; p->h = h; p->wd = wd; p->cout = cout; p->kh = kh; p->kw = kw; p->sh = sh; p->sw = sw;
+  p->pt = pt; p->pb = pb; p->pl = pl; p->pr = pr; p->dh = dh; p->dw = dw; p->groups = groups;
+  p->ho = ho; p->wo = wo;
+  p->m = cout / groups; p->n = ho * wo; p->k = cin / groups * kh * kw;
+  p->flag_1x1 = kh == 1 && kw == 1 && sh == 1 && sw == 1 && pt == 0 && pb == 0 && pl == 0 && pr == 0;
+  p->threads = threads < 1 ? 1 : threads;
+  p->w.assign(w, w + static_cast<size_t>(cout) * p->k);
+  p->col.resize(p->threads);
+  if (p->out_i8) p->i8.resize(p->threads); else p->f32.resize(p->threads);
+  for (int t = 0; t < p->threads; ++t) {
+    if (!p->flag_1x1) p->col[t].resize(static_cast<size_t>(p->k) * p->n);
+    if (p->out_i8)
+      prepare<int8_t>(&p->i8[t], p->w.data(), wscale, bias, groups, p->m, p->n, p->k, in_scale, out_scale, relu_type, relu_alpha);
+    else
+      prepare<float>(&p->f32[t], p->w.data(), wscale, bias, groups, p->m, p->n, p->k, in_scale, out_scale, relu_type, relu_alpha);
+  }
+  return p;
+}
+
+// = Conv2dCompute<kInt8,*>::Run (conv_compute.cc:292-341, :423-472) on `num` images, sharded over the instances.
+int ref_x86_conv_run(void* handle, const int8_t* x, void* out, int num) {
+  PreparedConv* p = static_cast<PreparedConv*>(handle);
+  if (!p) return -1;
+  if (p->out_i8) return run_prepared<int8_t>(p, p->i8, x, static_cast<int8_t*>(out), num);
+  return run_prepared<float>(p, p->f32, x, static_cast<float*>(out), num);
+}
+
+void ref_x86_conv_destroy(void* handle) { delete static_cast<PreparedConv*>(handle); }
+
+// Prepare + run + destroy in one call (tests and fixture generation).
 int ref_x86_conv_int8(const int8_t* x, const int8_t* w, const float* bias, void* out,
                       int out_is_int8, int num, int cin, int h, int wd, int cout, int kh, int kw,
                       int sh, int sw, int pt, int pb, int pl, int pr, int dh, int dw, int groups,
                       const float* wscale, float in_scale, float out_scale, int relu_type,
                       float relu_alpha, int threads) {
-  if (out_is_int8)
-    return conv_impl<int8_t>(x, w, bias, static_cast<int8_t*>(out), num, cin, h, wd, cout, kh,
-                             kw, sh, sw, pt, pb, pl, pr, dh, dw, groups, wscale, in_scale,
-                             out_scale, relu_type, relu_alpha, threads);
-  return conv_impl<float>(x, w, bias, static_cast<float*>(out), num, cin, h, wd, cout, kh, kw,
-                          sh, sw, pt, pb, pl, pr, dh, dw, groups, wscale, in_scale, out_scale,
-                          relu_type, relu_alpha, threads);
+  if (threads > num) threads = num;
+  void* h_ = ref_x86_conv_prepare(w, bias, out_is_int8, cin, h, wd, cout, kh, kw, sh, sw, pt, pb, pl, pr, dh, dw, groups,
+                                  wscale, in_scale, out_scale, relu_type, relu_alpha, threads);
+  if (!h_) return -1;
+  const int rc = ref_x86_conv_run(h_, x, out, num);
+  ref_x86_conv_destroy(h_);
+  return rc;
 }
 
 // fc in the conv orientation: wt [N,K] (the FcParam weight [K,N] transposed by the caller),
