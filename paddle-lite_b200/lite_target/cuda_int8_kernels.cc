@@ -14,7 +14,11 @@
 // Tensors handed to these kernels hold DEVICE memory (TargetType::kCUDA buffers, e.g. wrapped
 // with lite::Buffer(void*, TargetType, size_t), lite/core/memory.h:98-99); filters, scales
 // and biases are read on the host at PrepareForRun, exactly like the x86 kernels do.
+#include <cstdio>
+#include <map>
 #include <memory>
+#include <mutex>
+#include <utility>
 #include <vector>
 
 #include "include/plb200.h"
@@ -27,22 +31,58 @@ namespace lite {
 namespace kernels {
 namespace cuda {
 
-// One context per process and device stream.  The reference creates Context<TARGET> objects in
-// ContextScheduler (lite/core/context.h:430-484); until that has a kCUDA case the kernels share
-// this one (stream 0 of device 0, or the stream given through SetPlbStream()).
-inline plb_ctx*& SharedCtx() {
-  static plb_ctx* ctx = nullptr;
-  return ctx;
+// Which device and stream a kernel runs on.  The reference keeps both in Context<TARGET>, created per
+// predictor by ContextScheduler (lite/core/context.h:430-484) and handed to the kernel through
+// KernelBase::SetContext (lite/core/kernel.h:133-136).  In a tree that has the kCUDA context of
+// INTEGRATION.md (built with -DLITE_WITH_CUDA) the binding is read from there; otherwise from a per-thread
+// binding that the host sets with SetPlbBinding() before it prepares a predictor on that thread (what
+// PaddlePredictor::SetStream(TargetType, void*), lite/api/paddle_api.h:141, forwards to).  A kernel instance
+// looks its plb_ctx up once, in PrepareForRun, and keeps it: two predictors on different devices, streams or
+// threads never share a context, a workspace or a status word.
+struct PlbBinding {
+  int device = 0;
+  void* stream = nullptr;
+};
+inline PlbBinding& ThreadBinding() {
+  static thread_local PlbBinding b;
+  return b;
 }
-inline plb_ctx* GetCtx() {
-  if (SharedCtx() == nullptr) {
-    CHECK_EQ(plb_ctx_create(0, nullptr, &SharedCtx()), PLB_OK) << plb_last_error();
-  }
-  return SharedCtx();
+inline void SetPlbBinding(int device, void* stream) {
+  ThreadBinding().device = device;
+  ThreadBinding().stream = stream;
 }
 #define PLB_CHECK(call) CHECK_EQ((call), PLB_OK) << plb_last_error()
 
-inline int ActCode(const operators::ActivationParam& act, float* alpha) {
+inline plb_ctx* CtxFor(int device, void* stream) {
+  static std::mutex mu;
+  static std::map<std::pair<int, void*>, plb_ctx*> table;  // contexts live as long as the process
+  std::lock_guard<std::mutex> lock(mu);
+  auto key = std::make_pair(device, stream);
+  auto it = table.find(key);
+  if (it != table.end()) return it->second;
+  plb_ctx* ctx = nullptr;
+  PLB_CHECK(plb_ctx_create(device, stream, &ctx));
+  table[key] = ctx;
+  return ctx;
+}
+
+template <typename Kernel>
+inline plb_ctx* CtxOf(Kernel* kernel) {
+#ifdef LITE_WITH_CUDA
+  auto& c = kernel->mutable_context()->template As<CUDAContext>();
+  return CtxFor(c.device_id(), c.exec_stream());
+#else
+  (void)kernel;
+  return CtxFor(ThreadBinding().device, ThreadBinding().stream);
+#endif
+}
+
+// relu_type of the int8 kernels.  `strict` (sparse_conv2d): the ARM reference applies every activation the fuse
+// pass may hand it, hard_swish included (lite/kernels/arm/sparse_conv_compute.cc:91-100); this target implements
+// relu / relu6 / leaky_relu, so anything else must stop the program rather than run without activation.  conv2d /
+// depthwise_conv2d mirror the x86 int8 kernel, which leaves relu_type 0 for other types
+// (lite/kernels/x86/conv_compute.cc:257-270).
+inline int ActCode(const operators::ActivationParam& act, float* alpha, bool strict = false) {
   *alpha = 0.f;
   if (!act.has_active) return PLB_ACT_NONE;
   switch (act.active_type) {
@@ -55,7 +95,13 @@ inline int ActCode(const operators::ActivationParam& act, float* alpha) {
       *alpha = act.Leaky_relu_alpha;
       return PLB_ACT_LEAKY;
     default:
-      return PLB_ACT_NONE;  // the x86 int8 kernel ignores other types as well
+      if (strict) {
+        // builds without LITE_WITH_LOG abort silently on LOG(FATAL): say why first
+        std::fprintf(stderr, "sparse_conv2d on kCUDA: activation type %d (e.g. hard_swish) is not implemented; "
+                             "supported: relu, relu6, leaky_relu\n", static_cast<int>(act.active_type));
+        LOG(FATAL) << "sparse_conv2d on kCUDA: unsupported activation type " << static_cast<int>(act.active_type);
+      }
+      return PLB_ACT_NONE;
   }
 }
 
@@ -94,18 +140,20 @@ class ConvInt8Compute : public KernelLite<TARGET(kCUDA), PRECISION(kInt8)> {
     d.impl = PLB_IMPL_AUTO;
     const float* bias = param.bias ? param.bias->template data<float>() : nullptr;
     plb_conv* conv = nullptr;
-    PLB_CHECK(plb_conv_prepare(GetCtx(), &d, param.filter->template data<int8_t>(),
+    PLB_CHECK(plb_conv_prepare(CtxOf(this), &d, param.filter->template data<int8_t>(),
                                param.weight_scale.data(), static_cast<int>(param.weight_scale.size()),
                                bias, &conv));
     conv_.reset(conv);
+    in_c_ = d.cin;
     in_h_ = d.h;
     in_w_ = d.w;
   }
 
   void ReInitWhenNeeded() override {
-    // a prepared layer is bound to its input height/width; re-plan when they change
+    // A prepared layer is bound to its input channels / height / width (the batch is given per run); re-plan
+    // when they change.  (The x86 kernel freezes them at the first PrepareForRun, conv_compute.cc:225-228.)
     auto x_dims = this->Param<param_t>().x->dims();
-    if (conv_ && (x_dims[2] != in_h_ || x_dims[3] != in_w_)) PrepareForRun();
+    if (conv_ && (x_dims[1] != in_c_ || x_dims[2] != in_h_ || x_dims[3] != in_w_)) PrepareForRun();
   }
 
   void Run() override {
@@ -122,7 +170,7 @@ class ConvInt8Compute : public KernelLite<TARGET(kCUDA), PRECISION(kInt8)> {
     void operator()(plb_conv* p) const { plb_conv_destroy(p); }
   };
   std::unique_ptr<plb_conv, Deleter> conv_;
-  int64_t in_h_{0}, in_w_{0};
+  int64_t in_c_{0}, in_h_{0}, in_w_{0};
 };
 
 // The same layer on channels-last tensors (DATALAYOUT(kNHWC)).  Registered next to the NCHW
@@ -164,10 +212,18 @@ class ConvInt8NhwcCompute : public KernelLite<TARGET(kCUDA), PRECISION(kInt8), D
     d.impl = PLB_IMPL_AUTO;
     const float* bias = param.bias ? param.bias->template data<float>() : nullptr;
     plb_conv* conv = nullptr;
-    PLB_CHECK(plb_conv_prepare(GetCtx(), &d, param.filter->template data<int8_t>(),
+    PLB_CHECK(plb_conv_prepare(CtxOf(this), &d, param.filter->template data<int8_t>(),
                                param.weight_scale.data(), static_cast<int>(param.weight_scale.size()),
                                bias, &conv));
     conv_.reset(conv);
+    in_c_ = d.cin;
+    in_h_ = d.h;
+    in_w_ = d.w;
+  }
+
+  void ReInitWhenNeeded() override {
+    auto x_dims = this->Param<param_t>().x->dims();
+    if (conv_ && (x_dims[1] != in_c_ || x_dims[2] != in_h_ || x_dims[3] != in_w_)) PrepareForRun();
   }
 
   void Run() override {
@@ -184,6 +240,7 @@ class ConvInt8NhwcCompute : public KernelLite<TARGET(kCUDA), PRECISION(kInt8), D
     void operator()(plb_conv* p) const { plb_conv_destroy(p); }
   };
   std::unique_ptr<plb_conv, Deleter> conv_;
+  int64_t in_c_{0}, in_h_{0}, in_w_{0};
 };
 
 template <PrecisionType OutType>
@@ -204,7 +261,7 @@ class FcInt8Compute : public KernelLite<TARGET(kCUDA), PRECISION(kInt8)> {
     }
     const float* bias = param.bias ? param.bias->template data<float>() : nullptr;
     plb_fc* fc = nullptr;
-    PLB_CHECK(plb_fc_prepare(GetCtx(), k, n, act, alpha, param.input_scale, param.output_scale,
+    PLB_CHECK(plb_fc_prepare(CtxOf(this), k, n, act, alpha, param.input_scale, param.output_scale,
                              OutType == PRECISION(kInt8) ? PLB_OUT_I8 : PLB_OUT_F32,
                              param.w->template data<int8_t>(), param.weight_scale.data(),
                              static_cast<int>(param.weight_scale.size()), bias, &fc));
@@ -244,7 +301,7 @@ class SparseConvCompute : public KernelLite<TARGET(kCUDA), InType> {
     d.out_dtype = OutType == PRECISION(kInt8) ? PLB_OUT_I8 : PLB_OUT_F32;
     d.flag_semi = param.flag_semi;
     d.first_ic = param.first_ic;
-    d.act = ActCode(param.activation_param, &d.act_alpha);
+    d.act = ActCode(param.activation_param, &d.act_alpha, /*strict=*/true);
     d.in_scale = param.input_scale;
     d.out_scale = param.output_scale;
     d.leaky_compat = 1;  // sparse_conv_compute.cc:86-90 divides the slope as well
@@ -253,12 +310,22 @@ class SparseConvCompute : public KernelLite<TARGET(kCUDA), InType> {
                                : static_cast<const void*>(param.nonzero_weights->template data<float>());
     const float* bias = param.bias ? param.bias->template data<float>() : nullptr;
     plb_sparse* sp = nullptr;
-    PLB_CHECK(plb_sparse_prepare(GetCtx(), &d, nz, static_cast<int>(param.nonzero_weights->numel()),
+    PLB_CHECK(plb_sparse_prepare(CtxOf(this), &d, nz, static_cast<int>(param.nonzero_weights->numel()),
                                  param.oc_nonzeros->template data<uint32_t>(),
                                  param.diffs->template data<int32_t>(),
                                  static_cast<int>(param.diffs->numel()), param.weight_scale.data(),
                                  static_cast<int>(param.weight_scale.size()), bias, &sp));
     sp_.reset(sp);
+    in_c_ = d.cin;
+    in_h_ = d.h;
+    in_w_ = d.w;
+  }
+
+  void ReInitWhenNeeded() override {
+    // diffs are byte offsets scaled by H*W, so the encoding itself belongs to one image size; a graph that
+    // changes it re-runs the detect pass and hands this kernel new tensors
+    auto x_dims = this->template Param<param_t>().x->dims();
+    if (sp_ && (x_dims[1] != in_c_ || x_dims[2] != in_h_ || x_dims[3] != in_w_)) PrepareForRun();
   }
 
   void Run() override {
@@ -277,33 +344,43 @@ class SparseConvCompute : public KernelLite<TARGET(kCUDA), InType> {
     void operator()(plb_sparse* p) const { plb_sparse_destroy(p); }
   };
   std::unique_ptr<plb_sparse, Deleter> sp_;
+  int64_t in_c_{0}, in_h_{0}, in_w_{0};
 };
 
 // calib fp32 <-> int8 between layers (mirrors lite/kernels/x86/calib_compute.cc:28-36, :156-168;
 // operators::CalibParam, lite/operators/op_params.h:74-78).
 class CalibFp32ToInt8Compute : public KernelLite<TARGET(kCUDA), PRECISION(kInt8)> {
  public:
+  void PrepareForRun() override { plb_ = CtxOf(this); }
   void Run() override {
     auto& param = this->Param<operators::CalibParam>();
-    PLB_CHECK(plb_calib_f32_to_i8(GetCtx(), param.input->template data<float>(),
+    PLB_CHECK(plb_calib_f32_to_i8(plb_, param.input->template data<float>(),
                                   param.output->template mutable_data<int8_t>(TARGET(kCUDA)),
                                   static_cast<size_t>(param.input->numel()), param.scale));
   }
+
+ private:
+  plb_ctx* plb_{nullptr};
 };
 class CalibInt8ToFp32Compute : public KernelLite<TARGET(kCUDA), PRECISION(kInt8)> {
  public:
+  void PrepareForRun() override { plb_ = CtxOf(this); }
   void Run() override {
     auto& param = this->Param<operators::CalibParam>();
-    PLB_CHECK(plb_calib_i8_to_f32(GetCtx(), param.input->template data<int8_t>(),
+    PLB_CHECK(plb_calib_i8_to_f32(plb_, param.input->template data<int8_t>(),
                                   param.output->template mutable_data<float>(TARGET(kCUDA)),
                                   static_cast<size_t>(param.input->numel()), param.scale));
   }
+
+ private:
+  plb_ctx* plb_{nullptr};
 };
 
 // softmax over the last axis of an fp32 tensor (classifier head; operators::SoftmaxParam,
 // lite/operators/op_params.h:292-297; x86 kernel lite/kernels/x86/softmax_compute.h).
 class SoftmaxCompute : public KernelLite<TARGET(kCUDA), PRECISION(kFloat)> {
  public:
+  void PrepareForRun() override { plb_ = CtxOf(this); }
   void Run() override {
     auto& param = this->Param<operators::SoftmaxParam>();
     auto dims = param.x->dims();
@@ -312,15 +389,19 @@ class SoftmaxCompute : public KernelLite<TARGET(kCUDA), PRECISION(kFloat)> {
     CHECK_EQ(axis, rank - 1) << "the kCUDA softmax kernel handles the last axis";
     const int cols = static_cast<int>(dims[rank - 1]);
     const int rows = static_cast<int>(dims.production() / cols);
-    PLB_CHECK(plb_softmax_f32(GetCtx(), param.x->template data<float>(),
+    PLB_CHECK(plb_softmax_f32(plb_, param.x->template data<float>(),
                               param.output->template mutable_data<float>(TARGET(kCUDA)), rows, cols));
   }
+
+ private:
+  plb_ctx* plb_{nullptr};
 };
 
 // io_copy host <-> device (mirrors lite/kernels/xpu/io_copy_compute.cc:54-116; operators::IoCopyParam,
 // lite/operators/op_params.h:60-66).  The destination keeps the source's dims, precision and LoD.
 class IoCopyHostToCudaCompute : public KernelLite<TARGET(kCUDA), PRECISION(kAny), DATALAYOUT(kAny)> {
  public:
+  void PrepareForRun() override { plb_ = CtxOf(this); }
   void Run() override {
     auto& param = this->Param<operators::IoCopyParam>();
     CHECK(param.x != nullptr && param.y != nullptr) << "io_copy handles single tensors";
@@ -329,11 +410,15 @@ class IoCopyHostToCudaCompute : public KernelLite<TARGET(kCUDA), PRECISION(kAny)
     param.y->set_precision(param.x->precision());
     param.y->set_lod(param.x->lod());
     void* dst = param.y->mutable_data(TARGET(kCUDA), bytes);
-    PLB_CHECK(plb_copy_h2d(GetCtx(), dst, param.x->raw_data(), bytes));
+    PLB_CHECK(plb_copy_h2d(plb_, dst, param.x->raw_data(), bytes));
   }
+
+ private:
+  plb_ctx* plb_{nullptr};
 };
 class IoCopyCudaToHostCompute : public KernelLite<TARGET(kCUDA), PRECISION(kAny), DATALAYOUT(kAny)> {
  public:
+  void PrepareForRun() override { plb_ = CtxOf(this); }
   void Run() override {
     auto& param = this->Param<operators::IoCopyParam>();
     CHECK(param.x != nullptr && param.y != nullptr) << "io_copy handles single tensors";
@@ -342,8 +427,11 @@ class IoCopyCudaToHostCompute : public KernelLite<TARGET(kCUDA), PRECISION(kAny)
     param.y->set_precision(param.x->precision());
     param.y->set_lod(param.x->lod());
     void* dst = param.y->mutable_data(TARGET(kHost), bytes);
-    PLB_CHECK(plb_copy_d2h(GetCtx(), dst, param.x->raw_data(), bytes));
+    PLB_CHECK(plb_copy_d2h(plb_, dst, param.x->raw_data(), bytes));
   }
+
+ private:
+  plb_ctx* plb_{nullptr};
 };
 
 }  // namespace cuda
