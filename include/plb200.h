@@ -77,6 +77,8 @@ long plb_ctx_launch_count(const plb_ctx* ctx);
 long plb_ctx_window_launch_count(const plb_ctx* ctx);
 /* How many 1x1 convolutions ran directly on NCHW tensors (no layout staging passes).  For tests. */
 long plb_ctx_nchw_launch_count(const plb_ctx* ctx);
+/* How many GEMMs ran as two-SM tiles (256 x N output tiles on pairs of SMs).  For tests. */
+long plb_ctx_pair_launch_count(const plb_ctx* ctx);
 /* Bytes of layout-staging scratch the ctx currently holds (its own or the caller's).  Test hook. */
 size_t plb_ctx_workspace_size(const plb_ctx* ctx);
 

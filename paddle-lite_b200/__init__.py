@@ -58,6 +58,7 @@ SYMBOLS = {
     "plb_ctx_launch_count": (C.c_long, [_P]),
     "plb_ctx_window_launch_count": (C.c_long, [_P]),
     "plb_ctx_nchw_launch_count": (C.c_long, [_P]),
+    "plb_ctx_pair_launch_count": (C.c_long, [_P]),
     "plb_ctx_workspace_size": (C.c_size_t, [_P]),
     "plb_conv_plan_cache_hits": (C.c_long, [_P]),
     "plb_conv_prepare": (C.c_int, [_P, C.POINTER(ConvDesc), _P, _P, C.c_int, _P, C.POINTER(_P)]),
@@ -149,6 +150,9 @@ class Context:
 
     def nchw_launch_count(self):
         return lib().plb_ctx_nchw_launch_count(self.handle)
+
+    def pair_launch_count(self):
+        return lib().plb_ctx_pair_launch_count(self.handle)
 
     def workspace_size(self):
         return lib().plb_ctx_workspace_size(self.handle)

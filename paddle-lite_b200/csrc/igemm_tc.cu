@@ -20,6 +20,7 @@
 // Every mbarrier wait is bounded; a wait that runs out records a fault in the ctx status
 // word and the CTA drains and exits instead of hanging.
 #include "igemm_tc.cuh"
+#include "igemm_pair.cuh"
 #include "tc_device.cuh"
 
 #include <algorithm>
@@ -1738,6 +1739,7 @@ int igemm_tc_plan(plb_ctx* ctx, const IgemmProblem& p, const TcSwitches& sw_, Ig
 }  // namespace
 
 int igemm_tc_launch(plb_ctx* ctx, const IgemmProblem& p, IgemmPlanCache* cache) {
+  if (igemm_pair_wanted(ctx, p)) return igemm_pair_launch(ctx, p);
   static const TcSwitches kDefaults;
   const TcSwitches& sw = p.sw ? *p.sw : kDefaults;
   const IgemmPlan* plan = nullptr;

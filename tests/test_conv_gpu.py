@@ -164,6 +164,33 @@ def test_nchw_native_switch_off(plb, ctx, monkeypatch):
     assert ctx.nchw_launch_count() == before
 
 
+# (n, cin, h, w, cout, k, stride, pad, act)
+PAIR_CASES = [
+    (4, 128, 28, 28, 128, 3, 1, 1, 1),    # 13 pair tiles of 256 pixels, the last one ragged
+    (8, 256, 14, 14, 256, 3, 1, 1, 1),    # 256-wide channel tile: each CTA holds 128 filter rows
+    (2, 512, 28, 28, 256, 1, 1, 0, 2),    # flat GEMM, four K steps of 128
+    (5, 512, 7, 7, 512, 3, 1, 1, 0),      # 245 rows: the follower CTA of the only row tile has no valid row; two channel tiles
+    (2, 64, 56, 56, 64, 3, 1, 1, 3),      # 64-channel tile (32 filter rows per CTA), K steps of 64
+    (3, 128, 30, 30, 128, 3, 2, 1, 1),    # strided
+    (150, 128, 8, 8, 320, 3, 1, 1, 1),    # more tiles than pairs: several tiles per pair, ragged second channel tile
+    (1, 96, 20, 20, 64, 3, 1, 1, 1),      # three channel chunks of 32 per tap
+]
+
+
+@pytest.mark.parametrize("case", PAIR_CASES, ids=lambda c: "x".join(map(str, c[:7])))
+def test_two_sm_tiles_bit_exact(plb, ctx, case, monkeypatch):
+    """256 x N output tiles on pairs of SMs (tcgen05.mma.cta_group::2, each CTA holding its 128 rows of A and half of
+    the filter tile), forced on for shapes of every kind: accumulators, fp32 and int8 outputs against the oracle."""
+    monkeypatch.setenv("PLB_TC_PAIR", "1")
+    monkeypatch.setenv("PLB_TC_NCHW", "0")  # 1x1 layers through the channels-last kernels, where the pair tiles live
+    n, cin, h, w, cout, k, s, p, act = case
+    xq, in_s, wq, ws, bias = conv_case(hash(case) % 10000, n, cin, h, w, cout, k)
+    before = ctx.pair_launch_count()
+    run_case(plb, ctx, xq, in_s, wq, ws, bias, stride=(s, s), pads=(p, p, p, p), act=act, alpha=6.0 if act == 2 else 0.1)
+    assert ctx.pair_launch_count() == before + 3, "the two-SM kernel was not taken"
+    ctx.sync()
+
+
 def test_golden_config1_shape(plb, ctx):
     """The single-layer benchmark config (1 x 64 x 56 x 56 -> 64, 3x3, pad 1, ReLU) against the committed output of
     the reference objects, through the NCHW entry point; and bit-identical to the oracle."""

@@ -75,6 +75,29 @@ def test_golden_fc_sweep_shape(plb, ctx):
     assert np.array_equal(y, O.fc_int8(g["x"], g["w"], g["ws"], g["in_s"], g["bias"], O.ACT_RELU6, 6.0))
 
 
+@pytest.mark.parametrize("m,k,n", [(300, 1024, 1000), (64, 2048, 256), (515, 512, 128)])
+def test_fc_two_sm_tiles(plb, ctx, m, k, n, monkeypatch):
+    """fc as 256-row tiles on pairs of SMs (forced): ragged rows and a ragged last channel tile."""
+    monkeypatch.setenv("PLB_TC_PAIR", "1")
+    x, wq, ws, bias = fc_case(m + n, m, k, n)
+    acc_ref = O.fc_acc_i32(x, wq)
+    y_ref = O.epilogue(acc_ref, ws, 0.02, bias, O.ACT_RELU6, 6.0)
+    out_s = float(max(np.abs(y_ref).max(), 1e-6) / 127)
+    q_ref = O.epilogue(acc_ref, ws, 0.02, bias, O.ACT_RELU6, 6.0, out_scale=out_s)
+    xd = dev(x)
+    before = ctx.pair_launch_count()
+    f32 = plb.Fc(ctx, wq, ws, 0.02, bias, O.ACT_RELU6, 6.0)
+    acc = f32.acc_i32(xd).cpu().numpy()
+    y = f32.run(xd).cpu().numpy()
+    q = plb.Fc(ctx, wq, ws, 0.02, bias, O.ACT_RELU6, 6.0, out_scale=out_s).run(xd).cpu().numpy()
+    ctx.sync()
+    # (rows of 1000 int8 outputs are not 16-byte multiples: that layer keeps the one-SM kernel)
+    assert ctx.pair_launch_count() == before + (3 if n % 16 == 0 else 2)
+    assert np.array_equal(acc, acc_ref)
+    assert np.array_equal(y, y_ref)
+    assert np.array_equal(q, q_ref)
+
+
 def test_fc_errors(plb, ctx):
     x, wq, ws, bias = fc_case(1, 4, 64, 8)
     with pytest.raises(plb.PlbError):
