@@ -721,6 +721,62 @@ __global__ void __launch_bounds__(kBlock)
   y[(n * g.cout + oc) * static_cast<long>(g.hw) + p] = act_apply(v, act, alpha);
 }
 
+// fp32, pixel tiles: a block stages x[all cin][P = 4 * PG pixels] of one image in shared memory.  PG lanes cover the
+// tile with one float4 each, so a warp walks 32 / PG output channels at a time; its 8 warps share the channels.  Per
+// non-zero a lane group reads one packed {input channel, weight} pair (the same address in all its lanes: a
+// broadcast), one float4 of the staged tile and does four fused multiply-adds -- the per-pixel sum is formed exactly as
+// in sparse_f32_kernel: bias first, then one fmaf per non-zero in stored (ascending input channel) order.  The loads
+// of a tile and the stores of its outputs are full 512-byte rows.
+template <int PG>
+__global__ void __launch_bounds__(kBlock)
+    sparse_f32_tile_kernel(const SparseGeom g, const float* __restrict__ x, const int* __restrict__ row_ptr,
+                           const int2* __restrict__ col_val, const float* __restrict__ bias, const int act,
+                           const float alpha, float* __restrict__ y) {
+  pdl_sync_with_previous_kernel();
+  extern __shared__ uint32_t slab[];
+  float4* sl = reinterpret_cast<float4*>(slab);  // [cin][PG] float4
+  constexpr int P = 4 * PG;
+  const long n = blockIdx.y;
+  const int p0 = blockIdx.x * P;
+  const float* xb = x + n * g.cin * static_cast<long>(g.hw) + p0;
+  const int valid = min(P, g.hw - p0);  // a multiple of 4
+  for (int i = threadIdx.x; i < g.cin * PG; i += kBlock) {
+    const int c = i / PG, q = i - c * PG;
+    sl[i] = 4 * q < valid ? __ldg(reinterpret_cast<const float4*>(xb + static_cast<long>(c) * g.hw) + q)
+                          : make_float4(0.f, 0.f, 0.f, 0.f);
+  }
+  __syncthreads();
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  constexpr int kPerWarp = 32 / PG;             // output channels a warp walks at once
+  const int q = lane % PG, sub = lane / PG;
+  const bool store = 4 * q < valid;
+  for (int oc0 = warp * kPerWarp; oc0 < g.cout; oc0 += (kBlock / 32) * kPerWarp) {
+    const int oc = oc0 + sub;
+    const bool live = oc < g.cout;
+    const float b = (live && bias) ? __ldg(bias + oc) : 0.f;
+    float4 acc = make_float4(b, b, b, b);
+    int t = live ? __ldg(row_ptr + oc) : 0;
+    const int t1 = live ? __ldg(row_ptr + oc + 1) : 0;
+    for (; t + 1 < t1; t += 2) {
+      const int2 cv0 = __ldg(col_val + t), cv1 = __ldg(col_val + t + 1);
+      const float4 x0 = sl[cv0.x * PG + q], x1 = sl[cv1.x * PG + q];
+      const float w0 = __int_as_float(cv0.y), w1 = __int_as_float(cv1.y);
+      acc.x = fmaf(w0, x0.x, acc.x); acc.y = fmaf(w0, x0.y, acc.y); acc.z = fmaf(w0, x0.z, acc.z); acc.w = fmaf(w0, x0.w, acc.w);
+      acc.x = fmaf(w1, x1.x, acc.x); acc.y = fmaf(w1, x1.y, acc.y); acc.z = fmaf(w1, x1.z, acc.z); acc.w = fmaf(w1, x1.w, acc.w);
+    }
+    if (t < t1) {
+      const int2 cv = __ldg(col_val + t);
+      const float4 xv = sl[cv.x * PG + q];
+      const float w = __int_as_float(cv.y);
+      acc.x = fmaf(w, xv.x, acc.x); acc.y = fmaf(w, xv.y, acc.y); acc.z = fmaf(w, xv.z, acc.z); acc.w = fmaf(w, xv.w, acc.w);
+    }
+    if (live && store)
+      *reinterpret_cast<float4*>(y + (n * g.cout + oc) * static_cast<long>(g.hw) + p0 + 4 * q) =
+          make_float4(act_apply(acc.x, act, alpha), act_apply(acc.y, act, alpha), act_apply(acc.z, act, alpha),
+                      act_apply(acc.w, act, alpha));
+  }
+}
+
 // fp32 with the input slab in shared memory: a block stages x[all cin][256*VEC pixels] of one
 // image and each thread walks every output channel for VEC consecutive pixels.  Per pixel the
 // sum is formed exactly as above: bias first, then one fmaf per non-zero in stored order.
@@ -1357,9 +1413,22 @@ int sparse_slab_launch(plb_ctx* ctx, const SparseGeom& g, const int8_t* x, const
 }
 
 int sparse_csr_launch(plb_ctx* ctx, const SparseGeom& g, const void* x, const int* row_ptr,
-                      const int* col, const void* val, const float* bias_raw, const EpiParams& epi,
-                      void* y) {
+                      const int* col, const void* val, const void* col_val, const float* bias_raw,
+                      const EpiParams& epi, void* y) {
   if (g.batch == 0 || g.hw == 0) return PLB_OK;
+  if (!g.is_int8 && col_val && g.hw % 4 == 0 && g.cin <= 512 && g.batch <= 65535 &&
+      ((reinterpret_cast<uintptr_t>(x) | reinterpret_cast<uintptr_t>(y)) & 15) == 0) {
+    // pixel-tile kernel: the widest tile whose slab stays at 64 KiB, so that two blocks share an SM
+    const int pg = g.cin <= 128 ? 32 : (g.cin <= 256 ? 16 : 8);
+    auto kern = pg == 32 ? sparse_f32_tile_kernel<32> : (pg == 16 ? sparse_f32_tile_kernel<16> : sparse_f32_tile_kernel<8>);
+    const size_t smem = static_cast<size_t>(g.cin) * pg * 16;
+    PLB_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, 64 * 1024));
+    dim3 grid((g.hw + 4 * pg - 1) / (4 * pg), g.batch);
+    PLB_CUDA(launch_kernel(kern, grid, dim3(kBlock), smem, ctx->stream, g, static_cast<const float*>(x), row_ptr,
+                           static_cast<const int2*>(col_val), bias_raw, epi.act, epi.alpha, static_cast<float*>(y)));
+    ctx->launches++;
+    return PLB_OK;
+  }
   if (g.cout > 65535 || g.batch > 65535) return fail(PLB_E_UNSUPPORTED, "sparse grid too large");
   if (g.is_int8) {
     const bool vec4 = (g.hw & 3) == 0 && (reinterpret_cast<uintptr_t>(x) & 3) == 0 &&

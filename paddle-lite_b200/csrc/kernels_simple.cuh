@@ -48,9 +48,11 @@ struct SparseGeom {
   int is_int8;     // input/weight type
   int out_mode;    // OUT_F32 / OUT_I8
 };
+// col_val (fp32 only, nullable): {input channel, weight bits} pairs, one 8-byte word per non-zero, for the pixel-tile
+// kernel.
 int sparse_csr_launch(plb_ctx* ctx, const SparseGeom& g, const void* x, const int* row_ptr,
-                      const int* col, const void* val, const float* bias_raw, const EpiParams& epi,
-                      void* y);
+                      const int* col, const void* val, const void* col_val, const float* bias_raw,
+                      const EpiParams& epi, void* y);
 
 // int8 variant that stages the input slab in shared memory and walks non-zeros four at a time
 // with dp4a (grp_ptr [cout+1], grp_idx = 4 x uint16 input channels, grp_w = 4 x int8 weights).

@@ -149,6 +149,7 @@ struct plb_sparse {
   plb_sparse_desc d;
   int nnz = 0;
   DeviceBuf row_ptr, col, val, bias_raw;
+  DeviceBuf col_val;  // fp32: {input channel, weight bits} per non-zero
   DeviceBuf grp_ptr, grp_idx, grp_w;  // int8: non-zeros in groups of four for the slab kernel
   DeviceBuf scale, bias;
   float alpha = 0.f;
@@ -886,6 +887,14 @@ int plb_sparse_prepare(plb_ctx* ctx, const plb_sparse_desc* desc, const void* no
   if (d.is_int8) rc = s->val.upload(val8.data(), val8.size());
   else rc = s->val.upload(valf.data(), valf.size() * sizeof(float));
   if (rc) return rc;
+  if (!d.is_int8) {
+    std::vector<int32_t> cv(2 * col.size());
+    for (size_t i = 0; i < col.size(); ++i) {
+      cv[2 * i] = col[i];
+      memcpy(&cv[2 * i + 1], &valf[i], 4);
+    }
+    if ((rc = s->col_val.upload(cv.data(), cv.size() * sizeof(int32_t)))) return rc;
+  }
   if (d.is_int8) {
     std::vector<int> gptr(d.cout + 1, 0);
     std::vector<uint32_t> gidx, gw;
@@ -957,7 +966,7 @@ int plb_sparse_run(plb_sparse* sp, const void* x, void* y, int batch) {
   if (sparse_slab_supported(g, x, y))
     return sparse_slab_launch(sp->ctx, g, static_cast<const int8_t*>(x), sp->grp_ptr.as<int>(), sp->grp_idx.p,
                               sp->grp_w.p, e, y);
-  return sparse_csr_launch(sp->ctx, g, x, sp->row_ptr.as<int>(), sp->col.as<int>(), sp->val.p,
+  return sparse_csr_launch(sp->ctx, g, x, sp->row_ptr.as<int>(), sp->col.as<int>(), sp->val.p, sp->col_val.p,
                            sp->bias_raw.as<float>(), e, y);
 }
 

@@ -27,7 +27,9 @@ def sparse_weights(seed, cout, cin, semi, keep=0.2):
 SHAPES = [(32, 64, 12, 2), (128, 128, 14, 2), (256, 256, 7, 3), (109, 33, 5, 1), (512, 512, 7, 1),
           # images of more than 1024 pixels (several blocks of the shared-memory slab kernels, ragged last block),
           # channel counts on each side of the slab kernels' pixels-per-thread thresholds, odd pixel counts
-          (24, 40, 36, 1), (48, 16, 34, 2), (100, 20, 33, 1), (150, 8, 36, 1)]
+          (24, 40, 36, 1), (48, 16, 34, 2), (100, 20, 33, 1), (150, 8, 36, 1),
+          # fp32 pixel-tile kernel: 16 and 8 lanes per output channel (cin > 128, > 256), ragged last tile, cin > 512 (fallback)
+          (200, 96, 16, 2), (512, 48, 12, 1), (130, 37, 30, 1), (520, 24, 8, 1)]
 
 
 @pytest.mark.parametrize("impl", [1, 2, 0], ids=["walk", "densified", "auto"])
@@ -57,7 +59,7 @@ def test_sparse_int8(plb, ctx, cin, cout, side, batch, semi, impl):
 
 
 @pytest.mark.parametrize("semi", [False, True], ids=["unstructured", "semi"])
-@pytest.mark.parametrize("cin,cout,side,batch", SHAPES[:4] + SHAPES[5:])
+@pytest.mark.parametrize("cin,cout,side,batch", SHAPES[:4] + SHAPES[5:])  # (512 x 512 takes the oracle too long)
 def test_sparse_fp32(plb, ctx, cin, cout, side, batch, semi):
     wf = sparse_weights(cin * 3 + cout, cout, cin, semi)
     rng = np.random.default_rng(6)
