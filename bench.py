@@ -579,7 +579,7 @@ def main():
                           "frac": achieved / peak, "traffic": None,
                           "traffic_note": "no DRAM-counter capture of the current build at this size (a multi-launch "
                                           "capture of the full-size bench is outside the profiling size rule); "
-                                          "single-layer captures are under profiles/",
+                                          "single-launch captures exist per kernel",
                           "frac_of_8TBs": achieved / HBM_NOMINAL_GBS,
                           "peak_source": peak_kind + " copy bandwidth",
                           "kernel": "igemm_i8_tc_kernel", "launches_per_step": n_tc,

@@ -33,8 +33,8 @@ namespace cuda {
 
 // Which device and stream a kernel runs on.  The reference keeps both in Context<TARGET>, created per
 // predictor by ContextScheduler (lite/core/context.h:430-484) and handed to the kernel through
-// KernelBase::SetContext (lite/core/kernel.h:133-136).  In a tree that has the kCUDA context of
-// INTEGRATION.md (built with -DLITE_WITH_CUDA) the binding is read from there; otherwise from a per-thread
+// KernelBase::SetContext (lite/core/kernel.h:133-136).  In a tree that has Context<TargetType::kCUDA> (the patch
+// kcuda_target.patch next to this file, built with -DLITE_WITH_CUDA) the binding is read from there; otherwise from a per-thread
 // binding that the host sets with SetPlbBinding() before it prepares a predictor on that thread (what
 // PaddlePredictor::SetStream(TargetType, void*), lite/api/paddle_api.h:141, forwards to).  A kernel instance
 // looks its plb_ctx up once, in PrepareForRun, and keeps it: two predictors on different devices, streams or
