@@ -386,6 +386,36 @@ def layer_table(plb, ctx):
     return rows, vt
 
 
+# DRAM read + write bytes as a fraction of the algorithmic bytes, per class of tensor-core launch, from single-launch
+# ncu captures of one layer of each class at the benchmark's batch (dram__bytes_read.sum + dram__bytes_write.sum of
+# `layer_bench.py` commands).  Traffic below the algorithmic bytes means that a tensor written by one launch is still in
+# the 126 MB L2 when it ends; none of the classes re-reads.  bench.py scales each layer's algorithmic bytes by its
+# class's ratio to estimate the DRAM traffic of a step; only ResNet-50 at 128 images per GPU has captures behind it.
+TRAFFIC_RATIO = {"residual": 899.3 / 950.6,    # conv + fp32 residual + ReLU + calib, 64 -> 256 @ 56 x 56
+                 "block_tail": 508.3 / 565.2,  # the same with the shortcut GEMM inside
+                 "pointwise": 108.6 / 128.5,   # 1x1, int8 out, 256 -> 64 @ 56 x 56
+                 "conv3x3": 25.9 / 51.4}       # 3x3, int8 out, 64 -> 64 @ 56 x 56 (window mode)
+
+
+def estimated_traffic(spec, batch, per_layer, shortcuts):
+    """DRAM bytes per tensor-core launch of a step, estimated per class (see TRAFFIC_RATIO); None without captures."""
+    if spec["name"] != "resnet50_v1.5" or batch != 128:
+        return None
+    ops = {op["name"]: op for op in spec["ops"] if "name" in op}
+    total, n = 0.0, 0
+    for name, b, m, groups in per_layer:
+        op = ops[name]
+        if groups != 1 or op.get("src") == "x":
+            continue
+        if op["op"] == "conv_add_relu":
+            cls = "block_tail" if op["residual"] in shortcuts else "residual"
+        else:
+            cls = "conv3x3" if op["k"] == 3 else "pointwise"
+        total += b * TRAFFIC_RATIO[cls]
+        n += 1
+    return (total / n, total) if n else None
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -566,6 +596,8 @@ def main():
     total_bytes, macs, n_tc, per_layer = layer_bytes(spec, batch)
     peak, peak_kind = measured_peaks()
     achieved = total_bytes / (tc_ms_step / 1e3) / 1e9
+    fused = networks.fusable_shortcuts(spec) if os.environ.get("PLB_FUSE_BLOCKS", "1") != "0" else {}
+    traffic = estimated_traffic(spec, batch, per_layer, fused)
     tensor_tops = 2.0 * macs / (tc_ms_step / 1e3) / 1e12
     h2d_bytes = host_images.numel() * 4
     line = dict(base, value=value, ms_per_step=ms_step, clocks=clocks,
@@ -576,10 +608,12 @@ def main():
                      "host_cpus_bound": numa_cpus},
                 gpu_launches=int(launches_per_step * args.steps),
                 roofline={"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s",
-                          "frac": achieved / peak, "traffic": None,
-                          "traffic_note": "no DRAM-counter capture of the current build at this size (a multi-launch "
-                                          "capture of the full-size bench is outside the profiling size rule); "
-                                          "single-launch captures exist per kernel",
+                          "frac": achieved / peak, "traffic": traffic[0] if traffic else None,
+                          "traffic_note": "bytes per launch, estimated: each layer's algorithmic bytes x the DRAM / algorithmic "
+                                          "ratio of a single-launch ncu capture of its class (residual, block tail, "
+                                          "pointwise, 3x3); the fc launch is not counted" if traffic else
+                                          "no single-launch captures for this workload",
+                          "frac_of_traffic": (traffic[1] / (tc_ms_step / 1e3) / 1e9 / peak) if traffic else None,
                           "frac_of_8TBs": achieved / HBM_NOMINAL_GBS,
                           "peak_source": peak_kind + " copy bandwidth",
                           "kernel": "igemm_i8_tc_kernel", "launches_per_step": n_tc,

@@ -1338,6 +1338,7 @@ TcSwitches tc_switches_from_env() {
   TcSwitches s;
   s.slab = env_int("PLB_TC_SLAB", -1);
   s.bn = env_int("PLB_TC_BN", -1);
+  s.kc = env_int("PLB_TC_KC", -1);
   s.stages = env_int("PLB_TC_STAGES", -1);
   s.acc_bufs = env_int("PLB_TC_ACC_BUFS", -1);
   s.resident = env_int("PLB_TC_RESIDENT", 1);
@@ -1411,6 +1412,7 @@ int igemm_tc_plan(plb_ctx* ctx, const IgemmProblem& p, const TcSwitches& sw_, Ig
   a.m_total = p.m_total;
   a.cout = p.cout;
   a.kc = pick_kc(p.cin_pad);
+  if ((sw_.kc == 32 || sw_.kc == 64) && sw_.kc < a.kc) a.kc = sw_.kc;
   const bool dual = p.a2 != nullptr;
   if (dual) {
     if (p.out_mode != OUT_ADD_RELU || p.residual != nullptr || p.im2col || p.b2 == nullptr || p.cin_pad2 % 32 != 0 ||

@@ -17,6 +17,7 @@ enum OutMode : int {
 struct TcSwitches {
   int slab = -1;          // PLB_TC_SLAB: window mode off (0) / forced wherever it fits (1)
   int bn = -1;            // PLB_TC_BN: channel tile
+  int kc = -1;            // PLB_TC_KC: bytes of K per pipeline stage (32 / 64 / 128), at most what the channels allow
   int stages = -1;        // PLB_TC_STAGES: operand ring depth
   int acc_bufs = -1;      // PLB_TC_ACC_BUFS: accumulator buffers in tensor memory (2, 4, 8)
   int resident = 1;       // PLB_TC_RESIDENT=0: never keep the filter in shared memory
