@@ -1435,6 +1435,7 @@ int igemm_tc_plan(plb_ctx* ctx, const IgemmProblem& p, const TcSwitches& sw_, Ig
   // tiles must be a multiple of 32 wide: halve only down to such widths)
   while (bn > 32 && tiles_m * ((cout16 + bn - 1) / bn) < ctx->sm_count && (bn / 2) % 32 == 0) bn /= 2;
   bn = sw_or(sw_.bn, bn);
+  if (dual && bn > 128) bn = 128;  // also after an override: two accumulators per tile must fit the 512 TMEM columns
   if (bn > cout16) bn = cout16;
   if (bn < cout16 && bn % 32) bn = bn / 32 * 32;
   if (bn < 16 || bn > 256 || bn % 16) return fail(PLB_E_INVALID, "bad channel tile %d", bn);
@@ -1718,6 +1719,14 @@ int igemm_tc_plan(plb_ctx* ctx, const IgemmProblem& p, const TcSwitches& sw_, Ig
   }
   const size_t smem = smem_needed();
   if (smem > 227 * 1024) return fail(PLB_E_UNSUPPORTED, "pipeline needs %zu bytes of shared memory", smem);
+  {
+    // tensor memory: acc_bufs buffers of the tile's columns rounded up to a power of two (twice that in dual mode)
+    int acc_cols = 32;
+    while (acc_cols < bn) acc_cols <<= 1;
+    if (acc_cols * (dual ? 2 : 1) * a.acc_bufs > 512)
+      return fail(PLB_E_INVALID, "tile of %d columns with %d accumulator buffers does not fit the 512 columns of tensor memory",
+                  bn, a.acc_bufs);
+  }
   IgemmKernel kernel = pick_kernel(p.out_mode, p.epi.act, staged);
   {
     // the attribute belongs to (function, device): remember which pairs have been configured
