@@ -1434,6 +1434,14 @@ int igemm_tc_plan(plb_ctx* ctx, const IgemmProblem& p, const TcSwitches& sw_, Ig
   // (the epilogue works in chunks of 32 columns, so a tile that is not the last one of its row of
   // tiles must be a multiple of 32 wide: halve only down to such widths)
   while (bn > 32 && tiles_m * ((cout16 + bn - 1) / bn) < ctx->sm_count && (bn / 2) % 32 == 0) bn /= 2;
+  // Measured per layer (ResNet-50, batch 128): a convolution that adds an fp32 residual and writes fp32 + int8 is
+  // bound by its epilogue's HBM traffic and runs best with narrow tiles (512 channels on 28 x 28: 81 us at 64
+  // columns, 87 at 128, 90 at 256); a layer of 256 output channels has a single 256-wide tile per row of pixels
+  // and loses to wave quantisation (196 tiles on 148 SMs: 10.6 us against 9.9 us at 128 columns).
+  if (!dual && p.out_mode == OUT_ADD_RELU && p.residual != nullptr && cout16 >= 512 && bn > 64)
+    bn = 64;
+  else if (!dual && cout16 == 256 && bn == 256)
+    bn = 128;
   bn = sw_or(sw_.bn, bn);
   if (dual && bn > 128) bn = 128;  // also after an override: two accumulators per tile must fit the 512 TMEM columns
   if (bn > cout16) bn = cout16;
