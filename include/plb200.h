@@ -79,6 +79,8 @@ long plb_ctx_window_launch_count(const plb_ctx* ctx);
 long plb_ctx_nchw_launch_count(const plb_ctx* ctx);
 /* How many GEMMs ran as two-SM tiles (256 x N output tiles on pairs of SMs).  For tests. */
 long plb_ctx_pair_launch_count(const plb_ctx* ctx);
+/* How many depthwise + 1x1 pairs ran as one launch (plb_conv_run_nhwc_dwpw).  For tests. */
+long plb_ctx_dwpw_launch_count(const plb_ctx* ctx);
 /* Bytes of layout-staging scratch the ctx currently holds (its own or the caller's).  Test hook. */
 size_t plb_ctx_workspace_size(const plb_ctx* ctx);
 
@@ -160,6 +162,19 @@ int plb_conv_run_nhwc_add_relu(plb_conv* conv, const int8_t* x, const float* res
  * the kind the reference's MIR fusion passes perform; it has no single-kernel counterpart there. */
 int plb_conv_run_nhwc_block_add_relu(plb_conv* conv, const int8_t* x, plb_conv* shortcut, const int8_t* x_shortcut,
                                      float* y_f32, int8_t* y_i8, float next_scale, int batch);
+/* A depthwise 3x3 layer and the 1x1 layer that consumes it in one launch (a MobileNet block): the int8
+ * tensor between them is produced in shared memory as the tensor-core operand and never written, so the
+ * pair reads x and writes y and nothing else.  Arithmetic of the two-kernel sequence  depthwise_conv2d
+ * (int8_out) -> conv2d (int8_out)  bit for bit (lite/kernels/x86/conv_compute.cc:216-341 run twice).
+ * `dw` prepared with groups == cin == cout, 3x3, stride 1 or 2, int8 out, activation none / relu / relu6,
+ * 32 / 64 / 128 / 256 channels; `pw` an unpadded 1x1 layer on the depthwise output, int8 out, 32 .. 512
+ * output channels (a power of two), its filter small enough to stay in shared memory; both on the same
+ * ctx; x [batch,h,w,c], y [batch,ho,wo,cout] channels-last.  plb_conv_dwpw_fusable() tells whether a pair
+ * qualifies (1) or the two layers have to be run one after the other (0); the run call returns
+ * PLB_E_UNSUPPORTED for a pair that does not.  A graph-level fusion beyond the reference's fusion passes
+ * (lite/core/optimizer/mir/fusion/): it has no counterpart there. */
+int plb_conv_dwpw_fusable(const plb_conv* dw, const plb_conv* pw);
+int plb_conv_run_nhwc_dwpw(plb_conv* dw, plb_conv* pw, const int8_t* x, int8_t* y, int batch);
 int plb_conv_out_dims(const plb_conv* conv, int* ho, int* wo);
 /* A prepared layer keeps the tile plan and the TMA descriptors of the (batch, pointers) it has been
  * run on, so that a repeated Run() costs one kernel launch on the host (the reference re-derives

@@ -59,6 +59,9 @@ SYMBOLS = {
     "plb_ctx_window_launch_count": (C.c_long, [_P]),
     "plb_ctx_nchw_launch_count": (C.c_long, [_P]),
     "plb_ctx_pair_launch_count": (C.c_long, [_P]),
+    "plb_ctx_dwpw_launch_count": (C.c_long, [_P]),
+    "plb_conv_dwpw_fusable": (C.c_int, [_P, _P]),
+    "plb_conv_run_nhwc_dwpw": (C.c_int, [_P, _P, _P, _P, C.c_int]),
     "plb_ctx_workspace_size": (C.c_size_t, [_P]),
     "plb_conv_plan_cache_hits": (C.c_long, [_P]),
     "plb_conv_prepare": (C.c_int, [_P, C.POINTER(ConvDesc), _P, _P, C.c_int, _P, C.POINTER(_P)]),
@@ -153,6 +156,9 @@ class Context:
 
     def pair_launch_count(self):
         return lib().plb_ctx_pair_launch_count(self.handle)
+
+    def dwpw_launch_count(self):
+        return lib().plb_ctx_dwpw_launch_count(self.handle)
 
     def workspace_size(self):
         return lib().plb_ctx_workspace_size(self.handle)
@@ -354,6 +360,20 @@ class Conv:
                                                       _dev_ptr(yf), _dev_ptr(yq),
                                                       next_scale if next_scale is not None else 1.0, n))
         return yf, yq
+
+    def dwpw_fusable(self, pointwise):
+        """Whether this depthwise 3x3 layer and the 1x1 layer `pointwise` can run as one launch."""
+        return bool(lib().plb_conv_dwpw_fusable(self.handle, pointwise.handle))
+
+    def run_nhwc_dwpw(self, pointwise, x, out=None):
+        """pointwise(self(x)) in one launch: self a depthwise 3x3 layer, `pointwise` the 1x1 layer on its output,
+        both int8-out; the tensor between them is never written.  x [n,h,w,c] int8 channels-last."""
+        import torch
+        n = x.shape[0]
+        y = out if out is not None else torch.empty((n, pointwise.ho, pointwise.wo, pointwise.desc.cout),
+                                                    dtype=torch.int8, device=x.device)
+        _check(lib().plb_conv_run_nhwc_dwpw(self.handle, pointwise.handle, _dev_ptr(x), _dev_ptr(y), n))
+        return y
 
     def close(self):
         if self.handle:

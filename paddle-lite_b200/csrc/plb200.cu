@@ -6,6 +6,7 @@
 #include <memory>
 #include <mutex>
 
+#include "fused_dwpw.cuh"
 #include "igemm_nchw.cuh"
 #include "igemm_tc.cuh"
 #include "kernels_simple.cuh"
@@ -238,6 +239,7 @@ int plb_ctx_set_workspace(plb_ctx* ctx, void* dptr, size_t bytes) {
 long plb_ctx_launch_count(const plb_ctx* ctx) { return ctx ? ctx->launches : 0; }
 long plb_ctx_window_launch_count(const plb_ctx* ctx) { return ctx ? ctx->window_launches : 0; }
 long plb_ctx_nchw_launch_count(const plb_ctx* ctx) { return ctx ? ctx->nchw_launches : 0; }
+long plb_ctx_dwpw_launch_count(const plb_ctx* ctx) { return ctx ? ctx->dwpw_launches : 0; }
 long plb_ctx_pair_launch_count(const plb_ctx* ctx) { return ctx ? ctx->pair_launches : 0; }
 size_t plb_ctx_workspace_size(const plb_ctx* ctx) { return ctx ? ctx->ws_bytes : 0; }
 
@@ -568,6 +570,61 @@ int plb_conv_run_nhwc(plb_conv* conv, const int8_t* x, void* y, int batch) {
   PLB_CUDA(cudaSetDevice(conv->ctx->device));
   OutSpec o = out_spec(conv, conv->d.out_dtype == PLB_OUT_I8 ? OUT_I8 : OUT_F32, y);
   return conv_core(conv, x, batch, o);
+}
+
+namespace {
+// The problem of a depthwise 3x3 layer followed by a 1x1 layer as one launch; false when the pair does not qualify.
+bool dwpw_problem(const plb_conv* dw, const plb_conv* pw, int batch, const int8_t* x, int8_t* y, DwpwProblem* p,
+                  std::string* why) {
+  auto no = [&](const char* m) {
+    if (why) *why = m;
+    return false;
+  };
+  if (!dw || !pw || dw->ctx != pw->ctx) return no("both layers must belong to the same context");
+  const plb_conv_desc& a = dw->d;
+  const plb_conv_desc& b = pw->d;
+  if (dw->kind != 2 || a.kh != 3 || a.kw != 3 || a.dil_h != 1 || a.dil_w != 1 || a.stride_h != a.stride_w)
+    return no("first layer must be a depthwise 3x3 convolution");
+  if (a.out_dtype != PLB_OUT_I8 || dw->cin_pad != a.cin) return no("depthwise layer must write int8 and have unpadded channels");
+  if (pw->kind != 0 || pw->fold || b.kh != 1 || b.kw != 1 || b.stride_h != 1 || b.stride_w != 1 || b.pad_top || b.pad_bottom ||
+      b.pad_left || b.pad_right || b.groups != 1)
+    return no("second layer must be a plain 1x1 convolution");
+  if (b.cin != a.cout || pw->cin_pad != b.cin || b.h != dw->ho || b.w != dw->wo) return no("the 1x1 layer does not take the depthwise output");
+  if (b.out_dtype != PLB_OUT_I8) return no("the 1x1 layer must write int8");
+  if (dw->sw.dwpw == 0) return no("switched off");
+  memset(p, 0, sizeof(*p));
+  p->x = x; p->batch = batch; p->h = a.h; p->w = a.w; p->c = a.cin;
+  p->stride = a.stride_h; p->pad_t = a.pad_top; p->pad_l = a.pad_left; p->ho = dw->ho; p->wo = dw->wo;
+  p->wdw = dw->w.as<int8_t>(); p->cg_pad = dw->cg_pad;
+  p->dw_epi = out_spec(dw, OUT_I8, nullptr).epi;
+  p->wpw = pw->w.as<int8_t>(); p->cout = b.cout;
+  p->pw_epi = out_spec(pw, OUT_I8, nullptr).epi;
+  p->y = y; p->ldy = b.cout;
+  p->tw = dw->sw.dwpw_tw; p->seg_rows = dw->sw.dwpw_seg;
+  return dwpw_fused_supported(dw->ctx, *p, why);
+}
+}  // namespace
+
+int plb_conv_dwpw_fusable(const plb_conv* dw, const plb_conv* pw) {
+  DwpwProblem p;
+  // pointer alignment is checked at run time; any 16-byte aligned address stands in for it here
+  return dwpw_problem(dw, pw, 1, reinterpret_cast<const int8_t*>(uintptr_t(256)), reinterpret_cast<int8_t*>(uintptr_t(256)), &p,
+                      nullptr)
+             ? 1
+             : 0;
+}
+
+int plb_conv_run_nhwc_dwpw(plb_conv* dw, plb_conv* pw, const int8_t* x, int8_t* y, int batch) {
+  PLB_REQUIRE(dw != nullptr && pw != nullptr, "null argument");
+  PLB_REQUIRE(batch >= 0, "negative batch");
+  if (batch == 0) return PLB_OK;
+  PLB_REQUIRE(x && y, "null argument");
+  DwpwProblem p;
+  std::string why;
+  if (!dwpw_problem(dw, pw, batch, x, y, &p, &why))
+    return fail(PLB_E_UNSUPPORTED, "depthwise + 1x1 in one launch: %s", why.c_str());
+  PLB_CUDA(cudaSetDevice(dw->ctx->device));
+  return dwpw_fused_launch(dw->ctx, p);
 }
 
 int plb_conv_run_image_f32(plb_conv* conv, const float* x, void* y, int batch) {
