@@ -319,6 +319,8 @@ def tc_launches(runner, only_3x3=False):
             conv.run_nhwc_block_add_relu(runner.buf[src], sc_conv, runner.buf[sc_src], next_s,
                                          want_f32=df is not None, out_f32=runner.buf[df] if df else None,
                                          out_i8=runner.buf[dq] if dq else None)
+        elif st[0] == "dwpw":
+            st[1].run_nhwc_dwpw(st[2], runner.buf[st[3]], out=runner.buf[st[4]])
         elif st[0] == "fc":
             st[1].run(runner.buf[st[2]], out=runner.buf[st[3]])
 
@@ -374,6 +376,8 @@ def layer_table(plb, ctx):
             rows.append(L.fc(m, k, n, out, int8_measured_tops=vt))
     for cin, hw, stride in ((32, 112, 1), (64, 112, 2), (128, 56, 1), (512, 14, 1)):
         rows.append(L.conv(cin, hw, cin, 3, stride, 1, 256, "i8", groups=cin))
+    for cin, cout, hw, stride in ((32, 64, 112, 1), (64, 128, 112, 2), (128, 128, 56, 1), (256, 256, 28, 1)):
+        rows.append(L.dwpw(cin, cout, hw, stride, 256))                  # MobileNetV1 blocks: depthwise + 1x1 in one launch
     for cin, cout, hw in LB.SPARSE_SWEEP:
         rows.append(L.sparse(cin, cout, hw, 256, False, False, "auto"))
         rows.append(L.sparse(cin, cout, hw, 256, False, True, "auto"))

@@ -3,6 +3,7 @@
 
     python layer_bench.py conv   --cin 64 --hw 56 --cout 64 --k 3 --pad 1 --batch 128 [--out i8|f32|addrelu] [--nchw]
     python layer_bench.py dw     --cin 32 --hw 112 --stride 1 --batch 128
+    python layer_bench.py dwpw   --cin 128 --cout 128 --hw 56 --stride 1 --batch 256            # depthwise 3x3 + 1x1 in one launch
     python layer_bench.py block  --cin 64 --cin2 64 --hw 56 --cout 256 --stride 1 --batch 128   # projection-block tail
     python layer_bench.py fc     --m 4096 --kdim 4096 --n 4096 [--out i8|f32]
     python layer_bench.py sparse --cin 128 --cout 128 --hw 56 --batch 256 [--fp32] [--semi] [--impl walk|dense]
@@ -180,6 +181,35 @@ class Layers:
         return report("block %d->%d + %d->%d(s%d) %dx%d b%d" % (cin, cout, cin2, cout, s2, hw, hw, batch), us,
                       pix * (cin + cin2 + 5 * cout) + cout * (cin + cin2), 2.0 * pix * cout * (cin + cin2))
 
+    def dwpw(self, cin, cout, hw, stride, batch):
+        """Depthwise 3x3 + 1x1 convolution (a MobileNet block): one launch against the two launches it replaces."""
+        import torch
+        plb, ctx, rng = self.plb, self.ctx, self.rng
+        wdw = rng.integers(-127, 128, (cin, 1, 3, 3), dtype=np.int8)
+        wpw = rng.integers(-127, 128, (cout, cin, 1, 1), dtype=np.int8)
+        dw = plb.Conv(ctx, wdw, [0.002], 0.02, None, in_hw=(hw, hw), stride=(stride, stride), pads=(1,) * 4, groups=cin,
+                      act=plb.ACT_RELU, out_scale=0.05)
+        pw = plb.Conv(ctx, wpw, [0.001], 0.05, None, in_hw=(dw.ho, dw.wo), act=plb.ACT_RELU, out_scale=0.05)
+        x = torch.randint(-127, 128, (batch, hw, hw, cin), dtype=torch.int8, device="cuda")
+        mid = torch.empty((batch, dw.ho, dw.wo, cin), dtype=torch.int8, device="cuda")
+        y = torch.empty((batch, dw.ho, dw.wo, cout), dtype=torch.int8, device="cuda")
+
+        def two():
+            dw.run_nhwc(x, out=mid)
+            pw.run_nhwc(mid, out=y)
+        us2 = time_launches(two, self.iters, self.warm)
+        pix = batch * dw.ho * dw.wo
+        nbytes = x.numel() + y.numel() + 9 * cin + cin * cout
+        ops = 2.0 * pix * cin * (cout + 9)
+        extra = {"two_launches_us": round(us2, 2), "two_launches_bytes": int(nbytes + 2 * mid.numel())}
+        name = "dw3x3+1x1 cin%d %dx%d s%d cout%d b%d" % (cin, hw, hw, stride, cout, batch)
+        if not dw.dwpw_fusable(pw):
+            ctx.sync()
+            return report(name + " (two launches)", us2, nbytes + 2 * mid.numel(), ops, extra)
+        us = time_launches(lambda: dw.run_nhwc_dwpw(pw, x, out=y), self.iters, self.warm)
+        ctx.sync()
+        return report(name, us, nbytes, ops, extra)
+
     def int8_peak(self, n):
         """Not a kernel of this library: the vendor int8 GEMM on the same GPU, as a measured tensor-core denominator."""
         import torch
@@ -191,7 +221,7 @@ class Layers:
 
 def main():
     ap = argparse.ArgumentParser()
-    ap.add_argument("kind", choices=["conv", "dw", "block", "fc", "sparse", "fc-sweep", "sparse-sweep", "int8-peak"])
+    ap.add_argument("kind", choices=["conv", "dw", "dwpw", "block", "fc", "sparse", "fc-sweep", "sparse-sweep", "int8-peak"])
     ap.add_argument("--cin2", type=int, default=64, help="block: input channels of the shortcut conv")
     ap.add_argument("--cin", type=int, default=64)
     ap.add_argument("--cout", type=int, default=64)
@@ -224,6 +254,8 @@ def main():
         show(L.conv(args.cin, args.hw, args.cout, args.k, args.stride, args.pad, args.batch, args.out, nchw=args.nchw))
     elif args.kind == "dw":
         show(L.conv(args.cin, args.hw, args.cin, 3, args.stride, 1, args.batch, args.out, groups=args.cin))
+    elif args.kind == "dwpw":
+        show(L.dwpw(args.cin, args.cout, args.hw, args.stride, args.batch))
     elif args.kind == "fc":
         show(L.fc(args.m, args.kdim, args.n, args.out))
     elif args.kind == "fc-sweep":

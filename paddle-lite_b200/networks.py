@@ -276,8 +276,38 @@ class Runner:
                 self.buf[op["dst"]] = torch.empty((batch, op["n"]), dtype=torch.float32, device=dev)
                 self.steps.append(("fc", fc, op["src"], op["dst"]))
         self.in_scale = float(scales["x"])
+        # Measured slower than the two launches it replaces (both roles are bound by instruction issue and latency, and
+        # one CTA cannot hold as many warps of each as the two kernels do), so it is opt-in.
+        if os.environ.get("PLB_DWPW", "0") == "1":
+            self._fuse_depthwise_pairs()
         self.logits = torch.empty((full_batch, self.buf["logits"].shape[1]), dtype=torch.float32, device=dev)
         self.buf["logits"] = self.logits[:batch]
+
+    def _fuse_depthwise_pairs(self):
+        """A depthwise 3x3 layer whose only reader is the 1x1 layer after it runs in that layer's launch
+        (plb_conv_run_nhwc_dwpw) where the pair qualifies; the tensor between them is then never written."""
+        readers = {}
+        for st in self.steps:
+            for name in (st[2:3] if st[0] in ("conv", "conv_image") else ()):
+                readers[name] = readers.get(name, 0) + 1
+            if st[0] in ("conv_add_relu", "block_add_relu"):
+                for name in (st[2], st[3] if st[0] == "conv_add_relu" else st[4]):
+                    readers[name] = readers.get(name, 0) + 1
+            if st[0] in ("maxpool", "avgpool_calib"):
+                readers[st[1]] = readers.get(st[1], 0) + 1
+        fused, i = [], 0
+        while i < len(self.steps):
+            a = self.steps[i]
+            b = self.steps[i + 1] if i + 1 < len(self.steps) else None
+            if (a[0] == "conv" and b is not None and b[0] == "conv" and b[2] == a[3] and readers.get(a[3], 0) == 1
+                    and a[1].desc.groups > 1 and a[1].dwpw_fusable(b[1])):
+                fused.append(("dwpw", a[1], b[1], a[2], b[3]))
+                del self.buf[a[3]]
+                i += 2
+            else:
+                fused.append(a)
+                i += 1
+        self.steps = fused
 
     def forward(self, image_f32_nchw):
         """image_f32_nchw: device float32 [batch,3,224,224].  Returns the fp32 logits [batch,1000]."""
@@ -302,6 +332,8 @@ class Runner:
         for st in self.steps[1:]:
             if st[0] == "conv":
                 st[1].run_nhwc(b[st[2]], out=b[st[3]])
+            elif st[0] == "dwpw":
+                st[1].run_nhwc_dwpw(st[2], b[st[3]], out=b[st[4]])
             elif st[0] == "conv_add_relu":
                 _, conv, src, res, df, dq, next_s = st
                 conv.run_nhwc_add_relu(b[src], b[res], next_s, want_f32=df is not None,

@@ -43,6 +43,31 @@ def test_network_bit_exact(plb, ctx, name):
     assert np.isfinite(want["logits"]).all() and np.abs(want["logits"]).max() > 0
 
 
+def test_mobilenet_with_fused_depthwise_pairs(plb, ctx, monkeypatch):
+    """MobileNetV1 with every qualifying depthwise + 1x1 pair in one launch (blocks 1 - 6): same logits and
+    same 1x1 outputs as the oracle, and six launches fewer."""
+    N = nets()
+    spec = N.SPECS["mobilenet_v1"]()
+    qnet = N.build_quantized(spec, seed=7, calib_images=4, device="cuda")
+    rng = np.random.default_rng(99)
+    images = rng.standard_normal((2,) + spec["image"]).astype(np.float32)
+    monkeypatch.setenv("PLB_DWPW", "1")
+    runner = N.Runner(plb, ctx, qnet, 2)
+    fused = [st for st in runner.steps if st[0] == "dwpw"]
+    assert len(fused) == 6
+    before = ctx.dwpw_launch_count()
+    logits = runner.forward(torch.from_numpy(images).cuda())
+    ctx.sync()
+    assert ctx.dwpw_launch_count() == before + 6
+    want = net_oracle.forward(qnet, images)
+    for key, ref in want.items():
+        if key not in runner.buf or runner.buf[key].ndim != 4:
+            continue
+        got = runner.buf[key].cpu().numpy().transpose(0, 3, 1, 2)[:, :ref.shape[1]]
+        assert np.array_equal(got, ref), "tensor %s differs from the oracle" % key
+    assert np.array_equal(logits.cpu().numpy(), want["logits"])
+
+
 def test_graph_replay_matches_eager(plb, ctx):
     """The benchmark replays the forward pass as a CUDA graph; the replay must give the same
     logits as the eager enqueue."""
