@@ -79,6 +79,8 @@ long plb_ctx_window_launch_count(const plb_ctx* ctx);
 long plb_ctx_nchw_launch_count(const plb_ctx* ctx);
 /* How many GEMMs ran as two-SM tiles (256 x N output tiles on pairs of SMs).  For tests. */
 long plb_ctx_pair_launch_count(const plb_ctx* ctx);
+/* How many first layers ran from the fp32 image in one launch (plb_conv_run_image_f32 without a staging pass).  For tests. */
+long plb_ctx_stem_launch_count(const plb_ctx* ctx);
 /* How many depthwise + 1x1 pairs ran as one launch (plb_conv_run_nhwc_dwpw).  For tests. */
 long plb_ctx_dwpw_launch_count(const plb_ctx* ctx);
 /* Bytes of layout-staging scratch the ctx currently holds (its own or the caller's).  Test hook. */

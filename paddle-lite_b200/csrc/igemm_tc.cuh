@@ -29,6 +29,7 @@ struct TcSwitches {
   int pair = -1;          // PLB_TC_PAIR: two-SM tiles (cta_group::2) off (0) / forced wherever they fit (1)
   int nchw = -1;          // PLB_TC_NCHW: NCHW-native 1x1 kernel off (0) / forced wherever it fits (1)
   int dw_strip = -1;      // PLB_DW_STRIP: depthwise 3x3 rows per strip (0 = the register-tiled kernel)
+  int stem = -1;          // PLB_STEM=0: first layers always run as a staging pass + convolution
   int dwpw = -1;          // PLB_DWPW=0: depthwise + 1x1 pairs never run as one launch
   int dwpw_tw = -1;       // PLB_DWPW_TW: tile columns of the fused depthwise + 1x1 kernel (4 / 8 / 16)
   int dwpw_seg = -1;      // PLB_DWPW_SEG: output rows per work item of that kernel

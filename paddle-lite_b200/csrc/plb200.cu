@@ -10,6 +10,7 @@
 #include "igemm_nchw.cuh"
 #include "igemm_tc.cuh"
 #include "kernels_simple.cuh"
+#include "stem_tc.cuh"
 
 namespace plb {
 
@@ -239,6 +240,7 @@ int plb_ctx_set_workspace(plb_ctx* ctx, void* dptr, size_t bytes) {
 long plb_ctx_launch_count(const plb_ctx* ctx) { return ctx ? ctx->launches : 0; }
 long plb_ctx_window_launch_count(const plb_ctx* ctx) { return ctx ? ctx->window_launches : 0; }
 long plb_ctx_nchw_launch_count(const plb_ctx* ctx) { return ctx ? ctx->nchw_launches : 0; }
+long plb_ctx_stem_launch_count(const plb_ctx* ctx) { return ctx ? ctx->stem_launches : 0; }
 long plb_ctx_dwpw_launch_count(const plb_ctx* ctx) { return ctx ? ctx->dwpw_launches : 0; }
 long plb_ctx_pair_launch_count(const plb_ctx* ctx) { return ctx ? ctx->pair_launches : 0; }
 size_t plb_ctx_workspace_size(const plb_ctx* ctx) { return ctx ? ctx->ws_bytes : 0; }
@@ -635,6 +637,18 @@ int plb_conv_run_image_f32(plb_conv* conv, const float* x, void* y, int batch) {
   plb_ctx* ctx = conv->ctx;
   const plb_conv_desc& d = conv->d;
   PLB_CUDA(cudaSetDevice(ctx->device));
+  if (conv->fold && d.out_dtype == PLB_OUT_I8 && conv->sw.stem != 0 && d.dil_w == 1) {
+    // calib, row folding and the convolution in one launch where the shape allows it (stem_tc.cu)
+    StemProblem sp;
+    memset(&sp, 0, sizeof(sp));
+    sp.x = x; sp.batch = batch; sp.cin = d.cin; sp.h = d.h; sp.w = d.w;
+    sp.kh = d.kh; sp.kw = d.kw; sp.stride_h = d.stride_h; sp.stride_w = d.stride_w; sp.pad_t = d.pad_top; sp.pad_l = d.pad_left;
+    sp.ho = conv->ho; sp.wo = conv->wo; sp.fold_h = conv->fold_h; sp.fold_kh = conv->fold_kh;
+    sp.wfold = conv->w.as<int8_t>(); sp.cout = d.cout; sp.in_scale = d.in_scale;
+    sp.epi = out_spec(conv, OUT_I8, y).epi;
+    sp.y = static_cast<int8_t*>(y);
+    if (stem_tc_supported(ctx, sp, nullptr)) return stem_tc_launch(ctx, sp);
+  }
   const size_t x_bytes = staged_input_bytes(conv, batch);
   int rc = ctx->reserve(x_bytes);
   if (rc) return rc;

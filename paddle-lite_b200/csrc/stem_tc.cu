@@ -1,0 +1,489 @@
+// First layer of a network (RGB stem: 7x7 or 3x3, stride 2, 3 input channels) in ONE launch, from the fp32 NCHW image
+// to the int8 channels-last output.  The reference runs calib (fp32 -> int8, lite/backends/x86/math/calib.cc:25-151)
+// and then im2col + GEMM (lite/kernels/x86/conv_compute.cc:292-341); here the calib, the im2col and the GEMM operand
+// never reach memory: producer warps quantise the image rows a work item needs into shared memory (pixels x channels
+// interleaved, zero padding in place), copy for every output pixel the 32-byte windows of the row-folded layout
+// ([filter row pair j][row e of the pair][kw taps x 3 channels, padded to 32 bytes]) into the swizzled K-major operand
+// tile, tcgen05.mma multiplies by the resident folded filter, and 16 epilogue warps requantise and store through TMA.
+// Same arithmetic as the staged path (fold_rows + implicit GEMM), bit for bit: exact int32 sums of the same products.
+//
+// A work item is R output rows of one image with R * wo a multiple of 128 (8 rows of 112 pixels = 7 tiles), so tiles are
+// runs of 128 consecutive output pixels; a CTA takes items blockIdx.x, blockIdx.x + gridDim.x, ...
+// Roles: warps 0-7 producers (quantise, then fill operand tiles), warps 8-23 epilogue (4 groups x 4 TMEM lane quadrants,
+// group g takes every 4th tile), warp 24 MMA issue (with three idle companions: registers are handed out to warps four
+// at a time).  All waits are bounded (tc::mbar_wait).
+#include "stem_tc.cuh"
+
+#include <algorithm>
+#include <mutex>
+
+#include "igemm_tc.cuh"
+#include "tc_device.cuh"
+
+namespace plb {
+namespace {
+
+using namespace tc;
+
+constexpr int kProdWarps = 8;
+constexpr int kProdThreads = 32 * kProdWarps;
+constexpr int kEpiWarps = 16;
+constexpr int kMmaWarp = kProdWarps + kEpiWarps;
+constexpr int kThreads = 32 * (kMmaWarp + 4);
+constexpr int kProdRegs = 64, kEpiRegs = 88, kMmaRegs = 24;  // of the 72 per thread the CTA starts with
+constexpr int kMaxStages = 8;
+constexpr int kMaxAccBufs = 8;
+constexpr int kCtrlBytes = 1024;
+constexpr int kStagingPerWarp = 2 * 2048;  // two buffers of 32 pixels x up to 64 channels
+
+struct StemArgs {
+  const float* x;
+  int cin, h, w, ho, wo;
+  int stride_h, stride_w, pad_t;
+  int rows_in;        // image rows a work item needs
+  int row_words;      // words per quantised row buffer
+  int px0_word;       // word of pixel 0 in a row buffer (the left padding lies in front of it)
+  int base_off;       // byte of output column 0's window in a row buffer
+  int nwin;           // 32-byte windows per output pixel = fold_kh * fold_h
+  int fold_h;
+  int rows_item;      // output rows per work item (R)
+  int tiles_item;     // R * wo / 128
+  int items_per_image, total_items;
+  int kchunks;        // K / 128
+  int stages, stage_bytes;
+  int cout, acc_cols, acc_bufs, b_bytes;
+  float inv_scale;
+  const float* scale;
+  const float* bias;
+  float alpha;
+  int acc_small;
+  int* status;
+};
+
+__device__ __forceinline__ void prod_barrier() { asm volatile("bar.sync 1, %0;" ::"n"(kProdThreads) : "memory"); }
+// Barrier of the producer warps that also tells every one of them whether ANY of them wants to stop: the decision to
+// leave the item loop has to be the same in all of them, or the next barrier would wait for threads that have left.
+__device__ __forceinline__ bool prod_barrier_any(bool flag) {
+  uint32_t any;
+  asm volatile(
+      "{\n\t"
+      ".reg .pred p, q;\n\t"
+      "setp.ne.u32 q, %1, 0;\n\t"
+      "bar.red.or.pred p, 1, %2, q;\n\t"
+      "selp.u32 %0, 1, 0, p;\n\t"
+      "}"
+      : "=r"(any)
+      : "r"(static_cast<uint32_t>(flag)), "n"(kProdThreads)
+      : "memory");
+  return any != 0;
+}
+__device__ __forceinline__ void sts32(uint32_t addr, uint32_t v) {
+  asm volatile("st.shared.b32 [%0], %1;" ::"r"(addr), "r"(v) : "memory");
+}
+__device__ __forceinline__ uint32_t lds32(uint32_t addr) {
+  uint32_t v;
+  asm volatile("ld.shared.b32 %0, [%1];" : "=r"(v) : "r"(addr));
+  return v;
+}
+__device__ __forceinline__ void bulk_wait_read_1() { asm volatile("cp.async.bulk.wait_group.read 1;" ::: "memory"); }
+
+// calib of the reference: sat(rne(max(x / scale, -127))); rounding by adding 1.5 * 2^23, result in the low byte
+__device__ __forceinline__ uint32_t calib_bits(float v, float inv) {
+  return __float_as_uint(fminf(fmaxf(v * inv, -127.f), 127.f) + 12582912.f);
+}
+
+template <int ACT>
+__global__ void __launch_bounds__(kThreads, 1)
+    stem_tc_kernel(const __grid_constant__ CUtensorMap tmB, const __grid_constant__ CUtensorMap tmOut, const StemArgs a) {
+  extern __shared__ uint8_t smem_raw[];
+  const uint32_t raw_addr = smem_u32(smem_raw);
+  uint8_t* smem_al = smem_raw + (((raw_addr + 1023u) & ~1023u) - raw_addr);
+  // [epilogue staging][resident filter][operand ring][quantised image rows][barriers]
+  uint8_t* b_smem = smem_al + kEpiWarps * kStagingPerWarp;
+  uint8_t* ring_smem = b_smem + a.b_bytes;
+  uint32_t* rowbuf = reinterpret_cast<uint32_t*>(ring_smem + a.stages * a.stage_bytes);
+  uint8_t* ctrl = reinterpret_cast<uint8_t*>(rowbuf + ((a.rows_in * a.row_words + 255) & ~255));
+  uint64_t* full_bar = reinterpret_cast<uint64_t*>(ctrl);
+  uint64_t* empty_bar = full_bar + kMaxStages;
+  uint64_t* acc_full = empty_bar + kMaxStages;
+  uint64_t* acc_empty = acc_full + kMaxAccBufs;
+  uint64_t* b_bar = acc_empty + kMaxAccBufs;
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(b_bar + 1);
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
+
+  const int warp = threadIdx.x >> 5;
+  const int lane = threadIdx.x & 31;
+  const uint32_t tmem_cols = static_cast<uint32_t>(a.acc_cols * a.acc_bufs);
+  const int nb = (a.total_items - static_cast<int>(blockIdx.x) + static_cast<int>(gridDim.x) - 1) / static_cast<int>(gridDim.x);
+  const int total_tiles = nb * a.tiles_item;
+
+  if (warp == kMmaWarp) {
+    for (int i = lane; i < 2 * kMaxStages + 2 * kMaxAccBufs + 1; i += 32) {
+      uint32_t count = 1;
+      if (i < kMaxStages) count = kProdWarps;                                                           // full: one arrival per producer warp
+      else if (i >= 2 * kMaxStages + kMaxAccBufs && i < 2 * kMaxStages + 2 * kMaxAccBufs) count = 4;  // drained by one epilogue group
+      mbar_init(smem_u32(&full_bar[i]), count);
+    }
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    if (lane == 0) *abort_flag = 0;
+    if (lane < 2)
+      asm volatile("prefetch.tensormap [%0];" ::"l"(reinterpret_cast<uint64_t>(lane == 0 ? &tmB : &tmOut)) : "memory");
+    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(tmem_slot)), "r"(tmem_cols)
+                 : "memory");
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+  }
+  if (warp < kProdWarps) {
+    // the padding bytes of the row buffers stay zero for the whole kernel; image bytes are rewritten per item
+    for (int i = threadIdx.x; i < a.rows_in * a.row_words; i += kProdThreads) rowbuf[i] = 0;
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = *tmem_slot;
+  pdl_sync_with_previous_kernel();
+
+  if (warp < kProdWarps) {
+    // ---------------------------------------------------------------------------------------------- producers
+    asm volatile("setmaxnreg.dec.sync.aligned.u32 %0;" ::"n"(kProdRegs));
+    const int tid = threadIdx.x;
+    const int w4 = a.w >> 2;
+    const long plane = static_cast<long>(a.h) * a.w;
+    const uint32_t rb0 = smem_u32(rowbuf);
+    const uint32_t ring = smem_u32(ring_smem);
+    const int upt = 128 * a.nwin / kProdThreads;   // windows per thread and tile (2 or 4)
+    const int pstep = kProdThreads / a.nwin;       // pixels between a thread's consecutive windows
+    const int wv = tid % a.nwin;                   // this thread's window: filter row pair j, row e of the pair
+    const int wj = wv / a.fold_h, we = wv - wj * a.fold_h;
+    const int kch = wv >> 2, sub = wv & 3;
+    bool ok = true;
+    int qseq = 0;
+    for (int k = 0; k < nb; ++k) {
+      const int item = static_cast<int>(blockIdx.x) + k * static_cast<int>(gridDim.x);
+      const int n = item / a.items_per_image;
+      const int p0 = (item - n * a.items_per_image) * a.rows_item;
+      const int ih0 = p0 * a.stride_h - a.pad_t;
+      const float* img = a.x + static_cast<long>(n) * a.cin * plane;
+      // 1. calib: image rows -> [pixel][channel] bytes.  A thread takes 4 pixels of the three channels = 3 words.
+      for (int r = warp; r < a.rows_in; r += kProdWarps) {
+        const int ih = ih0 + r;
+        const bool inside = ih >= 0 && ih < a.h;
+        const uint32_t dst_row = rb0 + static_cast<uint32_t>((r * a.row_words + a.px0_word) * 4);
+        for (int t = lane; t < w4; t += 32) {
+          uint32_t w0 = 0, w1 = 0, w2 = 0;
+          if (inside) {
+            const float4* src = reinterpret_cast<const float4*>(img + static_cast<long>(ih) * a.w) + t;
+            const float4 c0 = __ldg(src), c1 = __ldg(src + (plane >> 2)), c2 = __ldg(src + 2 * (plane >> 2));
+            const uint32_t q00 = calib_bits(c0.x, a.inv_scale), q01 = calib_bits(c1.x, a.inv_scale), q02 = calib_bits(c2.x, a.inv_scale);
+            const uint32_t q10 = calib_bits(c0.y, a.inv_scale), q11 = calib_bits(c1.y, a.inv_scale), q12 = calib_bits(c2.y, a.inv_scale);
+            const uint32_t q20 = calib_bits(c0.z, a.inv_scale), q21 = calib_bits(c1.z, a.inv_scale), q22 = calib_bits(c2.z, a.inv_scale);
+            const uint32_t q30 = calib_bits(c0.w, a.inv_scale), q31 = calib_bits(c1.w, a.inv_scale), q32 = calib_bits(c2.w, a.inv_scale);
+            w0 = pack_low_bytes(q00, q01, q02, q10);
+            w1 = pack_low_bytes(q11, q12, q20, q21);
+            w2 = pack_low_bytes(q22, q30, q31, q32);
+          }
+          const uint32_t d = dst_row + static_cast<uint32_t>(t * 12);
+          sts32(d, w0);
+          sts32(d + 4, w1);
+          sts32(d + 8, w2);
+        }
+      }
+      prod_barrier();
+      // 2. operand tiles: for every output pixel the nwin windows of 32 bytes, word-unaligned in the row buffers
+      int py = 0, q = tid / a.nwin;  // output row (inside the item) and column of this thread's next window
+      while (q >= a.wo) {
+        q -= a.wo;
+        ++py;
+      }
+      for (int t = 0; t < a.tiles_item && ok; ++t, ++qseq) {
+        const int stage = qseq % a.stages, use = qseq / a.stages;
+        ok = mbar_wait(smem_u32(&empty_bar[stage]), (use & 1) ^ 1, abort_flag, a.status, FAULT_WAIT_EMPTY);
+        if (!ok) break;
+        const uint32_t tile = ring + static_cast<uint32_t>(stage * a.stage_bytes + kch * (128 * 128));
+        int m = tid / a.nwin;
+        for (int i = 0; i < upt; ++i) {
+          const int rb = (py + wj) * a.fold_h + we;
+          const int src = a.base_off + q * a.stride_w * 3;
+          const uint32_t s = rb0 + static_cast<uint32_t>((rb * a.row_words + (src >> 2)) * 4);
+          const uint32_t sh = static_cast<uint32_t>(src & 3) * 8;
+          uint32_t v[9], o[8];
+#pragma unroll
+          for (int j = 0; j < 9; ++j) v[j] = lds32(s + 4 * j);
+#pragma unroll
+          for (int j = 0; j < 8; ++j) o[j] = __funnelshift_r(v[j], v[j + 1], sh);
+          const uint32_t row = tile + static_cast<uint32_t>(m * 128);
+          const int sw = m & 7;
+          sts128(row + (((sub * 2) ^ sw) << 4), o[0], o[1], o[2], o[3]);
+          sts128(row + (((sub * 2 + 1) ^ sw) << 4), o[4], o[5], o[6], o[7]);
+          m += pstep;
+          q += pstep;
+          while (q >= a.wo) {
+            q -= a.wo;
+            ++py;
+          }
+        }
+        fence_proxy_async_smem();
+        __syncwarp();
+        if (lane == 0) mbar_arrive(smem_u32(&full_bar[stage]));
+      }
+      // the next item's calib overwrites the rows these windows were read from; and all producers stop together
+      if (prod_barrier_any(!ok || *abort_flag != 0)) break;
+    }
+  } else if (warp >= kMmaWarp) {
+    asm volatile("setmaxnreg.dec.sync.aligned.u32 %0;" ::"n"(kMmaRegs));
+    if (warp == kMmaWarp) {
+      // -------------------------------------------------------------------------------------------- MMA issue
+      const bool leader = elect_one();
+      mbar_expect_tx_if(smem_u32(b_bar), static_cast<uint32_t>(a.b_bytes), leader);
+      for (int kc = 0; kc < a.kchunks; ++kc)
+        tma_load_2d_if(smem_u32(b_smem) + static_cast<uint32_t>(kc * a.cout * 128), &tmB, smem_u32(b_bar), kc * 128, 0, leader);
+      bool ok = mbar_wait(smem_u32(b_bar), 0, abort_flag, a.status, FAULT_WAIT_FULL);
+      const uint32_t hi = static_cast<uint32_t>(make_smem_desc(0, 128) >> 32);
+      const uint32_t ring_lo = ((smem_u32(ring_smem) >> 4) & 0x3FFFu) | (1u << 16);
+      const uint32_t b_lo0 = ((smem_u32(b_smem) >> 4) & 0x3FFFu) | (1u << 16);
+      // D = s32, A = B = s8, both K-major, M = 128, N = cout
+      const uint32_t idesc = (2u << 4) | (1u << 7) | (1u << 10) | (static_cast<uint32_t>(a.cout >> 3) << 17) |
+                             (static_cast<uint32_t>(128 >> 4) << 24);
+      int stage = 0, buf = 0;
+      uint32_t full_parity = 0, acc_parity = 1;
+      for (int q = 0; q < total_tiles && ok; ++q) {
+        ok = mbar_wait(smem_u32(&acc_empty[buf]), acc_parity, abort_flag, a.status, FAULT_WAIT_ACCUM);
+        if (!ok) break;
+        ok = mbar_wait(smem_u32(&full_bar[stage]), full_parity, abort_flag, a.status, FAULT_WAIT_FULL);
+        if (!ok) break;
+        tc_fence_after();
+        const uint32_t a_lo = ring_lo + static_cast<uint32_t>((stage * a.stage_bytes) >> 4);
+        const uint32_t d_tmem = tmem_base + static_cast<uint32_t>(buf * a.acc_cols);
+        for (int kc = 0; kc < a.kchunks; ++kc) {
+          const uint32_t a_k = a_lo + static_cast<uint32_t>((kc * 128 * 128) >> 4);
+          const uint32_t b_k = b_lo0 + static_cast<uint32_t>((kc * a.cout * 128) >> 4);
+#pragma unroll
+          for (int j = 0; j < 4; ++j) tc_mma_i8_halves(d_tmem, a_k + 2u * j, hi, b_k + 2u * j, hi, idesc, (kc | j) ? 1u : 0u, leader);
+        }
+        tc_commit_if(smem_u32(&empty_bar[stage]), leader);
+        tc_commit_if(smem_u32(&acc_full[buf]), leader);
+        if (++stage == a.stages) {
+          stage = 0;
+          full_parity ^= 1;
+        }
+        if (++buf == a.acc_bufs) {
+          buf = 0;
+          acc_parity ^= 1;
+        }
+      }
+      if (!ok || *abort_flag) mbar_wait_drain(smem_u32(b_bar), 0);
+    }
+  } else {
+    // ---------------------------------------------------------------------------------------------- epilogue
+    asm volatile("setmaxnreg.inc.sync.aligned.u32 %0;" ::"n"(kEpiRegs));
+    const int e = warp - kProdWarps;
+    const int quad = e & 3, group = e >> 2;
+    const int wq = a.cout;  // bytes of a staged pixel row (32 or 64)
+    const uint32_t st0 = smem_u32(smem_al) + static_cast<uint32_t>(e * kStagingPerWarp);
+    const int b_swz = wq == 64 ? ((lane >> 1) & 3) : ((lane >> 2) & 1);
+    const float ub = quant_upper_bound<ACT>(a.alpha);
+    int sbuf = 0;
+    bool ok = true;
+    for (int q = group; q < total_tiles && ok; q += 4) {
+      const int buf = q % a.acc_bufs;
+      const uint32_t parity = static_cast<uint32_t>(q / a.acc_bufs) & 1u;
+      const int k = q / a.tiles_item, t = q - k * a.tiles_item;
+      const int item = static_cast<int>(blockIdx.x) + k * static_cast<int>(gridDim.x);
+      const int n = item / a.items_per_image;
+      const int p0 = (item - n * a.items_per_image) * a.rows_item;
+      const int row0 = (n * a.ho + p0) * a.wo + t * 128 + quad * 32;
+      ok = mbar_wait(smem_u32(&acc_full[buf]), parity, abort_flag, a.status, FAULT_WAIT_ACCUM);
+      if (!ok) break;
+      tc_fence_after();
+      const uint32_t lane_addr = tmem_base + static_cast<uint32_t>(buf * a.acc_cols) + (static_cast<uint32_t>(quad * 32) << 16);
+      const uint32_t st = st0 + static_cast<uint32_t>(sbuf * 2048);
+      if (lane == 0) bulk_wait_read_1();  // the store issued two tiles ago has finished reading this buffer
+      __syncwarp();
+      const uint32_t row = st + static_cast<uint32_t>(lane * wq);
+      for (int c = 0; c < a.cout; c += 32) {
+        uint32_t r[32];
+        tc_ld32(lane_addr + static_cast<uint32_t>(c), r);
+        tc_wait_ld();
+        const float4* sc4 = reinterpret_cast<const float4*>(a.scale + c);
+        const float4* bi4 = reinterpret_cast<const float4*>(a.bias + c);
+        const int chunk0 = c >> 4;
+#pragma unroll
+        for (int h = 0; h < 2; ++h) {
+          uint32_t v[4];
+          if (a.acc_small) {
+#pragma unroll
+            for (int j = 0; j < 4; ++j)
+              v[j] = quant4<ACT, true>(&r[16 * h + 4 * j], __ldg(sc4 + 4 * h + j), __ldg(bi4 + 4 * h + j), a.alpha, ub);
+          } else {
+#pragma unroll
+            for (int j = 0; j < 4; ++j)
+              v[j] = quant4<ACT, false>(&r[16 * h + 4 * j], __ldg(sc4 + 4 * h + j), __ldg(bi4 + 4 * h + j), a.alpha, ub);
+          }
+          sts128(row + (((chunk0 + h) ^ b_swz) << 4), v[0], v[1], v[2], v[3]);
+        }
+      }
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(smem_u32(&acc_empty[buf]));  // the accumulator is free before the store is issued
+      fence_proxy_async_smem();
+      __syncwarp();
+      if (lane == 0) {
+        tma_store_2d(&tmOut, st, 0, row0);
+        bulk_commit();
+      }
+      sbuf ^= 1;
+    }
+    if (lane == 0) bulk_wait_all();
+  }
+  tc_fence_before();
+  __syncthreads();
+  if (warp == kMmaWarp) {
+    __syncwarp();
+    tc_fence_after();
+    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(tmem_cols) : "memory");
+  }
+}
+
+typedef void (*StemKernel)(const CUtensorMap, const CUtensorMap, const StemArgs);
+StemKernel pick_kernel(int act) {
+  switch (act) {
+    case PLB_ACT_RELU: return stem_tc_kernel<PLB_ACT_RELU>;
+    case PLB_ACT_RELU6: return stem_tc_kernel<PLB_ACT_RELU6>;
+    case PLB_ACT_LEAKY: return stem_tc_kernel<PLB_ACT_LEAKY>;
+    default: return stem_tc_kernel<PLB_ACT_NONE>;
+  }
+}
+
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                                  const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
+                                  CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+EncodeTiledFn g_tiled = nullptr;
+std::mutex g_mutex;
+
+int load_encoder() {
+  std::lock_guard<std::mutex> lock(g_mutex);
+  if (g_tiled) return PLB_OK;
+  void* fn = nullptr;
+  cudaDriverEntryPointQueryResult qres;
+  cudaError_t e = cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &fn, cudaEnableDefault, &qres);
+  if (e != cudaSuccess || qres != cudaDriverEntryPointSuccess || !fn) return fail(PLB_E_CUDA, "cuTensorMapEncodeTiled unavailable");
+  g_tiled = reinterpret_cast<EncodeTiledFn>(fn);
+  return PLB_OK;
+}
+
+struct StemPlan {
+  int rows_item, tiles_item, rows_in, row_words, px0_word, base_off, nwin, k_bytes, stages;
+  size_t smem;
+};
+
+bool plan(const StemProblem& p, StemPlan* s, std::string* why) {
+  auto no = [&](const char* m) {
+    if (why) *why = m;
+    return false;
+  };
+  if (p.cin != 3) return no("3 input channels only");
+  if (p.w % 4 != 0 || (reinterpret_cast<uintptr_t>(p.x) & 15)) return no("image rows must be 16-byte aligned");
+  if (p.cout != 32 && p.cout != 64) return no("32 or 64 output channels only");
+  if (p.kw * p.cin > 32 || p.fold_h != p.stride_h || p.fold_h < 1) return no("filter row does not fit a 32-byte window");
+  s->nwin = p.fold_kh * p.fold_h;
+  if (s->nwin != 4 && s->nwin != 8) return no("4 or 8 windows per pixel only");
+  s->k_bytes = s->nwin * 32;
+  // output rows per item: the fewest whose pixels fill whole 128-pixel tiles
+  int g = 128, b = p.wo;
+  while (b) {
+    const int t = g % b;
+    g = b;
+    b = t;
+  }
+  s->rows_item = 128 / g;
+  if (s->rows_item > 16 || p.ho % s->rows_item != 0) return no("output rows do not group into whole 128-pixel tiles");
+  s->tiles_item = s->rows_item * p.wo / 128;
+  if (kProdThreads / s->nwin > p.wo) return no("image too narrow");
+  s->rows_in = (s->rows_item - 1) * p.stride_h + s->nwin;
+  const int pad_bytes = p.pad_l * p.cin;
+  s->px0_word = (pad_bytes + 3) / 4;
+  s->base_off = s->px0_word * 4 - pad_bytes;
+  // bytes a row buffer must hold: the last window read (9 words from its first word) and the image itself
+  const int last_src = s->base_off + (p.wo - 1) * p.stride_w * p.cin;
+  const int need_words = std::max((last_src >> 2) + 9, s->px0_word + (p.w * p.cin + 3) / 4);
+  s->row_words = need_words | 1;  // odd pitch: rows of one column fall into different banks
+  if ((reinterpret_cast<uintptr_t>(p.wfold) & 15) || (reinterpret_cast<uintptr_t>(p.y) & 15)) return no("filter / output alignment");
+  const size_t rowbuf_bytes = static_cast<size_t>((s->rows_in * s->row_words + 255) & ~255) * 4;
+  const size_t fixed = static_cast<size_t>(kEpiWarps) * kStagingPerWarp + static_cast<size_t>(p.cout) * s->k_bytes + rowbuf_bytes + kCtrlBytes + 1024;
+  const size_t stage_bytes = 128 * static_cast<size_t>(s->k_bytes);
+  if (fixed + 2 * stage_bytes > 227 * 1024) return no("does not fit shared memory");
+  s->stages = static_cast<int>(std::min<size_t>(kMaxStages, (227 * 1024 - fixed) / stage_bytes));
+  s->smem = fixed + s->stages * stage_bytes;
+  return true;
+}
+
+}  // namespace
+
+bool stem_tc_supported(const plb_ctx* ctx, const StemProblem& p, std::string* why) {
+  (void)ctx;
+  StemPlan s;
+  return plan(p, &s, why);
+}
+
+int stem_tc_launch(plb_ctx* ctx, const StemProblem& p) {
+  StemPlan s;
+  std::string why;
+  if (!plan(p, &s, &why)) return fail(PLB_E_UNSUPPORTED, "one-launch stem: %s", why.c_str());
+  int rc = load_encoder();
+  if (rc) return rc;
+  StemArgs a;
+  memset(&a, 0, sizeof(a));
+  a.x = p.x; a.cin = p.cin; a.h = p.h; a.w = p.w; a.ho = p.ho; a.wo = p.wo;
+  a.stride_h = p.stride_h; a.stride_w = p.stride_w; a.pad_t = p.pad_t;
+  a.rows_in = s.rows_in; a.row_words = s.row_words; a.px0_word = s.px0_word; a.base_off = s.base_off;
+  a.nwin = s.nwin; a.fold_h = p.fold_h;
+  a.rows_item = s.rows_item; a.tiles_item = s.tiles_item;
+  a.items_per_image = p.ho / s.rows_item;
+  const long items = static_cast<long>(p.batch) * a.items_per_image;
+  if (items > 0x3fffffff || static_cast<long>(p.batch) * p.ho * p.wo > 0x7fffffffL) return fail(PLB_E_UNSUPPORTED, "batch too large");
+  a.total_items = static_cast<int>(items);
+  a.kchunks = s.k_bytes / 128;
+  a.stages = s.stages;
+  a.stage_bytes = 128 * s.k_bytes;
+  a.cout = p.cout;
+  a.acc_cols = p.cout;
+  a.acc_bufs = std::min(kMaxAccBufs, 512 / a.acc_cols);
+  a.b_bytes = p.cout * s.k_bytes;
+  a.inv_scale = 1.f / p.in_scale;
+  a.scale = p.epi.scale; a.bias = p.epi.bias; a.alpha = p.epi.alpha; a.acc_small = p.epi.acc_small;
+  a.status = ctx->d_status;
+
+  CUtensorMap tmB, tmOut;
+  {
+    const cuuint64_t dims[2] = {static_cast<cuuint64_t>(s.k_bytes), static_cast<cuuint64_t>(p.cout)};
+    const cuuint64_t strides[1] = {static_cast<cuuint64_t>(s.k_bytes)};
+    const cuuint32_t box[2] = {128, static_cast<cuuint32_t>(p.cout)};
+    const cuuint32_t es[2] = {1, 1};
+    CUresult r = g_tiled(&tmB, CU_TENSOR_MAP_DATA_TYPE_UINT8, 2, const_cast<int8_t*>(p.wfold), dims, strides, box, es,
+                         CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                         CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    if (r != CUDA_SUCCESS) return fail(PLB_E_CUDA, "tensor map of the folded filter: error %d", static_cast<int>(r));
+  }
+  {
+    const cuuint64_t dims[2] = {static_cast<cuuint64_t>(p.cout), static_cast<cuuint64_t>(p.batch) * p.ho * p.wo};
+    const cuuint64_t strides[1] = {static_cast<cuuint64_t>(p.cout)};
+    const cuuint32_t box[2] = {static_cast<cuuint32_t>(p.cout), 32};
+    const cuuint32_t es[2] = {1, 1};
+    CUresult r = g_tiled(&tmOut, CU_TENSOR_MAP_DATA_TYPE_UINT8, 2, p.y, dims, strides, box, es, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                         p.cout == 64 ? CU_TENSOR_MAP_SWIZZLE_64B : CU_TENSOR_MAP_SWIZZLE_32B, CU_TENSOR_MAP_L2_PROMOTION_NONE,
+                         CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    if (r != CUDA_SUCCESS) return fail(PLB_E_CUDA, "tensor map of the output: error %d", static_cast<int>(r));
+  }
+  StemKernel kernel = pick_kernel(p.epi.act);
+  {
+    static std::mutex attr_mutex;
+    std::lock_guard<std::mutex> lock(attr_mutex);
+    PLB_CUDA(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024));
+  }
+  const int grid = static_cast<int>(std::min<long>(items, ctx->sm_count));
+  PLB_CUDA(launch_kernel(kernel, dim3(grid), dim3(kThreads), s.smem, ctx->stream, tmB, tmOut, a));
+  ++ctx->launches;
+  ++ctx->stem_launches;
+  return PLB_OK;
+}
+
+}  // namespace plb

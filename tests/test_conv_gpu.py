@@ -405,6 +405,42 @@ def test_image_entry(plb, ctx, cin, k, s, p, hw):
     assert np.array_equal(got_nchw, q_ref)
 
 
+@pytest.mark.parametrize("k,s,p,cout,hw,n,act,alpha", [
+    (7, 2, 3, 64, (224, 224), 3, 1, 0.0),    # the ResNet-50 stem
+    (3, 2, 1, 32, (224, 224), 5, 1, 0.0),    # the MobileNetV1 stem
+    (7, 2, 3, 64, (128, 256), 2, 2, 6.0),    # one output row = one tile
+    (7, 2, 3, 32, (96, 64), 4, 0, 0.0),      # four output rows per item, 32-pixel rows
+    (3, 2, 1, 64, (160, 224), 150, 3, 0.1),  # more work items than SMs: several items per CTA, ragged last round
+])
+def test_one_launch_stem(plb, ctx, k, s, p, cout, hw, n, act, alpha, monkeypatch):
+    """First layer from the fp32 image in one launch (calib, row folding and GEMM operand never reach memory):
+    bit-identical to the oracle and to the staged path it replaces."""
+    rng = np.random.default_rng(k * 100 + cout + hw[0])
+    img = rng.standard_normal((n, 3) + hw).astype(np.float32)
+    img[0, :, :3, :5] *= 40.0  # values far outside the quantiser's range saturate
+    in_s = float(np.abs(img[1:]).max() / 127) if n > 1 else 0.03
+    wq, ws = O.quantize_per_channel((rng.standard_normal((cout, 3, k, k)) * 0.1).astype(np.float32))
+    bias = (rng.standard_normal(cout) * 0.1).astype(np.float32)
+    kw = dict(stride=(s, s), pads=(p, p, p, p))
+    small = slice(0, min(n, 3))
+    xq = O.calib_f32_to_i8(img[small], in_s)
+    y_ref = O.conv_int8(xq, wq, ws, in_s, bias, act, alpha, **kw)
+    out_s = float(np.abs(y_ref).max() / 127)
+    q_ref = O.conv_int8(xq, wq, ws, in_s, bias, act, alpha, out_scale=out_s, leaky_compat=True, **kw)
+    conv = plb.Conv(ctx, wq, ws, in_s, bias, in_hw=hw, act=act, alpha=alpha, out_scale=out_s, leaky_compat=True, **kw)
+    before = ctx.stem_launch_count()
+    got = conv.run_image_f32(dev(img))
+    ctx.sync()
+    assert ctx.stem_launch_count() == before + 1
+    assert np.array_equal(got[small].cpu().numpy().transpose(0, 3, 1, 2), q_ref)
+    monkeypatch.setenv("PLB_STEM", "0")
+    staged = plb.Conv(ctx, wq, ws, in_s, bias, in_hw=hw, act=act, alpha=alpha, out_scale=out_s, leaky_compat=True, **kw)
+    want = staged.run_image_f32(dev(img))
+    ctx.sync()
+    assert ctx.stem_launch_count() == before + 1
+    assert torch.equal(got, want)
+
+
 def test_linearity_at_full_size(plb, ctx):
     """Size-independent property at benchmark scale (batch 32 of the 64->64 3x3 layer):
     accumulators are linear in the input, acc(x1) + acc(x2) == acc(x1 + x2) for inputs whose sum
