@@ -9,9 +9,10 @@
 //
 // A work item is R output rows of one image with R * wo a multiple of 128 (8 rows of 112 pixels = 7 tiles), so tiles are
 // runs of 128 consecutive output pixels; a CTA takes items blockIdx.x, blockIdx.x + gridDim.x, ...
-// Roles: warps 0-7 producers (quantise, then fill operand tiles), warps 8-23 epilogue (4 groups x 4 TMEM lane quadrants,
-// group g takes every 4th tile), warp 24 MMA issue (with three idle companions: registers are handed out to warps four
-// at a time).  All waits are bounded (tc::mbar_wait).
+// Roles: warps 0-7 calib team (image rows -> one of two quantised row buffers, one item ahead), warps 8-15 tile team
+// (row buffer -> operand tiles), warps 16-27 epilogue (3 groups x 4 TMEM lane quadrants, group g takes every 3rd tile),
+// warp 28 MMA issue (with three idle companions: registers are handed out to warps four at a time).  The teams hand
+// row buffers to each other through mbarriers; all waits are bounded (tc::mbar_wait).
 #include "stem_tc.cuh"
 
 #include <algorithm>
@@ -25,12 +26,15 @@ namespace {
 
 using namespace tc;
 
-constexpr int kProdWarps = 8;
-constexpr int kProdThreads = 32 * kProdWarps;
-constexpr int kEpiWarps = 16;
+constexpr int kCalibWarps = 8;                  // fp32 image rows -> quantised row buffers
+constexpr int kTileWarps = 8;                   // row buffers -> operand tiles
+constexpr int kTileThreads = 32 * kTileWarps;
+constexpr int kProdWarps = kCalibWarps + kTileWarps;
+constexpr int kEpiGroups = 3;
+constexpr int kEpiWarps = 4 * kEpiGroups;
 constexpr int kMmaWarp = kProdWarps + kEpiWarps;
 constexpr int kThreads = 32 * (kMmaWarp + 4);
-constexpr int kProdRegs = 64, kEpiRegs = 88, kMmaRegs = 24;  // of the 72 per thread the CTA starts with
+constexpr int kCalibRegs = 48, kEpiRegs = 88, kMmaRegs = 24;  // of the 64 per thread the CTA starts with (tile warps keep 64)
 constexpr int kMaxStages = 8;
 constexpr int kMaxAccBufs = 8;
 constexpr int kCtrlBytes = 1024;
@@ -60,23 +64,6 @@ struct StemArgs {
   int* status;
 };
 
-__device__ __forceinline__ void prod_barrier() { asm volatile("bar.sync 1, %0;" ::"n"(kProdThreads) : "memory"); }
-// Barrier of the producer warps that also tells every one of them whether ANY of them wants to stop: the decision to
-// leave the item loop has to be the same in all of them, or the next barrier would wait for threads that have left.
-__device__ __forceinline__ bool prod_barrier_any(bool flag) {
-  uint32_t any;
-  asm volatile(
-      "{\n\t"
-      ".reg .pred p, q;\n\t"
-      "setp.ne.u32 q, %1, 0;\n\t"
-      "bar.red.or.pred p, 1, %2, q;\n\t"
-      "selp.u32 %0, 1, 0, p;\n\t"
-      "}"
-      : "=r"(any)
-      : "r"(static_cast<uint32_t>(flag)), "n"(kProdThreads)
-      : "memory");
-  return any != 0;
-}
 __device__ __forceinline__ void sts32(uint32_t addr, uint32_t v) {
   asm volatile("st.shared.b32 [%0], %1;" ::"r"(addr), "r"(v) : "memory");
 }
@@ -92,7 +79,7 @@ __device__ __forceinline__ uint32_t calib_bits(float v, float inv) {
   return __float_as_uint(fminf(fmaxf(v * inv, -127.f), 127.f) + 12582912.f);
 }
 
-template <int ACT>
+template <int ACT, int NWIN>
 __global__ void __launch_bounds__(kThreads, 1)
     stem_tc_kernel(const __grid_constant__ CUtensorMap tmB, const __grid_constant__ CUtensorMap tmOut, const StemArgs a) {
   extern __shared__ uint8_t smem_raw[];
@@ -102,13 +89,16 @@ __global__ void __launch_bounds__(kThreads, 1)
   uint8_t* b_smem = smem_al + kEpiWarps * kStagingPerWarp;
   uint8_t* ring_smem = b_smem + a.b_bytes;
   uint32_t* rowbuf = reinterpret_cast<uint32_t*>(ring_smem + a.stages * a.stage_bytes);
-  uint8_t* ctrl = reinterpret_cast<uint8_t*>(rowbuf + ((a.rows_in * a.row_words + 255) & ~255));
+  const int rowbuf_words = (a.rows_in * a.row_words + 255) & ~255;  // per buffer; there are two
+  uint8_t* ctrl = reinterpret_cast<uint8_t*>(rowbuf + 2 * rowbuf_words);
   uint64_t* full_bar = reinterpret_cast<uint64_t*>(ctrl);
   uint64_t* empty_bar = full_bar + kMaxStages;
   uint64_t* acc_full = empty_bar + kMaxStages;
   uint64_t* acc_empty = acc_full + kMaxAccBufs;
   uint64_t* b_bar = acc_empty + kMaxAccBufs;
-  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(b_bar + 1);
+  uint64_t* rows_full = b_bar + 1;   // [2] a row buffer holds the quantised rows of an item
+  uint64_t* rows_empty = rows_full + 2;  // [2] its tiles are built
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(rows_empty + 2);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
 
   const int warp = threadIdx.x >> 5;
@@ -118,9 +108,10 @@ __global__ void __launch_bounds__(kThreads, 1)
   const int total_tiles = nb * a.tiles_item;
 
   if (warp == kMmaWarp) {
-    for (int i = lane; i < 2 * kMaxStages + 2 * kMaxAccBufs + 1; i += 32) {
+    for (int i = lane; i < 2 * kMaxStages + 2 * kMaxAccBufs + 5; i += 32) {
       uint32_t count = 1;
-      if (i < kMaxStages) count = kProdWarps;                                                           // full: one arrival per producer warp
+      if (i < kMaxStages) count = kTileWarps;                                                           // full: one arrival per tile warp
+      else if (i > 2 * kMaxStages + 2 * kMaxAccBufs) count = i <= 2 * kMaxStages + 2 * kMaxAccBufs + 2 ? kCalibWarps : kTileWarps;
       else if (i >= 2 * kMaxStages + kMaxAccBufs && i < 2 * kMaxStages + 2 * kMaxAccBufs) count = 4;  // drained by one epilogue group
       mbar_init(smem_u32(&full_bar[i]), count);
     }
@@ -134,7 +125,7 @@ __global__ void __launch_bounds__(kThreads, 1)
   }
   if (warp < kProdWarps) {
     // the padding bytes of the row buffers stay zero for the whole kernel; image bytes are rewritten per item
-    for (int i = threadIdx.x; i < a.rows_in * a.row_words; i += kProdThreads) rowbuf[i] = 0;
+    for (int i = threadIdx.x; i < 2 * rowbuf_words; i += 32 * kProdWarps) rowbuf[i] = 0;
   }
   tc_fence_before();
   __syncthreads();
@@ -142,54 +133,76 @@ __global__ void __launch_bounds__(kThreads, 1)
   const uint32_t tmem_base = *tmem_slot;
   pdl_sync_with_previous_kernel();
 
-  if (warp < kProdWarps) {
-    // ---------------------------------------------------------------------------------------------- producers
-    asm volatile("setmaxnreg.dec.sync.aligned.u32 %0;" ::"n"(kProdRegs));
+  if (warp < kCalibWarps) {
+    // ---------------------------------------------------------------------------------------------- calib team
+    // fp32 image rows of item k -> [pixel][channel] bytes in row buffer k & 1, one item ahead of the tile team.
+    asm volatile("setmaxnreg.dec.sync.aligned.u32 %0;" ::"n"(kCalibRegs));
     const int tid = threadIdx.x;
     const int w4 = a.w >> 2;
     const long plane = static_cast<long>(a.h) * a.w;
-    const uint32_t rb0 = smem_u32(rowbuf);
+    const int total_units = a.rows_in * w4;
+    const float inv = a.inv_scale;
+    for (int k = 0; k < nb; ++k) {
+      const int item = static_cast<int>(blockIdx.x) + k * static_cast<int>(gridDim.x);
+      const int n = item / a.items_per_image;
+      const int ih0 = (item - n * a.items_per_image) * a.rows_item * a.stride_h - a.pad_t;
+      const float* img = a.x + static_cast<long>(n) * a.cin * plane;
+      const int b = k & 1;
+      if (!mbar_wait(smem_u32(&rows_empty[b]), ((k >> 1) & 1) ^ 1, abort_flag, a.status, FAULT_WAIT_EMPTY)) break;
+      const uint32_t rb0 = smem_u32(rowbuf + b * rowbuf_words);
+      // a unit is 4 pixels of the three channels = 3 words; a thread takes units tid, tid + 256, ...
+      for (int u = tid; u < total_units; u += 32 * kCalibWarps) {
+        const int r = u / w4, t = u - r * w4;
+        const int ih = ih0 + r;
+        uint32_t w0 = 0, w1 = 0, w2 = 0;
+        if (ih >= 0 && ih < a.h) {
+          const float4* src = reinterpret_cast<const float4*>(img + static_cast<long>(ih) * a.w) + t;
+          const float4 c0 = __ldg(src), c1 = __ldg(src + (plane >> 2)), c2 = __ldg(src + 2 * (plane >> 2));
+          w0 = pack_low_bytes(calib_bits(c0.x, inv), calib_bits(c1.x, inv), calib_bits(c2.x, inv), calib_bits(c0.y, inv));
+          w1 = pack_low_bytes(calib_bits(c1.y, inv), calib_bits(c2.y, inv), calib_bits(c0.z, inv), calib_bits(c1.z, inv));
+          w2 = pack_low_bytes(calib_bits(c2.z, inv), calib_bits(c0.w, inv), calib_bits(c1.w, inv), calib_bits(c2.w, inv));
+        }
+        const uint32_t d = rb0 + static_cast<uint32_t>((r * a.row_words + a.px0_word) * 4 + t * 12);
+        sts32(d, w0);
+        sts32(d + 4, w1);
+        sts32(d + 8, w2);
+      }
+      __syncwarp();
+      if (lane == 0) mbar_arrive(smem_u32(&rows_full[b]));
+      // the rows of the item after the next one: into L2 while this team waits for a free buffer
+      if (k + 2 < nb) {
+        const int item2 = item + 2 * static_cast<int>(gridDim.x);
+        const int n2 = item2 / a.items_per_image;
+        const int ih02 = (item2 - n2 * a.items_per_image) * a.rows_item * a.stride_h - a.pad_t;
+        const float* img2 = a.x + static_cast<long>(n2) * a.cin * plane;
+        const int lpr = (a.w + 31) >> 5;  // 128-byte lines per image row
+        for (int l = tid; l < a.rows_in * 3 * lpr; l += 32 * kCalibWarps) {
+          const int rc = l / lpr, off = l - rc * lpr;
+          const int r = rc / 3, ch = rc - r * 3;
+          const int ih = ih02 + r;
+          if (ih >= 0 && ih < a.h)
+            asm volatile("prefetch.global.L2 [%0];" ::"l"(img2 + ch * plane + static_cast<long>(ih) * a.w + off * 32));
+        }
+      }
+    }
+  } else if (warp < kProdWarps) {
+    // ---------------------------------------------------------------------------------------------- tile team
+    // For every output pixel the NWIN windows of 32 bytes, word-unaligned in the row buffers, into the operand tile.
+    const int tid = threadIdx.x - 32 * kCalibWarps;
     const uint32_t ring = smem_u32(ring_smem);
-    const int upt = 128 * a.nwin / kProdThreads;   // windows per thread and tile (2 or 4)
-    const int pstep = kProdThreads / a.nwin;       // pixels between a thread's consecutive windows
-    const int wv = tid % a.nwin;                   // this thread's window: filter row pair j, row e of the pair
+    constexpr int kUpt = 128 * NWIN / kTileThreads;  // windows per thread and tile (2 or 4)
+    constexpr int kPstep = kTileThreads / NWIN;      // pixels between a thread's consecutive windows
+    const int wv = tid % NWIN;                       // this thread's window: filter row pair j, row e of the pair
     const int wj = wv / a.fold_h, we = wv - wj * a.fold_h;
     const int kch = wv >> 2, sub = wv & 3;
     bool ok = true;
     int qseq = 0;
-    for (int k = 0; k < nb; ++k) {
-      const int item = static_cast<int>(blockIdx.x) + k * static_cast<int>(gridDim.x);
-      const int n = item / a.items_per_image;
-      const int p0 = (item - n * a.items_per_image) * a.rows_item;
-      const int ih0 = p0 * a.stride_h - a.pad_t;
-      const float* img = a.x + static_cast<long>(n) * a.cin * plane;
-      // 1. calib: image rows -> [pixel][channel] bytes.  A thread takes 4 pixels of the three channels = 3 words.
-      for (int r = warp; r < a.rows_in; r += kProdWarps) {
-        const int ih = ih0 + r;
-        const bool inside = ih >= 0 && ih < a.h;
-        const uint32_t dst_row = rb0 + static_cast<uint32_t>((r * a.row_words + a.px0_word) * 4);
-        for (int t = lane; t < w4; t += 32) {
-          uint32_t w0 = 0, w1 = 0, w2 = 0;
-          if (inside) {
-            const float4* src = reinterpret_cast<const float4*>(img + static_cast<long>(ih) * a.w) + t;
-            const float4 c0 = __ldg(src), c1 = __ldg(src + (plane >> 2)), c2 = __ldg(src + 2 * (plane >> 2));
-            const uint32_t q00 = calib_bits(c0.x, a.inv_scale), q01 = calib_bits(c1.x, a.inv_scale), q02 = calib_bits(c2.x, a.inv_scale);
-            const uint32_t q10 = calib_bits(c0.y, a.inv_scale), q11 = calib_bits(c1.y, a.inv_scale), q12 = calib_bits(c2.y, a.inv_scale);
-            const uint32_t q20 = calib_bits(c0.z, a.inv_scale), q21 = calib_bits(c1.z, a.inv_scale), q22 = calib_bits(c2.z, a.inv_scale);
-            const uint32_t q30 = calib_bits(c0.w, a.inv_scale), q31 = calib_bits(c1.w, a.inv_scale), q32 = calib_bits(c2.w, a.inv_scale);
-            w0 = pack_low_bytes(q00, q01, q02, q10);
-            w1 = pack_low_bytes(q11, q12, q20, q21);
-            w2 = pack_low_bytes(q22, q30, q31, q32);
-          }
-          const uint32_t d = dst_row + static_cast<uint32_t>(t * 12);
-          sts32(d, w0);
-          sts32(d + 4, w1);
-          sts32(d + 8, w2);
-        }
-      }
-      prod_barrier();
-      // 2. operand tiles: for every output pixel the nwin windows of 32 bytes, word-unaligned in the row buffers
-      int py = 0, q = tid / a.nwin;  // output row (inside the item) and column of this thread's next window
+    for (int k = 0; k < nb && ok; ++k) {
+      const int b = k & 1;
+      ok = mbar_wait(smem_u32(&rows_full[b]), (k >> 1) & 1, abort_flag, a.status, FAULT_WAIT_FULL);
+      if (!ok) break;
+      const uint32_t rb0 = smem_u32(rowbuf + b * rowbuf_words);
+      int py = 0, q = tid / NWIN;  // output row (inside the item) and column of this thread's next window
       while (q >= a.wo) {
         q -= a.wo;
         ++py;
@@ -199,34 +212,38 @@ __global__ void __launch_bounds__(kThreads, 1)
         ok = mbar_wait(smem_u32(&empty_bar[stage]), (use & 1) ^ 1, abort_flag, a.status, FAULT_WAIT_EMPTY);
         if (!ok) break;
         const uint32_t tile = ring + static_cast<uint32_t>(stage * a.stage_bytes + kch * (128 * 128));
-        int m = tid / a.nwin;
-        for (int i = 0; i < upt; ++i) {
+        uint32_t v[kUpt][9], shift[kUpt];
+#pragma unroll
+        for (int i = 0; i < kUpt; ++i) {
           const int rb = (py + wj) * a.fold_h + we;
           const int src = a.base_off + q * a.stride_w * 3;
-          const uint32_t s = rb0 + static_cast<uint32_t>((rb * a.row_words + (src >> 2)) * 4);
-          const uint32_t sh = static_cast<uint32_t>(src & 3) * 8;
-          uint32_t v[9], o[8];
+          const uint32_t sa = rb0 + static_cast<uint32_t>((rb * a.row_words + (src >> 2)) * 4);
+          shift[i] = static_cast<uint32_t>(src & 3) * 8;
 #pragma unroll
-          for (int j = 0; j < 9; ++j) v[j] = lds32(s + 4 * j);
-#pragma unroll
-          for (int j = 0; j < 8; ++j) o[j] = __funnelshift_r(v[j], v[j + 1], sh);
-          const uint32_t row = tile + static_cast<uint32_t>(m * 128);
-          const int sw = m & 7;
-          sts128(row + (((sub * 2) ^ sw) << 4), o[0], o[1], o[2], o[3]);
-          sts128(row + (((sub * 2 + 1) ^ sw) << 4), o[4], o[5], o[6], o[7]);
-          m += pstep;
-          q += pstep;
+          for (int j = 0; j < 9; ++j) v[i][j] = lds32(sa + 4 * j);
+          q += kPstep;
           while (q >= a.wo) {
             q -= a.wo;
             ++py;
           }
         }
+#pragma unroll
+        for (int i = 0; i < kUpt; ++i) {
+          const int m = tid / NWIN + i * kPstep;
+          uint32_t o[8];
+#pragma unroll
+          for (int j = 0; j < 8; ++j) o[j] = __funnelshift_r(v[i][j], v[i][j + 1], shift[i]);
+          const uint32_t row = tile + static_cast<uint32_t>(m * 128);
+          const int sw = m & 7;
+          sts128(row + (((sub * 2) ^ sw) << 4), o[0], o[1], o[2], o[3]);
+          sts128(row + (((sub * 2 + 1) ^ sw) << 4), o[4], o[5], o[6], o[7]);
+        }
         fence_proxy_async_smem();
         __syncwarp();
         if (lane == 0) mbar_arrive(smem_u32(&full_bar[stage]));
       }
-      // the next item's calib overwrites the rows these windows were read from; and all producers stop together
-      if (prod_barrier_any(!ok || *abort_flag != 0)) break;
+      __syncwarp();
+      if (lane == 0 && ok) mbar_arrive(smem_u32(&rows_empty[b]));  // the calib team may overwrite this buffer
     }
   } else if (warp >= kMmaWarp) {
     asm volatile("setmaxnreg.dec.sync.aligned.u32 %0;" ::"n"(kMmaRegs));
@@ -283,7 +300,7 @@ __global__ void __launch_bounds__(kThreads, 1)
     const float ub = quant_upper_bound<ACT>(a.alpha);
     int sbuf = 0;
     bool ok = true;
-    for (int q = group; q < total_tiles && ok; q += 4) {
+    for (int q = group; q < total_tiles && ok; q += kEpiGroups) {
       const int buf = q % a.acc_bufs;
       const uint32_t parity = static_cast<uint32_t>(q / a.acc_bufs) & 1u;
       const int k = q / a.tiles_item, t = q - k * a.tiles_item;
@@ -344,14 +361,16 @@ __global__ void __launch_bounds__(kThreads, 1)
 }
 
 typedef void (*StemKernel)(const CUtensorMap, const CUtensorMap, const StemArgs);
-StemKernel pick_kernel(int act) {
+template <int NWIN>
+StemKernel pick_act(int act) {
   switch (act) {
-    case PLB_ACT_RELU: return stem_tc_kernel<PLB_ACT_RELU>;
-    case PLB_ACT_RELU6: return stem_tc_kernel<PLB_ACT_RELU6>;
-    case PLB_ACT_LEAKY: return stem_tc_kernel<PLB_ACT_LEAKY>;
-    default: return stem_tc_kernel<PLB_ACT_NONE>;
+    case PLB_ACT_RELU: return stem_tc_kernel<PLB_ACT_RELU, NWIN>;
+    case PLB_ACT_RELU6: return stem_tc_kernel<PLB_ACT_RELU6, NWIN>;
+    case PLB_ACT_LEAKY: return stem_tc_kernel<PLB_ACT_LEAKY, NWIN>;
+    default: return stem_tc_kernel<PLB_ACT_NONE, NWIN>;
   }
 }
+StemKernel pick_kernel(int act, int nwin) { return nwin == 8 ? pick_act<8>(act) : pick_act<4>(act); }
 
 typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
                                   const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
@@ -397,7 +416,7 @@ bool plan(const StemProblem& p, StemPlan* s, std::string* why) {
   s->rows_item = 128 / g;
   if (s->rows_item > 16 || p.ho % s->rows_item != 0) return no("output rows do not group into whole 128-pixel tiles");
   s->tiles_item = s->rows_item * p.wo / 128;
-  if (kProdThreads / s->nwin > p.wo) return no("image too narrow");
+  if (p.wo < 8) return no("image too narrow");
   s->rows_in = (s->rows_item - 1) * p.stride_h + s->nwin;
   const int pad_bytes = p.pad_l * p.cin;
   s->px0_word = (pad_bytes + 3) / 4;
@@ -407,7 +426,7 @@ bool plan(const StemProblem& p, StemPlan* s, std::string* why) {
   const int need_words = std::max((last_src >> 2) + 9, s->px0_word + (p.w * p.cin + 3) / 4);
   s->row_words = need_words | 1;  // odd pitch: rows of one column fall into different banks
   if ((reinterpret_cast<uintptr_t>(p.wfold) & 15) || (reinterpret_cast<uintptr_t>(p.y) & 15)) return no("filter / output alignment");
-  const size_t rowbuf_bytes = static_cast<size_t>((s->rows_in * s->row_words + 255) & ~255) * 4;
+  const size_t rowbuf_bytes = 2 * static_cast<size_t>((s->rows_in * s->row_words + 255) & ~255) * 4;
   const size_t fixed = static_cast<size_t>(kEpiWarps) * kStagingPerWarp + static_cast<size_t>(p.cout) * s->k_bytes + rowbuf_bytes + kCtrlBytes + 1024;
   const size_t stage_bytes = 128 * static_cast<size_t>(s->k_bytes);
   if (fixed + 2 * stage_bytes > 227 * 1024) return no("does not fit shared memory");
@@ -473,7 +492,7 @@ int stem_tc_launch(plb_ctx* ctx, const StemProblem& p) {
                          CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
     if (r != CUDA_SUCCESS) return fail(PLB_E_CUDA, "tensor map of the output: error %d", static_cast<int>(r));
   }
-  StemKernel kernel = pick_kernel(p.epi.act);
+  StemKernel kernel = pick_kernel(p.epi.act, s.nwin);
   {
     static std::mutex attr_mutex;
     std::lock_guard<std::mutex> lock(attr_mutex);
