@@ -75,14 +75,17 @@ def test_fused_equals_the_two_layer_sequence(plb, ctx, shape):
     check_pair(plb, ctx, 100 + c + h, n, c, h, w, cout, s)
 
 
-@pytest.mark.parametrize("tw,seg", [(16, 8), (16, 0), (8, 16), (8, 32), (4, 32), (4, 0)])
-@pytest.mark.parametrize("shape", [(3, 128, 40, 36, 128, 1), (2, 256, 33, 18, 128, 2), (4, 64, 45, 45, 64, 1)])
+FORCED = [(shape, tw, seg)
+          for shape in [(3, 128, 40, 36, 128, 1), (2, 256, 33, 18, 128, 2), (4, 64, 45, 45, 64, 1)]
+          for tw, seg in [(16, 8), (16, 0), (8, 16), (8, 32), (4, 32), (4, 0)]
+          if shape[1] * tw >= 512 and not (tw == 4 and shape[1] < 128)]  # a strip needs at least one warp of threads
+
+
+@pytest.mark.parametrize("shape,tw,seg", FORCED)
 def test_forced_tile_shapes(plb, ctx, shape, tw, seg, monkeypatch):
     """Tile columns and rows per work item forced through the tuning switches: partial last tiles, work items
     with several tiles, the alternating swizzle phase of 4-column tiles, more items than groups."""
     n, c, h, w, cout, s = shape
-    if c * tw < 512:
-        pytest.skip("fewer than 32 threads per strip")
     monkeypatch.setenv("PLB_DWPW_TW", str(tw))
     if seg:
         monkeypatch.setenv("PLB_DWPW_SEG", str(seg))
@@ -102,8 +105,7 @@ def test_many_images_more_items_than_slots(plb, ctx):
 @pytest.mark.parametrize("c,cout,hw,stride", [(32, 64, 112, 1), (64, 128, 112, 2), (128, 128, 56, 1), (128, 256, 56, 2),
                                               (256, 256, 28, 1), (256, 512, 28, 2)])
 def test_mobilenet_v1_block_shapes(plb, ctx, c, cout, hw, stride):
-    """The first six blocks of MobileNetV1 at their real sizes, batch 2, against the library's own two launches
-    (themselves checked against the oracle elsewhere) and, on a corner crop, against the oracle."""
+    """The first six blocks of MobileNetV1 at their real sizes, batch 2, against the oracle's two-layer sequence."""
     dw, pw, x, q1, q2 = make_pair(plb, ctx, 900 + c + hw, 2, c, hw, hw, cout, stride)
     y = dw.run_nhwc_dwpw(pw, x)
     ctx.sync()
