@@ -4,6 +4,7 @@
     python layer_bench.py conv   --cin 64 --hw 56 --cout 64 --k 3 --pad 1 --batch 128 [--out i8|f32|addrelu] [--nchw]
     python layer_bench.py dw     --cin 32 --hw 112 --stride 1 --batch 128
     python layer_bench.py dwpw   --cin 128 --cout 128 --hw 56 --stride 1 --batch 256            # depthwise 3x3 + 1x1 in one launch
+    python layer_bench.py stem   --k 7 --cout 64 --batch 128                                   # first layer from the fp32 image
     python layer_bench.py block  --cin 64 --cin2 64 --hw 56 --cout 256 --stride 1 --batch 128   # projection-block tail
     python layer_bench.py fc     --m 4096 --kdim 4096 --n 4096 [--out i8|f32]
     python layer_bench.py sparse --cin 128 --cout 128 --hw 56 --batch 256 [--fp32] [--semi] [--impl walk|dense]
@@ -210,6 +211,22 @@ class Layers:
         ctx.sync()
         return report(name, us, nbytes, ops, extra)
 
+    def stem(self, k, cout, batch, hw=224):
+        """First layer of a network from the fp32 NCHW image (calib + convolution), int8 channels-last out."""
+        import torch
+        plb, ctx, rng = self.plb, self.ctx, self.rng
+        w = rng.integers(-127, 128, (cout, 3, k, k), dtype=np.int8)
+        conv = plb.Conv(ctx, w, [0.001], 0.03, None, in_hw=(hw, hw), stride=(2, 2), pads=(k // 2,) * 4, act=plb.ACT_RELU,
+                        out_scale=0.05)
+        img = torch.randn((batch, 3, hw, hw), device="cuda")
+        y = torch.empty((batch, conv.ho, conv.wo, cout), dtype=torch.int8, device="cuda")
+        before = ctx.stem_launch_count()
+        us = time_launches(lambda: conv.run_image_f32(img, out=y), self.iters, self.warm)
+        one = ctx.stem_launch_count() > before
+        ctx.sync()
+        return report("stem k%d 3->%d %dx%d b%d %s" % (k, cout, hw, hw, batch, "one launch" if one else "staged"), us,
+                      img.numel() * 4 + y.numel() + w.size, 2.0 * batch * conv.ho * conv.wo * cout * 3 * k * k)
+
     def int8_peak(self, n):
         """Not a kernel of this library: the vendor int8 GEMM on the same GPU, as a measured tensor-core denominator."""
         import torch
@@ -221,7 +238,7 @@ class Layers:
 
 def main():
     ap = argparse.ArgumentParser()
-    ap.add_argument("kind", choices=["conv", "dw", "dwpw", "block", "fc", "sparse", "fc-sweep", "sparse-sweep", "int8-peak"])
+    ap.add_argument("kind", choices=["conv", "dw", "dwpw", "stem", "block", "fc", "sparse", "fc-sweep", "sparse-sweep", "int8-peak"])
     ap.add_argument("--cin2", type=int, default=64, help="block: input channels of the shortcut conv")
     ap.add_argument("--cin", type=int, default=64)
     ap.add_argument("--cout", type=int, default=64)
@@ -254,6 +271,8 @@ def main():
         show(L.conv(args.cin, args.hw, args.cout, args.k, args.stride, args.pad, args.batch, args.out, nchw=args.nchw))
     elif args.kind == "dw":
         show(L.conv(args.cin, args.hw, args.cin, 3, args.stride, 1, args.batch, args.out, groups=args.cin))
+    elif args.kind == "stem":
+        show(L.stem(args.k, args.cout, args.batch))
     elif args.kind == "dwpw":
         show(L.dwpw(args.cin, args.cout, args.hw, args.stride, args.batch))
     elif args.kind == "fc":
