@@ -77,6 +77,8 @@ long plb_ctx_launch_count(const plb_ctx* ctx);
 long plb_ctx_window_launch_count(const plb_ctx* ctx);
 /* How many 1x1 convolutions ran directly on NCHW tensors (no layout staging passes).  For tests. */
 long plb_ctx_nchw_launch_count(const plb_ctx* ctx);
+/* ... of which on images whose pixel count is not a multiple of 16 (operand tiles filled by gather warps).  For tests. */
+long plb_ctx_nchw_gather_launch_count(const plb_ctx* ctx);
 /* How many GEMMs ran as two-SM tiles (256 x N output tiles on pairs of SMs).  For tests. */
 long plb_ctx_pair_launch_count(const plb_ctx* ctx);
 /* How many first layers ran from the fp32 image in one launch (plb_conv_run_image_f32 without a staging pass).  For tests. */

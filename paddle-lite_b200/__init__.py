@@ -61,6 +61,7 @@ SYMBOLS = {
     "plb_ctx_pair_launch_count": (C.c_long, [_P]),
     "plb_ctx_dwpw_launch_count": (C.c_long, [_P]),
     "plb_ctx_stem_launch_count": (C.c_long, [_P]),
+    "plb_ctx_nchw_gather_launch_count": (C.c_long, [_P]),
     "plb_conv_dwpw_fusable": (C.c_int, [_P, _P]),
     "plb_conv_run_nhwc_dwpw": (C.c_int, [_P, _P, _P, _P, C.c_int]),
     "plb_ctx_workspace_size": (C.c_size_t, [_P]),
@@ -157,6 +158,9 @@ class Context:
 
     def pair_launch_count(self):
         return lib().plb_ctx_pair_launch_count(self.handle)
+
+    def nchw_gather_launch_count(self):
+        return lib().plb_ctx_nchw_gather_launch_count(self.handle)
 
     def stem_launch_count(self):
         return lib().plb_ctx_stem_launch_count(self.handle)

@@ -11,7 +11,7 @@ import sys
 HERE = os.path.dirname(os.path.abspath(__file__))
 CSRC = os.path.join(HERE, "csrc")
 LIB = os.path.join(HERE, "libplb200.so")
-SOURCES = ["plb200.cu", "igemm_tc.cu", "igemm_nchw.cu", "igemm_pair.cu", "fused_dwpw.cu", "stem_tc.cu", "kernels_simple.cu"]
+SOURCES = ["plb200.cu", "igemm_tc.cu", "igemm_nchw.cu", "igemm_nchw_gather.cu", "igemm_pair.cu", "fused_dwpw.cu", "stem_tc.cu", "kernels_simple.cu"]
 HEADERS = ["common.cuh", "igemm_tc.cuh", "tc_device.cuh", "igemm_nchw.cuh", "igemm_pair.cuh", "fused_dwpw.cuh", "stem_tc.cuh", "dw_device.cuh", "kernels_simple.cuh", os.path.join("..", "..", "include", "plb200.h")]
 NVCC_FLAGS = ["-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17",
               "-Xcompiler", "-fPIC"]

@@ -55,6 +55,7 @@ struct plb_ctx {
   long pair_launches = 0;       // GEMMs that ran as two-SM tiles (cta_group::2)
   long stem_launches = 0;       // first layers that ran from the fp32 image in one launch (no staging pass)
   long dwpw_launches = 0;       // depthwise + 1x1 pairs that ran as one launch
+  long nchw_gather_launches = 0;  // ... of which on images TMA cannot address (operand tiles filled by gather warps)
   long nchw_launches = 0;       // 1x1 convolutions that ran on NCHW tensors directly (no layout staging)
   int reserve(size_t bytes);    // make ws at least `bytes`
 };

@@ -1354,6 +1354,7 @@ TcSwitches tc_switches_from_env() {
   s.pair = env_int("PLB_TC_PAIR", -1);
   s.nchw = env_int("PLB_TC_NCHW", -1);
   s.dw_strip = env_int("PLB_DW_STRIP", -1);
+  s.nchw_gather = env_int("PLB_TC_NCHW_GATHER", -1);
   s.stem = env_int("PLB_STEM", -1);
   s.dwpw = env_int("PLB_DWPW", -1);
   s.dwpw_tw = env_int("PLB_DWPW_TW", -1);

@@ -240,6 +240,7 @@ int plb_ctx_set_workspace(plb_ctx* ctx, void* dptr, size_t bytes) {
 long plb_ctx_launch_count(const plb_ctx* ctx) { return ctx ? ctx->launches : 0; }
 long plb_ctx_window_launch_count(const plb_ctx* ctx) { return ctx ? ctx->window_launches : 0; }
 long plb_ctx_nchw_launch_count(const plb_ctx* ctx) { return ctx ? ctx->nchw_launches : 0; }
+long plb_ctx_nchw_gather_launch_count(const plb_ctx* ctx) { return ctx ? ctx->nchw_gather_launches : 0; }
 long plb_ctx_stem_launch_count(const plb_ctx* ctx) { return ctx ? ctx->stem_launches : 0; }
 long plb_ctx_dwpw_launch_count(const plb_ctx* ctx) { return ctx ? ctx->dwpw_launches : 0; }
 long plb_ctx_pair_launch_count(const plb_ctx* ctx) { return ctx ? ctx->pair_launches : 0; }
@@ -489,6 +490,11 @@ bool nchw_native(const plb_conv* c, const int8_t* x, void* y, int batch, int mod
   p->batch = batch; p->cin = d.cin; p->cin_pad = c->cin_pad; p->cout = d.cout; p->hw = d.h * d.w;
   p->out_mode = mode; p->y = y;
   if (p->hw % 16 != 0) {
+    // rows TMA cannot address: gather warps fill the operand tiles (igemm_nchw_gather.cu), several small images per tile
+    if (c->sw.nchw_gather != 0 && igemm_nchw_gather_supported(*p, nullptr)) {
+      p->x_pitch = -1;  // marks the gather kernel for the caller
+      return true;
+    }
     // Images of fewer than 100 pixels would fill under half of a 128-pixel tile: the channels-last path, whose
     // tiles run across images, serves them better.
     if (p->hw < 100 && c->sw.nchw != 1) return false;
@@ -510,6 +516,10 @@ int conv_run_nchw(plb_conv* c, const int8_t* x, void* y, int batch, int mode) {
     NchwProblem np;
     if (nchw_native(c, x, y, batch, mode, &np)) {
       np.epi = out_spec(c, mode, y).epi;
+      if (np.x_pitch < 0) {
+        np.x_pitch = 0;
+        return igemm_nchw_gather_launch(ctx, np);
+      }
       if (np.x_pitch == 0) return igemm_nchw_launch(ctx, np);
       // pixel counts that are not a multiple of 16: re-pitch the rows into the workspace, run, copy back
       const int eb = mode == OUT_I8 ? 1 : 4;
