@@ -13,6 +13,7 @@ struct NchwProblem {
   int out_mode;      // OUT_I8 / OUT_F32 / OUT_ACC
   void* y;           // [batch][cout][hw] int8 / float / int32
   EpiParams epi;
+  int bres_switch;   // gather kernel only: 0 = never the pixel-resident order, 1 = wherever it fits (tuning switch; else planner)
 };
 
 bool igemm_nchw_supported(const NchwProblem& p, std::string* why);

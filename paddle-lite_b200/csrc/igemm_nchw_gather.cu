@@ -1,9 +1,9 @@
-// 1x1 convolution on NCHW tensors whose images TMA cannot address (pixel counts that are not a multiple of 16: 14 x 14,
-// 7 x 7, ...), without any re-pitching pass.  Same orientation and arithmetic as igemm_nchw.cu (M = output channels,
+// 1x1 convolution on NCHW tensors whose images TMA cannot address (pixel counts that are a multiple of 4 but not of 16:
+// 14 x 14, 10 x 10, 18 x 18, ...), without any re-pitching pass.  Same orientation and arithmetic as igemm_nchw.cu (M = output channels,
 // N = pixels, B = X[n] = [cin][hw] as an MN-major operand, exact int32 accumulators, the same requantiser); what differs
 // is how the pixels get in and out:
-//   * 8 gather warps copy X rows with plain 4-byte (or, for odd row lengths, 1-byte) loads into the 128-byte-swizzled
-//     MN-major operand tile that TMA would have written; a tile's columns are the pixels of G whole images, each padded
+//   * 8 gather warps copy X rows with 4-byte asynchronous copies (cp.async, several stages in flight) into the
+//     128-byte-swizzled MN-major operand tile that TMA would have written; a tile's columns are the pixels of G whole images, each padded
 //     to P = hw rounded up to 16 columns (G = 256 / P), or 256-pixel runs of one larger image;
 //   * the epilogue warps requantise 32 columns at a time into a small staging tile and write it out row by row, so that
 //     the lanes of a warp store consecutive pixels of ONE output row.
@@ -12,6 +12,7 @@
 // lite/kernels/arm/sparse_conv_compute.cc:155-267 for the densified sparse_conv2d).
 // Roles: warps 0-15 epilogue (4 groups x 4 TMEM lane quadrants), warps 16-23 gather, warp 24 filter TMA, warp 25 MMA issue
 // (warps 26-27 idle: registers are handed out four warps at a time and re-balanced with setmaxnreg).  All waits bounded.
+#include <algorithm>
 #include <mutex>
 
 #include "igemm_nchw.cuh"
@@ -35,6 +36,7 @@ constexpr int kCtrlBytes = 1024;
 constexpr int kStagePitch = 80;                                  // bytes between rows of an epilogue staging tile (64 + 16)
 constexpr int kStagingBytes = kEpilogueWarps * 32 * kStagePitch;
 constexpr int kMaxResidentW = 64 * 1024;
+constexpr int kInFlight = 4;                                     // stages of copies a gather lane keeps pending
 constexpr int kMaxIter = 2;                                      // 4-byte words of a 256-pixel row per gather lane: 64 / 32
 
 struct GatherArgs {
@@ -48,8 +50,10 @@ struct GatherArgs {
   int kc, ksteps, stages;
   int tiles_m, tiles_p, num_tiles;
   int resident_w, resident_bytes;
+  int bres;               // pixel tiles stay in shared memory for ALL channel tiles: a CTA gathers a pixel tile once, then
+                          // runs the channel tiles over it with the filter streamed through its own ring (wstages)
+  int wstages, num_ptiles;
   int dup;
-  int bytewise;           // hw % 4 != 0: rows are not 4-byte aligned, pixels move one byte at a time
   const float* scale;
   const float* bias;
   float alpha;
@@ -57,8 +61,19 @@ struct GatherArgs {
   int* status;
 };
 
-__device__ __forceinline__ void sts32(uint32_t addr, uint32_t v) {
-  asm volatile("st.shared.b32 [%0], %1;" ::"r"(addr), "r"(v) : "memory");
+// 4-byte asynchronous copy global -> shared; `take` false: the word is written as zero and nothing is read
+__device__ __forceinline__ void cp_async4(uint32_t dst, const void* src, bool take) {
+  asm volatile("cp.async.ca.shared.global [%0], [%1], 4, %2;" ::"r"(dst), "l"(src), "r"(take ? 4 : 0) : "memory");
+}
+// waits until at most n (0 .. 4) of this thread's committed copy groups are pending
+__device__ __forceinline__ void cp_async_wait_pending(int n) {
+  switch (n) {
+    case 0: asm volatile("cp.async.wait_group 0;" ::: "memory"); break;
+    case 1: asm volatile("cp.async.wait_group 1;" ::: "memory"); break;
+    case 2: asm volatile("cp.async.wait_group 2;" ::: "memory"); break;
+    case 3: asm volatile("cp.async.wait_group 3;" ::: "memory"); break;
+    default: asm volatile("cp.async.wait_group 4;" ::: "memory"); break;
+  }
 }
 __device__ __forceinline__ uint32_t lds32(uint32_t addr) {
   uint32_t v;
@@ -77,6 +92,25 @@ __device__ __forceinline__ void decode_tile(const GatherArgs& a, int t, int& m0,
   p0 = pt * a.bn;
 }
 
+// The j-th (channel tile, pixel tile) of this CTA; false past the end.  Streaming order: tiles blockIdx.x, + gridDim.x, ...
+// with the channel tile fastest across CTAs.  Pixel-resident order (bres): pixel tiles blockIdx.x, + gridDim.x, ..., and
+// for each of them every channel tile in turn.
+__device__ __forceinline__ bool cta_tile(const GatherArgs& a, int j, int& m0, int& p0, int& img) {
+  if (!a.bres) {
+    const long t = static_cast<long>(blockIdx.x) + static_cast<long>(j) * gridDim.x;
+    if (t >= a.num_tiles) return false;
+    decode_tile(a, static_cast<int>(t), m0, p0, img);
+    return true;
+  }
+  const int ptl = j / a.tiles_m;
+  const long pt = static_cast<long>(blockIdx.x) + static_cast<long>(ptl) * gridDim.x;
+  if (pt >= a.num_ptiles) return false;
+  m0 = (j - ptl * a.tiles_m) * kTileCout;
+  p0 = static_cast<int>(pt % a.tiles_p) * a.bn;
+  img = static_cast<int>(pt / a.tiles_p) * a.group_images;
+  return true;
+}
+
 template <int MODE, int ACT>
 __global__ void __launch_bounds__(kThreads, 1)
     igemm_nchw_gather_kernel(const __grid_constant__ CUtensorMap tmW, const GatherArgs a) {
@@ -85,18 +119,21 @@ __global__ void __launch_bounds__(kThreads, 1)
   uint8_t* smem_al = smem_raw + (((raw_addr + 1023u) & ~1023u) - raw_addr);
   // [epilogue staging][resident filter][operand ring: per stage filter tile (unless resident) + pixel tile][barriers]
   const int halves = (a.bn + 127) >> 7;
-  const int stage_a = a.resident_w ? 0 : kTileCout * a.kc;
+  const int stage_a = (a.resident_w || a.bres) ? 0 : kTileCout * a.kc;
   const int stage_b = a.kc * 128 * halves;
   const int stage_bytes = stage_a + stage_b;
   uint8_t* smem_wres = smem_al + ((kStagingBytes + 1023) & ~1023);
   uint8_t* smem = smem_wres + a.resident_bytes;
-  uint8_t* ctrl = smem + a.stages * stage_bytes;
+  uint8_t* wring = smem + a.stages * stage_bytes;  // bres: ring of filter tiles
+  uint8_t* ctrl = wring + a.wstages * kTileCout * a.kc;
   uint64_t* full_bar = reinterpret_cast<uint64_t*>(ctrl);
   uint64_t* empty_bar = full_bar + kMaxStages;
   uint64_t* acc_full = empty_bar + kMaxStages;  // [2]
   uint64_t* acc_empty = acc_full + 2;           // [2]
   uint64_t* wres_bar = acc_empty + 2;
-  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(wres_bar + 1);
+  uint64_t* wfull = wres_bar + 1;        // [kMaxStages] bres: filter ring
+  uint64_t* wempty = wfull + kMaxStages;
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(wempty + kMaxStages);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
 
   const int warp = threadIdx.x >> 5;
@@ -104,10 +141,10 @@ __global__ void __launch_bounds__(kThreads, 1)
   const uint32_t tmem_cols = 2u * static_cast<uint32_t>(a.acc_stride);
 
   if (warp == kProducerWarp) {
-    constexpr int kBarriers = 2 * kMaxStages + 4 + 1;
+    constexpr int kBarriers = 4 * kMaxStages + 4 + 1;
     for (int i = lane; i < kBarriers; i += 32) {
       uint32_t count = 1;
-      if (i < kMaxStages) count = kGatherWarps + (a.resident_w ? 0 : 1);  // gather warps (+ the filter copy's arrival)
+      if (i < kMaxStages) count = kGatherWarps + ((a.resident_w || a.bres) ? 0 : 1);  // gather warps (+ the filter copy's arrival)
       else if (i >= 2 * kMaxStages + 2 && i < 2 * kMaxStages + 4) count = 8;  // two epilogue groups of four warps drain a buffer
       mbar_init(smem_u32(&full_bar[i]), count);
     }
@@ -141,16 +178,42 @@ __global__ void __launch_bounds__(kThreads, 1)
 
   if (warp >= kProducerWarp) {
     asm volatile("setmaxnreg.dec.sync.aligned.u32 %0;" ::"n"(kCtrlRegs));
-    if (warp == kProducerWarp && !a.resident_w) {
+    if (warp == kProducerWarp && a.bres) {
+      // ------------------------------------------------------------ filter tiles through TMA, a ring of their own
+      const bool leader = elect_one();
+      int ws = 0;
+      uint32_t wparity = 1;
+      bool ok = true;
+      const uint32_t wbase = smem_u32(wring);
+      const uint32_t wbytes = static_cast<uint32_t>(kTileCout * a.kc);
+      int m0, p0, img;
+      for (int j = 0; ok && cta_tile(a, j, m0, p0, img); ++j) {
+        for (int ks = 0; ks < a.ksteps; ++ks) {
+          ok = mbar_wait(smem_u32(&wempty[ws]), wparity, abort_flag, a.status, FAULT_WAIT_EMPTY);
+          if (!ok) break;
+          const uint32_t bar = smem_u32(&wfull[ws]);
+          const uint32_t dst = wbase + ws * wbytes;
+          mbar_expect_tx_if(bar, wbytes, leader);
+          tma_load_2d_if(dst, &tmW, bar, ks * a.kc, m0, leader);
+          if (a.dup) tma_load_2d_if(dst + 64 * a.kc, &tmW, bar, ks * a.kc, m0, leader);
+          if (++ws == a.wstages) {
+            ws = 0;
+            wparity ^= 1;
+          }
+        }
+      }
+      if (!ok || *abort_flag) {
+        for (int jj = 0; jj < a.wstages; ++jj) mbar_wait_drain(smem_u32(&wfull[jj]), jj < ws ? (wparity ^ 1u) : wparity);
+      }
+    } else if (warp == kProducerWarp && !a.resident_w) {
       // ------------------------------------------------------------ filter tiles through TMA
       const bool leader = elect_one();
       int s = 0;
       uint32_t empty_parity = 1;
       bool ok = true;
       const uint32_t smem_base = smem_u32(smem);
-      for (int tile = blockIdx.x; tile < a.num_tiles && ok; tile += gridDim.x) {
-        int m0, p0, img;
-        decode_tile(a, tile, m0, p0, img);
+      int m0, p0, img;
+      for (int j = 0; ok && cta_tile(a, j, m0, p0, img); ++j) {
         for (int ks = 0; ks < a.ksteps; ++ks) {
           ok = mbar_wait(smem_u32(&empty_bar[s]), empty_parity, abort_flag, a.status, FAULT_WAIT_EMPTY);
           if (!ok) break;
@@ -194,25 +257,46 @@ __global__ void __launch_bounds__(kThreads, 1)
         ok = mbar_wait(smem_u32(wres_bar), 0, abort_flag, a.status, FAULT_WAIT_FULL);
         tc_fence_after();
       }
-      for (int tile = blockIdx.x; tile < a.num_tiles && ok; tile += gridDim.x, ++it) {
+      const uint32_t wring_lo = (smem_u32(wring) >> 4) & 0x3FFFu;
+      int ws = 0;
+      uint32_t wparity = 0;
+      int m0, p0, img;
+      for (; ok && cta_tile(a, it, m0, p0, img); ++it) {
         const int buf = it & 1;
         ok = mbar_wait(smem_u32(&acc_empty[buf]), ((it >> 1) & 1) ^ 1, abort_flag, a.status, FAULT_WAIT_ACCUM);
         if (!ok) break;
         tc_fence_after();
         const uint32_t d_tmem = tmem_base + buf * a.acc_stride;
+        // pixel-resident order: the chunks of a pixel tile are waited for in its first channel-tile pass and given back
+        // in its last one (stages == ksteps there, so s == ks and the parity follows the pixel tile)
+        const int mt = a.bres ? it % a.tiles_m : 0;
+        const bool first_pass = !a.bres || mt == 0, last_pass = !a.bres || mt == a.tiles_m - 1;
         for (int ks = 0; ks < a.ksteps; ++ks) {
-          ok = mbar_wait(smem_u32(&full_bar[s]), full_parity, abort_flag, a.status, FAULT_WAIT_FULL);
-          if (!ok) break;
+          if (first_pass) {
+            ok = mbar_wait(smem_u32(&full_bar[s]), full_parity, abort_flag, a.status, FAULT_WAIT_FULL);
+            if (!ok) break;
+          }
+          if (a.bres) {
+            ok = mbar_wait(smem_u32(&wfull[ws]), wparity, abort_flag, a.status, FAULT_WAIT_FULL);
+            if (!ok) break;
+          }
           tc_fence_after();
           const uint32_t st_lo = ring_lo + s * stage_lo;
-          const uint32_t a_lo = (a.resident_w ? wres_lo + ks * wstep_lo : st_lo) | (1u << 16);
+          const uint32_t a_lo = (a.bres ? wring_lo + ws * wstep_lo : (a.resident_w ? wres_lo + ks * wstep_lo : st_lo)) | (1u << 16);
           const uint32_t b_lo = (st_lo + stage_a_lo) | lbo_b;
           for (int j = 0; j < mma_per_stage; ++j)  // 32 bytes of K: +32 B inside A's swizzle span, +32 rows (4 KiB) of B
             tc_mma_i8_halves(d_tmem, a_lo + 2u * j, hi_a, b_lo + 256u * j, hi_b, idesc, (ks | j) ? 1u : 0u, leader);
-          tc_commit_if(smem_u32(&empty_bar[s]), leader);
+          if (a.bres) {
+            tc_commit_if(smem_u32(&wempty[ws]), leader);
+            if (++ws == a.wstages) {
+              ws = 0;
+              wparity ^= 1;
+            }
+          }
+          if (last_pass) tc_commit_if(smem_u32(&empty_bar[s]), leader);
           if (++s == a.stages) {
             s = 0;
-            full_parity ^= 1;
+            if (last_pass) full_parity ^= 1;
           }
         }
         if (!ok) break;
@@ -221,21 +305,33 @@ __global__ void __launch_bounds__(kThreads, 1)
     }
   } else if (warp >= kGatherWarp0) {
     // -------------------------------------------------------------- gather: X rows -> MN-major operand tile
+    // Asynchronous 4-byte copies (cp.async, zero-filled where a word lies outside the image or the channels): a lane
+    // issues the 32 words of its rows of a stage without holding them in registers and goes on to the next stage, so
+    // several stages of loads are in flight per SM; a stage is handed to the MMA warp when the copies of the stage
+    // issued kInFlight stages later have been committed and this one's have landed.
     asm volatile("setmaxnreg.dec.sync.aligned.u32 %0;" ::"n"(kGatherRegs));
     const int gw = warp - kGatherWarp0;  // rows gw, gw + 8, ...: (row & 7) == gw, the swizzle phase of all of them
     const int words = a.bn >> 2;         // 4-byte words of a tile row
     const long plane = static_cast<long>(a.cin) * a.hw;
-    int s = 0;
+    const int in_flight = a.stages - 1 < kInFlight ? a.stages - 1 : kInFlight;  // stages a lane keeps pending
+    int s = 0, s_done = 0, pending = 0;
     uint32_t empty_parity = 1;
     bool ok = true;
     const uint32_t smem_base = smem_u32(smem);
-    for (int tile = blockIdx.x; tile < a.num_tiles && ok; tile += gridDim.x) {
-      int m0, p0, img;
-      decode_tile(a, tile, m0, p0, img);
+    // hand over the oldest pending stage: its copies (and all older ones) have landed
+    auto retire = [&]() {
+      fence_proxy_async_smem();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(smem_u32(&full_bar[s_done]));
+      if (++s_done == a.stages) s_done = 0;
+      --pending;
+    };
+    int m0, p0, img;
+    for (int j = 0; ok && cta_tile(a, j, m0, p0, img); j += a.bres ? a.tiles_m : 1) {
       // this lane's words of a row: where they come from (image, pixel) and where they go (block of 128 columns, swizzled chunk)
       long goff[kMaxIter];
       uint32_t soff[kMaxIter];
-      int nvalid[kMaxIter];  // valid bytes of the word (0 .. 4)
+      bool valid[kMaxIter], used[kMaxIter];
 #pragma unroll
       for (int it = 0; it < kMaxIter; ++it) {
         const int w = lane + 32 * it;
@@ -245,62 +341,46 @@ __global__ void __launch_bounds__(kThreads, 1)
           g = col / a.image_cols;
           p = col - g * a.image_cols;
         }
-        int nv = a.hw - p;
-        nv = nv < 0 ? 0 : (nv > 4 ? 4 : nv);
-        if (w >= words || img + g >= a.batch) nv = 0;
-        nvalid[it] = nv;
-        goff[it] = static_cast<long>(img + g) * plane + p;
+        used[it] = w < words;
+        valid[it] = used[it] && p < a.hw && img + g < a.batch;  // hw % 4 == 0: a word is inside the image or outside
+        goff[it] = valid[it] ? static_cast<long>(img + g) * plane + p : 0;
         const int colb = col & 127;
         soff[it] = static_cast<uint32_t>((col >> 7) * (a.kc * 128) + (((colb >> 4) ^ gw) << 4) + (colb & 15));
       }
       for (int ks = 0; ks < a.ksteps; ++ks) {
-        ok = mbar_wait(smem_u32(&empty_bar[s]), empty_parity, abort_flag, a.status, FAULT_WAIT_EMPTY);
-        if (!ok) break;
-        const uint32_t dst = smem_base + s * stage_bytes + stage_a;
-        for (int c = gw; c < a.kc; c += 32) {
-          // four rows at a time: all loads are issued before the first store
-          uint32_t v[4][kMaxIter];
-#pragma unroll
-          for (int r = 0; r < 4; ++r) {
-            const int cc = c + 8 * r;
-            const int ch = ks * a.kc + cc;
-            const bool row_ok = cc < a.kc && ch < a.cin;
-            const int8_t* src = a.x + static_cast<long>(ch) * a.hw;
-#pragma unroll
-            for (int it = 0; it < kMaxIter; ++it) {
-              uint32_t val = 0;
-              if (row_ok && nvalid[it] > 0) {
-                const int8_t* q = src + goff[it];
-                if (!a.bytewise) {
-                  val = __ldg(reinterpret_cast<const uint32_t*>(q));  // hw % 4 == 0: whole words, 4-byte aligned
-                } else {
-#pragma unroll
-                  for (int b = 0; b < 4; ++b)
-                    if (b < nvalid[it]) val |= static_cast<uint32_t>(static_cast<uint8_t>(__ldg(q + b))) << (8 * b);
-                }
-              }
-              v[r][it] = val;
-            }
-          }
-#pragma unroll
-          for (int r = 0; r < 4; ++r) {
-            const int cc = c + 8 * r;
-            if (cc < a.kc) {
-#pragma unroll
-              for (int it = 0; it < kMaxIter; ++it)
-                if (lane + 32 * it < words) sts32(dst + static_cast<uint32_t>(cc * 128) + soff[it], v[r][it]);
-            }
-          }
+        if (!mbar_try_wait(smem_u32(&empty_bar[s]), empty_parity)) {
+          // About to block on the MMA warp: everything issued so far has to be handed over first.  In the pixel-resident
+          // order a chunk is given back only after the LAST channel-tile pass over ALL chunks of its pixel tile, which
+          // cannot start before the chunks still pending here have arrived.
+          asm volatile("cp.async.wait_all;" ::: "memory");
+          while (pending > 0) retire();
+          ok = mbar_wait(smem_u32(&empty_bar[s]), empty_parity, abort_flag, a.status, FAULT_WAIT_EMPTY);
+          if (!ok) break;
         }
-        fence_proxy_async_smem();
-        __syncwarp();
-        if (lane == 0) mbar_arrive(smem_u32(&full_bar[s]));
+        const uint32_t dst = smem_base + s * stage_bytes + stage_a;
+        for (int cc = gw; cc < a.kc; cc += 8) {
+          const int ch = ks * a.kc + cc;
+          const bool row_ok = ch < a.cin;
+          const int8_t* src = a.x + static_cast<long>(row_ok ? ch : 0) * a.hw;
+#pragma unroll
+          for (int it = 0; it < kMaxIter; ++it)
+            if (used[it]) cp_async4(dst + static_cast<uint32_t>(cc * 128) + soff[it], src + goff[it], row_ok && valid[it]);
+        }
+        asm volatile("cp.async.commit_group;" ::: "memory");
+        ++pending;
         if (++s == a.stages) {
           s = 0;
           empty_parity ^= 1;
         }
+        if (pending > in_flight) {
+          cp_async_wait_pending(in_flight);
+          retire();
+        }
       }
     }
+    // the copies still in flight land (bounded by the memory system, not by another role), then their stages are handed over
+    asm volatile("cp.async.wait_all;" ::: "memory");
+    while (pending > 0) retire();
   } else {
     // -------------------------------------------------------------- epilogue: 4 groups x 4 warps
     // Groups 0/1 take the CTA's even tiles (buffer 0), groups 2/3 the odd ones; the two groups of a tile take alternate
@@ -317,10 +397,8 @@ __global__ void __launch_bounds__(kThreads, 1)
     const bool grouped = a.group_images > 1 || a.tiles_p == 1;
     bool ok = true;
     for (int it = buf; ok; it += 2) {
-      const long tile_l = static_cast<long>(blockIdx.x) + static_cast<long>(it) * gridDim.x;
-      if (tile_l >= a.num_tiles) break;
       int m0, p0, img;
-      decode_tile(a, static_cast<int>(tile_l), m0, p0, img);
+      if (!cta_tile(a, it, m0, p0, img)) break;
       const int row0 = m0 + row_quad * 32;
       const bool active = row0 < a.cout;  // warp-uniform
       const int ch = row0 + lane;
@@ -361,9 +439,7 @@ __global__ void __launch_bounds__(kThreads, 1)
             g = col / a.image_cols;
             p = col - g * a.image_cols;
           }
-          int nv = a.hw - p;
-          nv = nv < 0 ? 0 : (nv > 4 ? 4 : nv);
-          if (col >= a.bn || img + g >= a.batch) nv = 0;
+          const int nv = (col < a.bn && p < a.hw && img + g < a.batch) ? 4 : 0;
           int8_t* ybase = static_cast<int8_t*>(a.y) + (static_cast<long>(img + g) * a.cout) * a.hw + p;
 #pragma unroll
           for (int pass = 0; pass < 8; ++pass) {
@@ -372,13 +448,7 @@ __global__ void __launch_bounds__(kThreads, 1)
             const int co = row0 + rr;
             if (co < a.cout && nv > 0) {
               int8_t* dstp = ybase + static_cast<long>(co) * a.hw;
-              if (!a.bytewise) {
-                *reinterpret_cast<uint32_t*>(dstp) = word;
-              } else {
-#pragma unroll
-                for (int b = 0; b < 4; ++b)
-                  if (b < nv) dstp[b] = static_cast<int8_t>(word >> (8 * b));
-              }
+              *reinterpret_cast<uint32_t*>(dstp) = word;  // hw % 4 == 0: whole words, 4-byte aligned
             }
           }
         } else {
@@ -475,6 +545,7 @@ bool igemm_nchw_gather_supported(const NchwProblem& p, std::string* why) {
   if (p.x_pitch || p.y_pitch) return no("dense NCHW tensors only");
   if (p.cin_pad % 32 != 0 || p.cin > p.cin_pad) return no("filter rows must be padded to a multiple of 32 bytes");
   if (p.batch <= 0 || p.cout <= 0 || p.cin <= 0 || p.hw <= 0) return no("empty problem");
+  if (p.hw % 4 != 0) return no("image rows must be a multiple of 4 bytes (4-byte asynchronous copies)");
   if (reinterpret_cast<uintptr_t>(p.w) & 15) return no("the filter must be 16-byte aligned");
   if ((reinterpret_cast<uintptr_t>(p.x) & 3) || (reinterpret_cast<uintptr_t>(p.y) & 3)) return no("tensors must be 4-byte aligned");
   if (static_cast<long>(p.batch) * p.cin * p.hw > 0x7fffffffL * 16) return no("tensor too large");
@@ -497,12 +568,20 @@ int igemm_nchw_gather_launch(plb_ctx* ctx, const NchwProblem& p) {
   a.ksteps = p.cin_pad / a.kc;
   a.tiles_m = (p.cout + kTileCout - 1) / kTileCout;
   a.dup = p.cout <= 64;
-  a.bytewise = p.hw % 4 != 0;
+  const int staging = (kStagingBytes + 1023) & ~1023;
+  const int budget = 225 * 1024 - staging - kCtrlBytes;
+  const int wtile = kTileCout * a.kc;
+  // Pixel-resident order (a pixel tile is gathered once and all channel tiles run over it) needs every K chunk of the
+  // pixel tile plus a ring of at least three filter tiles in shared memory; it pays as soon as there are two channel tiles.
+  auto bres_fits = [&](int bn) { return a.ksteps <= kMaxStages && a.ksteps * a.kc * 128 * ((bn + 127) / 128) + 3 * wtile <= budget; };
   long groups;
   if (p.hw <= 256) {
     // whole images per tile, each padded to a multiple of 16 columns
     a.image_cols = (p.hw + 15) / 16 * 16;
     a.group_images = 256 / a.image_cols;
+    // prefer a tile that fits the pixel-resident order (long K: 128 columns instead of 256)
+    if (a.tiles_m >= 2 && !bres_fits(a.group_images * a.image_cols) && a.image_cols <= 128 && bres_fits(128))
+      a.group_images = 128 / a.image_cols;
     // small grids: fewer images per tile so that every SM gets one
     while (a.group_images > 1 && static_cast<long>((p.batch + a.group_images - 1) / a.group_images) * a.tiles_m < ctx->sm_count)
       a.group_images /= 2;
@@ -511,27 +590,43 @@ int igemm_nchw_gather_launch(plb_ctx* ctx, const NchwProblem& p) {
     groups = (p.batch + a.group_images - 1) / a.group_images;
   } else {
     a.group_images = 1;
-    a.bn = 256;
+    a.bn = (a.tiles_m >= 2 && !bres_fits(256) && bres_fits(128)) ? 128 : 256;
     a.image_cols = a.bn;
     a.tiles_p = (p.hw + a.bn - 1) / a.bn;
     groups = p.batch;
   }
   a.acc_stride = 32;
   while (a.acc_stride < a.bn) a.acc_stride <<= 1;
-  const long tiles = groups * a.tiles_p * a.tiles_m;
+  const long ptiles = groups * a.tiles_p;
+  const long tiles = ptiles * a.tiles_m;
   if (tiles > 0x7fffffffL) return fail(PLB_E_UNSUPPORTED, "too many tiles");
   a.num_tiles = static_cast<int>(tiles);
-  const int resident_bytes = a.ksteps * kTileCout * a.kc;
-  const long grid_l = tiles < ctx->sm_count ? tiles : ctx->sm_count;
-  a.resident_w = grid_l % a.tiles_m == 0 && resident_bytes <= kMaxResidentW && tiles > grid_l;
-  a.resident_bytes = a.resident_w ? resident_bytes : 0;
+  a.num_ptiles = static_cast<int>(ptiles);
   const int halves = (a.bn + 127) / 128;
-  const int stage_bytes = (a.resident_w ? 0 : kTileCout * a.kc) + a.kc * 128 * halves;
-  const int staging = (kStagingBytes + 1023) & ~1023;
-  int stages = (225 * 1024 - staging - a.resident_bytes - kCtrlBytes) / stage_bytes;
-  if (stages > kMaxStages) stages = kMaxStages;
-  if (stages < 2) return fail(PLB_E_UNSUPPORTED, "NCHW gather path: the operand ring does not fit");
-  a.stages = stages;
+  const int stage_b = a.kc * 128 * halves;
+  a.bres = a.tiles_m >= 2 && bres_fits(a.bn) && (p.bres_switch == 1 || (p.bres_switch != 0 && ptiles >= ctx->sm_count / 2));
+  long grid_l;
+  int stage_bytes;
+  if (a.bres) {
+    grid_l = ptiles < ctx->sm_count ? ptiles : ctx->sm_count;
+    a.resident_w = 0;
+    a.resident_bytes = 0;
+    stage_bytes = stage_b;
+    a.stages = a.ksteps;
+    a.wstages = std::min(kMaxStages, (budget - a.ksteps * stage_b) / wtile);
+  } else {
+    const int resident_bytes = a.ksteps * wtile;
+    grid_l = tiles < ctx->sm_count ? tiles : ctx->sm_count;
+    a.resident_w = grid_l % a.tiles_m == 0 && resident_bytes <= kMaxResidentW && tiles > grid_l;
+    a.resident_bytes = a.resident_w ? resident_bytes : 0;
+    stage_bytes = (a.resident_w ? 0 : wtile) + stage_b;
+    int stages = (budget - a.resident_bytes) / stage_bytes;
+    if (stages > kMaxStages) stages = kMaxStages;
+    if (stages < 2) return fail(PLB_E_UNSUPPORTED, "NCHW gather path: the operand ring does not fit");
+    a.stages = stages;
+    a.wstages = 0;
+  }
+  const int stages = a.stages;
   a.scale = p.epi.scale; a.bias = p.epi.bias; a.alpha = p.epi.alpha; a.acc_small = p.epi.acc_small;
   a.status = ctx->d_status;
 
@@ -548,7 +643,8 @@ int igemm_nchw_gather_launch(plb_ctx* ctx, const NchwProblem& p) {
                           CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
     if (r != CUDA_SUCCESS) return fail(PLB_E_CUDA, "cuTensorMapEncodeTiled(filter) failed: %d", (int)r);
   }
-  const size_t smem = static_cast<size_t>(staging) + a.resident_bytes + static_cast<size_t>(stages) * stage_bytes + kCtrlBytes + 1024;
+  const size_t smem = static_cast<size_t>(staging) + a.resident_bytes + static_cast<size_t>(stages) * stage_bytes +
+                      static_cast<size_t>(a.wstages) * wtile + kCtrlBytes + 1024;
   GatherKernel kernel = pick_kernel(p.out_mode, p.epi.act);
   {
     std::lock_guard<std::mutex> lock(g_mutex);

@@ -1355,6 +1355,7 @@ TcSwitches tc_switches_from_env() {
   s.nchw = env_int("PLB_TC_NCHW", -1);
   s.dw_strip = env_int("PLB_DW_STRIP", -1);
   s.nchw_gather = env_int("PLB_TC_NCHW_GATHER", -1);
+  s.nchw_bres = env_int("PLB_TC_NCHW_BRES", -1);
   s.stem = env_int("PLB_STEM", -1);
   s.dwpw = env_int("PLB_DWPW", -1);
   s.dwpw_tw = env_int("PLB_DWPW_TW", -1);

@@ -29,6 +29,7 @@ struct TcSwitches {
   int pair = -1;          // PLB_TC_PAIR: two-SM tiles (cta_group::2) off (0) / forced wherever they fit (1)
   int nchw = -1;          // PLB_TC_NCHW: NCHW-native 1x1 kernel off (0) / forced wherever it fits (1)
   int nchw_gather = -1;   // PLB_TC_NCHW_GATHER=0: images whose pixel count is not a multiple of 16 are re-pitched / staged instead
+  int nchw_bres = -1;     // PLB_TC_NCHW_BRES=0: that kernel never keeps a pixel tile resident for all channel tiles
   int dw_strip = -1;      // PLB_DW_STRIP: depthwise 3x3 rows per strip (0 = the register-tiled kernel)
   int stem = -1;          // PLB_STEM=0: first layers always run as a staging pass + convolution
   int dwpw = -1;          // PLB_DWPW=0: depthwise + 1x1 pairs never run as one launch

@@ -489,6 +489,7 @@ bool nchw_native(const plb_conv* c, const int8_t* x, void* y, int batch, int mod
   p->x = x; p->w = c->w.as<int8_t>();
   p->batch = batch; p->cin = d.cin; p->cin_pad = c->cin_pad; p->cout = d.cout; p->hw = d.h * d.w;
   p->out_mode = mode; p->y = y;
+  p->bres_switch = c->sw.nchw_bres;
   if (p->hw % 16 != 0) {
     // rows TMA cannot address: gather warps fill the operand tiles (igemm_nchw_gather.cu), several small images per tile
     if (c->sw.nchw_gather != 0 && igemm_nchw_gather_supported(*p, nullptr)) {

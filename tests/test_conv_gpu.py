@@ -142,14 +142,18 @@ NCHW_1X1_CASES = [
     (1, 40, 5, 7, 24, 3),         # 35 pixels, ragged channels
     (7, 32, 1, 1, 16, 0),         # one pixel per image
 ]
-# more of those, for the kernel whose operand tiles are filled by gather warps
+# more of those; rows that are a multiple of 4 bytes take the kernel whose operand tiles are filled by gather warps
 NCHW_GATHER_CASES = [c for c in NCHW_1X1_CASES if (c[2] * c[3]) % 16] + [
-    (300, 64, 7, 7, 64, 1),       # four images per tile, more tiles than SMs, filter resident, duplicated accumulator rows
+    (300, 64, 6, 6, 64, 1),       # 36 pixels -> 48 columns, five images per tile, more tiles than SMs, filter resident,
+                                  # duplicated accumulator rows
     (37, 128, 14, 14, 160, 2),    # one image per tile (208 columns), ragged second channel tile
     (9, 96, 10, 10, 128, 1),      # 100 pixels -> 112 columns, two images per tile, odd image count
-    (3, 64, 17, 17, 96, 3),       # 289 pixels: more than a tile, byte-wise rows
-    (2, 160, 18, 18, 64, 1),      # 324 pixels: two tiles per image, word-wise rows
-    (170, 1024, 7, 7, 256, 1),    # streamed filter, long K
+    (3, 64, 17, 17, 96, 3),       # 289 pixels, odd rows: re-pitched
+    (2, 160, 18, 18, 64, 1),      # 324 pixels: two tiles per image
+    (170, 1024, 6, 6, 256, 1),    # streamed filter, long K, several stages of copies in flight
+    (5, 64, 6, 14, 96, 0),        # 84 pixels -> 96 columns, two images per tile, odd image count
+    (330, 128, 10, 10, 256, 1),   # more pixel tiles than SMs: several resident pixel tiles per CTA, chunks handed back
+                                  # only after the last channel-tile pass
 ]
 
 
@@ -166,18 +170,21 @@ def test_nchw_native_1x1(plb, ctx, case, monkeypatch):
 
 
 @pytest.mark.parametrize("case", NCHW_GATHER_CASES, ids=lambda c: "x".join(map(str, c[:5])))
-@pytest.mark.parametrize("gather", ["1", "0"])
+@pytest.mark.parametrize("gather", ["resident", "streamed", "0"])
 def test_nchw_images_tma_cannot_address(plb, ctx, case, gather, monkeypatch):
     """Images whose pixel count is not a multiple of 16: gather warps fill the operand tiles and the epilogue writes the
-    rows itself (default), or the rows are re-pitched around the TMA kernel (switch off); both bit-identical to the oracle."""
+    rows itself -- with a pixel tile kept in shared memory for all channel tiles ("resident", where it fits) or gathered
+    per channel tile ("streamed") -- or the rows are re-pitched around the TMA kernel ("0"); all bit-identical to the oracle."""
     monkeypatch.setenv("PLB_TC_NCHW", "1")
+    monkeypatch.setenv("PLB_TC_NCHW_BRES", "1" if gather == "resident" else "0")
+    gather = "0" if gather == "0" else "1"
     monkeypatch.setenv("PLB_TC_NCHW_GATHER", gather)
     n, cin, h, w, cout, act = case
     xq, in_s, wq, ws, bias = conv_case(hash(case) % 10000 + 1, n, cin, h, w, cout, 1)
     before, before_g = ctx.nchw_launch_count(), ctx.nchw_gather_launch_count()
     run_case(plb, ctx, xq, in_s, wq, ws, bias, act=act, alpha=6.0 if act == 2 else 0.1)
     assert ctx.nchw_launch_count() == before + 3
-    assert ctx.nchw_gather_launch_count() == before_g + (3 if gather == "1" else 0)
+    assert ctx.nchw_gather_launch_count() == before_g + (3 if gather == "1" and (h * w) % 4 == 0 else 0)
 
 
 def test_nchw_native_switch_off(plb, ctx, monkeypatch):
