@@ -1131,6 +1131,42 @@ __global__ void __launch_bounds__(kBlock)
   reinterpret_cast<uint4*>(y)[m * c16 + cq] = best;
 }
 
+// The same for the usual 3 x 3 window: the nine loads are issued together (the generic kernel's loops with a run-time
+// window serialise them, one memory latency each).
+__global__ void __launch_bounds__(kBlock)
+    maxpool3x3_nhwc_i8_v16_kernel(const int8_t* __restrict__ x, int8_t* __restrict__ y, int c16, int h, int w, int ho,
+                                  int wo, int stride, int pad, long total) {
+  pdl_sync_with_previous_kernel();
+  const long idx = static_cast<long>(blockIdx.x) * kBlock + threadIdx.x;
+  if (idx >= total) return;
+  const int cq = static_cast<int>(idx % c16);
+  const long m = idx / c16;
+  const int ow = static_cast<int>(m % wo);
+  const int oh = static_cast<int>((m / wo) % ho);
+  const long n = m / (static_cast<long>(wo) * ho);
+  const int ih0 = oh * stride - pad, iw0 = ow * stride - pad;
+  const uint4* base = reinterpret_cast<const uint4*>(x) + ((n * h + ih0) * w + iw0) * c16 + cq;
+  uint4 v[9];
+#pragma unroll
+  for (int r = 0; r < 3; ++r)
+#pragma unroll
+    for (int s = 0; s < 3; ++s) {
+      const bool inside = static_cast<unsigned>(ih0 + r) < static_cast<unsigned>(h) &&
+                          static_cast<unsigned>(iw0 + s) < static_cast<unsigned>(w);
+      v[r * 3 + s] = inside ? __ldg(base + (static_cast<long>(r) * w + s) * c16)
+                            : make_uint4(0x80808080u, 0x80808080u, 0x80808080u, 0x80808080u);
+    }
+  uint4 best = v[0];
+#pragma unroll
+  for (int i = 1; i < 9; ++i) {
+    best.x = __vmaxs4(best.x, v[i].x);
+    best.y = __vmaxs4(best.y, v[i].y);
+    best.z = __vmaxs4(best.z, v[i].z);
+    best.w = __vmaxs4(best.w, v[i].w);
+  }
+  reinterpret_cast<uint4*>(y)[m * c16 + cq] = best;
+}
+
 // x [n,hw,c] -> y [n,c] = (sum over hw in ascending order) / hw; optional calib to int8.
 __global__ void global_avgpool_kernel(const float* __restrict__ x, float* __restrict__ y,
                                       int8_t* __restrict__ q, int hw, int c, float inv, long total) {
@@ -1572,8 +1608,12 @@ int maxpool_nhwc_i8_launch(plb_ctx* ctx, const int8_t* x, int8_t* y, int n, int 
   if (c % 16 == 0 && (reinterpret_cast<uintptr_t>(x) & 15) == 0 && (reinterpret_cast<uintptr_t>(y) & 15) == 0) {
     const long total16 = static_cast<long>(n) * ho * wo * (c / 16);
     if (total16 == 0) return PLB_OK;
-    PLB_CUDA(launch_kernel(maxpool_nhwc_i8_v16_kernel, dim3(blocks_for(total16)), dim3(kBlock), 0, ctx->stream,
-                           x, y, c / 16, h, w, ho, wo, k, stride, pad, total16));
+    if (k == 3)
+      PLB_CUDA(launch_kernel(maxpool3x3_nhwc_i8_v16_kernel, dim3(blocks_for(total16)), dim3(kBlock), 0, ctx->stream, x, y,
+                             c / 16, h, w, ho, wo, stride, pad, total16));
+    else
+      PLB_CUDA(launch_kernel(maxpool_nhwc_i8_v16_kernel, dim3(blocks_for(total16)), dim3(kBlock), 0, ctx->stream,
+                             x, y, c / 16, h, w, ho, wo, k, stride, pad, total16));
     ctx->launches++;
     return PLB_OK;
   }

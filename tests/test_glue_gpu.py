@@ -50,6 +50,10 @@ def test_pooling(plb, ctx):
     x = rng.integers(-128, 128, (2, 64, 23, 23), dtype=np.int8)
     y = ctx.maxpool_nhwc_i8(dev(x.transpose(0, 2, 3, 1)), 3, 2, 1).cpu().numpy()
     assert np.array_equal(y.transpose(0, 3, 1, 2), O.maxpool_i8(x, 3, 2, 1))
+    # other windows (generic kernel), stride 1, and a channel count that is not a multiple of 16
+    for xs, k, s, p in ((x, 2, 2, 0), (x, 3, 1, 1), (x[:, :20], 3, 2, 1), (x, 5, 2, 2)):
+        y = ctx.maxpool_nhwc_i8(dev(xs.transpose(0, 2, 3, 1)), k, s, p).cpu().numpy()
+        assert np.array_equal(y.transpose(0, 3, 1, 2), O.maxpool_i8(np.ascontiguousarray(xs), k, s, p))
     f = rng.standard_normal((3, 7, 7, 96)).astype(np.float32)
     s = np.zeros((3, 96), dtype=np.float32)
     for p in range(49):
