@@ -371,6 +371,8 @@ def layer_table(plb, ctx):
     rows.append(L.conv(64, 56, 64, 3, 1, 1, 128, "i8"))                  # the same layer at the network's batch
     for cin, hw in ((128, 28), (256, 14), (512, 7)):
         rows.append(L.conv(cin, hw, cin, 3, 1, 1, 128, "i8"))
+    for cin, hw in ((64, 56), (128, 28), (256, 14), (512, 7)):
+        rows.append(L.conv(cin, hw, cin, 3, 1, 1, 1024, "i8"))           # the same layers in launches of 1024 images
     for m, k, n in LB.FC_SWEEP:
         for out in ("f32", "i8"):
             rows.append(L.fc(m, k, n, out, int8_measured_tops=vt))
@@ -665,7 +667,7 @@ def main():
                 ctx.sync()
             del g_full, g_body, g_tc, g_3x3, runner
             torch.cuda.empty_cache()
-            others = [("mobilenet_v1", 32, None), ("mobilenet_v1", 256, None), ("resnet50", 1024, 128)]
+            others = [("mobilenet_v1", 32, None), ("mobilenet_v1", 256, None), ("resnet50", 1024, None)]
             if args.net != "resnet50":
                 others = [("resnet50", 128, None)]
             for net, b, mb in others:

@@ -533,7 +533,7 @@ struct Tiling {
 };
 
 // Estimated cost of a tiling, in warp instructions on the busiest SM (both roles share the SM's issue slots).
-double tiling_cost(const DwpwProblem& p, const Tiling& t, int sm_count) {
+double tiling_cost(const DwpwProblem& p, const Tiling& t) {
   const int nb_max = (t.total_items + t.grid - 1) / t.grid;
   const int rounds = (nb_max + t.groups - 1) / t.groups;
   const int T = t.seg_rows / t.th;
@@ -544,7 +544,6 @@ double tiling_cost(const DwpwProblem& p, const Tiling& t, int sm_count) {
   const double epi_total = static_cast<double>(nb_max) * T * 128.0 * p.cout * 4.5 / 32.0;
   // a round cannot finish before its slowest group: a lone warp issues at most about every other cycle
   const double critical = rounds * per_item_thread * 2.0;
-  (void)sm_count;
   return std::max((dw_total + epi_total) / 4.0 / 0.8, critical);
 }
 
@@ -581,7 +580,7 @@ int plan_tiling(const plb_ctx* ctx, const DwpwProblem& p, Tiling* out) {
       if (items > 0x3fffffff) continue;
       t.total_items = static_cast<int>(items);
       t.grid = static_cast<int>(std::min<long>(items, ctx->sm_count));
-      const double cost = tiling_cost(p, t, ctx->sm_count);
+      const double cost = tiling_cost(p, t);
       if (!have || cost < best) {
         best = cost;
         *out = t;
@@ -670,9 +669,17 @@ int dwpw_fused_launch(plb_ctx* ctx, const DwpwProblem& p) {
   }
   DwpwKernel kernel = p.stride == 1 ? pick_pitch<1>(p.c, p.pw_epi.act) : pick_pitch<2>(p.c, p.pw_epi.act);
   {
+    // once per (kernel, device)
     static std::mutex attr_mutex;
+    static std::vector<std::pair<const void*, int>> configured;
     std::lock_guard<std::mutex> lock(attr_mutex);
-    PLB_CUDA(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024));
+    const std::pair<const void*, int> key(reinterpret_cast<const void*>(kernel), ctx->device);
+    bool found = false;
+    for (auto& k : configured) found = found || k == key;
+    if (!found) {
+      PLB_CUDA(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024));
+      configured.push_back(key);
+    }
   }
   PLB_CUDA(launch_kernel(kernel, dim3(t.grid), dim3(kThreads), smem, ctx->stream, tmB, tmOut, a));
   ++ctx->launches;

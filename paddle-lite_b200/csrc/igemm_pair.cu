@@ -451,8 +451,11 @@ bool igemm_pair_wanted(const plb_ctx* ctx, const IgemmProblem& p) {
   // one-SM kernel is bound by shared-memory bandwidth (4096^3: 51 us against 56 us, 2.69 POP/s).  Convolutions
   // fetched tap by tap stay with the one-SM kernel: they are bound by the number of TMA instructions per K step,
   // which pairing does not change (3x3 128 -> 128 on 28 x 28: 20 us against 18 us).
+  // Large launches of convolutions with 256-wide channel tiles gain too once every pair has several tiles (3x3 256 -> 256
+  // on 14 x 14: 25.9 us against 26.2 at 256 images, 46 against 49 at 512, 86 against 97 at 1024 = 0.61 of the datasheet peak).
   const long tiles = static_cast<long>((p.m_total + 255) / 256) * ((p.cout + bn - 1) / bn);
-  return !p.im2col && p.cin_pad >= 2048 && bn == 256 && tiles >= ctx->sm_count / 2;
+  if (p.im2col) return bn == 256 && tiles >= ctx->sm_count;
+  return p.cin_pad >= 2048 && bn == 256 && tiles >= ctx->sm_count / 2;
 }
 
 int igemm_pair_launch(plb_ctx* ctx, const IgemmProblem& p) {

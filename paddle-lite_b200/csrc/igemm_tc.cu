@@ -1446,8 +1446,8 @@ int igemm_tc_plan(plb_ctx* ctx, const IgemmProblem& p, const TcSwitches& sw_, Ig
   // and loses to wave quantisation (196 tiles on 148 SMs: 10.6 us against 9.9 us at 128 columns).
   if (!dual && p.out_mode == OUT_ADD_RELU && p.residual != nullptr && cout16 >= 512 && bn > 64)
     bn = 64;
-  else if (!dual && cout16 == 256 && bn == 256)
-    bn = 128;
+  else if (!dual && cout16 == 256 && bn == 256 && tiles_m <= 2 * ctx->sm_count)
+    bn = 128;  // (with more tiles the wide tile wins again: 3x3 256 -> 256 on 14 x 14 at 512 images, 49 us against 57)
   bn = sw_or(sw_.bn, bn);
   if (dual && bn > 128) bn = 128;  // also after an override: two accumulators per tile must fit the 512 TMEM columns
   if (bn > cout16) bn = cout16;

@@ -494,9 +494,17 @@ int stem_tc_launch(plb_ctx* ctx, const StemProblem& p) {
   }
   StemKernel kernel = pick_kernel(p.epi.act, s.nwin);
   {
+    // once per (kernel, device)
     static std::mutex attr_mutex;
+    static std::vector<std::pair<const void*, int>> configured;
     std::lock_guard<std::mutex> lock(attr_mutex);
-    PLB_CUDA(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024));
+    const std::pair<const void*, int> key(reinterpret_cast<const void*>(kernel), ctx->device);
+    bool found = false;
+    for (auto& k : configured) found = found || k == key;
+    if (!found) {
+      PLB_CUDA(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024));
+      configured.push_back(key);
+    }
   }
   const int grid = static_cast<int>(std::min<long>(items, ctx->sm_count));
   PLB_CUDA(launch_kernel(kernel, dim3(grid), dim3(kThreads), s.smem, ctx->stream, tmB, tmOut, a));
