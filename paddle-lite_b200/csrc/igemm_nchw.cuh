@@ -20,7 +20,7 @@ bool igemm_nchw_supported(const NchwProblem& p, std::string* why);
 int igemm_nchw_launch(plb_ctx* ctx, const NchwProblem& p);
 // The same on images whose rows TMA cannot address (pixel counts that are not a multiple of 16; igemm_nchw_gather.cu):
 // dense tensors (no pitch), 4-byte aligned.
-bool igemm_nchw_gather_supported(const NchwProblem& p, std::string* why);
+bool igemm_nchw_gather_supported(const plb_ctx* ctx, const NchwProblem& p, std::string* why);
 int igemm_nchw_gather_launch(plb_ctx* ctx, const NchwProblem& p);
 
 }  // namespace plb

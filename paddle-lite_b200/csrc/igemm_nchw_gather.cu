@@ -1,9 +1,10 @@
-// 1x1 convolution on NCHW tensors whose images TMA cannot address (pixel counts that are a multiple of 4 but not of 16:
-// 14 x 14, 10 x 10, 18 x 18, ...), without any re-pitching pass.  Same orientation and arithmetic as igemm_nchw.cu (M = output channels,
+// 1x1 convolution on NCHW tensors whose images TMA cannot address (pixel counts that are not a multiple of 16: 14 x 14,
+// 7 x 7, 10 x 10, ...), without any re-pitching pass.  Same orientation and arithmetic as igemm_nchw.cu (M = output channels,
 // N = pixels, B = X[n] = [cin][hw] as an MN-major operand, exact int32 accumulators, the same requantiser); what differs
 // is how the pixels get in and out:
-//   * 8 gather warps copy X rows with 4-byte asynchronous copies (cp.async, several stages in flight) into the
-//     128-byte-swizzled MN-major operand tile that TMA would have written; a tile's columns are the pixels of G whole images, each padded
+//   * 8 gather warps copy X rows into the 128-byte-swizzled MN-major operand tile that TMA would have written: with
+//     4-byte asynchronous copies (cp.async, several stages in flight) where the rows are a multiple of 4 bytes long,
+//     otherwise with aligned 4-byte loads that are funnel-shifted into place in registers; a tile's columns are the pixels of G whole images, each padded
 //     to P = hw rounded up to 16 columns (G = 256 / P), or 256-pixel runs of one larger image;
 //   * the epilogue warps requantise 32 columns at a time into a small staging tile and write it out row by row, so that
 //     the lanes of a warp store consecutive pixels of ONE output row.
@@ -54,6 +55,7 @@ struct GatherArgs {
                           // runs the channel tiles over it with the filter streamed through its own ring (wstages)
   int wstages, num_ptiles;
   int dup;
+  int bytewise;           // hw % 4 != 0: image rows start at any byte; they are fetched as aligned words and funnel-shifted
   const float* scale;
   const float* bias;
   float alpha;
@@ -74,6 +76,9 @@ __device__ __forceinline__ void cp_async_wait_pending(int n) {
     case 3: asm volatile("cp.async.wait_group 3;" ::: "memory"); break;
     default: asm volatile("cp.async.wait_group 4;" ::: "memory"); break;
   }
+}
+__device__ __forceinline__ void sts32(uint32_t addr, uint32_t v) {
+  asm volatile("st.shared.b32 [%0], %1;" ::"r"(addr), "r"(v) : "memory");
 }
 __device__ __forceinline__ uint32_t lds32(uint32_t addr) {
   uint32_t v;
@@ -332,6 +337,8 @@ __global__ void __launch_bounds__(kThreads, 1)
       long goff[kMaxIter];
       uint32_t soff[kMaxIter];
       bool valid[kMaxIter], used[kMaxIter];
+      int nbytes[kMaxIter];     // bytewise: bytes of the word that lie inside the image (0 .. 4)
+      bool next_has[kMaxIter];  // bytewise: the next lane holds the following word of the same image row
 #pragma unroll
       for (int it = 0; it < kMaxIter; ++it) {
         const int w = lane + 32 * it;
@@ -343,6 +350,8 @@ __global__ void __launch_bounds__(kThreads, 1)
         }
         used[it] = w < words;
         valid[it] = used[it] && p < a.hw && img + g < a.batch;  // hw % 4 == 0: a word is inside the image or outside
+        nbytes[it] = valid[it] ? (a.hw - p < 4 ? a.hw - p : 4) : 0;
+        next_has[it] = lane < 31 && p + 4 < a.hw && (p + 4 < a.image_cols || !(a.group_images > 1 || a.tiles_p == 1));
         goff[it] = valid[it] ? static_cast<long>(img + g) * plane + p : 0;
         const int colb = col & 127;
         soff[it] = static_cast<uint32_t>((col >> 7) * (a.kc * 128) + (((colb >> 4) ^ gw) << 4) + (colb & 15));
@@ -358,6 +367,54 @@ __global__ void __launch_bounds__(kThreads, 1)
           if (!ok) break;
         }
         const uint32_t dst = smem_base + s * stage_bytes + stage_a;
+        if (a.bytewise) {
+          // Rows at any byte alignment: a lane loads the aligned word that holds the first byte of its word, takes the
+          // following aligned word from the next lane (or loads it itself where the next lane holds something else), and
+          // funnel-shifts.  No aligned word is read that does not contain a byte of the image.  Four rows per batch.
+          for (int c0 = gw; c0 < a.kc; c0 += 32) {
+            uint32_t lo[4][kMaxIter], hi[4][kMaxIter];
+#pragma unroll
+            for (int r = 0; r < 4; ++r) {
+              const int cc = c0 + 8 * r;
+              const int ch = ks * a.kc + cc;
+              const bool row_ok = ch < a.cin;
+              const int8_t* src = a.x + static_cast<long>(row_ok ? ch : 0) * a.hw;
+#pragma unroll
+              for (int it = 0; it < kMaxIter; ++it) {
+                const uintptr_t addr = reinterpret_cast<uintptr_t>(src + goff[it]);
+                const uint32_t shift = static_cast<uint32_t>(addr & 3u);
+                const uint32_t* wp = reinterpret_cast<const uint32_t*>(addr & ~static_cast<uintptr_t>(3));
+                const bool take = row_ok && nbytes[it] > 0;
+                lo[r][it] = take ? __ldg(wp) : 0u;
+                const bool need_hi = take && shift + static_cast<uint32_t>(nbytes[it]) > 4u;
+                hi[r][it] = (need_hi && !next_has[it]) ? __ldg(wp + 1) : 0u;
+              }
+            }
+#pragma unroll
+            for (int r = 0; r < 4; ++r) {
+              const int cc = c0 + 8 * r;
+              const int ch = ks * a.kc + cc;
+              const int8_t* src = a.x + static_cast<long>(ch < a.cin ? ch : 0) * a.hw;
+#pragma unroll
+              for (int it = 0; it < kMaxIter; ++it) {
+                const uint32_t from_next = __shfl_down_sync(0xffffffffu, lo[r][it], 1);
+                const uint32_t shift = static_cast<uint32_t>(reinterpret_cast<uintptr_t>(src + goff[it]) & 3u);
+                const uint32_t h = next_has[it] ? from_next : hi[r][it];
+                const uint32_t val = __funnelshift_r(lo[r][it], h, shift * 8u);
+                if (cc < a.kc && used[it]) sts32(dst + static_cast<uint32_t>(cc * 128) + soff[it], val);
+              }
+            }
+          }
+          fence_proxy_async_smem();
+          __syncwarp();
+          if (lane == 0) mbar_arrive(smem_u32(&full_bar[s]));
+          if (++s_done == a.stages) s_done = 0;
+          if (++s == a.stages) {
+            s = 0;
+            empty_parity ^= 1;
+          }
+          continue;
+        }
         for (int cc = gw; cc < a.kc; cc += 8) {
           const int ch = ks * a.kc + cc;
           const bool row_ok = ch < a.cin;
@@ -439,7 +496,9 @@ __global__ void __launch_bounds__(kThreads, 1)
             g = col / a.image_cols;
             p = col - g * a.image_cols;
           }
-          const int nv = (col < a.bn && p < a.hw && img + g < a.batch) ? 4 : 0;
+          int nv = a.hw - p;
+          nv = nv < 0 ? 0 : (nv > 4 ? 4 : nv);
+          if (col >= a.bn || img + g >= a.batch) nv = 0;
           int8_t* ybase = static_cast<int8_t*>(a.y) + (static_cast<long>(img + g) * a.cout) * a.hw + p;
 #pragma unroll
           for (int pass = 0; pass < 8; ++pass) {
@@ -448,7 +507,13 @@ __global__ void __launch_bounds__(kThreads, 1)
             const int co = row0 + rr;
             if (co < a.cout && nv > 0) {
               int8_t* dstp = ybase + static_cast<long>(co) * a.hw;
-              *reinterpret_cast<uint32_t*>(dstp) = word;  // hw % 4 == 0: whole words, 4-byte aligned
+              if (!a.bytewise) {
+                *reinterpret_cast<uint32_t*>(dstp) = word;  // hw % 4 == 0: whole words, 4-byte aligned
+              } else {
+#pragma unroll
+                for (int b = 0; b < 4; ++b)
+                  if (b < nv) dstp[b] = static_cast<int8_t>(word >> (8 * b));
+              }
             }
           }
         } else {
@@ -536,7 +601,16 @@ int load_encoder() {
 
 }  // namespace
 
-bool igemm_nchw_gather_supported(const NchwProblem& p, std::string* why) {
+namespace {
+
+struct GatherPlan {
+  GatherArgs a;
+  long grid;
+  size_t smem;
+};
+
+// Tile shapes, tile order and shared-memory layout of a problem; false (with the reason) when the kernel cannot take it.
+bool plan_gather(const plb_ctx* ctx, const NchwProblem& p, GatherPlan* plan, std::string* why) {
   auto no = [&](const char* msg) {
     if (why) *why = msg;
     return false;
@@ -545,22 +619,10 @@ bool igemm_nchw_gather_supported(const NchwProblem& p, std::string* why) {
   if (p.x_pitch || p.y_pitch) return no("dense NCHW tensors only");
   if (p.cin_pad % 32 != 0 || p.cin > p.cin_pad) return no("filter rows must be padded to a multiple of 32 bytes");
   if (p.batch <= 0 || p.cout <= 0 || p.cin <= 0 || p.hw <= 0) return no("empty problem");
-  if (p.hw % 4 != 0) return no("image rows must be a multiple of 4 bytes (4-byte asynchronous copies)");
   if (reinterpret_cast<uintptr_t>(p.w) & 15) return no("the filter must be 16-byte aligned");
   if ((reinterpret_cast<uintptr_t>(p.x) & 3) || (reinterpret_cast<uintptr_t>(p.y) & 3)) return no("tensors must be 4-byte aligned");
   if (static_cast<long>(p.batch) * p.cin * p.hw > 0x7fffffffL * 16) return no("tensor too large");
-  return true;
-}
-
-int igemm_nchw_gather_launch(plb_ctx* ctx, const NchwProblem& p) {
-  std::string why;
-  if (!igemm_nchw_gather_supported(p, &why)) return fail(PLB_E_UNSUPPORTED, "NCHW gather path: %s", why.c_str());
-  {
-    std::lock_guard<std::mutex> lock(g_mutex);
-    int rc = load_encoder();
-    if (rc) return rc;
-  }
-  GatherArgs a;
+  GatherArgs& a = plan->a;
   memset(&a, 0, sizeof(a));
   a.x = p.x; a.y = p.y;
   a.batch = p.batch; a.cin = p.cin; a.cout = p.cout; a.hw = p.hw;
@@ -568,47 +630,62 @@ int igemm_nchw_gather_launch(plb_ctx* ctx, const NchwProblem& p) {
   a.ksteps = p.cin_pad / a.kc;
   a.tiles_m = (p.cout + kTileCout - 1) / kTileCout;
   a.dup = p.cout <= 64;
+  a.bytewise = p.hw % 4 != 0;
   const int staging = (kStagingBytes + 1023) & ~1023;
   const int budget = 225 * 1024 - staging - kCtrlBytes;
   const int wtile = kTileCout * a.kc;
   // Pixel-resident order (a pixel tile is gathered once and all channel tiles run over it) needs every K chunk of the
   // pixel tile plus a ring of at least three filter tiles in shared memory; it pays as soon as there are two channel tiles.
   auto bres_fits = [&](int bn) { return a.ksteps <= kMaxStages && a.ksteps * a.kc * 128 * ((bn + 127) / 128) + 3 * wtile <= budget; };
+  const bool want_bres = a.tiles_m >= 2 && p.bres_switch != 0;
   long groups;
+  bool bres = false;
   if (p.hw <= 256) {
     // whole images per tile, each padded to a multiple of 16 columns
     a.image_cols = (p.hw + 15) / 16 * 16;
     a.group_images = 256 / a.image_cols;
     // prefer a tile that fits the pixel-resident order (long K: 128 columns instead of 256)
-    if (a.tiles_m >= 2 && !bres_fits(a.group_images * a.image_cols) && a.image_cols <= 128 && bres_fits(128))
+    if (want_bres && !bres_fits(a.group_images * a.image_cols) && a.image_cols <= 128 && bres_fits(128))
       a.group_images = 128 / a.image_cols;
-    // small grids: fewer images per tile so that every SM gets one
-    while (a.group_images > 1 && static_cast<long>((p.batch + a.group_images - 1) / a.group_images) * a.tiles_m < ctx->sm_count)
+    bres = want_bres && bres_fits(a.group_images * a.image_cols);
+    // small grids: fewer images per tile so that every SM gets a tile (a pixel tile in the pixel-resident order), as
+    // long as a tile keeps at least 128 columns
+    auto work_items = [&](int g) {
+      const long pt = (p.batch + g - 1) / g;
+      return bres ? pt : pt * a.tiles_m;
+    };
+    while (a.group_images > 1 && work_items(a.group_images) < ctx->sm_count &&
+           ((a.group_images / 2) * a.image_cols >= 128 || work_items(a.group_images) < ctx->sm_count / 2))
       a.group_images /= 2;
     a.bn = a.group_images * a.image_cols;
     a.tiles_p = 1;
     groups = (p.batch + a.group_images - 1) / a.group_images;
   } else {
     a.group_images = 1;
-    a.bn = (a.tiles_m >= 2 && !bres_fits(256) && bres_fits(128)) ? 128 : 256;
+    a.bn = (want_bres && !bres_fits(256) && bres_fits(128)) ? 128 : 256;
     a.image_cols = a.bn;
     a.tiles_p = (p.hw + a.bn - 1) / a.bn;
     groups = p.batch;
+    bres = want_bres && bres_fits(a.bn);
   }
   a.acc_stride = 32;
   while (a.acc_stride < a.bn) a.acc_stride <<= 1;
   const long ptiles = groups * a.tiles_p;
   const long tiles = ptiles * a.tiles_m;
-  if (tiles > 0x7fffffffL) return fail(PLB_E_UNSUPPORTED, "too many tiles");
+  if (tiles > 0x7fffffffL) return no("too many tiles");
   a.num_tiles = static_cast<int>(tiles);
   a.num_ptiles = static_cast<int>(ptiles);
   const int halves = (a.bn + 127) / 128;
   const int stage_b = a.kc * 128 * halves;
-  a.bres = a.tiles_m >= 2 && bres_fits(a.bn) && (p.bres_switch == 1 || (p.bres_switch != 0 && ptiles >= ctx->sm_count / 2));
-  long grid_l;
+  a.bres = bres && (p.bres_switch == 1 || ptiles >= ctx->sm_count / 2);
+  // Where this kernel is the better choice (measured, batch 256): in the pixel-resident order (512 -> 512 on 14 x 14:
+  // 40 us against 48 re-pitched; 1024 -> 1024 on 7 x 7: 49 against 58 staged); gathered per channel tile only with
+  // 4-byte outputs and 4-byte-aligned rows (66 against 152).  An explicit switch (tests) overrides.
+  if (p.bres_switch != 0 && p.bres_switch != 1 && !a.bres && (a.bytewise || p.out_mode == OUT_I8))
+    return no("not the better path for this shape");
   int stage_bytes;
   if (a.bres) {
-    grid_l = ptiles < ctx->sm_count ? ptiles : ctx->sm_count;
+    plan->grid = ptiles < ctx->sm_count ? ptiles : ctx->sm_count;
     a.resident_w = 0;
     a.resident_bytes = 0;
     stage_bytes = stage_b;
@@ -616,17 +693,40 @@ int igemm_nchw_gather_launch(plb_ctx* ctx, const NchwProblem& p) {
     a.wstages = std::min(kMaxStages, (budget - a.ksteps * stage_b) / wtile);
   } else {
     const int resident_bytes = a.ksteps * wtile;
-    grid_l = tiles < ctx->sm_count ? tiles : ctx->sm_count;
-    a.resident_w = grid_l % a.tiles_m == 0 && resident_bytes <= kMaxResidentW && tiles > grid_l;
+    plan->grid = tiles < ctx->sm_count ? tiles : ctx->sm_count;
+    a.resident_w = plan->grid % a.tiles_m == 0 && resident_bytes <= kMaxResidentW && tiles > plan->grid;
     a.resident_bytes = a.resident_w ? resident_bytes : 0;
     stage_bytes = (a.resident_w ? 0 : wtile) + stage_b;
     int stages = (budget - a.resident_bytes) / stage_bytes;
     if (stages > kMaxStages) stages = kMaxStages;
-    if (stages < 2) return fail(PLB_E_UNSUPPORTED, "NCHW gather path: the operand ring does not fit");
+    if (stages < 2) return no("the operand ring does not fit");
     a.stages = stages;
     a.wstages = 0;
   }
-  const int stages = a.stages;
+  plan->smem = static_cast<size_t>(staging) + a.resident_bytes + static_cast<size_t>(a.stages) * stage_bytes +
+               static_cast<size_t>(a.wstages) * wtile + kCtrlBytes + 1024;
+  return true;
+}
+
+}  // namespace
+
+bool igemm_nchw_gather_supported(const plb_ctx* ctx, const NchwProblem& p, std::string* why) {
+  GatherPlan plan;
+  return plan_gather(ctx, p, &plan, why);
+}
+
+int igemm_nchw_gather_launch(plb_ctx* ctx, const NchwProblem& p) {
+  std::string why;
+  GatherPlan plan;
+  if (!plan_gather(ctx, p, &plan, &why)) return fail(PLB_E_UNSUPPORTED, "NCHW gather path: %s", why.c_str());
+  {
+    std::lock_guard<std::mutex> lock(g_mutex);
+    int rc = load_encoder();
+    if (rc) return rc;
+  }
+  GatherArgs& a = plan.a;
+  const long grid_l = plan.grid;
+  const size_t smem = plan.smem;
   a.scale = p.epi.scale; a.bias = p.epi.bias; a.alpha = p.epi.alpha; a.acc_small = p.epi.acc_small;
   a.status = ctx->d_status;
 
@@ -643,8 +743,6 @@ int igemm_nchw_gather_launch(plb_ctx* ctx, const NchwProblem& p) {
                           CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
     if (r != CUDA_SUCCESS) return fail(PLB_E_CUDA, "cuTensorMapEncodeTiled(filter) failed: %d", (int)r);
   }
-  const size_t smem = static_cast<size_t>(staging) + a.resident_bytes + static_cast<size_t>(stages) * stage_bytes +
-                      static_cast<size_t>(a.wstages) * wtile + kCtrlBytes + 1024;
   GatherKernel kernel = pick_kernel(p.out_mode, p.epi.act);
   {
     std::lock_guard<std::mutex> lock(g_mutex);

@@ -492,7 +492,7 @@ bool nchw_native(const plb_conv* c, const int8_t* x, void* y, int batch, int mod
   p->bres_switch = c->sw.nchw_bres;
   if (p->hw % 16 != 0) {
     // rows TMA cannot address: gather warps fill the operand tiles (igemm_nchw_gather.cu), several small images per tile
-    if (c->sw.nchw_gather != 0 && igemm_nchw_gather_supported(*p, nullptr)) {
+    if (c->sw.nchw_gather != 0 && igemm_nchw_gather_supported(c->ctx, *p, nullptr)) {
       p->x_pitch = -1;  // marks the gather kernel for the caller
       return true;
     }
