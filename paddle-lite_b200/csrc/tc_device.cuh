@@ -11,6 +11,10 @@ constexpr uint32_t kWaitLimit = PLB_TC_TEST_WAIT_LIMIT;  // test build: waits gi
 #else
 constexpr uint32_t kWaitLimit = 1u << 22;      // polls before a wait is declared lost
 #endif
+#ifndef PLB_POLL_SPIN
+#define PLB_POLL_SPIN 8
+#endif
+constexpr uint32_t kPollSpin = PLB_POLL_SPIN;  // polls in a row before a waiting warp starts to sleep between polls
 constexpr uint32_t kDrainLimit = 1u << 12;     // polls per barrier while a CTA that gave up waits for its copies in flight
 
 // ---------------------------------------------------------------- PTX wrappers
@@ -43,7 +47,7 @@ __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatil
                                           int* status, int code) {
   for (uint32_t it = 0; it < kWaitLimit; ++it) {
     if (mbar_try_wait(bar, parity)) return true;
-    if (it > 64) {
+    if (it > kPollSpin) {
       __nanosleep(32);
       if ((it & 255u) == 0 && *abort_flag) return false;
     }
