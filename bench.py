@@ -95,6 +95,10 @@ class ClockSampler:
             return
         self.thread = threading.Thread(target=self._poll, daemon=True)
         self.thread.start()
+        # the first NVML reads of a process are slow (library and driver set-up): let them happen before anything is timed
+        t0 = time.perf_counter()
+        while len(self.samples) < 3 and self.err is None and time.perf_counter() - t0 < 1.0:
+            time.sleep(0.005)
 
     def _poll(self):
         nv = self.nv
