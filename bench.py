@@ -536,6 +536,9 @@ def main():
         # ---- device-resident throughput
         sampler = ClockSampler(_nvml_index(local_rank))
         sampler.start()
+        for _ in range(5):  # settle a fresh process (first replays of a new graph, clocks) before the warm-up proper
+            g_full.replay()
+        torch.cuda.synchronize()
         for _ in range(warmup):
             g_full.replay()
         barrier()
