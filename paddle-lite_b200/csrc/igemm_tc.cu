@@ -1353,6 +1353,7 @@ TcSwitches tc_switches_from_env() {
   s.fast_window = env_int("PLB_TC_FAST_WINDOW", 1);
   s.pair = env_int("PLB_TC_PAIR", -1);
   s.nchw = env_int("PLB_TC_NCHW", -1);
+  s.res_prefetch_tiles = env_int("PLB_TC_RES_PREFETCH_TILES", -1);
   s.dw_strip = env_int("PLB_DW_STRIP", -1);
   s.nchw_gather = env_int("PLB_TC_NCHW_GATHER", -1);
   s.nchw_bres = env_int("PLB_TC_NCHW_BRES", -1);
@@ -1468,9 +1469,14 @@ int igemm_tc_plan(plb_ctx* ctx, const IgemmProblem& p, const TcSwitches& sw_, Ig
   } else if (!aligned16(p.y)) {
     staged = false;
   }
-  // Fetching the residual one chunk ahead pays when a CTA has only a few tiles (latency bound);
-  // long runs are bandwidth bound and do better with the wider int8 stores of the plain path.
-  const bool short_run = static_cast<long>(tiles_m) * ((p.cout + bn - 1) / bn) <= 3L * ctx->sm_count;
+  // The residual tile is fetched one chunk ahead of its use.  Measured inside the network (ResNet-50, 128 images, graph
+  // replays on one box): 1.799 ms per step with the prefetch in all twelve residual convolutions, 1.842 with it only in
+  // the launches of up to 12 tiles per SM, 1.848 with up to 3 (the earlier rule, taken from single-layer loops, in which
+  // the residual tensor of the previous iteration is still in L2 and the prefetch measures slower).
+  // In launches of 1024 images (170 - 340 tiles per SM) it costs 2 % (80.9k against 82.6k images/s), at 256 images it is
+  // neutral: the limit is 50 tiles per SM (PLB_TC_RES_PREFETCH_TILES).
+  const bool short_run = static_cast<long>(tiles_m) * ((p.cout + bn - 1) / bn) <=
+                         static_cast<long>(sw_or(sw_.res_prefetch_tiles, 50)) * ctx->sm_count;
   a.res_prefetch = staged && p.out_mode == OUT_ADD_RELU && p.residual != nullptr && !p.im2col &&
                    sw_or(sw_.res_prefetch, short_run ? 1 : 0) != 0;
   a.staging_w_bytes = staged && want_w ? kEpilogueWarps * (a.res_prefetch ? 8192 : 4096) : 0;

@@ -22,6 +22,7 @@ struct TcSwitches {
   int acc_bufs = -1;      // PLB_TC_ACC_BUFS: accumulator buffers in tensor memory (2, 4, 8)
   int resident = 1;       // PLB_TC_RESIDENT=0: never keep the filter in shared memory
   int staged = 1;         // PLB_TC_STAGED=0: epilogue with direct global accesses
+  int res_prefetch_tiles = -1;  // PLB_TC_RES_PREFETCH_TILES: ... by default for launches of up to this many tiles per SM
   int res_prefetch = -1;  // PLB_TC_RES_PREFETCH: residual tile fetched one chunk ahead
   int acc_small = 1;      // PLB_TC_ACC_SMALL=0: int -> float through the conversion pipe always
   int sb_smem = 1;        // PLB_TC_SB_SMEM=0: scale / bias tables stay in global memory
