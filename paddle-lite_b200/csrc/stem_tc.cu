@@ -74,9 +74,14 @@ __device__ __forceinline__ uint32_t lds32(uint32_t addr) {
 }
 __device__ __forceinline__ void bulk_wait_read_1() { asm volatile("cp.async.bulk.wait_group.read 1;" ::: "memory"); }
 
-// calib of the reference: sat(rne(max(x / scale, -127))); rounding by adding 1.5 * 2^23, result in the low byte
-__device__ __forceinline__ uint32_t calib_bits(float v, float inv) {
-  return __float_as_uint(fminf(fmaxf(v * inv, -127.f), 127.f) + 12582912.f);
+// calib of the reference: sat(rne(max(x / scale, -127))); rounding by adding 1.5 * 2^23, result in the low byte.
+// Two values per multiply and per add (f32x2 forms, IEEE per lane: the same bits as the scalar sequence).
+__device__ __forceinline__ float clamp127(float v) { return fminf(fmaxf(v, -127.f), 127.f); }
+__device__ __forceinline__ void calib_bits2(float x, float y, float2 inv2, uint32_t& bx, uint32_t& by) {
+  const float2 p = __fmul2_rn(make_float2(x, y), inv2);
+  const float2 r = __fadd2_rn(make_float2(clamp127(p.x), clamp127(p.y)), make_float2(12582912.f, 12582912.f));
+  bx = __float_as_uint(r.x);
+  by = __float_as_uint(r.y);
 }
 
 template <int ACT, int NWIN>
@@ -141,7 +146,7 @@ __global__ void __launch_bounds__(kThreads, 1)
     const int w4 = a.w >> 2;
     const long plane = static_cast<long>(a.h) * a.w;
     const int total_units = a.rows_in * w4;
-    const float inv = a.inv_scale;
+    const float2 inv2 = make_float2(a.inv_scale, a.inv_scale);
     for (int k = 0; k < nb; ++k) {
       const int item = static_cast<int>(blockIdx.x) + k * static_cast<int>(gridDim.x);
       const int n = item / a.items_per_image;
@@ -158,9 +163,16 @@ __global__ void __launch_bounds__(kThreads, 1)
         if (ih >= 0 && ih < a.h) {
           const float4* src = reinterpret_cast<const float4*>(img + static_cast<long>(ih) * a.w) + t;
           const float4 c0 = __ldg(src), c1 = __ldg(src + (plane >> 2)), c2 = __ldg(src + 2 * (plane >> 2));
-          w0 = pack_low_bytes(calib_bits(c0.x, inv), calib_bits(c1.x, inv), calib_bits(c2.x, inv), calib_bits(c0.y, inv));
-          w1 = pack_low_bytes(calib_bits(c1.y, inv), calib_bits(c2.y, inv), calib_bits(c0.z, inv), calib_bits(c1.z, inv));
-          w2 = pack_low_bytes(calib_bits(c2.z, inv), calib_bits(c0.w, inv), calib_bits(c1.w, inv), calib_bits(c2.w, inv));
+          uint32_t b[12];  // pixel-major: (c0, c1, c2) of pixel 0, then pixel 1, ...
+          calib_bits2(c0.x, c1.x, inv2, b[0], b[1]);
+          calib_bits2(c2.x, c0.y, inv2, b[2], b[3]);
+          calib_bits2(c1.y, c2.y, inv2, b[4], b[5]);
+          calib_bits2(c0.z, c1.z, inv2, b[6], b[7]);
+          calib_bits2(c2.z, c0.w, inv2, b[8], b[9]);
+          calib_bits2(c1.w, c2.w, inv2, b[10], b[11]);
+          w0 = pack_low_bytes(b[0], b[1], b[2], b[3]);
+          w1 = pack_low_bytes(b[4], b[5], b[6], b[7]);
+          w2 = pack_low_bytes(b[8], b[9], b[10], b[11]);
         }
         const uint32_t d = rb0 + static_cast<uint32_t>((r * a.row_words + a.px0_word) * 4 + t * 12);
         sts32(d, w0);
@@ -192,24 +204,28 @@ __global__ void __launch_bounds__(kThreads, 1)
     const uint32_t ring = smem_u32(ring_smem);
     constexpr int kUpt = 128 * NWIN / kTileThreads;  // windows per thread and tile (2 or 4)
     constexpr int kPstep = kTileThreads / NWIN;      // pixels between a thread's consecutive windows
-    const int wv = tid % NWIN;                       // this thread's window: filter row pair j, row e of the pair
+    // Lane -> (pixel, window).  With 8 windows per pixel a quarter warp takes windows 0-3 (or 4-7) of an even and an
+    // odd pixel: its eight 16-byte stores then fall on eight different chunks of the swizzled 128-byte rows (the two
+    // K chunks of one pixel, 16 KB apart, would meet in the same banks).
+    const int pix0 = NWIN == 8 ? (tid >> 5) * 4 + ((lane >> 4) << 1) + ((lane >> 2) & 1) : tid / NWIN;
+    const int wv = NWIN == 8 ? ((lane >> 3) & 1) * 4 + (lane & 3) : tid % NWIN;  // filter row pair j, row e of the pair
     const int wj = wv / a.fold_h, we = wv - wj * a.fold_h;
     const int kch = wv >> 2, sub = wv & 3;
     bool ok = true;
-    int qseq = 0;
+    int stage = 0;
+    uint32_t empty_parity = 1;
     for (int k = 0; k < nb && ok; ++k) {
       const int b = k & 1;
       ok = mbar_wait(smem_u32(&rows_full[b]), (k >> 1) & 1, abort_flag, a.status, FAULT_WAIT_FULL);
       if (!ok) break;
       const uint32_t rb0 = smem_u32(rowbuf + b * rowbuf_words);
-      int py = 0, q = tid / NWIN;  // output row (inside the item) and column of this thread's next window
+      int py = 0, q = pix0;  // output row (inside the item) and column of this thread's next window
       while (q >= a.wo) {
         q -= a.wo;
         ++py;
       }
-      for (int t = 0; t < a.tiles_item && ok; ++t, ++qseq) {
-        const int stage = qseq % a.stages, use = qseq / a.stages;
-        ok = mbar_wait(smem_u32(&empty_bar[stage]), (use & 1) ^ 1, abort_flag, a.status, FAULT_WAIT_EMPTY);
+      for (int t = 0; t < a.tiles_item && ok; ++t) {
+        ok = mbar_wait(smem_u32(&empty_bar[stage]), empty_parity, abort_flag, a.status, FAULT_WAIT_EMPTY);
         if (!ok) break;
         const uint32_t tile = ring + static_cast<uint32_t>(stage * a.stage_bytes + kch * (128 * 128));
         uint32_t v[kUpt][9], shift[kUpt];
@@ -229,7 +245,7 @@ __global__ void __launch_bounds__(kThreads, 1)
         }
 #pragma unroll
         for (int i = 0; i < kUpt; ++i) {
-          const int m = tid / NWIN + i * kPstep;
+          const int m = pix0 + i * kPstep;
           uint32_t o[8];
 #pragma unroll
           for (int j = 0; j < 8; ++j) o[j] = __funnelshift_r(v[i][j], v[i][j + 1], shift[i]);
@@ -241,6 +257,10 @@ __global__ void __launch_bounds__(kThreads, 1)
         fence_proxy_async_smem();
         __syncwarp();
         if (lane == 0) mbar_arrive(smem_u32(&full_bar[stage]));
+        if (++stage == a.stages) {
+          stage = 0;
+          empty_parity ^= 1;
+        }
       }
       __syncwarp();
       if (lane == 0 && ok) mbar_arrive(smem_u32(&rows_empty[b]));  // the calib team may overwrite this buffer
@@ -300,14 +320,20 @@ __global__ void __launch_bounds__(kThreads, 1)
     const float ub = quant_upper_bound<ACT>(a.alpha);
     int sbuf = 0;
     bool ok = true;
-    for (int q = group; q < total_tiles && ok; q += kEpiGroups) {
-      const int buf = q % a.acc_bufs;
-      const uint32_t parity = static_cast<uint32_t>(q / a.acc_bufs) & 1u;
-      const int k = q / a.tiles_item, t = q - k * a.tiles_item;
-      const int item = static_cast<int>(blockIdx.x) + k * static_cast<int>(gridDim.x);
-      const int n = item / a.items_per_image;
-      const int p0 = (item - n * a.items_per_image) * a.rows_item;
-      const int row0 = (n * a.ho + p0) * a.wo + t * 128 + quad * 32;
+    // tile q of this CTA = tile t of its k-th item; the counters advance by one epilogue round (no divisions)
+    int buf = group % a.acc_bufs, t = group, item = static_cast<int>(blockIdx.x);
+    uint32_t parity = static_cast<uint32_t>(group / a.acc_bufs) & 1u;
+    for (int q = group; q < total_tiles && ok; q += kEpiGroups, buf += kEpiGroups, t += kEpiGroups) {
+      while (buf >= a.acc_bufs) {
+        buf -= a.acc_bufs;
+        parity ^= 1u;
+      }
+      while (t >= a.tiles_item) {
+        t -= a.tiles_item;
+        item += static_cast<int>(gridDim.x);
+      }
+      // an item is rows_item whole output rows of one image = tiles_item runs of 128 consecutive output pixels
+      const int row0 = (item * a.tiles_item + t) * 128 + quad * 32;
       ok = mbar_wait(smem_u32(&acc_full[buf]), parity, abort_flag, a.status, FAULT_WAIT_ACCUM);
       if (!ok) break;
       tc_fence_after();
