@@ -68,6 +68,8 @@ struct EpiParams {
   float alpha;          // already divided by out_s where the reference does so
   int acc_small = 0;    // 1: 128 * (largest sum of |w| over one output channel) < 2^22, so every accumulator is
                         // below 2^22 in magnitude and converts to float exactly through the mantissa trick
+  const float* h_scale = nullptr;  // host copies of scale / bias (or null): the one-launch first layer passes the
+  const float* h_bias = nullptr;   // tables inside its kernel arguments
 };
 
 #ifdef __CUDACC__

@@ -125,6 +125,7 @@ struct plb_conv {
   int cg_pad = 0;      // filter row length per tap
   DeviceBuf w;         // repacked filter
   DeviceBuf scale_f32, bias_f32, scale_i8, bias_i8;
+  std::vector<float> h_scale_i8, h_bias_i8;  // host copies of the int8-out tables (row-folded first layers only)
   float alpha_f32 = 0.f, alpha_i8 = 0.f;
   bool acc_small = false;  // 128 * max over channels of sum |w| < 2^22: accumulators convert to float exactly by the mantissa trick
   TcSwitches sw;           // tuning switches, read from the environment when the layer was prepared
@@ -364,6 +365,10 @@ int plb_conv_prepare(plb_ctx* ctx, const plb_conv_desc* desc, const int8_t* filt
   if ((rc = c->bias_f32.upload(f.bias_f32.data(), cb))) return rc;
   if ((rc = c->scale_i8.upload(f.scale_i8.data(), cb))) return rc;
   if ((rc = c->bias_i8.upload(f.bias_i8.data(), cb))) return rc;
+  if (c->fold) {  // the one-launch first layer takes its requantiser tables as kernel arguments
+    c->h_scale_i8 = f.scale_i8;
+    c->h_bias_i8 = f.bias_i8;
+  }
   c->alpha_f32 = f.alpha_f32;
   c->alpha_i8 = f.alpha_i8;
   *out = c.release();
@@ -469,6 +474,10 @@ OutSpec out_spec(const plb_conv* c, int mode, void* y) {
   if (mode == OUT_I8) {
     o.epi.scale = c->scale_i8.as<float>(); o.epi.bias = c->bias_i8.as<float>();
     o.epi.alpha = c->alpha_i8;
+    if (!c->h_scale_i8.empty()) {
+      o.epi.h_scale = c->h_scale_i8.data();
+      o.epi.h_bias = c->h_bias_i8.data();
+    }
   } else {
     o.epi.scale = c->scale_f32.as<float>(); o.epi.bias = c->bias_f32.as<float>();
     o.epi.alpha = c->alpha_f32;

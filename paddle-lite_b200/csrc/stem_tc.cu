@@ -57,8 +57,7 @@ struct StemArgs {
   int stages, stage_bytes;
   int cout, acc_cols, acc_bufs, b_bytes;
   float inv_scale;
-  const float* scale;
-  const float* bias;
+  float scale[64], bias[64];  // requantiser tables: kernel arguments, read as constant-bank operands (compile-time columns)
   float alpha;
   int acc_small;
   int* status;
@@ -342,28 +341,27 @@ __global__ void __launch_bounds__(kThreads, 1)
       if (lane == 0) bulk_wait_read_1();  // the store issued two tiles ago has finished reading this buffer
       __syncwarp();
       const uint32_t row = st + static_cast<uint32_t>(lane * wq);
-      for (int c = 0; c < a.cout; c += 32) {
-        uint32_t r[32];
-        tc_ld32(lane_addr + static_cast<uint32_t>(c), r);
-        tc_wait_ld();
-        const float4* sc4 = reinterpret_cast<const float4*>(a.scale + c);
-        const float4* bi4 = reinterpret_cast<const float4*>(a.bias + c);
-        const int chunk0 = c >> 4;
-#pragma unroll
-        for (int h = 0; h < 2; ++h) {
-          uint32_t v[4];
-          if (a.acc_small) {
-#pragma unroll
-            for (int j = 0; j < 4; ++j)
-              v[j] = quant4<ACT, true>(&r[16 * h + 4 * j], __ldg(sc4 + 4 * h + j), __ldg(bi4 + 4 * h + j), a.alpha, ub);
-          } else {
-#pragma unroll
-            for (int j = 0; j < 4; ++j)
-              v[j] = quant4<ACT, false>(&r[16 * h + 4 * j], __ldg(sc4 + 4 * h + j), __ldg(bi4 + 4 * h + j), a.alpha, ub);
-          }
-          sts128(row + (((chunk0 + h) ^ b_swz) << 4), v[0], v[1], v[2], v[3]);
-        }
-      }
+      // scale / bias of a compile-time column are constant-bank operands: no loads in this loop
+#define PLB_STEM_CHUNK(COL)                                                                                        \
+  if (COL < a.cout) {                                                                                              \
+    uint32_t r[32];                                                                                                \
+    tc_ld32(lane_addr + COL, r);                                                                                   \
+    tc_wait_ld();                                                                                                  \
+    _Pragma("unroll") for (int h = 0; h < 2; ++h) {                                                                \
+      uint32_t v[4];                                                                                               \
+      _Pragma("unroll") for (int j = 0; j < 4; ++j) {                                                              \
+        const int c0 = COL + 16 * h + 4 * j;                                                                       \
+        const float4 sc = make_float4(a.scale[c0], a.scale[c0 + 1], a.scale[c0 + 2], a.scale[c0 + 3]);             \
+        const float4 bi = make_float4(a.bias[c0], a.bias[c0 + 1], a.bias[c0 + 2], a.bias[c0 + 3]);                 \
+        v[j] = a.acc_small ? quant4<ACT, true>(&r[16 * h + 4 * j], sc, bi, a.alpha, ub)                            \
+                           : quant4<ACT, false>(&r[16 * h + 4 * j], sc, bi, a.alpha, ub);                          \
+      }                                                                                                            \
+      sts128(row + (((COL / 16 + h) ^ b_swz) << 4), v[0], v[1], v[2], v[3]);                                       \
+    }                                                                                                              \
+  }
+      PLB_STEM_CHUNK(0)
+      PLB_STEM_CHUNK(32)
+#undef PLB_STEM_CHUNK
       tc_fence_before();
       __syncwarp();
       if (lane == 0) mbar_arrive(smem_u32(&acc_empty[buf]));  // the accumulator is free before the store is issued
@@ -428,6 +426,7 @@ bool plan(const StemProblem& p, StemPlan* s, std::string* why) {
   if (p.cin != 3) return no("3 input channels only");
   if (p.w % 4 != 0 || (reinterpret_cast<uintptr_t>(p.x) & 15)) return no("image rows must be 16-byte aligned");
   if (p.cout != 32 && p.cout != 64) return no("32 or 64 output channels only");
+  if (p.epi.h_scale == nullptr || p.epi.h_bias == nullptr) return no("requantiser tables not available on the host");
   if (p.kw * p.cin > 32 || p.fold_h != p.stride_h || p.fold_h < 1) return no("filter row does not fit a 32-byte window");
   s->nwin = p.fold_kh * p.fold_h;
   if (s->nwin != 4 && s->nwin != 8) return no("4 or 8 windows per pixel only");
@@ -494,7 +493,9 @@ int stem_tc_launch(plb_ctx* ctx, const StemProblem& p) {
   a.acc_bufs = std::min(kMaxAccBufs, 512 / a.acc_cols);
   a.b_bytes = p.cout * s.k_bytes;
   a.inv_scale = 1.f / p.in_scale;
-  a.scale = p.epi.scale; a.bias = p.epi.bias; a.alpha = p.epi.alpha; a.acc_small = p.epi.acc_small;
+  memcpy(a.scale, p.epi.h_scale, sizeof(float) * p.cout);
+  memcpy(a.bias, p.epi.h_bias, sizeof(float) * p.cout);
+  a.alpha = p.epi.alpha; a.acc_small = p.epi.acc_small;
   a.status = ctx->d_status;
 
   CUtensorMap tmB, tmOut;
