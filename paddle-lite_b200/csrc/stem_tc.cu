@@ -145,6 +145,8 @@ __global__ void __launch_bounds__(kThreads, 1)
     const int w4 = a.w >> 2;
     const long plane = static_cast<long>(a.h) * a.w;
     const int total_units = a.rows_in * w4;
+    const int unit_r0 = tid / w4, unit_t0 = tid - unit_r0 * w4;
+    const int unit_dr = (32 * kCalibWarps) / w4, unit_dt = 32 * kCalibWarps - unit_dr * w4;
     const float2 inv2 = make_float2(a.inv_scale, a.inv_scale);
     for (int k = 0; k < nb; ++k) {
       const int item = static_cast<int>(blockIdx.x) + k * static_cast<int>(gridDim.x);
@@ -155,8 +157,9 @@ __global__ void __launch_bounds__(kThreads, 1)
       if (!mbar_wait(smem_u32(&rows_empty[b]), ((k >> 1) & 1) ^ 1, abort_flag, a.status, FAULT_WAIT_EMPTY)) break;
       const uint32_t rb0 = smem_u32(rowbuf + b * rowbuf_words);
       // a unit is 4 pixels of the three channels = 3 words; a thread takes units tid, tid + 256, ...
+      // (row r and position t of a unit advance by the quotient and remainder of the step: no division per unit)
+      int r = unit_r0, t = unit_t0;
       for (int u = tid; u < total_units; u += 32 * kCalibWarps) {
-        const int r = u / w4, t = u - r * w4;
         const int ih = ih0 + r;
         uint32_t w0 = 0, w1 = 0, w2 = 0;
         if (ih >= 0 && ih < a.h) {
@@ -177,6 +180,12 @@ __global__ void __launch_bounds__(kThreads, 1)
         sts32(d, w0);
         sts32(d + 4, w1);
         sts32(d + 8, w2);
+        r += unit_dr;
+        t += unit_dt;
+        if (t >= w4) {
+          t -= w4;
+          ++r;
+        }
       }
       __syncwarp();
       if (lane == 0) mbar_arrive(smem_u32(&rows_full[b]));
