@@ -34,7 +34,11 @@ constexpr int kEpiGroups = 3;
 constexpr int kEpiWarps = 4 * kEpiGroups;
 constexpr int kMmaWarp = kProdWarps + kEpiWarps;
 constexpr int kThreads = 32 * (kMmaWarp + 4);
-constexpr int kCalibRegs = 48, kEpiRegs = 88, kMmaRegs = 24;  // of the 64 per thread the CTA starts with (tile warps keep 64)
+// Registers per thread and role, of the 64 the CTA starts with (setmaxnreg: a role's warpgroups give registers back or
+// take more).  The MMA warp's loop is the pace maker of every tile: with 24 registers it spilled four of them.
+constexpr int kCalibRegs = 56, kTileRegs = 72, kEpiRegs = 64, kMmaRegs = 56;
+static_assert(32 * (kCalibWarps * kCalibRegs + kTileWarps * kTileRegs + kEpiWarps * kEpiRegs + 4 * kMmaRegs) <= 64 * kThreads,
+              "the roles together may not ask for more registers than the CTA was launched with: an increase would wait forever");
 constexpr int kMaxStages = 8;
 constexpr int kMaxAccBufs = 8;
 constexpr int kCtrlBytes = 1024;
@@ -70,6 +74,12 @@ __device__ __forceinline__ uint32_t lds32(uint32_t addr) {
   uint32_t v;
   asm volatile("ld.shared.b32 %0, [%1];" : "=r"(v) : "r"(addr));
   return v;
+}
+// All warps of a role's warpgroups: change the registers per thread from the launch value (64) to R.
+template <int R>
+__device__ __forceinline__ void role_registers() {
+  if (R > 64) asm volatile("setmaxnreg.inc.sync.aligned.u32 %0;" ::"n"(R));
+  if (R < 64) asm volatile("setmaxnreg.dec.sync.aligned.u32 %0;" ::"n"(R));
 }
 __device__ __forceinline__ void bulk_wait_read_1() { asm volatile("cp.async.bulk.wait_group.read 1;" ::: "memory"); }
 
@@ -140,7 +150,7 @@ __global__ void __launch_bounds__(kThreads, 1)
   if (warp < kCalibWarps) {
     // ---------------------------------------------------------------------------------------------- calib team
     // fp32 image rows of item k -> [pixel][channel] bytes in row buffer k & 1, one item ahead of the tile team.
-    asm volatile("setmaxnreg.dec.sync.aligned.u32 %0;" ::"n"(kCalibRegs));
+    role_registers<kCalibRegs>();
     const int tid = threadIdx.x;
     const int w4 = a.w >> 2;
     const long plane = static_cast<long>(a.h) * a.w;
@@ -208,6 +218,7 @@ __global__ void __launch_bounds__(kThreads, 1)
   } else if (warp < kProdWarps) {
     // ---------------------------------------------------------------------------------------------- tile team
     // For every output pixel the NWIN windows of 32 bytes, word-unaligned in the row buffers, into the operand tile.
+    role_registers<kTileRegs>();
     const int tid = threadIdx.x - 32 * kCalibWarps;
     const uint32_t ring = smem_u32(ring_smem);
     constexpr int kUpt = 128 * NWIN / kTileThreads;  // windows per thread and tile (2 or 4)
@@ -274,7 +285,7 @@ __global__ void __launch_bounds__(kThreads, 1)
       if (lane == 0 && ok) mbar_arrive(smem_u32(&rows_empty[b]));  // the calib team may overwrite this buffer
     }
   } else if (warp >= kMmaWarp) {
-    asm volatile("setmaxnreg.dec.sync.aligned.u32 %0;" ::"n"(kMmaRegs));
+    role_registers<kMmaRegs>();
     if (warp == kMmaWarp) {
       // -------------------------------------------------------------------------------------------- MMA issue
       const bool leader = elect_one();
@@ -319,7 +330,7 @@ __global__ void __launch_bounds__(kThreads, 1)
     }
   } else {
     // ---------------------------------------------------------------------------------------------- epilogue
-    asm volatile("setmaxnreg.inc.sync.aligned.u32 %0;" ::"n"(kEpiRegs));
+    role_registers<kEpiRegs>();
     const int e = warp - kProdWarps;
     const int quad = e & 3, group = e >> 2;
     const int wq = a.cout;  // bytes of a staged pixel row (32 or 64)
