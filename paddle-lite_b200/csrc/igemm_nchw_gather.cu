@@ -31,7 +31,7 @@ constexpr int kGatherWarp0 = kEpilogueWarps;
 constexpr int kProducerWarp = kEpilogueWarps + kGatherWarps;
 constexpr int kMmaWarp = kProducerWarp + 1;
 constexpr int kThreads = 32 * (kEpilogueWarps + kGatherWarps + 4);
-constexpr int kEpiRegs = 88, kGatherRegs = 56, kCtrlRegs = 40;  // of the 72 per thread the CTA starts with
+constexpr int kEpiRegs = 80, kGatherRegs = 64, kCtrlRegs = 56;  // of the 72 per thread the CTA starts with
 constexpr int kMaxStages = 8;
 constexpr int kCtrlBytes = 1024;
 constexpr int kStagePitch = 80;                                  // bytes between rows of an epilogue staging tile (64 + 16)
