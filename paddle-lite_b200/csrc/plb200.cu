@@ -124,6 +124,7 @@ struct plb_conv {
   int cin_pad = 0;     // channel stride of the NHWC staging input
   int cg_pad = 0;      // filter row length per tap
   DeviceBuf w;         // repacked filter
+  DeviceBuf w16;       // first layers with filter rows of at most 16 bytes: the folded filter with 16-byte rows
   DeviceBuf scale_f32, bias_f32, scale_i8, bias_i8;
   std::vector<float> h_scale_i8, h_bias_i8;  // host copies of the int8-out tables (row-folded first layers only)
   float alpha_f32 = 0.f, alpha_i8 = 0.f;
@@ -291,7 +292,7 @@ int plb_conv_prepare(plb_ctx* ctx, const plb_conv_desc* desc, const int8_t* filt
     }
     c->acc_small = worst * 128 < (1L << 22);
   }
-  std::vector<int8_t> packed;
+  std::vector<int8_t> packed, packed16;
   if (depthwise && d.impl != PLB_IMPL_TC) {
     c->kind = 2;
     c->cin_pad = static_cast<int>(align_up(d.cin, 16));
@@ -318,6 +319,16 @@ int plb_conv_prepare(plb_ctx* ctx, const plb_conv_desc* desc, const int8_t* filt
           for (int sx = 0; sx < d.kw; ++sx)
             packed[(static_cast<size_t>(co) * c->fold_kh + r / c->fold_h) * c->cin_pad + (r % c->fold_h) * 32 +
                    sx * d.cin + ci] = filter_h[((static_cast<size_t>(co) * d.cin + ci) * d.kh + r) * d.kw + sx];
+    if (d.cin * d.kw <= 16 && c->fold_kh * c->fold_h == 4) {
+      // the same filter with 16-byte rows, [cout][r][s*cin + ci], for the one-launch first layer (stem_tc.cu)
+      packed16.assign(static_cast<size_t>(d.cout) * 4 * 16, 0);
+      for (int co = 0; co < d.cout; ++co)
+        for (int ci = 0; ci < d.cin; ++ci)
+          for (int r = 0; r < d.kh; ++r)
+            for (int sx = 0; sx < d.kw; ++sx)
+              packed16[(static_cast<size_t>(co) * 4 + r) * 16 + sx * d.cin + ci] =
+                  filter_h[((static_cast<size_t>(co) * d.cin + ci) * d.kh + r) * d.kw + sx];
+    }
   } else if (d.groups == 1) {
     c->cin_pad = static_cast<int>(align_up(d.cin, 32));
     c->cg_pad = c->cin_pad;
@@ -358,6 +369,7 @@ int plb_conv_prepare(plb_ctx* ctx, const plb_conv_desc* desc, const int8_t* filt
   }
   int rc = c->w.upload(packed.data(), packed.size());
   if (rc) return rc;
+  if (!packed16.empty() && (rc = c->w16.upload(packed16.data(), packed16.size()))) return rc;
   Folded f = fold(d.cout, wscale_h, n_wscale, bias_h, d.in_scale,
                   d.out_dtype == PLB_OUT_I8 ? d.out_scale : 1.f, d.act, d.act_alpha, d.leaky_compat);
   const size_t cb = sizeof(float) * d.cout;
@@ -664,7 +676,7 @@ int plb_conv_run_image_f32(plb_conv* conv, const float* x, void* y, int batch) {
     sp.x = x; sp.batch = batch; sp.cin = d.cin; sp.h = d.h; sp.w = d.w;
     sp.kh = d.kh; sp.kw = d.kw; sp.stride_h = d.stride_h; sp.stride_w = d.stride_w; sp.pad_t = d.pad_top; sp.pad_l = d.pad_left;
     sp.ho = conv->ho; sp.wo = conv->wo; sp.fold_h = conv->fold_h; sp.fold_kh = conv->fold_kh;
-    sp.wfold = conv->w.as<int8_t>(); sp.cout = d.cout; sp.in_scale = d.in_scale;
+    sp.wfold = conv->w.as<int8_t>(); sp.wfold16 = conv->w16.as<int8_t>(); sp.cout = d.cout; sp.in_scale = d.in_scale;
     sp.epi = out_spec(conv, OUT_I8, y).epi;
     sp.y = static_cast<int8_t*>(y);
     if (stem_tc_supported(ctx, sp, nullptr)) return stem_tc_launch(ctx, sp);

@@ -3,7 +3,8 @@
 // and then im2col + GEMM (lite/kernels/x86/conv_compute.cc:292-341); here the calib, the im2col and the GEMM operand
 // never reach memory: producer warps quantise the image rows a work item needs into shared memory (pixels x channels
 // interleaved, zero padding in place), copy for every output pixel the 32-byte windows of the row-folded layout
-// ([filter row pair j][row e of the pair][kw taps x 3 channels, padded to 32 bytes]) into the swizzled K-major operand
+// ([filter row pair j][row e of the pair][kw taps x 3 channels, padded to 32 bytes, or to 16 where a filter row has at
+// most 16 bytes and a pixel 4 windows: 3x3 on RGB]) into the swizzled K-major operand
 // tile, tcgen05.mma multiplies by the resident folded filter, and 16 epilogue warps requantise and store through TMA.
 // Same arithmetic as the staged path (fold_rows + implicit GEMM), bit for bit: exact int32 sums of the same products.
 //
@@ -57,7 +58,8 @@ struct StemArgs {
   int rows_item;      // output rows per work item (R)
   int tiles_item;     // R * wo / 128
   int items_per_image, total_items;
-  int kchunks;        // K / 128
+  int kchunks;        // K / row_bytes
+  int row_bytes;      // bytes of K per operand-tile row: 128 (32-byte windows) or 64 (16-byte windows, 4 per pixel)
   int stages, stage_bytes;
   int cout, acc_cols, acc_bufs, b_bytes;
   float inv_scale;
@@ -93,7 +95,7 @@ __device__ __forceinline__ void calib_bits2(float x, float y, float2 inv2, uint3
   by = __float_as_uint(r.y);
 }
 
-template <int ACT, int NWIN>
+template <int ACT, int NWIN, int WB>
 __global__ void __launch_bounds__(kThreads, 1)
     stem_tc_kernel(const __grid_constant__ CUtensorMap tmB, const __grid_constant__ CUtensorMap tmOut, const StemArgs a) {
   extern __shared__ uint8_t smem_raw[];
@@ -217,7 +219,9 @@ __global__ void __launch_bounds__(kThreads, 1)
     }
   } else if (warp < kProdWarps) {
     // ---------------------------------------------------------------------------------------------- tile team
-    // For every output pixel the NWIN windows of 32 bytes, word-unaligned in the row buffers, into the operand tile.
+    // For every output pixel the NWIN windows of WB (32 or 16) bytes, word-unaligned in the row buffers, into the
+    // operand tile.  16-byte windows (a filter row of at most 16 bytes, 4 windows per pixel) make rows of 64 bytes with
+    // the 64-byte swizzle: half the stores, loads and MMAs of the 32-byte form.
     role_registers<kTileRegs>();
     const int tid = threadIdx.x - 32 * kCalibWarps;
     const uint32_t ring = smem_u32(ring_smem);
@@ -247,7 +251,8 @@ __global__ void __launch_bounds__(kThreads, 1)
         ok = mbar_wait(smem_u32(&empty_bar[stage]), empty_parity, abort_flag, a.status, FAULT_WAIT_EMPTY);
         if (!ok) break;
         const uint32_t tile = ring + static_cast<uint32_t>(stage * a.stage_bytes + kch * (128 * 128));
-        uint32_t v[kUpt][9], shift[kUpt];
+        constexpr int kWords = WB / 4;
+        uint32_t v[kUpt][kWords + 1], shift[kUpt];
 #pragma unroll
         for (int i = 0; i < kUpt; ++i) {
           const int rb = (py + wj) * a.fold_h + we;
@@ -255,7 +260,7 @@ __global__ void __launch_bounds__(kThreads, 1)
           const uint32_t sa = rb0 + static_cast<uint32_t>((rb * a.row_words + (src >> 2)) * 4);
           shift[i] = static_cast<uint32_t>(src & 3) * 8;
 #pragma unroll
-          for (int j = 0; j < 9; ++j) v[i][j] = lds32(sa + 4 * j);
+          for (int j = 0; j <= kWords; ++j) v[i][j] = lds32(sa + 4 * j);
           q += kPstep;
           while (q >= a.wo) {
             q -= a.wo;
@@ -265,13 +270,20 @@ __global__ void __launch_bounds__(kThreads, 1)
 #pragma unroll
         for (int i = 0; i < kUpt; ++i) {
           const int m = pix0 + i * kPstep;
-          uint32_t o[8];
+          uint32_t o[kWords];
 #pragma unroll
-          for (int j = 0; j < 8; ++j) o[j] = __funnelshift_r(v[i][j], v[i][j + 1], shift[i]);
-          const uint32_t row = tile + static_cast<uint32_t>(m * 128);
-          const int sw = m & 7;
-          sts128(row + (((sub * 2) ^ sw) << 4), o[0], o[1], o[2], o[3]);
-          sts128(row + (((sub * 2 + 1) ^ sw) << 4), o[4], o[5], o[6], o[7]);
+          for (int j = 0; j < kWords; ++j) o[j] = __funnelshift_r(v[i][j], v[i][j + 1], shift[i]);
+          if (WB == 32) {
+            const uint32_t row = tile + static_cast<uint32_t>(m * 128);
+            const int sw = m & 7;
+            sts128(row + (((sub * 2) ^ sw) << 4), o[0], o[1], o[2], o[3]);
+            sts128(row + (((sub * 2 + 1) ^ sw) << 4), o[kWords - 4], o[kWords - 3], o[kWords - 2], o[kWords - 1]);
+          } else {
+            // rows of 64 bytes, 64-byte swizzle: chunk j of row m lives at j ^ ((m >> 1) & 3); a quarter warp (an even
+            // and an odd pixel x 4 windows) covers one 128-byte line
+            const uint32_t row = tile + static_cast<uint32_t>(m * 64);
+            sts128(row + ((wv ^ ((m >> 1) & 3)) << 4), o[0], o[1], o[2], o[3]);
+          }
         }
         fence_proxy_async_smem();
         __syncwarp();
@@ -291,9 +303,10 @@ __global__ void __launch_bounds__(kThreads, 1)
       const bool leader = elect_one();
       mbar_expect_tx_if(smem_u32(b_bar), static_cast<uint32_t>(a.b_bytes), leader);
       for (int kc = 0; kc < a.kchunks; ++kc)
-        tma_load_2d_if(smem_u32(b_smem) + static_cast<uint32_t>(kc * a.cout * 128), &tmB, smem_u32(b_bar), kc * 128, 0, leader);
+        tma_load_2d_if(smem_u32(b_smem) + static_cast<uint32_t>(kc * a.cout * a.row_bytes), &tmB, smem_u32(b_bar),
+                       kc * a.row_bytes, 0, leader);
       bool ok = mbar_wait(smem_u32(b_bar), 0, abort_flag, a.status, FAULT_WAIT_FULL);
-      const uint32_t hi = static_cast<uint32_t>(make_smem_desc(0, 128) >> 32);
+      const uint32_t hi = static_cast<uint32_t>(make_smem_desc(0, WB == 32 ? 128 : 64) >> 32);
       const uint32_t ring_lo = ((smem_u32(ring_smem) >> 4) & 0x3FFFu) | (1u << 16);
       const uint32_t b_lo0 = ((smem_u32(b_smem) >> 4) & 0x3FFFu) | (1u << 16);
       // D = s32, A = B = s8, both K-major, M = 128, N = cout
@@ -310,10 +323,10 @@ __global__ void __launch_bounds__(kThreads, 1)
         const uint32_t a_lo = ring_lo + static_cast<uint32_t>((stage * a.stage_bytes) >> 4);
         const uint32_t d_tmem = tmem_base + static_cast<uint32_t>(buf * a.acc_cols);
         for (int kc = 0; kc < a.kchunks; ++kc) {
-          const uint32_t a_k = a_lo + static_cast<uint32_t>((kc * 128 * 128) >> 4);
-          const uint32_t b_k = b_lo0 + static_cast<uint32_t>((kc * a.cout * 128) >> 4);
+          const uint32_t a_k = a_lo + static_cast<uint32_t>((kc * 128 * a.row_bytes) >> 4);
+          const uint32_t b_k = b_lo0 + static_cast<uint32_t>((kc * a.cout * a.row_bytes) >> 4);
 #pragma unroll
-          for (int j = 0; j < 4; ++j) tc_mma_i8_halves(d_tmem, a_k + 2u * j, hi, b_k + 2u * j, hi, idesc, (kc | j) ? 1u : 0u, leader);
+          for (int j = 0; j < (WB == 32 ? 4 : 2); ++j) tc_mma_i8_halves(d_tmem, a_k + 2u * j, hi, b_k + 2u * j, hi, idesc, (kc | j) ? 1u : 0u, leader);
         }
         tc_commit_if(smem_u32(&empty_bar[stage]), leader);
         tc_commit_if(smem_u32(&acc_full[buf]), leader);
@@ -405,16 +418,19 @@ __global__ void __launch_bounds__(kThreads, 1)
 }
 
 typedef void (*StemKernel)(const CUtensorMap, const CUtensorMap, const StemArgs);
-template <int NWIN>
+template <int NWIN, int WB>
 StemKernel pick_act(int act) {
   switch (act) {
-    case PLB_ACT_RELU: return stem_tc_kernel<PLB_ACT_RELU, NWIN>;
-    case PLB_ACT_RELU6: return stem_tc_kernel<PLB_ACT_RELU6, NWIN>;
-    case PLB_ACT_LEAKY: return stem_tc_kernel<PLB_ACT_LEAKY, NWIN>;
-    default: return stem_tc_kernel<PLB_ACT_NONE, NWIN>;
+    case PLB_ACT_RELU: return stem_tc_kernel<PLB_ACT_RELU, NWIN, WB>;
+    case PLB_ACT_RELU6: return stem_tc_kernel<PLB_ACT_RELU6, NWIN, WB>;
+    case PLB_ACT_LEAKY: return stem_tc_kernel<PLB_ACT_LEAKY, NWIN, WB>;
+    default: return stem_tc_kernel<PLB_ACT_NONE, NWIN, WB>;
   }
 }
-StemKernel pick_kernel(int act, int nwin) { return nwin == 8 ? pick_act<8>(act) : pick_act<4>(act); }
+StemKernel pick_kernel(int act, int nwin, int wb) {
+  if (nwin == 8) return pick_act<8, 32>(act);
+  return wb == 16 ? pick_act<4, 16>(act) : pick_act<4, 32>(act);
+}
 
 typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
                                   const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
@@ -434,7 +450,7 @@ int load_encoder() {
 }
 
 struct StemPlan {
-  int rows_item, tiles_item, rows_in, row_words, px0_word, base_off, nwin, k_bytes, stages;
+  int rows_item, tiles_item, rows_in, row_words, px0_word, base_off, nwin, win_bytes, k_bytes, stages;
   size_t smem;
 };
 
@@ -450,7 +466,9 @@ bool plan(const StemProblem& p, StemPlan* s, std::string* why) {
   if (p.kw * p.cin > 32 || p.fold_h != p.stride_h || p.fold_h < 1) return no("filter row does not fit a 32-byte window");
   s->nwin = p.fold_kh * p.fold_h;
   if (s->nwin != 4 && s->nwin != 8) return no("4 or 8 windows per pixel only");
-  s->k_bytes = s->nwin * 32;
+  // a filter row of at most 16 bytes (3x3 on RGB: 9) in 4 windows: 16-byte windows, K = 64, where the layer has that filter form
+  s->win_bytes = (s->nwin == 4 && p.kw * p.cin <= 16 && p.wfold16 != nullptr && (reinterpret_cast<uintptr_t>(p.wfold16) & 15) == 0) ? 16 : 32;
+  s->k_bytes = s->nwin * s->win_bytes;
   // output rows per item: the fewest whose pixels fill whole 128-pixel tiles
   int g = 128, b = p.wo;
   while (b) {
@@ -505,7 +523,8 @@ int stem_tc_launch(plb_ctx* ctx, const StemProblem& p) {
   const long items = static_cast<long>(p.batch) * a.items_per_image;
   if (items > 0x3fffffff || static_cast<long>(p.batch) * p.ho * p.wo > 0x7fffffffL) return fail(PLB_E_UNSUPPORTED, "batch too large");
   a.total_items = static_cast<int>(items);
-  a.kchunks = s.k_bytes / 128;
+  a.row_bytes = std::min(128, s.k_bytes);
+  a.kchunks = s.k_bytes / a.row_bytes;
   a.stages = s.stages;
   a.stage_bytes = 128 * s.k_bytes;
   a.cout = p.cout;
@@ -522,11 +541,12 @@ int stem_tc_launch(plb_ctx* ctx, const StemProblem& p) {
   {
     const cuuint64_t dims[2] = {static_cast<cuuint64_t>(s.k_bytes), static_cast<cuuint64_t>(p.cout)};
     const cuuint64_t strides[1] = {static_cast<cuuint64_t>(s.k_bytes)};
-    const cuuint32_t box[2] = {128, static_cast<cuuint32_t>(p.cout)};
+    const cuuint32_t box[2] = {static_cast<cuuint32_t>(a.row_bytes), static_cast<cuuint32_t>(p.cout)};
     const cuuint32_t es[2] = {1, 1};
-    CUresult r = g_tiled(&tmB, CU_TENSOR_MAP_DATA_TYPE_UINT8, 2, const_cast<int8_t*>(p.wfold), dims, strides, box, es,
-                         CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
-                         CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    const int8_t* wf = s.win_bytes == 16 ? p.wfold16 : p.wfold;
+    CUresult r = g_tiled(&tmB, CU_TENSOR_MAP_DATA_TYPE_UINT8, 2, const_cast<int8_t*>(wf), dims, strides, box, es,
+                         CU_TENSOR_MAP_INTERLEAVE_NONE, a.row_bytes == 128 ? CU_TENSOR_MAP_SWIZZLE_128B : CU_TENSOR_MAP_SWIZZLE_64B,
+                         CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
     if (r != CUDA_SUCCESS) return fail(PLB_E_CUDA, "tensor map of the folded filter: error %d", static_cast<int>(r));
   }
   {
@@ -539,7 +559,7 @@ int stem_tc_launch(plb_ctx* ctx, const StemProblem& p) {
                          CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
     if (r != CUDA_SUCCESS) return fail(PLB_E_CUDA, "tensor map of the output: error %d", static_cast<int>(r));
   }
-  StemKernel kernel = pick_kernel(p.epi.act, s.nwin);
+  StemKernel kernel = pick_kernel(p.epi.act, s.nwin, s.win_bytes);
   {
     // once per (kernel, device)
     static std::mutex attr_mutex;

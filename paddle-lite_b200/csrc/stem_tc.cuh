@@ -12,6 +12,7 @@ struct StemProblem {
   int ho, wo;
   int fold_h, fold_kh;  // input rows per folded row group (= stride_h), filter row groups
   const int8_t* wfold;  // [cout][fold_kh][fold_h * 32] int8, the layer's row-folded filter
+  const int8_t* wfold16;  // [cout][fold_kh * fold_h][16] int8 or null: the same filter with 16-byte rows (kw * cin <= 16)
   int cout;
   float in_scale;
   EpiParams epi;        // int8 requantiser
