@@ -445,6 +445,9 @@ def test_image_entry(plb, ctx, cin, k, s, p, hw):
     (7, 2, 3, 64, (128, 256), 2, 2, 6.0),    # one output row = one tile
     (7, 2, 3, 32, (96, 64), 4, 0, 0.0),      # four output rows per item, 32-pixel rows
     (3, 2, 1, 64, (160, 224), 150, 3, 0.1),  # more work items than SMs: several items per CTA, ragged last round
+    (4, 2, 1, 32, (64, 128), 3, 1, 0.0),     # 4x4: all four 16-byte windows of a pixel carry filter taps
+    (3, 2, 1, 32, (96, 64), 4, 2, 6.0),      # 16-byte windows, four output rows per item
+    (8, 2, 3, 64, (64, 128), 2, 1, 0.0),     # 8x8: all eight 32-byte windows carry filter taps
 ])
 def test_one_launch_stem(plb, ctx, k, s, p, cout, hw, n, act, alpha, monkeypatch):
     """First layer from the fp32 image in one launch (calib, row folding and GEMM operand never reach memory):
