@@ -5,7 +5,7 @@
 // interleaved, zero padding in place), copy for every output pixel the 32-byte windows of the row-folded layout
 // ([filter row pair j][row e of the pair][kw taps x 3 channels, padded to 32 bytes, or to 16 where a filter row has at
 // most 16 bytes and a pixel 4 windows: 3x3 on RGB]) into the swizzled K-major operand
-// tile, tcgen05.mma multiplies by the resident folded filter, and 16 epilogue warps requantise and store through TMA.
+// tile, tcgen05.mma multiplies by the resident folded filter, and 12 epilogue warps requantise and store through TMA.
 // Same arithmetic as the staged path (fold_rows + implicit GEMM), bit for bit: exact int32 sums of the same products.
 //
 // A work item is R output rows of one image with R * wo a multiple of 128 (8 rows of 112 pixels = 7 tiles), so tiles are
